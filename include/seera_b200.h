@@ -1,0 +1,200 @@
+/* seera_b200.h - C ABI of the B200-native Seera training engine.
+ *
+ * Drop-in boundary for the reference's GPU engine: every entry of the reference's
+ * `seera_cuda` namespace (engine_cuda/include/seera_engine_cuda.hpp:9-123) and every
+ * memory/transfer lambda of its Python binding (engine_cuda/src/cuda_bindings.cpp:23-170)
+ * has a function here with the same name (prefixed `seera_`), the same argument order and
+ * the same meaning.  Plain pointers and sizes only; all tensor pointers are device
+ * addresses of dense, C-contiguous buffers (fp32 unless stated; activations NCHW).
+ *
+ * Differences from the reference that a caller can observe:
+ *   - every function returns an int status: 0 = ok, otherwise a SEERA_E_* code;
+ *     seera_last_error() gives the text.  The reference returns void and drops errors.
+ *   - calls ENQUEUE work on the engine's stream and return; results are complete after
+ *     seera_synchronize() or any seera_to_host_* call.  The reference blocks in every call.
+ *   - max-pool writes cuda_maxpool_fwd's mask as the window-local argmax index kh*KW+kw of
+ *     the first strict maximum (the reference CPU engine's rule, engine/src/pool_ops.cpp:21-38)
+ *     in the first N*C*OH*OW ints of the caller's N*C*H*W-int buffer; cuda_maxpool_bwd reads
+ *     that encoding.  When OH*OW > H*W (stride-1 pooling with padding) the buffer is too small
+ *     and the call fails with SEERA_E_ARG.
+ *   - argmax/argmin return the FIRST extremal index (NumPy's rule); the reference GPU kernel
+ *     returns the last (engine_cuda/src/reductionKernels.cu:81,104).
+ *
+ * Not thread-safe: one host thread drives one device, as in the reference.
+ */
+#ifndef SEERA_B200_H
+#define SEERA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    SEERA_OK = 0,
+    SEERA_E_CUDA = 1,     /* a CUDA runtime call failed (sticky)            */
+    SEERA_E_ARG = 2,      /* bad size / shape / null pointer                */
+    SEERA_E_OOM = 3,      /* device allocation failed                       */
+    SEERA_E_DEVICE = 4,   /* a kernel reported a status word != 0           */
+    SEERA_E_LIMIT = 5     /* size beyond a documented maximum               */
+};
+
+/* ---- runtime ------------------------------------------------------------------ */
+int         seera_init(int device);                 /* selects the device, creates the stream; idempotent */
+int         seera_synchronize(void);                /* waits for the engine's stream                     */
+int         seera_set_stream(void *cuda_stream);    /* adopt an external cudaStream_t (NULL = own stream) */
+void       *seera_get_stream(void);
+const char *seera_last_error(void);
+int         seera_last_status(void);                /* last non-zero status since seera_clear_status()   */
+void        seera_clear_status(void);
+uint64_t    seera_launch_count(void);               /* kernels launched by this library so far           */
+int         seera_device_sm_count(void);
+/* Precision of the GEMM / convolution contractions:
+ *   0 fp32 CUDA-core tiles (bit-for-bit fp32 products, default for the fp32 configurations)
+ *   1 bf16 operands, fp32 accumulate on the tensor cores (one pass)
+ *   2 bf16x3: a_hi*b_hi + a_hi*b_lo + a_lo*b_hi on the tensor cores (fp32-class accuracy) */
+int         seera_set_precision(int mode);
+int         seera_get_precision(void);
+
+/* ---- memory (cuda_bindings.cpp:23-66) ----------------------------------------------- */
+void *seera_cuda_malloc(size_t n_bytes);            /* :23  pooled, stream-ordered; NULL on failure */
+void *seera_cuda_malloc_f32(int n_elements);        /* :37 (and cuda_malloc_f16 :30, same size)     */
+void *seera_cuda_malloc_i32(int n_elements);        /* :44 */
+void *seera_cuda_malloc_i16(int n_elements);        /* :51 */
+int   seera_cuda_free(void *ptr);                   /* :58  returns the block to the pool           */
+int   seera_cuda_memcopy_devicetodevice(void *dst, const void *src, int num_elem); /* :61 counts FLOAT elements */
+int   seera_cuda_memset(void *ptr, int value, size_t n_bytes);                     /* :65 */
+int   seera_pool_trim(void);                        /* releases cached blocks to the driver         */
+size_t seera_pool_bytes_reserved(void);
+void *seera_host_alloc_pinned(size_t n_bytes);      /* page-locked staging for callers that time H2D */
+int   seera_host_free_pinned(void *p);
+
+/* ---- transfers (cuda_bindings.cpp:73-170) ------------------------------------------------ */
+void *seera_to_device(const void *host, size_t n_bytes);              /* :98,:155,:164 allocate + upload */
+int   seera_upload(void *dev, const void *host, size_t n_bytes);      /* upload into an existing buffer  */
+int   seera_to_host(void *host, const void *dev, size_t n_bytes);     /* :107,:123,:139 download + sync  */
+
+/* ---- unary ops: out = f(x), grad = f'(x)   (seera_engine_cuda.hpp:9-25) -------------------- */
+int seera_cuda_relu_fwd(const float *x, float *out, float *grad, int size);
+int seera_cuda_sigmoid_fwd(const float *x, float *out, float *grad, int size);
+int seera_cuda_tanh_fwd(const float *x, float *out, float *grad, int size);
+int seera_cuda_log_fwd(const float *x, float *out, float *grad, int size);
+int seera_cuda_exp_fwd(const float *x, float *out, float *grad, int size);
+int seera_cuda_abs_fwd(const float *x, float *out, float *grad, int size);
+int seera_cuda_sqrt_fwd(const float *x, float *out, float *grad, int size);
+int seera_cuda_pow_fwd(const float *x, float exponent, float *out, float *grad, int size);
+int seera_cuda_clip_fwd(const float *x, float lo, float hi, float *out, float *grad, int size);
+
+/* ---- softmax over the last axis (seera_engine_cuda.hpp:27-29) ------------------------------ */
+int seera_cuda_softmax_fwd(const float *x, float *out, int N, int C);
+int seera_cuda_softmax_vjp(const float *s, const float *dout, float *dx, int N, int C);
+
+/* ---- GEMM (seera_engine_cuda.hpp:40-44) ------------------------------------------------------
+ * cuda_matmul:      C[b,M,N] = A[b,M,K] * B[K,N]           (B shared by all batches)
+ * cuda_matmul_bwd:  dA[b,M,K] = dC[b,M,N] * B^T ;  dB[K,N] = sum_b A[b]^T * dC[b]            */
+int seera_cuda_matmul(const float *A, const float *B, float *C, int M, int N, int K, int Nbatch);
+int seera_cuda_matmul_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB,
+                          int M, int N, int K, int Nbatch);
+int seera_cuda_transpose_2d(const float *in, float *out, int rows, int cols);
+int seera_cuda_transpose_3d(const float *in, float *out, int Nbatch, int M, int K);
+
+/* ---- Conv2D (seera_engine_cuda.hpp:31-38)  X[N,C,H,W], W[F,C,R,S], Y[N,F,OH,OW] --------------
+ * note the argument order: fwd takes pad before stride, bwd takes stride before pad.          */
+int seera_cuda_conv2d_fwd(const float *image, const float *kernel, float *out,
+                          int batchN, int C, int H, int W, int F, int R, int S,
+                          int pad_h, int pad_w, int stride_h, int stride_w);
+int seera_cuda_conv2d_bwd(const float *W, const float *X, const float *dY, float *dX, float *dW,
+                          int batch, int C, int H, int W_in, int F, int R, int S,
+                          int strideh, int stridew, int padh, int padw);
+
+/* ---- ConvTranspose2D (seera_engine_cuda.hpp:45-53)  X[N,Cin,H,W], W[Cin,Cout,KH,KW] ----------
+ * Hout = (H-1)*stride - 2*pad + KH                                                             */
+int seera_cuda_conv2DTranpose_fwd(const float *X, const float *W, float *out, int batch,
+                                  int Cin, int Hin, int Win, int Cout, int KH, int KW,
+                                  int strideh, int stridew, int padh, int padw);
+int seera_cuda_conv2DTranspose_bwd(const float *W, const float *X, const float *dY, float *dX, float *dW,
+                                   int batch, int Cin, int Hin, int Win, int Cout, int KH, int KW,
+                                   int strideh, int stridew, int padh, int padw);
+
+/* ---- pooling (seera_engine_cuda.hpp:55-71) ---------------------------------------------------- */
+int seera_cuda_maxpool_fwd(const float *image, float *out, int *mask, int batchN, int C, int H, int W,
+                           int R, int S, int pad_h, int pad_w, int stride_h, int stride_w);
+int seera_cuda_maxpool_bwd(const float *dout, const int *mask, float *dX, int batchN, int C, int H, int W,
+                           int R, int S, int pad_h, int pad_w, int stride_h, int stride_w);
+int seera_cuda_unpooling_fwd(const float *inp, float *out, int batchN, int C, int H, int W, int sh, int sw);
+int seera_cuda_unpooling_bwd(const float *dout, float *dx, int batchN, int C, int H, int W, int sh, int sw);
+
+/* ---- single-axis reductions (seera_engine_cuda.hpp:72-95); dimarr is a HOST array of ndims ints -- */
+int seera_cuda_sum_fwd(const float *A, float *out, int ndims, int dim, const int *dimarr);
+int seera_cuda_mean_fwd(const float *A, float *out, int ndims, int dim, const int *dimarr);
+int seera_cuda_max_fwd(const float *A, float *out, int ndims, int dim, const int *dimarr);
+int seera_cuda_min_fwd(const float *A, float *out, int ndims, int dim, const int *dimarr);
+int seera_cuda_argmax_fwd(const float *A, int *out, int ndims, int dim, const int *dimarr);
+int seera_cuda_argmin_fwd(const float *A, int *out, int ndims, int dim, const int *dimarr);
+int seera_cuda_sum_bwd(const float *dOut, float *dA, int ndims, int dim, const int *dimarr);
+int seera_cuda_mean_bwd(const float *dOut, float *dA, int ndims, int dim, const int *dimarr);
+int seera_cuda_max_bwd(const float *dOut, const float *fwdInput, const float *fwdOutput, float *dA,
+                       int ndims, int dim, const int *dimarr);   /* adds into dA (caller zero-fills) */
+int seera_cuda_min_bwd(const float *dOut, const float *fwdInput, const float *fwdOutput, float *dA,
+                       int ndims, int dim, const int *dimarr);
+
+/* ---- in-place scalar ops and fills (seera_engine_cuda.hpp:97-108) ------------------------------- */
+int seera_cuda_scaler_multiply_f(float *arr, float k, int total_elements);
+int seera_cuda_scaler_add_f(float *arr, float k, int total_elements);
+int seera_cuda_scaler_power_f(float *arr, float k, int total_elements);
+int seera_cuda_ones_f(float *arr, int total_elements);
+int seera_cuda_zeros_f(float *arr, int total_elements);
+
+/* ---- flat binary ops (seera_engine_cuda.hpp:110-116) --------------------------------------------- */
+int seera_cuda_elemadd_gputogpu(const float *A, const float *B, float *C, int size);
+int seera_cuda_elemmult_gputogpu(const float *A, const float *B, float *C, int size);
+int seera_cuda_elemsub_gputogpu(const float *A, const float *B, float *C, int size);
+int seera_cuda_elemdiv_gputogpu(const float *A, const float *B, float *C, int size);
+
+/* ---- NumPy-rule broadcast of two <=4-D tensors (seera_engine_cuda.hpp:119-127) -------------------- */
+int seera_broadcast_add_4d(const float *A, const float *B, float *C, int aN, int aC, int aH, int aW,
+                           int bN, int bC, int bH, int bW);
+int seera_broadcast_mul_4d(const float *A, const float *B, float *C, int aN, int aC, int aH, int aW,
+                           int bN, int bC, int bH, int bW);
+
+/* =====================================================================================================
+ * Additive entry points.  The reference composes these steps from several calls above (bias add +
+ * activation, activation gradient, bias gradient, the optimizers); here each is one pass over HBM.
+ * ===================================================================================================== */
+enum { SEERA_ACT_NONE = 0, SEERA_ACT_RELU = 1, SEERA_ACT_SIGMOID = 2, SEERA_ACT_TANH = 3 };
+
+/* y = act(z + bias[channel]); element i belongs to channel (i / inner) % channels.
+ * Replaces broadcast_add_4d + cuda_*_fwd (Seera.py:136-137, :255-258). In place allowed (y == z). */
+int seera_bias_act_fwd(const float *z, const float *bias, float *y, int size, int channels, int inner, int act);
+/* dz = dy * act'(y), with the derivative written in terms of the OUTPUT y (relu: y > 0; sigmoid:
+ * y(1-y); tanh: 1-y^2), and dbias[c] = sum of dz over that channel.  Replaces cuda_elemmult with the
+ * stored local gradient plus broadcast_mul_4d + three cuda_sum_fwd (Seera_Engine.py:571-583, :43-65). */
+int seera_act_bias_bwd(const float *dy, const float *y, float *dz, float *dbias,
+                       int size, int channels, int inner, int act);
+/* Softmax + categorical cross-entropy: the reference's chain softmax -> clip(eps, 1-eps) -> log ->
+ * (-y * .) -> sum(-1) -> mean (Seera.py:955-969) and its backward (Seera_Engine.py:352-379, :571-583)
+ * evaluated row by row.  Writes p = softmax(z), loss_rows[n] = -sum_c y*log(clip(p)),
+ * *loss_mean = inv_count * sum_n loss_rows[n] (summed in index order), and
+ * dz = d(inv_count * sum_n loss_rows[n]) / dz.  inv_count is 1/N for a single process and
+ * 1/(global batch) when the batch is sharded over ranks. */
+int seera_softmax_cce_fwd_bwd(const float *z, const float *onehot, float *p, float *loss_rows,
+                              float *loss_mean, float *dz, int N, int C, float eps, float inv_count);
+/* Mean-squared error (Seera.py:943-945): *loss_mean = inv_count * sum (p-y)^2 (deterministic two-stage
+ * sum; `partials` is caller scratch of seera_mse_partials(size) floats), dp = 2 (p-y) * inv_count. */
+int seera_mse_partials(int size);
+int seera_mse_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp,
+                      int size, float inv_count);
+
+/* Adam (Seera.py:1069-1084) and SGD with momentum (Seera.py:1006-1008) in one pass, in place.
+ * The caller passes the fp32-rounded scalars omb1 = 1-beta1, omb2 = 1-beta2, c1 = 1-beta1^t,
+ * c2 = 1-beta2^t; g is multiplied by grad_scale first (1/world for data-parallel averaging). */
+int seera_adam_step(float *w, const float *g, float *m, float *v, int n, float lr, float beta1, float omb1,
+                    float beta2, float omb2, float eps, float c1, float c2, float grad_scale);
+int seera_sgd_step(float *w, const float *g, float *vel, int n, float lr, float momentum, float grad_scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SEERA_B200_H */

@@ -1,0 +1,55 @@
+// Shared host-side state and helpers for the engine's translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include "seera_b200.h"
+
+namespace seera {
+
+struct Runtime {
+    int device = -1;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;      // the stream every kernel is enqueued on
+    cudaStream_t own_stream = nullptr;
+    int precision = 0;
+    int status = 0;
+    uint64_t launches = 0;
+    char err[512] = {0};
+};
+Runtime &rt();
+int fail(int code, const char *fmt, ...);       // records the status + message, returns code
+int check_cuda(cudaError_t e, const char *what);
+int ensure_init();
+
+// Grid for a grid-stride kernel over `work_items` with `threads` per block: enough blocks to cover
+// the work once, capped at a whole number of waves (8 resident 256-thread CTAs per SM).
+inline int stride_grid(long long work_items, int threads = 256) {
+    long long need = (work_items + threads - 1) / threads;
+    long long cap = (long long)rt().sm_count * 8;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+inline void count_launch(int n = 1) { rt().launches += n; }
+
+#define SEERA_ENSURE()                      \
+    do {                                    \
+        int _s = seera::ensure_init();      \
+        if (_s) return _s;                  \
+    } while (0)
+
+#define SEERA_LAUNCH_CHECK(name)                                                   \
+    do {                                                                           \
+        seera::count_launch();                                                     \
+        cudaError_t _e = cudaGetLastError();                                       \
+        if (_e != cudaSuccess) return seera::check_cuda(_e, name);                 \
+    } while (0)
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Pool-backed scratch for internal use (split-K partials, operand shadows).
+void *scratch_alloc(size_t bytes);
+void scratch_free(void *p);
+
+}  // namespace seera

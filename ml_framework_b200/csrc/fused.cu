@@ -1,0 +1,417 @@
+// Fused bandwidth-bound passes of the training step: bias + activation forward, activation gradient +
+// bias gradient backward, row softmax and its VJP, softmax/cross-entropy and MSE loss heads, and the
+// Adam / SGD-momentum updates.
+//
+// The reference runs each of these as a chain of separate launches with intermediates in HBM:
+//   bias add + activation   broadcast_add_4d then cuda_*_fwd writing out AND grad   (Seera.py:136-137, :255-258)
+//   activation backward     cuda_elemmult(local_grad, cp) then cuda_elemadd        (Seera_Engine.py:571-583)
+//   bias gradient           broadcast_mul_4d + up to three cuda_sum_fwd            (Seera_Engine.py:43-65)
+//   softmax / VJP           one 256-thread block per row                           (engine_cuda/src/activations.cu:87-157)
+//   Adam / SGD              ~30 cuten operator launches per parameter tensor       (Seera.py:1038-1063, :992-1001)
+// Arithmetic follows the CPU engine, the parity oracle (engine/src/activation_ops.cpp:84-115,
+// Seera.py:1069-1084, :1006-1008).
+#include "common.cuh"
+
+namespace seera {
+
+__device__ __forceinline__ float act_fwd(float z, int act) {
+    switch (act) {
+        case SEERA_ACT_RELU: return z > 0.f ? z : 0.f;
+        case SEERA_ACT_SIGMOID: return 1.f / (1.f + expf(-z));
+        case SEERA_ACT_TANH: return tanhf(z);
+        default: return z;
+    }
+}
+// derivative expressed through the output y = act(z)
+__device__ __forceinline__ float act_grad_from_out(float y, int act) {
+    switch (act) {
+        case SEERA_ACT_RELU: return y > 0.f ? 1.f : 0.f;
+        case SEERA_ACT_SIGMOID: return y * (1.f - y);
+        case SEERA_ACT_TANH: return 1.f - y * y;
+        default: return 1.f;
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over a 256-thread block; result valid in thread 0. `sm` holds 8 floats.
+__device__ __forceinline__ float block_sum_256(float v, float *sm) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.f;
+    if (threadIdx.x < 32) {
+        r = threadIdx.x < (blockDim.x >> 5) ? sm[threadIdx.x] : 0.f;
+        r = warp_sum(r);
+    }
+    __syncthreads();
+    return r;
+}
+
+// ---- y = act(z + bias[channel]) ------------------------------------------------------------------
+// mode 0: scalar; mode 1: inner % 4 == 0 (one channel per float4); mode 2: inner == 1 and
+// channels % 4 == 0 (four consecutive channels per float4).
+__global__ void __launch_bounds__(256) bias_act_kernel(const float *__restrict__ z, const float *__restrict__ bias,
+                                                       float *__restrict__ y, long long n, int channels, int inner,
+                                                       int act, int mode) {
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    if (mode == 0) {
+        for (long long i = tid; i < n; i += nthr) {
+            float b = bias ? __ldg(bias + (i / inner) % channels) : 0.f;
+            y[i] = act_fwd(z[i] + b, act);
+        }
+        return;
+    }
+    long long n4 = n >> 2;
+    const float4 *z4 = reinterpret_cast<const float4 *>(z);
+    float4 *y4 = reinterpret_cast<float4 *>(y);
+    for (long long i = tid; i < n4; i += nthr) {
+        float4 v = z4[i], b;
+        if (!bias) b = make_float4(0.f, 0.f, 0.f, 0.f);
+        else if (mode == 1) { float s = __ldg(bias + ((i << 2) / inner) % channels); b = make_float4(s, s, s, s); }
+        else b = __ldg(reinterpret_cast<const float4 *>(bias) + ((i << 2) % channels >> 2));
+        v.x = act_fwd(v.x + b.x, act); v.y = act_fwd(v.y + b.y, act);
+        v.z = act_fwd(v.z + b.z, act); v.w = act_fwd(v.w + b.w, act);
+        y4[i] = v;
+    }
+}
+
+// ---- dz = dy * act'(y); per-channel partial sums of dz ----------------------------------------------
+// Channel-major case (inner > 1, NCHW): grid (channels, splits); block (c, s) walks samples
+// n = s, s + splits, ... and the contiguous `inner` run of channel c in each; writes partial[s*channels + c].
+__global__ void __launch_bounds__(256) act_bias_bwd_nchw_kernel(const float *__restrict__ dy, const float *__restrict__ y,
+                                                                float *__restrict__ dz, float *__restrict__ partial,
+                                                                int outer, int channels, int inner, int act, bool vec) {
+    __shared__ float sm[8];
+    int c = blockIdx.x, s = blockIdx.y, splits = gridDim.y;
+    float acc = 0.f;
+    for (int n = s; n < outer; n += splits) {
+        long long base = ((long long)n * channels + c) * inner;
+        if (vec) {
+            const float4 *d4 = reinterpret_cast<const float4 *>(dy + base), *y4 = reinterpret_cast<const float4 *>(y + base);
+            float4 *o4 = reinterpret_cast<float4 *>(dz + base);
+            for (int i = threadIdx.x; i < (inner >> 2); i += blockDim.x) {
+                float4 d = d4[i], yy = y4[i], r;
+                r.x = d.x * act_grad_from_out(yy.x, act); r.y = d.y * act_grad_from_out(yy.y, act);
+                r.z = d.z * act_grad_from_out(yy.z, act); r.w = d.w * act_grad_from_out(yy.w, act);
+                o4[i] = r;
+                acc += (r.x + r.y) + (r.z + r.w);
+            }
+        } else {
+            for (int i = threadIdx.x; i < inner; i += blockDim.x) {
+                float r = dy[base + i] * act_grad_from_out(y[base + i], act);
+                dz[base + i] = r;
+                acc += r;
+            }
+        }
+    }
+    float tot = block_sum_256(acc, sm);
+    if (threadIdx.x == 0 && partial) partial[(long long)s * channels + c] = tot;
+}
+
+// Row-major case (inner == 1, [rows, channels]): block = 32 columns x 8 row lanes; grid (ceil(channels/32), splits).
+__global__ void __launch_bounds__(256) act_bias_bwd_rows_kernel(const float *__restrict__ dy, const float *__restrict__ y,
+                                                                float *__restrict__ dz, float *__restrict__ partial,
+                                                                int rows, int channels, int act) {
+    __shared__ float sm[8][33];
+    int col = blockIdx.x * 32 + (threadIdx.x & 31), lane_r = threadIdx.x >> 5;
+    int s = blockIdx.y, splits = gridDim.y;
+    float acc = 0.f;
+    if (col < channels) {
+        for (int r = s * 8 + lane_r; r < rows; r += splits * 8) {
+            long long i = (long long)r * channels + col;
+            float v = dy[i] * act_grad_from_out(y[i], act);
+            dz[i] = v;
+            acc += v;
+        }
+    }
+    sm[lane_r][threadIdx.x & 31] = acc;
+    __syncthreads();
+    if (lane_r == 0 && col < channels && partial) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) t += sm[k][threadIdx.x];
+        partial[(long long)s * channels + col] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256) sum_partials_kernel(const float *__restrict__ partial, float *__restrict__ out,
+                                                           int channels, int splits) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    float t = 0.f;
+    for (int s = 0; s < splits; s++) t += partial[(long long)s * channels + c];
+    out[c] = t;
+}
+
+// ---- row softmax: one warp per row --------------------------------------------------------------------
+__global__ void __launch_bounds__(256) softmax_fwd_kernel(const float *__restrict__ x, float *__restrict__ out, int N, int C) {
+    int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    int nwarp = gridDim.x * (blockDim.x >> 5);
+    for (; row < N; row += nwarp) {
+        const float *r = x + (long long)row * C;
+        float *o = out + (long long)row * C;
+        float mx = -INFINITY;
+        for (int c = lane; c < C; c += 32) mx = fmaxf(mx, r[c]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int c = lane; c < C; c += 32) { float e = expf(r[c] - mx); o[c] = e; sum += e; }
+        sum = warp_sum(sum);
+        float inv = 1.f / sum;
+        for (int c = lane; c < C; c += 32) o[c] *= inv;
+    }
+}
+
+__global__ void __launch_bounds__(256) softmax_vjp_kernel(const float *__restrict__ s, const float *__restrict__ d,
+                                                          float *__restrict__ dx, int N, int C) {
+    int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    int nwarp = gridDim.x * (blockDim.x >> 5);
+    for (; row < N; row += nwarp) {
+        const float *sr = s + (long long)row * C, *dr = d + (long long)row * C;
+        float dot = 0.f;
+        for (int c = lane; c < C; c += 32) dot += dr[c] * sr[c];
+        dot = warp_sum(dot);
+        for (int c = lane; c < C; c += 32) dx[(long long)row * C + c] = sr[c] * (dr[c] - dot);
+    }
+}
+
+// softmax -> clip -> log -> -y* -> sum(-1), and the gradient of inv_count * sum_rows w.r.t. z
+__global__ void __launch_bounds__(256) softmax_cce_kernel(const float *__restrict__ z, const float *__restrict__ yhot,
+                                                          float *__restrict__ p, float *__restrict__ loss_rows,
+                                                          float *__restrict__ dz, int N, int C, float eps, float inv_count) {
+    int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    int nwarp = gridDim.x * (blockDim.x >> 5);
+    float hi = 1.0f - eps;
+    for (; row < N; row += nwarp) {
+        const float *r = z + (long long)row * C, *yr = yhot + (long long)row * C;
+        float *pr = p + (long long)row * C, *dr = dz + (long long)row * C;
+        float mx = -INFINITY;
+        for (int c = lane; c < C; c += 32) mx = fmaxf(mx, r[c]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int c = lane; c < C; c += 32) { float e = expf(r[c] - mx); pr[c] = e; sum += e; }
+        sum = warp_sum(sum);
+        float inv = 1.f / sum, loss = 0.f, dot = 0.f;
+        for (int c = lane; c < C; c += 32) {
+            float pv = pr[c] * inv;
+            pr[c] = pv;
+            float pc = pv < eps ? eps : (pv > hi ? hi : pv);
+            float negy = yr[c] * -1.0f;
+            loss += negy * logf(pc);
+            float g = (pv >= eps && pv <= hi) ? (1.0f / pc) * (negy * inv_count) : 0.f;   // d loss / d p
+            dr[c] = g;
+            dot += g * pv;
+        }
+        loss = warp_sum(loss);
+        dot = warp_sum(dot);
+        for (int c = lane; c < C; c += 32) dr[c] = pr[c] * (dr[c] - dot);
+        if (lane == 0) loss_rows[row] = loss;
+    }
+}
+
+// Deterministic single-block sum of n floats times scale.
+__global__ void __launch_bounds__(256) scaled_sum_kernel(const float *__restrict__ v, float *__restrict__ out, int n, float scale) {
+    __shared__ float sm[8];
+    float acc = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) acc += v[i];
+    float t = block_sum_256(acc, sm);
+    if (threadIdx.x == 0) *out = t * scale;
+}
+
+__global__ void __launch_bounds__(256) mse_kernel(const float *__restrict__ p, const float *__restrict__ y,
+                                                  float *__restrict__ partials, float *__restrict__ dp,
+                                                  long long n, float inv_count) {
+    __shared__ float sm[8];
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    float acc = 0.f;
+    for (long long i = tid; i < n; i += nthr) {
+        float d = p[i] + y[i] * -1.0f;
+        acc += d * d;
+        dp[i] = (2.0f * d) * inv_count;
+    }
+    float t = block_sum_256(acc, sm);
+    if (threadIdx.x == 0) partials[blockIdx.x] = t;
+}
+
+// ---- optimizers -------------------------------------------------------------------------------------------
+struct AdamArgs { float lr, b1, omb1, b2, omb2, eps, c1, c2, gs; };
+
+__device__ __forceinline__ void adam_one(float &w, float g, float &m, float &v, const AdamArgs &a) {
+    g *= a.gs;
+    m = a.b1 * m + a.omb1 * g;
+    v = a.b2 * v + a.omb2 * (g * g);
+    float mh = m / a.c1, vh = v / a.c2;
+    w -= (a.lr * mh) / (sqrtf(vh) + a.eps);
+}
+
+__global__ void __launch_bounds__(256) adam_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ m,
+                                                   float *__restrict__ v, long long n, bool vec, AdamArgs a) {
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    if (vec) {
+        long long n4 = n >> 2;
+        float4 *w4 = reinterpret_cast<float4 *>(w), *m4 = reinterpret_cast<float4 *>(m), *v4 = reinterpret_cast<float4 *>(v);
+        const float4 *g4 = reinterpret_cast<const float4 *>(g);
+        for (long long i = tid; i < n4; i += nthr) {
+            float4 ww = w4[i], gg = g4[i], mm = m4[i], vv = v4[i];
+            adam_one(ww.x, gg.x, mm.x, vv.x, a); adam_one(ww.y, gg.y, mm.y, vv.y, a);
+            adam_one(ww.z, gg.z, mm.z, vv.z, a); adam_one(ww.w, gg.w, mm.w, vv.w, a);
+            w4[i] = ww; m4[i] = mm; v4[i] = vv;
+        }
+        for (long long i = (n4 << 2) + tid; i < n; i += nthr) adam_one(w[i], g[i], m[i], v[i], a);
+    } else {
+        for (long long i = tid; i < n; i += nthr) adam_one(w[i], g[i], m[i], v[i], a);
+    }
+}
+
+__global__ void __launch_bounds__(256) sgd_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ vel,
+                                                  long long n, bool vec, float lr, float mu, float gs) {
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    if (vec) {
+        long long n4 = n >> 2;
+        float4 *w4 = reinterpret_cast<float4 *>(w), *v4 = reinterpret_cast<float4 *>(vel);
+        const float4 *g4 = reinterpret_cast<const float4 *>(g);
+        for (long long i = tid; i < n4; i += nthr) {
+            float4 ww = w4[i], gg = g4[i], vv = v4[i];
+            vv.x = mu * vv.x + lr * (gg.x * gs); vv.y = mu * vv.y + lr * (gg.y * gs);
+            vv.z = mu * vv.z + lr * (gg.z * gs); vv.w = mu * vv.w + lr * (gg.w * gs);
+            ww.x -= vv.x; ww.y -= vv.y; ww.z -= vv.z; ww.w -= vv.w;
+            w4[i] = ww; v4[i] = vv;
+        }
+        for (long long i = (n4 << 2) + tid; i < n; i += nthr) { vel[i] = mu * vel[i] + lr * (g[i] * gs); w[i] -= vel[i]; }
+    } else {
+        for (long long i = tid; i < n; i += nthr) { vel[i] = mu * vel[i] + lr * (g[i] * gs); w[i] -= vel[i]; }
+    }
+}
+
+}  // namespace seera
+
+using namespace seera;
+
+extern "C" {
+
+int seera_bias_act_fwd(const float *z, const float *bias, float *y, int size, int channels, int inner, int act) {
+    SEERA_ENSURE();
+    if (size < 0 || channels < 1 || inner < 1 || (size > 0 && (!z || !y))) return fail(SEERA_E_ARG, "bias_act_fwd: bad argument");
+    if (size == 0) return SEERA_OK;
+    int mode = 0;
+    if (aligned16(z) && aligned16(y) && size % 4 == 0) {
+        if (inner % 4 == 0) mode = 1;
+        else if (inner == 1 && channels % 4 == 0 && (!bias || aligned16(bias))) mode = 2;
+    }
+    bias_act_kernel<<<stride_grid(mode ? size / 4 : size), 256, 0, rt().stream>>>(z, bias, y, size, channels, inner, act, mode);
+    SEERA_LAUNCH_CHECK("bias_act_fwd");
+    return SEERA_OK;
+}
+
+int seera_act_bias_bwd(const float *dy, const float *y, float *dz, float *dbias, int size, int channels, int inner, int act) {
+    SEERA_ENSURE();
+    if (size < 0 || channels < 1 || inner < 1 || (size > 0 && (!dy || !dz)) || (act != SEERA_ACT_NONE && !y) ||
+        size % (channels * inner) != 0)
+        return fail(SEERA_E_ARG, "act_bias_bwd: bad argument");
+    if (size == 0) return SEERA_OK;
+    if (!y) y = dy;   // act == NONE never reads it
+    int outer = size / (channels * inner);
+    // splits: enough blocks for ~4 waves, never more than the rows available
+    int splits;
+    float *partial = nullptr;
+    if (inner == 1) {
+        int colblocks = (channels + 31) / 32;
+        splits = (rt().sm_count * 4 + colblocks - 1) / colblocks;
+        int maxs = (outer + 7) / 8; if (splits > maxs) splits = maxs; if (splits < 1) splits = 1;
+        if (dbias) { partial = (float *)scratch_alloc((size_t)splits * channels * sizeof(float)); if (!partial) return SEERA_E_OOM; }
+        act_bias_bwd_rows_kernel<<<dim3(colblocks, splits), 256, 0, rt().stream>>>(dy, y, dz, partial, outer, channels, act);
+        SEERA_LAUNCH_CHECK("act_bias_bwd(rows)");
+    } else {
+        splits = (rt().sm_count * 4 + channels - 1) / channels;
+        if (splits > outer) splits = outer; if (splits < 1) splits = 1;
+        if (splits > 65535) splits = 65535;
+        if (dbias) { partial = (float *)scratch_alloc((size_t)splits * channels * sizeof(float)); if (!partial) return SEERA_E_OOM; }
+        bool vec = (inner % 4 == 0) && aligned16(dy) && aligned16(y) && aligned16(dz);
+        act_bias_bwd_nchw_kernel<<<dim3(channels, splits), 256, 0, rt().stream>>>(dy, y, dz, partial, outer, channels, inner, act, vec);
+        SEERA_LAUNCH_CHECK("act_bias_bwd(nchw)");
+    }
+    if (dbias) {
+        sum_partials_kernel<<<(channels + 255) / 256, 256, 0, rt().stream>>>(partial, dbias, channels, splits);
+        scratch_free(partial);
+        SEERA_LAUNCH_CHECK("act_bias_bwd(sum)");
+    }
+    return SEERA_OK;
+}
+
+int seera_cuda_softmax_fwd(const float *x, float *out, int N, int C) {
+    SEERA_ENSURE();
+    if (N < 0 || C < 1 || (N > 0 && (!x || !out))) return fail(SEERA_E_ARG, "cuda_softmax_fwd: bad argument");
+    if (N == 0) return SEERA_OK;
+    softmax_fwd_kernel<<<stride_grid((long long)N * 32), 256, 0, rt().stream>>>(x, out, N, C);
+    SEERA_LAUNCH_CHECK("cuda_softmax_fwd");
+    return SEERA_OK;
+}
+
+int seera_cuda_softmax_vjp(const float *s, const float *dout, float *dx, int N, int C) {
+    SEERA_ENSURE();
+    if (N < 0 || C < 1 || (N > 0 && (!s || !dout || !dx))) return fail(SEERA_E_ARG, "cuda_softmax_vjp: bad argument");
+    if (N == 0) return SEERA_OK;
+    softmax_vjp_kernel<<<stride_grid((long long)N * 32), 256, 0, rt().stream>>>(s, dout, dx, N, C);
+    SEERA_LAUNCH_CHECK("cuda_softmax_vjp");
+    return SEERA_OK;
+}
+
+int seera_softmax_cce_fwd_bwd(const float *z, const float *onehot, float *p, float *loss_rows, float *loss_mean,
+                              float *dz, int N, int C, float eps, float inv_count) {
+    SEERA_ENSURE();
+    if (N < 1 || C < 1 || !z || !onehot || !p || !loss_rows || !loss_mean || !dz)
+        return fail(SEERA_E_ARG, "softmax_cce_fwd_bwd: bad argument");
+    softmax_cce_kernel<<<stride_grid((long long)N * 32), 256, 0, rt().stream>>>(z, onehot, p, loss_rows, dz, N, C, eps, inv_count);
+    SEERA_LAUNCH_CHECK("softmax_cce");
+    scaled_sum_kernel<<<1, 256, 0, rt().stream>>>(loss_rows, loss_mean, N, inv_count);
+    SEERA_LAUNCH_CHECK("softmax_cce(sum)");
+    return SEERA_OK;
+}
+
+int seera_mse_partials(int size) {
+    int g = size > 0 ? stride_grid(size) : 1;
+    return g;
+}
+
+int seera_mse_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp, int size, float inv_count) {
+    SEERA_ENSURE();
+    if (size < 1 || !p || !y || !partials || !loss_mean || !dp) return fail(SEERA_E_ARG, "mse_fwd_bwd: bad argument");
+    int g = stride_grid(size);
+    mse_kernel<<<g, 256, 0, rt().stream>>>(p, y, partials, dp, size, inv_count);
+    SEERA_LAUNCH_CHECK("mse");
+    scaled_sum_kernel<<<1, 256, 0, rt().stream>>>(partials, loss_mean, g, inv_count);
+    SEERA_LAUNCH_CHECK("mse(sum)");
+    return SEERA_OK;
+}
+
+int seera_adam_step(float *w, const float *g, float *m, float *v, int n, float lr, float beta1, float omb1,
+                    float beta2, float omb2, float eps, float c1, float c2, float grad_scale) {
+    SEERA_ENSURE();
+    if (n < 0 || (n > 0 && (!w || !g || !m || !v))) return fail(SEERA_E_ARG, "adam_step: bad argument");
+    if (n == 0) return SEERA_OK;
+    bool vec = aligned16(w) && aligned16(g) && aligned16(m) && aligned16(v);
+    AdamArgs a{lr, beta1, omb1, beta2, omb2, eps, c1, c2, grad_scale};
+    adam_kernel<<<stride_grid(vec ? (n + 3) / 4 : n), 256, 0, rt().stream>>>(w, g, m, v, n, vec, a);
+    SEERA_LAUNCH_CHECK("adam_step");
+    return SEERA_OK;
+}
+
+int seera_sgd_step(float *w, const float *g, float *vel, int n, float lr, float momentum, float grad_scale) {
+    SEERA_ENSURE();
+    if (n < 0 || (n > 0 && (!w || !g || !vel))) return fail(SEERA_E_ARG, "sgd_step: bad argument");
+    if (n == 0) return SEERA_OK;
+    bool vec = aligned16(w) && aligned16(g) && aligned16(vel);
+    sgd_kernel<<<stride_grid(vec ? (n + 3) / 4 : n), 256, 0, rt().stream>>>(w, g, vel, n, vec, lr, momentum, grad_scale);
+    SEERA_LAUNCH_CHECK("sgd_step");
+    return SEERA_OK;
+}
+
+}  // extern "C"

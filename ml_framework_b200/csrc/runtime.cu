@@ -1,0 +1,197 @@
+// Runtime: device/stream selection, status, the pooled stream-ordered allocator and the
+// host<->device transfers behind the memory entries of the boundary
+// (reference: engine_cuda/src/cuda_bindings.cpp:23-170, which calls cudaMalloc / cudaFree /
+// cudaMemcpy directly on every call).
+//
+// Allocator: freed blocks are kept in per-size free lists and handed out again for the same
+// rounded size.  All work runs on one stream, so a block returned by cuda_free may be reused
+// by the next allocation without waiting: every kernel that still reads it was enqueued earlier.
+#include "common.cuh"
+#include <cstdarg>
+#include <cstring>
+#include <map>
+#include <unordered_map>
+#include <vector>
+
+namespace seera {
+
+Runtime &rt() { static Runtime r; return r; }
+
+int fail(int code, const char *fmt, ...) {
+    Runtime &r = rt();
+    va_list ap; va_start(ap, fmt);
+    vsnprintf(r.err, sizeof(r.err), fmt, ap);
+    va_end(ap);
+    r.status = code;
+    return code;
+}
+
+int check_cuda(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return SEERA_OK;
+    return fail(SEERA_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int ensure_init() {
+    if (rt().device >= 0) return SEERA_OK;
+    return seera_init(0);
+}
+
+namespace {
+struct Pool {
+    std::map<size_t, std::vector<void *>> free_lists;   // rounded size -> cached blocks
+    std::unordered_map<void *, size_t> live;            // every block handed out -> rounded size
+    size_t reserved = 0;
+};
+Pool &pool() { static Pool p; return p; }
+
+size_t round_size(size_t n) {
+    if (n == 0) n = 1;
+    if (n <= (1u << 20)) return (n + 511) & ~size_t(511);                 // 512 B granules up to 1 MiB
+    return (n + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);        // 2 MiB granules above
+}
+}  // namespace
+
+void *scratch_alloc(size_t bytes) { return seera_cuda_malloc(bytes); }
+void scratch_free(void *p) { seera_cuda_free(p); }
+
+}  // namespace seera
+
+using namespace seera;
+
+extern "C" {
+
+int seera_init(int device) {
+    Runtime &r = rt();
+    if (r.device == device && r.stream) return SEERA_OK;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        return fail(SEERA_E_CUDA, "seera_init: no CUDA device (%s)", cudaGetErrorString(e));
+    if (device < 0 || device >= n) return fail(SEERA_E_ARG, "seera_init: device %d of %d", device, n);
+    if (int s = check_cuda(cudaSetDevice(device), "cudaSetDevice")) return s;
+    cudaDeviceProp p;
+    if (int s = check_cuda(cudaGetDeviceProperties(&p, device), "cudaGetDeviceProperties")) return s;
+    r.sm_count = p.multiProcessorCount;
+    if (!r.own_stream)
+        if (int s = check_cuda(cudaStreamCreateWithFlags(&r.own_stream, cudaStreamNonBlocking), "cudaStreamCreate")) return s;
+    r.stream = r.own_stream;
+    r.device = device;
+    return SEERA_OK;
+}
+
+int seera_synchronize(void) {
+    SEERA_ENSURE();
+    return check_cuda(cudaStreamSynchronize(rt().stream), "cudaStreamSynchronize");
+}
+
+int seera_set_stream(void *s) {
+    SEERA_ENSURE();
+    rt().stream = s ? reinterpret_cast<cudaStream_t>(s) : rt().own_stream;
+    return SEERA_OK;
+}
+void *seera_get_stream(void) { return ensure_init() ? nullptr : (void *)rt().stream; }
+const char *seera_last_error(void) { return rt().err; }
+int seera_last_status(void) { return rt().status; }
+void seera_clear_status(void) { rt().status = 0; rt().err[0] = 0; }
+uint64_t seera_launch_count(void) { return rt().launches; }
+int seera_device_sm_count(void) { return ensure_init() ? 0 : rt().sm_count; }
+int seera_set_precision(int mode) {
+    if (mode < 0 || mode > 2) return fail(SEERA_E_ARG, "seera_set_precision: mode %d", mode);
+    rt().precision = mode;
+    return SEERA_OK;
+}
+int seera_get_precision(void) { return rt().precision; }
+
+void *seera_cuda_malloc(size_t n_bytes) {
+    if (ensure_init()) return nullptr;
+    Pool &p = pool();
+    size_t sz = round_size(n_bytes);
+    auto it = p.free_lists.find(sz);
+    if (it != p.free_lists.end() && !it->second.empty()) {
+        void *b = it->second.back();
+        it->second.pop_back();
+        p.live[b] = sz;
+        return b;
+    }
+    void *b = nullptr;
+    cudaError_t e = cudaMalloc(&b, sz);
+    if (e != cudaSuccess) {            // give cached blocks back to the driver and retry once
+        cudaGetLastError();
+        seera_pool_trim();
+        e = cudaMalloc(&b, sz);
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        fail(SEERA_E_OOM, "cuda_malloc(%zu): %s", n_bytes, cudaGetErrorString(e));
+        return nullptr;
+    }
+    p.reserved += sz;
+    p.live[b] = sz;
+    return b;
+}
+void *seera_cuda_malloc_f32(int n) { return n < 0 ? nullptr : seera_cuda_malloc((size_t)n * 4); }
+void *seera_cuda_malloc_i32(int n) { return n < 0 ? nullptr : seera_cuda_malloc((size_t)n * 4); }
+void *seera_cuda_malloc_i16(int n) { return n < 0 ? nullptr : seera_cuda_malloc((size_t)n * 2); }
+
+int seera_cuda_free(void *ptr) {
+    if (!ptr) return SEERA_OK;
+    Pool &p = pool();
+    auto it = p.live.find(ptr);
+    if (it == p.live.end()) return fail(SEERA_E_ARG, "cuda_free(%p): not a live block of this pool", ptr);
+    p.free_lists[it->second].push_back(ptr);
+    p.live.erase(it);
+    return SEERA_OK;
+}
+
+int seera_pool_trim(void) {
+    Pool &p = pool();
+    if (rt().stream) cudaStreamSynchronize(rt().stream);
+    for (auto &kv : p.free_lists) {
+        for (void *b : kv.second) { cudaFree(b); p.reserved -= kv.first; }
+        kv.second.clear();
+    }
+    return SEERA_OK;
+}
+size_t seera_pool_bytes_reserved(void) { return pool().reserved; }
+
+void *seera_host_alloc_pinned(size_t n) {
+    if (ensure_init()) return nullptr;
+    void *p = nullptr;
+    if (cudaMallocHost(&p, n ? n : 1) != cudaSuccess) { cudaGetLastError(); fail(SEERA_E_OOM, "cudaMallocHost(%zu)", n); return nullptr; }
+    return p;
+}
+int seera_host_free_pinned(void *p) { return p ? check_cuda(cudaFreeHost(p), "cudaFreeHost") : SEERA_OK; }
+
+int seera_cuda_memcopy_devicetodevice(void *dst, const void *src, int num_elem) {
+    SEERA_ENSURE();
+    if (num_elem < 0 || !dst || !src) return fail(SEERA_E_ARG, "memcopy_devicetodevice: bad argument");
+    return check_cuda(cudaMemcpyAsync(dst, src, (size_t)num_elem * sizeof(float), cudaMemcpyDeviceToDevice, rt().stream),
+                      "cudaMemcpyAsync d2d");
+}
+int seera_cuda_memset(void *ptr, int value, size_t n_bytes) {
+    SEERA_ENSURE();
+    if (!ptr) return fail(SEERA_E_ARG, "cuda_memset: null");
+    return check_cuda(cudaMemsetAsync(ptr, value, n_bytes, rt().stream), "cudaMemsetAsync");
+}
+
+void *seera_to_device(const void *host, size_t n_bytes) {
+    void *d = seera_cuda_malloc(n_bytes);
+    if (!d) return nullptr;
+    if (n_bytes && seera_upload(d, host, n_bytes)) { seera_cuda_free(d); return nullptr; }
+    return d;
+}
+int seera_upload(void *dev, const void *host, size_t n_bytes) {
+    SEERA_ENSURE();
+    if (!dev || !host) return fail(SEERA_E_ARG, "upload: null");
+    // From pageable memory the runtime stages the copy before returning, so the caller may reuse
+    // `host` at once; from pinned memory the copy is asynchronous and ordered on the stream.
+    return check_cuda(cudaMemcpyAsync(dev, host, n_bytes, cudaMemcpyHostToDevice, rt().stream), "cudaMemcpyAsync h2d");
+}
+int seera_to_host(void *host, const void *dev, size_t n_bytes) {
+    SEERA_ENSURE();
+    if (!dev || !host) return fail(SEERA_E_ARG, "to_host: null");
+    if (int s = check_cuda(cudaMemcpyAsync(host, dev, n_bytes, cudaMemcpyDeviceToHost, rt().stream), "cudaMemcpyAsync d2h")) return s;
+    return check_cuda(cudaStreamSynchronize(rt().stream), "cudaStreamSynchronize");
+}
+
+}  // extern "C"

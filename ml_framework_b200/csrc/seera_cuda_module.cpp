@@ -1,0 +1,168 @@
+// Python module `seera_cuda`: a thin pybind11 shim over the C ABI in include/seera_b200.h.
+//
+// Exports the same function names, positional argument orders and pointer convention as the
+// reference's binding (engine_cuda/src/cuda_bindings.cpp:14-533): device addresses cross as Python
+// ints, `dimarr` of the reductions is a host int32 NumPy array, cuda_ones_f / cuda_zeros_f allocate
+// and return an address, to_host_* take (address, shape tuple).  A non-zero status from the C ABI
+// becomes a RuntimeError carrying seera_last_error(); the reference ignores errors.
+// No compute happens here.
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "seera_b200.h"
+
+namespace py = pybind11;
+using arr_f = py::array_t<float, py::array::c_style | py::array::forcecast>;
+using arr_i = py::array_t<int32_t, py::array::c_style | py::array::forcecast>;
+using arr_s = py::array_t<int16_t, py::array::c_style | py::array::forcecast>;
+using uptr = uintptr_t;
+
+static inline void ck(int status) {
+    if (status) throw std::runtime_error(std::string("[seera_cuda] ") + seera_last_error());
+}
+static inline uptr ckp(void *p) {
+    if (!p) throw std::runtime_error(std::string("[seera_cuda] ") + seera_last_error());
+    return reinterpret_cast<uptr>(p);
+}
+template <class T> static inline T *P(uptr a) { return reinterpret_cast<T *>(a); }
+using F = float;
+
+template <class T, class Arr>
+static Arr download(uptr ptr, const py::tuple &shape) {
+    std::vector<py::ssize_t> dims;
+    size_t n = 1;
+    for (auto s : shape) { py::ssize_t d = s.cast<py::ssize_t>(); dims.push_back(d); n *= (size_t)d; }
+    Arr out(dims);
+    if (n) ck(seera_to_host(out.mutable_data(), P<const void>(ptr), n * sizeof(T)));
+    return out;
+}
+
+PYBIND11_MODULE(seera_cuda, m) {
+    m.doc() = "Seera CUDA engine for NVIDIA B200 (sm_100a)";
+
+    // ---- memory ----------------------------------------------------------------------------------
+    m.def("cuda_malloc", [](size_t n) { return ckp(seera_cuda_malloc(n)); });
+    m.def("cuda_malloc_f16", [](int n) { return ckp(seera_cuda_malloc_f32(n)); });   // fp32 storage, as in the reference
+    m.def("cuda_malloc_f32", [](int n) { return ckp(seera_cuda_malloc_f32(n)); });
+    m.def("cuda_malloc_i32", [](int n) { return ckp(seera_cuda_malloc_i32(n)); });
+    m.def("cuda_malloc_i16", [](int n) { return ckp(seera_cuda_malloc_i16(n)); });
+    m.def("cuda_free", [](uptr p) { seera_cuda_free(P<void>(p)); });
+    m.def("cuda_memcopy_devicetodevice", [](uptr d, uptr s, int n) { ck(seera_cuda_memcopy_devicetodevice(P<void>(d), P<const void>(s), n)); });
+    m.def("cuda_memset", [](uptr p, int v, size_t n) { ck(seera_cuda_memset(P<void>(p), v, n)); });
+
+    // ---- transfers -------------------------------------------------------------------------------
+    m.def("to_device_f16", [](arr_f a) { return ckp(seera_to_device(a.data(), (size_t)a.size() * 4)); });
+    m.def("to_device_f32", [](arr_f a) { return ckp(seera_to_device(a.data(), (size_t)a.size() * 4)); });
+    m.def("to_device_i32", [](arr_i a) { return ckp(seera_to_device(a.data(), (size_t)a.size() * 4)); });
+    m.def("to_device_i16", [](arr_s a) { return ckp(seera_to_device(a.data(), (size_t)a.size() * 2)); });
+    m.def("to_host_f16", [](uptr p, py::tuple s) { return download<float, arr_f>(p, s); });
+    m.def("to_host_f32", [](uptr p, py::tuple s) { return download<float, arr_f>(p, s); });
+    m.def("to_host_i32", [](uptr p, py::tuple s) { return download<int32_t, arr_i>(p, s); });
+    m.def("to_host_i16", [](uptr p, py::tuple s) { return download<int16_t, arr_s>(p, s); });
+
+    // ---- unary ops -------------------------------------------------------------------------------
+    m.def("cuda_relu_fwd", [](uptr x, uptr o, uptr g, int n) { ck(seera_cuda_relu_fwd(P<const F>(x), P<F>(o), P<F>(g), n)); });
+    m.def("cuda_sigmoid_fwd", [](uptr x, uptr o, uptr g, int n) { ck(seera_cuda_sigmoid_fwd(P<const F>(x), P<F>(o), P<F>(g), n)); });
+    m.def("cuda_tanh_fwd", [](uptr x, uptr o, uptr g, int n) { ck(seera_cuda_tanh_fwd(P<const F>(x), P<F>(o), P<F>(g), n)); });
+    m.def("cuda_log_fwd", [](uptr x, uptr o, uptr g, int n) { ck(seera_cuda_log_fwd(P<const F>(x), P<F>(o), P<F>(g), n)); });
+    m.def("cuda_exp_fwd", [](uptr x, uptr o, uptr g, int n) { ck(seera_cuda_exp_fwd(P<const F>(x), P<F>(o), P<F>(g), n)); });
+    m.def("cuda_abs_fwd", [](uptr x, uptr o, uptr g, int n) { ck(seera_cuda_abs_fwd(P<const F>(x), P<F>(o), P<F>(g), n)); });
+    m.def("cuda_sqrt_fwd", [](uptr x, uptr o, uptr g, int n) { ck(seera_cuda_sqrt_fwd(P<const F>(x), P<F>(o), P<F>(g), n)); });
+    m.def("cuda_pow_fwd", [](uptr x, float e, uptr o, uptr g, int n) { ck(seera_cuda_pow_fwd(P<const F>(x), e, P<F>(o), P<F>(g), n)); });
+    m.def("cuda_clip_fwd", [](uptr x, float lo, float hi, uptr o, uptr g, int n) { ck(seera_cuda_clip_fwd(P<const F>(x), lo, hi, P<F>(o), P<F>(g), n)); });
+
+    // ---- softmax ---------------------------------------------------------------------------------
+    m.def("cuda_softmax_fwd", [](uptr x, uptr o, int N, int C) { ck(seera_cuda_softmax_fwd(P<const F>(x), P<F>(o), N, C)); });
+    m.def("cuda_softmax_vjp", [](uptr s, uptr d, uptr dx, int N, int C) { ck(seera_cuda_softmax_vjp(P<const F>(s), P<const F>(d), P<F>(dx), N, C)); });
+
+    // ---- GEMM ------------------------------------------------------------------------------------
+    m.def("cuda_matmul", [](uptr A, uptr B, uptr C, int M, int N, int K, int nb) { ck(seera_cuda_matmul(P<const F>(A), P<const F>(B), P<F>(C), M, N, K, nb)); });
+    m.def("cuda_matmul_bwd", [](uptr A, uptr B, uptr dC, uptr dA, uptr dB, int M, int N, int K, int nb) {
+        ck(seera_cuda_matmul_bwd(P<const F>(A), P<const F>(B), P<const F>(dC), P<F>(dA), P<F>(dB), M, N, K, nb)); });
+    m.def("cuda_transpose_2d", [](uptr i, uptr o, int r, int c) { ck(seera_cuda_transpose_2d(P<const F>(i), P<F>(o), r, c)); });
+    m.def("cuda_transpose_3d", [](uptr i, uptr o, int nb, int M, int K) { ck(seera_cuda_transpose_3d(P<const F>(i), P<F>(o), nb, M, K)); });
+
+    // ---- convolutions ----------------------------------------------------------------------------
+    m.def("cuda_conv2d_fwd", [](uptr x, uptr w, uptr o, int n, int C, int H, int W, int Fo, int R, int S, int ph, int pw, int sh, int sw) {
+        ck(seera_cuda_conv2d_fwd(P<const F>(x), P<const F>(w), P<F>(o), n, C, H, W, Fo, R, S, ph, pw, sh, sw)); });
+    m.def("cuda_conv2d_bwd", [](uptr w, uptr x, uptr dy, uptr dx, uptr dw, int n, int C, int H, int W, int Fo, int R, int S, int sh, int sw, int ph, int pw) {
+        ck(seera_cuda_conv2d_bwd(P<const F>(w), P<const F>(x), P<const F>(dy), P<F>(dx), P<F>(dw), n, C, H, W, Fo, R, S, sh, sw, ph, pw)); });
+    m.def("cuda_conv2DTranpose_fwd", [](uptr x, uptr w, uptr o, int n, int Ci, int H, int W, int Co, int KH, int KW, int sh, int sw, int ph, int pw) {
+        ck(seera_cuda_conv2DTranpose_fwd(P<const F>(x), P<const F>(w), P<F>(o), n, Ci, H, W, Co, KH, KW, sh, sw, ph, pw)); });
+    m.def("cuda_conv2DTranspose_bwd", [](uptr w, uptr x, uptr dy, uptr dx, uptr dw, int n, int Ci, int H, int W, int Co, int KH, int KW, int sh, int sw, int ph, int pw) {
+        ck(seera_cuda_conv2DTranspose_bwd(P<const F>(w), P<const F>(x), P<const F>(dy), P<F>(dx), P<F>(dw), n, Ci, H, W, Co, KH, KW, sh, sw, ph, pw)); });
+
+    // ---- pooling ---------------------------------------------------------------------------------
+    m.def("cuda_maxpool_fwd", [](uptr x, uptr o, uptr mk, int n, int C, int H, int W, int R, int S, int ph, int pw, int sh, int sw) {
+        ck(seera_cuda_maxpool_fwd(P<const F>(x), P<F>(o), P<int>(mk), n, C, H, W, R, S, ph, pw, sh, sw)); });
+    m.def("cuda_maxpool_bwd", [](uptr d, uptr mk, uptr dx, int n, int C, int H, int W, int R, int S, int ph, int pw, int sh, int sw) {
+        ck(seera_cuda_maxpool_bwd(P<const F>(d), P<const int>(mk), P<F>(dx), n, C, H, W, R, S, ph, pw, sh, sw)); });
+    m.def("cuda_unpooling_fwd", [](uptr i, uptr o, int n, int C, int H, int W, int sh, int sw) { ck(seera_cuda_unpooling_fwd(P<const F>(i), P<F>(o), n, C, H, W, sh, sw)); });
+    m.def("cuda_unpooling_bwd", [](uptr d, uptr dx, int n, int C, int H, int W, int sh, int sw) { ck(seera_cuda_unpooling_bwd(P<const F>(d), P<F>(dx), n, C, H, W, sh, sw)); });
+
+    // ---- reductions (dimarr: host int32 array) -----------------------------------------------------
+    m.def("cuda_sum_fwd", [](uptr A, uptr o, int nd, int dim, arr_i da) { ck(seera_cuda_sum_fwd(P<const F>(A), P<F>(o), nd, dim, da.data())); });
+    m.def("cuda_mean_fwd", [](uptr A, uptr o, int nd, int dim, arr_i da) { ck(seera_cuda_mean_fwd(P<const F>(A), P<F>(o), nd, dim, da.data())); });
+    m.def("cuda_max_fwd", [](uptr A, uptr o, int nd, int dim, arr_i da) { ck(seera_cuda_max_fwd(P<const F>(A), P<F>(o), nd, dim, da.data())); });
+    m.def("cuda_min_fwd", [](uptr A, uptr o, int nd, int dim, arr_i da) { ck(seera_cuda_min_fwd(P<const F>(A), P<F>(o), nd, dim, da.data())); });
+    m.def("cuda_argmax_fwd", [](uptr A, uptr o, int nd, int dim, arr_i da) { ck(seera_cuda_argmax_fwd(P<const F>(A), P<int>(o), nd, dim, da.data())); });
+    m.def("cuda_argmin_fwd", [](uptr A, uptr o, int nd, int dim, arr_i da) { ck(seera_cuda_argmin_fwd(P<const F>(A), P<int>(o), nd, dim, da.data())); });
+    m.def("cuda_sum_bwd", [](uptr d, uptr dA, int nd, int dim, arr_i da) { ck(seera_cuda_sum_bwd(P<const F>(d), P<F>(dA), nd, dim, da.data())); });
+    m.def("cuda_mean_bwd", [](uptr d, uptr dA, int nd, int dim, arr_i da) { ck(seera_cuda_mean_bwd(P<const F>(d), P<F>(dA), nd, dim, da.data())); });
+    m.def("cuda_max_bwd", [](uptr d, uptr fi, uptr fo, uptr dA, int nd, int dim, arr_i da) {
+        ck(seera_cuda_max_bwd(P<const F>(d), P<const F>(fi), P<const F>(fo), P<F>(dA), nd, dim, da.data())); });
+    m.def("cuda_min_bwd", [](uptr d, uptr fi, uptr fo, uptr dA, int nd, int dim, arr_i da) {
+        ck(seera_cuda_min_bwd(P<const F>(d), P<const F>(fi), P<const F>(fo), P<F>(dA), nd, dim, da.data())); });
+
+    // ---- scalar ops, fills, flat binary ops, broadcast ----------------------------------------------
+    m.def("cuda_scaler_multiply_f", [](uptr a, float k, int n) { ck(seera_cuda_scaler_multiply_f(P<F>(a), k, n)); });
+    m.def("cuda_scaler_add_f", [](uptr a, float k, int n) { ck(seera_cuda_scaler_add_f(P<F>(a), k, n)); });
+    m.def("cuda_power_of", [](uptr a, float k, int n) { ck(seera_cuda_scaler_power_f(P<F>(a), k, n)); });
+    m.def("cuda_ones_f", [](int n) { uptr p = ckp(seera_cuda_malloc_f32(n)); ck(seera_cuda_ones_f(P<F>(p), n)); return p; });
+    m.def("cuda_zeros_f", [](int n) { uptr p = ckp(seera_cuda_malloc_f32(n)); ck(seera_cuda_zeros_f(P<F>(p), n)); return p; });
+    m.def("cuda_elemadd", [](uptr A, uptr B, uptr C, int n) { ck(seera_cuda_elemadd_gputogpu(P<const F>(A), P<const F>(B), P<F>(C), n)); });
+    m.def("cuda_elemsub", [](uptr A, uptr B, uptr C, int n) { ck(seera_cuda_elemsub_gputogpu(P<const F>(A), P<const F>(B), P<F>(C), n)); });
+    m.def("cuda_elemdiv", [](uptr A, uptr B, uptr C, int n) { ck(seera_cuda_elemdiv_gputogpu(P<const F>(A), P<const F>(B), P<F>(C), n)); });
+    m.def("cuda_elemmult", [](uptr A, uptr B, uptr C, int n) { ck(seera_cuda_elemmult_gputogpu(P<const F>(A), P<const F>(B), P<F>(C), n)); });
+    m.def("broadcast_add_4d", [](uptr A, uptr B, uptr C, int aN, int aC, int aH, int aW, int bN, int bC, int bH, int bW) {
+        ck(seera_broadcast_add_4d(P<const F>(A), P<const F>(B), P<F>(C), aN, aC, aH, aW, bN, bC, bH, bW)); });
+    m.def("broadcast_mul_4d", [](uptr A, uptr B, uptr C, int aN, int aC, int aH, int aW, int bN, int bC, int bH, int bW) {
+        ck(seera_broadcast_mul_4d(P<const F>(A), P<const F>(B), P<F>(C), aN, aC, aH, aW, bN, bC, bH, bW)); });
+
+    // ---- additive entries (no counterpart in the reference binding) ---------------------------------
+    m.def("init", [](int dev) { ck(seera_init(dev)); });
+    m.def("stream_synchronize", []() { ck(seera_synchronize()); });
+    m.def("set_stream", [](uptr s) { ck(seera_set_stream(P<void>(s))); });
+    m.def("get_stream", []() { return reinterpret_cast<uptr>(seera_get_stream()); });
+    m.def("last_status", []() { return seera_last_status(); });
+    m.def("last_error", []() { return std::string(seera_last_error()); });
+    m.def("clear_status", []() { seera_clear_status(); });
+    m.def("launch_count", []() { return seera_launch_count(); });
+    m.def("set_precision", [](int mode) { ck(seera_set_precision(mode)); });
+    m.def("get_precision", []() { return seera_get_precision(); });
+    m.def("pool_trim", []() { ck(seera_pool_trim()); });
+    m.def("pool_bytes_reserved", []() { return seera_pool_bytes_reserved(); });
+    m.def("upload_f32", [](uptr dst, arr_f a) { ck(seera_upload(P<void>(dst), a.data(), (size_t)a.size() * 4)); });
+    m.def("upload_from_host_ptr", [](uptr dst, uptr host, size_t nbytes) { ck(seera_upload(P<void>(dst), P<const void>(host), nbytes)); });
+    m.def("host_alloc_pinned", [](size_t n) { return ckp(seera_host_alloc_pinned(n)); });
+    m.def("host_free_pinned", [](uptr p) { ck(seera_host_free_pinned(P<void>(p))); });
+    m.def("bias_act_fwd", [](uptr z, uptr b, uptr y, int n, int ch, int inner, int act) {
+        ck(seera_bias_act_fwd(P<const F>(z), P<const F>(b), P<F>(y), n, ch, inner, act)); });
+    m.def("act_bias_bwd", [](uptr dy, uptr y, uptr dz, uptr db, int n, int ch, int inner, int act) {
+        ck(seera_act_bias_bwd(P<const F>(dy), P<const F>(y), P<F>(dz), P<F>(db), n, ch, inner, act)); });
+    m.def("softmax_cce_fwd_bwd", [](uptr z, uptr y, uptr p, uptr rows, uptr loss, uptr dz, int N, int C, float eps, float inv) {
+        ck(seera_softmax_cce_fwd_bwd(P<const F>(z), P<const F>(y), P<F>(p), P<F>(rows), P<F>(loss), P<F>(dz), N, C, eps, inv)); });
+    m.def("mse_partials", [](int n) { return seera_mse_partials(n); });
+    m.def("mse_fwd_bwd", [](uptr p, uptr y, uptr part, uptr loss, uptr dp, int n, float inv) {
+        ck(seera_mse_fwd_bwd(P<const F>(p), P<const F>(y), P<F>(part), P<F>(loss), P<F>(dp), n, inv)); });
+    m.def("cuda_adam_step", [](uptr w, uptr g, uptr mm, uptr v, int n, float lr, float b1, float omb1, float b2, float omb2,
+                               float eps, float c1, float c2, float gs) {
+        ck(seera_adam_step(P<F>(w), P<const F>(g), P<F>(mm), P<F>(v), n, lr, b1, omb1, b2, omb2, eps, c1, c2, gs)); });
+    m.def("cuda_sgd_step", [](uptr w, uptr g, uptr vel, int n, float lr, float mu, float gs) {
+        ck(seera_sgd_step(P<F>(w), P<const F>(g), P<F>(vel), n, lr, mu, gs)); });
+}

@@ -1,0 +1,765 @@
+"""Training front end on the B200 engine: Sequential, layers, Loss, SGD, Adam, autograd4nn, Tensor.
+
+Mirrors the user-facing API of the reference (Seera.py:26-1086, Seera_Engine.py:22-26) - same class
+names, constructor arguments, method names (`forward`, `zero_grad`, `fit`, `step`, `set_weights`,
+`get_weights`, the attribute spelled `bais`) and error behaviour - so a training script written for
+the reference's `device="cuda"` path runs here with the import line changed.  What differs is the
+machinery underneath:
+
+  * autograd works per LAYER, not per scalar op.  A layer's forward enqueues its contraction plus
+    ONE fused bias+activation pass, and records a backward closure that enqueues ONE fused
+    activation-gradient+bias-gradient pass and the dX / dW contractions.  The reference builds a node
+    per elementary op with five placeholder buffers each (Seera_init.py:75-80) and walks them in
+    Seera_Engine.backward_step (Seera_Engine.py:259-598).
+  * all parameters live in one contiguous device arena, with matching arenas for gradients and
+    optimizer state: the optimizer is a single kernel launch over the arena (Seera.py:1038-1063 issues
+    ~30 launches per tensor) and a data-parallel run all-reduces the gradient arena in place.
+  * weights are updated in place; device addresses of parameters are stable across steps.
+  * nothing blocks: calls enqueue on the engine's stream, the loss value is read when asked for.
+
+There is no CPU path here: `device` must be "cuda" and the compiled engine must be present.
+"""
+from __future__ import annotations
+
+import pickle
+
+import numpy as np
+
+from . import seera_cuda as sc
+from .cuTen import cuten
+
+_ACT = {None: 0, "relu": 1, "sigmoid": 2, "tanh": 3}
+_ACTIVATIONS = ("relu", "sigmoid", "softmax", "tanh")
+f32 = np.float32
+
+
+def _numel(shape):
+    n = 1
+    for d in shape:
+        n *= d
+    return n
+
+
+def _new(shape):
+    return cuten._wrap(sc.cuda_malloc_f32(_numel(shape)), shape)
+
+
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+# Tensor: a device value, its gradient, and the closure that propagates the gradient
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+class Tensor:
+    def __init__(self, value, dtype="float32", is_leaf=False, device="cuda"):
+        if isinstance(value, Tensor):
+            value = value.value
+        if not isinstance(value, cuten):
+            value = cuten(np.ascontiguousarray(np.asarray(value, dtype=np.float32)))
+        self.value = value
+        self.dtype = dtype
+        self.is_leaf = is_leaf
+        self.grad = None                 # cuten, set by backward
+        self._parents = ()
+        self._backward = None            # fn(grad: cuten) -> None, deposits into parents via _accumulate
+        self._softmax_logits = None      # for a softmax output: the Tensor of logits it came from
+        self._grad_slot = None           # for a parameter: its view into the model's gradient arena
+
+    # the reference reads gradients as `t.node.cp` (Seera_init.py:53-55)
+    @property
+    def node(self):
+        return self
+
+    @property
+    def cp(self):
+        return self.grad
+
+    @cp.setter
+    def cp(self, g):
+        self.grad = g
+
+    @property
+    def shape(self):
+        return self.value.shape
+
+    def _grad_target(self):
+        """Buffer a backward kernel should write this tensor's gradient contribution into: the arena
+        slot when the gradient restarts from zero, otherwise a fresh buffer to be added."""
+        if self.grad is None and self._grad_slot is not None:
+            return self._grad_slot
+        return _new(self.value.shape)
+
+    def _accumulate(self, g):
+        """Add a gradient contribution (a cuten of this tensor's shape)."""
+        if self.grad is None:
+            self.grad = g
+        else:
+            out = _new(self.value.shape)
+            sc.cuda_elemadd(self.grad.main_ptr, g.main_ptr, out.main_ptr, self.value.size)
+            self.grad = out
+
+    def to_numpy(self):
+        return self.value.to_host_f32().copy()
+
+    def item(self):
+        a = self.value.to_host_f32()
+        if a.size != 1:
+            raise ValueError("Can only convert tensors with a single element to Python scalars")
+        return a.item()
+
+    def mean(self):
+        if self.value.size == 1:
+            return self
+        raise NotImplementedError("Tensor.mean on a non-scalar: losses of this front end are already scalar")
+
+    def detach(self):
+        return Tensor(self.value, is_leaf=True)
+
+    @classmethod
+    def zeros(cls, shape, dtype="float32", device="cuda"):
+        return cls(cuten.zeros(shape), is_leaf=True)
+
+    @classmethod
+    def ones(cls, shape, dtype="float32", device="cuda"):
+        return cls(cuten.ones(shape), is_leaf=True)
+
+    def __repr__(self):
+        return f"Tensor(GPU)\n({self.value.to_host_f32()},\nshape={self.value.shape})"
+
+
+tensor = Tensor
+
+
+class autograd4nn:
+    """Reverse pass from a scalar loss: `autograd4nn(loss)` (same call shape as Seera_Engine.py:24-26)."""
+
+    def __init__(self, hook):
+        self.hook = hook
+        self.backward()
+
+    def backward(self):
+        order, seen = [], set()
+        stack = [(self.hook, False)]
+        while stack:                                   # iterative DFS: no recursion limit on deep nets
+            t, done = stack.pop()
+            if done:
+                order.append(t)
+                continue
+            if id(t) in seen:
+                continue
+            seen.add(id(t))
+            stack.append((t, True))
+            for p in t._parents:
+                stack.append((p, False))
+        for t in order:
+            if not t.is_leaf:
+                t.grad = None
+        self.hook.grad = cuten.ones_like(self.hook.value)
+        for t in reversed(order):
+            if t._backward is not None and t.grad is not None:
+                t._backward(t.grad)
+
+
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+# Layers
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+class Layer:
+    def __init__(self):
+        self.inputs = []
+        self.outputs = []
+        self.activations = {a: a for a in _ACTIVATIONS}
+
+    def __call__(self, input_layer):
+        if not isinstance(input_layer, Layer):
+            raise TypeError("The input should be a Layer")
+        self.inpobj = input_layer
+        return self
+
+
+class Input(Layer):
+    def __init__(self, shape):
+        super().__init__()
+        self.shape = shape
+        self.weights = 0
+        self.bais = 0
+        self.inputs = None
+
+    def forward(self):
+        self.outputs = self.inputs
+        return self.outputs
+
+    def __repr__(self):
+        return f"Input Layer with shape {self.shape}"
+
+
+def _initial(kind_scale, shape):
+    kind, scale = kind_scale
+    if kind == "normal":
+        return (np.random.randn(*shape) * scale).astype(np.float32)
+    if kind == "uniform":
+        return np.random.uniform(-scale, scale, shape).astype(np.float32)
+    return (np.zeros if kind == "zeros" else np.ones)(shape, dtype=np.float32)
+
+
+def _initializers(fan_in, fan_out):
+    return {
+        "zeros": ("zeros", 0), "ones": ("ones", 1), "random_normal": ("normal", 1), "random_uniform": ("uniform", 0.05),
+        "he_normal": ("normal", np.sqrt(2 / fan_in)), "he_uniform": ("uniform", np.sqrt(6 / fan_in)),
+        "glorot_normal": ("normal", np.sqrt(2 / (fan_in + fan_out))), "glorot_uniform": ("uniform", np.sqrt(6 / (fan_in + fan_out))),
+        "lecun_normal": ("normal", np.sqrt(1 / fan_in)), "lecun_uniform": ("uniform", np.sqrt(3 / fan_in)),
+    }
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+class _ParamLayer(Layer):
+    """Shared parameter handling: host initial values until the model places them in its arena."""
+
+    def _check(self, activation, initializer, table):
+        if activation not in self.activations:
+            raise ValueError('Activation must be "relu", "sigmoid", "softmax", or "tanh"')
+        if initializer not in table:
+            raise ValueError(f"Initializer must be one of {list(table.keys())}")
+
+    def set_weights(self, W, B):
+        if isinstance(W, Tensor):
+            W, B = W.to_numpy(), B.to_numpy()
+        elif not isinstance(W, np.ndarray):
+            raise TypeError("Weights must be Tensor or numpy array")
+        W = np.ascontiguousarray(W, np.float32)
+        B = np.ascontiguousarray(B, np.float32)
+        self._w_init, self._b_init = W, B
+        if isinstance(self.weights, Tensor) and tuple(self.weights.value.shape) == W.shape:
+            sc.upload_f32(self.weights.value.main_ptr, W)            # keeps the arena slot and its address
+            sc.upload_f32(self.bais.value.main_ptr, B)
+        else:
+            self.weights = Tensor(W, is_leaf=True)
+            self.bais = Tensor(B, is_leaf=True)
+
+    def get_weights(self):
+        return self.weights, self.bais
+
+    def update_params(self, vW, vB):
+        """w -= vW, b -= vB with device tensors (Seera.py:140-147), in place."""
+        for t, v in ((self.weights, vW), (self.bais, vB)):
+            neg = v * (-1)
+            sc.cuda_elemadd(t.value.main_ptr, neg.main_ptr, t.value.main_ptr, t.value.size)
+
+    # fused epilogue / prologue shared by Dense, Conv2D, ConvTranspose2D
+    def _finish_forward(self, x, z, channels, inner, contraction_backward):
+        """z (pre-bias contraction output, cuten) -> activation output Tensor with its backward closure."""
+        act = self.layeract
+        W, b = self.weights, self.bais
+        if act == "softmax":
+            if len(z.shape) != 2:
+                raise ValueError("[Engine]: Softmax VJP requires at least 2D")
+            sc.bias_act_fwd(z.main_ptr, b.value.main_ptr, z.main_ptr, z.size, channels, inner, 0)
+            logits = Tensor(z)
+            y = _new(z.shape)
+            sc.cuda_softmax_fwd(z.main_ptr, y.main_ptr, z.shape[0], z.shape[1])
+            out = Tensor(y)
+            out._softmax_logits = logits
+            out._parents = (logits,)
+
+            def softmax_backward(g, y=y, logits=logits):
+                dz = _new(y.shape)
+                sc.cuda_softmax_vjp(y.main_ptr, g.main_ptr, dz.main_ptr, y.shape[0], y.shape[1])
+                logits._accumulate(dz)
+            out._backward = softmax_backward
+            node, code = logits, 0
+        else:
+            code = _ACT[act]
+            sc.bias_act_fwd(z.main_ptr, b.value.main_ptr, z.main_ptr, z.size, channels, inner, code)
+            out = Tensor(z)
+            node = out
+        node._parents = (x, W, b)
+
+        def layer_backward(g, y=node.value, code=code):
+            db = b._grad_target()
+            if code == 0:
+                dz = g
+                sc.act_bias_bwd(g.main_ptr, 0, g.main_ptr, db.main_ptr, y.size, channels, inner, 0)
+            else:
+                dz = _new(y.shape)
+                sc.act_bias_bwd(g.main_ptr, y.main_ptr, dz.main_ptr, db.main_ptr, y.size, channels, inner, code)
+            b._accumulate(db)
+            dx, dw = contraction_backward(dz)
+            W._accumulate(dw)
+            if dx is not None:
+                x._accumulate(dx)
+        node._backward = layer_backward
+        return out
+
+
+class Dense(_ParamLayer):
+    def __init__(self, in_units, out_units, activation=None, kernel_initializer="glorot_uniform",
+                 bias_initializer="zeros", kernel_regularizer=None, bias_regularizer=None):
+        super().__init__()
+        table = _initializers(in_units, out_units)
+        self._check(activation, kernel_initializer, table)
+        self.layeract, self.in_units, self.out_units = activation, in_units, out_units
+        self._w_init = _initial(table[kernel_initializer], (in_units, out_units))
+        self._b_init = _initial(table[bias_initializer], (1, out_units))
+        self.weights = Tensor(self._w_init, is_leaf=True)
+        self.bais = Tensor(self._b_init, is_leaf=True)
+
+    def forward(self):
+        x = self.inputs = self.inpobj.outputs
+        xv, W = x.value, self.weights.value
+        if len(xv.shape) != 2 or xv.shape[1] != self.in_units:
+            raise ValueError(f"[cuTen]: matmul: inner dimensions must agree, got {xv.shape} @ {W.shape}")
+        M, K, N = xv.shape[0], self.in_units, self.out_units
+        z = _new((M, N))
+        sc.cuda_matmul(xv.main_ptr, W.main_ptr, z.main_ptr, M, N, K, 1)
+
+        def contraction_backward(dz, need_dx=not x.is_leaf):
+            dw = self.weights._grad_target()
+            dx = _new(xv.shape) if need_dx else None
+            sc.cuda_matmul_bwd(xv.main_ptr, W.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr, M, N, K, 1)
+            return dx, dw
+        self.outputs = self._finish_forward(x, z, N, 1, contraction_backward)
+        return self.outputs
+
+    def __repr__(self):
+        return f"Dense({self.in_units}→{self.out_units}, act={self.layeract}, params={self.in_units * self.out_units + self.out_units})"
+
+
+class Conv2D(_ParamLayer):
+    def __init__(self, out_channels, in_channels, kernel_size, activation, stride=1, zero_padding=0,
+                 kernel_initializer="he_normal", bias_initializer="zeros"):
+        super().__init__()
+        fan_in = in_channels * kernel_size[0] * kernel_size[1]
+        table = _initializers(fan_in, out_channels * kernel_size[0] * kernel_size[1])
+        self._check(activation, kernel_initializer, table)
+        self.layeract, self.in_channels, self.out_channels = activation, in_channels, out_channels
+        self.kernel_size, self.stride, self.zero_padding = tuple(kernel_size), _pair(stride), _pair(zero_padding)
+        self._w_init = _initial(table[kernel_initializer], (out_channels, in_channels) + self.kernel_size)
+        self._b_init = np.zeros((1, out_channels, 1, 1), np.float32)
+        self.weights = Tensor(self._w_init, is_leaf=True)
+        self.bais = Tensor(self._b_init, is_leaf=True)
+
+    def forward(self):
+        x = self.inputs = self.inpobj.outputs
+        xv, W = x.value, self.weights.value
+        if len(xv.shape) == 3:
+            xv = xv.reshape((1,) + tuple(xv.shape))
+        if len(xv.shape) != 4:
+            raise ValueError("[cuTen]: conv2d expects 4-D tensors (N,C,H,W) and (F,C,KH,KW)")
+        N, C, H, Wd = xv.shape
+        F, (KH, KW), (sh, sw), (ph, pw) = self.out_channels, self.kernel_size, self.stride, self.zero_padding
+        OH, OW = (H + 2 * ph - KH) // sh + 1, (Wd + 2 * pw - KW) // sw + 1
+        z = _new((N, F, OH, OW))
+        sc.cuda_conv2d_fwd(xv.main_ptr, W.main_ptr, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw)
+
+        def contraction_backward(dz, need_dx=not x.is_leaf):
+            dw = self.weights._grad_target()
+            dx = _new(xv.shape) if need_dx else None
+            sc.cuda_conv2d_bwd(W.main_ptr, xv.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
+                               N, C, H, Wd, F, KH, KW, sh, sw, ph, pw)
+            return dx, dw
+        self.outputs = self._finish_forward(x, z, F, OH * OW, contraction_backward)
+        return self.outputs
+
+    def __repr__(self):
+        return f"Conv2D({self.in_channels}→{self.out_channels}, kernel={self.kernel_size}, act={self.layeract})"
+
+
+class ConvTranspose2D(_ParamLayer):
+    def __init__(self, out_channels, in_channels, kernel_size, activation, stride=1, zero_padding=0,
+                 kernel_initializer="he_normal"):
+        super().__init__()
+        fan_in = in_channels * kernel_size[0] * kernel_size[1]
+        table = _initializers(fan_in, out_channels * kernel_size[0] * kernel_size[1])
+        for k in ("lecun_normal", "lecun_uniform"):
+            table.pop(k)
+        self._check(activation, kernel_initializer, table)
+        self.layeract, self.in_channels, self.out_channels = activation, in_channels, out_channels
+        self.kernel_size, self.stride, self.zero_padding = tuple(kernel_size), _pair(stride), _pair(zero_padding)
+        self._w_init = _initial(table[kernel_initializer], (in_channels, out_channels) + self.kernel_size)
+        self._b_init = np.zeros((1, out_channels, 1, 1), np.float32)
+        self.weights = Tensor(self._w_init, is_leaf=True)
+        self.bais = Tensor(self._b_init, is_leaf=True)
+
+    def forward(self):
+        x = self.inputs = self.inpobj.outputs
+        xv, W = x.value, self.weights.value
+        if len(xv.shape) != 4:
+            raise ValueError("[cuTen]: conv2d_transpose expects 4-D tensors (N,Cin,H,W) and (Cin,Cout,KH,KW)")
+        N, Cin, H, Wd = xv.shape
+        Cout, (KH, KW), (sh, sw), (ph, pw) = self.out_channels, self.kernel_size, self.stride, self.zero_padding
+        Ho, Wo = (H - 1) * sh - 2 * ph + KH, (Wd - 1) * sw - 2 * pw + KW
+        z = _new((N, Cout, Ho, Wo))
+        sc.cuda_conv2DTranpose_fwd(xv.main_ptr, W.main_ptr, z.main_ptr, N, Cin, H, Wd, Cout, KH, KW, sh, sw, ph, pw)
+
+        def contraction_backward(dz, need_dx=not x.is_leaf):
+            dw = self.weights._grad_target()
+            dx = _new(xv.shape) if need_dx else None
+            sc.cuda_conv2DTranspose_bwd(W.main_ptr, xv.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
+                                        N, Cin, H, Wd, Cout, KH, KW, sh, sw, ph, pw)
+            return dx, dw
+        self.outputs = self._finish_forward(x, z, Cout, Ho * Wo, contraction_backward)
+        return self.outputs
+
+    def __repr__(self):
+        return (f"ConvTranspose2D({self.in_channels}→{self.out_channels}, kernel={self.kernel_size}, "
+                f"stride={self.stride}, act={self.layeract})")
+
+
+class MaxPool2D(Layer):
+    def __init__(self, pool_size=(2, 2), stride=1, padding=0):
+        super().__init__()
+        if not isinstance(pool_size, tuple):
+            raise ValueError("kernelsize should be a tuple (height, width)")
+        self.pool_size, self.stride, self.padding = pool_size, _pair(stride), _pair(padding)
+
+    def __call__(self, input_layer):
+        if not isinstance(input_layer, Layer):
+            raise TypeError("Input must be a Layer instance.")
+        self.inpobj = input_layer
+        return self
+
+    def forward(self):
+        x = self.inputs = self.inpobj.outputs
+        xv = x.value
+        if len(xv.shape) != 4:
+            raise ValueError("[cuTen]: maxpool2d expects 4-D tensor (N,C,H,W)")
+        N, C, H, W = xv.shape
+        (KH, KW), (sh, sw), (ph, pw) = self.pool_size, self.stride, self.padding
+        OH, OW = (H + 2 * ph - KH) // sh + 1, (W + 2 * pw - KW) // sw + 1
+        y = _new((N, C, OH, OW))
+        mask = cuten._wrap(sc.cuda_malloc_i32(N * C * OH * OW), (N, C, OH, OW), "int32")
+        if OH * OW > H * W:
+            raise ValueError("[cuTen]: maxpool2d with more outputs than inputs is not supported")
+        sc.cuda_maxpool_fwd(xv.main_ptr, y.main_ptr, mask.main_ptr, N, C, H, W, KH, KW, ph, pw, sh, sw)
+        out = Tensor(y)
+        out._parents = (x,)
+        self.mask = mask
+
+        def backward(g):
+            dx = _new(xv.shape)
+            sc.cuda_maxpool_bwd(g.main_ptr, mask.main_ptr, dx.main_ptr, N, C, H, W, KH, KW, ph, pw, sh, sw)
+            x._accumulate(dx)
+        out._backward = backward
+        self.outputs = out
+        return out
+
+    def __repr__(self):
+        return f"MaxPool2D(pool={self.pool_size}, stride={self.stride})"
+
+
+class Unpool2D_Nearest(Layer):
+    def __init__(self, size=(2, 2)):
+        super().__init__()
+        self.size = size
+
+    def __call__(self, input_layer):
+        if not isinstance(input_layer, Layer):
+            raise TypeError("Input must be a Layer instance.")
+        self.inpobj = input_layer
+        return self
+
+    def forward(self):
+        x = self.inputs = self.inpobj.outputs
+        xv = x.value
+        if len(xv.shape) != 4:
+            raise ValueError("[cuTen]:unpool expects 4-D tensor (N,C,H,W)")
+        sw, sh = self.size                       # the reference unpacks (sw, sh) (Seera_init.py:793)
+        N, C, H, W = xv.shape
+        y = _new((N, C, H * sh, W * sw))
+        sc.cuda_unpooling_fwd(xv.main_ptr, y.main_ptr, N, C, H, W, sh, sw)
+        out = Tensor(y)
+        out._parents = (x,)
+
+        def backward(g):
+            dx = _new(xv.shape)
+            sc.cuda_unpooling_bwd(g.main_ptr, dx.main_ptr, N, C, H, W, sh, sw)
+            x._accumulate(dx)
+        out._backward = backward
+        self.outputs = out
+        return out
+
+    def __repr__(self):
+        return f"Unpool2D_Nearest(size={self.size})"
+
+
+class Flatten(Layer):
+    def __call__(self, input_layer):
+        if not isinstance(input_layer, Layer):
+            raise TypeError("Input must be a Layer instance.")
+        self.inpobj = input_layer
+        return self
+
+    def forward(self):
+        x = self.inputs = self.inpobj.outputs
+        out = Tensor(x.value.flatten())
+        out._parents = (x,)
+        out._backward = lambda g: x._accumulate(g.reshape(x.value.shape))
+        self.outputs = out
+        return out
+
+    def __repr__(self):
+        return "Flatten Layer"
+
+
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+# Sequential
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+class Sequential:
+    def __init__(self, layers, device="cuda"):
+        if not isinstance(layers, list):
+            raise TypeError("Layers must be a list")
+        if not isinstance(layers[0], Input):
+            raise TypeError("First layer must be an Input layer")
+        if device != "cuda":
+            raise ValueError("this engine has no CPU path: Sequential(..., device=\"cuda\")")
+        self.device = device
+        self.model = [layers[0]] + [layer(layers[i]) for i, layer in enumerate(layers[1:])]
+        self.world, self._allreduce = 1, None
+        self._build_arena()
+
+    # one contiguous block each for parameters and gradients; slots are 64-float aligned
+    def _build_arena(self):
+        self.param_layers = [l for l in self.model if isinstance(l, _ParamLayer)]
+        offs, total = [], 0
+        for l in self.param_layers:
+            for init in (l._w_init, l._b_init):
+                offs.append((total, init.shape, init.size))
+                total += (init.size + 63) // 64 * 64
+        self.n_arena = total
+        host = np.zeros(max(total, 1), np.float32)
+        for (o, _, n), init in zip(offs, [a for l in self.param_layers for a in (l._w_init, l._b_init)]):
+            host[o:o + n] = init.ravel()
+        self.params = cuten(host)
+        self.grads = cuten._wrap(sc.cuda_zeros_f(max(total, 1)), (max(total, 1),))
+        it = iter(offs)
+        for l in self.param_layers:
+            for name in ("weights", "bais"):
+                o, shape, n = next(it)
+                v = cuten._wrap(self.params.main_ptr + 4 * o, shape)
+                v._owns_memory, v._base = False, self.params
+                t = Tensor(v, is_leaf=True)
+                t._arena_off, t._arena_n = o, n
+                t._grad_slot = self._grad_view(t)
+                setattr(l, name, t)
+        self._grad_fresh = True
+
+    def _grad_view(self, t):
+        v = cuten._wrap(self.grads.main_ptr + 4 * t._arena_off, t.value.shape)
+        v._owns_memory, v._base = False, self.grads
+        return v
+
+    def parameters(self):
+        return [t for l in self.param_layers for t in (l.weights, l.bais)]
+
+    def forward(self, X=None):
+        if X is not None:
+            if isinstance(X, np.ndarray):
+                X = Tensor(X, is_leaf=True)
+            if not isinstance(X, Tensor):
+                raise TypeError("Input must be a Tensor or numpy array.")
+            self.model[0].inputs = X
+        out = None
+        for layer in self.model:
+            out = layer.forward()
+        return out
+
+    def predict(self, X):
+        return self.forward(X)
+
+    def zero_grad(self):
+        """Parameter gradients restart from zero: the next backward writes them instead of adding."""
+        for t in self.parameters():
+            t.grad = None
+
+    def get_params(self):
+        for l in self.param_layers:
+            print(l.get_weights())
+
+    def summary(self):
+        print("=" * 60 + "\nModel Summary\n" + "=" * 60)
+        for i, l in enumerate(self.model):
+            print(f"  Layer {i}: {l}")
+        print("=" * 60)
+
+    def gather_grads(self):
+        """Copy every parameter gradient into its slot of the gradient arena (no-op for slots already there)."""
+        for t in self.parameters():
+            g = t.grad
+            dst = self.grads.main_ptr + 4 * t._arena_off
+            if g is None:
+                sc.cuda_memset(dst, 0, 4 * t._arena_n)
+            elif g.main_ptr != dst:
+                sc.cuda_memcopy_devicetodevice(dst, g.main_ptr, t._arena_n)
+                t.grad = self._grad_view(t)
+
+    def fit(self, X_train, y, Optimizer, Loss, Epochs, batch_size=1, Loss_interval=20):
+        history = []
+        n = X_train.shape[0]
+        for epoch in range(Epochs):
+            perm = np.random.permutation(n)
+            Xs, ys = X_train[perm], y[perm]
+            total, batches = 0.0, 0
+            for s in range(0, n, batch_size):
+                e = min(s + batch_size, n)
+                ypred = self.forward(Tensor(Xs[s:e], is_leaf=True))
+                loss = Loss(ypred, Tensor(ys[s:e], is_leaf=True))
+                self.zero_grad()
+                autograd4nn(loss)
+                Optimizer.step()
+                total += float(loss.value.to_host_f32().ravel()[0])
+                batches += 1
+            history.append(total / batches)
+            if epoch % Loss_interval == 0 or epoch == Epochs - 1:
+                print(f"Epoch {epoch + 1}/{Epochs} — Loss: {history[-1]:.6f}")
+        return np.array(history)
+
+    # checkpoint: layer configs + host copies of the weights (same record layout as Seera.py:790-860)
+    def save(self, filepath):
+        data = []
+        for l in self.model:
+            info = {"class": l.__class__.__name__, "config": {}}
+            if isinstance(l, Input):
+                info["config"]["shape"] = l.shape
+            elif isinstance(l, Dense):
+                info["config"] = {"in_units": l.in_units, "out_units": l.out_units, "layeract": l.layeract}
+            elif isinstance(l, (Conv2D, ConvTranspose2D)):
+                info["config"] = {"out_channels": l.out_channels, "in_channels": l.in_channels, "kernel_size": l.kernel_size,
+                                  "layeract": l.layeract, "stride": l.stride, "zero_padding": l.zero_padding}
+            elif isinstance(l, MaxPool2D):
+                info["config"] = {"pool_size": l.pool_size, "stride": l.stride, "padding": l.padding}
+            elif isinstance(l, Unpool2D_Nearest):
+                info["config"] = {"size": l.size}
+            if isinstance(l, _ParamLayer):
+                info["weights"], info["bais"] = l.weights.to_numpy(), l.bais.to_numpy()
+            data.append(info)
+        with open(filepath, "wb") as f:
+            pickle.dump(data, f)
+
+    @classmethod
+    def load(cls, filepath):
+        with open(filepath, "rb") as f:
+            data = pickle.load(f)
+        layers = []
+        for info in data:
+            c, k = info["config"], info["class"]
+            if k == "Input":
+                l = Input(c["shape"])
+            elif k == "Dense":
+                l = Dense(c["in_units"], c["out_units"], activation=c["layeract"])
+            elif k in ("Conv2D", "ConvTranspose2D"):
+                l = (Conv2D if k == "Conv2D" else ConvTranspose2D)(c["out_channels"], c["in_channels"], c["kernel_size"],
+                                                                 activation=c["layeract"], stride=c.get("stride", 1),
+                                                                 zero_padding=c.get("zero_padding", 0))
+            elif k == "MaxPool2D":
+                l = MaxPool2D(pool_size=c["pool_size"], stride=c["stride"], padding=c["padding"])
+            elif k in ("Unpool2D_Nearest", "UpSampling2D_Nearest"):
+                l = Unpool2D_Nearest(size=c["size"])
+            elif k == "Flatten":
+                l = Flatten()
+            else:
+                raise ValueError(f"Unknown layer type: {k}")
+            if "weights" in info:
+                l._w_init = np.ascontiguousarray(info["weights"], np.float32)
+                l._b_init = np.ascontiguousarray(info["bais"], np.float32)
+            layers.append(l)
+        return cls(layers)
+
+
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+# Losses
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+class Loss:
+    """inv_scale: set by a data-parallel driver so that each rank's loss is divided by the GLOBAL
+    batch (the ranks' gradient sum is then the gradient of the global mean)."""
+    world = 1
+
+    def categorical_cross_entropy(self, y_pred, y, epsilon=1e-7):
+        """mean over the batch of -sum(y * log(clip(y_pred, eps, 1-eps)))  (Seera.py:955-969)."""
+        if y_pred._softmax_logits is None:
+            raise NotImplementedError("categorical_cross_entropy expects the output of a softmax layer")
+        logits = y_pred._softmax_logits
+        z, yv = logits.value, y.value
+        N, C = z.shape
+        if tuple(yv.shape) != (N, C):
+            raise ValueError(f"[cuTen]: Shapes {tuple(yv.shape)} and {(N, C)} not broadcastable")
+        rows, loss, dz = _new((N,)), _new((1,)), _new((N, C))
+        sc.softmax_cce_fwd_bwd(z.main_ptr, yv.main_ptr, y_pred.value.main_ptr, rows.main_ptr, loss.main_ptr, dz.main_ptr,
+                               N, C, float(epsilon), float(f32(1.0 / (N * Loss.world))))
+        out = Tensor(loss)
+        out._parents = (logits,)
+        out._keep = (rows, yv)
+        out._backward = lambda g: logits._accumulate(dz)       # g is the all-ones seed of a scalar loss
+        return out
+
+    def mse(self, y_pred, y):
+        """mean((y_pred - y)^2) over all elements (Seera.py:943-945)."""
+        p, yv = y_pred.value, y.value
+        if p.size != yv.size:
+            raise ValueError(f"[cuTen]: Shapes {tuple(p.shape)} and {tuple(yv.shape)} not broadcastable")
+        part, loss, dp = _new((sc.mse_partials(p.size),)), _new((1,)), _new(p.shape)
+        sc.mse_fwd_bwd(p.main_ptr, yv.main_ptr, part.main_ptr, loss.main_ptr, dp.main_ptr, p.size,
+                       float(f32(1.0 / (p.size * Loss.world))))
+        out = Tensor(loss)
+        out._parents = (y_pred,)
+        out._keep = (part, yv)
+        out._backward = lambda g: y_pred._accumulate(dp)
+        return out
+
+    def mae(self, y_pred, y):
+        raise NotImplementedError("mae is outside the accelerated training path")
+
+    def binary_cross_entropy(self, y_pred, y, epsilon=1e-15):
+        raise NotImplementedError("binary_cross_entropy is outside the accelerated training path")
+
+
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+# Optimizers: one fused launch over the whole parameter arena
+# ─────────────────────────────────────────────────────────────────────────────────────────────
+class _Optimizer:
+    def __init__(self, model):
+        if not isinstance(model, Sequential):
+            raise TypeError("Model should be Sequential")
+        self.model = model
+        self.use_gpu = True
+
+    def _state(self):
+        n = max(self.model.n_arena, 1)
+        return cuten._wrap(sc.cuda_zeros_f(n), (n,))
+
+    def _grads_ready(self):
+        m = self.model
+        m.gather_grads()
+        if m._allreduce is not None:
+            m._allreduce(m.grads)
+        return f32(1.0 / m.world) if m._allreduce is not None else f32(1.0)
+
+
+class SGD(_Optimizer):
+    """vel = momentum*vel + lr*g ; w -= vel   (Seera.py:986-1008)."""
+
+    def __init__(self, model, lr, momentum=0):
+        super().__init__(model)
+        self.lr, self.momentum = lr, momentum
+        self.velocity = self._state()
+
+    def step(self):
+        gs = self._grads_ready()
+        m = self.model
+        sc.cuda_sgd_step(m.params.main_ptr, m.grads.main_ptr, self.velocity.main_ptr, m.n_arena,
+                         float(f32(self.lr)), float(f32(self.momentum)), float(gs))
+
+
+class Adam(_Optimizer):
+    """m, v exponential averages with bias correction, t starting at 1 (Seera.py:1014-1086)."""
+
+    def __init__(self, model, lr=0.001, beta1=0.9, beta2=0.999, eps=1e-8):
+        super().__init__(model)
+        self.lr, self.beta1, self.beta2, self.eps, self.t = lr, beta1, beta2, eps, 1
+        self.m, self.v = self._state(), self._state()
+
+    def step(self):
+        gs = self._grads_ready()
+        md, b1, b2 = self.model, self.beta1, self.beta2
+        sc.cuda_adam_step(md.params.main_ptr, md.grads.main_ptr, self.m.main_ptr, self.v.main_ptr, md.n_arena,
+                          float(f32(self.lr)), float(f32(b1)), float(f32(1 - b1)), float(f32(b2)), float(f32(1 - b2)),
+                          float(f32(self.eps)), float(f32(1 - b1 ** self.t)), float(f32(1 - b2 ** self.t)), float(gs))
+        self.t += 1

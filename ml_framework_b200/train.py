@@ -1,0 +1,78 @@
+"""Builds a Sequential model, optimizer and loss from a workload record and runs training steps.
+
+`Trainer.step(X, Y)` is one pass of the hot path: forward, loss, backward, optimizer update.
+X / Y may be host arrays (uploaded each step: the end-to-end path) or device tensors already
+resident (the kernel-only path).
+"""
+import numpy as np
+
+from . import seera as S
+from . import seera_cuda as sc
+from .cuTen import cuten
+
+
+def build_model(work, params=None):
+    layers = [S.Input(tuple(work.in_shape))]
+    for L in work.layers:
+        t = L["type"]
+        if t == "dense":
+            layers.append(S.Dense(L["in"], L["out"], activation=L["act"]))
+        elif t == "conv":
+            layers.append(S.Conv2D(L["out"], L["in"], L["k"], L["act"], stride=L["stride"], zero_padding=L["pad"]))
+        elif t == "convT":
+            layers.append(S.ConvTranspose2D(L["out"], L["in"], L["k"], L["act"], stride=L["stride"], zero_padding=L["pad"]))
+        elif t == "maxpool":
+            layers.append(S.MaxPool2D(L["k"], stride=L["stride"], padding=L["pad"]))
+        elif t == "unpool":
+            layers.append(S.Unpool2D_Nearest(L["size"]))
+        elif t == "flatten":
+            layers.append(S.Flatten())
+        else:
+            raise ValueError(t)
+    if params is not None:
+        for lay, P in zip(layers[1:], params):
+            if P is not None:
+                lay.set_weights(P[0], P[1])
+    return S.Sequential(layers, device="cuda")
+
+
+class Trainer:
+    def __init__(self, work, params=None, seed=0):
+        self.work = work
+        self.model = build_model(work, work.params(seed) if params is None else params)
+        o = work.opt
+        if o["kind"] == "adam":
+            self.opt = S.Adam(self.model, lr=o["lr"], beta1=o.get("beta1", 0.9), beta2=o.get("beta2", 0.999), eps=o.get("eps", 1e-8))
+        else:
+            self.opt = S.SGD(self.model, lr=o["lr"], momentum=o.get("momentum", 0))
+        L = S.Loss()
+        self.lossf = L.categorical_cross_entropy if work.loss == "cce" else L.mse
+        self.pred = None
+
+    def forward_backward(self, X, Y):
+        x = X if isinstance(X, S.Tensor) else S.Tensor(X, is_leaf=True)
+        y = Y if isinstance(Y, S.Tensor) else S.Tensor(Y, is_leaf=True)
+        self.pred = self.model.forward(x)
+        loss = self.lossf(self.pred, y)
+        self.model.zero_grad()
+        S.autograd4nn(loss)
+        return loss
+
+    def step(self, X, Y):
+        loss = self.forward_backward(X, Y)
+        self.opt.step()
+        return loss
+
+    def host_params(self):
+        return [None if not isinstance(l, S._ParamLayer) else (l.weights.to_numpy(), l.bais.to_numpy())
+                for l in self.model.model[1:]]
+
+    def host_grads(self):
+        self.model.gather_grads()
+        out = []
+        for l in self.model.model[1:]:
+            if isinstance(l, S._ParamLayer):
+                out.append((l.weights.grad.to_host_f32(), l.bais.grad.to_host_f32()))
+            else:
+                out.append(None)
+        return out

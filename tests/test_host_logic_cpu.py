@@ -1,0 +1,238 @@
+"""CPU tests of the Python host logic (tensor class, layer autograd, arenas, optimizers) on a
+host-memory stand-in for the device binding (tests/fake_seera_cuda.py).  No GPU, no product
+fallback: the stand-in is installed by a fixture for these tests only."""
+import importlib
+import os
+import sys
+import types
+
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+from oracle import cpu_oracle as co
+from oracle.train_oracle import RefNet
+import cases
+
+REFERENCE = "/root/reference"
+
+
+@pytest.fixture(scope="module")
+def host():
+    """Package modules re-imported over the fake binding; restored afterwards."""
+    import fake_seera_cuda as fake
+    import ml_framework_b200 as pkg
+    names = ["ml_framework_b200.seera_cuda", "ml_framework_b200.cuTen", "ml_framework_b200.seera", "ml_framework_b200.train"]
+    saved = {n: sys.modules.pop(n, None) for n in names}
+    saved_attr = getattr(pkg, "seera_cuda", None)
+    sys.modules["ml_framework_b200.seera_cuda"] = fake
+    pkg.seera_cuda = fake
+    ns = types.SimpleNamespace(fake=fake,
+                               cuTen=importlib.import_module("ml_framework_b200.cuTen"),
+                               seera=importlib.import_module("ml_framework_b200.seera"),
+                               train=importlib.import_module("ml_framework_b200.train"))
+    yield ns
+    for n in names:
+        sys.modules.pop(n, None)
+        if saved[n] is not None:
+            sys.modules[n] = saved[n]
+    if saved_attr is not None:
+        pkg.seera_cuda = saved_attr
+    elif hasattr(pkg, "seera_cuda"):
+        del pkg.seera_cuda
+
+
+def test_lazy_constants_allocate_nothing(host):
+    host.fake.reset()
+    ct = host.cuTen.cuten
+    x = ct(np.arange(6, dtype=np.float32).reshape(2, 3))
+    before = dict(host.fake.CALLS)
+    z, o = ct.zeros_like(x), ct.ones_like(x)
+    s = (z + x)
+    m = (o * x)
+    assert host.fake.CALLS == before                      # no allocation, no kernel
+    assert s.main_ptr == x.main_ptr and m.main_ptr == x.main_ptr and s is not x
+    assert np.array_equal(z.to_host_f32(), np.zeros((2, 3), np.float32))
+    assert np.array_equal((o * 3.0).to_host_f32(), np.full((2, 3), 3, np.float32))
+    assert z.main_ptr is not None                         # materialises on demand
+    assert np.array_equal(host.fake.to_host_f32(z.main_ptr, (2, 3)), np.zeros((2, 3), np.float32))
+
+
+def test_operators_have_value_semantics(host):
+    ct = host.cuTen.cuten
+    g = ct(np.array([[1.0, -2.0], [3.0, 4.0]], np.float32))
+    ref = g.to_host_f32()
+    assert np.allclose((g * 5.0).to_host_f32(), ref * 5)
+    assert np.allclose((g + 10.0).to_host_f32(), ref + 10)
+    assert np.allclose((g ** 2.0).to_host_f32(), ref ** 2)
+    assert np.allclose((-g).to_host_f32(), -ref)
+    assert np.allclose((g - g).to_host_f32(), 0)
+    assert np.allclose((1.0 - g).to_host_f32(), 1 - ref)
+    assert np.allclose((g / g).to_host_f32(), 1)
+    assert np.array_equal(g.to_host_f32(), ref)           # g untouched
+    b = ct(np.array([[10.0, 20.0]], np.float32))
+    assert np.allclose((g + b).to_host_f32(), ref + [[10, 20]])
+    assert np.allclose((g * b).to_host_f32(), ref * [[10, 20]])
+    assert (g @ ct(np.eye(2, dtype=np.float32))).shape == (2, 2)
+    assert np.allclose(g.T.to_host_f32(), ref.T)
+    with pytest.raises(ValueError):
+        g + ct(np.ones((3, 3), np.float32))
+    with pytest.raises(ValueError):
+        g.reshape((3,))
+    with pytest.raises(ValueError):
+        ct(np.ones(2), dtype="float64")
+
+
+def test_views_keep_owner_alive_and_memory_is_returned(host):
+    host.fake.reset()
+    ct = host.cuTen.cuten
+    a = ct(np.ones((4, 3), np.float32))
+    p = a.main_ptr
+    v = a.flatten().reshape((3, 4))
+    del a
+    assert p in host.fake.LIVE and v.main_ptr == p
+    assert np.array_equal(v.to_host_f32(), np.ones((3, 4), np.float32))
+    del v
+    assert p not in host.fake.LIVE
+
+
+def _run_trainer(host, work, n, seed, steps=2):
+    tr = host.train.Trainer(work, seed=seed)
+    X, Y = work.batch(n, seed)
+    ref = RefNet(work.layers, work.params(seed), work.loss, work.opt, co)
+    for s in range(steps):
+        loss = tr.forward_backward(X, Y)
+        got_grads = tr.host_grads()
+        tr.opt.step()
+        P = ref.forward(X)
+        rl, dP = ref.loss_and_grad(P, Y)
+        rg = ref.backward(dP)
+        ref.apply(rg)
+        assert abs(float(loss.value.to_host_f32()[0]) - float(rl)) < 1e-5 * max(1, abs(float(rl)))
+        assert rel_l2(tr.pred.to_numpy(), P) < 1e-5
+        for G, R in zip(got_grads, rg):
+            if R is not None:
+                assert rel_l2(G[0], R[0]) < 2e-5 and rel_l2(G[1].ravel(), R[1].ravel()) < 2e-5
+        for Pm, Rm in zip(tr.host_params(), ref.params):
+            if Rm is not None:
+                assert rel_l2(Pm[0], Rm[0]) < 1e-5 and rel_l2(Pm[1].ravel(), Rm[1].ravel()) < 1e-3 + 1e-9
+    return tr
+
+
+@pytest.mark.parametrize("case", ["c2s", "c3s", "c4s"])
+def test_layer_autograd_matches_step_oracle(host, case):
+    work, n = cases.small_cases()[case]
+    _run_trainer(host, work, n, seed=2)
+
+
+def test_gradients_accumulate_without_zero_grad_and_addresses_are_stable(host):
+    work, n = cases.small_cases()["c2s"]
+    tr = host.train.Trainer(work, seed=2)
+    X, Y = work.batch(n, 2)
+    w_ptr = tr.model.param_layers[0].weights.value.main_ptr
+    tr.forward_backward(X, Y)
+    g1 = tr.host_grads()[0][0].copy()
+    S = host.seera
+    pred = tr.model.forward(S.Tensor(X, is_leaf=True))
+    loss = tr.lossf(pred, S.Tensor(Y, is_leaf=True))
+    S.autograd4nn(loss)                                   # no zero_grad: must add
+    g2 = tr.host_grads()[0][0]
+    assert rel_l2(g2, 2 * g1) < 1e-6
+    tr.opt.step()
+    assert tr.model.param_layers[0].weights.value.main_ptr == w_ptr
+
+
+def test_api_errors_match_the_reference(host):
+    S = host.seera
+    with pytest.raises(ValueError):
+        S.Dense(4, 4, activation="gelu")
+    with pytest.raises(ValueError):
+        S.Dense(4, 4, activation="relu", kernel_initializer="nope")
+    with pytest.raises(TypeError):
+        S.Sequential((S.Input((4,)),))
+    with pytest.raises(TypeError):
+        S.Sequential([S.Dense(4, 4, activation="relu")])
+    with pytest.raises(TypeError):
+        S.SGD(object(), lr=0.1)
+    with pytest.raises(ValueError):
+        S.MaxPool2D(pool_size=2)
+    with pytest.raises(ValueError):
+        S.Sequential([S.Input((4,)), S.Dense(4, 4, activation="relu")], device="cpu")
+
+
+def test_save_load_round_trip(host, tmp_path):
+    work, n = cases.small_cases()["c3s"]
+    tr = host.train.Trainer(work, seed=2)
+    f = str(tmp_path / "m.pkl")
+    tr.model.save(f)
+    m2 = host.seera.Sequential.load(f)
+    X, _ = work.batch(n, 2)
+    a = tr.model.forward(host.seera.Tensor(X, is_leaf=True)).to_numpy()
+    b = m2.forward(host.seera.Tensor(X, is_leaf=True)).to_numpy()
+    assert np.array_equal(a, b)
+
+
+@pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="reference checkout not present")
+def test_unmodified_reference_python_layer_runs_on_this_cuten(host, golden_dir):
+    """Drop-in check of the tensor class: the reference's own Seera.py / Seera_init.py /
+    Seera_Engine.py, device="cuda", over this package's cuTen and the stand-in binding."""
+    from ml_framework_b200 import workloads as wl
+    saved = {k: sys.modules.get(k) for k in ("seera_cuda", "cuTen", "matplotlib", "matplotlib.pyplot",
+                                             "Seera", "Seera_init", "Seera_Engine", "seera_cpp")}
+    try:
+        for k in ("Seera", "Seera_init", "Seera_Engine"):
+            sys.modules.pop(k, None)
+        sys.modules["seera_cuda"] = host.fake
+        sys.modules["cuTen"] = host.cuTen
+        mpl = types.ModuleType("matplotlib"); mpl.pyplot = types.ModuleType("matplotlib.pyplot")
+        sys.modules["matplotlib"], sys.modules["matplotlib.pyplot"] = mpl, mpl.pyplot
+        sys.modules["seera_cpp"] = None                   # force the reference's own NumPy path off the table
+        sys.path.insert(0, REFERENCE)
+        import Seera as RS
+        from Seera_Engine import Tensor as RT, autograd4nn as rauto
+        work = wl.c1_small_cnn()
+        params = work.params(1)
+        layers = [RS.Input((1, 28, 28))]
+        for L, P in zip(work.layers, params):
+            t = L["type"]
+            lay = {"conv": lambda: RS.Conv2D(L["out"], L["in"], L["k"], L["act"], stride=L["stride"], zero_padding=L["pad"]),
+                   "maxpool": lambda: RS.MaxPool2D(L["k"], stride=L["stride"], padding=L["pad"]),
+                   "flatten": lambda: RS.Flatten(),
+                   "dense": lambda: RS.Dense(L["in"], L["out"], activation=L["act"])}[t]()
+            if P is not None:
+                lay.set_weights(P[0].copy(), P[1].copy())
+            layers.append(lay)
+        model = RS.Sequential(layers, device="cuda")
+        X, Y = work.batch(64, 1)
+        opt = RS.Adam(model, lr=1e-3)
+        gold = np.load(golden_dir + "/c1_two_steps.npz")
+        host.fake.reset_calls = host.fake.CALLS.clear()
+        for s in range(2):
+            yp = model.forward(RT(X, is_leaf=True, device="cuda"))
+            loss = RS.Loss().categorical_cross_entropy(yp, RT(Y, device="cuda"))
+            lv = float(loss.value.to_host_f32().ravel()[0])
+            model.zero_grad()
+            rauto(loss)
+            assert abs(lv - float(gold["loss%d" % s])) < 2e-5
+            if s == 0:
+                k = 0
+                for lay in model.model:
+                    if hasattr(lay, "update_params"):
+                        assert rel_l2(lay.weights.node.cp.to_host_f32(), gold["dW%d" % k]) < 2e-5
+                        assert rel_l2(lay.bais.node.cp.to_host_f32().ravel(), gold["db%d" % k].ravel()) < 2e-5
+                        k += 1
+            opt.step()
+            k = 0
+            for lay in model.model:
+                if hasattr(lay, "update_params"):
+                    assert rel_l2(lay.weights.value.to_host_f32(), gold["W%d_s%d" % (k, s)]) < 2e-5
+                    k += 1
+        # the lazy constants keep host->device uploads to the real inputs
+        assert host.fake.CALLS.get("to_device", 0) < 40
+    finally:
+        if REFERENCE in sys.path:
+            sys.path.remove(REFERENCE)
+        for k, v in saved.items():
+            sys.modules.pop(k, None)
+            if v is not None:
+                sys.modules[k] = v
