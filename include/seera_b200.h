@@ -51,6 +51,16 @@ int         seera_last_status(void);                /* last non-zero status sinc
 void        seera_clear_status(void);
 uint64_t    seera_launch_count(void);               /* kernels launched by this library so far           */
 int         seera_device_sm_count(void);
+/* CUDA events on the engine's stream, for callers that time the hot path without another CUDA binding. */
+void       *seera_event_create(void);
+int         seera_event_record(void *event);
+float       seera_event_elapsed_ms(void *start, void *stop);   /* waits for `stop`; < 0 on error */
+int         seera_event_destroy(void *event);
+/* Contraction profile: while enabled, every GEMM / convolution launch of this library is bracketed by
+ * events; seera_profile_read() waits for them and returns their count, summed device time and summed
+ * algorithmic FLOPs (2*M*N*K each), then clears the record. */
+int         seera_profile_enable(int on);
+int         seera_profile_read(uint64_t *launches, double *ms, double *flops);
 /* Precision of the GEMM / convolution contractions:
  *   0 fp32 CUDA-core tiles (bit-for-bit fp32 products, default for the fp32 configurations)
  *   1 bf16 operands, fp32 accumulate on the tensor cores (one pass)

@@ -48,6 +48,10 @@ inline void count_launch(int n = 1) { rt().launches += n; }
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Contraction profile (seera_profile_enable): bracket a launch sequence with events and book its FLOPs.
+void profile_begin();
+void profile_end(double flops);
+
 // Pool-backed scratch for internal use (split-K partials, operand shadows).
 void *scratch_alloc(size_t bytes);
 void scratch_free(void *p);

@@ -262,6 +262,7 @@ int run_contraction(const AL &al, const BL &bl, const CS &cs, int M, int N, int 
     dim3 grid((N + BN - 1) / BN, (M + bm - 1) / bm, splits);
     if (grid.y > 65535 || grid.z > 65535) { if (partial) scratch_free(partial); return fail(SEERA_E_LIMIT, "%s: grid too large", name); }
     cudaStream_t st = rt().stream;
+    profile_begin();
     if (bm == 32) contraction_kernel<32, A_MFAST, B_KFAST><<<grid, NT, 0, st>>>(al, bl, cs, partial, M, N, K, kchunk);
     else if (bm == 64) contraction_kernel<64, A_MFAST, B_KFAST><<<grid, NT, 0, st>>>(al, bl, cs, partial, M, N, K, kchunk);
     else contraction_kernel<128, A_MFAST, B_KFAST><<<grid, NT, 0, st>>>(al, bl, cs, partial, M, N, K, kchunk);
@@ -273,6 +274,7 @@ int run_contraction(const AL &al, const BL &bl, const CS &cs, int M, int N, int 
         e = cudaGetLastError();
     }
     if (partial) scratch_free(partial);
+    profile_end(2.0 * M * N * (double)K);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 

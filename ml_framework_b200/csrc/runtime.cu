@@ -51,6 +51,26 @@ size_t round_size(size_t n) {
 }
 }  // namespace
 
+struct ProfRec { cudaEvent_t a, b; double flops; };
+struct Prof { bool on = false; std::vector<ProfRec> recs; cudaEvent_t pending = nullptr; };
+static Prof &prof() { static Prof p; return p; }
+
+void profile_begin() {
+    Prof &p = prof();
+    if (!p.on) return;
+    cudaEventCreate(&p.pending);
+    cudaEventRecord(p.pending, rt().stream);
+}
+void profile_end(double flops) {
+    Prof &p = prof();
+    if (!p.on || !p.pending) return;
+    ProfRec r{p.pending, nullptr, flops};
+    cudaEventCreate(&r.b);
+    cudaEventRecord(r.b, rt().stream);
+    p.recs.push_back(r);
+    p.pending = nullptr;
+}
+
 void *scratch_alloc(size_t bytes) { return seera_cuda_malloc(bytes); }
 void scratch_free(void *p) { seera_cuda_free(p); }
 
@@ -95,6 +115,48 @@ int seera_last_status(void) { return rt().status; }
 void seera_clear_status(void) { rt().status = 0; rt().err[0] = 0; }
 uint64_t seera_launch_count(void) { return rt().launches; }
 int seera_device_sm_count(void) { return ensure_init() ? 0 : rt().sm_count; }
+void *seera_event_create(void) {
+    if (ensure_init()) return nullptr;
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return (void *)e;
+}
+int seera_event_record(void *ev) {
+    SEERA_ENSURE();
+    if (!ev) return fail(SEERA_E_ARG, "event_record: null");
+    return check_cuda(cudaEventRecord((cudaEvent_t)ev, rt().stream), "cudaEventRecord");
+}
+float seera_event_elapsed_ms(void *a, void *b) {
+    if (!a || !b) return -1.f;
+    if (cudaEventSynchronize((cudaEvent_t)b) != cudaSuccess) { check_cuda(cudaGetLastError(), "cudaEventSynchronize"); return -1.f; }
+    float ms = -1.f;
+    if (cudaEventElapsedTime(&ms, (cudaEvent_t)a, (cudaEvent_t)b) != cudaSuccess) { cudaGetLastError(); return -1.f; }
+    return ms;
+}
+int seera_event_destroy(void *ev) { return ev ? check_cuda(cudaEventDestroy((cudaEvent_t)ev), "cudaEventDestroy") : SEERA_OK; }
+
+int seera_profile_enable(int on) {
+    seera::prof().on = on != 0;
+    return SEERA_OK;
+}
+int seera_profile_read(uint64_t *launches, double *ms, double *flops) {
+    SEERA_ENSURE();
+    auto &p = seera::prof();
+    double t = 0, f = 0;
+    for (auto &r : p.recs) {
+        float e = 0.f;
+        cudaEventSynchronize(r.b);
+        cudaEventElapsedTime(&e, r.a, r.b);
+        t += e; f += r.flops;
+        cudaEventDestroy(r.a); cudaEventDestroy(r.b);
+    }
+    if (launches) *launches = p.recs.size();
+    if (ms) *ms = t;
+    if (flops) *flops = f;
+    p.recs.clear();
+    return SEERA_OK;
+}
+
 int seera_set_precision(int mode) {
     if (mode < 0 || mode > 2) return fail(SEERA_E_ARG, "seera_set_precision: mode %d", mode);
     rt().precision = mode;

@@ -143,6 +143,12 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("last_error", []() { return std::string(seera_last_error()); });
     m.def("clear_status", []() { seera_clear_status(); });
     m.def("launch_count", []() { return seera_launch_count(); });
+    m.def("event_create", []() { return ckp(seera_event_create()); });
+    m.def("event_record", [](uptr e) { ck(seera_event_record(P<void>(e))); });
+    m.def("event_elapsed_ms", [](uptr a, uptr b) { return seera_event_elapsed_ms(P<void>(a), P<void>(b)); });
+    m.def("event_destroy", [](uptr e) { ck(seera_event_destroy(P<void>(e))); });
+    m.def("profile_enable", [](int on) { ck(seera_profile_enable(on)); });
+    m.def("profile_read", []() { uint64_t n = 0; double ms = 0, fl = 0; ck(seera_profile_read(&n, &ms, &fl)); return py::make_tuple(n, ms, fl); });
     m.def("set_precision", [](int mode) { ck(seera_set_precision(mode)); });
     m.def("get_precision", []() { return seera_get_precision(); });
     m.def("pool_trim", []() { ck(seera_pool_trim()); });

@@ -284,6 +284,9 @@ class _ParamLayer(Layer):
             b._accumulate(db)
             dx, dw = contraction_backward(dz)
             W._accumulate(dw)
+            hook = getattr(getattr(self, "_model", None), "_on_grad_ready", None)
+            if hook is not None and W.grad is W._grad_slot and b.grad is b._grad_slot:
+                hook(W)                      # this layer's gradients sit in the arena: a bucket may go out
             if dx is not None:
                 x._accumulate(dx)
         node._backward = layer_backward
@@ -513,8 +516,10 @@ class Sequential:
             raise ValueError("this engine has no CPU path: Sequential(..., device=\"cuda\")")
         self.device = device
         self.model = [layers[0]] + [layer(layers[i]) for i, layer in enumerate(layers[1:])]
-        self.world, self._allreduce = 1, None
+        self.world, self._allreduce, self._on_grad_ready = 1, None, None
         self._build_arena()
+        for l in self.param_layers:
+            l._model = self
 
     # one contiguous block each for parameters and gradients; slots are 64-float aligned
     def _build_arena(self):
