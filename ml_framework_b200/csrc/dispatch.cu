@@ -1,6 +1,8 @@
 // Public GEMM / convolution entries: choose the contraction engine by the precision mode.
-//   mode 0  fp32 CUDA-core tiles (gemm_conv_simt.cu)
-//   mode 1/2 tensor-core tiles where a kernel exists for the shape, otherwise mode 0
+//   mode 0    fp32 CUDA-core tiles (gemm_conv_simt.cu)
+//   mode 1/2  tcgen05 tensor-core tiles (contraction_tc.cu): bf16 single pass / bf16x3
+// Argument validation is shared: the CUDA-core entry checks are repeated by the tensor-core path through
+// the same geometry tests before any launch.
 #include "common.cuh"
 #include "internal.h"
 
@@ -9,26 +11,26 @@ using namespace seera;
 extern "C" {
 
 int seera_cuda_matmul(const float *A, const float *B, float *C, int M, int N, int K, int Nbatch) {
-    return seera_simt_matmul(A, B, C, M, N, K, Nbatch);
+    return rt().precision ? seera_tc_matmul(A, B, C, M, N, K, Nbatch) : seera_simt_matmul(A, B, C, M, N, K, Nbatch);
 }
 int seera_cuda_matmul_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB, int M, int N, int K, int Nbatch) {
-    return seera_simt_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch);
+    return rt().precision ? seera_tc_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch) : seera_simt_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch);
 }
 int seera_cuda_conv2d_fwd(const float *image, const float *kernel, float *out, int batchN, int C, int H, int W, int F, int R, int S,
                           int pad_h, int pad_w, int stride_h, int stride_w) {
-    return seera_simt_conv2d_fwd(image, kernel, out, batchN, C, H, W, F, R, S, pad_h, pad_w, stride_h, stride_w);
+    return rt().precision ? seera_tc_conv2d_fwd(image, kernel, out, batchN, C, H, W, F, R, S, pad_h, pad_w, stride_h, stride_w) : seera_simt_conv2d_fwd(image, kernel, out, batchN, C, H, W, F, R, S, pad_h, pad_w, stride_h, stride_w);
 }
 int seera_cuda_conv2d_bwd(const float *W, const float *X, const float *dY, float *dX, float *dW, int batch, int C, int H, int W_in,
                           int F, int R, int S, int strideh, int stridew, int padh, int padw) {
-    return seera_simt_conv2d_bwd(W, X, dY, dX, dW, batch, C, H, W_in, F, R, S, strideh, stridew, padh, padw);
+    return rt().precision ? seera_tc_conv2d_bwd(W, X, dY, dX, dW, batch, C, H, W_in, F, R, S, strideh, stridew, padh, padw) : seera_simt_conv2d_bwd(W, X, dY, dX, dW, batch, C, H, W_in, F, R, S, strideh, stridew, padh, padw);
 }
 int seera_cuda_conv2DTranpose_fwd(const float *X, const float *W, float *out, int batch, int Cin, int Hin, int Win, int Cout,
                                   int KH, int KW, int strideh, int stridew, int padh, int padw) {
-    return seera_simt_convT_fwd(X, W, out, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw);
+    return rt().precision ? seera_tc_convT_fwd(X, W, out, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw) : seera_simt_convT_fwd(X, W, out, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw);
 }
 int seera_cuda_conv2DTranspose_bwd(const float *W, const float *X, const float *dY, float *dX, float *dW, int batch, int Cin, int Hin,
                                    int Win, int Cout, int KH, int KW, int strideh, int stridew, int padh, int padw) {
-    return seera_simt_convT_bwd(W, X, dY, dX, dW, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw);
+    return rt().precision ? seera_tc_convT_bwd(W, X, dY, dX, dW, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw) : seera_simt_convT_bwd(W, X, dY, dX, dW, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw);
 }
 
 }  // extern "C"

@@ -1,0 +1,140 @@
+"""GPU parity of the tcgen05 tensor-core contraction (precision modes 1 and 2) through the C ABI.
+
+Mode 1 (bf16 operands, fp32 accumulate) is compared with the CPU oracle fed the SAME bf16-rounded
+operands ("matched quantisation": products of bf16 values are exact in fp32, so only the summation
+order differs): rel-L2 <= 1e-5.  Mode 2 (bf16x3 split) is compared with the untouched fp32 oracle:
+rel-L2 <= 2e-5 (observed ~5e-6), far inside the 2e-3 gate of the training configurations."""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+from oracle import cpu_oracle as co
+from oracle.train_oracle import RefNet
+from ml_framework_b200 import workloads as wl
+import cases
+
+pytestmark = pytest.mark.gpu
+
+TOL = {1: 1e-5, 2: 2e-5}
+
+
+@pytest.fixture(scope="module")
+def E():
+    from ml_framework_b200 import engine_np, capi
+    L = capi.load()
+    capi.check(L.seera_init(capi.default_device()))
+    yield engine_np
+    assert L.seera_tc_device_status() == 0            # no bounded wait ever expired
+    L.seera_set_precision(0)
+
+
+def _prep(mode, *arrays):
+    from ml_framework_b200 import capi
+    capi.load().seera_set_precision(mode)
+    return [wl.bf16_round(a) if mode == 1 else a for a in arrays]
+
+
+MATMUL = [(1, 3, 2), (5, 7, 3), (128, 64, 32), (129, 65, 33), (64, 784, 10), (300, 10, 1024), (257, 1000, 255), (4096, 1024, 1024)]
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("M,K,N", MATMUL)
+def test_matmul_and_backward(E, mode, M, K, N):
+    rs = np.random.RandomState(M + K + N)
+    A, B, dC = _prep(mode, *(rs.standard_normal(s).astype(np.float32) for s in ((M, K), (K, N), (M, N))))
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    assert rel_l2(E.matmul(A, B), ref) < TOL[mode]
+    dA, dB = E.matmul_backward(A, B, dC)
+    assert rel_l2(dA, dC.astype(np.float64) @ B.T.astype(np.float64)) < TOL[mode]
+    assert rel_l2(dB, A.T.astype(np.float64) @ dC.astype(np.float64)) < TOL[mode]
+
+
+CONV = [(1, 1, 5, 5, 1, 3, 3, 1, 1, 0, 0), (2, 3, 8, 8, 4, 3, 3, 1, 1, 1, 1), (3, 5, 9, 7, 6, 3, 3, 2, 1, 1, 2),
+        (2, 4, 11, 13, 7, 5, 3, 2, 2, 2, 1), (4, 8, 14, 14, 16, 1, 1, 1, 1, 0, 0), (8, 32, 32, 32, 64, 3, 3, 2, 2, 1, 1),
+        (2, 130, 6, 6, 70, 3, 3, 1, 1, 1, 1), (16, 64, 16, 16, 300, 3, 3, 1, 1, 1, 1)]
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("shape", CONV)
+def test_conv2d(E, mode, shape):
+    N, C, H, W, F, KH, KW, sh, sw, ph, pw = shape
+    rs = np.random.RandomState(sum(shape))
+    X, Wt = _prep(mode, rs.standard_normal((N, C, H, W)).astype(np.float32), rs.standard_normal((F, C, KH, KW)).astype(np.float32))
+    R = co.conv2d_forward(X, Wt, sh, sw, ph, pw)
+    assert rel_l2(E.conv2d_forward(X, Wt, sh, sw, ph, pw), R) < TOL[mode]
+    dY, = _prep(mode, rs.standard_normal(R.shape).astype(np.float32))
+    dX, dW = E.conv2d_backward(dY, X, Wt, sh, sw, ph, pw)
+    rX, rW = co.conv2d_backward(dY, X, Wt, sh, sw, ph, pw)
+    assert rel_l2(dX, rX) < TOL[mode] and rel_l2(dW, rW) < TOL[mode]
+
+
+CONVT = [(1, 1, 4, 4, 1, 3, 3, 1, 1, 0, 0), (2, 4, 5, 6, 3, 4, 3, 2, 2, 1, 0), (8, 64, 16, 16, 32, 4, 4, 2, 2, 1, 1),
+         (3, 6, 7, 5, 5, 3, 3, 1, 1, 1, 1), (2, 5, 5, 5, 7, 3, 5, 3, 2, 1, 2), (4, 32, 16, 16, 1, 3, 3, 1, 1, 1, 1)]
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("shape", CONVT)
+def test_conv_transpose2d(E, mode, shape):
+    N, Ci, H, W, Co, KH, KW, sh, sw, ph, pw = shape
+    rs = np.random.RandomState(sum(shape) + 1)
+    X, Wt = _prep(mode, rs.standard_normal((N, Ci, H, W)).astype(np.float32), rs.standard_normal((Ci, Co, KH, KW)).astype(np.float32))
+    R = co.conv_transpose2d_forward(X, Wt, sh, sw, ph, pw)
+    assert rel_l2(E.conv_transpose2d_forward(X, Wt, sh, sw, ph, pw), R) < TOL[mode]
+    dY, = _prep(mode, rs.standard_normal(R.shape).astype(np.float32))
+    dX, dW = E.conv_transpose2d_backward(dY, X, Wt, sh, sw, ph, pw)
+    rX, rW = co.conv_transpose2d_backward(dY, X, Wt, sh, sw, ph, pw)
+    assert rel_l2(dX, rX) < TOL[mode] and rel_l2(dW, rW) < TOL[mode]
+
+
+def test_c5_conv_backward_point_bf16(E):
+    """One point of the Conv2D-backward sweep at reduced batch (C = K = 64, 56x56, 3x3 s1 p1), bf16 operands."""
+    X, Wt, dY = wl.c5_conv_bwd(64, 56, n=4)
+    _prep(1)
+    dX, dW = E.conv2d_backward(dY, X, Wt, 1, 1, 1, 1)
+    rX, rW = co.conv2d_backward(dY, X, Wt, 1, 1, 1, 1)
+    assert rel_l2(dX, rX) < 1e-5 and rel_l2(dW, rW) < 1e-5
+
+
+@pytest.mark.parametrize("name,n", [("c1", 64), ("c3", 32), ("c4", 16)])
+def test_training_step_bf16x3_against_fp32_oracle(E, name, n):
+    """fp32 configurations on the tensor cores (mode 2) against the untouched fp32 step oracle: gate 2e-3."""
+    from ml_framework_b200 import train, seera_cuda as sc
+    sc.set_precision(2)
+    work = wl.WORKLOADS[name]()
+    tr = train.Trainer(work, seed=3)
+    X, Y = work.batch(n, 3)
+    ref = RefNet(work.layers, work.params(3), work.loss, work.opt, co)
+    loss = tr.forward_backward(X, Y)
+    grads = tr.host_grads()
+    tr.opt.step()
+    rl = ref.step(X, Y)
+    assert abs(float(loss.value.to_host_f32()[0]) - rl) <= 2e-3 * max(1.0, abs(rl))
+    worst = 0.0
+    for G, R in zip(grads, ref.grads):
+        if R is not None:
+            worst = max(worst, rel_l2(G[0], R[0]), rel_l2(G[1].ravel(), R[1].ravel()))
+    assert worst < 2e-3, worst
+    for P, R in zip(tr.host_params(), ref.params):
+        if R is not None:
+            assert rel_l2(P[0], R[0]) < 2e-3
+
+
+def test_training_step_bf16_against_matched_oracle(E):
+    """C2 (bf16 inputs, fp32 accumulate) against the step oracle whose GEMM operands carry the same rounding."""
+    from ml_framework_b200 import train, seera_cuda as sc
+    sc.set_precision(1)
+    work = wl.c2_mlp()
+    tr = train.Trainer(work, seed=3)
+    X, Y = work.batch(512, 3)
+    ref = RefNet(work.layers, work.params(3), work.loss, work.opt, co, quant=wl.bf16_round)
+    loss = tr.forward_backward(X, Y)
+    grads = tr.host_grads()
+    tr.opt.step()
+    rl = ref.step(X, Y)
+    assert abs(float(loss.value.to_host_f32()[0]) - rl) <= 2e-3 * max(1.0, abs(rl))
+    for G, R in zip(grads, ref.grads):
+        if R is not None:
+            assert rel_l2(G[0], R[0]) < 2e-3 and rel_l2(G[1].ravel(), R[1].ravel()) < 2e-3
+    for P, R in zip(tr.host_params(), ref.params):
+        if R is not None:
+            assert rel_l2(P[0], R[0]) < 2e-3
