@@ -67,6 +67,10 @@ int         seera_profile_read(uint64_t *launches, double *ms, double *flops);
  *   2 bf16x3: a_hi*b_hi + a_hi*b_lo + a_lo*b_hi on the tensor cores (fp32-class accuracy) */
 int         seera_set_precision(int mode);
 int         seera_get_precision(void);
+/* Engine options by name.  "dense_tma" (default 1): in precision modes 1/2 the Dense GEMMs convert their
+ * operands to bf16 shadows once and feed the tensor cores by TMA; 0 selects the kernel that converts inside
+ * its producer warps (the one the convolution family uses). */
+int         seera_set_option(const char *name, int value);
 /* Status word of the tensor-core kernels: 0 when every bounded wait inside them completed, otherwise
  * the code of the first wait that ran out (1 producer, 2 MMA issuer, 3 epilogue); reading clears it.
  * Synchronises the stream.  -1 if it could not be read. */

@@ -13,6 +13,7 @@ struct Runtime {
     cudaStream_t stream = nullptr;      // the stream every kernel is enqueued on
     cudaStream_t own_stream = nullptr;
     int precision = 0;
+    bool dense_tma = true;              // Dense GEMMs in modes 1/2: TMA-fed kernel (false: in-kernel conversion kernel)
     bool tc_used = false;               // a tensor-core kernel ran since the status word was last read
     int status = 0;
     uint64_t launches = 0;

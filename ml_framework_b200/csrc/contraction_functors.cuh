@@ -109,10 +109,12 @@ struct Col2imByPixel {
 
 // ---- output functors -----------------------------------------------------------------------------------------
 struct StoreDense {        // C[m*ld + n]
+    static constexpr bool kMContiguous = false;
     float *C; long long ld;
     __device__ void operator()(int m, int n, float v) const { C[(long long)m * ld + n] = v; }
 };
 struct StoreNCHW {         // n = (img, p): out[(img*M + m)*P + p]
+    static constexpr bool kMContiguous = false;
     float *out; int M, P;
     __device__ void operator()(int m, int n, float v) const {
         int img = n / P, p = n - img * P;
@@ -123,10 +125,12 @@ struct StoreNCHW {         // n = (img, p): out[(img*M + m)*P + p]
 
 // Output functors for kernels whose M index is the long (pixel / batch-row) dimension.
 struct StoreDenseT {       // C[n*ld + m]
+    static constexpr bool kMContiguous = true;
     float *C; long long ld;
     __device__ void operator()(int m, int n, float v) const { C[(long long)n * ld + m] = v; }
 };
 struct StorePixelRows {    // m = (img, p): out[(img*Nch + n)*P + p]
+    static constexpr bool kMContiguous = true;
     float *out; int Nch, P;
     __device__ void operator()(int m, int n, float v) const {
         int img = m / P, p = m - img * P;

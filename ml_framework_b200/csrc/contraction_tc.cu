@@ -23,97 +23,10 @@
 // all roles leave their loops, and TMEM is still released before the CTA exits.
 #include "common.cuh"
 #include "contraction_functors.cuh"
-#include <cuda_bf16.h>
+#include "tc_epilogue.cuh"
+#include "tc_ptx.cuh"
 
 namespace seera {
-
-constexpr int TC_BM = 128, TC_BK = 64, TC_PRODUCERS = 256, TC_THREADS = 288;
-constexpr unsigned long long TC_WAIT_CLOCKS = 4000000000ull;      // ~2 s at 2 GHz
-
-// ---- PTX wrappers ----------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: false when the budget ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (*abort_flag) return false;
-        if (clock64() - t0 > TC_WAIT_CLOCKS) {
-            *abort_flag = 1;
-            if (status) atomicCAS(status, 0, code);
-            return false;
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// D[tmem] (+)= A[smem desc] * B[smem desc], bf16 inputs, fp32 accumulate, one CTA.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// mbarrier arrives once every MMA issued so far by this thread has finished reading smem / writing TMEM
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-                   "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                   "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile whose rows are 128 bytes (64 bf16) with the 128-byte
-// swizzle; 8-row groups are 1024 bytes apart.  `addr` must be 1024-byte aligned plus a multiple of 32
-// bytes selecting the K=16 slice inside the row.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                           // leading byte offset (unused for this layout)
-    d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                           // descriptor version for sm_100
-    d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor: D fp32, A and B bf16, both K-major, M = 128, N = bn.
-__device__ __forceinline__ uint32_t umma_idesc_bf16(int bn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&v);
-}
 
 // Writes 8 consecutive-k values of one tile row as a 16-byte chunk (and, for bf16x3, the chunk of the
 // rounding residuals) at the swizzled position of (row, kgroup).
@@ -251,23 +164,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_contraction_kernel(AL al, BL
         tc_fence_after();
         if (ok) {
             const int q = warp & 3, half = warp >> 2;
-            const int m = m0 + q * 32 + lane;
             const int cols_per_half = bn >= 64 ? bn / 2 : bn;          // bn = 32: the second warp group has nothing to do
             if (bn >= 64 || half == 0) {
-                for (int c = half * cols_per_half; c < (half + 1) * cols_per_half; c += 32) {
-                    float v[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
-                    if (m < p.M) {
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            int n = n0 + c + j;
-                            if (n < p.N) {
-                                if (p.partial) p.partial[((long long)blockIdx.z * p.M + m) * p.N + n] = v[j];
-                                else cs(m, n, v[j]);
-                            }
-                        }
-                    }
-                }
+                // every MMA has completed, so the operand stages are free: reuse them as per-warp staging
+                float *stage = reinterpret_cast<float *>(smem + (size_t)warp * EPI_WARP_SMEM);
+                int cb = half * cols_per_half;
+                drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)cb, m0 + q * 32, n0, cb, cb + cols_per_half,
+                                  p.M, p.N, cs, p.partial, (long long)blockIdx.z * p.M * p.N, stage);
             }
         }
     }

@@ -5,16 +5,23 @@
 // the same geometry tests before any launch.
 #include "common.cuh"
 #include "internal.h"
+#include <cstring>
 
 using namespace seera;
 
 extern "C" {
 
+int seera_set_option(const char *name, int value) {
+    if (!name) return fail(SEERA_E_ARG, "set_option: null name");
+    if (!strcmp(name, "dense_tma")) { rt().dense_tma = value != 0; return SEERA_OK; }
+    return fail(SEERA_E_ARG, "set_option: unknown option '%s'", name);
+}
+
 int seera_cuda_matmul(const float *A, const float *B, float *C, int M, int N, int K, int Nbatch) {
-    return rt().precision ? seera_tc_matmul(A, B, C, M, N, K, Nbatch) : seera_simt_matmul(A, B, C, M, N, K, Nbatch);
+    return rt().precision ? (rt().dense_tma ? seera_tma_matmul(A, B, C, M, N, K, Nbatch) : seera_tc_matmul(A, B, C, M, N, K, Nbatch)) : seera_simt_matmul(A, B, C, M, N, K, Nbatch);
 }
 int seera_cuda_matmul_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB, int M, int N, int K, int Nbatch) {
-    return rt().precision ? seera_tc_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch) : seera_simt_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch);
+    return rt().precision ? (rt().dense_tma ? seera_tma_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch) : seera_tc_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch)) : seera_simt_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch);
 }
 int seera_cuda_conv2d_fwd(const float *image, const float *kernel, float *out, int batchN, int C, int H, int W, int F, int R, int S,
                           int pad_h, int pad_w, int stride_h, int stride_w) {

@@ -150,6 +150,7 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("profile_enable", [](int on) { ck(seera_profile_enable(on)); });
     m.def("profile_read", []() { uint64_t n = 0; double ms = 0, fl = 0; ck(seera_profile_read(&n, &ms, &fl)); return py::make_tuple(n, ms, fl); });
     m.def("set_precision", [](int mode) { ck(seera_set_precision(mode)); });
+    m.def("set_option", [](const std::string &name, int v) { ck(seera_set_option(name.c_str(), v)); });
     m.def("tc_device_status", []() { return seera_tc_device_status(); });
     m.def("get_precision", []() { return seera_get_precision(); });
     m.def("pool_trim", []() { ck(seera_pool_trim()); });

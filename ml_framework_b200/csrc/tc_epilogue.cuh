@@ -1,0 +1,51 @@
+// Accumulator drain shared by the tensor-core kernels: one warp moves its 32 TMEM lanes (rows) x `ncols`
+// columns to global memory through the output functor.
+#pragma once
+#include "tc_ptx.cuh"
+
+namespace seera {
+
+constexpr int EPI_WARP_SMEM = 32 * 33 * 4;      // bytes of staging per epilogue warp (N-contiguous outputs)
+
+// taddr: TMEM address of (first lane of this warp's quarter, column c_begin); row_base: global row of lane 0.
+// Outputs contiguous along m (NCHW pixels, transposed dense) are stored straight from registers: lanes hold
+// consecutive rows, so each store instruction is one coalesced line.  Outputs contiguous along n (row-major
+// C, split-K partials) go through a 32x33 shared-memory transpose so that lanes hold consecutive columns.
+template <class CS>
+__device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, int col_base, int c_begin, int c_end,
+                                                  int M, int N, const CS &cs, float *partial, long long partial_off,
+                                                  float *stage /* EPI_WARP_SMEM bytes, this warp's own */) {
+    const int lane = threadIdx.x & 31;
+    const bool transpose = partial != nullptr || !CS::kMContiguous;
+    for (int c = c_begin; c < c_end; c += 32) {
+        float v[32];
+        tmem_ld32(taddr + (uint32_t)(c - c_begin), v);
+        if (!transpose) {
+            int m = row_base + lane;
+            if (m < M) {
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    int n = col_base + c + j;
+                    if (n < N) cs(m, n, v[j]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) stage[lane * 33 + j] = v[j];
+            __syncwarp();
+            int n = col_base + c + lane;
+#pragma unroll 4
+            for (int r = 0; r < 32; r++) {
+                int m = row_base + r;
+                if (m < M && n < N) {
+                    float x = stage[r * 33 + lane];
+                    if (partial) partial[partial_off + (long long)m * N + n] = x;
+                    else cs(m, n, x);
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+
+}  // namespace seera
