@@ -64,10 +64,12 @@ int         seera_profile_read(uint64_t *launches, double *ms, double *flops);
 /* Precision of the GEMM / convolution contractions:
  *   0 fp32 CUDA-core tiles (bit-for-bit fp32 products, default for the fp32 configurations)
  *   1 bf16 operands, fp32 accumulate on the tensor cores (one pass)
- *   2 bf16x3: a_hi*b_hi + a_hi*b_lo + a_lo*b_hi on the tensor cores (fp32-class accuracy) */
+ *   2 bf16x3: a_hi*b_hi + a_hi*b_lo + a_lo*b_hi on the tensor cores (16 mantissa bits per operand, ~5e-6)
+ *   3 bf16x6: three-way split hi+lo+lo2, six products (24 mantissa bits per operand, fp32-class); on the
+ *     TMA-fed kernels; the kernel that gathers in its producer warps runs mode 3 as mode 2 */
 int         seera_set_precision(int mode);
 int         seera_get_precision(void);
-/* Engine options by name.  "dense_tma" (default 1): in precision modes 1/2 the Dense GEMMs convert their
+/* Engine options by name.  "conv_tma" (default 1) does the same for the convolution family (TMA im2col); "dense_tma" (default 1): in precision modes 1/2 the Dense GEMMs convert their
  * operands to bf16 shadows once and feed the tensor cores by TMA; 0 selects the kernel that converts inside
  * its producer warps (the one the convolution family uses). */
 int         seera_set_option(const char *name, int value);

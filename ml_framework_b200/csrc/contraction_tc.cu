@@ -202,7 +202,7 @@ int *tc_status_word() {
 template <bool A_KFAST, bool B_KFAST, class AL, class BL, class CS>
 int run_tc(const AL &al, const BL &bl, const CS &cs, int M, int N, int K, bool allow_split, const char *name) {
     if (M < 1 || N < 1 || K < 1) return fail(SEERA_E_ARG, "%s: empty problem %dx%dx%d", name, M, N, K);
-    const bool split3 = rt().precision == 2;
+    const bool split3 = rt().precision >= 2;      // mode 3 (three-way split) runs as the two-way split here
     int bn = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
     if (split3 && bn > 128) bn = 128;
     size_t stage = (size_t)(split3 ? 2 : 1) * (TC_BM * 128 + (size_t)bn * 128);

@@ -1,0 +1,303 @@
+// Convolution family as implicit GEMM on the tensor cores, operands fetched by TMA in im2col mode.
+//
+// Replaces engine_cuda/src/convolution.cu:15-453 and upsampling.cu:15-401 (explicit fp32 column buffers of up
+// to 1.85 GB and per-sample dW scratch of up to 2.4 GB, one warp per 16x16 WMMA tile).  Nothing here writes an
+// im2col matrix: the TMA unit walks the filter windows of a channels-last activation tensor and lands each
+// (tap, 64-channel) slice in shared memory already in the swizzled layout tcgen05.mma reads.
+//
+// The boundary hands over fp32 NCHW, so each call first makes bf16 channels-last shadows (one transposing pass;
+// 1, 2 or 3 copies by precision mode) and small re-ordered weight shadows:
+//     forward   Y[pix, f]   = sum_{tap,c} X_nhwc[window(pix)+tap, c] * Wf[f][tap][c]        A im2col, B rows
+//     dX        dX[pix, c]  = sum_{tap,f} dY_nhwc[window'(pix)+tap, f] * Wd[c][tap'][f]     same kernel on dY with the
+//               (stride 1)                                                                  taps flipped, pad' = K-1-pad
+//     dW        dW[f][tap,c] = sum_pix dY_nhwc[pix, f] * X_nhwc[window(pix)+tap, c]         A = (tap,c) boxes by im2col,
+//                                                                                          B = dY columns, split over pixels
+// A transposed convolution is the same three kernels with the roles exchanged (its forward is a dX, its dX a
+// forward, its dW a dW with X and dY swapped).  Data gradients with stride > 1 go to the kernel that gathers in
+// its producer warps (contraction_tc.cu).  Outputs are written fp32 NCHW straight from TMEM (lanes run along
+// pixels, so stores are coalesced).  Arithmetic follows engine/src/conv_ops.cpp:95-287.
+#include "internal.h"
+#include "tma_gemm_kernel.cuh"
+
+namespace seera {
+
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const int *, const int *, cuuint32_t, cuuint32_t, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeIm2colFn encode_im2col_fn() {
+    static EncodeIm2colFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &p, cudaEnableDefault, &q) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        fn = reinterpret_cast<EncodeIm2colFn>(p);
+    }
+    return fn;
+}
+
+// Channels-last bf16 tensor [NB, H, W, Cp]; windows of R x S taps, lower padding (ph, pw), traversal stride (sh, sw).
+// The box of valid window corners runs from (-pw, -ph) to (W + pw_up - S, H + ph_up - R) with symmetric padding.
+static int make_map_im2col(CUtensorMap *m, const void *base, int NB, int H, int W, int Cp, int R, int S, int sh, int sw, int ph, int pw,
+                           int channels_per_pixel, int pixels_per_column) {
+    EncodeIm2colFn enc = encode_im2col_fn();
+    if (!enc) return fail(SEERA_E_CUDA, "cuTensorMapEncodeIm2col is not available from this driver");
+    cuuint64_t dims[4] = {(cuuint64_t)Cp, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)NB};
+    cuuint64_t strides[3] = {(cuuint64_t)Cp * 2, (cuuint64_t)W * Cp * 2, (cuuint64_t)H * W * Cp * 2};
+    int lower[2] = {-pw, -ph};
+    int upper[2] = {pw - (S - 1), ph - (R - 1)};
+    cuuint32_t estr[4] = {1, (cuuint32_t)sw, (cuuint32_t)sh, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, lower, upper,
+                     (cuuint32_t)channels_per_pixel, (cuuint32_t)pixels_per_column, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(SEERA_E_CUDA, "cuTensorMapEncodeIm2col failed (%d) for %dx%dx%dx%d window %dx%d stride %d,%d pad %d,%d", (int)r, NB, H, W,
+                    Cp, R, S, sh, sw, ph, pw);
+    // Drivers up to CUDA 13.1 mis-encode one descriptor bit for tensors smaller than 128 KiB; clear it as the vendor's
+    // own templates do for the same driver range.
+    int drv = 0;
+    if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 && (size_t)NB * H * W * Cp * 2 < 131072)
+        reinterpret_cast<uint64_t *>(m)[1] &= ~(1ull << 21);
+    return SEERA_OK;
+}
+
+// ---- fp32 NCHW -> bf16 channels-last shadows: [NB, C, P] -> [NB, P, Cp], 32 x 32 tiles through shared memory ----
+template <int NS>
+__global__ void __launch_bounds__(256) shadow_nhwc_kernel(const float *__restrict__ src, int C, int P, int Cp,
+                                                          __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
+                                                          __nv_bfloat16 *__restrict__ d2) {
+    __shared__ float tile[32][33];
+    const int img = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const float *s = src + (long long)img * C * P;
+    for (int i = ty; i < 32; i += 8) {          // read: lanes along pixels
+        int c = c0 + i, p = p0 + tx;
+        tile[i][tx] = (c < C && p < P) ? __ldg(s + (long long)c * P + p) : 0.f;
+    }
+    __syncthreads();
+    for (int i = ty; i < 32; i += 8) {          // write: lanes along channels
+        int p = p0 + i, c = c0 + tx;
+        if (p < P && c < Cp) {
+            float v = tile[tx][i];
+            long long o = ((long long)img * P + p) * Cp + c;
+            __nv_bfloat16 h = __float2bfloat16_rn(v);
+            d0[o] = h;
+            if (NS >= 2) { v -= __bfloat162float(h); __nv_bfloat16 l = __float2bfloat16_rn(v); d1[o] = l;
+                           if (NS >= 3) { v -= __bfloat162float(l); d2[o] = __float2bfloat16_rn(v); } }
+        }
+    }
+}
+
+struct NhwcShadow {
+    __nv_bfloat16 *p[3] = {nullptr, nullptr, nullptr};
+    int NB = 0, H = 0, W = 0, C = 0, Cp = 0;
+};
+static void free_nhwc(NhwcShadow &s) {
+    for (int i = 0; i < 3; i++) { if (s.p[i]) scratch_free(s.p[i]); s.p[i] = nullptr; }
+}
+static int make_nhwc(const float *src, int NB, int C, int H, int W, int ns, NhwcShadow &s) {
+    s.NB = NB; s.H = H; s.W = W; s.C = C; s.Cp = (C + 7) / 8 * 8;
+    size_t bytes = (size_t)NB * H * W * s.Cp * 2;
+    for (int i = 0; i < ns; i++) { s.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!s.p[i]) return SEERA_E_OOM; }
+    int P = H * W;
+    dim3 grid((P + 31) / 32, (s.Cp + 31) / 32, NB);
+    if (grid.z > 65535 || grid.y > 65535) return fail(SEERA_E_LIMIT, "channels-last shadow: batch or channel count too large");
+    cudaStream_t st = rt().stream;
+    if (ns == 1) shadow_nhwc_kernel<1><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
+    else if (ns == 2) shadow_nhwc_kernel<2><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
+    else shadow_nhwc_kernel<3><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, "shadow_nhwc");
+}
+
+// ---- weight shadows: out[o][tap][ip] = W[o*so + i*si + (flip ? taps-1-tap : tap)], zero for i >= I --------------
+template <int NS>
+__global__ void __launch_bounds__(256) shadow_weight_kernel(const float *__restrict__ Wt, int O, int I, int Ip, int taps, long long so,
+                                                            long long si, int flip, __nv_bfloat16 *__restrict__ d0,
+                                                            __nv_bfloat16 *__restrict__ d1, __nv_bfloat16 *__restrict__ d2) {
+    long long total = (long long)O * taps * Ip;
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    for (long long e = tid; e < total; e += nthr) {
+        int i = (int)(e % Ip); long long t2 = e / Ip;
+        int tap = (int)(t2 % taps); int o = (int)(t2 / taps);
+        float v = i < I ? __ldg(Wt + o * so + i * si + (flip ? taps - 1 - tap : tap)) : 0.f;
+        __nv_bfloat16 h = __float2bfloat16_rn(v);
+        d0[e] = h;
+        if (NS >= 2) { v -= __bfloat162float(h); __nv_bfloat16 l = __float2bfloat16_rn(v); d1[e] = l;
+                       if (NS >= 3) { v -= __bfloat162float(l); d2[e] = __float2bfloat16_rn(v); } }
+    }
+}
+// Result is a row-major matrix [O, taps*Ip] (Shadow with ld = cols).
+static int make_weight_shadow(const float *Wt, int O, int I, int taps, long long so, long long si, int flip, int ns, Shadow &s) {
+    int Ip = (I + 7) / 8 * 8;
+    if (int e = alloc_shadow(s, O, taps * Ip, ns)) return e;
+    long long total = (long long)O * taps * Ip;
+    int grid = stride_grid(total);
+    cudaStream_t st = rt().stream;
+    if (ns == 1) shadow_weight_kernel<1><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2]);
+    else if (ns == 2) shadow_weight_kernel<2><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2]);
+    else shadow_weight_kernel<3><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2]);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, "shadow_weight");
+}
+
+// dW element for accumulator row m = (tap, channel) and column n = output-side channel: dW[(n*C + c)*taps + tap]
+struct StoreWgrad {
+    static constexpr bool kMContiguous = true;
+    float *dW; int C, taps, c64;
+    __device__ void operator()(int m, int n, float v) const {
+        int tap = m / c64, c = m - tap * c64;
+        if (c < C) dW[((long long)n * C + c) * taps + tap] = v;
+    }
+};
+
+// Y[NB, F, OH, OW] = conv(X_nhwc, weights Wk[F][tap][Cp]) with window R x S, stride, lower padding.
+static int tma_fprop(const NhwcShadow &x, const Shadow &wk, float *Y, int F, int R, int S, int sh, int sw, int ph, int pw,
+                     int OH, int OW, int ns, const char *name) {
+    TmaGemmParams p{};
+    p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
+    p.M = x.NB * OH * OW; p.N = F;
+    p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
+    p.K = p.taps * p.cchunks * 64;
+    p.OW = OW; p.OHW = OH * OW; p.sw = sw; p.sh = sh; p.pw = pw; p.ph = ph;
+    p.bn = tma_pick_bn(F, ns, 0);
+    TmaMaps maps;
+    for (int i = 0; i < 3; i++) {
+        int j = i < ns ? i : 0;
+        if (int s = make_map_im2col(&maps.a[i], x.p[j], x.NB, x.H, x.W, x.Cp, R, S, sh, sw, ph, pw, 64, TC_BM)) return s;
+        if (int s = make_map_2d(&maps.b[i], wk.p[j], wk.rows, wk.cols, wk.ld, 64, p.bn)) return s;
+    }
+    double flops = 2.0 * p.M * (double)F * x.C * R * S;
+    return launch_tma_gemm(maps, p, StorePixelRows{Y, F, OH * OW}, ns, false, flops, name);
+}
+
+// dW[Fo][C][R][S] = sum over output pixels of dY_nhwc[pix, f] * X_nhwc[window(pix)+tap, c]
+static int tma_wgrad(const NhwcShadow &x, const NhwcShadow &dy, float *dW, int R, int S, int sh, int sw, int ph, int pw, int ns,
+                     const char *name) {
+    const int OH = dy.H, OW = dy.W, F = dy.C;
+    TmaGemmParams p{};
+    p.a_mode = TMA_A_TAPS; p.b_mn = 1;
+    p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
+    p.M = p.taps * p.cchunks * 64; p.N = F;
+    p.K = x.NB * OH * OW;
+    p.OW = OW; p.OHW = OH * OW; p.sw = sw; p.sh = sh; p.pw = pw; p.ph = ph;
+    p.bn = tma_pick_bn(F, ns, 1);
+    TmaMaps maps;
+    for (int i = 0; i < 3; i++) {
+        int j = i < ns ? i : 0;
+        if (int s = make_map_im2col(&maps.a[i], x.p[j], x.NB, x.H, x.W, x.Cp, R, S, sh, sw, ph, pw, 64, 64)) return s;
+        if (int s = make_map_2d(&maps.b[i], dy.p[j], dy.NB * OH * OW, dy.Cp, dy.Cp, 64, 64)) return s;
+    }
+    double flops = 2.0 * p.K * (double)F * x.C * R * S;
+    return launch_tma_gemm(maps, p, StoreWgrad{dW, x.C, R * S, p.cchunks * 64}, ns, true, flops, name);
+}
+
+static bool conv_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
+    return NB >= 1 && C >= 1 && H >= 1 && W >= 1 && F >= 1 && R >= 1 && S >= 1 && sh >= 1 && sw >= 1 && ph >= 0 && pw >= 0 &&
+           (long long)NB * (C > F ? C : F) * H * W * (long long)(sh * sw) < (1LL << 31);
+}
+// limits of the im2col descriptor: traversal strides <= 8, corner offsets within [-128, 127], batch <= 65535 for the shadow grid
+static bool tma_conv_supported(int NB, int R, int S, int sh, int sw, int ph, int pw) {
+    return sh <= 8 && sw <= 8 && ph <= 127 && pw <= 127 && R - 1 - ph <= 127 && S - 1 - pw <= 127 && ph <= R - 1 && pw <= S - 1 &&
+           NB <= 65535;
+}
+
+}  // namespace seera
+
+using namespace seera;
+
+extern "C" {
+
+int seera_tma_conv2d_fwd(const float *X, const float *Wt, float *Y, int NB, int C, int H, int W, int F, int R, int S,
+                         int ph, int pw, int sh, int sw) {
+    SEERA_ENSURE();
+    if (!conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) || !X || !Wt || !Y) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: bad argument");
+    int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
+    if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: kernel larger than padded input");
+    if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return seera_tc_conv2d_fwd(X, Wt, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw);
+    int ns = precision_copies();
+    NhwcShadow xs; Shadow wk;
+    int s = make_nhwc(X, NB, C, H, W, ns, xs);
+    if (!s) s = make_weight_shadow(Wt, F, C, R * S, (long long)C * R * S, R * S, 0, ns, wk);
+    if (!s) s = tma_fprop(xs, wk, Y, F, R, S, sh, sw, ph, pw, OH, OW, ns, "cuda_conv2d_fwd");
+    free_nhwc(xs); free_shadow(wk);
+    return s;
+}
+
+int seera_tma_conv2d_bwd(const float *Wt, const float *X, const float *dY, float *dX, float *dW, int NB, int C, int H, int W,
+                         int F, int R, int S, int sh, int sw, int ph, int pw) {
+    SEERA_ENSURE();
+    if (!conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) || !X || !Wt || !dY) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: bad argument");
+    int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
+    if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: kernel larger than padded input");
+    if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return seera_tc_conv2d_bwd(Wt, X, dY, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw);
+    int ns = precision_copies();
+    NhwcShadow dys, xs; Shadow wd;
+    int s = make_nhwc(dY, NB, F, OH, OW, ns, dys);
+    if (!s && dX) {
+        if (sh == 1 && sw == 1) {     // dX = forward convolution of dY with flipped taps and swapped channel roles, pad' = K-1-pad
+            s = make_weight_shadow(Wt, C, F, R * S, R * S, (long long)C * R * S, 1, ns, wd);
+            if (!s) s = tma_fprop(dys, wd, dX, C, R, S, 1, 1, R - 1 - ph, S - 1 - pw, H, W, ns, "cuda_conv2d_bwd(dX)");
+        } else {
+            s = seera_tc_conv2d_bwd(Wt, X, dY, dX, nullptr, NB, C, H, W, F, R, S, sh, sw, ph, pw);
+        }
+    }
+    if (!s && dW) {
+        s = make_nhwc(X, NB, C, H, W, ns, xs);
+        if (!s) s = tma_wgrad(xs, dys, dW, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dW)");
+    }
+    free_nhwc(dys); free_nhwc(xs); free_shadow(wd);
+    return s;
+}
+
+// Transposed convolution X[NB,Cin,H,W], Wt[Cin,Cout,KH,KW] -> out[NB,Cout,Ho,Wo]: the data gradient of the convolution
+// whose filter bank has Cin filters over Cout channels.
+int seera_tma_convT_fwd(const float *X, const float *Wt, float *out, int NB, int Cin, int H, int W, int Cout, int KH, int KW,
+                        int sh, int sw, int ph, int pw) {
+    SEERA_ENSURE();
+    int Ho = (H - 1) * sh - 2 * ph + KH, Wo = (W - 1) * sw - 2 * pw + KW;
+    if (!conv_ok(NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw) || Ho < 1 || Wo < 1 || !X || !Wt || !out)
+        return fail(SEERA_E_ARG, "cuda_conv2DTranpose_fwd: bad argument");
+    if (sh != 1 || sw != 1 || !tma_conv_supported(NB, KH, KW, sh, sw, ph, pw))
+        return seera_tc_convT_fwd(X, Wt, out, NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw);
+    int ns = precision_copies();
+    NhwcShadow xs; Shadow wd;
+    int taps = KH * KW;
+    int s = make_nhwc(X, NB, Cin, H, W, ns, xs);
+    if (!s) s = make_weight_shadow(Wt, Cout, Cin, taps, taps, (long long)Cout * taps, 1, ns, wd);
+    if (!s) s = tma_fprop(xs, wd, out, Cout, KH, KW, 1, 1, KH - 1 - ph, KW - 1 - pw, Ho, Wo, ns, "cuda_conv2DTranpose_fwd");
+    free_nhwc(xs); free_shadow(wd);
+    return s;
+}
+
+int seera_tma_convT_bwd(const float *Wt, const float *X, const float *dY, float *dX, float *dW, int NB, int Cin, int H, int W,
+                        int Cout, int KH, int KW, int sh, int sw, int ph, int pw) {
+    SEERA_ENSURE();
+    int Ho = (H - 1) * sh - 2 * ph + KH, Wo = (W - 1) * sw - 2 * pw + KW;
+    if (!conv_ok(NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw) || Ho < 1 || Wo < 1 || !X || !Wt || !dY ||
+        (Ho + 2 * ph - KH) / sh + 1 != H || (Wo + 2 * pw - KW) / sw + 1 != W)
+        return fail(SEERA_E_ARG, "cuda_conv2DTranspose_bwd: bad argument");
+    if (!tma_conv_supported(NB, KH, KW, sh, sw, ph, pw))
+        return seera_tc_convT_bwd(Wt, X, dY, dX, dW, NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw);
+    int ns = precision_copies();
+    int taps = KH * KW;
+    NhwcShadow dys, xs; Shadow wk;
+    int s = make_nhwc(dY, NB, Cout, Ho, Wo, ns, dys);
+    if (!s && dX) {      // dX[NB,Cin,H,W] = convolution of dY with Wt read as [F = Cin][C = Cout][KH][KW]
+        s = make_weight_shadow(Wt, Cin, Cout, taps, (long long)Cout * taps, taps, 0, ns, wk);
+        if (!s) s = tma_fprop(dys, wk, dX, Cin, KH, KW, sh, sw, ph, pw, H, W, ns, "cuda_conv2DTranspose_bwd(dX)");
+    }
+    if (!s && dW) {      // dW[Cin][Cout][KH][KW]: weight gradient of that convolution with dY as its input and X as its output gradient
+        s = make_nhwc(X, NB, Cin, H, W, ns, xs);
+        if (!s) s = tma_wgrad(dys, xs, dW, KH, KW, sh, sw, ph, pw, ns, "cuda_conv2DTranspose_bwd(dW)");
+    }
+    free_nhwc(dys); free_nhwc(xs); free_shadow(wk);
+    return s;
+}
+
+}  // extern "C"

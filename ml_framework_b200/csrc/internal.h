@@ -13,6 +13,14 @@ int seera_simt_convT_bwd(const float *Wt, const float *X, const float *dY, float
                          int Cout, int KH, int KW, int sh, int sw, int ph, int pw);
 int seera_tma_matmul(const float *A, const float *B, float *C, int M, int N, int K, int Nbatch);
 int seera_tma_matmul_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB, int M, int N, int K, int Nbatch);
+int seera_tma_conv2d_fwd(const float *X, const float *Wt, float *Y, int NB, int C, int H, int W, int F, int R, int S,
+                         int ph, int pw, int sh, int sw);
+int seera_tma_conv2d_bwd(const float *Wt, const float *X, const float *dY, float *dX, float *dW, int NB, int C, int H, int W,
+                         int F, int R, int S, int sh, int sw, int ph, int pw);
+int seera_tma_convT_fwd(const float *X, const float *Wt, float *out, int NB, int Cin, int H, int W, int Cout, int KH, int KW,
+                        int sh, int sw, int ph, int pw);
+int seera_tma_convT_bwd(const float *Wt, const float *X, const float *dY, float *dX, float *dW, int NB, int Cin, int H, int W,
+                        int Cout, int KH, int KW, int sh, int sw, int ph, int pw);
 int seera_tc_matmul(const float *A, const float *B, float *C, int M, int N, int K, int Nbatch);
 int seera_tc_matmul_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB, int M, int N, int K, int Nbatch);
 int seera_tc_conv2d_fwd(const float *X, const float *Wt, float *Y, int NB, int C, int H, int W, int F, int R, int S,

@@ -158,7 +158,7 @@ int seera_profile_read(uint64_t *launches, double *ms, double *flops) {
 }
 
 int seera_set_precision(int mode) {
-    if (mode < 0 || mode > 2) return fail(SEERA_E_ARG, "seera_set_precision: mode %d", mode);
+    if (mode < 0 || mode > 3) return fail(SEERA_E_ARG, "seera_set_precision: mode %d", mode);
     rt().precision = mode;
     return SEERA_OK;
 }

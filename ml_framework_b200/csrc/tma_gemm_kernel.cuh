@@ -1,0 +1,430 @@
+// TMA-fed tcgen05 GEMM kernel, tensor-map helpers and bf16 shadow conversion shared by the Dense and the
+// convolution entry points.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+#include "contraction_functors.cuh"
+#include "tc_epilogue.cuh"
+#include "tc_ptx.cuh"
+
+namespace seera {
+
+
+// ---- tensor maps -----------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// bf16 row-major matrix [rows, cols] with pitch ld (elements, multiple of 8): 2-D map, inner dimension = cols.
+// Box = box_inner x box_outer elements, 128-byte swizzle, out-of-range elements read as zero.
+inline int make_map_2d(CUtensorMap *m, const void *base, int rows, int cols, int ld, int box_inner, int box_outer) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return fail(SEERA_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SEERA_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for %dx%d ld %d box %dx%d", (int)r, rows, cols, ld,
+                                       box_inner, box_outer);
+    return SEERA_OK;
+}
+
+// ---- fp32 -> bf16 shadows -----------------------------------------------------------------------------------
+// NS = 1: hi = bf16(x).  NS = 2: plus lo = bf16(x - hi).  NS = 3: plus lo2 = bf16(x - hi - lo) (24 mantissa bits).
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t packed, int odd) {
+    return __uint_as_float(odd ? (packed & 0xFFFF0000u) : (packed << 16));
+}
+// Rounds 8 values to bf16 and writes them as one 16-byte chunk; `v` is replaced by the residuals.
+__device__ __forceinline__ uint4 split_chunk(float *v) {
+    uint4 h;
+    h.x = pack_bf16x2(v[0], v[1]); h.y = pack_bf16x2(v[2], v[3]); h.z = pack_bf16x2(v[4], v[5]); h.w = pack_bf16x2(v[6], v[7]);
+    const uint32_t w[4] = {h.x, h.y, h.z, h.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] -= bf16_bits_to_float(w[i >> 1], i & 1);
+    return h;
+}
+
+struct Shadow {
+    __nv_bfloat16 *p[3] = {nullptr, nullptr, nullptr};
+    int rows = 0, cols = 0, ld = 0;
+};
+
+template <int NS>
+__global__ void __launch_bounds__(256) shadow_rows_kernel(const float *__restrict__ src, long long src_ld, int rows, int cols,
+                                                          __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
+                                                          __nv_bfloat16 *__restrict__ d2, int ld) {
+    // one thread per 8 consecutive elements of a row; ld is a multiple of 8 so the 16-byte stores are aligned
+    long long groups_per_row = ld >> 3, total = (long long)rows * groups_per_row;
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    for (long long g = tid; g < total; g += nthr) {
+        int r = (int)(g / groups_per_row), c0 = (int)(g - (long long)r * groups_per_row) * 8;
+        const float *s = src + (long long)r * src_ld + c0;
+        float v[8];
+        if (c0 + 8 <= cols && ((reinterpret_cast<uintptr_t>(s) & 15) == 0)) {
+            float4 a = __ldg(reinterpret_cast<const float4 *>(s)), b = __ldg(reinterpret_cast<const float4 *>(s) + 1);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = (c0 + i < cols) ? __ldg(s + i) : 0.f;
+        }
+        long long o = (long long)r * ld + c0;
+        *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
+        if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
+        if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+    }
+}
+
+inline int precision_copies() { int m = rt().precision; return m < 1 ? 1 : (m > 3 ? 3 : m); }
+
+inline int alloc_shadow(Shadow &s, int rows, int cols, int ns) {
+    s.rows = rows; s.cols = cols; s.ld = (cols + 7) / 8 * 8;
+    for (int i = 0; i < ns; i++) {
+        s.p[i] = (__nv_bfloat16 *)scratch_alloc((size_t)rows * s.ld * 2);
+        if (!s.p[i]) return SEERA_E_OOM;
+    }
+    return SEERA_OK;
+}
+inline void free_shadow(Shadow &s) {
+    for (int i = 0; i < 3; i++) { if (s.p[i]) scratch_free(s.p[i]); s.p[i] = nullptr; }
+}
+// Row-major fp32 [rows, cols] -> bf16 shadows of the same layout (pitch rounded up to 8 elements).
+inline int make_shadow(const float *src, int rows, int cols, int ns, Shadow &s) {
+    if (int e = alloc_shadow(s, rows, cols, ns)) return e;
+    long long groups = (long long)rows * (s.ld / 8);
+    int grid = stride_grid(groups);
+    cudaStream_t st = rt().stream;
+    if (ns == 1) shadow_rows_kernel<1><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
+    else if (ns == 2) shadow_rows_kernel<2><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
+    else shadow_rows_kernel<3><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, "shadow_rows");
+}
+
+// ---- TMA + mbarrier PTX -------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// im2col-mode load from an NHWC tensor: {c, w, h, n} is the channel offset and the position of the filter
+// window's corner for the FIRST pixel of the column; {off_w, off_h} selects the filter tap.  The copy walks
+// pixelsPerColumn window positions (w fastest, then h, then n) and fetches channelsPerPixel channels of each.
+__device__ __forceinline__ void tma_load_im2col(uint32_t dst_smem, const CUtensorMap *map, int c, int w, int h, int n,
+                                                int off_w, int off_h, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6], {%7, %8};"
+                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(c), "r"(w), "r"(h), "r"(n), "r"(bar),
+                   "h"((unsigned short)off_w), "h"((unsigned short)off_h) : "memory");
+}
+
+// MN-major operand tile: 64 contiguous row-index elements (128 bytes) per k line, 8 k lines per 1024-byte
+// atom; atoms of the next 64 row indices start box_bytes later.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t addr, uint32_t box_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((box_bytes >> 4) & 0x3FFF) << 16;   // leading byte offset: next 64 elements along M/N
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset: next 8 k lines
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// How the producer thread forms the A tile of a stage:
+//   TMA_A_ROWS    2-D map of a row-major matrix [M, K], read along its rows (K-major)
+//   TMA_A_COLS    2-D map of a row-major matrix [K, M], read along its columns (MN-major, two 64-wide boxes)
+//   TMA_A_IM2COL  im2col map of an NHWC tensor; M = output pixels, K = (tap, channel): one tap x 64 channels
+//                 per stage (K-major).  B is then [N, (tap, channel)] read along its rows.
+//   TMA_A_TAPS    im2col map of an NHWC tensor; M = (tap, channel), K = output pixels: 64 pixels per stage,
+//                 two boxes of 64 channels (MN-major).  B is then [pixels, N] read along its columns.
+enum { TMA_A_ROWS = 0, TMA_A_COLS = 1, TMA_A_IM2COL = 2, TMA_A_TAPS = 3 };
+
+struct TmaGemmParams {
+    int M, N, K, kchunk, bn, stages;
+    int a_mode, b_mn;        // b_mn = 1: B read along its contiguous row index (MN-major)
+    // convolution geometry for the im2col modes
+    int OW, OHW;             // output width and pixels per image of the traversal
+    int sw, sh, pw, ph;      // window stride and lower padding
+    int S, taps;             // filter width and R*S
+    int cpad, cchunks;       // channel pitch of the weight rows / channels rounded up to 64, in chunks of 64
+    float *partial;
+    int *status;
+};
+
+constexpr int TG_THREADS = 192;
+
+template <int NS, class CS>
+__global__ void __launch_bounds__(TG_THREADS, 1)
+tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
+                const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapB0,
+                const __grid_constant__ CUtensorMap mapB1, const __grid_constant__ CUtensorMap mapB2, CS cs, TmaGemmParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int bn = p.bn, stages = p.stages;
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * bn;
+    const int kbeg = blockIdx.z * p.kchunk, kend = min(p.K, kbeg + p.kchunk);
+    const int ktiles = (kend - kbeg + TC_BK - 1) / TC_BK;
+    const bool a_mn = p.a_mode == TMA_A_COLS || p.a_mode == TMA_A_TAPS;
+
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t a_bytes = TC_BM * 128, b_bytes = (uint32_t)bn * 128;
+    const uint32_t stage_bytes = (uint32_t)NS * (a_bytes + b_bytes);
+    const uint32_t smem0 = smem_u32(smem);
+    auto a_tile = [&](int s, int i) { return smem0 + (uint32_t)s * stage_bytes + (uint32_t)i * a_bytes; };
+    auto b_tile = [&](int s, int i) { return smem0 + (uint32_t)s * stage_bytes + (uint32_t)NS * a_bytes + (uint32_t)i * b_bytes; };
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[8]), accum = smem_u32(&bars[16]);
+    const uint32_t tmem_cols = (uint32_t)(bn < 32 ? 32 : bn);
+
+    if (t == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum, 1);
+        fence_mbar_init();
+        fence_async_smem();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------- TMA producer ----------------
+        const CUtensorMap *mA[3] = {&mapA0, &mapA1, &mapA2};
+        const CUtensorMap *mB[3] = {&mapB0, &mapB1, &mapB2};
+        // im2col, M = pixels: window corner of this tile's first output pixel
+        int pix_img = 0, pix_w = 0, pix_h = 0;
+        if (p.a_mode == TMA_A_IM2COL) {
+            pix_img = m0 / p.OHW;
+            int rem = m0 - pix_img * p.OHW, oh = rem / p.OW, ow = rem - oh * p.OW;
+            pix_w = ow * p.sw - p.pw; pix_h = oh * p.sh - p.ph;
+        }
+        // im2col, M = (tap, channel): the two 64-channel boxes of this tile
+        int box_c[2] = {0, 0}, box_s[2] = {0, 0}, box_r[2] = {0, 0};
+        bool box_ok[2] = {true, true};
+        uint32_t tx_bytes = stage_bytes;
+        if (p.a_mode == TMA_A_TAPS) {
+            int c64 = p.cchunks * 64;
+            for (int b = 0; b < 2; b++) {
+                int mb = m0 + 64 * b, tap = mb / c64;
+                box_ok[b] = tap < p.taps;
+                box_c[b] = mb - tap * c64; box_r[b] = tap / p.S; box_s[b] = tap - box_r[b] * p.S;
+                if (!box_ok[b]) tx_bytes -= (uint32_t)NS * 8192u;
+            }
+        }
+        int issued = 0;
+        for (int kt = 0; kt < ktiles; kt++) {
+            int s = kt % stages;
+            uint32_t ph = (uint32_t)(kt / stages) & 1u;
+            if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, p.status, 1)) break;
+            int k0 = kbeg + kt * TC_BK;
+            uint32_t bar = full0 + 8 * s;
+            mbar_expect_tx(bar, tx_bytes);
+            int bk = k0;                                  // B's coordinate along the contraction
+            if (p.a_mode == TMA_A_ROWS) {
+#pragma unroll
+                for (int i = 0; i < NS; i++) tma_load_2d(a_tile(s, i), mA[i], k0, m0, bar);
+            } else if (p.a_mode == TMA_A_COLS) {
+#pragma unroll
+                for (int i = 0; i < NS; i++)
+                    for (int b = 0; b < 2; b++) tma_load_2d(a_tile(s, i) + b * 8192, mA[i], m0 + 64 * b, k0, bar);
+            } else if (p.a_mode == TMA_A_IM2COL) {
+                int ktile = k0 >> 6, tap = ktile / p.cchunks, c0 = (ktile - tap * p.cchunks) * 64;
+                int r = tap / p.S, sx = tap - r * p.S;
+#pragma unroll
+                for (int i = 0; i < NS; i++) tma_load_im2col(a_tile(s, i), mA[i], c0, pix_w, pix_h, pix_img, sx, r, bar);
+                bk = tap * p.cpad + c0;
+            } else {
+                int img = k0 / p.OHW, rem = k0 - img * p.OHW, oh = rem / p.OW, ow = rem - oh * p.OW;
+                int w = ow * p.sw - p.pw, h = oh * p.sh - p.ph;
+#pragma unroll
+                for (int i = 0; i < NS; i++)
+                    for (int b = 0; b < 2; b++)
+                        if (box_ok[b]) tma_load_im2col(a_tile(s, i) + b * 8192, mA[i], box_c[b], w, h, img, box_s[b], box_r[b], bar);
+            }
+            if (p.b_mn) {
+#pragma unroll
+                for (int i = 0; i < NS; i++)
+                    for (int b = 0; b < bn / 64; b++) tma_load_2d(b_tile(s, i) + b * 8192, mB[i], n0 + 64 * b, bk, bar);
+            } else {
+#pragma unroll
+                for (int i = 0; i < NS; i++) tma_load_2d(b_tile(s, i), mB[i], bk, n0, bar);
+            }
+            issued = kt + 1;
+        }
+        if (*abortp) {
+            // give copies already in flight a bounded chance to land before the CTA's shared memory goes away
+            for (int kt = max(0, issued - stages); kt < issued; kt++) {
+                unsigned long long t0 = clock64();
+                while (!mbar_try_wait(full0 + 8 * (kt % stages), (uint32_t)(kt / stages) & 1u) && clock64() - t0 < TC_WAIT_CLOCKS) {}
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = umma_idesc_bf16(bn) | ((uint32_t)(a_mn ? 1 : 0) << 15) | ((uint32_t)p.b_mn << 16);
+        const uint32_t a_step = a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;   // bytes per K=16 slice
+        // split products kept: hi*hi | + hi*lo, lo*hi | + hi*lo2, lo2*hi, lo*lo
+        constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
+        const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
+        bool alive = true;
+        uint32_t acc = 0;
+        for (int kt = 0; kt < ktiles && alive; kt++) {
+            int s = kt % stages;
+            uint32_t ph = (uint32_t)(kt / stages) & 1u;
+            alive = mbar_wait(full0 + 8 * s, ph, abortp, p.status, 2);
+            if (!alive) break;
+            tc_fence_after();
+#pragma unroll
+            for (int j = 0; j < TC_BK / 16; j++) {
+                uint64_t da[NS], db[NS];
+#pragma unroll
+                for (int i = 0; i < NS; i++) {
+                    uint32_t aa = a_tile(s, i) + j * a_step, ba = b_tile(s, i) + j * b_step;
+                    da[i] = a_mn ? umma_desc_sw128_mn(aa, 8192) : umma_desc_sw128(aa);
+                    db[i] = p.b_mn ? umma_desc_sw128_mn(ba, 8192) : umma_desc_sw128(ba);
+                }
+#pragma unroll
+                for (int q = 0; q < NPROD; q++) {
+                    umma_bf16(tmem_base, da[pa[q]], db[pb[q]], idesc, acc);
+                    acc = 1;
+                }
+            }
+            umma_commit(empty0 + 8 * s);
+        }
+        if (alive) umma_commit(accum);
+    } else if (warp >= 2) {
+        // ---------------- epilogue: warp w drains TMEM lane quarter w % 4 ----------------
+        bool ok = mbar_wait(accum, 0, abortp, p.status, 3);
+        tc_fence_after();
+        if (ok) {
+            // every MMA has completed, so the operand stages are free: reuse them as per-warp staging
+            const int q = warp & 3;
+            float *stage = reinterpret_cast<float *>(smem + (size_t)(warp - 2) * EPI_WARP_SMEM);
+            drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16), m0 + q * 32, n0, 0, bn, p.M, p.N, cs, p.partial,
+                              (long long)blockIdx.z * p.M * p.N, stage);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+template <class CS>
+__global__ void __launch_bounds__(256) tma_splitk_reduce_kernel(const float *__restrict__ partial, CS cs, int M, int N, int splits) {
+    long long total = (long long)M * N;
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    for (long long i = tid; i < total; i += nthr) {
+        float s = 0.f;
+        for (int z = 0; z < splits; z++) s += partial[(long long)z * total + i];
+        cs((int)(i / N), (int)(i % N), s);
+    }
+}
+
+int *tc_status_word();
+
+struct TmaMaps { CUtensorMap a[3], b[3]; };
+
+inline int tma_pick_bn(int N, int ns, int b_mn) {
+    int bn = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
+    if (b_mn && bn < 64) bn = 64;
+    if (ns >= 2 && bn > 128) bn = 128;
+    return bn;
+}
+
+// Launches the kernel on prepared tensor maps.  p.M, p.N, p.K (contraction length in elements), a_mode, b_mn, bn
+// and the geometry fields must be set; kchunk, stages, partial and status are filled here.
+template <class CS>
+int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, bool allow_split, double flops, const char *name) {
+    size_t stage = (size_t)ns * (TC_BM * 128 + (size_t)p.bn * 128);
+    int stages = (int)((200 * 1024) / stage);
+    if (stages > 8) stages = 8;
+    if (stages < 2) return fail(SEERA_E_LIMIT, "%s: tile does not fit shared memory", name);
+    size_t smem = stage * stages + 1024;
+    long long tiles = (long long)((p.M + TC_BM - 1) / TC_BM) * ((p.N + p.bn - 1) / p.bn);
+    int splits = 1;
+    if (allow_split) {
+        long long want = (rt().sm_count + tiles - 1) / tiles;
+        long long maxs = p.K / (TC_BK * 4);
+        splits = (int)(want < maxs ? want : maxs);
+        if (splits < 1) splits = 1;
+        if (splits > 256) splits = 256;
+    }
+    p.kchunk = ((p.K + splits - 1) / splits + TC_BK - 1) / TC_BK * TC_BK;
+    splits = (p.K + p.kchunk - 1) / p.kchunk;
+    p.stages = stages;
+    p.status = tc_status_word();
+    p.partial = nullptr;
+    if (splits > 1) {
+        p.partial = (float *)scratch_alloc((size_t)splits * p.M * p.N * sizeof(float));
+        if (!p.partial) return SEERA_E_OOM;
+    }
+    dim3 grid((p.M + TC_BM - 1) / TC_BM, (p.N + p.bn - 1) / p.bn, splits);
+    cudaStream_t st = rt().stream;
+    cudaError_t e;
+    profile_begin();
+#define SEERA_TMA_LAUNCH(NSV)                                                                                              \
+    {                                                                                                                      \
+        auto kern = tma_gemm_kernel<NSV, CS>;                                                                              \
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                            \
+        if (e == cudaSuccess) {                                                                                            \
+            kern<<<grid, TG_THREADS, smem, st>>>(maps.a[0], maps.a[1], maps.a[2], maps.b[0], maps.b[1], maps.b[2], cs, p); \
+            e = cudaGetLastError();                                                                                        \
+        }                                                                                                                  \
+    }
+    if (ns == 1) SEERA_TMA_LAUNCH(1) else if (ns == 2) SEERA_TMA_LAUNCH(2) else SEERA_TMA_LAUNCH(3)
+#undef SEERA_TMA_LAUNCH
+    count_launch();
+    if (e == cudaSuccess && p.partial) {
+        tma_splitk_reduce_kernel<<<stride_grid((long long)p.M * p.N), 256, 0, st>>>(p.partial, cs, p.M, p.N, splits);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    if (p.partial) scratch_free(p.partial);
+    profile_end(flops);
+    rt().tc_used = true;
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
+}
+
+// Dense: A operand shadow `sa`; a_mn = 0: sa is [M, K] (read along its rows); a_mn = 1: sa is [K, M].  Likewise B with N.
+template <class CS>
+int run_tma_gemm(const Shadow &sa, int a_mn, const Shadow &sb, int b_mn, const CS &cs, int M, int N, int K,
+                 bool allow_split, const char *name) {
+    const int ns = precision_copies();
+    TmaGemmParams p{};
+    p.M = M; p.N = N; p.K = K; p.a_mode = a_mn ? TMA_A_COLS : TMA_A_ROWS; p.b_mn = b_mn;
+    p.bn = tma_pick_bn(N, ns, b_mn);
+    TmaMaps maps;
+    for (int i = 0; i < 3; i++) {
+        int j = i < ns ? i : 0;
+        // K-major: inner dimension = K (cols of the shadow), box 64 x rows-of-tile; MN-major: inner = M/N, box 64 x 64 k lines
+        if (int s = make_map_2d(&maps.a[i], sa.p[j], sa.rows, sa.cols, sa.ld, 64, a_mn ? 64 : TC_BM)) return s;
+        if (int s = make_map_2d(&maps.b[i], sb.p[j], sb.rows, sb.cols, sb.ld, 64, b_mn ? 64 : p.bn)) return s;
+    }
+    return launch_tma_gemm(maps, p, cs, ns, allow_split, 2.0 * M * N * (double)K, name);
+}
+
+}  // namespace seera
