@@ -88,6 +88,15 @@ int   seera_cuda_memcopy_devicetodevice(void *dst, const void *src, int num_elem
 int   seera_cuda_memset(void *ptr, int value, size_t n_bytes);                     /* :65 */
 int   seera_pool_trim(void);                        /* releases cached blocks to the driver         */
 size_t seera_pool_bytes_reserved(void);
+/* Stream capture of a whole step into a CUDA graph.  Between graph_begin and graph_end every call of this
+ * library is recorded instead of executed; blocks the recorded work allocates stay reserved for the graph
+ * (they are written again by every replay) until graph_destroy.  Run the step eagerly at least once first.
+ * No call that reads back to the host (seera_to_host, seera_synchronize) may be made while capturing. */
+int   seera_graph_begin(void);
+void *seera_graph_end(void);                        /* NULL on failure */
+int   seera_graph_launch(void *graph);
+int   seera_graph_destroy(void *graph);
+int   seera_is_capturing(void);
 void *seera_host_alloc_pinned(size_t n_bytes);      /* page-locked staging for callers that time H2D */
 int   seera_host_free_pinned(void *p);
 
@@ -213,6 +222,11 @@ int seera_mse_fwd_bwd(const float *p, const float *y, float *partials, float *lo
 int seera_adam_step(float *w, const float *g, float *m, float *v, int n, float lr, float beta1, float omb1,
                     float beta2, float omb2, float eps, float c1, float c2, float grad_scale);
 int seera_sgd_step(float *w, const float *g, float *vel, int n, float lr, float momentum, float grad_scale);
+/* The same updates with the scalars read from DEVICE memory at run time, so a captured graph can be replayed
+ * with a new step count: hyper = {lr, beta1, 1-beta1, beta2, 1-beta2, eps, 1-beta1^t, 1-beta2^t, grad_scale}
+ * for Adam, {lr, momentum, grad_scale} for SGD. */
+int seera_adam_step_dev(float *w, const float *g, float *m, float *v, int n, const float *hyper);
+int seera_sgd_step_dev(float *w, const float *g, float *vel, int n, const float *hyper);
 
 #ifdef __cplusplus
 }

@@ -15,6 +15,7 @@ struct Runtime {
     int precision = 0;
     bool dense_tma = true;              // Dense GEMMs in modes 1/2: TMA-fed kernel (false: in-kernel conversion kernel)
     bool conv_tma = true;               // convolutions in modes 1-3: TMA im2col kernel (false: in-kernel gather kernel)
+    bool capturing = false;             // a stream capture (seera_graph_begin) is open
     bool tc_used = false;               // a tensor-core kernel ran since the status word was last read
     int status = 0;
     uint64_t launches = 0;

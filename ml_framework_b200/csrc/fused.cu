@@ -271,6 +271,19 @@ __global__ void __launch_bounds__(256) adam_kernel(float *__restrict__ w, const 
     }
 }
 
+__global__ void __launch_bounds__(256) adam_dev_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ m,
+                                                       float *__restrict__ v, long long n, const float *__restrict__ h) {
+    AdamArgs a{h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8]};
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    for (long long i = tid; i < n; i += nthr) adam_one(w[i], g[i], m[i], v[i], a);
+}
+__global__ void __launch_bounds__(256) sgd_dev_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ vel,
+                                                      long long n, const float *__restrict__ h) {
+    float lr = h[0], mu = h[1], gs = h[2];
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    for (long long i = tid; i < n; i += nthr) { vel[i] = mu * vel[i] + lr * (g[i] * gs); w[i] -= vel[i]; }
+}
+
 __global__ void __launch_bounds__(256) sgd_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ vel,
                                                   long long n, bool vec, float lr, float mu, float gs) {
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
@@ -401,6 +414,23 @@ int seera_adam_step(float *w, const float *g, float *m, float *v, int n, float l
     AdamArgs a{lr, beta1, omb1, beta2, omb2, eps, c1, c2, grad_scale};
     adam_kernel<<<stride_grid(vec ? (n + 3) / 4 : n), 256, 0, rt().stream>>>(w, g, m, v, n, vec, a);
     SEERA_LAUNCH_CHECK("adam_step");
+    return SEERA_OK;
+}
+
+int seera_adam_step_dev(float *w, const float *g, float *m, float *v, int n, const float *hyper) {
+    SEERA_ENSURE();
+    if (n < 0 || (n > 0 && (!w || !g || !m || !v || !hyper))) return fail(SEERA_E_ARG, "adam_step_dev: bad argument");
+    if (n == 0) return SEERA_OK;
+    adam_dev_kernel<<<stride_grid(n), 256, 0, rt().stream>>>(w, g, m, v, n, hyper);
+    SEERA_LAUNCH_CHECK("adam_step_dev");
+    return SEERA_OK;
+}
+int seera_sgd_step_dev(float *w, const float *g, float *vel, int n, const float *hyper) {
+    SEERA_ENSURE();
+    if (n < 0 || (n > 0 && (!w || !g || !vel || !hyper))) return fail(SEERA_E_ARG, "sgd_step_dev: bad argument");
+    if (n == 0) return SEERA_OK;
+    sgd_dev_kernel<<<stride_grid(n), 256, 0, rt().stream>>>(w, g, vel, n, hyper);
+    SEERA_LAUNCH_CHECK("sgd_step_dev");
     return SEERA_OK;
 }
 

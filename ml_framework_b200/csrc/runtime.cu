@@ -37,10 +37,22 @@ int ensure_init() {
 }
 
 namespace {
+struct GraphRec {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<std::pair<void *, size_t>> blocks;      // every block handed out while the graph was captured
+    uint64_t kernels = 0;                               // kernel launches recorded in the graph
+    uint64_t launches_at_begin = 0;
+};
 struct Pool {
     std::map<size_t, std::vector<void *>> free_lists;   // rounded size -> cached blocks
     std::unordered_map<void *, size_t> live;            // every block handed out -> rounded size
     size_t reserved = 0;
+    // stream capture: blocks used inside a captured step stay reserved for the graph that replays it
+    bool capturing = false;
+    std::map<size_t, std::vector<void *>> cap_free;     // freed during capture: reusable only inside the capture
+    std::unordered_map<void *, GraphRec *> owner;       // block -> graph whose replay writes it
+    GraphRec *cur = nullptr;
 };
 Pool &pool() { static Pool p; return p; }
 
@@ -57,7 +69,7 @@ static Prof &prof() { static Prof p; return p; }
 
 void profile_begin() {
     Prof &p = prof();
-    if (!p.on) return;
+    if (!p.on || rt().capturing) return;
     cudaEventCreate(&p.pending);
     cudaEventRecord(p.pending, rt().stream);
 }
@@ -101,6 +113,7 @@ int seera_init(int device) {
 
 int seera_synchronize(void) {
     SEERA_ENSURE();
+    if (rt().capturing) return fail(SEERA_E_ARG, "synchronize: not allowed while a graph is being captured");
     return check_cuda(cudaStreamSynchronize(rt().stream), "cudaStreamSynchronize");
 }
 
@@ -168,11 +181,21 @@ void *seera_cuda_malloc(size_t n_bytes) {
     if (ensure_init()) return nullptr;
     Pool &p = pool();
     size_t sz = round_size(n_bytes);
+    if (p.capturing) {
+        auto ic = p.cap_free.find(sz);
+        if (ic != p.cap_free.end() && !ic->second.empty()) {
+            void *b = ic->second.back();
+            ic->second.pop_back();
+            p.live[b] = sz;
+            return b;
+        }
+    }
     auto it = p.free_lists.find(sz);
     if (it != p.free_lists.end() && !it->second.empty()) {
         void *b = it->second.back();
         it->second.pop_back();
         p.live[b] = sz;
+        if (p.capturing) { p.owner[b] = p.cur; p.cur->blocks.push_back({b, sz}); }
         return b;
     }
     void *b = nullptr;
@@ -189,6 +212,7 @@ void *seera_cuda_malloc(size_t n_bytes) {
     }
     p.reserved += sz;
     p.live[b] = sz;
+    if (p.capturing) { p.owner[b] = p.cur; p.cur->blocks.push_back({b, sz}); }
     return b;
 }
 void *seera_cuda_malloc_f32(int n) { return n < 0 ? nullptr : seera_cuda_malloc((size_t)n * 4); }
@@ -200,7 +224,13 @@ int seera_cuda_free(void *ptr) {
     Pool &p = pool();
     auto it = p.live.find(ptr);
     if (it == p.live.end()) return fail(SEERA_E_ARG, "cuda_free(%p): not a live block of this pool", ptr);
-    p.free_lists[it->second].push_back(ptr);
+    auto ow = p.owner.find(ptr);
+    if (ow != p.owner.end()) {
+        // a block a captured graph writes on every replay: reusable inside that capture, otherwise kept aside
+        if (p.capturing && ow->second == p.cur) p.cap_free[it->second].push_back(ptr);
+    } else {
+        p.free_lists[it->second].push_back(ptr);
+    }
     p.live.erase(it);
     return SEERA_OK;
 }
@@ -215,6 +245,64 @@ int seera_pool_trim(void) {
     return SEERA_OK;
 }
 size_t seera_pool_bytes_reserved(void) { return pool().reserved; }
+
+int seera_graph_begin(void) {
+    SEERA_ENSURE();
+    Pool &p = pool();
+    if (p.capturing) return fail(SEERA_E_ARG, "graph_begin: a capture is already open");
+    if (int s = check_cuda(cudaStreamBeginCapture(rt().stream, cudaStreamCaptureModeRelaxed), "cudaStreamBeginCapture")) return s;
+    p.cur = new GraphRec();
+    p.cur->launches_at_begin = rt().launches;
+    p.cap_free.clear();
+    p.capturing = true;
+    rt().capturing = true;
+    return SEERA_OK;
+}
+
+void *seera_graph_end(void) {
+    Pool &p = pool();
+    if (!p.capturing) { fail(SEERA_E_ARG, "graph_end: no capture is open"); return nullptr; }
+    p.capturing = false;
+    rt().capturing = false;
+    p.cap_free.clear();
+    GraphRec *g = p.cur;
+    p.cur = nullptr;
+    g->kernels = rt().launches - g->launches_at_begin;
+    rt().launches = g->launches_at_begin;               // recorded, not executed
+    cudaError_t e = cudaStreamEndCapture(rt().stream, &g->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e != cudaSuccess) {
+        check_cuda(e, "graph_end");
+        cudaGetLastError();
+        seera_graph_destroy(g);
+        return nullptr;
+    }
+    return g;
+}
+
+int seera_graph_launch(void *graph) {
+    SEERA_ENSURE();
+    GraphRec *g = static_cast<GraphRec *>(graph);
+    if (!g || !g->exec) return fail(SEERA_E_ARG, "graph_launch: not a captured graph");
+    rt().launches += g->kernels;
+    return check_cuda(cudaGraphLaunch(g->exec, rt().stream), "cudaGraphLaunch");
+}
+
+int seera_graph_destroy(void *graph) {
+    GraphRec *g = static_cast<GraphRec *>(graph);
+    if (!g) return SEERA_OK;
+    Pool &p = pool();
+    if (rt().stream) cudaStreamSynchronize(rt().stream);
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    for (auto &b : g->blocks) {
+        p.owner.erase(b.first);
+        if (!p.live.count(b.first)) p.free_lists[b.second].push_back(b.first);   // idle: back to the general pool
+    }
+    delete g;
+    return SEERA_OK;
+}
+int seera_is_capturing(void) { return pool().capturing ? 1 : 0; }
 
 void *seera_host_alloc_pinned(size_t n) {
     if (ensure_init()) return nullptr;
@@ -252,6 +340,7 @@ int seera_upload(void *dev, const void *host, size_t n_bytes) {
 int seera_to_host(void *host, const void *dev, size_t n_bytes) {
     SEERA_ENSURE();
     if (!dev || !host) return fail(SEERA_E_ARG, "to_host: null");
+    if (rt().capturing) return fail(SEERA_E_ARG, "to_host: not allowed while a graph is being captured");
     if (int s = check_cuda(cudaMemcpyAsync(host, dev, n_bytes, cudaMemcpyDeviceToHost, rt().stream), "cudaMemcpyAsync d2h")) return s;
     return check_cuda(cudaStreamSynchronize(rt().stream), "cudaStreamSynchronize");
 }

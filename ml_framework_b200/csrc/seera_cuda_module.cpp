@@ -150,6 +150,15 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("profile_enable", [](int on) { ck(seera_profile_enable(on)); });
     m.def("profile_read", []() { uint64_t n = 0; double ms = 0, fl = 0; ck(seera_profile_read(&n, &ms, &fl)); return py::make_tuple(n, ms, fl); });
     m.def("set_precision", [](int mode) { ck(seera_set_precision(mode)); });
+    m.def("graph_begin", []() { ck(seera_graph_begin()); });
+    m.def("graph_end", []() { return ckp(seera_graph_end()); });
+    m.def("graph_launch", [](uptr g) { ck(seera_graph_launch(P<void>(g))); });
+    m.def("graph_destroy", [](uptr g) { ck(seera_graph_destroy(P<void>(g))); });
+    m.def("is_capturing", []() { return seera_is_capturing() != 0; });
+    m.def("cuda_adam_step_dev", [](uptr w, uptr g, uptr mm, uptr v, int n, uptr h) {
+        ck(seera_adam_step_dev(P<F>(w), P<const F>(g), P<F>(mm), P<F>(v), n, P<const F>(h))); });
+    m.def("cuda_sgd_step_dev", [](uptr w, uptr g, uptr vel, int n, uptr h) {
+        ck(seera_sgd_step_dev(P<F>(w), P<const F>(g), P<F>(vel), n, P<const F>(h))); });
     m.def("set_option", [](const std::string &name, int v) { ck(seera_set_option(name.c_str(), v)); });
     m.def("tc_device_status", []() { return seera_tc_device_status(); });
     m.def("get_precision", []() { return seera_get_precision(); });

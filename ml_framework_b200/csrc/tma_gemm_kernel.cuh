@@ -159,7 +159,7 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t addr, uint32_t b
 enum { TMA_A_ROWS = 0, TMA_A_COLS = 1, TMA_A_IM2COL = 2, TMA_A_TAPS = 3 };
 
 struct TmaGemmParams {
-    int M, N, K, kchunk, bn, stages;
+    int M, N, K, kchunk, splits, bn, stages;
     int a_mode, b_mn;        // b_mn = 1: B read along its contiguous row index (MN-major)
     // convolution geometry for the im2col modes
     int OW, OHW;             // output width and pixels per image of the traversal
@@ -172,21 +172,23 @@ struct TmaGemmParams {
 
 constexpr int TG_THREADS = 192;
 
+// Persistent kernel: each CTA walks tiles  id = blockIdx.x, blockIdx.x + gridDim.x, ...  (m-tile fastest, then n-tile,
+// then K split).  The operand ring keeps streaming across tile boundaries and the accumulator is double-buffered in
+// TMEM (2 x bn columns), so the epilogue of tile i overlaps the main loop of tile i+1.
 template <int NS, class CS>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
                 const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapB0,
                 const __grid_constant__ CUtensorMap mapB1, const __grid_constant__ CUtensorMap mapB2, CS cs, TmaGemmParams p) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1];
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 4];      // full[8], empty[8], tfull[2], tempty[2]
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int bn = p.bn, stages = p.stages;
-    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * bn;
-    const int kbeg = blockIdx.z * p.kchunk, kend = min(p.K, kbeg + p.kchunk);
-    const int ktiles = (kend - kbeg + TC_BK - 1) / TC_BK;
+    const int mtiles = (p.M + TC_BM - 1) / TC_BM, ntiles = (p.N + bn - 1) / bn;
+    const int total_tiles = mtiles * ntiles * p.splits;
     const bool a_mn = p.a_mode == TMA_A_COLS || p.a_mode == TMA_A_TAPS;
 
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -195,13 +197,14 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
     const uint32_t smem0 = smem_u32(smem);
     auto a_tile = [&](int s, int i) { return smem0 + (uint32_t)s * stage_bytes + (uint32_t)i * a_bytes; };
     auto b_tile = [&](int s, int i) { return smem0 + (uint32_t)s * stage_bytes + (uint32_t)NS * a_bytes + (uint32_t)i * b_bytes; };
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[8]), accum = smem_u32(&bars[16]);
-    const uint32_t tmem_cols = (uint32_t)(bn < 32 ? 32 : bn);
+    unsigned char *epi_smem = smem + (size_t)stages * stage_bytes;   // 4 x EPI_WARP_SMEM after the ring
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[8]), tfull0 = smem_u32(&bars[16]), tempty0 = smem_u32(&bars[18]);
+    const uint32_t tmem_cols = (uint32_t)(2 * bn < 32 ? 32 : 2 * bn);
 
     if (t == 0) {
         abort_flag = 0;
         for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(accum, 1);
+        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
         fence_mbar_init();
         fence_async_smem();
     }
@@ -212,75 +215,90 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
     const uint32_t tmem_base = tmem_base_slot;
     volatile int *abortp = &abort_flag;
 
+    // tile id -> origin and K range
+    auto tile_origin = [&](int id, int &m0, int &n0, int &kbeg, int &ktiles, int &z) {
+        int mt = id % mtiles, rest = id / mtiles, nt = rest % ntiles;
+        z = rest / ntiles;
+        m0 = mt * TC_BM; n0 = nt * bn;
+        kbeg = z * p.kchunk;
+        int kend = min(p.K, kbeg + p.kchunk);
+        ktiles = (kend - kbeg + TC_BK - 1) / TC_BK;
+    };
+
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
         const CUtensorMap *mA[3] = {&mapA0, &mapA1, &mapA2};
         const CUtensorMap *mB[3] = {&mapB0, &mapB1, &mapB2};
-        // im2col, M = pixels: window corner of this tile's first output pixel
-        int pix_img = 0, pix_w = 0, pix_h = 0;
-        if (p.a_mode == TMA_A_IM2COL) {
-            pix_img = m0 / p.OHW;
-            int rem = m0 - pix_img * p.OHW, oh = rem / p.OW, ow = rem - oh * p.OW;
-            pix_w = ow * p.sw - p.pw; pix_h = oh * p.sh - p.ph;
-        }
-        // im2col, M = (tap, channel): the two 64-channel boxes of this tile
-        int box_c[2] = {0, 0}, box_s[2] = {0, 0}, box_r[2] = {0, 0};
-        bool box_ok[2] = {true, true};
-        uint32_t tx_bytes = stage_bytes;
-        if (p.a_mode == TMA_A_TAPS) {
-            int c64 = p.cchunks * 64;
-            for (int b = 0; b < 2; b++) {
-                int mb = m0 + 64 * b, tap = mb / c64;
-                box_ok[b] = tap < p.taps;
-                box_c[b] = mb - tap * c64; box_r[b] = tap / p.S; box_s[b] = tap - box_r[b] * p.S;
-                if (!box_ok[b]) tx_bytes -= (uint32_t)NS * 8192u;
+        int it = 0, issued_from = 0;
+        bool alive = true;
+        for (int id = blockIdx.x; id < total_tiles && alive; id += gridDim.x) {
+            int m0, n0, kbeg, ktiles, z;
+            tile_origin(id, m0, n0, kbeg, ktiles, z);
+            // im2col, M = pixels: window corner of this tile's first output pixel
+            int pix_img = 0, pix_w = 0, pix_h = 0;
+            if (p.a_mode == TMA_A_IM2COL) {
+                pix_img = m0 / p.OHW;
+                int rem = m0 - pix_img * p.OHW, oh = rem / p.OW, ow = rem - oh * p.OW;
+                pix_w = ow * p.sw - p.pw; pix_h = oh * p.sh - p.ph;
             }
-        }
-        int issued = 0;
-        for (int kt = 0; kt < ktiles; kt++) {
-            int s = kt % stages;
-            uint32_t ph = (uint32_t)(kt / stages) & 1u;
-            if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, p.status, 1)) break;
-            int k0 = kbeg + kt * TC_BK;
-            uint32_t bar = full0 + 8 * s;
-            mbar_expect_tx(bar, tx_bytes);
-            int bk = k0;                                  // B's coordinate along the contraction
-            if (p.a_mode == TMA_A_ROWS) {
-#pragma unroll
-                for (int i = 0; i < NS; i++) tma_load_2d(a_tile(s, i), mA[i], k0, m0, bar);
-            } else if (p.a_mode == TMA_A_COLS) {
-#pragma unroll
-                for (int i = 0; i < NS; i++)
-                    for (int b = 0; b < 2; b++) tma_load_2d(a_tile(s, i) + b * 8192, mA[i], m0 + 64 * b, k0, bar);
-            } else if (p.a_mode == TMA_A_IM2COL) {
-                int ktile = k0 >> 6, tap = ktile / p.cchunks, c0 = (ktile - tap * p.cchunks) * 64;
-                int r = tap / p.S, sx = tap - r * p.S;
-#pragma unroll
-                for (int i = 0; i < NS; i++) tma_load_im2col(a_tile(s, i), mA[i], c0, pix_w, pix_h, pix_img, sx, r, bar);
-                bk = tap * p.cpad + c0;
-            } else {
-                int img = k0 / p.OHW, rem = k0 - img * p.OHW, oh = rem / p.OW, ow = rem - oh * p.OW;
-                int w = ow * p.sw - p.pw, h = oh * p.sh - p.ph;
-#pragma unroll
-                for (int i = 0; i < NS; i++)
-                    for (int b = 0; b < 2; b++)
-                        if (box_ok[b]) tma_load_im2col(a_tile(s, i) + b * 8192, mA[i], box_c[b], w, h, img, box_s[b], box_r[b], bar);
+            // im2col, M = (tap, channel): the two 64-channel boxes of this tile
+            int box_c[2] = {0, 0}, box_s[2] = {0, 0}, box_r[2] = {0, 0};
+            bool box_ok[2] = {true, true};
+            uint32_t tx_bytes = stage_bytes;
+            if (p.a_mode == TMA_A_TAPS) {
+                int c64 = p.cchunks * 64;
+                for (int b = 0; b < 2; b++) {
+                    int mb = m0 + 64 * b, tap = mb / c64;
+                    box_ok[b] = tap < p.taps;
+                    box_c[b] = mb - tap * c64; box_r[b] = tap / p.S; box_s[b] = tap - box_r[b] * p.S;
+                    if (!box_ok[b]) tx_bytes -= (uint32_t)NS * 8192u;
+                }
             }
-            if (p.b_mn) {
+            for (int kt = 0; kt < ktiles; kt++, it++) {
+                int s = it % stages;
+                uint32_t ph = (uint32_t)(it / stages) & 1u;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, p.status, 1)) { alive = false; break; }
+                int k0 = kbeg + kt * TC_BK;
+                uint32_t bar = full0 + 8 * s;
+                mbar_expect_tx(bar, tx_bytes);
+                int bk = k0;                                  // B's coordinate along the contraction
+                if (p.a_mode == TMA_A_ROWS) {
 #pragma unroll
-                for (int i = 0; i < NS; i++)
-                    for (int b = 0; b < bn / 64; b++) tma_load_2d(b_tile(s, i) + b * 8192, mB[i], n0 + 64 * b, bk, bar);
-            } else {
+                    for (int i = 0; i < NS; i++) tma_load_2d(a_tile(s, i), mA[i], k0, m0, bar);
+                } else if (p.a_mode == TMA_A_COLS) {
 #pragma unroll
-                for (int i = 0; i < NS; i++) tma_load_2d(b_tile(s, i), mB[i], bk, n0, bar);
+                    for (int i = 0; i < NS; i++)
+                        for (int b = 0; b < 2; b++) tma_load_2d(a_tile(s, i) + b * 8192, mA[i], m0 + 64 * b, k0, bar);
+                } else if (p.a_mode == TMA_A_IM2COL) {
+                    int ktile = k0 >> 6, tap = ktile / p.cchunks, c0 = (ktile - tap * p.cchunks) * 64;
+                    int r = tap / p.S, sx = tap - r * p.S;
+#pragma unroll
+                    for (int i = 0; i < NS; i++) tma_load_im2col(a_tile(s, i), mA[i], c0, pix_w, pix_h, pix_img, sx, r, bar);
+                    bk = tap * p.cpad + c0;
+                } else {
+                    int img = k0 / p.OHW, rem = k0 - img * p.OHW, oh = rem / p.OW, ow = rem - oh * p.OW;
+                    int w = ow * p.sw - p.pw, h = oh * p.sh - p.ph;
+#pragma unroll
+                    for (int i = 0; i < NS; i++)
+                        for (int b = 0; b < 2; b++)
+                            if (box_ok[b]) tma_load_im2col(a_tile(s, i) + b * 8192, mA[i], box_c[b], w, h, img, box_s[b], box_r[b], bar);
+                }
+                if (p.b_mn) {
+#pragma unroll
+                    for (int i = 0; i < NS; i++)
+                        for (int b = 0; b < bn / 64; b++) tma_load_2d(b_tile(s, i) + b * 8192, mB[i], n0 + 64 * b, bk, bar);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < NS; i++) tma_load_2d(b_tile(s, i), mB[i], bk, n0, bar);
+                }
             }
-            issued = kt + 1;
         }
         if (*abortp) {
             // give copies already in flight a bounded chance to land before the CTA's shared memory goes away
-            for (int kt = max(0, issued - stages); kt < issued; kt++) {
+            issued_from = it - stages < 0 ? 0 : it - stages;
+            for (int k = issued_from; k < it; k++) {
                 unsigned long long t0 = clock64();
-                while (!mbar_try_wait(full0 + 8 * (kt % stages), (uint32_t)(kt / stages) & 1u) && clock64() - t0 < TC_WAIT_CLOCKS) {}
+                while (!mbar_try_wait(full0 + 8 * (k % stages), (uint32_t)(k / stages) & 1u) && clock64() - t0 < TC_WAIT_CLOCKS) {}
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -291,41 +309,58 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
         const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
         bool alive = true;
-        uint32_t acc = 0;
-        for (int kt = 0; kt < ktiles && alive; kt++) {
-            int s = kt % stages;
-            uint32_t ph = (uint32_t)(kt / stages) & 1u;
-            alive = mbar_wait(full0 + 8 * s, ph, abortp, p.status, 2);
+        int it = 0, local = 0;
+        for (int id = blockIdx.x; id < total_tiles && alive; id += gridDim.x, local++) {
+            int m0, n0, kbeg, ktiles, z;
+            tile_origin(id, m0, n0, kbeg, ktiles, z);
+            const int buf = local & 1;
+            // the epilogue must have drained this accumulator buffer (two tiles ago)
+            alive = mbar_wait(tempty0 + 8 * buf, (((uint32_t)local >> 1) & 1u) ^ 1u, abortp, p.status, 4);
             if (!alive) break;
             tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
+            uint32_t acc = 0;
+            for (int kt = 0; kt < ktiles && alive; kt++, it++) {
+                int s = it % stages;
+                uint32_t ph = (uint32_t)(it / stages) & 1u;
+                alive = mbar_wait(full0 + 8 * s, ph, abortp, p.status, 2);
+                if (!alive) break;
+                tc_fence_after();
 #pragma unroll
-            for (int j = 0; j < TC_BK / 16; j++) {
-                uint64_t da[NS], db[NS];
+                for (int j = 0; j < TC_BK / 16; j++) {
+                    uint64_t da[NS], db[NS];
 #pragma unroll
-                for (int i = 0; i < NS; i++) {
-                    uint32_t aa = a_tile(s, i) + j * a_step, ba = b_tile(s, i) + j * b_step;
-                    da[i] = a_mn ? umma_desc_sw128_mn(aa, 8192) : umma_desc_sw128(aa);
-                    db[i] = p.b_mn ? umma_desc_sw128_mn(ba, 8192) : umma_desc_sw128(ba);
+                    for (int i = 0; i < NS; i++) {
+                        uint32_t aa = a_tile(s, i) + j * a_step, ba = b_tile(s, i) + j * b_step;
+                        da[i] = a_mn ? umma_desc_sw128_mn(aa, 8192) : umma_desc_sw128(aa);
+                        db[i] = p.b_mn ? umma_desc_sw128_mn(ba, 8192) : umma_desc_sw128(ba);
+                    }
+#pragma unroll
+                    for (int q = 0; q < NPROD; q++) {
+                        umma_bf16(d_tmem, da[pa[q]], db[pb[q]], idesc, acc);
+                        acc = 1;
+                    }
                 }
-#pragma unroll
-                for (int q = 0; q < NPROD; q++) {
-                    umma_bf16(tmem_base, da[pa[q]], db[pb[q]], idesc, acc);
-                    acc = 1;
-                }
+                umma_commit(empty0 + 8 * s);
             }
-            umma_commit(empty0 + 8 * s);
+            if (alive) umma_commit(tfull0 + 8 * buf);        // accumulator of this tile complete
         }
-        if (alive) umma_commit(accum);
     } else if (warp >= 2) {
         // ---------------- epilogue: warp w drains TMEM lane quarter w % 4 ----------------
-        bool ok = mbar_wait(accum, 0, abortp, p.status, 3);
-        tc_fence_after();
-        if (ok) {
-            // every MMA has completed, so the operand stages are free: reuse them as per-warp staging
-            const int q = warp & 3;
-            float *stage = reinterpret_cast<float *>(smem + (size_t)(warp - 2) * EPI_WARP_SMEM);
-            drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16), m0 + q * 32, n0, 0, bn, p.M, p.N, cs, p.partial,
-                              (long long)blockIdx.z * p.M * p.N, stage);
+        const int q = warp & 3;
+        float *stage = reinterpret_cast<float *>(epi_smem + (size_t)(warp - 2) * EPI_WARP_SMEM);
+        int local = 0;
+        for (int id = blockIdx.x; id < total_tiles; id += gridDim.x, local++) {
+            int m0, n0, kbeg, ktiles, z;
+            tile_origin(id, m0, n0, kbeg, ktiles, z);
+            const int buf = local & 1;
+            if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)local >> 1) & 1u, abortp, p.status, 3)) break;
+            tc_fence_after();
+            drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, 0, bn, p.M, p.N, cs,
+                              p.partial, (long long)z * p.M * p.N, stage);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
         }
     }
     tc_fence_before();
@@ -352,6 +387,7 @@ inline int tma_pick_bn(int N, int ns, int b_mn) {
     int bn = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
     if (b_mn && bn < 64) bn = 64;
     if (ns >= 2 && bn > 128) bn = 128;
+    if (ns >= 3 && bn > 64) bn = 64;        // three operand copies per stage: keep two stages in shared memory
     return bn;
 }
 
@@ -360,10 +396,10 @@ inline int tma_pick_bn(int N, int ns, int b_mn) {
 template <class CS>
 int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, bool allow_split, double flops, const char *name) {
     size_t stage = (size_t)ns * (TC_BM * 128 + (size_t)p.bn * 128);
-    int stages = (int)((200 * 1024) / stage);
+    int stages = (int)((200 * 1024 - 4 * EPI_WARP_SMEM) / stage);
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(SEERA_E_LIMIT, "%s: tile does not fit shared memory", name);
-    size_t smem = stage * stages + 1024;
+    size_t smem = stage * stages + 4 * EPI_WARP_SMEM + 1024;
     long long tiles = (long long)((p.M + TC_BM - 1) / TC_BM) * ((p.N + p.bn - 1) / p.bn);
     int splits = 1;
     if (allow_split) {
@@ -375,6 +411,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
     }
     p.kchunk = ((p.K + splits - 1) / splits + TC_BK - 1) / TC_BK * TC_BK;
     splits = (p.K + p.kchunk - 1) / p.kchunk;
+    p.splits = splits;
     p.stages = stages;
     p.status = tc_status_word();
     p.partial = nullptr;
@@ -382,7 +419,8 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
         p.partial = (float *)scratch_alloc((size_t)splits * p.M * p.N * sizeof(float));
         if (!p.partial) return SEERA_E_OOM;
     }
-    dim3 grid((p.M + TC_BM - 1) / TC_BM, (p.N + p.bn - 1) / p.bn, splits);
+    long long all_tiles = tiles * splits;
+    dim3 grid((unsigned)(all_tiles < rt().sm_count ? all_tiles : rt().sm_count));     // persistent: one CTA per SM at most
     cudaStream_t st = rt().stream;
     cudaError_t e;
     profile_begin();

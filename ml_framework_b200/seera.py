@@ -720,11 +720,15 @@ class Loss:
 # Optimizers: one fused launch over the whole parameter arena
 # ─────────────────────────────────────────────────────────────────────────────────────────────
 class _Optimizer:
+    """Keeps its step scalars in a small device buffer so that a captured step graph can be replayed: the
+    update kernel reads them at run time, `advance()` refreshes them before each replay."""
+
     def __init__(self, model):
         if not isinstance(model, Sequential):
             raise TypeError("Model should be Sequential")
         self.model = model
         self.use_gpu = True
+        self._hyper = cuten(np.zeros(16, np.float32))
 
     def _state(self):
         n = max(self.model.n_arena, 1)
@@ -735,7 +739,21 @@ class _Optimizer:
         m.gather_grads()
         if m._allreduce is not None:
             m._allreduce(m.grads)
-        return f32(1.0 / m.world) if m._allreduce is not None else f32(1.0)
+
+    def _grad_scale(self):
+        return 1.0 / self.model.world if self.model._allreduce is not None else 1.0
+
+    def _upload(self, values):
+        h = np.zeros(16, np.float32)
+        h[:len(values)] = np.asarray(values, np.float32)
+        sc.upload_f32(self._hyper.main_ptr, h)
+
+    def step(self):
+        """One update.  Outside a capture this also refreshes the device scalars and advances the step count."""
+        if not sc.is_capturing():
+            self.advance()
+        self._grads_ready()
+        self._enqueue()
 
 
 class SGD(_Optimizer):
@@ -746,11 +764,12 @@ class SGD(_Optimizer):
         self.lr, self.momentum = lr, momentum
         self.velocity = self._state()
 
-    def step(self):
-        gs = self._grads_ready()
+    def advance(self):
+        self._upload([self.lr, self.momentum, self._grad_scale()])
+
+    def _enqueue(self):
         m = self.model
-        sc.cuda_sgd_step(m.params.main_ptr, m.grads.main_ptr, self.velocity.main_ptr, m.n_arena,
-                         float(f32(self.lr)), float(f32(self.momentum)), float(gs))
+        sc.cuda_sgd_step_dev(m.params.main_ptr, m.grads.main_ptr, self.velocity.main_ptr, m.n_arena, self._hyper.main_ptr)
 
 
 class Adam(_Optimizer):
@@ -761,10 +780,12 @@ class Adam(_Optimizer):
         self.lr, self.beta1, self.beta2, self.eps, self.t = lr, beta1, beta2, eps, 1
         self.m, self.v = self._state(), self._state()
 
-    def step(self):
-        gs = self._grads_ready()
-        md, b1, b2 = self.model, self.beta1, self.beta2
-        sc.cuda_adam_step(md.params.main_ptr, md.grads.main_ptr, self.m.main_ptr, self.v.main_ptr, md.n_arena,
-                          float(f32(self.lr)), float(f32(b1)), float(f32(1 - b1)), float(f32(b2)), float(f32(1 - b2)),
-                          float(f32(self.eps)), float(f32(1 - b1 ** self.t)), float(f32(1 - b2 ** self.t)), float(gs))
+    def advance(self):
+        b1, b2 = self.beta1, self.beta2
+        self._upload([self.lr, b1, 1 - b1, b2, 1 - b2, self.eps, 1 - b1 ** self.t, 1 - b2 ** self.t, self._grad_scale()])
         self.t += 1
+
+    def _enqueue(self):
+        md = self.model
+        sc.cuda_adam_step_dev(md.params.main_ptr, md.grads.main_ptr, self.m.main_ptr, self.v.main_ptr, md.n_arena,
+                              self._hyper.main_ptr)

@@ -63,6 +63,40 @@ class Trainer:
         self.opt.step()
         return loss
 
+    # ---- whole-step CUDA graph -------------------------------------------------------------------
+    def capture(self, X, Y):
+        """Records forward + loss + backward + optimizer on the device tensors X, Y into a CUDA graph.
+        Run `step` eagerly at least twice first.  Afterwards `replay()` re-runs the recorded step on
+        whatever X and Y hold at that moment; the loss tensor returned here is rewritten by every replay."""
+        if not (isinstance(X, S.Tensor) and isinstance(Y, S.Tensor)):
+            raise TypeError("capture needs device-resident Tensors")
+        if self.model._allreduce is not None:
+            raise RuntimeError("capture is for single-process training; the data-parallel step runs eagerly")
+        self.opt.advance()
+        sc.graph_begin()
+        try:
+            loss = self.step(X, Y)
+        except Exception:
+            try:
+                sc.graph_end()
+            except Exception:
+                pass
+            raise
+        self._graph = sc.graph_end()
+        self._graph_keep = (X, Y, loss, self.pred)
+        return loss
+
+    def replay(self):
+        self.opt.advance()
+        sc.graph_launch(self._graph)
+        return self._graph_keep[2]
+
+    def release_graph(self):
+        g = getattr(self, "_graph", None)
+        if g:
+            sc.graph_destroy(g)
+            self._graph, self._graph_keep = None, None
+
     def host_params(self):
         return [None if not isinstance(l, S._ParamLayer) else (l.weights.to_numpy(), l.bais.to_numpy())
                 for l in self.model.model[1:]]

@@ -318,6 +318,19 @@ def cuda_adam_step(w, g, m, v, n, lr, b1, omb1, b2, omb2, eps, c1, c2, gs):
     W[:] = W - (f(lr) * (M / f(c1))) / (np.sqrt(V / f(c2)) + f(eps))
 
 
+def is_capturing(): return False
+
+
+def cuda_adam_step_dev(w, g, m, v, n, h):
+    hv = _view(h, 9)
+    cuda_adam_step(w, g, m, v, n, *[float(x) for x in hv])
+
+
+def cuda_sgd_step_dev(w, g, vel, n, h):
+    hv = _view(h, 3)
+    cuda_sgd_step(w, g, vel, n, *[float(x) for x in hv])
+
+
 def cuda_sgd_step(w, g, vel, n, lr, mu, gs):
     _count("sgd")
     f = np.float32

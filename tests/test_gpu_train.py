@@ -118,3 +118,31 @@ def test_full_size_properties(T):
     for F, A, B in zip(outs[0], *halves):
         if F is not None:
             assert rel_l2(F[0], 0.5 * (A[0] + B[0])) < 1e-4   # each half's loss is a mean over 256
+
+
+@pytest.mark.parametrize("name,n,mode", [("c1", 64, 0), ("c2", 256, 1), ("c3", 16, 2)])
+def test_captured_step_graph_replays_like_eager_steps(T, name, n, mode):
+    """A CUDA graph of the whole step, replayed k times, gives the weights k eager steps give (bit for bit:
+    same kernels, same order, deterministic reductions)."""
+    from ml_framework_b200 import seera as S, seera_cuda as sc
+    sc.set_precision(mode)
+    work = wl.WORKLOADS[name]()
+    X, Y = work.batch(n, 5)
+    a, b = T.Trainer(work, seed=5), T.Trainer(work, seed=5)
+    Xa, Ya = S.Tensor(X, is_leaf=True), S.Tensor(Y, is_leaf=True)
+    Xb, Yb = S.Tensor(X, is_leaf=True), S.Tensor(Y, is_leaf=True)
+    for _ in range(2):
+        a.step(Xa, Ya)
+        b.step(Xb, Yb)
+    for _ in range(4):
+        la = a.step(Xa, Ya)
+    lb = b.capture(Xb, Yb)          # recording executes nothing
+    for _ in range(4):
+        lb = b.replay()
+    assert float(la.value.to_host_f32()[0]) == float(lb.value.to_host_f32()[0])
+    for Pa, Pb in zip(a.host_params(), b.host_params()):
+        if Pa is not None:
+            assert np.array_equal(Pa[0], Pb[0]) and np.array_equal(Pa[1], Pb[1])
+    b.release_graph()
+    sc.set_precision(0)
+    assert sc.tc_device_status() == 0
