@@ -64,30 +64,32 @@ static int make_map_im2col(CUtensorMap *m, const void *base, int NB, int H, int 
     return SEERA_OK;
 }
 
-// ---- fp32 NCHW -> bf16 channels-last shadows: [NB, C, P] -> [NB, P, Cp], 32 x 32 tiles through shared memory ----
+// ---- fp32 NCHW -> bf16 channels-last shadows: [NB, C, P] -> [NB, P, Cp] ---------------------------------------
+// Tile of 64 channels x 32 pixels through shared memory: reads are coalesced along pixels (128 bytes per warp
+// row), writes are 16-byte chunks of 8 channels, 8 threads covering the 128 contiguous bytes of one pixel.
 template <int NS>
 __global__ void __launch_bounds__(256) shadow_nhwc_kernel(const float *__restrict__ src, int C, int P, int Cp,
                                                           __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
                                                           __nv_bfloat16 *__restrict__ d2) {
-    __shared__ float tile[32][33];
-    const int img = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * 32;
+    __shared__ float tile[64][33];
+    const int img = blockIdx.z, c0 = blockIdx.y * 64, p0 = blockIdx.x * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
     const float *s = src + (long long)img * C * P;
-    for (int i = ty; i < 32; i += 8) {          // read: lanes along pixels
+    for (int i = ty; i < 64; i += 8) {
         int c = c0 + i, p = p0 + tx;
         tile[i][tx] = (c < C && p < P) ? __ldg(s + (long long)c * P + p) : 0.f;
     }
     __syncthreads();
-    for (int i = ty; i < 32; i += 8) {          // write: lanes along channels
-        int p = p0 + i, c = c0 + tx;
-        if (p < P && c < Cp) {
-            float v = tile[tx][i];
-            long long o = ((long long)img * P + p) * Cp + c;
-            __nv_bfloat16 h = __float2bfloat16_rn(v);
-            d0[o] = h;
-            if (NS >= 2) { v -= __bfloat162float(h); __nv_bfloat16 l = __float2bfloat16_rn(v); d1[o] = l;
-                           if (NS >= 3) { v -= __bfloat162float(l); d2[o] = __float2bfloat16_rn(v); } }
-        }
+    const int cg = threadIdx.x & 7, pl = threadIdx.x >> 3;      // channel group of 8, pixel within the tile
+    const int p = p0 + pl, c = c0 + cg * 8;
+    if (p < P && c < Cp) {                                      // Cp is a multiple of 8: a group is all in or all out
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = tile[cg * 8 + i][pl];
+        long long o = ((long long)img * P + p) * Cp + c;
+        *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
+        if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
+        if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
     }
 }
 
@@ -103,7 +105,7 @@ static int make_nhwc(const float *src, int NB, int C, int H, int W, int ns, Nhwc
     size_t bytes = (size_t)NB * H * W * s.Cp * 2;
     for (int i = 0; i < ns; i++) { s.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!s.p[i]) return SEERA_E_OOM; }
     int P = H * W;
-    dim3 grid((P + 31) / 32, (s.Cp + 31) / 32, NB);
+    dim3 grid((P + 31) / 32, (s.Cp + 63) / 64, NB);
     if (grid.z > 65535 || grid.y > 65535) return fail(SEERA_E_LIMIT, "channels-last shadow: batch or channel count too large");
     cudaStream_t st = rt().stream;
     if (ns == 1) shadow_nhwc_kernel<1><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
@@ -197,6 +199,51 @@ static int tma_wgrad(const NhwcShadow &x, const NhwcShadow &dy, float *dW, int R
     return launch_tma_gemm(maps, p, StoreWgrad{dW, x.C, R * S, p.cchunks * 64}, ns, true, flops, name);
 }
 
+// ---- first-layer case: C*R*S <= 64 ----------------------------------------------------------------------------
+// With one or three input channels a (tap, 64-channel) slice is almost all padding.  Here the whole patch of a
+// pixel fits one K step, so the patches are written once as a bf16 matrix [pixels, C*R*S] (a few tens of MB) and
+// the forward pass and the weight gradient run as plain TMA GEMMs on it.
+template <int NS>
+__global__ void __launch_bounds__(256) patch_rows_kernel(const float *__restrict__ X, int C, int H, int W, int OH, int OW, int R, int S,
+                                                         int sh, int sw, int ph, int pw, long long pixels, int K, int Kp,
+                                                         __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
+                                                         __nv_bfloat16 *__restrict__ d2) {
+    const int groups = Kp >> 3;
+    long long total = pixels * groups;
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    for (long long e = tid; e < total; e += nthr) {
+        long long pix = e / groups;
+        int kg = (int)(e - pix * groups);
+        int P = OH * OW, img = (int)(pix / P), rem = (int)(pix - (long long)img * P), oh = rem / OW, ow = rem - oh * OW;
+        const float *xb = X + (long long)img * C * H * W;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            int k = kg * 8 + i, c = k / (R * S), rs = k - c * R * S, r = rs / S, sx = rs - r * S;
+            int ih = oh * sh + r - ph, iw = ow * sw + sx - pw;
+            v[i] = (k < K && (unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) ? __ldg(xb + ((long long)c * H + ih) * W + iw) : 0.f;
+        }
+        long long o = pix * Kp + kg * 8;
+        *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
+        if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
+        if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+    }
+}
+static int make_patch_rows(const float *X, int NB, int C, int H, int W, int OH, int OW, int R, int S, int sh, int sw, int ph, int pw,
+                           int ns, Shadow &s) {
+    int K = C * R * S;
+    long long pixels = (long long)NB * OH * OW;
+    if (int e = alloc_shadow(s, (int)pixels, K, ns)) return e;
+    int grid = stride_grid(pixels * (s.ld / 8));
+    cudaStream_t st = rt().stream;
+    if (ns == 1) patch_rows_kernel<1><<<grid, 256, 0, st>>>(X, C, H, W, OH, OW, R, S, sh, sw, ph, pw, pixels, K, s.ld, s.p[0], s.p[1], s.p[2]);
+    else if (ns == 2) patch_rows_kernel<2><<<grid, 256, 0, st>>>(X, C, H, W, OH, OW, R, S, sh, sw, ph, pw, pixels, K, s.ld, s.p[0], s.p[1], s.p[2]);
+    else patch_rows_kernel<3><<<grid, 256, 0, st>>>(X, C, H, W, OH, OW, R, S, sh, sw, ph, pw, pixels, K, s.ld, s.p[0], s.p[1], s.p[2]);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, "patch_rows");
+}
+
 static bool conv_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     return NB >= 1 && C >= 1 && H >= 1 && W >= 1 && F >= 1 && R >= 1 && S >= 1 && sh >= 1 && sw >= 1 && ph >= 0 && pw >= 0 &&
            (long long)NB * (C > F ? C : F) * H * W * (long long)(sh * sw) < (1LL << 31);
@@ -222,7 +269,16 @@ int seera_tma_conv2d_fwd(const float *X, const float *Wt, float *Y, int NB, int 
     if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return seera_tc_conv2d_fwd(X, Wt, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw);
     int ns = precision_copies();
     NhwcShadow xs; Shadow wk;
-    int s = make_nhwc(X, NB, C, H, W, ns, xs);
+    int s;
+    if (C * R * S <= 64) {            // first-layer case: patches as rows, one K step
+        Shadow patches;
+        s = make_patch_rows(X, NB, C, H, W, OH, OW, R, S, sh, sw, ph, pw, ns, patches);
+        if (!s) s = make_shadow(Wt, F, C * R * S, ns, wk);
+        if (!s) s = run_tma_gemm(patches, 0, wk, 0, StorePixelRows{Y, F, OH * OW}, NB * OH * OW, F, C * R * S, false, "cuda_conv2d_fwd");
+        free_shadow(patches); free_shadow(wk);
+        return s;
+    }
+    s = make_nhwc(X, NB, C, H, W, ns, xs);
     if (!s) s = make_weight_shadow(Wt, F, C, R * S, (long long)C * R * S, R * S, 0, ns, wk);
     if (!s) s = tma_fprop(xs, wk, Y, F, R, S, sh, sw, ph, pw, OH, OW, ns, "cuda_conv2d_fwd");
     free_nhwc(xs); free_shadow(wk);
@@ -248,8 +304,17 @@ int seera_tma_conv2d_bwd(const float *Wt, const float *X, const float *dY, float
         }
     }
     if (!s && dW) {
-        s = make_nhwc(X, NB, C, H, W, ns, xs);
-        if (!s) s = tma_wgrad(xs, dys, dW, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dW)");
+        if (C * R * S <= 64) {        // first-layer case: dW[f][k] = sum_pix dY[pix][f] * patches[pix][k]
+            Shadow patches, dyr;
+            s = make_patch_rows(X, NB, C, H, W, OH, OW, R, S, sh, sw, ph, pw, ns, patches);
+            for (int i = 0; i < 3; i++) dyr.p[i] = dys.p[i];
+            dyr.rows = NB * OH * OW; dyr.cols = dys.Cp; dyr.ld = dys.Cp;
+            if (!s) s = run_tma_gemm(patches, 1, dyr, 1, StoreDenseT{dW, C * R * S}, C * R * S, F, NB * OH * OW, true, "cuda_conv2d_bwd(dW)");
+            free_shadow(patches);
+        } else {
+            s = make_nhwc(X, NB, C, H, W, ns, xs);
+            if (!s) s = tma_wgrad(xs, dys, dW, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dW)");
+        }
     }
     free_nhwc(dys); free_nhwc(xs); free_shadow(wd);
     return s;

@@ -93,24 +93,27 @@ __global__ void __launch_bounds__(256) act_bias_bwd_nchw_kernel(const float *__r
     __shared__ float sm[8];
     int c = blockIdx.x, s = blockIdx.y, splits = gridDim.y;
     float acc = 0.f;
-    for (int n = s; n < outer; n += splits) {
-        long long base = ((long long)n * channels + c) * inner;
-        if (vec) {
-            const float4 *d4 = reinterpret_cast<const float4 *>(dy + base), *y4 = reinterpret_cast<const float4 *>(y + base);
-            float4 *o4 = reinterpret_cast<float4 *>(dz + base);
-            for (int i = threadIdx.x; i < (inner >> 2); i += blockDim.x) {
-                float4 d = d4[i], yy = y4[i], r;
-                r.x = d.x * act_grad_from_out(yy.x, act); r.y = d.y * act_grad_from_out(yy.y, act);
-                r.z = d.z * act_grad_from_out(yy.z, act); r.w = d.w * act_grad_from_out(yy.w, act);
-                o4[i] = r;
-                acc += (r.x + r.y) + (r.z + r.w);
-            }
-        } else {
-            for (int i = threadIdx.x; i < inner; i += blockDim.x) {
-                float r = dy[base + i] * act_grad_from_out(y[base + i], act);
-                dz[base + i] = r;
-                acc += r;
-            }
+    // this block's samples are n = s, s + splits, ...; walk (sample, element) pairs flattened so that all threads
+    // stay busy when a channel plane is smaller than the block
+    const int cnt = (outer - s + splits - 1) / splits;
+    if (vec) {
+        const int q = inner >> 2;
+        for (long long j = threadIdx.x; j < (long long)cnt * q; j += blockDim.x) {
+            int k = (int)(j / q), i = (int)(j - (long long)k * q);
+            long long base = ((long long)(s + k * splits) * channels + c) * inner;
+            float4 d = reinterpret_cast<const float4 *>(dy + base)[i], yy = reinterpret_cast<const float4 *>(y + base)[i], r;
+            r.x = d.x * act_grad_from_out(yy.x, act); r.y = d.y * act_grad_from_out(yy.y, act);
+            r.z = d.z * act_grad_from_out(yy.z, act); r.w = d.w * act_grad_from_out(yy.w, act);
+            reinterpret_cast<float4 *>(dz + base)[i] = r;
+            acc += (r.x + r.y) + (r.z + r.w);
+        }
+    } else {
+        for (long long j = threadIdx.x; j < (long long)cnt * inner; j += blockDim.x) {
+            int k = (int)(j / inner), i = (int)(j - (long long)k * inner);
+            long long at = ((long long)(s + k * splits) * channels + c) * inner + i;
+            float r = dy[at] * act_grad_from_out(y[at], act);
+            dz[at] = r;
+            acc += r;
         }
     }
     float tot = block_sum_256(acc, sm);

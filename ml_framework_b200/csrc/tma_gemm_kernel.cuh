@@ -396,7 +396,8 @@ inline int tma_pick_bn(int N, int ns, int b_mn) {
 template <class CS>
 int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, bool allow_split, double flops, const char *name) {
     size_t stage = (size_t)ns * (TC_BM * 128 + (size_t)p.bn * 128);
-    int stages = (int)((200 * 1024 - 4 * EPI_WARP_SMEM) / stage);
+    // 227 KB per CTA on sm_100a; keep 2 KB for the kernel's static shared memory and alignment slack
+    int stages = (int)((225 * 1024 - 4 * EPI_WARP_SMEM - 1024) / stage);
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(SEERA_E_LIMIT, "%s: tile does not fit shared memory", name);
     size_t smem = stage * stages + 4 * EPI_WARP_SMEM + 1024;

@@ -72,7 +72,6 @@ class Trainer:
             raise TypeError("capture needs device-resident Tensors")
         if self.model._allreduce is not None:
             raise RuntimeError("capture is for single-process training; the data-parallel step runs eagerly")
-        self.opt.advance()
         sc.graph_begin()
         try:
             loss = self.step(X, Y)
