@@ -327,39 +327,61 @@ int seera_bias_act_fwd(const float *z, const float *bias, float *y, int size, in
     return SEERA_OK;
 }
 
-int seera_act_bias_bwd(const float *dy, const float *y, float *dz, float *dbias, int size, int channels, int inner, int act) {
-    SEERA_ENSURE();
-    if (size < 0 || channels < 1 || inner < 1 || (size > 0 && (!dy || !dz)) || (act != SEERA_ACT_NONE && !y) ||
-        size % (channels * inner) != 0)
-        return fail(SEERA_E_ARG, "act_bias_bwd: bad argument");
-    if (size == 0) return SEERA_OK;
-    if (!y) y = dy;   // act == NONE never reads it
-    int outer = size / (channels * inner);
-    // splits: enough blocks for ~4 waves, never more than the rows available
+// Split count of the activation-backward pass: enough blocks for ~4 waves, never more than the rows available.
+static int act_bias_splits(int outer, int channels, int inner) {
     int splits;
-    float *partial = nullptr;
     if (inner == 1) {
         int colblocks = (channels + 31) / 32;
         splits = (rt().sm_count * 4 + colblocks - 1) / colblocks;
-        int maxs = (outer + 7) / 8; if (splits > maxs) splits = maxs; if (splits < 1) splits = 1;
-        if (dbias) { partial = (float *)scratch_alloc((size_t)splits * channels * sizeof(float)); if (!partial) return SEERA_E_OOM; }
+        int maxs = (outer + 7) / 8;
+        if (splits > maxs) splits = maxs;
+    } else {
+        splits = (rt().sm_count * 4 + channels - 1) / channels;
+        if (splits > outer) splits = outer;
+        if (splits > 65535) splits = 65535;
+    }
+    return splits < 1 ? 1 : splits;
+}
+
+// Launches dz = dy * act'(y) and, when dbias is wanted, the two-stage per-channel sum through `partial`
+// (splits * channels floats of scratch owned by the caller of this helper).
+static int act_bias_bwd_launch(const float *dy, const float *y, float *dz, float *dbias, float *partial, int outer, int channels,
+                               int inner, int act, int splits) {
+    if (inner == 1) {
+        int colblocks = (channels + 31) / 32;
         act_bias_bwd_rows_kernel<<<dim3(colblocks, splits), 256, 0, rt().stream>>>(dy, y, dz, partial, outer, channels, act);
         SEERA_LAUNCH_CHECK("act_bias_bwd(rows)");
     } else {
-        splits = (rt().sm_count * 4 + channels - 1) / channels;
-        if (splits > outer) splits = outer; if (splits < 1) splits = 1;
-        if (splits > 65535) splits = 65535;
-        if (dbias) { partial = (float *)scratch_alloc((size_t)splits * channels * sizeof(float)); if (!partial) return SEERA_E_OOM; }
         bool vec = (inner % 4 == 0) && aligned16(dy) && aligned16(y) && aligned16(dz);
         act_bias_bwd_nchw_kernel<<<dim3(channels, splits), 256, 0, rt().stream>>>(dy, y, dz, partial, outer, channels, inner, act, vec);
         SEERA_LAUNCH_CHECK("act_bias_bwd(nchw)");
     }
     if (dbias) {
         sum_partials_kernel<<<(channels + 255) / 256, 256, 0, rt().stream>>>(partial, dbias, channels, splits);
-        scratch_free(partial);
         SEERA_LAUNCH_CHECK("act_bias_bwd(sum)");
     }
     return SEERA_OK;
+}
+
+static int act_bias_bwd_check(const float *dy, const float *y, float *dz, int size, int channels, int inner, int act, const char *name) {
+    if (size < 0 || channels < 1 || inner < 1 || (size > 0 && (!dy || !dz)) || (act != SEERA_ACT_NONE && !y) ||
+        size % (channels * inner) != 0)
+        return fail(SEERA_E_ARG, "%s: bad argument", name);
+    return SEERA_OK;
+}
+
+int seera_act_bias_bwd(const float *dy, const float *y, float *dz, float *dbias, int size, int channels, int inner, int act) {
+    SEERA_ENSURE();
+    if (int s = act_bias_bwd_check(dy, y, dz, size, channels, inner, act, "act_bias_bwd")) return s;
+    if (size == 0) return SEERA_OK;
+    if (!y) y = dy;   // act == NONE never reads it
+    int outer = size / (channels * inner);
+    int splits = act_bias_splits(outer, channels, inner);
+    float *partial = nullptr;
+    if (dbias) { partial = (float *)scratch_alloc((size_t)splits * channels * sizeof(float)); if (!partial) return SEERA_E_OOM; }
+    int s = act_bias_bwd_launch(dy, y, dz, dbias, partial, outer, channels, inner, act, splits);
+    if (partial) scratch_free(partial);
+    return s;
 }
 
 int seera_cuda_softmax_fwd(const float *x, float *out, int N, int C) {
