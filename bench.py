@@ -158,34 +158,10 @@ def setup_data_parallel(model, world, local_rank):
     torch.cuda.set_stream(stream)
     sc.set_stream(stream.cuda_stream)               # the engine enqueues on the stream NCCL orders against
     full = torch.as_tensor(_ArenaView(model.grads.main_ptr, model.n_arena), device="cuda")
-    # buckets: contiguous arena ranges, last layers first (their gradients are ready first in backward)
-    params = model.parameters()
-    target = max(1, model.n_arena // 3)
-    buckets, cur_end, cur_beg = [], model.n_arena, model.n_arena
-    for t in reversed(params):
-        cur_beg = t._arena_off
-        if cur_end - cur_beg >= target or t is params[0]:
-            buckets.append((cur_beg, cur_end))
-            cur_end = cur_beg
-    state = {"works": [], "next": 0}
-
-    def on_grad_ready(t):
-        """Called when parameter t's gradient sits in the arena; fires every bucket that is now complete."""
-        while state["next"] < len(buckets) and t._arena_off <= buckets[state["next"]][0]:
-            b, e = buckets[state["next"]]
-            state["works"].append(dist.all_reduce(full[b:e], op=dist.ReduceOp.SUM, async_op=True))
-            state["next"] += 1
-
-    def finish(_grads):
-        while state["next"] < len(buckets):
-            b, e = buckets[state["next"]]
-            state["works"].append(dist.all_reduce(full[b:e], op=dist.ReduceOp.SUM, async_op=True))
-            state["next"] += 1
-        for w in state["works"]:
-            w.wait()
-        state["works"], state["next"] = [], 0
-
-    model.world, model._allreduce, model._on_grad_ready = world, finish, on_grad_ready
+    from ml_framework_b200 import dp
+    dp.attach(model, world,
+              reduce_range=lambda b, e: dist.all_reduce(full[b:e], op=dist.ReduceOp.SUM, async_op=True),
+              wait=lambda w: w.wait())
     return dist, torch
 
 
