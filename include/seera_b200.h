@@ -202,6 +202,22 @@ int seera_bias_act_fwd(const float *z, const float *bias, float *y, int size, in
  * stored local gradient plus broadcast_mul_4d + three cuda_sum_fwd (Seera_Engine.py:571-583, :43-65). */
 int seera_act_bias_bwd(const float *dy, const float *y, float *dz, float *dbias,
                        int size, int channels, int inner, int act);
+/* seera_act_bias_bwd for callers that must not allocate.  No counterpart in the reference.
+ * Some hosts of this library cannot let a call reach cudaMalloc: code that runs between fixed memory budgets
+ * (an inference server or a plugin that was handed its device memory up front), code on a latency path where a
+ * pool miss would stall on the driver's allocator, and code that has already begun recording work it will
+ * replay.  The regular entry takes its partial-sum scratch from the pool; this one uses a fixed 256 KiB device
+ * array built into the library (present on every GPU that loads it, until exit) and never calls cudaMalloc,
+ * cudaFree or the pool.  Same arguments and results as seera_act_bias_bwd, with these limits:
+ *   - channels <= 65536; when splits * channels would not fit, fewer and longer partial sums are used (dbias
+ *     then differs from the regular entry only by summation order); more channels -> SEERA_E_LIMIT.
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call before any stream capture begins.
+ *   - all calls share the one array: two calls whose kernels overlap on the GPU (different streams or
+ *     processes sharing a context) race on it.  Calls on this library's single stream are ordered and safe.
+ *   - the array keeps the last call's partial sums; every element a call reads it has written first. */
+int seera_act_bias_bwd_noalloc(const float *dy, const float *y, float *dz, float *dbias,
+                               int size, int channels, int inner, int act);
 /* Softmax + categorical cross-entropy: the reference's chain softmax -> clip(eps, 1-eps) -> log ->
  * (-y * .) -> sum(-1) -> mean (Seera.py:955-969) and its backward (Seera_Engine.py:352-379, :571-583)
  * evaluated row by row.  Writes p = softmax(z), loss_rows[n] = -sum_c y*log(clip(p)),

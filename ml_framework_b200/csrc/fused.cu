@@ -384,6 +384,44 @@ int seera_act_bias_bwd(const float *dy, const float *y, float *dz, float *dbias,
     return s;
 }
 
+// ---- activation backward without any allocation -------------------------------------------------------------
+// Scratch for the per-channel partial sums lives in this fixed device array instead of the pool.  It is part of
+// the library image: every GPU that loads the library carries these 256 KiB until the process exits.
+#define SEERA_STATIC_PARTIALS 65536
+static __device__ __align__(256) float g_act_bias_partials[SEERA_STATIC_PARTIALS];
+
+// In host code the array's name is only a handle for the runtime, not a device address; the address a kernel can
+// use has to be asked for, once per device, while that device is current.
+static float *static_partials_for_current_device(int *status) {
+    static float *per_device[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *status = fail(SEERA_E_CUDA, "act_bias_bwd_noalloc: cannot identify the current device"); return nullptr; }
+    if (!per_device[dev]) {
+        float *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void **)&p, g_act_bias_partials);
+        if (e != cudaSuccess || !p) { *status = check_cuda(e == cudaSuccess ? cudaErrorInvalidSymbol : e, "cudaGetSymbolAddress(act_bias partials)"); return nullptr; }
+        per_device[dev] = p;
+    }
+    return per_device[dev];
+}
+
+int seera_act_bias_bwd_noalloc(const float *dy, const float *y, float *dz, float *dbias, int size, int channels, int inner, int act) {
+    SEERA_ENSURE();
+    if (int s = act_bias_bwd_check(dy, y, dz, size, channels, inner, act, "act_bias_bwd_noalloc")) return s;
+    if (size == 0) return SEERA_OK;
+    if (!y) y = dy;
+    int outer = size / (channels * inner);
+    if (channels > SEERA_STATIC_PARTIALS)
+        return fail(SEERA_E_LIMIT, "act_bias_bwd_noalloc: %d channels exceed the fixed scratch of %d partial sums", channels, SEERA_STATIC_PARTIALS);
+    int splits = act_bias_splits(outer, channels, inner);
+    if ((long long)splits * channels > SEERA_STATIC_PARTIALS) splits = SEERA_STATIC_PARTIALS / channels;   // fewer, longer partial sums
+    int st = SEERA_OK;
+    float *partial = dbias ? static_partials_for_current_device(&st) : nullptr;
+    if (dbias && !partial) return st;
+    // every partial that is read is written first by this call, so nothing needs clearing
+    return act_bias_bwd_launch(dy, y, dz, dbias, partial, outer, channels, inner, act, splits);
+}
+
 int seera_cuda_softmax_fwd(const float *x, float *out, int N, int C) {
     SEERA_ENSURE();
     if (N < 0 || C < 1 || (N > 0 && (!x || !out))) return fail(SEERA_E_ARG, "cuda_softmax_fwd: bad argument");
