@@ -170,8 +170,9 @@ def run_gpu(args, work):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     from ml_framework_b200 import seera_cuda as sc, seera as S, train
     sc.init(local)
-    sc.set_precision(args.precision)
-    tr = train.Trainer(work, seed=0)
+    prec = tuple(int(v) for v in args.precision.split("/"))
+    prec = prec if len(prec) == 2 else (prec[0], prec[0])
+    tr = train.Trainer(work, seed=0, precision=prec)
     dist = torch = None
     if world > 1:
         dist, torch = setup_data_parallel(tr.model, world, local)
@@ -291,7 +292,8 @@ def run_gpu(args, work):
                    "sample": "%d-sample steps, %.0f ms each; %s" % (sample, cms, how)}
         line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": {0: "f32", 1: "bf16 (f32 accumulate)", 2: "bf16x3 (f32 accumulate)"}[args.precision],
+                "dtype": {"0": "f32", "1": "bf16 (f32 accumulate)", "2": "bf16x3 (f32 accumulate)", "3": "bf16x6 (f32 accumulate)",
+                          "3/2": "bf16 split products, f32 accumulate (forward 6-term, backward 3-term)"}.get(args.precision, args.precision),
                 "data": "synthetic (seeded, shapes and value ranges of the configuration)",
                 "config": {"workload": work.name, "per_gpu_batch": n, "global_batch": n * world,
                            "parallelism": "dp%d" % world if world > 1 else "single",
@@ -312,19 +314,81 @@ def run_gpu(args, work):
         dist.destroy_process_group()
 
 
+def run_c5(args):
+    """Conv2D-backward microbenchmark (configuration 5): dX and dW of a 3x3 s1 p1 convolution with C = K, bf16
+    operands (precision mode 1), operands resident in HBM, timed with CUDA events; TFLOP/s against the measured
+    bf16 peak.  One JSON line with the per-shape table; `value` is the geometric mean over the shapes run."""
+    from ml_framework_b200 import seera_cuda as sc
+    from ml_framework_b200.cuTen import cuten
+    sc.init(int(os.environ.get("LOCAL_RANK", "0")))
+    mode = int(args.precision or "1")
+    sc.set_precision(mode)
+    peaks = _peaks()
+    shapes = [tuple(int(v) for v in args.c5_shape.split(","))] if args.c5_shape else wl.C5_SHAPES
+    nb = args.c5_batch
+    rows, l0 = [], sc.launch_count()
+    for ck, hw in shapes:
+        X, W, dY = wl.c5_conv_bwd(ck, hw, n=nb)
+        x, w, dy = cuten(X), cuten(W), cuten(dY)
+        dx, dw = cuten(np.zeros_like(X)), cuten(np.zeros_like(W))
+        fl = 2.0 * nb * hw * hw * ck * ck * 9
+        res = {"C=K": ck, "H=W": hw, "N": nb, "gflop_each": fl / 1e9}
+        for name, pdx, pdw in (("dX", dx.main_ptr, 0), ("dW", 0, dw.main_ptr), ("both", dx.main_ptr, dw.main_ptr)):
+            call = lambda: sc.cuda_conv2d_bwd(w.main_ptr, x.main_ptr, dy.main_ptr, pdx, pdw, nb, ck, hw, hw, ck, 3, 3, 1, 1, 1, 1)
+            for _ in range(max(args.warmup, 3)):
+                call()
+            sc.stream_synchronize()
+            e0, e1 = sc.event_create(), sc.event_create()
+            sc.event_record(e0)
+            for _ in range(args.steps):
+                call()
+            sc.event_record(e1)
+            ms = sc.event_elapsed_ms(e0, e1) / args.steps
+            sc.profile_enable(1)
+            for _ in range(args.steps):
+                call()
+            sc.stream_synchronize()
+            cnt, kms, kfl = sc.profile_read()
+            sc.profile_enable(0)
+            nfl = fl * (2 if name == "both" else 1)
+            res[name] = {"ms_call": ms, "tflops_call": nfl / ms / 1e9, "ms_kernel": kms / args.steps,
+                         "tflops_kernel": kfl / (kms / 1e3) / 1e12 if kms > 0 else None}
+        rows.append(res)
+    assert sc.tc_device_status() == 0
+    gm = float(np.exp(np.mean([np.log(r["both"]["tflops_call"]) for r in rows])))
+    best = max(r["both"]["tflops_kernel"] or 0 for r in rows)
+    print(json.dumps({"metric": "Conv2D backward (dX + dW) TFLOP/s, call including operand conversion", "value": gm, "unit": "TFLOP/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "vs_baseline": None,
+                      "dtype": {1: "bf16 (f32 accumulate)", 2: "bf16x3", 3: "bf16x6", 0: "f32"}[mode], "data": "synthetic (seeded)",
+                      "config": {"workload": "C5 Conv2D backward sweep 3x3 s1 p1, N=%d" % nb, "shapes": rows},
+                      "roofline": {"bound": "tensor", "achieved": best, "peak": peaks["tensor"], "unit": "TFLOP/s",
+                                   "frac": best / peaks["tensor"], "traffic": None, "kernel": "tma_gemm_kernel (best shape, kernel only)"},
+                      "gpu_launches": int(sc.launch_count() - l0)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c3", choices=sorted(wl.WORKLOADS))
+    ap.add_argument("--workload", default="c3", choices=sorted(wl.WORKLOADS) + ["c5"])
+    ap.add_argument("--c5-shape", default=None, help="C,HW of one point of the C5 sweep (default: the four diagonal shapes)")
+    ap.add_argument("--c5-batch", type=int, default=256)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--precision", type=int, default=0, choices=[0, 1, 2])
+    ap.add_argument("--precision", default=None,
+                    help="0 fp32 CUDA cores | 1 bf16 | 2 bf16x3 | 3 bf16x6 | F/B per phase; default: 1 for c2 (a bf16 configuration), "
+                         "3/2 for the fp32 configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a captured step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.workload == "c5":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_c5(args)
+        return
     work = wl.WORKLOADS[args.workload]()
+    if args.precision is None:
+        args.precision = "1" if work.precision == "bf16" else "3/2"
     if args.impl == "reference":
         run_reference(args, work)
     else:
