@@ -112,6 +112,9 @@ struct StoreDense {        // C[m*ld + n]
     static constexpr bool kMContiguous = false;
     float *C; long long ld;
     __device__ void operator()(int m, int n, float v) const { C[(long long)m * ld + n] = v; }
+    // every output functor is affine in n: element (m, n) lives at row(m)[n * nstride()]; row(m) == nullptr skips the row
+    __device__ float *row(int m) const { return C + (long long)m * ld; }
+    __device__ long long nstride() const { return 1; }
 };
 struct StoreNCHW {         // n = (img, p): out[(img*M + m)*P + p]
     static constexpr bool kMContiguous = false;
@@ -120,7 +123,7 @@ struct StoreNCHW {         // n = (img, p): out[(img*M + m)*P + p]
         int img = n / P, p = n - img * P;
         out[((long long)img * M + m) * P + p] = v;
     }
-};
+};   // (used by the CUDA-core kernel only, whose N index is the pixel)
 
 
 // Output functors for kernels whose M index is the long (pixel / batch-row) dimension.
@@ -128,6 +131,8 @@ struct StoreDenseT {       // C[n*ld + m]
     static constexpr bool kMContiguous = true;
     float *C; long long ld;
     __device__ void operator()(int m, int n, float v) const { C[(long long)n * ld + m] = v; }
+    __device__ float *row(int m) const { return C + m; }
+    __device__ long long nstride() const { return ld; }
 };
 struct StorePixelRows {    // m = (img, p): out[(img*Nch + n)*P + p]
     static constexpr bool kMContiguous = true;
@@ -136,6 +141,8 @@ struct StorePixelRows {    // m = (img, p): out[(img*Nch + n)*P + p]
         int img = m / P, p = m - img * P;
         out[((long long)img * Nch + n) * P + p] = v;
     }
+    __device__ float *row(int m) const { int img = m / P, p = m - img * P; return out + (long long)img * Nch * P + p; }
+    __device__ long long nstride() const { return P; }
 };
 
 }  // namespace seera

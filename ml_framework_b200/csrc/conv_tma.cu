@@ -156,6 +156,8 @@ struct StoreWgrad {
         int tap = m / c64, c = m - tap * c64;
         if (c < C) dW[((long long)n * C + c) * taps + tap] = v;
     }
+    __device__ float *row(int m) const { int tap = m / c64, c = m - tap * c64; return c < C ? dW + (long long)c * taps + tap : nullptr; }
+    __device__ long long nstride() const { return (long long)C * taps; }
 };
 
 // Y[NB, F, OH, OW] = conv(X_nhwc, weights Wk[F][tap][Cp]) with window R x S, stride, lower padding.

@@ -17,30 +17,39 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, 
                                                   float *stage /* EPI_WARP_SMEM bytes, this warp's own */) {
     const int lane = threadIdx.x & 31;
     const bool transpose = partial != nullptr || !CS::kMContiguous;
+    const long long sn = cs.nstride();
+    // direct path: this lane owns row m; its address part is computed once, not per element
+    const int m_own = row_base + lane;
+    float *own = (!transpose && m_own < M) ? cs.row(m_own) : nullptr;
     for (int c = c_begin; c < c_end; c += 32) {
         float v[32];
         tmem_ld32(taddr + (uint32_t)(c - c_begin), v);
         if (!transpose) {
-            int m = row_base + lane;
-            if (m < M) {
+            if (own) {
+                float *q = own + (long long)(col_base + c) * sn;
+                const int nvalid = N - (col_base + c);
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    int n = col_base + c + j;
-                    if (n < N) cs(m, n, v[j]);
-                }
+                for (int j = 0; j < 32; j++)
+                    if (j < nvalid) q[j * sn] = v[j];
             }
         } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) stage[lane * 33 + j] = v[j];
             __syncwarp();
-            int n = col_base + c + lane;
+            const int n = col_base + c + lane;
+            if (n < N) {
+                if (partial) {
+                    float *q = partial + partial_off + (long long)row_base * N + n;
+                    const int rows = min(32, M - row_base);
+                    for (int r = 0; r < rows; r++) q[(long long)r * N] = stage[r * 33 + lane];
+                } else {
 #pragma unroll 4
-            for (int r = 0; r < 32; r++) {
-                int m = row_base + r;
-                if (m < M && n < N) {
-                    float x = stage[r * 33 + lane];
-                    if (partial) partial[partial_off + (long long)m * N + n] = x;
-                    else cs(m, n, x);
+                    for (int r = 0; r < 32; r++) {
+                        if (row_base + r < M) {
+                            float *rp = cs.row(row_base + r);
+                            if (rp) rp[n * sn] = stage[r * 33 + lane];
+                        }
+                    }
                 }
             }
             __syncwarp();
