@@ -152,10 +152,12 @@ def setup_data_parallel(model, world, local_rank):
     import torch
     import torch.distributed as dist
     from ml_framework_b200 import seera_cuda as sc, seera as S
+    import datetime
     torch.cuda.set_device(local_rank)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=120))
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
+    sc.stream_synchronize()                         # uploads enqueued so far ran on the engine's own stream
     sc.set_stream(stream.cuda_stream)               # the engine enqueues on the stream NCCL orders against
     full = torch.as_tensor(_ArenaView(model.grads.main_ptr, model.n_arena), device="cuda")
     from ml_framework_b200 import dp
@@ -174,7 +176,7 @@ def run_gpu(args, work):
     prec = prec if len(prec) == 2 else (prec[0], prec[0])
     tr = train.Trainer(work, seed=0, precision=prec)
     dist = torch = None
-    if world > 1:
+    if world > 1 or os.environ.get("SEERA_BENCH_FORCE_DP"):      # the variable exercises the collective path on one rank
         dist, torch = setup_data_parallel(tr.model, world, local)
     n = work.batch_size                                  # per-rank batch: weak scaling
     X, Y = work.batch(n, seed=100 + rank)
@@ -194,15 +196,16 @@ def run_gpu(args, work):
         return float(t.item())
 
     # ---- warm-up: eager steps until the memory pool has stopped growing, then (single process) capture the step
+    # (with several ranks every rank must run the SAME number of steps: each step holds collectives)
     reserved = -1
-    for i in range(max(args.warmup, 3) + 8):
+    for i in range(max(args.warmup, 3) + (2 if world > 1 else 8)):
         tr.step(Xd, Yd)
         sc.stream_synchronize()
         r = sc.pool_bytes_reserved()
-        if i + 1 >= max(args.warmup, 3) and r == reserved:
+        if world == 1 and i + 1 >= max(args.warmup, 3) and r == reserved:
             break
         reserved = r
-    use_graph = (world == 1 and not args.no_graph)
+    use_graph = (dist is None and not args.no_graph)
     eager_ms = None
     if use_graph:
         e0, e1 = sc.event_create(), sc.event_create()
@@ -229,11 +232,13 @@ def run_gpu(args, work):
             loss = run_step()
         sc.event_record(e1)
         barrier()
-        # keep the device busy long enough for the 200 ms clock sampler to see it under load
-        while time.perf_counter() - t_wall < 1.0:
+        ms = reduce_max(sc.event_elapsed_ms(e0, e1))
+        # keep the device busy for about a second so the 200 ms clock sampler sees it under load; the count is
+        # derived from the rank-reduced time, so every rank runs the same number of extra steps
+        extra = int(min(5000, max(0.0, 1000.0 - ms) / max(ms / args.steps, 1e-3)))
+        for _ in range(extra):
             run_step()
         sc.stream_synchronize()
-    ms = reduce_max(sc.event_elapsed_ms(e0, e1))
     launches = (sc.launch_count() - l0)
     value = n * world * args.steps / (ms / 1e3)
     clocks = clk.summary()
@@ -267,14 +272,14 @@ def run_gpu(args, work):
 
     # ---- roofline of the contraction kernels: a separate profiled pass (events around each launch) -----
     roof = None
+    peaks = _peaks()
+    sc.profile_enable(1 if rank == 0 else 0)
+    for _ in range(min(args.steps, 5)):             # every rank steps (collectives), rank 0 records
+        tr.step(Xd, Yd)
+    sc.stream_synchronize()
+    cnt, pms, pfl = sc.profile_read()
+    sc.profile_enable(0)
     if rank == 0:
-        peaks = _peaks()
-        sc.profile_enable(1)
-        for _ in range(min(args.steps, 5)):
-            tr.step(Xd, Yd)
-        sc.stream_synchronize()
-        cnt, pms, pfl = sc.profile_read()
-        sc.profile_enable(0)
         if cnt and pms > 0:
             ach = pfl / (pms / 1e3) / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": ach / peaks["tensor"],
