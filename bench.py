@@ -161,6 +161,7 @@ def setup_data_parallel(model, world, local_rank):
     sc.set_stream(stream.cuda_stream)               # the engine enqueues on the stream NCCL orders against
     full = torch.as_tensor(_ArenaView(model.grads.main_ptr, model.n_arena), device="cuda")
     from ml_framework_b200 import dp
+    model._arena_allreduce = lambda: dist.all_reduce(full, op=dist.ReduceOp.SUM)     # whole arena, stream-ordered
     dp.attach(model, world,
               reduce_range=lambda b, e: dist.all_reduce(full[b:e], op=dist.ReduceOp.SUM, async_op=True),
               wait=lambda w: w.wait())
@@ -198,16 +199,21 @@ def run_gpu(args, work):
     # ---- warm-up: eager steps until the memory pool has stopped growing, then (single process) capture the step
     # (with several ranks every rank must run the SAME number of steps: each step holds collectives)
     reserved = -1
-    for i in range(max(args.warmup, 3) + (2 if world > 1 else 8)):
+    for i in range(max(args.warmup, 3) + (17 if dist is not None else 8)):      # NCCL sets its channels up lazily
         tr.step(Xd, Yd)
         sc.stream_synchronize()
         r = sc.pool_bytes_reserved()
-        if world == 1 and i + 1 >= max(args.warmup, 3) and r == reserved:
+        if dist is None and i + 1 >= max(args.warmup, 3) and r == reserved:
             break
         reserved = r
-    use_graph = (dist is None and not args.no_graph)
+    use_graph = not args.no_graph
     eager_ms = None
-    if use_graph:
+    if use_graph and dist is not None:
+        loss_t = tr.capture_data_parallel(Xd, Yd, tr.model._arena_allreduce)
+        for _ in range(args.warmup):
+            tr.replay_data_parallel()
+        run_step = tr.replay_data_parallel
+    elif use_graph:
         e0, e1 = sc.event_create(), sc.event_create()
         sc.event_record(e0)
         for _ in range(5):
@@ -309,7 +315,9 @@ def run_gpu(args, work):
                 "e2e": {"value": e2e, "unit": "samples/s", "h2d_bytes_per_step": int(X.nbytes + Y.nbytes) * world,
                         "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
                 "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": launches_per_step, "final_loss": last,
-                "step_mode": "CUDA graph replay of the captured step" if use_graph else "eager launches",
+                "step_mode": ("eager launches, bucketed all-reduce overlapping backward" if not use_graph else
+                              "CUDA graph replay of forward+backward, one NCCL all-reduce of the gradient arena, fused optimizer"
+                              if dist is not None else "CUDA graph replay of the captured step"),
                 "eager_ms_per_step": eager_ms,
                 "algorithmic_gflop_per_step": work.flops_per_sample() * n * world / 1e9,
                 "roofline": roof, "cpu_baseline": cpu}

@@ -100,6 +100,37 @@ class Trainer:
         sc.graph_launch(self._graph)
         return self._graph_keep[2]
 
+    def capture_data_parallel(self, X, Y, allreduce_arena):
+        """Data-parallel variant: records forward + loss + backward (gradients gathered in the arena) as one graph;
+        `replay_data_parallel` then launches it, calls `allreduce_arena()` (one in-place sum of the whole gradient
+        arena over the ranks, enqueued on the engine's stream) and enqueues the optimizer.  The bucketed overlap of
+        the eager path is traded for a step without per-kernel launch cost; the arena is a few MB."""
+        if not (isinstance(X, S.Tensor) and isinstance(Y, S.Tensor)):
+            raise TypeError("capture needs device-resident Tensors")
+        hook, self.model._on_grad_ready = self.model._on_grad_ready, None
+        sc.graph_begin()
+        try:
+            loss = self.forward_backward(X, Y)
+            self.model.gather_grads()
+        except Exception:
+            try:
+                sc.graph_end()
+            except Exception:
+                pass
+            self.model._on_grad_ready = hook
+            raise
+        self._graph = sc.graph_end()
+        self._graph_keep = (X, Y, loss, self.pred, hook)
+        self._graph_allreduce = allreduce_arena
+        return loss
+
+    def replay_data_parallel(self):
+        sc.graph_launch(self._graph)
+        self._graph_allreduce()
+        self.opt.advance()
+        self.opt._enqueue()
+        return self._graph_keep[2]
+
     def release_graph(self):
         g = getattr(self, "_graph", None)
         if g:
