@@ -41,14 +41,24 @@ static EncodeIm2colFn encode_im2col_fn() {
 
 // Channels-last bf16 tensor [NB, H, W, Cp]; windows of R x S taps, lower padding (ph, pw), traversal stride (sh, sw).
 // The box of valid window corners runs from (-pw, -ph) to (W + pw_up - S, H + ph_up - R) with symmetric padding.
+static int make_map_im2col_box(CUtensorMap *m, const void *base, int NB, int H, int W, int Cp, int sh, int sw, int lower_w, int lower_h,
+                               int upper_w, int upper_h, int channels_per_pixel, int pixels_per_column);
+
 static int make_map_im2col(CUtensorMap *m, const void *base, int NB, int H, int W, int Cp, int R, int S, int sh, int sw, int ph, int pw,
                            int channels_per_pixel, int pixels_per_column) {
+    return make_map_im2col_box(m, base, NB, H, W, Cp, sh, sw, -pw, -ph, pw - (S - 1), ph - (R - 1), channels_per_pixel, pixels_per_column);
+}
+
+// General form: window corners run over w in [lower_w, W + upper_w), h in [lower_h, H + upper_h), stepping by (sw, sh).
+static int make_map_im2col_box(CUtensorMap *m, const void *base, int NB, int H, int W, int Cp, int sh, int sw, int lower_w, int lower_h,
+                               int upper_w, int upper_h, int channels_per_pixel, int pixels_per_column) {
+    const int R = 0, S = 0, ph = -lower_h, pw = -lower_w;
     EncodeIm2colFn enc = encode_im2col_fn();
     if (!enc) return fail(SEERA_E_CUDA, "cuTensorMapEncodeIm2col is not available from this driver");
     cuuint64_t dims[4] = {(cuuint64_t)Cp, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)NB};
     cuuint64_t strides[3] = {(cuuint64_t)Cp * 2, (cuuint64_t)W * Cp * 2, (cuuint64_t)H * W * Cp * 2};
-    int lower[2] = {-pw, -ph};
-    int upper[2] = {pw - (S - 1), ph - (R - 1)};
+    int lower[2] = {lower_w, lower_h};
+    int upper[2] = {upper_w, upper_h};
     cuuint32_t estr[4] = {1, (cuuint32_t)sw, (cuuint32_t)sh, 1};
     CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, lower, upper,
                      (cuuint32_t)channels_per_pixel, (cuuint32_t)pixels_per_column, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -148,6 +158,41 @@ static int make_weight_shadow(const float *Wt, int O, int I, int taps, long long
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, "shadow_weight");
 }
 
+// Filter shadow of one output phase of a strided data gradient: out[o][(t',u')][ip] = W[o*so + i*si + r*S + s] with
+// r = r0 + sh*(Ta-1-t'), s = s0 + sw*(Ub-1-u')  (the taps that reach this phase, flipped), zero for i >= I.
+template <int NS>
+__global__ void __launch_bounds__(256) shadow_weight_phase_kernel(const float *__restrict__ Wt, int O, int I, int Ip, long long so, long long si,
+                                                                  int S, int r0, int sh, int Ta, int s0, int sw, int Ub,
+                                                                  __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
+                                                                  __nv_bfloat16 *__restrict__ d2) {
+    const int taps = Ta * Ub;
+    long long total = (long long)O * taps * Ip;
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    for (long long e = tid; e < total; e += nthr) {
+        int i = (int)(e % Ip); long long t2 = e / Ip;
+        int tap = (int)(t2 % taps); int o = (int)(t2 / taps);
+        int tp = tap / Ub, up = tap - tp * Ub;
+        int r = r0 + sh * (Ta - 1 - tp), sx = s0 + sw * (Ub - 1 - up);
+        float v = i < I ? __ldg(Wt + o * so + i * si + r * S + sx) : 0.f;
+        __nv_bfloat16 h = __float2bfloat16_rn(v);
+        d0[e] = h;
+        if (NS >= 2) { v -= __bfloat162float(h); __nv_bfloat16 l = __float2bfloat16_rn(v); d1[e] = l;
+                       if (NS >= 3) { v -= __bfloat162float(l); d2[e] = __float2bfloat16_rn(v); } }
+    }
+}
+
+// Output of one phase: row m = (img, i, j) of the phase grid is pixel (a + sh*i, b + sw*j) of the full-resolution tensor.
+struct StorePhaseRows {
+    static constexpr bool kMContiguous = true;
+    float *out; int Nch, H, W, Hg, Wg, a, b, sh, sw;
+    __device__ float *row(int m) const {
+        int pg = Hg * Wg, img = m / pg, rem = m - img * pg, i = rem / Wg, j = rem - i * Wg;
+        return out + (long long)img * Nch * H * W + (long long)(a + sh * i) * W + (b + sw * j);
+    }
+    __device__ long long nstride() const { return (long long)H * W; }
+    __device__ void operator()(int m, int n, float v) const { row(m)[n * nstride()] = v; }
+};
+
 // dW element for accumulator row m = (tap, channel) and column n = output-side channel: dW[(n*C + c)*taps + tap]
 struct StoreWgrad {
     static constexpr bool kMContiguous = true;
@@ -199,6 +244,87 @@ static int tma_wgrad(const NhwcShadow &x, const NhwcShadow &dy, float *dW, int R
     }
     double flops = 2.0 * p.K * (double)F * x.C * R * S;
     return launch_tma_gemm(maps, p, StoreWgrad{dW, x.C, R * S, p.cchunks * 64}, ns, true, flops, name);
+}
+
+// ---- strided data gradient by output phase ---------------------------------------------------------------------
+// out[n, c, h, w] = sum over (f, r, s) with (h + ph - r) % sh == 0 and (w + pw - s) % sw == 0 of
+//                   g[n, f, (h + ph - r)/sh, (w + pw - s)/sw] * Wt[o = c, i = f, r, s].
+// Output pixels with h % sh == a and w % sw == b see only the taps r = r0 + sh*t, s = s0 + sw*u (r0 = (a + ph) % sh,
+// s0 = (b + pw) % sw), and over the phase grid (i, j) = (h / sh, w / sw) the sum is a unit-stride convolution of g with
+// those taps: window corner (i + qa - (Ta-1), j + qb - (Ub-1)), qa = (a + ph - r0)/sh.  Each phase is one TMA
+// implicit-GEMM launch with its own window box and filter shadow, scattering into the full-resolution tensor.
+struct PhaseAxis { int r0, T, q, lower, upper, G; };
+static PhaseAxis phase_axis(int a, int pad, int stride, int K, int full, int gdim) {
+    PhaseAxis x;
+    x.r0 = (a + pad) % stride;
+    x.T = x.r0 < K ? (K - x.r0 + stride - 1) / stride : 0;
+    x.q = (a + pad - x.r0) / stride;
+    x.G = a < full ? (full - a + stride - 1) / stride : 0;
+    x.lower = x.q - (x.T - 1);
+    x.upper = x.G - gdim + x.lower;
+    return x;
+}
+static bool phases_supported(int H, int W, int GH, int GW, int R, int S, int sh, int sw, int ph, int pw) {
+    for (int a = 0; a < sh; a++) {
+        PhaseAxis y = phase_axis(a, ph, sh, R, H, GH);
+        if (y.T && y.G && (y.lower < -128 || y.lower > 127 || y.upper > 0 || y.upper < -128)) return false;
+    }
+    for (int b = 0; b < sw; b++) {
+        PhaseAxis x = phase_axis(b, pw, sw, S, W, GW);
+        if (x.T && x.G && (x.lower < -128 || x.lower > 127 || x.upper > 0 || x.upper < -128)) return false;
+    }
+    return true;
+}
+static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, long long si, float *out, int Nch, int H, int W,
+                            int R, int S, int sh, int sw, int ph, int pw, int ns, const char *name) {
+    cudaStream_t st = rt().stream;
+    bool hole = false;
+    for (int a = 0; a < sh; a++) hole |= phase_axis(a, ph, sh, R, H, g.H).T == 0;
+    for (int b = 0; b < sw; b++) hole |= phase_axis(b, pw, sw, S, W, g.W).T == 0;
+    if (hole) {       // stride larger than the filter: some output pixels receive nothing
+        cudaError_t e = cudaMemsetAsync(out, 0, (size_t)g.NB * Nch * H * W * sizeof(float), st);
+        if (e != cudaSuccess) return check_cuda(e, name);
+    }
+    const int Ip = g.Cp;
+    for (int a = 0; a < sh; a++) {
+        PhaseAxis y = phase_axis(a, ph, sh, R, H, g.H);
+        if (!y.T || !y.G) continue;
+        for (int b = 0; b < sw; b++) {
+            PhaseAxis x = phase_axis(b, pw, sw, S, W, g.W);
+            if (!x.T || !x.G) continue;
+            Shadow wk;
+            const int taps = y.T * x.T;
+            if (int e = alloc_shadow(wk, Nch, taps * Ip, ns)) return e;
+            long long total = (long long)Nch * taps * Ip;
+            int grid = stride_grid(total);
+            if (ns == 1) shadow_weight_phase_kernel<1><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2]);
+            else if (ns == 2) shadow_weight_phase_kernel<2><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2]);
+            else shadow_weight_phase_kernel<3><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2]);
+            count_launch();
+            cudaError_t ce = cudaGetLastError();
+            if (ce != cudaSuccess) { free_shadow(wk); return check_cuda(ce, "shadow_weight_phase"); }
+
+            TmaGemmParams p{};
+            p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
+            p.M = g.NB * y.G * x.G; p.N = Nch;
+            p.cchunks = (g.Cp + 63) / 64; p.cpad = g.Cp; p.taps = taps; p.S = x.T;
+            p.K = p.taps * p.cchunks * 64;
+            p.OW = x.G; p.OHW = y.G * x.G; p.sw = 1; p.sh = 1; p.pw = -x.lower; p.ph = -y.lower;
+            p.bn = tma_pick_bn(Nch, ns, 0);
+            TmaMaps maps;
+            int e = SEERA_OK;
+            for (int i = 0; i < 3 && !e; i++) {
+                int j = i < ns ? i : 0;
+                e = make_map_im2col_box(&maps.a[i], g.p[j], g.NB, g.H, g.W, g.Cp, 1, 1, x.lower, y.lower, x.upper, y.upper, 64, TC_BM);
+                if (!e) e = make_map_2d(&maps.b[i], wk.p[j], wk.rows, wk.cols, wk.ld, 64, p.bn);
+            }
+            double flops = 2.0 * p.M * (double)Nch * g.C * taps;
+            if (!e) e = launch_tma_gemm(maps, p, StorePhaseRows{out, Nch, H, W, y.G, x.G, a, b, sh, sw}, ns, false, flops, name);
+            free_shadow(wk);
+            if (e) return e;
+        }
+    }
+    return SEERA_OK;
 }
 
 // ---- first-layer case: C*R*S <= 64 ----------------------------------------------------------------------------
@@ -301,6 +427,8 @@ int seera_tma_conv2d_bwd(const float *Wt, const float *X, const float *dY, float
         if (sh == 1 && sw == 1) {     // dX = forward convolution of dY with flipped taps and swapped channel roles, pad' = K-1-pad
             s = make_weight_shadow(Wt, C, F, R * S, R * S, (long long)C * R * S, 1, ns, wd);
             if (!s) s = tma_fprop(dys, wd, dX, C, R, S, 1, 1, R - 1 - ph, S - 1 - pw, H, W, ns, "cuda_conv2d_bwd(dX)");
+        } else if (phases_supported(H, W, OH, OW, R, S, sh, sw, ph, pw)) {
+            s = tma_dgrad_phases(dys, Wt, R * S, (long long)C * R * S, dX, C, H, W, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dX)");
         } else {
             s = seera_tc_conv2d_bwd(Wt, X, dY, dX, nullptr, NB, C, H, W, F, R, S, sh, sw, ph, pw);
         }
@@ -330,14 +458,19 @@ int seera_tma_convT_fwd(const float *X, const float *Wt, float *out, int NB, int
     int Ho = (H - 1) * sh - 2 * ph + KH, Wo = (W - 1) * sw - 2 * pw + KW;
     if (!conv_ok(NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw) || Ho < 1 || Wo < 1 || !X || !Wt || !out)
         return fail(SEERA_E_ARG, "cuda_conv2DTranpose_fwd: bad argument");
-    if (sh != 1 || sw != 1 || !tma_conv_supported(NB, KH, KW, sh, sw, ph, pw))
+    const bool unit = sh == 1 && sw == 1;
+    if (!tma_conv_supported(NB, KH, KW, sh, sw, ph, pw) || (!unit && !phases_supported(Ho, Wo, H, W, KH, KW, sh, sw, ph, pw)))
         return seera_tc_convT_fwd(X, Wt, out, NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw);
     int ns = precision_copies();
     NhwcShadow xs; Shadow wd;
     int taps = KH * KW;
     int s = make_nhwc(X, NB, Cin, H, W, ns, xs);
-    if (!s) s = make_weight_shadow(Wt, Cout, Cin, taps, taps, (long long)Cout * taps, 1, ns, wd);
-    if (!s) s = tma_fprop(xs, wd, out, Cout, KH, KW, 1, 1, KH - 1 - ph, KW - 1 - pw, Ho, Wo, ns, "cuda_conv2DTranpose_fwd");
+    if (!s && unit) {
+        s = make_weight_shadow(Wt, Cout, Cin, taps, taps, (long long)Cout * taps, 1, ns, wd);
+        if (!s) s = tma_fprop(xs, wd, out, Cout, KH, KW, 1, 1, KH - 1 - ph, KW - 1 - pw, Ho, Wo, ns, "cuda_conv2DTranpose_fwd");
+    } else if (!s) {
+        s = tma_dgrad_phases(xs, Wt, taps, (long long)Cout * taps, out, Cout, Ho, Wo, KH, KW, sh, sw, ph, pw, ns, "cuda_conv2DTranpose_fwd");
+    }
     free_nhwc(xs); free_shadow(wd);
     return s;
 }

@@ -51,7 +51,8 @@ def test_matmul_and_backward(E, mode, M, K, N):
 
 CONV = [(1, 1, 5, 5, 1, 3, 3, 1, 1, 0, 0), (2, 3, 8, 8, 4, 3, 3, 1, 1, 1, 1), (3, 5, 9, 7, 6, 3, 3, 2, 1, 1, 2),
         (2, 4, 11, 13, 7, 5, 3, 2, 2, 2, 1), (4, 8, 14, 14, 16, 1, 1, 1, 1, 0, 0), (8, 32, 32, 32, 64, 3, 3, 2, 2, 1, 1),
-        (2, 130, 6, 6, 70, 3, 3, 1, 1, 1, 1), (16, 64, 16, 16, 300, 3, 3, 1, 1, 1, 1)]
+        (2, 130, 6, 6, 70, 3, 3, 1, 1, 1, 1), (16, 64, 16, 16, 300, 3, 3, 1, 1, 1, 1),
+        (2, 3, 9, 9, 4, 1, 1, 2, 2, 0, 0), (2, 8, 32, 32, 8, 3, 3, 2, 2, 0, 0), (2, 16, 15, 17, 12, 4, 4, 3, 2, 2, 1)]
 
 
 @pytest.mark.parametrize("mode", [1, 2])
@@ -69,7 +70,8 @@ def test_conv2d(E, mode, shape):
 
 
 CONVT = [(1, 1, 4, 4, 1, 3, 3, 1, 1, 0, 0), (2, 4, 5, 6, 3, 4, 3, 2, 2, 1, 0), (8, 64, 16, 16, 32, 4, 4, 2, 2, 1, 1),
-         (3, 6, 7, 5, 5, 3, 3, 1, 1, 1, 1), (2, 5, 5, 5, 7, 3, 5, 3, 2, 1, 2), (4, 32, 16, 16, 1, 3, 3, 1, 1, 1, 1)]
+         (3, 6, 7, 5, 5, 3, 3, 1, 1, 1, 1), (2, 5, 5, 5, 7, 3, 5, 3, 2, 1, 2), (4, 32, 16, 16, 1, 3, 3, 1, 1, 1, 1),
+         (2, 4, 5, 5, 3, 2, 2, 3, 3, 0, 0), (16, 128, 8, 8, 64, 4, 4, 2, 2, 1, 1)]
 
 
 @pytest.mark.parametrize("mode", [1, 2])
