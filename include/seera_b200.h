@@ -197,6 +197,17 @@ enum { SEERA_ACT_NONE = 0, SEERA_ACT_RELU = 1, SEERA_ACT_SIGMOID = 2, SEERA_ACT_
 /* y = act(z + bias[channel]); element i belongs to channel (i / inner) % channels.
  * Replaces broadcast_add_4d + cuda_*_fwd (Seera.py:136-137, :255-258). In place allowed (y == z). */
 int seera_bias_act_fwd(const float *z, const float *bias, float *y, int size, int channels, int inner, int act);
+/* Forward products with the bias and activation applied before the one store of the output:
+ *   C   = act(A[M,K] * B[K,N] + bias[n])                       (Dense.forward, Seera.py:133-138)
+ *   out = act(conv2d(image, kernel) + bias[f])                 (Conv2D.forward, Seera.py:235-259)
+ *   out = act(conv2DTranspose(X, W) + bias[cout])              (ConvTranspose2D.forward, Seera.py:398-423)
+ * Arguments as cuda_matmul / cuda_conv2d_fwd / cuda_conv2DTranpose_fwd plus bias (may be NULL) and a SEERA_ACT_*
+ * code.  Same values as the product followed by seera_bias_act_fwd in place. */
+int seera_matmul_bias_act_fwd(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, int act);
+int seera_conv2d_bias_act_fwd(const float *image, const float *kernel, const float *bias, float *out, int batchN, int C, int H, int W,
+                              int F, int R, int S, int pad_h, int pad_w, int stride_h, int stride_w, int act);
+int seera_conv2DTranspose_bias_act_fwd(const float *X, const float *W, const float *bias, float *out, int batch, int Cin, int Hin,
+                                       int Win, int Cout, int KH, int KW, int strideh, int stridew, int padh, int padw, int act);
 /* dz = dy * act'(y), with the derivative written in terms of the OUTPUT y (relu: y > 0; sigmoid:
  * y(1-y); tanh: 1-y^2), and dbias[c] = sum of dz over that channel.  Replaces cuda_elemmult with the
  * stored local gradient plus broadcast_mul_4d + three cuda_sum_fwd (Seera_Engine.py:571-583, :43-65). */

@@ -207,8 +207,9 @@ struct StoreWgrad {
 
 // Y[NB, F, OH, OW] = conv(X_nhwc, weights Wk[F][tap][Cp]) with window R x S, stride, lower padding.
 static int tma_fprop(const NhwcShadow &x, const Shadow &wk, float *Y, int F, int R, int S, int sh, int sw, int ph, int pw,
-                     int OH, int OW, int ns, const char *name) {
+                     int OH, int OW, int ns, const char *name, const float *bias = nullptr, int act = 0) {
     TmaGemmParams p{};
+    p.bias = bias; p.act = act;
     p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
     p.M = x.NB * OH * OW; p.N = F;
     p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
@@ -276,12 +277,14 @@ static bool phases_supported(int H, int W, int GH, int GW, int R, int S, int sh,
     return true;
 }
 static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, long long si, float *out, int Nch, int H, int W,
-                            int R, int S, int sh, int sw, int ph, int pw, int ns, const char *name) {
+                            int R, int S, int sh, int sw, int ph, int pw, int ns, const char *name, const float *bias = nullptr,
+                            int act = 0) {
     cudaStream_t st = rt().stream;
     bool hole = false;
     for (int a = 0; a < sh; a++) hole |= phase_axis(a, ph, sh, R, H, g.H).T == 0;
     for (int b = 0; b < sw; b++) hole |= phase_axis(b, pw, sw, S, W, g.W).T == 0;
-    if (hole) {       // stride larger than the filter: some output pixels receive nothing
+    if (hole) {       // stride larger than the filter: some output pixels receive nothing from the sum
+        if (bias || act) return fail(SEERA_E_LIMIT, "%s: fused bias/activation needs every output pixel under some tap", name);
         cudaError_t e = cudaMemsetAsync(out, 0, (size_t)g.NB * Nch * H * W * sizeof(float), st);
         if (e != cudaSuccess) return check_cuda(e, name);
     }
@@ -305,6 +308,7 @@ static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, 
             if (ce != cudaSuccess) { free_shadow(wk); return check_cuda(ce, "shadow_weight_phase"); }
 
             TmaGemmParams p{};
+            p.bias = bias; p.act = act;
             p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
             p.M = g.NB * y.G * x.G; p.N = Nch;
             p.cchunks = (g.Cp + 63) / 64; p.cpad = g.Cp; p.taps = taps; p.S = x.T;
@@ -327,51 +331,6 @@ static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, 
     return SEERA_OK;
 }
 
-// ---- first-layer case: C*R*S <= 64 ----------------------------------------------------------------------------
-// With one or three input channels a (tap, 64-channel) slice is almost all padding.  Here the whole patch of a
-// pixel fits one K step, so the patches are written once as a bf16 matrix [pixels, C*R*S] (a few tens of MB) and
-// the forward pass and the weight gradient run as plain TMA GEMMs on it.
-template <int NS>
-__global__ void __launch_bounds__(256) patch_rows_kernel(const float *__restrict__ X, int C, int H, int W, int OH, int OW, int R, int S,
-                                                         int sh, int sw, int ph, int pw, long long pixels, int K, int Kp,
-                                                         __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
-                                                         __nv_bfloat16 *__restrict__ d2) {
-    const int groups = Kp >> 3;
-    long long total = pixels * groups;
-    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
-    for (long long e = tid; e < total; e += nthr) {
-        long long pix = e / groups;
-        int kg = (int)(e - pix * groups);
-        int P = OH * OW, img = (int)(pix / P), rem = (int)(pix - (long long)img * P), oh = rem / OW, ow = rem - oh * OW;
-        const float *xb = X + (long long)img * C * H * W;
-        float v[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            int k = kg * 8 + i, c = k / (R * S), rs = k - c * R * S, r = rs / S, sx = rs - r * S;
-            int ih = oh * sh + r - ph, iw = ow * sw + sx - pw;
-            v[i] = (k < K && (unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) ? __ldg(xb + ((long long)c * H + ih) * W + iw) : 0.f;
-        }
-        long long o = pix * Kp + kg * 8;
-        *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
-        if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
-        if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
-    }
-}
-static int make_patch_rows(const float *X, int NB, int C, int H, int W, int OH, int OW, int R, int S, int sh, int sw, int ph, int pw,
-                           int ns, Shadow &s) {
-    int K = C * R * S;
-    long long pixels = (long long)NB * OH * OW;
-    if (int e = alloc_shadow(s, (int)pixels, K, ns)) return e;
-    int grid = stride_grid(pixels * (s.ld / 8));
-    cudaStream_t st = rt().stream;
-    if (ns == 1) patch_rows_kernel<1><<<grid, 256, 0, st>>>(X, C, H, W, OH, OW, R, S, sh, sw, ph, pw, pixels, K, s.ld, s.p[0], s.p[1], s.p[2]);
-    else if (ns == 2) patch_rows_kernel<2><<<grid, 256, 0, st>>>(X, C, H, W, OH, OW, R, S, sh, sw, ph, pw, pixels, K, s.ld, s.p[0], s.p[1], s.p[2]);
-    else patch_rows_kernel<3><<<grid, 256, 0, st>>>(X, C, H, W, OH, OW, R, S, sh, sw, ph, pw, pixels, K, s.ld, s.p[0], s.p[1], s.p[2]);
-    count_launch();
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? SEERA_OK : check_cuda(e, "patch_rows");
-}
-
 static bool conv_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     return NB >= 1 && C >= 1 && H >= 1 && W >= 1 && F >= 1 && R >= 1 && S >= 1 && sh >= 1 && sw >= 1 && ph >= 0 && pw >= 0 &&
            (long long)NB * (C > F ? C : F) * H * W * (long long)(sh * sw) < (1LL << 31);
@@ -390,25 +349,28 @@ extern "C" {
 
 int seera_tma_conv2d_fwd(const float *X, const float *Wt, float *Y, int NB, int C, int H, int W, int F, int R, int S,
                          int ph, int pw, int sh, int sw) {
+    return seera_tma_conv2d_bias_act_fwd(X, Wt, nullptr, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw, SEERA_ACT_NONE);
+}
+
+// Y = act(conv(X, Wt) + bias[f]); bias may be null.
+int seera_tma_conv2d_bias_act_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F,
+                                  int R, int S, int ph, int pw, int sh, int sw, int act) {
     SEERA_ENSURE();
     if (!conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) || !X || !Wt || !Y) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: bad argument");
     int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
     if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: kernel larger than padded input");
-    if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return seera_tc_conv2d_fwd(X, Wt, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw);
-    int ns = precision_copies();
-    NhwcShadow xs; Shadow wk;
-    int s;
-    if (C * R * S <= 64) {            // first-layer case: patches as rows, one K step
-        Shadow patches;
-        s = make_patch_rows(X, NB, C, H, W, OH, OW, R, S, sh, sw, ph, pw, ns, patches);
-        if (!s) s = make_shadow(Wt, F, C * R * S, ns, wk);
-        if (!s) s = run_tma_gemm(patches, 0, wk, 0, StorePixelRows{Y, F, OH * OW}, NB * OH * OW, F, C * R * S, false, "cuda_conv2d_fwd");
-        free_shadow(patches); free_shadow(wk);
+    if (conv_first_applies(C, R, S))  // short patch: direct fp32 kernel
+        return conv_first_fwd(X, Wt, bias, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw, act, "cuda_conv2d_fwd");
+    if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) {
+        int s = seera_tc_conv2d_fwd(X, Wt, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw);
+        if (!s && (bias || act)) s = seera_bias_act_fwd(Y, bias, Y, NB * F * OH * OW, F, OH * OW, act);
         return s;
     }
-    s = make_nhwc(X, NB, C, H, W, ns, xs);
+    int ns = precision_copies();
+    NhwcShadow xs; Shadow wk;
+    int s = make_nhwc(X, NB, C, H, W, ns, xs);
     if (!s) s = make_weight_shadow(Wt, F, C, R * S, (long long)C * R * S, R * S, 0, ns, wk);
-    if (!s) s = tma_fprop(xs, wk, Y, F, R, S, sh, sw, ph, pw, OH, OW, ns, "cuda_conv2d_fwd");
+    if (!s) s = tma_fprop(xs, wk, Y, F, R, S, sh, sw, ph, pw, OH, OW, ns, "cuda_conv2d_fwd", bias, act);
     free_nhwc(xs); free_shadow(wk);
     return s;
 }
@@ -422,7 +384,9 @@ int seera_tma_conv2d_bwd(const float *Wt, const float *X, const float *dY, float
     if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return seera_tc_conv2d_bwd(Wt, X, dY, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw);
     int ns = precision_copies();
     NhwcShadow dys, xs; Shadow wd;
-    int s = make_nhwc(dY, NB, F, OH, OW, ns, dys);
+    const bool first = conv_first_applies(C, R, S);
+    int s = SEERA_OK;
+    if (dX || (dW && !first)) s = make_nhwc(dY, NB, F, OH, OW, ns, dys);
     if (!s && dX) {
         if (sh == 1 && sw == 1) {     // dX = forward convolution of dY with flipped taps and swapped channel roles, pad' = K-1-pad
             s = make_weight_shadow(Wt, C, F, R * S, R * S, (long long)C * R * S, 1, ns, wd);
@@ -434,13 +398,8 @@ int seera_tma_conv2d_bwd(const float *Wt, const float *X, const float *dY, float
         }
     }
     if (!s && dW) {
-        if (C * R * S <= 64) {        // first-layer case: dW[f][k] = sum_pix dY[pix][f] * patches[pix][k]
-            Shadow patches, dyr;
-            s = make_patch_rows(X, NB, C, H, W, OH, OW, R, S, sh, sw, ph, pw, ns, patches);
-            for (int i = 0; i < 3; i++) dyr.p[i] = dys.p[i];
-            dyr.rows = NB * OH * OW; dyr.cols = dys.Cp; dyr.ld = dys.Cp;
-            if (!s) s = run_tma_gemm(patches, 1, dyr, 1, StoreDenseT{dW, C * R * S}, C * R * S, F, NB * OH * OW, true, "cuda_conv2d_bwd(dW)");
-            free_shadow(patches);
+        if (first) {                  // short patch: direct fp32 kernel on the NCHW tensors
+            s = conv_first_wgrad(X, dY, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw, "cuda_conv2d_bwd(dW)");
         } else {
             s = make_nhwc(X, NB, C, H, W, ns, xs);
             if (!s) s = tma_wgrad(xs, dys, dW, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dW)");
@@ -454,22 +413,33 @@ int seera_tma_conv2d_bwd(const float *Wt, const float *X, const float *dY, float
 // whose filter bank has Cin filters over Cout channels.
 int seera_tma_convT_fwd(const float *X, const float *Wt, float *out, int NB, int Cin, int H, int W, int Cout, int KH, int KW,
                         int sh, int sw, int ph, int pw) {
+    return seera_tma_convT_bias_act_fwd(X, Wt, nullptr, out, NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw, SEERA_ACT_NONE);
+}
+
+// out = act(convT(X, Wt) + bias[cout]); bias may be null.
+int seera_tma_convT_bias_act_fwd(const float *X, const float *Wt, const float *bias, float *out, int NB, int Cin, int H, int W,
+                                 int Cout, int KH, int KW, int sh, int sw, int ph, int pw, int act) {
     SEERA_ENSURE();
     int Ho = (H - 1) * sh - 2 * ph + KH, Wo = (W - 1) * sw - 2 * pw + KW;
     if (!conv_ok(NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw) || Ho < 1 || Wo < 1 || !X || !Wt || !out)
         return fail(SEERA_E_ARG, "cuda_conv2DTranpose_fwd: bad argument");
     const bool unit = sh == 1 && sw == 1;
-    if (!tma_conv_supported(NB, KH, KW, sh, sw, ph, pw) || (!unit && !phases_supported(Ho, Wo, H, W, KH, KW, sh, sw, ph, pw)))
-        return seera_tc_convT_fwd(X, Wt, out, NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw);
+    if (!tma_conv_supported(NB, KH, KW, sh, sw, ph, pw) || (!unit && !phases_supported(Ho, Wo, H, W, KH, KW, sh, sw, ph, pw)) ||
+        (!unit && (bias || act) && (sh > KH || sw > KW))) {
+        int s = seera_tc_convT_fwd(X, Wt, out, NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw);
+        if (!s && (bias || act)) s = seera_bias_act_fwd(out, bias, out, NB * Cout * Ho * Wo, Cout, Ho * Wo, act);
+        return s;
+    }
     int ns = precision_copies();
     NhwcShadow xs; Shadow wd;
     int taps = KH * KW;
     int s = make_nhwc(X, NB, Cin, H, W, ns, xs);
     if (!s && unit) {
         s = make_weight_shadow(Wt, Cout, Cin, taps, taps, (long long)Cout * taps, 1, ns, wd);
-        if (!s) s = tma_fprop(xs, wd, out, Cout, KH, KW, 1, 1, KH - 1 - ph, KW - 1 - pw, Ho, Wo, ns, "cuda_conv2DTranpose_fwd");
+        if (!s) s = tma_fprop(xs, wd, out, Cout, KH, KW, 1, 1, KH - 1 - ph, KW - 1 - pw, Ho, Wo, ns, "cuda_conv2DTranpose_fwd", bias, act);
     } else if (!s) {
-        s = tma_dgrad_phases(xs, Wt, taps, (long long)Cout * taps, out, Cout, Ho, Wo, KH, KW, sh, sw, ph, pw, ns, "cuda_conv2DTranpose_fwd");
+        s = tma_dgrad_phases(xs, Wt, taps, (long long)Cout * taps, out, Cout, Ho, Wo, KH, KW, sh, sw, ph, pw, ns, "cuda_conv2DTranpose_fwd",
+                             bias, act);
     }
     free_nhwc(xs); free_shadow(wd);
     return s;

@@ -41,4 +41,32 @@ int seera_cuda_conv2DTranspose_bwd(const float *W, const float *X, const float *
     return rt().precision ? (rt().conv_tma ? seera_tma_convT_bwd(W, X, dY, dX, dW, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw) : seera_tc_convT_bwd(W, X, dY, dX, dW, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw)) : seera_simt_convT_bwd(W, X, dY, dX, dW, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw);
 }
 
+
+// ---- forward products with the bias and activation applied before the one store of the output ----------------
+static int bias_act_after(int s, float *y, const float *bias, long long size, int channels, int inner, int act) {
+    if (s || (!bias && !act)) return s;
+    if (size > 0x7fffffff) return seera::fail(SEERA_E_LIMIT, "bias_act: tensor too large");
+    return seera_bias_act_fwd(y, bias, y, (int)size, channels, inner, act);
+}
+int seera_matmul_bias_act_fwd(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, int act) {
+    if (rt().precision && rt().dense_tma) return seera_tma_matmul_bias_act(A, B, bias, C, M, N, K, 1, act);
+    return bias_act_after(seera_cuda_matmul(A, B, C, M, N, K, 1), C, bias, (long long)M * N, N, 1, act);
+}
+int seera_conv2d_bias_act_fwd(const float *image, const float *kernel, const float *bias, float *out, int batchN, int C, int H, int W,
+                              int F, int R, int S, int pad_h, int pad_w, int stride_h, int stride_w, int act) {
+    if (rt().precision && rt().conv_tma)
+        return seera_tma_conv2d_bias_act_fwd(image, kernel, bias, out, batchN, C, H, W, F, R, S, pad_h, pad_w, stride_h, stride_w, act);
+    int OH = (H + 2 * pad_h - R) / (stride_h > 0 ? stride_h : 1) + 1, OW = (W + 2 * pad_w - S) / (stride_w > 0 ? stride_w : 1) + 1;
+    return bias_act_after(seera_cuda_conv2d_fwd(image, kernel, out, batchN, C, H, W, F, R, S, pad_h, pad_w, stride_h, stride_w), out, bias,
+                          (long long)batchN * F * OH * OW, F, OH * OW, act);
+}
+int seera_conv2DTranspose_bias_act_fwd(const float *X, const float *W, const float *bias, float *out, int batch, int Cin, int Hin, int Win,
+                                       int Cout, int KH, int KW, int strideh, int stridew, int padh, int padw, int act) {
+    if (rt().precision && rt().conv_tma)
+        return seera_tma_convT_bias_act_fwd(X, W, bias, out, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw, act);
+    int Ho = (Hin - 1) * strideh - 2 * padh + KH, Wo = (Win - 1) * stridew - 2 * padw + KW;
+    return bias_act_after(seera_cuda_conv2DTranpose_fwd(X, W, out, batch, Cin, Hin, Win, Cout, KH, KW, strideh, stridew, padh, padw), out,
+                          bias, (long long)batch * Cout * Ho * Wo, Cout, Ho * Wo, act);
+}
+
 }  // extern "C"

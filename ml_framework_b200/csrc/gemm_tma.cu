@@ -24,6 +24,11 @@ using namespace seera;
 extern "C" {
 
 int seera_tma_matmul(const float *A, const float *B, float *C, int M, int N, int K, int Nbatch) {
+    return seera_tma_matmul_bias_act(A, B, nullptr, C, M, N, K, Nbatch, SEERA_ACT_NONE);
+}
+
+// C = act(A * B + bias[column]); bias may be null.
+int seera_tma_matmul_bias_act(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, int Nbatch, int act) {
     SEERA_ENSURE();
     if (M < 1 || N < 1 || K < 1 || Nbatch < 1 || !A || !B || !C) return fail(SEERA_E_ARG, "cuda_matmul: bad argument");
     long long rows = (long long)M * Nbatch;
@@ -32,7 +37,7 @@ int seera_tma_matmul(const float *A, const float *B, float *C, int M, int N, int
     Shadow sa, sb;
     int s = make_shadow(A, (int)rows, K, ns, sa);
     if (!s) s = make_shadow(B, K, N, ns, sb);
-    if (!s) s = run_tma_gemm(sa, 0, sb, 1, StoreDense{C, N}, (int)rows, N, K, false, "cuda_matmul");
+    if (!s) s = run_tma_gemm(sa, 0, sb, 1, StoreDense{C, N}, (int)rows, N, K, false, "cuda_matmul", bias, act);
     free_shadow(sa); free_shadow(sb);
     return s;
 }

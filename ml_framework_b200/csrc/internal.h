@@ -21,6 +21,11 @@ int seera_tma_convT_fwd(const float *X, const float *Wt, float *out, int NB, int
                         int sh, int sw, int ph, int pw);
 int seera_tma_convT_bwd(const float *Wt, const float *X, const float *dY, float *dX, float *dW, int NB, int Cin, int H, int W,
                         int Cout, int KH, int KW, int sh, int sw, int ph, int pw);
+int seera_tma_matmul_bias_act(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, int Nbatch, int act);
+int seera_tma_conv2d_bias_act_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F,
+                                  int R, int S, int ph, int pw, int sh, int sw, int act);
+int seera_tma_convT_bias_act_fwd(const float *X, const float *Wt, const float *bias, float *out, int NB, int Cin, int H, int W,
+                                 int Cout, int KH, int KW, int sh, int sw, int ph, int pw, int act);
 int seera_tc_matmul(const float *A, const float *B, float *C, int M, int N, int K, int Nbatch);
 int seera_tc_matmul_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB, int M, int N, int K, int Nbatch);
 int seera_tc_conv2d_fwd(const float *X, const float *Wt, float *Y, int NB, int C, int H, int W, int F, int R, int S,
@@ -31,4 +36,13 @@ int seera_tc_convT_fwd(const float *X, const float *Wt, float *out, int NB, int 
                        int sh, int sw, int ph, int pw);
 int seera_tc_convT_bwd(const float *Wt, const float *X, const float *dY, float *dX, float *dW, int NB, int Cin, int H, int W,
                        int Cout, int KH, int KW, int sh, int sw, int ph, int pw);
+}
+
+namespace seera {
+// Direct fp32 kernels for convolutions with C*R*S <= 64 (conv_first.cu); bias may be null.
+bool conv_first_applies(int C, int R, int S);
+int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F, int R, int S,
+                   int ph, int pw, int sh, int sw, int act, const char *name);
+int conv_first_wgrad(const float *X, const float *dY, float *dW, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw,
+                     int ph, int pw, const char *name);
 }

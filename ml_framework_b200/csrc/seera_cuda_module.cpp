@@ -170,6 +170,15 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("host_free_pinned", [](uptr p) { ck(seera_host_free_pinned(P<void>(p))); });
     m.def("bias_act_fwd", [](uptr z, uptr b, uptr y, int n, int ch, int inner, int act) {
         ck(seera_bias_act_fwd(P<const F>(z), P<const F>(b), P<F>(y), n, ch, inner, act)); });
+    m.def("matmul_bias_act_fwd", [](uptr A, uptr B, uptr b, uptr C, int M, int N, int K, int act) {
+        ck(seera_matmul_bias_act_fwd(P<const F>(A), P<const F>(B), P<const F>(b), P<F>(C), M, N, K, act)); });
+    m.def("conv2d_bias_act_fwd", [](uptr x, uptr w, uptr b, uptr o, int N, int C, int H, int W, int Fo, int R, int S, int ph, int pw,
+                                    int sh, int sw, int act) {
+        ck(seera_conv2d_bias_act_fwd(P<const F>(x), P<const F>(w), P<const F>(b), P<F>(o), N, C, H, W, Fo, R, S, ph, pw, sh, sw, act)); });
+    m.def("conv2DTranspose_bias_act_fwd", [](uptr x, uptr w, uptr b, uptr o, int N, int Ci, int H, int W, int Co, int KH, int KW,
+                                             int sh, int sw, int ph, int pw, int act) {
+        ck(seera_conv2DTranspose_bias_act_fwd(P<const F>(x), P<const F>(w), P<const F>(b), P<F>(o), N, Ci, H, W, Co, KH, KW, sh, sw, ph,
+                                              pw, act)); });
     m.def("act_bias_bwd", [](uptr dy, uptr y, uptr dz, uptr db, int n, int ch, int inner, int act) {
         ck(seera_act_bias_bwd(P<const F>(dy), P<const F>(y), P<F>(dz), P<F>(db), n, ch, inner, act)); });
     m.def("softmax_cce_fwd_bwd", [](uptr z, uptr y, uptr p, uptr rows, uptr loss, uptr dz, int N, int C, float eps, float inv) {

@@ -168,6 +168,8 @@ struct TmaGemmParams {
     int cpad, cchunks;       // channel pitch of the weight rows / channels rounded up to 64, in chunks of 64
     float *partial;
     int *status;
+    const float *bias;       // per-column bias added before the store, or null
+    int act;                 // activation applied before the store (0 = none)
 };
 
 constexpr int TG_THREADS = 192;
@@ -357,7 +359,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)local >> 1) & 1u, abortp, p.status, 3)) break;
             tc_fence_after();
             drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, 0, bn, p.M, p.N, cs,
-                              p.partial, (long long)z * p.M * p.N, stage);
+                              p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
@@ -369,13 +371,16 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
 }
 
 template <class CS>
-__global__ void __launch_bounds__(256) tma_splitk_reduce_kernel(const float *__restrict__ partial, CS cs, int M, int N, int splits) {
+__global__ void __launch_bounds__(256) tma_splitk_reduce_kernel(const float *__restrict__ partial, CS cs, int M, int N, int splits,
+                                                                const float *__restrict__ bias, int act) {
     long long total = (long long)M * N;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
     for (long long i = tid; i < total; i += nthr) {
         float s = 0.f;
         for (int z = 0; z < splits; z++) s += partial[(long long)z * total + i];
-        cs((int)(i / N), (int)(i % N), s);
+        const int n = (int)(i % N);
+        if (bias) s += __ldg(bias + n);
+        cs((int)(i / N), n, epilogue_act(s, act));
     }
 }
 
@@ -428,7 +433,13 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
 #define SEERA_TMA_LAUNCH(NSV)                                                                                              \
     {                                                                                                                      \
         auto kern = tma_gemm_kernel<NSV, CS>;                                                                              \
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                            \
+        static int smem_set[64];                     /* per instantiation and device: raise the limit once */              \
+        const int dev = rt().device & 63;                                                                                  \
+        e = cudaSuccess;                                                                                                   \
+        if (!smem_set[dev]) {                                                                                              \
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);                       \
+            if (e == cudaSuccess) smem_set[dev] = 1;                                                                       \
+        }                                                                                                                  \
         if (e == cudaSuccess) {                                                                                            \
             kern<<<grid, TG_THREADS, smem, st>>>(maps.a[0], maps.a[1], maps.a[2], maps.b[0], maps.b[1], maps.b[2], cs, p); \
             e = cudaGetLastError();                                                                                        \
@@ -438,7 +449,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
 #undef SEERA_TMA_LAUNCH
     count_launch();
     if (e == cudaSuccess && p.partial) {
-        tma_splitk_reduce_kernel<<<stride_grid((long long)p.M * p.N), 256, 0, st>>>(p.partial, cs, p.M, p.N, splits);
+        tma_splitk_reduce_kernel<<<stride_grid((long long)p.M * p.N), 256, 0, st>>>(p.partial, cs, p.M, p.N, splits, p.bias, p.act);
         count_launch();
         e = cudaGetLastError();
     }
@@ -451,9 +462,10 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
 // Dense: A operand shadow `sa`; a_mn = 0: sa is [M, K] (read along its rows); a_mn = 1: sa is [K, M].  Likewise B with N.
 template <class CS>
 int run_tma_gemm(const Shadow &sa, int a_mn, const Shadow &sb, int b_mn, const CS &cs, int M, int N, int K,
-                 bool allow_split, const char *name) {
+                 bool allow_split, const char *name, const float *bias = nullptr, int act = 0) {
     const int ns = precision_copies();
     TmaGemmParams p{};
+    p.bias = bias; p.act = act;
     p.M = M; p.N = N; p.K = K; p.a_mode = a_mn ? TMA_A_COLS : TMA_A_ROWS; p.b_mn = b_mn;
     p.bn = tma_pick_bn(N, ns, b_mn);
     TmaMaps maps;

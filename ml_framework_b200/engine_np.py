@@ -151,6 +151,42 @@ def conv2d_forward(X, W, sh, sw, ph, pw):
         return d.down(o, (N, F, OH, OW))
 
 
+def conv2d_bias_act(X, W, bias, sh, sw, ph, pw, act):
+    """act(conv2d(X, W) + bias[f]) in one call; bias may be None, act is a SEERA_ACT_* code."""
+    X, W = np.asarray(X, np.float32), np.asarray(W, np.float32)
+    N, C, H, Wi = X.shape
+    F, _, KH, KW = W.shape
+    OH, OW = (H + 2 * ph - KH) // sh + 1, (Wi + 2 * pw - KW) // sw + 1
+    with _Dev() as d:
+        o = d.new(N * F * OH * OW)
+        b = d.up(np.asarray(bias, np.float32).ravel()) if bias is not None else None
+        capi.check(d.L.seera_conv2d_bias_act_fwd(d.up(X), d.up(W), b, o, N, C, H, Wi, F, KH, KW, ph, pw, sh, sw, act))
+        return d.down(o, (N, F, OH, OW))
+
+
+def conv_transpose2d_bias_act(X, W, bias, sh, sw, ph, pw, act):
+    X, W = np.asarray(X, np.float32), np.asarray(W, np.float32)
+    N, Ci, H, Wi = X.shape
+    _, Co, KH, KW = W.shape
+    Ho, Wo = (H - 1) * sh - 2 * ph + KH, (Wi - 1) * sw - 2 * pw + KW
+    with _Dev() as d:
+        o = d.new(N * Co * Ho * Wo)
+        b = d.up(np.asarray(bias, np.float32).ravel()) if bias is not None else None
+        capi.check(d.L.seera_conv2DTranspose_bias_act_fwd(d.up(X), d.up(W), b, o, N, Ci, H, Wi, Co, KH, KW, sh, sw, ph, pw, act))
+        return d.down(o, (N, Co, Ho, Wo))
+
+
+def matmul_bias_act(A, B, bias, act):
+    A, B = np.asarray(A, np.float32), np.asarray(B, np.float32)
+    M, K = A.shape
+    N = B.shape[1]
+    with _Dev() as d:
+        o = d.new(M * N)
+        b = d.up(np.asarray(bias, np.float32).ravel()) if bias is not None else None
+        capi.check(d.L.seera_matmul_bias_act_fwd(d.up(A), d.up(B), b, o, M, N, K, act))
+        return d.down(o, (M, N))
+
+
 def conv2d_backward(dout, X, W, sh, sw, ph, pw):
     X, W = np.asarray(X, np.float32), np.asarray(W, np.float32)
     N, C, H, Wi = X.shape

@@ -245,14 +245,15 @@ class _ParamLayer(Layer):
             sc.cuda_elemadd(t.value.main_ptr, neg.main_ptr, t.value.main_ptr, t.value.size)
 
     # fused epilogue / prologue shared by Dense, Conv2D, ConvTranspose2D
-    def _finish_forward(self, x, z, channels, inner, contraction_backward):
-        """z (pre-bias contraction output, cuten) -> activation output Tensor with its backward closure."""
+    def _finish_forward(self, x, z, channels, inner, product, contraction_backward):
+        """product(bias_ptr, act_code) fills z with act(contraction + bias) in one call; this wraps z as the layer's
+        output Tensor and attaches the backward closure."""
         act = self.layeract
         W, b = self.weights, self.bais
         if act == "softmax":
             if len(z.shape) != 2:
                 raise ValueError("[Engine]: Softmax VJP requires at least 2D")
-            sc.bias_act_fwd(z.main_ptr, b.value.main_ptr, z.main_ptr, z.size, channels, inner, 0)
+            product(b.value.main_ptr, 0)
             logits = Tensor(z)
             y = _new(z.shape)
             sc.cuda_softmax_fwd(z.main_ptr, y.main_ptr, z.shape[0], z.shape[1])
@@ -268,7 +269,7 @@ class _ParamLayer(Layer):
             node, code = logits, 0
         else:
             code = _ACT[act]
-            sc.bias_act_fwd(z.main_ptr, b.value.main_ptr, z.main_ptr, z.size, channels, inner, code)
+            product(b.value.main_ptr, code)
             out = Tensor(z)
             node = out
         node._parents = (x, W, b)
@@ -312,14 +313,16 @@ class Dense(_ParamLayer):
             raise ValueError(f"[cuTen]: matmul: inner dimensions must agree, got {xv.shape} @ {W.shape}")
         M, K, N = xv.shape[0], self.in_units, self.out_units
         z = _new((M, N))
-        sc.cuda_matmul(xv.main_ptr, W.main_ptr, z.main_ptr, M, N, K, 1)
+
+        def product(bias, code):
+            sc.matmul_bias_act_fwd(xv.main_ptr, W.main_ptr, bias, z.main_ptr, M, N, K, code)
 
         def contraction_backward(dz, need_dx=not x.is_leaf):
             dw = self.weights._grad_target()
             dx = _new(xv.shape) if need_dx else None
             sc.cuda_matmul_bwd(xv.main_ptr, W.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr, M, N, K, 1)
             return dx, dw
-        self.outputs = self._finish_forward(x, z, N, 1, contraction_backward)
+        self.outputs = self._finish_forward(x, z, N, 1, product, contraction_backward)
         return self.outputs
 
     def __repr__(self):
@@ -351,7 +354,9 @@ class Conv2D(_ParamLayer):
         F, (KH, KW), (sh, sw), (ph, pw) = self.out_channels, self.kernel_size, self.stride, self.zero_padding
         OH, OW = (H + 2 * ph - KH) // sh + 1, (Wd + 2 * pw - KW) // sw + 1
         z = _new((N, F, OH, OW))
-        sc.cuda_conv2d_fwd(xv.main_ptr, W.main_ptr, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw)
+
+        def product(bias, code):
+            sc.conv2d_bias_act_fwd(xv.main_ptr, W.main_ptr, bias, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw, code)
 
         def contraction_backward(dz, need_dx=not x.is_leaf):
             dw = self.weights._grad_target()
@@ -359,7 +364,7 @@ class Conv2D(_ParamLayer):
             sc.cuda_conv2d_bwd(W.main_ptr, xv.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
                                N, C, H, Wd, F, KH, KW, sh, sw, ph, pw)
             return dx, dw
-        self.outputs = self._finish_forward(x, z, F, OH * OW, contraction_backward)
+        self.outputs = self._finish_forward(x, z, F, OH * OW, product, contraction_backward)
         return self.outputs
 
     def __repr__(self):
@@ -391,7 +396,9 @@ class ConvTranspose2D(_ParamLayer):
         Cout, (KH, KW), (sh, sw), (ph, pw) = self.out_channels, self.kernel_size, self.stride, self.zero_padding
         Ho, Wo = (H - 1) * sh - 2 * ph + KH, (Wd - 1) * sw - 2 * pw + KW
         z = _new((N, Cout, Ho, Wo))
-        sc.cuda_conv2DTranpose_fwd(xv.main_ptr, W.main_ptr, z.main_ptr, N, Cin, H, Wd, Cout, KH, KW, sh, sw, ph, pw)
+
+        def product(bias, code):
+            sc.conv2DTranspose_bias_act_fwd(xv.main_ptr, W.main_ptr, bias, z.main_ptr, N, Cin, H, Wd, Cout, KH, KW, sh, sw, ph, pw, code)
 
         def contraction_backward(dz, need_dx=not x.is_leaf):
             dw = self.weights._grad_target()
@@ -399,7 +406,7 @@ class ConvTranspose2D(_ParamLayer):
             sc.cuda_conv2DTranspose_bwd(W.main_ptr, xv.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
                                         N, Cin, H, Wd, Cout, KH, KW, sh, sw, ph, pw)
             return dx, dw
-        self.outputs = self._finish_forward(x, z, Cout, Ho * Wo, contraction_backward)
+        self.outputs = self._finish_forward(x, z, Cout, Ho * Wo, product, contraction_backward)
         return self.outputs
 
     def __repr__(self):

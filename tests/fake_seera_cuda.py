@@ -278,6 +278,23 @@ def bias_act_fwd(z, b, y, n, ch, inner, act):
     _view(y, n)[:] = _act((zz + bb).astype(np.float32), act).ravel()
 
 
+def matmul_bias_act_fwd(A, B, b, C, M, N, K, act):
+    cuda_matmul(A, B, C, M, N, K, 1)
+    bias_act_fwd(C, b, C, M * N, N, 1, act)
+
+
+def conv2d_bias_act_fwd(x, w, b, o, N, C, H, W, Fo, R, S, ph, pw, sh, sw, act):
+    cuda_conv2d_fwd(x, w, o, N, C, H, W, Fo, R, S, ph, pw, sh, sw)
+    OH, OW = (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1
+    bias_act_fwd(o, b, o, N * Fo * OH * OW, Fo, OH * OW, act)
+
+
+def conv2DTranspose_bias_act_fwd(x, w, b, o, N, Ci, H, W, Co, KH, KW, sh, sw, ph, pw, act):
+    cuda_conv2DTranpose_fwd(x, w, o, N, Ci, H, W, Co, KH, KW, sh, sw, ph, pw)
+    Ho, Wo = (H - 1) * sh - 2 * ph + KH, (W - 1) * sw - 2 * pw + KW
+    bias_act_fwd(o, b, o, N * Co * Ho * Wo, Co, Ho * Wo, act)
+
+
 def act_bias_bwd(dy, y, dz, db, n, ch, inner, act):
     _count("act_bias_bwd")
     g = _view(dy, n).reshape(-1, ch, inner)

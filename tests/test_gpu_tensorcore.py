@@ -88,6 +88,69 @@ def test_conv_transpose2d(E, mode, shape):
     assert rel_l2(dX, rX) < TOL[mode] and rel_l2(dW, rW) < TOL[mode]
 
 
+def _act_ref(z, act):
+    z = z.astype(np.float64)
+    return [z, np.maximum(z, 0), 1 / (1 + np.exp(-z)), np.tanh(z)][act]
+
+
+# Convolutions whose whole patch is at most 64 values run as direct fp32 kernels: patches of 9, 25, 27, 48 and 64
+# values, strides, padding, filter counts that are not multiples of 4 or 64, pixel counts that are not multiples
+# of the tile.
+SHORT = [(2, 1, 28, 28, 8, 3, 3, 1, 1, 1, 1), (3, 3, 32, 32, 64, 3, 3, 1, 1, 1, 1), (2, 1, 9, 11, 70, 5, 5, 2, 1, 2, 0),
+         (2, 3, 13, 9, 5, 4, 4, 2, 3, 1, 2), (5, 4, 7, 7, 130, 4, 4, 1, 1, 0, 0), (64, 3, 32, 32, 64, 3, 3, 1, 1, 1, 1),
+         (1, 2, 6, 6, 3, 1, 1, 1, 1, 0, 0)]
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3])
+@pytest.mark.parametrize("shape", SHORT)
+def test_short_patch_conv_forward_and_weight_gradient(E, mode, shape):
+    N, C, H, W, F, KH, KW, sh, sw, ph, pw = shape
+    rs = np.random.RandomState(sum(shape) + 7)
+    X = rs.standard_normal((N, C, H, W)).astype(np.float32)
+    Wt = rs.standard_normal((F, C, KH, KW)).astype(np.float32)
+    b = rs.standard_normal(F).astype(np.float32)
+    _prep(mode)
+    R = co.conv2d_forward(X, Wt, sh, sw, ph, pw)
+    assert rel_l2(E.conv2d_forward(X, Wt, sh, sw, ph, pw), R) < 2e-6            # exact fp32 in every mode
+    for act in (0, 1, 2, 3):
+        want = _act_ref(R + b.reshape(1, F, 1, 1), act)
+        assert rel_l2(E.conv2d_bias_act(X, Wt, b, sh, sw, ph, pw, act), want) < 2e-6
+    assert rel_l2(E.conv2d_bias_act(X, Wt, None, sh, sw, ph, pw, 1), np.maximum(R, 0)) < 2e-6
+    dY = rs.standard_normal(R.shape).astype(np.float32)
+    dX, dW = E.conv2d_backward(dY, X, Wt, sh, sw, ph, pw)
+    rX, rW = co.conv2d_backward(dY, X, Wt, sh, sw, ph, pw)
+    assert rel_l2(dW, rW) < 2e-6 and rel_l2(dX, rX) < {1: 1e-2, 2: 2e-5, 3: 2e-5}[mode]
+
+
+FUSED_CONV = [(2, 70, 9, 9, 20, 3, 3, 1, 1, 1, 1), (4, 64, 16, 16, 128, 3, 3, 2, 2, 1, 1), (2, 130, 6, 6, 300, 3, 3, 1, 1, 1, 1)]
+FUSED_CONVT = [(2, 64, 8, 8, 32, 4, 4, 2, 2, 1, 1), (3, 16, 7, 5, 20, 3, 3, 1, 1, 1, 1), (2, 8, 5, 5, 7, 2, 2, 3, 3, 0, 0)]
+
+
+@pytest.mark.parametrize("mode", [2, 3])
+def test_bias_and_activation_in_the_epilogue(E, mode):
+    """The fused forward entries against product + bias + activation of the oracle, all activation codes."""
+    rs = np.random.RandomState(mode)
+    _prep(mode)
+    for shape in FUSED_CONV:
+        N, C, H, W, F, KH, KW, sh, sw, ph, pw = shape
+        X, Wt, b = (rs.standard_normal(s).astype(np.float32) for s in ((N, C, H, W), (F, C, KH, KW), (F,)))
+        R = co.conv2d_forward(X, Wt, sh, sw, ph, pw) + b.reshape(1, F, 1, 1)
+        for act in (0, 1, 2, 3):
+            assert rel_l2(E.conv2d_bias_act(X, Wt, b, sh, sw, ph, pw, act), _act_ref(R, act)) < 3e-5
+    for shape in FUSED_CONVT:
+        N, Ci, H, W, Co, KH, KW, sh, sw, ph, pw = shape
+        X, Wt, b = (rs.standard_normal(s).astype(np.float32) for s in ((N, Ci, H, W), (Ci, Co, KH, KW), (Co,)))
+        R = co.conv_transpose2d_forward(X, Wt, sh, sw, ph, pw) + b.reshape(1, Co, 1, 1)
+        for act in (0, 1, 3):
+            assert rel_l2(E.conv_transpose2d_bias_act(X, Wt, b, sh, sw, ph, pw, act), _act_ref(R, act)) < 3e-5
+    for M, K, N in [(5, 7, 3), (300, 1024, 10), (64, 4096, 256), (257, 1000, 255)]:      # the last two also through split-K
+        A, B, b = (rs.standard_normal(s).astype(np.float32) for s in ((M, K), (K, N), (N,)))
+        A /= np.float32(np.sqrt(K))                                   # keeps sigmoid and tanh off their flat ends
+        R = A.astype(np.float64) @ B.astype(np.float64) + b
+        for act in (0, 1, 2, 3):
+            assert rel_l2(E.matmul_bias_act(A, B, b, act), _act_ref(R, act)) < 3e-5
+
+
 def test_c5_conv_backward_point_bf16(E):
     """One point of the Conv2D-backward sweep at reduced batch (C = K = 64, 56x56, 3x3 s1 p1), bf16 operands."""
     X, Wt, dY = wl.c5_conv_bwd(64, 56, n=4)
