@@ -168,11 +168,18 @@ def setup_data_parallel(model, world, local_rank):
     return dist, torch
 
 
+def _apply_options(sc, args):
+    for item in args.option:
+        name, _, value = item.partition("=")
+        sc.set_option(name, int(value))
+
+
 def run_gpu(args, work):
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     from ml_framework_b200 import seera_cuda as sc, seera as S, train
     sc.init(local)
+    _apply_options(sc, args)
     prec = tuple(int(v) for v in args.precision.split("/"))
     prec = prec if len(prec) == 2 else (prec[0], prec[0])
     tr = train.Trainer(work, seed=0, precision=prec)
@@ -334,6 +341,7 @@ def run_c5(args):
     from ml_framework_b200 import seera_cuda as sc
     from ml_framework_b200.cuTen import cuten
     sc.init(int(os.environ.get("LOCAL_RANK", "0")))
+    _apply_options(sc, args)
     mode = int(args.precision or "1")
     sc.set_precision(mode)
     peaks = _peaks()
@@ -391,6 +399,8 @@ def main():
     ap.add_argument("--precision", default=None,
                     help="0 fp32 CUDA cores | 1 bf16 | 2 bf16x3 | 3 bf16x6 | F/B per phase; default: 1 for c2 (a bf16 configuration), "
                          "3/2 for the fp32 configurations")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="engine option for seera_set_option (repeatable), e.g. tile_n_cap3=128")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a captured step")
     args = ap.parse_args()

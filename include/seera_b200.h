@@ -69,9 +69,12 @@ int         seera_profile_read(uint64_t *launches, double *ms, double *flops);
  *     TMA-fed kernels; the kernel that gathers in its producer warps runs mode 3 as mode 2 */
 int         seera_set_precision(int mode);
 int         seera_get_precision(void);
-/* Engine options by name.  "conv_tma" (default 1) does the same for the convolution family (TMA im2col); "dense_tma" (default 1): in precision modes 1/2 the Dense GEMMs convert their
- * operands to bf16 shadows once and feed the tensor cores by TMA; 0 selects the kernel that converts inside
- * its producer warps (the one the convolution family uses). */
+/* Engine options by name.
+ *   "dense_tma" (default 1): in precision modes 1-3 the Dense GEMMs convert their operands to bf16 shadows once
+ *       and feed the tensor cores by TMA; 0 selects the kernel that converts inside its producer warps.
+ *   "conv_tma" (default 1): the same choice for the convolution family (TMA im2col).
+ *   "tile_n_cap2" / "tile_n_cap3" (64, 128 or 256; defaults 128 / 128): widest accumulator tile used with two /
+ *       three bf16 copies per operand; wider tiles raise the arithmetic per byte loaded but leave fewer stages. */
 int         seera_set_option(const char *name, int value);
 /* Status word of the tensor-core kernels: 0 when every bounded wait inside them completed, otherwise
  * the code of the first wait that ran out (1 producer, 2 MMA issuer, 3 epilogue); reading clears it.

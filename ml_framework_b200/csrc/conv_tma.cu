@@ -454,6 +454,12 @@ int seera_tma_convT_bwd(const float *Wt, const float *X, const float *dY, float 
         return fail(SEERA_E_ARG, "cuda_conv2DTranspose_bwd: bad argument");
     if (!tma_conv_supported(NB, KH, KW, sh, sw, ph, pw))
         return seera_tc_convT_bwd(Wt, X, dY, dX, dW, NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw);
+    if (conv_first_applies(Cout, KH, KW)) {      // short patch on the output side (e.g. a one-channel image): direct fp32 kernels
+        int s = SEERA_OK;
+        if (dX) s = conv_first_fwd(dY, Wt, nullptr, dX, NB, Cout, Ho, Wo, Cin, KH, KW, ph, pw, sh, sw, SEERA_ACT_NONE, "cuda_conv2DTranspose_bwd(dX)");
+        if (!s && dW) s = conv_first_wgrad(dY, X, dW, NB, Cout, Ho, Wo, Cin, KH, KW, sh, sw, ph, pw, "cuda_conv2DTranspose_bwd(dW)");
+        return s;
+    }
     int ns = precision_copies();
     int taps = KH * KW;
     NhwcShadow dys, xs; Shadow wk;

@@ -123,6 +123,38 @@ __global__ void __launch_bounds__(256) unpool_bwd_kernel(const float *__restrict
     }
 }
 
+// Fast paths for tensors under 2^31 elements: 32-bit index arithmetic (the 64-bit divisions above cost more than the
+// memory traffic) and, when the output width is a multiple of 4, one 16-byte store per thread.
+template <bool V4>
+__global__ void __launch_bounds__(256) unpool_fwd32_kernel(const float *__restrict__ x, float *__restrict__ out, unsigned items,
+                                                           unsigned H, unsigned W, unsigned sh, unsigned sw) {
+    const unsigned Ho = H * sh, Wo = W * sw, Wq = V4 ? Wo / 4 : Wo;
+    for (unsigned q = blockIdx.x * blockDim.x + threadIdx.x; q < items; q += gridDim.x * blockDim.x) {
+        unsigned row = q / Wq, wq = q - row * Wq;
+        unsigned nc = row / Ho, h = row - nc * Ho;
+        const float *src = x + ((size_t)nc * H + h / sh) * W;
+        if (V4) {
+            unsigned w0 = wq * 4;
+            float4 v = make_float4(__ldg(src + w0 / sw), __ldg(src + (w0 + 1) / sw), __ldg(src + (w0 + 2) / sw), __ldg(src + (w0 + 3) / sw));
+            *reinterpret_cast<float4 *>(out + (size_t)q * 4) = v;
+        } else {
+            out[q] = __ldg(src + wq / sw);
+        }
+    }
+}
+__global__ void __launch_bounds__(256) unpool_bwd32_kernel(const float *__restrict__ dout, float *__restrict__ dx, unsigned total,
+                                                           unsigned H, unsigned W, unsigned sh, unsigned sw) {
+    const unsigned Wo = W * sw;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        unsigned row = i / W, w = i - row * W;             // row = nc * H + h
+        const float *src = dout + (size_t)row * sh * Wo + w * sw;
+        float s = 0.f;
+        for (unsigned a = 0; a < sh; a++)
+            for (unsigned b = 0; b < sw; b++) s += __ldg(src + (size_t)a * Wo + b);
+        dx[i] = s;
+    }
+}
+
 // ---- reductions over a tensor viewed as [outer, n, inner] ------------------------------------------------
 enum { R_SUM = 0, R_MEAN = 1, R_MAX = 2, R_MIN = 3 };
 
@@ -329,7 +361,14 @@ int seera_cuda_unpooling_fwd(const float *inp, float *out, int N, int C, int H, 
     SEERA_ENSURE();
     if (N < 1 || C < 1 || H < 1 || W < 1 || sh < 1 || sw < 1 || !inp || !out) return fail(SEERA_E_ARG, "cuda_unpooling_fwd: bad argument");
     long long total = (long long)N * C * H * sh * W * sw;
-    unpool_fwd_kernel<<<stride_grid(total), 256, 0, rt().stream>>>(inp, out, total, H, W, sh, sw);
+    if (total < (1LL << 31)) {
+        const bool v4 = (W * sw) % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        unsigned items = (unsigned)(v4 ? total / 4 : total);
+        if (v4) unpool_fwd32_kernel<true><<<stride_grid(items), 256, 0, rt().stream>>>(inp, out, items, H, W, sh, sw);
+        else unpool_fwd32_kernel<false><<<stride_grid(items), 256, 0, rt().stream>>>(inp, out, items, H, W, sh, sw);
+    } else {
+        unpool_fwd_kernel<<<stride_grid(total), 256, 0, rt().stream>>>(inp, out, total, H, W, sh, sw);
+    }
     SEERA_LAUNCH_CHECK("cuda_unpooling_fwd");
     return SEERA_OK;
 }
@@ -337,7 +376,8 @@ int seera_cuda_unpooling_bwd(const float *dout, float *dx, int N, int C, int H, 
     SEERA_ENSURE();
     if (N < 1 || C < 1 || H < 1 || W < 1 || sh < 1 || sw < 1 || !dout || !dx) return fail(SEERA_E_ARG, "cuda_unpooling_bwd: bad argument");
     long long total = (long long)N * C * H * W;
-    unpool_bwd_kernel<<<stride_grid(total), 256, 0, rt().stream>>>(dout, dx, total, H, W, sh, sw);
+    if (total * sh * sw < (1LL << 31)) unpool_bwd32_kernel<<<stride_grid(total), 256, 0, rt().stream>>>(dout, dx, (unsigned)total, H, W, sh, sw);
+    else unpool_bwd_kernel<<<stride_grid(total), 256, 0, rt().stream>>>(dout, dx, total, H, W, sh, sw);
     SEERA_LAUNCH_CHECK("cuda_unpooling_bwd");
     return SEERA_OK;
 }

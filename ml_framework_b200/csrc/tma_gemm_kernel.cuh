@@ -391,8 +391,10 @@ struct TmaMaps { CUtensorMap a[3], b[3]; };
 inline int tma_pick_bn(int N, int ns, int b_mn) {
     int bn = N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256));
     if (b_mn && bn < 64) bn = 64;
-    if (ns >= 2 && bn > 128) bn = 128;
-    if (ns >= 3 && bn > 64) bn = 64;        // three operand copies per stage: keep two stages in shared memory
+    if (ns == 2 && bn > rt().tile_n_cap2) bn = rt().tile_n_cap2;
+    if (ns >= 3 && bn > rt().tile_n_cap3) bn = rt().tile_n_cap3;
+    // at least two stages of ns * (128 + bn) * 128 bytes must fit beside the epilogue staging
+    while (bn > 32 && 2 * (size_t)ns * (TC_BM + bn) * 128 > 225 * 1024 - 4 * EPI_WARP_SMEM - 1024) bn >>= 1;
     return bn;
 }
 
