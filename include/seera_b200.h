@@ -211,6 +211,29 @@ int seera_conv2d_bias_act_fwd(const float *image, const float *kernel, const flo
                               int F, int R, int S, int pad_h, int pad_w, int stride_h, int stride_w, int act);
 int seera_conv2DTranspose_bias_act_fwd(const float *X, const float *W, const float *bias, float *out, int batch, int Cin, int Hin,
                                        int Win, int Cout, int KH, int KW, int strideh, int stridew, int padh, int padw, int act);
+/* Channels-last bf16 copies of one NCHW activation tensor, as the tensor-core convolutions read them.  A forward call
+ * can hand the copies of its input to the matching backward call instead of producing them twice.  Opaque; owned
+ * by the caller once returned; release with seera_shadow_free (stream-ordered, NULL allowed).
+ * No counterpart in the reference, whose convolutions re-run im2col in every call (engine_cuda/src/conv_fwd.cu,
+ * conv_bwd.cu). */
+typedef struct seera_shadow seera_shadow_t;
+void seera_shadow_free(seera_shadow_t *s);
+/* seera_conv2d_bias_act_fwd with kept copies: x_in (may be NULL) are copies of `image` from an earlier call;
+ * *x_keep (x_keep may be NULL) receives the copies this call produced, or NULL when it produced none (x_in was
+ * used, or the shape does not run on copies: exact-fp32 mode, short patches, unsupported geometry). */
+int seera_conv2d_bias_act_fwd_s(const float *image, const float *kernel, const float *bias, float *out, int batchN, int C, int H,
+                                int W, int F, int R, int S, int pad_h, int pad_w, int stride_h, int stride_w, int act,
+                                seera_shadow_t *x_in, seera_shadow_t **x_keep);
+/* Backward of y = act(conv2d(X, W) + bias) in one call (Conv2D backward: Seera_Engine.py:571-583 activation,
+ * :43-65 bias, :67-115 convolution; with gp also MaxPool2D backward, :117-131).  The gradient arrives either
+ * as g = dL/dy [N,F,OH,OW] or as gp = dL/d(maxpool2x2(y)) [N,F,OH/2,OW/2] with that pool's mask from
+ * cuda_maxpool_fwd (window 2x2, stride 2, no padding); exactly one of g / gp is non-NULL.  Produces dX (may be
+ * NULL), dW and dbias (may be NULL).  dz = dy * act'(y) goes straight into the bf16 copies the tensor-core
+ * kernels read and is never stored in fp32; shapes those kernels do not serve run as the separate entries.
+ * x_shadow: kept copies of X from the forward call, or NULL. */
+int seera_conv2d_act_bwd(const float *W, const float *X, const float *y, const float *g, const float *gp, const int *pool_mask,
+                         float *dX, float *dW, float *dbias, int batch, int C, int H, int W_in, int F, int R, int S,
+                         int strideh, int stridew, int padh, int padw, int act, seera_shadow_t *x_shadow);
 /* dz = dy * act'(y), with the derivative written in terms of the OUTPUT y (relu: y > 0; sigmoid:
  * y(1-y); tanh: 1-y^2), and dbias[c] = sum of dz over that channel.  Replaces cuda_elemmult with the
  * stored local gradient plus broadcast_mul_4d + three cuda_sum_fwd (Seera_Engine.py:571-583, :43-65). */

@@ -32,11 +32,32 @@ __device__ __forceinline__ float first_act(float z, int act) {
 }
 
 // Patch element table: for k = (c, r, s) the offset c*H*W + r*W + s and the window row / column, packed.
-__device__ __forceinline__ void fill_patch_table(int *koff, int *krs, const FirstGeom &g, int KP) {
+// krs[k] = -1 marks padding; -2 (only when ones_col is set) marks the column k == K whose patch value is the
+// constant 1, so that the weight-gradient GEMM also yields the per-filter sum of the output gradient.
+__device__ __forceinline__ void fill_patch_table(int *koff, int *krs, const FirstGeom &g, int KP, bool ones_col = false) {
     for (int k = threadIdx.x; k < KP; k += blockDim.x) {
         int c = k / (g.R * g.S), rs = k - c * g.R * g.S, r = rs / g.S, s = rs - r * g.S;
         koff[k] = c * g.H * g.W + r * g.W + s;
-        krs[k] = k < g.K ? ((r << 16) | s) : -1;
+        krs[k] = k < g.K ? ((r << 16) | s) : ((ones_col && k == g.K) ? -2 : -1);
+    }
+}
+
+// Where the weight gradient takes the output gradient dz[img][f][pixel] from: a stored fp32 tensor, or computed on the
+// fly as dy * act'(y) with dy either a full-resolution gradient g or the gradient gp of a 2x2 / stride-2 max-pool of
+// y routed through the pool's window-local argmax indices.
+struct DzSource {
+    const float *dz;            // stored gradient, or null
+    const float *g, *gp;        // exactly one of these when dz is null
+    const int *mask;
+    const float *y;
+    int act;
+};
+__device__ __forceinline__ float first_slope(float y, int act) {
+    switch (act) {
+        case SEERA_ACT_RELU: return y > 0.f ? 1.f : 0.f;
+        case SEERA_ACT_SIGMOID: return y * (1.f - y);
+        case SEERA_ACT_TANH: return 1.f - y * y;
+        default: return 1.f;
     }
 }
 
@@ -133,8 +154,8 @@ struct FirstWgradShape {
 };
 
 template <int KP>
-__global__ void __launch_bounds__(256) conv_first_wgrad_kernel(const float *__restrict__ X, const float *__restrict__ dY,
-                                                               float *__restrict__ partial, FirstGeom g, int ntiles) {
+__global__ void __launch_bounds__(256) conv_first_wgrad_kernel(const float *__restrict__ X, DzSource src,
+                                                               float *__restrict__ partial, FirstGeom g, int ntiles, int ones_col) {
     using Sh = FirstWgradShape<KP>;
     constexpr int FT = Sh::FT, PS = Sh::PS, KG = Sh::KG;
     __shared__ __align__(16) float Ps[FIRST_TP][KP + 4];      // + 4: staging stores of one warp spread over 8 banks
@@ -142,10 +163,11 @@ __global__ void __launch_bounds__(256) conv_first_wgrad_kernel(const float *__re
     __shared__ int koff[KP], krs[KP];
     const int f0 = blockIdx.y * FIRST_FC;
     const int fcount = min(FIRST_FC, g.F - f0);
-    fill_patch_table(koff, krs, g, KP);
+    fill_patch_table(koff, krs, g, KP, ones_col != 0);
     __syncthreads();
 
     const int P = g.OH * g.OW;
+    const int OWq = g.OW >> 1, Pq = (g.OH >> 1) * OWq;
     const long long pixels = (long long)g.NB * P;
     const int t = threadIdx.x;
     // compute role
@@ -173,13 +195,40 @@ __global__ void __launch_bounds__(256) conv_first_wgrad_kernel(const float *__re
             int rs = krs[k];
             int ih = ih0 + (rs >> 16), iw = iw0 + (rs & 0xffff);
             bool ok = live && rs >= 0 && (unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W;
-            Ps[sp][k] = ok ? __ldg(xb + koff[k]) : 0.f;
+            Ps[sp][k] = ok ? __ldg(xb + koff[k]) : ((rs == -2 && live) ? 1.f : 0.f);
         }
-        const float *db = dY + ((long long)img * g.F + f0) * P + rem;
+        const long long plane0 = (long long)img * g.F + f0;
+        if (src.dz) {
+            const float *db = src.dz + plane0 * P + rem;
 #pragma unroll
-        for (int i = 0; i < FIRST_FC / 4; i++) {
-            int f = sq * (FIRST_FC / 4) + i;
-            Ds[f][sp] = (live && f < fcount) ? __ldg(db + (long long)f * P) : 0.f;
+            for (int i = 0; i < FIRST_FC / 4; i++) {
+                int f = sq * (FIRST_FC / 4) + i;
+                Ds[f][sp] = (live && f < fcount) ? __ldg(db + (long long)f * P) : 0.f;
+            }
+        } else {
+            // all loads of a batch are issued before any is used: the tile is latency-bound otherwise
+            const int win = (oh >> 1) * OWq + (ow >> 1), loc = ((oh & 1) << 1) | (ow & 1);
+            constexpr int FB = 8;
+#pragma unroll
+            for (int i0 = 0; i0 < FIRST_FC / 4; i0 += FB) {
+                float dy[FB], yv[FB];
+                int mk[FB];
+#pragma unroll
+                for (int i = 0; i < FB; i++) {
+                    const int f = min(sq * (FIRST_FC / 4) + i0 + i, fcount - 1);
+                    const long long plane = plane0 + f;
+                    if (src.gp) { mk[i] = __ldg(src.mask + plane * Pq + win); dy[i] = __ldg(src.gp + plane * Pq + win); }
+                    else { mk[i] = loc; dy[i] = __ldg(src.g + plane * P + rem); }
+                    yv[i] = src.act == SEERA_ACT_NONE ? 1.f : __ldg(src.y + plane * P + rem);
+                }
+#pragma unroll
+                for (int i = 0; i < FB; i++) {
+                    const int f = sq * (FIRST_FC / 4) + i0 + i;
+                    float dz = mk[i] == loc ? dy[i] : 0.f;
+                    if (src.act != SEERA_ACT_NONE) dz *= first_slope(yv[i], src.act);
+                    Ds[f][sp] = (live && f < fcount) ? dz : 0.f;
+                }
+            }
         }
         __syncthreads();
 #pragma unroll 4
@@ -230,8 +279,8 @@ __global__ void __launch_bounds__(256) conv_first_wgrad_kernel(const float *__re
 
 // dW[f][k] = sum over blocks of partial[chunk][block][f - f0][k].  A block of 8 warps owns 32 outputs (one per lane);
 // warp w adds blocks w, w + 8, ... in order and the eight sums meet in shared memory in warp order: a fixed order.
-__global__ void __launch_bounds__(256) conv_first_wgrad_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dW, int F,
-                                                                      int K, int KP, int nblocks) {
+__global__ void __launch_bounds__(256) conv_first_wgrad_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dW,
+                                                                      float *__restrict__ dbias, int F, int K, int KP, int nblocks) {
     __shared__ float part[8][32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int e = blockIdx.x * 32 + lane;                  // index into the padded [F rounded to 64][KP] grid
@@ -247,11 +296,12 @@ __global__ void __launch_bounds__(256) conv_first_wgrad_reduce_kernel(const floa
     if (b < nblocks) s0 += p[(long long)b * (FIRST_FC * KP)];
     part[warp][lane] = s0 + s1;
     __syncthreads();
-    if (warp == 0 && f < F && k < K) {
+    if (warp == 0 && f < F && (k < K || (dbias && k == K))) {
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; w++) s += part[w][lane];
-        dW[(long long)f * K + k] = s;
+        if (k < K) dW[(long long)f * K + k] = s;
+        else dbias[f] = s;                       // the column of ones: sum of the output gradient per filter
     }
 }
 
@@ -286,14 +336,12 @@ int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y,
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 
-int conv_first_wgrad(const float *X, const float *dY, float *dW, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw,
-                     int ph, int pw, const char *name) {
-    FirstGeom g;
-    if (!first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
-    long long pixels = (long long)NB * g.OH * g.OW;
+static int first_wgrad_run(const float *X, const DzSource &src, float *dW, float *dbias, const FirstGeom &g, const char *name) {
+    long long pixels = (long long)g.NB * g.OH * g.OW;
     int ntiles = (int)((pixels + FIRST_TP - 1) / FIRST_TP);
-    int chunks = (F + FIRST_FC - 1) / FIRST_FC;
+    int chunks = (g.F + FIRST_FC - 1) / FIRST_FC;
     int KP = g.K <= 16 ? 16 : g.K <= 32 ? 32 : 64;
+    if (dbias && g.K >= KP) return fail(SEERA_E_LIMIT, "%s: no spare patch column for the bias gradient", name);
     int nblocks = rt().sm_count * 4 / chunks;
     if (nblocks < 1) nblocks = 1;
     if (nblocks > ntiles) nblocks = ntiles;
@@ -301,20 +349,45 @@ int conv_first_wgrad(const float *X, const float *dY, float *dW, int NB, int C, 
     if (!partial) return SEERA_E_OOM;
     cudaStream_t st = rt().stream;
     dim3 grid((unsigned)nblocks, (unsigned)chunks);
+    const int ones = dbias ? 1 : 0;
     profile_begin();
-    if (KP == 16) conv_first_wgrad_kernel<16><<<grid, 256, 0, st>>>(X, dY, partial, g, ntiles);
-    else if (KP == 32) conv_first_wgrad_kernel<32><<<grid, 256, 0, st>>>(X, dY, partial, g, ntiles);
-    else conv_first_wgrad_kernel<64><<<grid, 256, 0, st>>>(X, dY, partial, g, ntiles);
+    if (KP == 16) conv_first_wgrad_kernel<16><<<grid, 256, 0, st>>>(X, src, partial, g, ntiles, ones);
+    else if (KP == 32) conv_first_wgrad_kernel<32><<<grid, 256, 0, st>>>(X, src, partial, g, ntiles, ones);
+    else conv_first_wgrad_kernel<64><<<grid, 256, 0, st>>>(X, src, partial, g, ntiles, ones);
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) {
-        conv_first_wgrad_reduce_kernel<<<chunks * FIRST_FC * KP / 32, 256, 0, st>>>(partial, dW, F, g.K, KP, nblocks);
+        conv_first_wgrad_reduce_kernel<<<chunks * FIRST_FC * KP / 32, 256, 0, st>>>(partial, dW, dbias, g.F, g.K, KP, nblocks);
         count_launch();
         e = cudaGetLastError();
     }
-    profile_end(2.0 * pixels * (double)F * g.K);
+    profile_end(2.0 * pixels * (double)g.F * g.K);
     scratch_free(partial);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
+}
+
+int conv_first_wgrad(const float *X, const float *dY, float *dW, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw,
+                     int ph, int pw, const char *name) {
+    FirstGeom g;
+    if (!first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
+    return first_wgrad_run(X, DzSource{dY, nullptr, nullptr, nullptr, nullptr, SEERA_ACT_NONE}, dW, nullptr, g, name);
+}
+
+// True when conv_first_act_wgrad can also produce the bias gradient (a spare column in the padded patch).
+bool conv_first_fuses_bias(int C, int R, int S) {
+    int K = C * R * S;
+    return K <= 64 && K != 16 && K != 32 && K != 64;
+}
+
+// dW and dbias of y = act(conv(X, W) + b) from the gradient of y (g) or of its 2x2 / stride-2 max-pool (gp with the
+// pool's argmax indices): dz = dy * act'(y) is formed while the tile is staged and never stored.
+int conv_first_act_wgrad(const float *X, const float *y, const float *g, const float *gp, const int *mask, float *dW, float *dbias,
+                         int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw, int act, const char *name) {
+    FirstGeom geo;
+    if (!first_geom(geo, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
+    if ((g == nullptr) == (gp == nullptr) || (gp && (!mask || (geo.OH & 1) || (geo.OW & 1))) || (act != SEERA_ACT_NONE && !y))
+        return fail(SEERA_E_ARG, "%s: bad argument", name);
+    return first_wgrad_run(X, DzSource{nullptr, g, gp, mask, y, act}, dW, dbias, geo, name);
 }
 
 }  // namespace seera

@@ -331,6 +331,93 @@ static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, 
     return SEERA_OK;
 }
 
+// ---- activation backward written straight into channels-last shadows ------------------------------------------
+// dz = dy * act'(y) for a layer output y[NB, C, H, W]; dy is either the full-resolution gradient g or, when gp is
+// given, the gradient gp[NB, C, H/2, W/2] of a 2x2 / stride-2 max-pool of y routed through the pool's window-local
+// argmax indices (the pool backward folded in).  The fp32 dz never reaches HBM: each 64-channel x 32-pixel tile is
+// transposed in shared memory and stored as bf16 copies [NB, H*W, Cp], which is what the convolution backward
+// reads.  Per-channel sums of dz (the bias gradient) are accumulated per thread in a fixed order, reduced by warp
+// shuffles and written as one partial row per block.
+__device__ __forceinline__ float slope_from_output(float y, int act) {
+    switch (act) {
+        case SEERA_ACT_RELU: return y > 0.f ? 1.f : 0.f;
+        case SEERA_ACT_SIGMOID: return y * (1.f - y);
+        case SEERA_ACT_TANH: return 1.f - y * y;
+        default: return 1.f;
+    }
+}
+template <int NS>
+__global__ void __launch_bounds__(256) dz_shadow_kernel(const float *__restrict__ g, const float *__restrict__ gp, const int *__restrict__ mask,
+                                                        const float *__restrict__ y, int C, int H, int W, int Cp, int items, int ptiles,
+                                                        int act, __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
+                                                        __nv_bfloat16 *__restrict__ d2, float *__restrict__ partial) {
+    // warp = group of 8 consecutive channels, lane = pixel: every load is one 128-byte line of a channel plane and each
+    // thread ends up with the 8 channels of its pixel, i.e. one 16-byte chunk of the channels-last row: no transpose.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cb = blockIdx.y * 64 + warp * 8;
+    const int P = H * W, Wq = W >> 1, Pq = (H >> 1) * Wq;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+    if (cb < Cp) {
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const int img = item / ptiles, p = (item - img * ptiles) * 32 + lane;
+            if (p >= P) continue;
+            float dy[8], yv[8];
+            if (gp) {
+                const int h = p / W, w = p - h * W;
+                const int win = (h >> 1) * Wq + (w >> 1), loc = ((h & 1) << 1) | (w & 1);
+                int mk[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const long long q = ((long long)img * C + min(cb + i, C - 1)) * Pq + win;
+                    mk[i] = __ldg(mask + q);
+                    dy[i] = __ldg(gp + q);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) dy[i] = mk[i] == loc ? dy[i] : 0.f;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) dy[i] = __ldg(g + ((long long)img * C + min(cb + i, C - 1)) * P + p);
+            }
+            if (act != SEERA_ACT_NONE) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) yv[i] = __ldg(y + ((long long)img * C + min(cb + i, C - 1)) * P + p);
+#pragma unroll
+                for (int i = 0; i < 8; i++) dy[i] *= slope_from_output(yv[i], act);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (cb + i >= C) dy[i] = 0.f;          // padding channels of the last group
+                acc[i] += dy[i];
+            }
+            const long long o = ((long long)img * P + p) * Cp + cb;
+            *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(dy);
+            if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(dy);
+            if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(dy);
+        }
+    }
+    if (partial) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float t = acc[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (lane == 0 && cb + i < C) partial[(long long)blockIdx.x * C + cb + i] = t;
+        }
+    }
+}
+// out[c] = sum over splits of partial[s][c]: one warp per channel, lanes stride over the splits, then a shuffle tree.
+__global__ void __launch_bounds__(256) dz_bias_sum_kernel(const float *__restrict__ partial, float *__restrict__ out, int channels, int splits) {
+    const int lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (c >= channels) return;
+    float t = 0.f;
+    for (int s = lane; s < splits; s += 32) t += partial[(long long)s * channels + c];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) out[c] = t;
+}
+
 static bool conv_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     return NB >= 1 && C >= 1 && H >= 1 && W >= 1 && F >= 1 && R >= 1 && S >= 1 && sh >= 1 && sw >= 1 && ph >= 0 && pw >= 0 &&
            (long long)NB * (C > F ? C : F) * H * W * (long long)(sh * sw) < (1LL << 31);
@@ -339,6 +426,66 @@ static bool conv_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, in
 static bool tma_conv_supported(int NB, int R, int S, int sh, int sw, int ph, int pw) {
     return sh <= 8 && sw <= 8 && ph <= 127 && pw <= 127 && R - 1 - ph <= 127 && S - 1 - pw <= 127 && ph <= R - 1 && pw <= S - 1 &&
            NB <= 65535;
+}
+
+}  // namespace seera
+
+// Channels-last bf16 copies of one NCHW tensor, handed across calls (forward -> backward, activation backward ->
+// convolution backward) so that they are produced once.
+struct seera_shadow {
+    seera::NhwcShadow s;
+    int ns;
+};
+
+namespace seera {
+
+static const NhwcShadow *usable(const seera_shadow *h, int ns, int NB, int C, int H, int W) {
+    if (!h || h->ns < ns || h->s.NB != NB || h->s.C != C || h->s.H != H || h->s.W != W) return nullptr;
+    return &h->s;
+}
+
+// Convolution backward; xk / dyk are optional kept shadows of X / dY (dY itself may then be null unless the short-patch
+// weight gradient or a fallback needs the fp32 tensor).
+static int tma_conv2d_bwd_kept(const float *Wt, const float *X, const float *dY, float *dX, float *dW, int NB, int C, int H, int W,
+                               int F, int R, int S, int sh, int sw, int ph, int pw, const seera_shadow *xk, const seera_shadow *dyk) {
+    SEERA_ENSURE();
+    if (!conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) || !X || !Wt || (!dY && !dyk)) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: bad argument");
+    int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
+    if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: kernel larger than padded input");
+    const bool first = conv_first_applies(C, R, S);
+    const bool phases = !(sh == 1 && sw == 1) && phases_supported(H, W, OH, OW, R, S, sh, sw, ph, pw);
+    const bool need_fp32_dy = !tma_conv_supported(NB, R, S, sh, sw, ph, pw) || (dW && first) || (dX && !(sh == 1 && sw == 1) && !phases);
+    if (need_fp32_dy && !dY) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: this shape needs the fp32 output gradient");
+    if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return seera_tc_conv2d_bwd(Wt, X, dY, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw);
+    int ns = precision_copies();
+    NhwcShadow dys_local, xs_local; Shadow wd;
+    const NhwcShadow *dys = usable(dyk, ns, NB, F, OH, OW), *xs = usable(xk, ns, NB, C, H, W);
+    int s = SEERA_OK;
+    if (!dys && (dX || (dW && !first))) {
+        if (!dY) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: kept gradient copies do not fit this call and no fp32 gradient was given");
+        s = make_nhwc(dY, NB, F, OH, OW, ns, dys_local);
+        dys = &dys_local;
+    }
+    if (!s && dX) {
+        if (sh == 1 && sw == 1) {     // dX = forward convolution of dY with flipped taps and swapped channel roles, pad' = K-1-pad
+            s = make_weight_shadow(Wt, C, F, R * S, R * S, (long long)C * R * S, 1, ns, wd);
+            if (!s) s = tma_fprop(*dys, wd, dX, C, R, S, 1, 1, R - 1 - ph, S - 1 - pw, H, W, ns, "cuda_conv2d_bwd(dX)");
+        } else if (phases) {
+            s = tma_dgrad_phases(*dys, Wt, R * S, (long long)C * R * S, dX, C, H, W, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dX)");
+        } else {
+            s = seera_tc_conv2d_bwd(Wt, X, dY, dX, nullptr, NB, C, H, W, F, R, S, sh, sw, ph, pw);
+        }
+    }
+    if (!s && dW) {
+        if (first) {                  // short patch: direct fp32 kernel on the NCHW tensors
+            s = conv_first_wgrad(X, dY, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw, "cuda_conv2d_bwd(dW)");
+        } else {
+            if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, xs_local); xs = &xs_local; }
+            if (!s) s = tma_wgrad(*xs, *dys, dW, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dW)");
+        }
+    }
+    free_nhwc(dys_local); free_nhwc(xs_local); free_shadow(wd);
+    return s;
 }
 
 }  // namespace seera
@@ -377,35 +524,113 @@ int seera_tma_conv2d_bias_act_fwd(const float *X, const float *Wt, const float *
 
 int seera_tma_conv2d_bwd(const float *Wt, const float *X, const float *dY, float *dX, float *dW, int NB, int C, int H, int W,
                          int F, int R, int S, int sh, int sw, int ph, int pw) {
+    return tma_conv2d_bwd_kept(Wt, X, dY, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw, nullptr, nullptr);
+}
+
+// ---- entries that hand channels-last copies from one call to the next ---------------------------------------------
+static bool keeps_shadows(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
+    return rt().precision && rt().conv_tma && conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) && tma_conv_supported(NB, R, S, sh, sw, ph, pw) &&
+           !conv_first_applies(C, R, S);
+}
+
+void seera_shadow_free(seera_shadow_t *h) {
+    if (!h) return;
+    free_nhwc(h->s);
+    delete h;
+}
+
+int seera_conv2d_bias_act_fwd_s(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F,
+                                int R, int S, int ph, int pw, int sh, int sw, int act, seera_shadow_t *x_in, seera_shadow_t **x_keep) {
     SEERA_ENSURE();
-    if (!conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) || !X || !Wt || !dY) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: bad argument");
+    if (x_keep) *x_keep = nullptr;
+    if (!keeps_shadows(NB, C, H, W, F, R, S, sh, sw, ph, pw))
+        return seera_conv2d_bias_act_fwd(X, Wt, bias, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw, act);
+    if (!X || !Wt || !Y) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: bad argument");
     int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
-    if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: kernel larger than padded input");
-    if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return seera_tc_conv2d_bwd(Wt, X, dY, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw);
+    if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: kernel larger than padded input");
     int ns = precision_copies();
-    NhwcShadow dys, xs; Shadow wd;
-    const bool first = conv_first_applies(C, R, S);
+    NhwcShadow local; Shadow wk;
+    const NhwcShadow *xs = usable(x_in, ns, NB, C, H, W);
     int s = SEERA_OK;
-    if (dX || (dW && !first)) s = make_nhwc(dY, NB, F, OH, OW, ns, dys);
-    if (!s && dX) {
-        if (sh == 1 && sw == 1) {     // dX = forward convolution of dY with flipped taps and swapped channel roles, pad' = K-1-pad
-            s = make_weight_shadow(Wt, C, F, R * S, R * S, (long long)C * R * S, 1, ns, wd);
-            if (!s) s = tma_fprop(dys, wd, dX, C, R, S, 1, 1, R - 1 - ph, S - 1 - pw, H, W, ns, "cuda_conv2d_bwd(dX)");
-        } else if (phases_supported(H, W, OH, OW, R, S, sh, sw, ph, pw)) {
-            s = tma_dgrad_phases(dys, Wt, R * S, (long long)C * R * S, dX, C, H, W, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dX)");
-        } else {
-            s = seera_tc_conv2d_bwd(Wt, X, dY, dX, nullptr, NB, C, H, W, F, R, S, sh, sw, ph, pw);
-        }
+    if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, local); xs = &local; }
+    if (!s) s = make_weight_shadow(Wt, F, C, R * S, (long long)C * R * S, R * S, 0, ns, wk);
+    if (!s) s = tma_fprop(*xs, wk, Y, F, R, S, sh, sw, ph, pw, OH, OW, ns, "cuda_conv2d_fwd", bias, act);
+    free_shadow(wk);
+    if (!s && x_keep && xs == &local) {
+        *x_keep = new seera_shadow{local, ns};          // ownership of the device copies moves to the handle
+    } else {
+        free_nhwc(local);
     }
-    if (!s && dW) {
-        if (first) {                  // short patch: direct fp32 kernel on the NCHW tensors
-            s = conv_first_wgrad(X, dY, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw, "cuda_conv2d_bwd(dW)");
-        } else {
-            s = make_nhwc(X, NB, C, H, W, ns, xs);
-            if (!s) s = tma_wgrad(xs, dys, dW, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dW)");
-        }
+    return s;
+}
+
+// dz = dy * act'(y) as channels-last copies plus dbias; dy = g, or gp through a 2x2 / stride-2 max-pool mask.
+static int make_dz_shadow(const float *g, const float *gp, const int *mask, const float *y, float *dbias, int NB, int C, int H, int W,
+                          int act, int ns, NhwcShadow &out) {
+    out.NB = NB; out.H = H; out.W = W; out.C = C; out.Cp = (C + 7) / 8 * 8;
+    size_t bytes = (size_t)NB * H * W * out.Cp * 2;
+    for (int i = 0; i < ns; i++) { out.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!out.p[i]) return SEERA_E_OOM; }
+    const int P = H * W, ptiles = (P + 31) / 32, cchunks = (out.Cp + 63) / 64;
+    const long long items = (long long)NB * ptiles;
+    int splits = rt().sm_count * 8 / cchunks;
+    if (splits < 1) splits = 1;
+    if (splits > items) splits = (int)items;
+    if (items > 0x7fffffff || cchunks > 65535) return fail(SEERA_E_LIMIT, "activation backward: tensor too large");
+    float *partial = nullptr;
+    if (dbias) { partial = (float *)scratch_alloc((size_t)splits * C * sizeof(float)); if (!partial) return SEERA_E_OOM; }
+    dim3 grid((unsigned)splits, (unsigned)cchunks);
+    cudaStream_t st = rt().stream;
+    if (ns == 1) dz_shadow_kernel<1><<<grid, 256, 0, st>>>(g, gp, mask, y, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+    else if (ns == 2) dz_shadow_kernel<2><<<grid, 256, 0, st>>>(g, gp, mask, y, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+    else dz_shadow_kernel<3><<<grid, 256, 0, st>>>(g, gp, mask, y, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && dbias) {
+        dz_bias_sum_kernel<<<(C + 7) / 8, 256, 0, st>>>(partial, dbias, C, splits);
+        count_launch();
+        e = cudaGetLastError();
     }
-    free_nhwc(dys); free_nhwc(xs); free_shadow(wd);
+    if (partial) scratch_free(partial);
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, "activation backward (channels-last)");
+}
+
+int seera_conv2d_act_bwd(const float *Wt, const float *X, const float *y, const float *g, const float *gp, const int *pool_mask,
+                         float *dX, float *dW, float *dbias, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw,
+                         int ph, int pw, int act, seera_shadow_t *x_shadow) {
+    SEERA_ENSURE();
+    if (!conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) || !X || !Wt || (g == nullptr) == (gp == nullptr) || (gp && !pool_mask) ||
+        (act != SEERA_ACT_NONE && !y))
+        return fail(SEERA_E_ARG, "conv2d_act_bwd: bad argument");
+    int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
+    if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "conv2d_act_bwd: kernel larger than padded input");
+    if (gp && ((OH & 1) || (OW & 1))) return fail(SEERA_E_ARG, "conv2d_act_bwd: pooled gradient needs even output height and width");
+    const long long out_elems = (long long)NB * F * OH * OW;
+    if (keeps_shadows(NB, C, H, W, F, R, S, sh, sw, ph, pw) &&
+        (sh == 1 && sw == 1 ? true : phases_supported(H, W, OH, OW, R, S, sh, sw, ph, pw) || !dX)) {
+        seera_shadow dz{NhwcShadow{}, precision_copies()};
+        int s = make_dz_shadow(g, gp, pool_mask, y, dbias, NB, F, OH, OW, act, dz.ns, dz.s);
+        if (!s) s = tma_conv2d_bwd_kept(Wt, X, nullptr, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw, x_shadow, &dz);
+        free_nhwc(dz.s);
+        return s;
+    }
+    if (rt().precision && rt().conv_tma && conv_first_applies(C, R, S) && !dX && dW && (!dbias || conv_first_fuses_bias(C, R, S)))
+        return conv_first_act_wgrad(X, y, g, gp, pool_mask, dW, dbias, NB, C, H, W, F, R, S, sh, sw, ph, pw, act, "conv2d_act_bwd");
+    // composition of the separate entries
+    float *dy_full = nullptr, *dz = nullptr;
+    int s = SEERA_OK;
+    if (gp) {
+        dy_full = (float *)scratch_alloc((size_t)out_elems * sizeof(float));
+        if (!dy_full) return SEERA_E_OOM;
+        s = seera_cuda_maxpool_bwd(gp, pool_mask, dy_full, NB, F, OH, OW, 2, 2, 0, 0, 2, 2);
+    }
+    if (!s) {
+        dz = (float *)scratch_alloc((size_t)out_elems * sizeof(float));
+        if (!dz) s = SEERA_E_OOM;
+    }
+    if (!s) s = seera_act_bias_bwd(gp ? dy_full : g, y, dz, dbias, (int)out_elems, F, OH * OW, act);
+    if (!s) s = seera_cuda_conv2d_bwd(Wt, X, dz, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw);
+    if (dy_full) scratch_free(dy_full);
+    if (dz) scratch_free(dz);
     return s;
 }
 

@@ -179,6 +179,17 @@ PYBIND11_MODULE(seera_cuda, m) {
                                              int sh, int sw, int ph, int pw, int act) {
         ck(seera_conv2DTranspose_bias_act_fwd(P<const F>(x), P<const F>(w), P<const F>(b), P<F>(o), N, Ci, H, W, Co, KH, KW, sh, sw, ph,
                                               pw, act)); });
+    m.def("conv2d_bias_act_fwd_s", [](uptr x, uptr w, uptr b, uptr o, int N, int C, int H, int W, int Fo, int R, int S, int ph, int pw,
+                                      int sh, int sw, int act, uptr x_in) {
+        seera_shadow_t *keep = nullptr;
+        ck(seera_conv2d_bias_act_fwd_s(P<const F>(x), P<const F>(w), P<const F>(b), P<F>(o), N, C, H, W, Fo, R, S, ph, pw, sh, sw, act,
+                                       P<seera_shadow_t>(x_in), &keep));
+        return reinterpret_cast<uptr>(keep); });
+    m.def("shadow_free", [](uptr h) { seera_shadow_free(P<seera_shadow_t>(h)); });
+    m.def("conv2d_act_bwd", [](uptr w, uptr x, uptr y, uptr g, uptr gp, uptr mask, uptr dx, uptr dw, uptr db, int N, int C, int H, int W,
+                               int Fo, int R, int S, int sh, int sw, int ph, int pw, int act, uptr x_shadow) {
+        ck(seera_conv2d_act_bwd(P<const F>(w), P<const F>(x), P<const F>(y), P<const F>(g), P<const F>(gp), P<const int>(mask), P<F>(dx),
+                                P<F>(dw), P<F>(db), N, C, H, W, Fo, R, S, sh, sw, ph, pw, act, P<seera_shadow_t>(x_shadow))); });
     m.def("act_bias_bwd", [](uptr dy, uptr y, uptr dz, uptr db, int n, int ch, int inner, int act) {
         ck(seera_act_bias_bwd(P<const F>(dy), P<const F>(y), P<F>(dz), P<F>(db), n, ch, inner, act)); });
     m.def("softmax_cce_fwd_bwd", [](uptr z, uptr y, uptr p, uptr rows, uptr loss, uptr dz, int N, int C, float eps, float inv) {

@@ -164,6 +164,35 @@ def conv2d_bias_act(X, W, bias, sh, sw, ph, pw, act):
         return d.down(o, (N, F, OH, OW))
 
 
+def conv2d_layer_roundtrip(X, W, bias, sh, sw, ph, pw, act, g=None, gp=None, need_dx=True, keep=True):
+    """Forward y = act(conv2d(X, W) + bias) with the input's copies kept, then seera_conv2d_act_bwd from g (gradient of
+    y) or gp (gradient of maxpool2x2(y); the pool runs here to get its mask).  Returns y, pooled, dX, dW, dbias."""
+    X, W = np.asarray(X, np.float32), np.asarray(W, np.float32)
+    N, C, H, Wi = X.shape
+    F, _, KH, KW = W.shape
+    OH, OW = (H + 2 * ph - KH) // sh + 1, (Wi + 2 * pw - KW) // sw + 1
+    with _Dev() as d:
+        L = d.L
+        xd, wd, bd = d.up(X), d.up(W), d.up(np.asarray(bias, np.float32).ravel())
+        y = d.new(N * F * OH * OW)
+        kept = ctypes.c_void_p()
+        capi.check(L.seera_conv2d_bias_act_fwd_s(xd, wd, bd, y, N, C, H, Wi, F, KH, KW, ph, pw, sh, sw, act, None,
+                                                 ctypes.byref(kept) if keep else None))
+        pooled = mask = None
+        if gp is not None:
+            pooled, mask = d.new(N * F * (OH // 2) * (OW // 2)), d.new(N * F * OH * OW)
+            capi.check(L.seera_cuda_maxpool_fwd(y, pooled, mask, N, F, OH, OW, 2, 2, 0, 0, 2, 2))
+        dx = d.new(X.size) if need_dx else None
+        dw, db = d.new(W.size), d.new(F)
+        try:
+            capi.check(L.seera_conv2d_act_bwd(wd, xd, y, d.up(g) if g is not None else None, d.up(gp) if gp is not None else None,
+                                              mask, dx, dw, db, N, C, H, Wi, F, KH, KW, sh, sw, ph, pw, act, kept))
+        finally:
+            L.seera_shadow_free(kept)
+        return (d.down(y, (N, F, OH, OW)), d.down(pooled, (N, F, OH // 2, OW // 2)) if gp is not None else None,
+                d.down(dx, X.shape) if need_dx else None, d.down(dw, W.shape), d.down(db, (F,)))
+
+
 def conv_transpose2d_bias_act(X, W, bias, sh, sw, ph, pw, act):
     X, W = np.asarray(X, np.float32), np.asarray(W, np.float32)
     N, Ci, H, Wi = X.shape

@@ -87,10 +87,15 @@ class Tensor:
         return _new(self.value.shape)
 
     def _accumulate(self, g):
-        """Add a gradient contribution (a cuten of this tensor's shape)."""
+        """Add a gradient contribution: a cuten of this tensor's shape, or a _PooledGrad (the gradient of a 2x2 max-pool
+        of this tensor, still in pooled form) when it is the only contribution."""
         if self.grad is None:
             self.grad = g
         else:
+            if isinstance(self.grad, _PooledGrad):
+                self.grad = self.grad.materialize()
+            if isinstance(g, _PooledGrad):
+                g = g.materialize()
             out = _new(self.value.shape)
             sc.cuda_elemadd(self.grad.main_ptr, g.main_ptr, out.main_ptr, self.value.size)
             self.grad = out
@@ -127,6 +132,37 @@ class Tensor:
 tensor = Tensor
 
 
+class _PooledGrad:
+    """Gradient of a 2x2 / stride-2 max-pool output, kept in pooled form with the pool's argmax mask.  A consumer that
+    can route it itself (Conv2D backward: one kernel forms dz from it) takes it as is; anything else materialises the
+    full-resolution gradient with cuda_maxpool_bwd."""
+    __slots__ = ("gp", "mask", "shape")
+
+    def __init__(self, gp, mask, shape):
+        self.gp, self.mask, self.shape = gp, mask, tuple(shape)
+
+    def materialize(self):
+        N, C, H, W = self.shape
+        dx = _new(self.shape)
+        sc.cuda_maxpool_bwd(self.gp.main_ptr, self.mask.main_ptr, dx.main_ptr, N, C, H, W, 2, 2, 0, 0, 2, 2)
+        return dx
+
+
+class _KeptCopies:
+    """Owner of the channels-last copies a forward call kept for its backward call (0: none kept)."""
+    __slots__ = ("h",)
+
+    def __init__(self):
+        self.h = 0
+
+    def release(self):
+        if self.h:
+            sc.shadow_free(self.h)
+            self.h = 0
+
+    __del__ = release
+
+
 class autograd4nn:
     """Reverse pass from a scalar loss: `autograd4nn(loss)` (same call shape as Seera_Engine.py:24-26)."""
 
@@ -154,6 +190,8 @@ class autograd4nn:
         self.hook.grad = cuten.ones_like(self.hook.value)
         for t in reversed(order):
             if t._backward is not None and t.grad is not None:
+                if isinstance(t.grad, _PooledGrad) and not getattr(t, "_takes_pooled", False):
+                    t.grad = t.grad.materialize()
                 t._backward(t.grad)
 
 
@@ -245,7 +283,7 @@ class _ParamLayer(Layer):
             sc.cuda_elemadd(t.value.main_ptr, neg.main_ptr, t.value.main_ptr, t.value.size)
 
     # fused epilogue / prologue shared by Dense, Conv2D, ConvTranspose2D
-    def _finish_forward(self, x, z, channels, inner, product, contraction_backward):
+    def _finish_forward(self, x, z, channels, inner, product, contraction_backward, fused_backward=None):
         """product(bias_ptr, act_code) fills z with act(contraction + bias) in one call; this wraps z as the layer's
         output Tensor and attaches the backward closure."""
         act = self.layeract
@@ -274,8 +312,20 @@ class _ParamLayer(Layer):
             node = out
         node._parents = (x, W, b)
 
+        node._takes_pooled = fused_backward is not None
+
         def layer_backward(g, y=node.value, code=code):
             db = b._grad_target()
+            if fused_backward is not None:          # activation, bias and contraction gradients in one call
+                dx, dw = fused_backward(g, y, code, db)
+                b._accumulate(db)
+                W._accumulate(dw)
+                hook = getattr(getattr(self, "_model", None), "_on_grad_ready", None)
+                if hook is not None and W.grad is W._grad_slot and b.grad is b._grad_slot:
+                    hook(W)
+                if dx is not None:
+                    x._accumulate(dx)
+                return
             if code == 0:
                 dz = g
                 sc.act_bias_bwd(g.main_ptr, 0, g.main_ptr, db.main_ptr, y.size, channels, inner, 0)
@@ -354,9 +404,22 @@ class Conv2D(_ParamLayer):
         F, (KH, KW), (sh, sw), (ph, pw) = self.out_channels, self.kernel_size, self.stride, self.zero_padding
         OH, OW = (H + 2 * ph - KH) // sh + 1, (Wd + 2 * pw - KW) // sw + 1
         z = _new((N, F, OH, OW))
+        kept = _KeptCopies()
 
         def product(bias, code):
-            sc.conv2d_bias_act_fwd(xv.main_ptr, W.main_ptr, bias, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw, code)
+            kept.h = sc.conv2d_bias_act_fwd_s(xv.main_ptr, W.main_ptr, bias, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw, code, 0)
+
+        def fused_backward(g, y, code, db, need_dx=not x.is_leaf):
+            dw = self.weights._grad_target()
+            dx = _new(xv.shape) if need_dx else None
+            if isinstance(g, _PooledGrad):
+                gptr, gpptr, mptr = 0, g.gp.main_ptr, g.mask.main_ptr
+            else:
+                gptr, gpptr, mptr = g.main_ptr, 0, 0
+            sc.conv2d_act_bwd(W.main_ptr, xv.main_ptr, y.main_ptr, gptr, gpptr, mptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
+                              db.main_ptr, N, C, H, Wd, F, KH, KW, sh, sw, ph, pw, code, kept.h)
+            kept.release()
+            return dx, dw
 
         def contraction_backward(dz, need_dx=not x.is_leaf):
             dw = self.weights._grad_target()
@@ -364,7 +427,7 @@ class Conv2D(_ParamLayer):
             sc.cuda_conv2d_bwd(W.main_ptr, xv.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
                                N, C, H, Wd, F, KH, KW, sh, sw, ph, pw)
             return dx, dw
-        self.outputs = self._finish_forward(x, z, F, OH * OW, product, contraction_backward)
+        self.outputs = self._finish_forward(x, z, F, OH * OW, product, contraction_backward, fused_backward)
         return self.outputs
 
     def __repr__(self):
@@ -444,7 +507,12 @@ class MaxPool2D(Layer):
         out._parents = (x,)
         self.mask = mask
 
+        tiles_exactly = (KH, KW, sh, sw, ph, pw) == (2, 2, 2, 2, 0, 0) and H % 2 == 0 and W % 2 == 0
+
         def backward(g):
+            if tiles_exactly and getattr(x, "_takes_pooled", False):
+                x._accumulate(_PooledGrad(g, mask, xv.shape))      # the producer routes it through the mask itself
+                return
             dx = _new(xv.shape)
             sc.cuda_maxpool_bwd(g.main_ptr, mask.main_ptr, dx.main_ptr, N, C, H, W, KH, KW, ph, pw, sh, sw)
             x._accumulate(dx)

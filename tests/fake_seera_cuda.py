@@ -295,6 +295,32 @@ def conv2DTranspose_bias_act_fwd(x, w, b, o, N, Ci, H, W, Co, KH, KW, sh, sw, ph
     bias_act_fwd(o, b, o, N * Co * Ho * Wo, Co, Ho * Wo, act)
 
 
+def conv2d_bias_act_fwd_s(x, w, b, o, N, C, H, W, Fo, R, S, ph, pw, sh, sw, act, x_in):
+    conv2d_bias_act_fwd(x, w, b, o, N, C, H, W, Fo, R, S, ph, pw, sh, sw, act)
+    return 0
+
+
+def shadow_free(h): pass
+
+
+def conv2d_act_bwd(w, x, y, g, gp, mask, dx, dw, db, N, C, H, W, Fo, R, S, sh, sw, ph, pw, act, x_shadow):
+    OH, OW = (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1
+    n = N * Fo * OH * OW
+    full = np.empty(n, np.float32)
+    if gp:
+        tmp = _alloc(n * 4)
+        cuda_maxpool_bwd(gp, mask, tmp, N, Fo, OH, OW, 2, 2, 0, 0, 2, 2)
+        full[:] = _view(tmp, n)
+        cuda_free(tmp)
+    else:
+        full[:] = _view(g, n)
+    tmp = _alloc(n * 4)
+    _view(tmp, n)[:] = full
+    act_bias_bwd(tmp, y, tmp, db, n, Fo, OH * OW, act)
+    cuda_conv2d_bwd(w, x, tmp, dx, dw, N, C, H, W, Fo, R, S, sh, sw, ph, pw)
+    cuda_free(tmp)
+
+
 def act_bias_bwd(dy, y, dz, db, n, ch, inner, act):
     _count("act_bias_bwd")
     g = _view(dy, n).reshape(-1, ch, inner)

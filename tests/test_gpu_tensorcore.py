@@ -151,6 +151,51 @@ def test_bias_and_activation_in_the_epilogue(E, mode):
             assert rel_l2(E.matmul_bias_act(A, B, b, act), _act_ref(R, act)) < 3e-5
 
 
+def _dact_ref(y, act):
+    y = y.astype(np.float64)
+    return [np.ones_like(y), (y > 0).astype(np.float64), y * (1 - y), 1 - y * y][act]
+
+
+# (N, C, H, W, F, KH, KW, sh, sw, ph, pw): tensor-core shapes (kept copies, dz never stored), short-patch shapes (the
+# bias gradient rides in a spare patch column; none spare when C*KH*KW is 16) and a strided one.
+LAYER_BWD = [(4, 16, 8, 8, 24, 3, 3, 1, 1, 1, 1), (2, 70, 12, 12, 130, 3, 3, 1, 1, 1, 1), (3, 8, 16, 16, 16, 3, 3, 2, 2, 1, 1),
+             (4, 3, 16, 16, 20, 3, 3, 1, 1, 1, 1), (2, 1, 12, 12, 6, 4, 4, 1, 1, 2, 2), (2, 1, 8, 8, 70, 3, 3, 1, 1, 1, 1)]
+
+
+@pytest.mark.parametrize("mode", [2, 3])
+@pytest.mark.parametrize("shape", LAYER_BWD)
+def test_conv_layer_backward_in_one_call(E, mode, shape):
+    """seera_conv2d_act_bwd from a full-resolution gradient and from a pooled one, against the oracle's separate steps."""
+    N, C, H, W, F, KH, KW, sh, sw, ph, pw = shape
+    rs = np.random.RandomState(sum(shape) + 11)
+    X, Wt, b = (rs.standard_normal(s).astype(np.float32) for s in ((N, C, H, W), (F, C, KH, KW), (F,)))
+    Wt /= np.float32(np.sqrt(C * KH * KW))
+    _prep(mode)
+    Z = co.conv2d_forward(X, Wt, sh, sw, ph, pw) + b.reshape(1, F, 1, 1)
+    OH, OW = Z.shape[2:]
+    for act in (0, 1, 2, 3):
+        for pooled in (False, True):
+            for need_dx in (True, False):
+                if pooled and (OH % 2 or OW % 2):
+                    continue
+                if pooled:
+                    gp = rs.standard_normal((N, F, OH // 2, OW // 2)).astype(np.float32)
+                    y, pool_out, dX, dW, db = E.conv2d_layer_roundtrip(X, Wt, b, sh, sw, ph, pw, act, gp=gp, need_dx=need_dx)
+                    ref_pool, mask = co.maxpool2d_forward(y, 2, 2, 2, 2, 0, 0)
+                    assert np.array_equal(pool_out, ref_pool)
+                    dy = co.maxpool2d_backward(gp, mask, N, F, OH, OW, 2, 2, 2, 2, 0, 0)
+                else:
+                    g = rs.standard_normal((N, F, OH, OW)).astype(np.float32)
+                    y, _, dX, dW, db = E.conv2d_layer_roundtrip(X, Wt, b, sh, sw, ph, pw, act, g=g, need_dx=need_dx, keep=act != 2)
+                    dy = g
+                assert rel_l2(y, _act_ref(Z, act)) < 3e-5
+                dz = (dy.astype(np.float64) * _dact_ref(y, act)).astype(np.float32)        # from the device's own y, as the kernel does
+                rX, rW = co.conv2d_backward(dz, X, Wt, sh, sw, ph, pw)
+                assert rel_l2(dW, rW) < 3e-5 and rel_l2(db, dz.astype(np.float64).sum(axis=(0, 2, 3))) < 3e-5
+                if need_dx:
+                    assert rel_l2(dX, rX) < 3e-5
+
+
 def test_c5_conv_backward_point_bf16(E):
     """One point of the Conv2D-backward sweep at reduced batch (C = K = 64, 56x56, 3x3 s1 p1), bf16 operands."""
     X, Wt, dY = wl.c5_conv_bwd(64, 56, n=4)
