@@ -224,6 +224,10 @@ void seera_shadow_free(seera_shadow_t *s);
 int seera_conv2d_bias_act_fwd_s(const float *image, const float *kernel, const float *bias, float *out, int batchN, int C, int H,
                                 int W, int F, int R, int S, int pad_h, int pad_w, int stride_h, int stride_w, int act,
                                 seera_shadow_t *x_in, seera_shadow_t **x_keep);
+/* cuda_maxpool_fwd for a 2x2 window, stride 2, no padding, even H and W, which also returns the channels-last
+ * copies of its OUTPUT in *out_shadow for the convolution that consumes it (pass them as x_in).  Same values
+ * and mask as cuda_maxpool_fwd.  *out_shadow is NULL when no copies were made (exact-fp32 mode). */
+int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, int H, int W, seera_shadow_t **out_shadow);
 /* Backward of y = act(conv2d(X, W) + bias) in one call (Conv2D backward: Seera_Engine.py:571-583 activation,
  * :43-65 bias, :67-115 convolution; with gp also MaxPool2D backward, :117-131).  The gradient arrives either
  * as g = dL/dy [N,F,OH,OW] or as gp = dL/d(maxpool2x2(y)) [N,F,OH/2,OW/2] with that pool's mask from

@@ -16,6 +16,8 @@
 // forward, its dW a dW with X and dY swapped).  Data gradients with stride > 1 go to the kernel that gathers in
 // its producer warps (contraction_tc.cu).  Outputs are written fp32 NCHW straight from TMEM (lanes run along
 // pixels, so stores are coalesced).  Arithmetic follows engine/src/conv_ops.cpp:95-287.
+#include <cfloat>
+
 #include "internal.h"
 #include "tma_gemm_kernel.cuh"
 
@@ -418,6 +420,48 @@ __global__ void __launch_bounds__(256) dz_bias_sum_kernel(const float *__restric
     if (lane == 0) out[c] = t;
 }
 
+// ---- 2x2 / stride-2 max-pool that also writes the channels-last copies of its output ---------------------------
+// Same thread layout as dz_shadow_kernel (warp = 8 channels, lane = output pixel).  The scan order and the strict
+// comparison match cuda_maxpool_fwd, so values and window-local argmax indices are the same bit for bit.
+template <int NS>
+__global__ void __launch_bounds__(256) pool2x2_shadow_kernel(const float *__restrict__ y, float *__restrict__ out, int *__restrict__ mask,
+                                                             int C, int H, int W, int Cp, int items, int ptiles,
+                                                             __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
+                                                             __nv_bfloat16 *__restrict__ d2) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cb = blockIdx.y * 64 + warp * 8;
+    const int OW = W >> 1, Pq = (H >> 1) * OW;
+    if (cb >= Cp) return;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int img = item / ptiles, q = (item - img * ptiles) * 32 + lane;
+        if (q >= Pq) continue;
+        const int oh = q / OW, ow = q - oh * OW;
+        float2 a[8], b[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float *r = y + (((long long)img * C + min(cb + i, C - 1)) * H + 2 * oh) * W + 2 * ow;
+            a[i] = __ldg(reinterpret_cast<const float2 *>(r));
+            b[i] = __ldg(reinterpret_cast<const float2 *>(r + W));
+        }
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float m = -FLT_MAX; int idx = 0;
+            if (a[i].x > m) { m = a[i].x; idx = 0; } if (a[i].y > m) { m = a[i].y; idx = 1; }
+            if (b[i].x > m) { m = b[i].x; idx = 2; } if (b[i].y > m) { m = b[i].y; idx = 3; }
+            if (cb + i < C) {
+                const long long o = ((long long)img * C + cb + i) * Pq + q;
+                out[o] = m; mask[o] = idx;
+            }
+            v[i] = cb + i < C ? m : 0.f;
+        }
+        const long long o = ((long long)img * Pq + q) * Cp + cb;
+        *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
+        if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
+        if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+    }
+}
+
 static bool conv_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     return NB >= 1 && C >= 1 && H >= 1 && W >= 1 && F >= 1 && R >= 1 && S >= 1 && sh >= 1 && sw >= 1 && ph >= 0 && pw >= 0 &&
            (long long)NB * (C > F ? C : F) * H * W * (long long)(sh * sw) < (1LL << 31);
@@ -562,6 +606,35 @@ int seera_conv2d_bias_act_fwd_s(const float *X, const float *Wt, const float *bi
         free_nhwc(local);
     }
     return s;
+}
+
+int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, int H, int W, seera_shadow_t **out_shadow) {
+    SEERA_ENSURE();
+    if (out_shadow) *out_shadow = nullptr;
+    if (N < 1 || C < 1 || H < 2 || W < 2 || (H & 1) || (W & 1) || !X || !out || !mask) return fail(SEERA_E_ARG, "maxpool2x2_fwd: bad argument");
+    const int Pq = (H / 2) * (W / 2), ptiles = (Pq + 31) / 32;
+    const long long items = (long long)N * ptiles;
+    if (!out_shadow || !rt().precision || !rt().conv_tma || N > 65535 || items > 0x7fffffff || (reinterpret_cast<uintptr_t>(X) & 7))
+        return seera_cuda_maxpool_fwd(X, out, mask, N, C, H, W, 2, 2, 0, 0, 2, 2);
+    const int ns = precision_copies();
+    NhwcShadow sh;
+    sh.NB = N; sh.H = H / 2; sh.W = W / 2; sh.C = C; sh.Cp = (C + 7) / 8 * 8;
+    size_t bytes = (size_t)N * Pq * sh.Cp * 2;
+    for (int i = 0; i < ns; i++) { sh.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!sh.p[i]) { free_nhwc(sh); return SEERA_E_OOM; } }
+    const int cchunks = (sh.Cp + 63) / 64;
+    int blocks = rt().sm_count * 8 / cchunks;
+    if (blocks < 1) blocks = 1;
+    if (blocks > items) blocks = (int)items;
+    dim3 grid((unsigned)blocks, (unsigned)cchunks);
+    cudaStream_t st = rt().stream;
+    if (ns == 1) pool2x2_shadow_kernel<1><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
+    else if (ns == 2) pool2x2_shadow_kernel<2><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
+    else pool2x2_shadow_kernel<3><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { free_nhwc(sh); return check_cuda(e, "maxpool2x2_fwd"); }
+    *out_shadow = new seera_shadow{sh, ns};
+    return SEERA_OK;
 }
 
 // dz = dy * act'(y) as channels-last copies plus dbias; dy = g, or gp through a 2x2 / stride-2 max-pool mask.

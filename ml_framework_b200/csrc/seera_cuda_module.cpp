@@ -185,6 +185,10 @@ PYBIND11_MODULE(seera_cuda, m) {
         ck(seera_conv2d_bias_act_fwd_s(P<const F>(x), P<const F>(w), P<const F>(b), P<F>(o), N, C, H, W, Fo, R, S, ph, pw, sh, sw, act,
                                        P<seera_shadow_t>(x_in), &keep));
         return reinterpret_cast<uptr>(keep); });
+    m.def("maxpool2x2_fwd_s", [](uptr x, uptr o, uptr mask, int N, int C, int H, int W) {
+        seera_shadow_t *keep = nullptr;
+        ck(seera_maxpool2x2_fwd_s(P<const F>(x), P<F>(o), P<int>(mask), N, C, H, W, &keep));
+        return reinterpret_cast<uptr>(keep); });
     m.def("shadow_free", [](uptr h) { seera_shadow_free(P<seera_shadow_t>(h)); });
     m.def("conv2d_act_bwd", [](uptr w, uptr x, uptr y, uptr g, uptr gp, uptr mask, uptr dx, uptr dw, uptr db, int N, int C, int H, int W,
                                int Fo, int R, int S, int sh, int sw, int ph, int pw, int act, uptr x_shadow) {

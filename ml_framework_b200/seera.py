@@ -393,6 +393,11 @@ class Conv2D(_ParamLayer):
         self.weights = Tensor(self._w_init, is_leaf=True)
         self.bais = Tensor(self._b_init, is_leaf=True)
 
+    def __call__(self, input_layer):
+        super().__call__(input_layer)
+        input_layer._feeds_conv = True        # a pooling producer then also emits the channels-last copies this layer reads
+        return self
+
     def forward(self):
         x = self.inputs = self.inpobj.outputs
         xv, W = x.value, self.weights.value
@@ -405,9 +410,11 @@ class Conv2D(_ParamLayer):
         OH, OW = (H + 2 * ph - KH) // sh + 1, (Wd + 2 * pw - KW) // sw + 1
         z = _new((N, F, OH, OW))
         kept = _KeptCopies()
+        given = getattr(x, "_copies", None) if x.value is xv else None       # copies made by the producer of x
 
         def product(bias, code):
-            kept.h = sc.conv2d_bias_act_fwd_s(xv.main_ptr, W.main_ptr, bias, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw, code, 0)
+            kept.h = sc.conv2d_bias_act_fwd_s(xv.main_ptr, W.main_ptr, bias, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw, code,
+                                              given.h if given else 0)
 
         def fused_backward(g, y, code, db, need_dx=not x.is_leaf):
             dw = self.weights._grad_target()
@@ -417,8 +424,10 @@ class Conv2D(_ParamLayer):
             else:
                 gptr, gpptr, mptr = g.main_ptr, 0, 0
             sc.conv2d_act_bwd(W.main_ptr, xv.main_ptr, y.main_ptr, gptr, gpptr, mptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
-                              db.main_ptr, N, C, H, Wd, F, KH, KW, sh, sw, ph, pw, code, kept.h)
+                              db.main_ptr, N, C, H, Wd, F, KH, KW, sh, sw, ph, pw, code, kept.h or (given.h if given else 0))
             kept.release()
+            if given:
+                given.release()
             return dx, dw
 
         def contraction_backward(dz, need_dx=not x.is_leaf):
@@ -502,12 +511,16 @@ class MaxPool2D(Layer):
         mask = cuten._wrap(sc.cuda_malloc_i32(N * C * OH * OW), (N, C, OH, OW), "int32")
         if OH * OW > H * W:
             raise ValueError("[cuTen]: maxpool2d with more outputs than inputs is not supported")
-        sc.cuda_maxpool_fwd(xv.main_ptr, y.main_ptr, mask.main_ptr, N, C, H, W, KH, KW, ph, pw, sh, sw)
+        tiles_exactly = (KH, KW, sh, sw, ph, pw) == (2, 2, 2, 2, 0, 0) and H % 2 == 0 and W % 2 == 0
+        copies = _KeptCopies()
+        if tiles_exactly and getattr(self, "_feeds_conv", False):   # also leaves the channels-last copies of y for that convolution
+            copies.h = sc.maxpool2x2_fwd_s(xv.main_ptr, y.main_ptr, mask.main_ptr, N, C, H, W)
+        else:
+            sc.cuda_maxpool_fwd(xv.main_ptr, y.main_ptr, mask.main_ptr, N, C, H, W, KH, KW, ph, pw, sh, sw)
         out = Tensor(y)
         out._parents = (x,)
+        out._copies = copies
         self.mask = mask
-
-        tiles_exactly = (KH, KW, sh, sw, ph, pw) == (2, 2, 2, 2, 0, 0) and H % 2 == 0 and W % 2 == 0
 
         def backward(g):
             if tiles_exactly and getattr(x, "_takes_pooled", False):

@@ -196,6 +196,46 @@ def test_conv_layer_backward_in_one_call(E, mode, shape):
                     assert rel_l2(dX, rX) < 3e-5
 
 
+@pytest.mark.parametrize("mode", [1, 2, 3])
+def test_pool_hands_its_copies_to_the_next_convolution(E, mode):
+    """seera_maxpool2x2_fwd_s: pooled values and mask bit-equal to the oracle; a convolution fed the returned copies gives
+    bit-equal results to one that makes its own."""
+    import ctypes
+    from ml_framework_b200 import capi
+    L = capi.load()
+    _prep(mode)
+    rs = np.random.RandomState(mode)
+    for (N, C, H, W, F) in [(3, 70, 12, 20, 40), (2, 16, 8, 8, 16), (5, 9, 6, 10, 7)]:
+        Y = rs.standard_normal((N, C, H, W)).astype(np.float32)
+        Wt = rs.standard_normal((F, C, 3, 3)).astype(np.float32)
+        want_out, want_mask = co.maxpool2d_forward(Y, 2, 2, 2, 2, 0, 0)
+        up = lambda a: L.seera_to_device(np.ascontiguousarray(a).ctypes.data_as(ctypes.c_void_p), a.nbytes)
+        yd, wd = up(Y), up(Wt)
+        n_out = N * C * (H // 2) * (W // 2)
+        od, md = L.seera_cuda_malloc(n_out * 4), L.seera_cuda_malloc(n_out * 4)
+        h = ctypes.c_void_p()
+        capi.check(L.seera_maxpool2x2_fwd_s(yd, od, md, N, C, H, W, ctypes.byref(h)))
+        assert h.value
+        out, mask = np.empty((N, C, H // 2, W // 2), np.float32), np.empty((N, C, H // 2, W // 2), np.int32)
+        capi.check(L.seera_to_host(out.ctypes.data_as(ctypes.c_void_p), od, out.nbytes))
+        capi.check(L.seera_to_host(mask.ctypes.data_as(ctypes.c_void_p), md, mask.nbytes))
+        assert np.array_equal(out, want_out) and np.array_equal(mask, want_mask)
+        res = []
+        for x_in in (h, None):
+            zd = L.seera_cuda_malloc(N * F * (H // 2) * (W // 2) * 4)
+            keep = ctypes.c_void_p()
+            capi.check(L.seera_conv2d_bias_act_fwd_s(od, wd, None, zd, N, C, H // 2, W // 2, F, 3, 3, 1, 1, 1, 1, 0, x_in, ctypes.byref(keep)))
+            assert bool(keep.value) == (x_in is None)         # copies are made only when none were given
+            z = np.empty((N, F, H // 2, W // 2), np.float32)
+            capi.check(L.seera_to_host(z.ctypes.data_as(ctypes.c_void_p), zd, z.nbytes))
+            res.append(z)
+            L.seera_shadow_free(keep); L.seera_cuda_free(zd)
+        assert np.array_equal(res[0], res[1])
+        L.seera_shadow_free(h)
+        for p in (yd, wd, od, md):
+            L.seera_cuda_free(p)
+
+
 def test_c5_conv_backward_point_bf16(E):
     """One point of the Conv2D-backward sweep at reduced batch (C = K = 64, 56x56, 3x3 s1 p1), bf16 operands."""
     X, Wt, dY = wl.c5_conv_bwd(64, 56, n=4)
