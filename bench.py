@@ -263,18 +263,22 @@ def run_gpu(args, work):
     ctypes.memmove(hx, X.ctypes.data, X.nbytes)
     ctypes.memmove(hy, Y.ctypes.data, Y.nbytes)
 
-    def e2e_step():
-        sc.upload_from_host_ptr(Xd.value.main_ptr, hx, X.nbytes)
-        sc.upload_from_host_ptr(Yd.value.main_ptr, hy, Y.nbytes)
-        return float(run_step().value.to_host_f32()[0])
-    for _ in range(2):
-        e2e_step()
+    # Graph mode streams the batches (Trainer.fit_stream: upload of batch i+1 and read-back of loss i-1 on the copy
+    # stream while step i runs); eager mode uploads, steps and reads the loss in turn.
+    def e2e_run(k):
+        if use_graph:
+            return tr.fit_stream(((hx, hy) for _ in range(k)), data_parallel=dist is not None)[-1]
+        last = 0.0
+        for _ in range(k):
+            sc.upload_from_host_ptr(Xd.value.main_ptr, hx, X.nbytes)
+            sc.upload_from_host_ptr(Yd.value.main_ptr, hy, Y.nbytes)
+            last = float(run_step().value.to_host_f32()[0])
+        return last
+    e2e_run(3)
     barrier()
     l1 = sc.launch_count()
     sc.event_record(e0)
-    last = 0.0
-    for _ in range(args.steps):
-        last = e2e_step()
+    last = e2e_run(args.steps)
     sc.event_record(e1)
     barrier()
     launches_per_step = (sc.launch_count() - l1) / args.steps

@@ -106,6 +106,15 @@ int   seera_host_free_pinned(void *p);
 /* ---- transfers (cuda_bindings.cpp:73-170) ------------------------------------------------ */
 void *seera_to_device(const void *host, size_t n_bytes);              /* :98,:155,:164 allocate + upload */
 int   seera_upload(void *dev, const void *host, size_t n_bytes);      /* upload into an existing buffer  */
+/* A second stream for transfers that overlap the compute stream (next batch in, previous loss out, while a step
+ * runs).  Host memory must be page-locked (seera_host_alloc_pinned).  The two fences order "everything queued so
+ * far" on one stream before everything queued later on the other.  Not usable while a graph is being captured.
+ * No counterpart in the reference, which copies synchronously on the default stream (cuda_bindings.cpp:98-170). */
+int   seera_copy_upload(void *dev, const void *pinned_host, size_t n_bytes);
+int   seera_copy_download(void *pinned_host, const void *dev, size_t n_bytes);
+int   seera_copy_wait_compute(void);     /* later copy-stream work waits for the compute stream's current tail */
+int   seera_compute_wait_copy(void);     /* later compute-stream work waits for the copy stream's current tail */
+int   seera_copy_synchronize(void);      /* host waits for the copy stream                                    */
 int   seera_to_host(void *host, const void *dev, size_t n_bytes);     /* :107,:123,:139 download + sync  */
 
 /* ---- unary ops: out = f(x), grad = f'(x)   (seera_engine_cuda.hpp:9-25) -------------------- */

@@ -337,6 +337,63 @@ int seera_upload(void *dev, const void *host, size_t n_bytes) {
     // `host` at once; from pinned memory the copy is asynchronous and ordered on the stream.
     return check_cuda(cudaMemcpyAsync(dev, host, n_bytes, cudaMemcpyHostToDevice, rt().stream), "cudaMemcpyAsync h2d");
 }
+// ---- copy stream: host<->device transfers that overlap the compute stream -----------------------------------
+// One extra non-blocking stream per process.  Ordering against the compute stream is explicit: each fence records an
+// event at the current tail of one stream and makes the other wait for it, so "everything queued so far" is the unit.
+static cudaStream_t copy_stream(int *status) {
+    static cudaStream_t cs[64] = {nullptr};
+    const int dev = rt().device & 63;
+    if (!cs[dev]) {
+        cudaError_t e = cudaStreamCreateWithFlags(&cs[dev], cudaStreamNonBlocking);
+        if (e != cudaSuccess) { *status = check_cuda(e, "cudaStreamCreate(copy)"); return nullptr; }
+    }
+    return cs[dev];
+}
+static int fence(cudaStream_t from, cudaStream_t to, const char *what) {
+    cudaEvent_t ev;
+    if (int s = check_cuda(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), what)) return s;
+    cudaError_t e = cudaEventRecord(ev, from);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(to, ev, 0);
+    cudaEventDestroy(ev);              // released once the recorded work has completed
+    return check_cuda(e, what);
+}
+static int copy_guard(const char *what) {
+    if (rt().capturing) return fail(SEERA_E_ARG, "%s: not allowed while a graph is being captured", what);
+    return SEERA_OK;
+}
+int seera_copy_upload(void *dev, const void *pinned_host, size_t n_bytes) {
+    SEERA_ENSURE();
+    if (!dev || !pinned_host) return fail(SEERA_E_ARG, "copy_upload: null");
+    if (int s = copy_guard("copy_upload")) return s;
+    int st = SEERA_OK; cudaStream_t cs = copy_stream(&st); if (!cs) return st;
+    return check_cuda(cudaMemcpyAsync(dev, pinned_host, n_bytes, cudaMemcpyHostToDevice, cs), "cudaMemcpyAsync h2d (copy stream)");
+}
+int seera_copy_download(void *pinned_host, const void *dev, size_t n_bytes) {
+    SEERA_ENSURE();
+    if (!dev || !pinned_host) return fail(SEERA_E_ARG, "copy_download: null");
+    if (int s = copy_guard("copy_download")) return s;
+    int st = SEERA_OK; cudaStream_t cs = copy_stream(&st); if (!cs) return st;
+    return check_cuda(cudaMemcpyAsync(pinned_host, dev, n_bytes, cudaMemcpyDeviceToHost, cs), "cudaMemcpyAsync d2h (copy stream)");
+}
+int seera_copy_wait_compute(void) {
+    SEERA_ENSURE();
+    if (int s = copy_guard("copy_wait_compute")) return s;
+    int st = SEERA_OK; cudaStream_t cs = copy_stream(&st); if (!cs) return st;
+    return fence(rt().stream, cs, "copy_wait_compute");
+}
+int seera_compute_wait_copy(void) {
+    SEERA_ENSURE();
+    if (int s = copy_guard("compute_wait_copy")) return s;
+    int st = SEERA_OK; cudaStream_t cs = copy_stream(&st); if (!cs) return st;
+    return fence(cs, rt().stream, "compute_wait_copy");
+}
+int seera_copy_synchronize(void) {
+    SEERA_ENSURE();
+    if (int s = copy_guard("copy_synchronize")) return s;
+    int st = SEERA_OK; cudaStream_t cs = copy_stream(&st); if (!cs) return st;
+    return check_cuda(cudaStreamSynchronize(cs), "cudaStreamSynchronize(copy)");
+}
+
 int seera_to_host(void *host, const void *dev, size_t n_bytes) {
     SEERA_ENSURE();
     if (!dev || !host) return fail(SEERA_E_ARG, "to_host: null");

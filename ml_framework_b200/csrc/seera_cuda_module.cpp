@@ -166,6 +166,11 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("pool_bytes_reserved", []() { return seera_pool_bytes_reserved(); });
     m.def("upload_f32", [](uptr dst, arr_f a) { ck(seera_upload(P<void>(dst), a.data(), (size_t)a.size() * 4)); });
     m.def("upload_from_host_ptr", [](uptr dst, uptr host, size_t nbytes) { ck(seera_upload(P<void>(dst), P<const void>(host), nbytes)); });
+    m.def("copy_upload", [](uptr dst, uptr host, size_t nbytes) { ck(seera_copy_upload(P<void>(dst), P<const void>(host), nbytes)); });
+    m.def("copy_download", [](uptr host, uptr src, size_t nbytes) { ck(seera_copy_download(P<void>(host), P<const void>(src), nbytes)); });
+    m.def("copy_wait_compute", []() { ck(seera_copy_wait_compute()); });
+    m.def("compute_wait_copy", []() { ck(seera_compute_wait_copy()); });
+    m.def("copy_synchronize", []() { ck(seera_copy_synchronize()); });
     m.def("host_alloc_pinned", [](size_t n) { return ckp(seera_host_alloc_pinned(n)); });
     m.def("host_free_pinned", [](uptr p) { ck(seera_host_free_pinned(P<void>(p))); });
     m.def("bias_act_fwd", [](uptr z, uptr b, uptr y, int n, int ch, int inner, int act) {

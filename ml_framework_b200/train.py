@@ -131,6 +131,48 @@ class Trainer:
         self.opt._enqueue()
         return self._graph_keep[2]
 
+    def fit_stream(self, host_batches, data_parallel=False):
+        """Runs the captured step once per host batch with the transfers on the copy stream: while step i runs, batch
+        i+1 is uploaded and the loss of step i-1 is read back, so the compute stream never waits for PCIe.
+        `host_batches` yields (x_ptr, y_ptr): addresses of page-locked host buffers (seera_cuda.host_alloc_pinned)
+        holding float32 arrays of the captured shapes.  Returns the losses, one per batch, in order."""
+        import ctypes
+        X, Y, loss = self._graph_keep[:3]
+        replay = self.replay_data_parallel if data_parallel else self.replay
+        if getattr(self, "_stage", None) is None:
+            self._stage = (S._new(X.value.shape), S._new(Y.value.shape), sc.host_alloc_pinned(8))
+        sx, sy, hl = self._stage
+        slots = (ctypes.c_float * 2).from_address(hl)
+        nbx, nby = X.value.size * 4, Y.value.size * 4
+
+        def upload(batch):
+            sc.copy_upload(sx.main_ptr, batch[0], nbx)
+            sc.copy_upload(sy.main_ptr, batch[1], nby)
+        losses, it, i = [], iter(host_batches), 0
+        batch = next(it, None)
+        if batch is not None:
+            sc.copy_wait_compute()                   # whatever still reads the staging buffers comes first
+            upload(batch)
+        while batch is not None:
+            sc.compute_wait_copy()                   # batch i has landed in the staging buffers
+            sc.cuda_memcopy_devicetodevice(X.value.main_ptr, sx.main_ptr, X.value.size)
+            sc.cuda_memcopy_devicetodevice(Y.value.main_ptr, sy.main_ptr, Y.value.size)
+            sc.copy_wait_compute()                   # the staging buffers are free again after those two copies
+            replay()
+            if i:                                    # loss of step i-1: the device is already busy with step i
+                sc.copy_synchronize()
+                losses.append(float(slots[(i - 1) & 1]))
+            batch = next(it, None)
+            if batch is not None:
+                upload(batch)
+            sc.copy_wait_compute()                   # the loss is final once step i has run
+            sc.copy_download(hl + 4 * (i & 1), loss.value.main_ptr, 4)
+            i += 1
+        if i:
+            sc.copy_synchronize()
+            losses.append(float(slots[(i - 1) & 1]))
+        return losses
+
     def release_graph(self):
         g = getattr(self, "_graph", None)
         if g:

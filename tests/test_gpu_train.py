@@ -146,3 +146,42 @@ def test_captured_step_graph_replays_like_eager_steps(T, name, n, mode):
     b.release_graph()
     sc.set_precision(0)
     assert sc.tc_device_status() == 0
+
+
+def test_streamed_batches_match_step_by_step_uploads(T):
+    """fit_stream (next batch uploaded and previous loss read back on the copy stream while a step runs) gives the
+    losses and weights of upload -> replay -> read, batch by batch, bit for bit."""
+    import ctypes
+    from ml_framework_b200 import seera as S, seera_cuda as sc
+    sc.set_precision(2)
+    work = wl.WORKLOADS["c1"]()
+    batches = [work.batch(32, 20 + i) for i in range(5)]
+    a, b = T.Trainer(work, seed=3), T.Trainer(work, seed=3)
+    dev = []
+    for tr in (a, b):
+        Xd, Yd = S.Tensor(batches[0][0], is_leaf=True), S.Tensor(batches[0][1], is_leaf=True)
+        for _ in range(2):
+            tr.step(Xd, Yd)
+        tr.capture(Xd, Yd)
+        dev.append((Xd, Yd))
+    want = []
+    for X, Y in batches:
+        sc.upload_f32(dev[0][0].value.main_ptr, np.ascontiguousarray(X, np.float32))
+        sc.upload_f32(dev[0][1].value.main_ptr, np.ascontiguousarray(Y, np.float32))
+        want.append(float(a.replay().value.to_host_f32()[0]))
+    pinned = []
+    for X, Y in batches:
+        X, Y = np.ascontiguousarray(X, np.float32), np.ascontiguousarray(Y, np.float32)
+        hx, hy = sc.host_alloc_pinned(X.nbytes), sc.host_alloc_pinned(Y.nbytes)
+        ctypes.memmove(hx, X.ctypes.data, X.nbytes)
+        ctypes.memmove(hy, Y.ctypes.data, Y.nbytes)
+        pinned.append((hx, hy))
+    got = b.fit_stream(pinned)
+    assert got == want
+    for Pa, Pb in zip(a.host_params(), b.host_params()):
+        if Pa is not None:
+            assert np.array_equal(Pa[0], Pb[0]) and np.array_equal(Pa[1], Pb[1])
+    for hx, hy in pinned:
+        sc.host_free_pinned(hx); sc.host_free_pinned(hy)
+    a.release_graph(); b.release_graph()
+    sc.set_precision(0)
