@@ -409,15 +409,25 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
     if (stages < 2) return fail(SEERA_E_LIMIT, "%s: tile does not fit shared memory", name);
     size_t smem = stage * stages + 4 * EPI_WARP_SMEM + 1024;
     long long tiles = (long long)((p.M + TC_BM - 1) / TC_BM) * ((p.N + p.bn - 1) / p.bn);
+    // Split of the contraction: every (tile, split) item is one pass of a persistent CTA, so the launch takes
+    // ceil(items / SMs) rounds of ceil(ksteps / splits) k-steps each, plus a fixed cost per item (pipeline fill, the
+    // partial tile written out, worth about four k-steps).  Take the split count with the smallest such estimate;
+    // ties go to fewer splits (less partial traffic).
     int splits = 1;
+    const long long ksteps = (p.K + TC_BK - 1) / TC_BK;
     if (allow_split) {
-        long long want = (rt().sm_count + tiles - 1) / tiles;
-        long long maxs = p.K / (TC_BK * 4);
-        splits = (int)(want < maxs ? want : maxs);
-        if (splits < 1) splits = 1;
-        if (splits > 256) splits = 256;
+        const long long sms = rt().sm_count;
+        long long maxs = ksteps / 4;
+        if (maxs > 256) maxs = 256;
+        long long best = -1;
+        for (long long sp = 1; sp <= maxs || sp == 1; sp++) {
+            long long per = (ksteps + sp - 1) / sp, eff = (ksteps + per - 1) / per;
+            long long rounds = (tiles * eff + sms - 1) / sms;
+            long long cost = rounds * (per + 4);
+            if (best < 0 || cost < best) { best = cost; splits = (int)eff; }
+        }
     }
-    p.kchunk = ((p.K + splits - 1) / splits + TC_BK - 1) / TC_BK * TC_BK;
+    p.kchunk = (int)((ksteps + splits - 1) / splits) * TC_BK;
     splits = (p.K + p.kchunk - 1) / p.kchunk;
     p.splits = splits;
     p.stages = stages;
