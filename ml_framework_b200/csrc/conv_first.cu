@@ -82,12 +82,14 @@ __global__ void __launch_bounds__(256) conv_first_fwd_kernel(const float *__rest
 
     const int P = g.OH * g.OW;
     const long long pixels = (long long)g.NB * P;
+    const long long groups = (pixels + 256 * PIX - 1) / (256 * PIX);
+  for (long long grp = blockIdx.x; grp < groups; grp += gridDim.x) {       // persistent: the filters above are staged once
     float x[PIX][KP];
     long long obase[PIX];
     bool live[PIX];
 #pragma unroll
     for (int j = 0; j < PIX; j++) {
-        long long pix = ((long long)blockIdx.x * PIX + j) * 256 + threadIdx.x;
+        long long pix = (grp * PIX + j) * 256 + threadIdx.x;
         live[j] = pix < pixels;
         int img = live[j] ? (int)(pix / P) : 0, rem = live[j] ? (int)(pix - (long long)img * P) : 0;
         int oh = rem / g.OW, ow = rem - oh * g.OW;
@@ -138,6 +140,7 @@ __global__ void __launch_bounds__(256) conv_first_fwd_kernel(const float *__rest
             yp[j] += 4 * P4;
         }
     }
+  }
 }
 
 // ---- weight gradient ----------------------------------------------------------------------------------------------
@@ -305,6 +308,15 @@ __global__ void __launch_bounds__(256) conv_first_wgrad_reduce_kernel(const floa
     }
 }
 
+// Blocks of `kernel` that one SM holds at once (256 threads, static shared memory only); a persistent grid of
+// exactly SMs x this many blocks runs as a single round.
+template <class K>
+static int resident_blocks(K kernel) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, 0) != cudaSuccess || n < 1) { cudaGetLastError(); n = 1; }
+    return n;
+}
+
 static bool first_geom(FirstGeom &g, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     g = FirstGeom{NB, C, H, W, F, R, S, sh, sw, ph, pw, (H + 2 * ph - R) / sh + 1, (W + 2 * pw - S) / sw + 1, C * R * S};
     return g.K <= 64 && R < 32768 && S < 32768 && (F + FIRST_FC - 1) / FIRST_FC <= 65535;
@@ -319,16 +331,23 @@ int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y,
     long long pixels = (long long)NB * g.OH * g.OW;
     unsigned chunks = (unsigned)((F + FIRST_FC - 1) / FIRST_FC);
     cudaStream_t st = rt().stream;
+    const int sms = rt().sm_count;
+    auto grid_for = [&](int per_sm, int pix_per_block) {
+        long long groups = (pixels + pix_per_block - 1) / pix_per_block;
+        long long blocks = (long long)sms * per_sm / chunks;
+        if (blocks < 1) blocks = 1;
+        return dim3((unsigned)(groups < blocks ? groups : blocks), chunks);
+    };
     profile_begin();
     if (g.K <= 16) {
-        dim3 grid((unsigned)((pixels + 511) / 512), chunks);
-        conv_first_fwd_kernel<16, 2><<<grid, 256, 0, st>>>(X, Wt, bias, Y, g, act);
+        static int occ = 0; if (!occ) occ = resident_blocks(conv_first_fwd_kernel<16, 2>);
+        conv_first_fwd_kernel<16, 2><<<grid_for(occ, 512), 256, 0, st>>>(X, Wt, bias, Y, g, act);
     } else if (g.K <= 32) {
-        dim3 grid((unsigned)((pixels + 511) / 512), chunks);
-        conv_first_fwd_kernel<32, 2><<<grid, 256, 0, st>>>(X, Wt, bias, Y, g, act);
+        static int occ = 0; if (!occ) occ = resident_blocks(conv_first_fwd_kernel<32, 2>);
+        conv_first_fwd_kernel<32, 2><<<grid_for(occ, 512), 256, 0, st>>>(X, Wt, bias, Y, g, act);
     } else {
-        dim3 grid((unsigned)((pixels + 255) / 256), chunks);
-        conv_first_fwd_kernel<64, 1><<<grid, 256, 0, st>>>(X, Wt, bias, Y, g, act);
+        static int occ = 0; if (!occ) occ = resident_blocks(conv_first_fwd_kernel<64, 1>);
+        conv_first_fwd_kernel<64, 1><<<grid_for(occ, 256), 256, 0, st>>>(X, Wt, bias, Y, g, act);
     }
     count_launch();
     cudaError_t e = cudaGetLastError();
@@ -342,7 +361,11 @@ static int first_wgrad_run(const float *X, const DzSource &src, float *dW, float
     int chunks = (g.F + FIRST_FC - 1) / FIRST_FC;
     int KP = g.K <= 16 ? 16 : g.K <= 32 ? 32 : 64;
     if (dbias && g.K >= KP) return fail(SEERA_E_LIMIT, "%s: no spare patch column for the bias gradient", name);
-    int nblocks = rt().sm_count * 4 / chunks;
+    static int occ[3] = {0, 0, 0};
+    int &o = occ[KP == 16 ? 0 : KP == 32 ? 1 : 2];
+    if (!o) o = KP == 16 ? resident_blocks(conv_first_wgrad_kernel<16>) : KP == 32 ? resident_blocks(conv_first_wgrad_kernel<32>)
+                                                                                   : resident_blocks(conv_first_wgrad_kernel<64>);
+    int nblocks = rt().sm_count * o / chunks;          // one round of resident blocks
     if (nblocks < 1) nblocks = 1;
     if (nblocks > ntiles) nblocks = ntiles;
     float *partial = (float *)scratch_alloc((size_t)chunks * nblocks * FIRST_FC * KP * sizeof(float));
