@@ -14,7 +14,10 @@
 // Replaces cuda_conv2d_fwd / the dW half of cuda_conv2d_bwd of the reference for these shapes
 // (engine_cuda/src/conv_fwd.cu, conv_bwd.cu: im2col + WMMA GEMM there).
 #include "common.cuh"
+#include "contraction_functors.cuh"
 #include "internal.h"
+#include "tc_epilogue.cuh"
+#include "tma_gemm_kernel.cuh"
 
 namespace seera {
 
@@ -317,6 +320,416 @@ static int resident_blocks(K kernel) {
     return n;
 }
 
+
+// =====================================================================================================================
+// Tensor-core variants (precision modes 1-3).  The patch of a pixel is at most 64 values, i.e. ONE 128-byte row of a
+// K-major operand tile, so the im2col matrix never needs to exist in HBM: producer warps gather the patches from the
+// fp32 NCHW input (a few MB, L2-resident), split them into bf16 copies in registers and write them straight into shared
+// memory in the 128-byte-swizzled layout tcgen05.mma reads (generic-proxy stores, fence.proxy.async, mbarrier).  The
+// layer then costs its output traffic: the CUDA-core kernels above spend ~4600 issue slots per 128 pixels, these ~1000.
+//
+//   forward   D[128 pixels, F] = A[128, K] * B[F, K]^T, one k-step per tile (only the ceil(K/16) slices that hold
+//             data are multiplied).  The filters are converted once per CTA and stay in shared memory.  4 producer
+//             warps (thread = pixel), 1 MMA warp, 4 epilogue warps (bias + activation, coalesced NCHW store); A ring
+//             and double-buffered TMEM accumulator as in the TMA kernel.
+//   dW        D[F (padded to 128), 64] += dz[64 pixels, F]^T * patches[64 pixels, 64], both operands MN-major (rows =
+//             pixels), accumulated in ONE TMEM tile per CTA over all its pixel steps; dz is formed by the producers
+//             from the stored gradient or from (pooled gradient, pool mask, layer output).  A column of ones in the
+//             patch matrix yields the bias gradient.  Per-CTA partial tiles are reduced in block order.
+// Every mbarrier wait is bounded (status word as for the other tensor-core kernels).
+constexpr int FT_PRODUCERS = 512;         // 16 producer warps: with one warp per scheduler the gathers' latency was the whole cost
+constexpr int FTC_THREADS = FT_PRODUCERS + 32 + 128;      // forward: warps 0-15 producers, 16 MMA, 17-20 epilogue
+constexpr int FTW_THREADS = FT_PRODUCERS + 32;            // dW: warps 0-15 producers, 16 MMA; warps 0-3 drain the accumulator at the end
+
+__device__ __forceinline__ uint32_t sw128_offset(int row, int chunk) {        // 16-byte chunk `chunk` of 128-byte row `row`
+    return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+template <int NS>
+__device__ __forceinline__ void store_copies(unsigned char *base, uint32_t copy_stride, uint32_t off, float *v) {
+    *reinterpret_cast<uint4 *>(base + off) = split_chunk(v);
+    if (NS >= 2) *reinterpret_cast<uint4 *>(base + copy_stride + off) = split_chunk(v);
+    if (NS >= 3) *reinterpret_cast<uint4 *>(base + 2 * copy_stride + off) = split_chunk(v);
+}
+
+template <int NS>
+__global__ void __launch_bounds__(FTC_THREADS, 1)
+first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, StorePixelRows cs, FirstGeom g,
+                    const float *__restrict__ bias, int act, int bn, int stages, int nslices, int *status) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 4];      // full[8], empty[8], tfull[2], tempty[2]
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    __shared__ int koff[64], krs[64];
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t a_bytes = TC_BM * 128, b_bytes = (uint32_t)bn * 128;
+    unsigned char *b_base = smem;                                           // NS filter tiles
+    unsigned char *a_base = smem + (size_t)NS * b_bytes;                    // stages x NS pixel tiles
+    unsigned char *epi_smem = a_base + (size_t)stages * NS * a_bytes;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[8]), tfull0 = smem_u32(&bars[16]), tempty0 = smem_u32(&bars[18]);
+    const uint32_t tmem_cols = (uint32_t)(2 * bn < 32 ? 32 : 2 * bn);
+    const int chunks = nslices * 2;                                         // 16-byte chunks of a row that carry data
+
+    if (t == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, FT_PRODUCERS / 32); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        fence_mbar_init();
+    }
+    fill_patch_table(koff, krs, g, 64);
+    // filters: row f, k along the row; rows past F and k past K are zero
+    for (int e = t; e < bn * chunks; e += FTC_THREADS) {
+        const int row = e / chunks, kg = e - row * chunks;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) { int k = kg * 8 + i; v[i] = (row < g.F && k < g.K) ? __ldg(Wt + (long long)row * g.K + k) : 0.f; }
+        store_copies<NS>(b_base, b_bytes, sw128_offset(row, kg), v);
+    }
+    fence_async_smem();
+    constexpr int MMA_WARP = FT_PRODUCERS / 32;
+    if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+
+    const int P = g.OH * g.OW;
+    const long long pixels = (long long)g.NB * P;
+    const int tiles = (int)((pixels + TC_BM - 1) / TC_BM);
+
+    if (warp < MMA_WARP) {
+        // ---------------- producers: thread = (tile row = pixel, quarter of the row's chunks) ----------------
+        const int row = t & 127, cg = t >> 7;
+        // the patch elements this thread gathers (chunks cg and cg + 4) are the same for every tile: keep their
+        // offsets and window positions in registers
+        int off[2][8], wr[2][8], ws[2][8];
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int k = (cg + 4 * h) * 8 + i, rs = (cg + 4 * h) < chunks ? krs[k] : -1;
+                off[h][i] = koff[k];
+                wr[h][i] = rs >= 0 ? (rs >> 16) : -(1 << 20);          // a row far outside every image: the bounds test rejects it
+                ws[h][i] = rs & 0xffff;
+            }
+        const bool second = cg + 4 < chunks;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, it++) {
+            const int s = it % stages;
+            if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
+            const int pix = tile * TC_BM + row;                  // the launcher keeps the pixel count below 2^31
+            const bool live = pix < (int)pixels;
+            const int img = live ? pix / P : 0, rem = live ? pix - img * P : 0;
+            const int oh = rem / g.OW, ow = rem - oh * g.OW;
+            const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
+            const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
+            unsigned char *a_stage = a_base + (size_t)s * NS * a_bytes;
+            float v0[8], v1[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const bool ok = (unsigned)(ih0 + wr[0][i]) < (unsigned)g.H && (unsigned)(iw0 + ws[0][i]) < (unsigned)g.W;
+                v0[i] = ok ? __ldg(xb + off[0][i]) : 0.f;
+            }
+            if (second) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const bool ok = (unsigned)(ih0 + wr[1][i]) < (unsigned)g.H && (unsigned)(iw0 + ws[1][i]) < (unsigned)g.W;
+                    v1[i] = ok ? __ldg(xb + off[1][i]) : 0.f;
+                }
+            }
+            if (cg < chunks) store_copies<NS>(a_stage, a_bytes, sw128_offset(row, cg), v0);
+            if (second) store_copies<NS>(a_stage, a_bytes, sw128_offset(row, cg + 4), v1);
+            fence_async_smem();                      // generic-proxy stores -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8 * s);        // one arrival per warp: 512 arrivals on one barrier serialise
+        }
+    } else if (warp == MMA_WARP && lane == 0) {
+        // ---------------- MMA issuer ----------------
+        const uint32_t idesc = umma_idesc_bf16(bn);
+        constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
+        const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
+        int it = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, it++) {
+            const int s = it % stages, buf = it & 1;
+            if (!mbar_wait(tempty0 + 8 * buf, (((uint32_t)it >> 1) & 1u) ^ 1u, abortp, status, 4)) break;
+            if (!mbar_wait(full0 + 8 * s, ((uint32_t)(it / stages)) & 1u, abortp, status, 2)) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
+            const uint32_t a0 = smem_u32(a_base + (size_t)s * NS * a_bytes), b0 = smem_u32(b_base);
+            uint32_t acc = 0;
+            for (int j = 0; j < nslices; j++) {
+                uint64_t da[NS], db[NS];
+#pragma unroll
+                for (int i = 0; i < NS; i++) {
+                    da[i] = umma_desc_sw128(a0 + i * a_bytes + j * 32);
+                    db[i] = umma_desc_sw128(b0 + i * b_bytes + j * 32);
+                }
+#pragma unroll
+                for (int q = 0; q < NPROD; q++) { umma_bf16(d_tmem, da[pa[q]], db[pb[q]], idesc, acc); acc = 1; }
+            }
+            umma_commit(empty0 + 8 * s);
+            umma_commit(tfull0 + 8 * buf);
+        }
+    } else if (warp > MMA_WARP) {
+        // ---------------- epilogue: warp w drains TMEM lane quarter w % 4 ----------------
+        const int q = warp & 3;
+        float *stage = reinterpret_cast<float *>(epi_smem + (size_t)(warp - MMA_WARP - 1) * EPI_WARP_SMEM);
+        int it = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, it++) {
+            const int buf = it & 1;
+            if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)it >> 1) & 1u, abortp, status, 3)) break;
+            tc_fence_after();
+            drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), tile * TC_BM + q * 32, 0, 0, bn,
+                              (int)pixels, g.F, cs, nullptr, 0, stage, bias, act);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+template <int NS>
+__global__ void __launch_bounds__(FTW_THREADS, 1)
+first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restrict__ partial, FirstGeom g, int nsteps, int stages,
+                      int ones_col, int *status) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * 8 + 1];      // full[8], empty[8], done
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    __shared__ int koff[64], krs[64];
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr uint32_t A_BYTES = 16384, B_BYTES = 8192;              // dz: two boxes of 64 filters; patches: one box of 64 values
+    const uint32_t stage_bytes = (uint32_t)NS * (A_BYTES + B_BYTES);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[8]), done = smem_u32(&bars[16]);
+
+    if (t == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, FT_PRODUCERS / 32); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(done, 1);
+        fence_mbar_init();
+    }
+    fill_patch_table(koff, krs, g, 64, ones_col != 0);
+    // chunks that no producer ever writes (filters past F, patch values past K) must read as zero
+    for (uint32_t e = t; e < (uint32_t)stages * stage_bytes / 16; e += FTW_THREADS) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
+    fence_async_smem();
+    constexpr int MMA_WARP = FT_PRODUCERS / 32;
+    if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), 64);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+
+    const int P = g.OH * g.OW, OWq = g.OW >> 1, Pq = (g.OH >> 1) * OWq;
+    const long long pixels = (long long)g.NB * P;
+    const int kchunks = (g.K + (ones_col ? 1 : 0) + 7) / 8;          // patch chunks that carry data (<= 8)
+    const int fchunks = (g.F + 7) / 8;                               // filter chunks that carry data (<= 16)
+
+    if (warp < MMA_WARP) {
+        // ---------------- producers: thread = (pixel of the step, job slot); jobs = filter chunks of dz, then patch chunks ----------------
+        const int p = t & 63, slot = t >> 6;                          // 8 slots, jobs slot and slot + 8
+        const int mode = src.dz ? 0 : (src.gp ? 2 : 1);               // stored dz | full-resolution gradient | pooled gradient
+        const float *grad = src.dz ? src.dz : (src.gp ? src.gp : src.g);
+        const bool slope = mode != 0 && src.act != SEERA_ACT_NONE;
+        // what this thread produces is the same at every step: job slot (and slot + 8) -> a filter chunk of dz or a patch chunk
+        const int job0 = slot, job1 = slot + 8;
+        const int fc0 = job0 < fchunks ? job0 : -1, fc1 = job1 < fchunks ? job1 : -1;
+        const int kc0 = (job0 >= fchunks && job0 - fchunks < kchunks) ? job0 - fchunks : -1;
+        const int kc1 = (job1 >= fchunks && job1 - fchunks < kchunks) ? job1 - fchunks : -1;
+        const int kc = kc0 >= 0 ? kc0 : kc1;                          // at most one patch chunk per thread (kchunks <= 8)
+        int off[8], wr[8], ws[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int k = (kc < 0 ? 0 : kc) * 8 + i, rs = kc < 0 ? -1 : krs[k];
+            off[i] = koff[k];
+            wr[i] = rs >= 0 ? (rs >> 16) : -(1 << 20);
+            ws[i] = rs == -2 ? -2 : (rs & 0xffff);                    // -2: the column of ones
+        }
+        int it = 0;
+        for (int step = blockIdx.x; step < nsteps; step += gridDim.x, it++) {
+            const int s = it % stages;
+            if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
+            unsigned char *a_stage = smem + (size_t)s * stage_bytes, *b_stage = a_stage + (size_t)NS * A_BYTES;
+            const int pix = step * 64 + p;
+            const bool live = pix < (int)pixels;
+            const int img = live ? pix / P : 0, rem = live ? pix - img * P : 0;
+            const int oh = rem / g.OW, ow = rem - oh * g.OW;
+            const int win = (oh >> 1) * OWq + (ow >> 1), loc = ((oh & 1) << 1) | (ow & 1);
+            const long long ybase = (long long)img * g.F * P + rem;                       // + f * P
+            const long long gbase = mode == 2 ? (long long)img * g.F * Pq + win : ybase;   // + f * (Pq or P)
+            const int gstride = mode == 2 ? Pq : P;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int fc = h ? fc1 : fc0;
+                if (fc < 0) continue;
+                // dz chunk: 8 filters of this pixel; every load of the chunk is issued before any is used
+                float dy[8], yv[8];
+                int mk[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int f = min(fc * 8 + i, g.F - 1);
+                    dy[i] = __ldg(grad + gbase + (long long)f * gstride);
+                    mk[i] = mode == 2 ? __ldg(src.mask + gbase + (long long)f * gstride) : loc;
+                    yv[i] = slope ? __ldg(src.y + ybase + (long long)f * P) : 1.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    float dz = mk[i] == loc ? dy[i] : 0.f;
+                    if (slope) dz *= first_slope(yv[i], src.act);
+                    dy[i] = (live && fc * 8 + i < g.F) ? dz : 0.f;
+                }
+                store_copies<NS>(a_stage, A_BYTES, (uint32_t)(fc >> 3) * 8192u + sw128_offset(p, fc & 7), dy);
+            }
+            if (kc >= 0) {
+                const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
+                const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const bool ok = (unsigned)(ih0 + wr[i]) < (unsigned)g.H && (unsigned)(iw0 + ws[i]) < (unsigned)g.W && ws[i] != -2;
+                    v[i] = ok ? __ldg(xb + off[i]) : ((ws[i] == -2 && live) ? 1.f : 0.f);
+                }
+                store_copies<NS>(b_stage, B_BYTES, sw128_offset(p, kc), v);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8 * s);
+        }
+    } else if (lane == 0) {
+        // ---------------- MMA issuer: one accumulator for the whole CTA ----------------
+        const uint32_t idesc = umma_idesc_bf16(64) | (1u << 15) | (1u << 16);       // both operands MN-major
+        constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
+        const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
+        uint32_t acc = 0;
+        int it = 0;
+        bool alive = true;
+        for (int step = blockIdx.x; step < nsteps && alive; step += gridDim.x, it++) {
+            const int s = it % stages;
+            alive = mbar_wait(full0 + 8 * s, ((uint32_t)(it / stages)) & 1u, abortp, status, 2);
+            if (!alive) break;
+            tc_fence_after();
+            const uint32_t a0 = smem_u32(smem + (size_t)s * stage_bytes), b0 = a0 + (uint32_t)NS * A_BYTES;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint64_t da[NS], db[NS];
+#pragma unroll
+                for (int i = 0; i < NS; i++) {
+                    da[i] = umma_desc_sw128_mn(a0 + i * A_BYTES + j * 2048, 8192);
+                    db[i] = umma_desc_sw128_mn(b0 + i * B_BYTES + j * 2048, 8192);
+                }
+#pragma unroll
+                for (int q = 0; q < NPROD; q++) { umma_bf16(tmem_base, da[pa[q]], db[pb[q]], idesc, acc); acc = 1; }
+            }
+            umma_commit(empty0 + 8 * s);
+        }
+        if (alive) umma_commit(done);
+    }
+    __syncwarp();
+    if (warp < 4) {
+        // ---------------- accumulator -> this CTA's partial tile, laid out [filter box][block][64 filters][64] ----------------
+        if (mbar_wait(done, 0, abortp, status, 3)) {
+            tc_fence_after();
+            const int f = warp * 32 + lane;
+            float *out = partial + (((long long)(f >> 6) * gridDim.x + blockIdx.x) * 64 + (f & 63)) * 64;
+#pragma unroll
+            for (int c = 0; c < 64; c += 32) {
+                float v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c, v);
+                if (f < ((g.F + 63) / 64) * 64) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4 *>(out + c + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, 64);
+}
+
+// Dynamic shared memory limit raised once per kernel instantiation and device.
+template <class K>
+static cudaError_t raise_smem_limit(K kernel, int *done_flags) {
+    const int dev = rt().device & 63;
+    if (done_flags[dev]) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+    if (e == cudaSuccess) done_flags[dev] = 1;
+    return e;
+}
+
+static bool first_tc_fwd_ok(const FirstGeom &g) { return rt().precision >= 1 && g.F <= 128 && (long long)g.NB * g.OH * g.OW < (1LL << 31) - 256; }
+static bool first_tc_wgrad_ok(const FirstGeom &g, bool want_bias) {
+    // 16 producer jobs per pixel: the 8-filter chunks of dz plus the 8-value chunks of the patch
+    return rt().precision >= 1 && (g.F + 7) / 8 + (g.K + (want_bias ? 1 : 0) + 7) / 8 <= 16 && (!want_bias || g.K < 64) && (long long)g.NB * g.OH * g.OW < (1LL << 31) - 256;
+}
+
+static int first_tc_fwd(const float *X, const float *Wt, const float *bias, float *Y, const FirstGeom &g, int act, const char *name) {
+    const int ns = precision_copies();
+    const int bn = g.F <= 32 ? 32 : (g.F <= 64 ? 64 : 128);
+    const int nslices = (g.K + 15) / 16;
+    const long long pixels = (long long)g.NB * g.OH * g.OW;
+    const int tiles = (int)((pixels + TC_BM - 1) / TC_BM);
+    const size_t fixed = (size_t)ns * bn * 128 + 4 * EPI_WARP_SMEM + 1024;
+    int stages = (int)((225 * 1024 - fixed) / ((size_t)ns * TC_BM * 128));
+    if (stages > 4) stages = 4;
+    if (stages < 2) return fail(SEERA_E_LIMIT, "%s: tile does not fit shared memory", name);
+    const size_t smem = fixed + (size_t)stages * ns * TC_BM * 128;
+    const dim3 grid((unsigned)(tiles < rt().sm_count ? tiles : rt().sm_count));
+    StorePixelRows cs{Y, g.F, g.OH * g.OW};
+    cudaStream_t st = rt().stream;
+    cudaError_t e;
+    static int f1[64], f2[64], f3[64];
+    profile_begin();
+    if (ns == 1) { e = raise_smem_limit(first_tc_fwd_kernel<1>, f1); if (e == cudaSuccess) first_tc_fwd_kernel<1><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, tc_status_word()); }
+    else if (ns == 2) { e = raise_smem_limit(first_tc_fwd_kernel<2>, f2); if (e == cudaSuccess) first_tc_fwd_kernel<2><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, tc_status_word()); }
+    else { e = raise_smem_limit(first_tc_fwd_kernel<3>, f3); if (e == cudaSuccess) first_tc_fwd_kernel<3><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, tc_status_word()); }
+    count_launch();
+    if (e == cudaSuccess) e = cudaGetLastError();
+    profile_end(2.0 * pixels * (double)g.F * g.K);
+    rt().tc_used = true;
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
+}
+
+static int first_tc_wgrad(const float *X, const DzSource &src, float *dW, float *dbias, const FirstGeom &g, const char *name) {
+    const int ns = precision_copies();
+    const long long pixels = (long long)g.NB * g.OH * g.OW;
+    const int nsteps = (int)((pixels + 63) / 64);
+    const size_t stage = (size_t)ns * (16384 + 8192);
+    int stages = (int)((220 * 1024) / stage);
+    if (stages > 4) stages = 4;
+    const size_t smem = stage * stages + 1024;
+    const int nblocks = nsteps < rt().sm_count ? nsteps : rt().sm_count;
+    const int boxes = (g.F + 63) / 64;
+    float *partial = (float *)scratch_alloc((size_t)boxes * nblocks * 64 * 64 * sizeof(float));
+    if (!partial) return SEERA_E_OOM;
+    cudaStream_t st = rt().stream;
+    cudaError_t e;
+    static int f1[64], f2[64], f3[64];
+    const int ones = dbias ? 1 : 0;
+    profile_begin();
+    if (ns == 1) { e = raise_smem_limit(first_tc_wgrad_kernel<1>, f1); if (e == cudaSuccess) first_tc_wgrad_kernel<1><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, tc_status_word()); }
+    else if (ns == 2) { e = raise_smem_limit(first_tc_wgrad_kernel<2>, f2); if (e == cudaSuccess) first_tc_wgrad_kernel<2><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, tc_status_word()); }
+    else { e = raise_smem_limit(first_tc_wgrad_kernel<3>, f3); if (e == cudaSuccess) first_tc_wgrad_kernel<3><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, tc_status_word()); }
+    count_launch();
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e == cudaSuccess) {
+        conv_first_wgrad_reduce_kernel<<<boxes * 64 * 64 / 32, 256, 0, st>>>(partial, dW, dbias, g.F, g.K, 64, nblocks);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    profile_end(2.0 * pixels * (double)g.F * g.K);
+    scratch_free(partial);
+    rt().tc_used = true;
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
+}
+
 static bool first_geom(FirstGeom &g, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     g = FirstGeom{NB, C, H, W, F, R, S, sh, sw, ph, pw, (H + 2 * ph - R) / sh + 1, (W + 2 * pw - S) / sw + 1, C * R * S};
     return g.K <= 64 && R < 32768 && S < 32768 && (F + FIRST_FC - 1) / FIRST_FC <= 65535;
@@ -328,6 +741,7 @@ int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y,
                    int ph, int pw, int sh, int sw, int act, const char *name) {
     FirstGeom g;
     if (!first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
+    if (first_tc_fwd_ok(g)) return first_tc_fwd(X, Wt, bias, Y, g, act, name);
     long long pixels = (long long)NB * g.OH * g.OW;
     unsigned chunks = (unsigned)((F + FIRST_FC - 1) / FIRST_FC);
     cudaStream_t st = rt().stream;
@@ -356,6 +770,7 @@ int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y,
 }
 
 static int first_wgrad_run(const float *X, const DzSource &src, float *dW, float *dbias, const FirstGeom &g, const char *name) {
+    if (first_tc_wgrad_ok(g, dbias != nullptr)) return first_tc_wgrad(X, src, dW, dbias, g, name);
     long long pixels = (long long)g.NB * g.OH * g.OW;
     int ntiles = (int)((pixels + FIRST_TP - 1) / FIRST_TP);
     int chunks = (g.F + FIRST_FC - 1) / FIRST_FC;
@@ -399,7 +814,7 @@ int conv_first_wgrad(const float *X, const float *dY, float *dW, int NB, int C, 
 // True when conv_first_act_wgrad can also produce the bias gradient (a spare column in the padded patch).
 bool conv_first_fuses_bias(int C, int R, int S) {
     int K = C * R * S;
-    return K <= 64 && K != 16 && K != 32 && K != 64;
+    return K <= 64 && K != 16 && K != 32 && K != 64;         // holds for the CUDA-core kernel; the tensor-core one needs only K < 64
 }
 
 // dW and dbias of y = act(conv(X, W) + b) from the gradient of y (g) or of its 2x2 / stride-2 max-pool (gp with the

@@ -43,19 +43,38 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, 
                 __syncwarp();
                 stage[lane] = (bias && n < N) ? __ldg(bias + n) : 0.f;
                 __syncwarp();
+                if (act == 1) {    // relu: the common case without a switch per value
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    const float4 b4 = *reinterpret_cast<const float4 *>(stage + j);
-                    v[j] = epilogue_act(v[j] + b4.x, act); v[j + 1] = epilogue_act(v[j + 1] + b4.y, act);
-                    v[j + 2] = epilogue_act(v[j + 2] + b4.z, act); v[j + 3] = epilogue_act(v[j + 3] + b4.w, act);
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 b4 = *reinterpret_cast<const float4 *>(stage + j);
+                        float z;
+                        z = v[j] + b4.x; v[j] = z > 0.f ? z : 0.f;
+                        z = v[j + 1] + b4.y; v[j + 1] = z > 0.f ? z : 0.f;
+                        z = v[j + 2] + b4.z; v[j + 2] = z > 0.f ? z : 0.f;
+                        z = v[j + 3] + b4.w; v[j + 3] = z > 0.f ? z : 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 b4 = *reinterpret_cast<const float4 *>(stage + j);
+                        v[j] = epilogue_act(v[j] + b4.x, act); v[j + 1] = epilogue_act(v[j + 1] + b4.y, act);
+                        v[j + 2] = epilogue_act(v[j + 2] + b4.z, act); v[j + 3] = epilogue_act(v[j + 3] + b4.w, act);
+                    }
                 }
             }
             if (own) {
-                float *q = own + (long long)(col_base + c) * sn;
+                float *q = own + (long long)(col_base + c) * sn;       // one pointer, advanced by the column stride
                 const int nvalid = N - (col_base + c);
+                if (nvalid >= 32) {
 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    if (j < nvalid) q[j * sn] = v[j];
+                    for (int j = 0; j < 32; j++) { *q = v[j]; q += sn; }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (j < nvalid) *q = v[j];
+                        q += sn;
+                    }
+                }
             }
         } else {
 #pragma unroll
