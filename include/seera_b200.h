@@ -243,9 +243,11 @@ int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, 
  * cuda_maxpool_fwd (window 2x2, stride 2, no padding); exactly one of g / gp is non-NULL.  Produces dX (may be
  * NULL), dW and dbias (may be NULL).  dz = dy * act'(y) goes straight into the bf16 copies the tensor-core
  * kernels read and is never stored in fp32; shapes those kernels do not serve run as the separate entries.
+ * y_pooled (with gp; may be NULL): that pool's output.  It equals y at each window's argmax, the only pixel of the
+ * window with a non-zero dz, so the activation slope is taken from it and y (four times larger) is not read.
  * x_shadow: kept copies of X from the forward call, or NULL. */
 int seera_conv2d_act_bwd(const float *W, const float *X, const float *y, const float *g, const float *gp, const int *pool_mask,
-                         float *dX, float *dW, float *dbias, int batch, int C, int H, int W_in, int F, int R, int S,
+                         const float *y_pooled, float *dX, float *dW, float *dbias, int batch, int C, int H, int W_in, int F, int R, int S,
                          int strideh, int stridew, int padh, int padw, int act, seera_shadow_t *x_shadow);
 /* dz = dy * act'(y), with the derivative written in terms of the OUTPUT y (relu: y > 0; sigmoid:
  * y(1-y); tanh: 1-y^2), and dbias[c] = sum of dz over that channel.  Replaces cuda_elemmult with the

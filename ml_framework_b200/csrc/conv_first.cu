@@ -54,6 +54,7 @@ struct DzSource {
     const int *mask;
     const float *y;
     int act;
+    const float *yp;            // with gp: the pool's output (y at each window's argmax), or null
 };
 __device__ __forceinline__ float first_slope(float y, int act) {
     switch (act) {
@@ -496,7 +497,7 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
 template <int NS>
 __global__ void __launch_bounds__(FTW_THREADS, 1)
 first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restrict__ partial, FirstGeom g, int nsteps, int stages,
-                      int ones_col, int *status) {
+                      int ones_col, int by_window, int *status) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * 8 + 1];      // full[8], empty[8], done
     __shared__ uint32_t tmem_base_slot;
@@ -511,7 +512,8 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
 
     if (t == 0) {
         abort_flag = 0;
-        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, FT_PRODUCERS / 32); mbar_init(empty0 + 8 * s, 1); }
+        // by_window: one group of 4 producer warps per stage; otherwise all 16 warps fill every stage
+        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, by_window ? 4 : FT_PRODUCERS / 32); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(done, 1);
         fence_mbar_init();
     }
@@ -532,7 +534,112 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
     const int kchunks = (g.K + (ones_col ? 1 : 0) + 7) / 8;          // patch chunks that carry data (<= 8)
     const int fchunks = (g.F + 7) / 8;                               // filter chunks that carry data (<= 16)
 
-    if (warp < MMA_WARP) {
+    if (warp < MMA_WARP && by_window) {
+        // ---------------- producers, pooled gradient: a step is 16 pool windows = 64 pixels, row = 4 * window + position ----------------
+        // A window's gradient, argmax index and pooled output are loaded ONCE for its four pixels (dz is zero at the other
+        // three), and each group of 4 warps works on its own step, so up to `stages` steps' loads are in flight per SM.
+        const int group = t >> 7, tg = t & 127;
+        const long long windows = (long long)g.NB * Pq;
+        const bool slope = src.act != SEERA_ACT_NONE;
+        const int wl = tg & 15, fcg = tg >> 4;                      // dz job: window of the step, filter chunks fcg and fcg + 8
+        const int pr = tg & 63, kq = tg >> 6;                       // patch jobs: row of the step, patch chunks kq, kq + 2, ...
+        int off[2][8], wr[2][8], ws[2][8];
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int kc = kq + 2 * h, k = (kc * 8 + i) & 63, rs = kc < kchunks ? krs[k] : -1;
+                off[h][i] = koff[k];
+                wr[h][i] = rs >= 0 ? (rs >> 16) : -(1 << 20);
+                ws[h][i] = rs == -2 ? -2 : (rs & 0xffff);
+            }
+        if (group < stages) {
+            for (int it = group;; it += stages) {
+                const long long step = blockIdx.x + (long long)it * gridDim.x;
+                if (step >= nsteps) break;
+                const int s = group;                                // it % stages
+                if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
+                unsigned char *a_stage = smem + (size_t)s * stage_bytes, *b_stage = a_stage + (size_t)NS * A_BYTES;
+                // ---- patch rows ----
+                {
+                    const long long wi = step * 16 + (pr >> 2);
+                    const bool live = wi < windows;
+                    const int img = live ? (int)(wi / Pq) : 0, wrem = live ? (int)(wi - (long long)img * Pq) : 0;
+                    const int ohq = wrem / OWq, owq = wrem - ohq * OWq;
+                    const int oh = 2 * ohq + ((pr >> 1) & 1), ow = 2 * owq + (pr & 1);
+                    const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
+                    const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
+                    float v0[8], v1[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const bool ok = (unsigned)(ih0 + wr[0][i]) < (unsigned)g.H && (unsigned)(iw0 + ws[0][i]) < (unsigned)g.W && ws[0][i] != -2;
+                        v0[i] = ok ? __ldg(xb + off[0][i]) : ((ws[0][i] == -2 && live) ? 1.f : 0.f);
+                    }
+                    if (kq + 2 < kchunks) {
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const bool ok = (unsigned)(ih0 + wr[1][i]) < (unsigned)g.H && (unsigned)(iw0 + ws[1][i]) < (unsigned)g.W && ws[1][i] != -2;
+                            v1[i] = ok ? __ldg(xb + off[1][i]) : ((ws[1][i] == -2 && live) ? 1.f : 0.f);
+                        }
+                    }
+                    // ---- dz rows of this thread's window: loads first ----
+                    const long long wj = step * 16 + wl;
+                    const bool wlive = wj < windows;
+                    const int wimg = wlive ? (int)(wj / Pq) : 0, wwrem = wlive ? (int)(wj - (long long)wimg * Pq) : 0;
+                    const long long wbase = (long long)wimg * g.F * Pq + wwrem;
+                    float gv[2][8], pv[2][8];
+                    int mk[2][8];
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int fc = fcg + 8 * h;
+                        if (fc < fchunks) {
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const long long q = wbase + (long long)min(fc * 8 + i, g.F - 1) * Pq;
+                                gv[h][i] = __ldg(src.gp + q);
+                                mk[h][i] = __ldg(src.mask + q);
+                                pv[h][i] = slope ? __ldg(src.yp + q) : 1.f;
+                            }
+                        }
+                    }
+                    if (kq < kchunks) store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kq), v0);
+                    if (kq + 2 < kchunks) store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kq + 2), v1);
+                    for (int kc = kq + 4; kc < kchunks; kc += 2) {          // patches longer than 32 values: tables from shared memory
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const int k = kc * 8 + i, rs = krs[k];
+                            const int ih = ih0 + (rs >> 16), iw = iw0 + (rs & 0xffff);
+                            const bool ok = live && rs >= 0 && (unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W;
+                            v[i] = ok ? __ldg(xb + koff[k]) : ((rs == -2 && live) ? 1.f : 0.f);
+                        }
+                        store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kc), v);
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const int fc = fcg + 8 * h;
+                        if (fc < fchunks) {
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                float dz = slope ? gv[h][i] * first_slope(pv[h][i], src.act) : gv[h][i];
+                                gv[h][i] = (wlive && fc * 8 + i < g.F) ? dz : 0.f;
+                            }
+#pragma unroll
+                            for (int pos = 0; pos < 4; pos++) {
+                                float v[8];
+#pragma unroll
+                                for (int i = 0; i < 8; i++) v[i] = mk[h][i] == pos ? gv[h][i] : 0.f;
+                                store_copies<NS>(a_stage, A_BYTES, (uint32_t)(fc >> 3) * 8192u + sw128_offset(4 * wl + pos, fc & 7), v);
+                            }
+                        }
+                    }
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8 * s);
+            }
+        }
+    } else if (warp < MMA_WARP) {
         // ---------------- producers: thread = (pixel of the step, job slot); jobs = filter chunks of dz, then patch chunks ----------------
         const int p = t & 63, slot = t >> 6;                          // 8 slots, jobs slot and slot + 8
         const int mode = src.dz ? 0 : (src.gp ? 2 : 1);               // stored dz | full-resolution gradient | pooled gradient
@@ -700,7 +807,9 @@ static int first_tc_fwd(const float *X, const float *Wt, const float *bias, floa
 static int first_tc_wgrad(const float *X, const DzSource &src, float *dW, float *dbias, const FirstGeom &g, const char *name) {
     const int ns = precision_copies();
     const long long pixels = (long long)g.NB * g.OH * g.OW;
-    const int nsteps = (int)((pixels + 63) / 64);
+    // pooled gradient with the pool's output at hand: steps of 16 pool windows, one producer group per stage
+    const int by_window = (src.gp && (src.yp || src.act == SEERA_ACT_NONE)) ? 1 : 0;
+    const int nsteps = by_window ? (int)(((long long)g.NB * (g.OH / 2) * (g.OW / 2) + 15) / 16) : (int)((pixels + 63) / 64);
     const size_t stage = (size_t)ns * (16384 + 8192);
     int stages = (int)((220 * 1024) / stage);
     if (stages > 4) stages = 4;
@@ -714,9 +823,9 @@ static int first_tc_wgrad(const float *X, const DzSource &src, float *dW, float 
     static int f1[64], f2[64], f3[64];
     const int ones = dbias ? 1 : 0;
     profile_begin();
-    if (ns == 1) { e = raise_smem_limit(first_tc_wgrad_kernel<1>, f1); if (e == cudaSuccess) first_tc_wgrad_kernel<1><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, tc_status_word()); }
-    else if (ns == 2) { e = raise_smem_limit(first_tc_wgrad_kernel<2>, f2); if (e == cudaSuccess) first_tc_wgrad_kernel<2><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, tc_status_word()); }
-    else { e = raise_smem_limit(first_tc_wgrad_kernel<3>, f3); if (e == cudaSuccess) first_tc_wgrad_kernel<3><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, tc_status_word()); }
+    if (ns == 1) { e = raise_smem_limit(first_tc_wgrad_kernel<1>, f1); if (e == cudaSuccess) first_tc_wgrad_kernel<1><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, by_window, tc_status_word()); }
+    else if (ns == 2) { e = raise_smem_limit(first_tc_wgrad_kernel<2>, f2); if (e == cudaSuccess) first_tc_wgrad_kernel<2><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, by_window, tc_status_word()); }
+    else { e = raise_smem_limit(first_tc_wgrad_kernel<3>, f3); if (e == cudaSuccess) first_tc_wgrad_kernel<3><<<nblocks, FTW_THREADS, smem, st>>>(X, src, partial, g, nsteps, stages, ones, by_window, tc_status_word()); }
     count_launch();
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e == cudaSuccess) {
@@ -808,7 +917,7 @@ int conv_first_wgrad(const float *X, const float *dY, float *dW, int NB, int C, 
                      int ph, int pw, const char *name) {
     FirstGeom g;
     if (!first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
-    return first_wgrad_run(X, DzSource{dY, nullptr, nullptr, nullptr, nullptr, SEERA_ACT_NONE}, dW, nullptr, g, name);
+    return first_wgrad_run(X, DzSource{dY, nullptr, nullptr, nullptr, nullptr, SEERA_ACT_NONE, nullptr}, dW, nullptr, g, name);
 }
 
 // True when conv_first_act_wgrad can also produce the bias gradient (a spare column in the padded patch).
@@ -819,13 +928,14 @@ bool conv_first_fuses_bias(int C, int R, int S) {
 
 // dW and dbias of y = act(conv(X, W) + b) from the gradient of y (g) or of its 2x2 / stride-2 max-pool (gp with the
 // pool's argmax indices): dz = dy * act'(y) is formed while the tile is staged and never stored.
-int conv_first_act_wgrad(const float *X, const float *y, const float *g, const float *gp, const int *mask, float *dW, float *dbias,
-                         int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw, int act, const char *name) {
+int conv_first_act_wgrad(const float *X, const float *y, const float *g, const float *gp, const int *mask, const float *y_pooled,
+                         float *dW, float *dbias, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw,
+                         int act, const char *name) {
     FirstGeom geo;
     if (!first_geom(geo, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
     if ((g == nullptr) == (gp == nullptr) || (gp && (!mask || (geo.OH & 1) || (geo.OW & 1))) || (act != SEERA_ACT_NONE && !y))
         return fail(SEERA_E_ARG, "%s: bad argument", name);
-    return first_wgrad_run(X, DzSource{nullptr, g, gp, mask, y, act}, dW, dbias, geo, name);
+    return first_wgrad_run(X, DzSource{nullptr, g, gp, mask, y, act, y_pooled}, dW, dbias, geo, name);
 }
 
 }  // namespace seera

@@ -350,7 +350,8 @@ __device__ __forceinline__ float slope_from_output(float y, int act) {
 }
 template <int NS>
 __global__ void __launch_bounds__(256) dz_shadow_kernel(const float *__restrict__ g, const float *__restrict__ gp, const int *__restrict__ mask,
-                                                        const float *__restrict__ y, int C, int H, int W, int Cp, int items, int ptiles,
+                                                        const float *__restrict__ y, const float *__restrict__ yp, int C, int H, int W,
+                                                        int Cp, int items, int ptiles,
                                                         int act, __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
                                                         __nv_bfloat16 *__restrict__ d2, float *__restrict__ partial) {
     // warp = group of 8 consecutive channels, lane = pixel: every load is one 128-byte line of a channel plane and each
@@ -366,6 +367,7 @@ __global__ void __launch_bounds__(256) dz_shadow_kernel(const float *__restrict_
             const int img = item / ptiles, p = (item - img * ptiles) * 32 + lane;
             if (p >= P) continue;
             float dy[8], yv[8];
+            bool sloped = false;
             if (gp) {
                 const int h = p / W, w = p - h * W;
                 const int win = (h >> 1) * Wq + (w >> 1), loc = ((h & 1) << 1) | (w & 1);
@@ -375,14 +377,21 @@ __global__ void __launch_bounds__(256) dz_shadow_kernel(const float *__restrict_
                     const long long q = ((long long)img * C + min(cb + i, C - 1)) * Pq + win;
                     mk[i] = __ldg(mask + q);
                     dy[i] = __ldg(gp + q);
+                    // the pool's output is y at the window's argmax, the only pixel of the window where dz is not zero
+                    yv[i] = (yp && act != SEERA_ACT_NONE) ? __ldg(yp + q) : 1.f;
                 }
 #pragma unroll
                 for (int i = 0; i < 8; i++) dy[i] = mk[i] == loc ? dy[i] : 0.f;
+                if (yp && act != SEERA_ACT_NONE) {
+                    sloped = true;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) dy[i] *= slope_from_output(yv[i], act);
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; i++) dy[i] = __ldg(g + ((long long)img * C + min(cb + i, C - 1)) * P + p);
             }
-            if (act != SEERA_ACT_NONE) {
+            if (act != SEERA_ACT_NONE && !sloped) {
 #pragma unroll
                 for (int i = 0; i < 8; i++) yv[i] = __ldg(y + ((long long)img * C + min(cb + i, C - 1)) * P + p);
 #pragma unroll
@@ -638,8 +647,8 @@ int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, 
 }
 
 // dz = dy * act'(y) as channels-last copies plus dbias; dy = g, or gp through a 2x2 / stride-2 max-pool mask.
-static int make_dz_shadow(const float *g, const float *gp, const int *mask, const float *y, float *dbias, int NB, int C, int H, int W,
-                          int act, int ns, NhwcShadow &out) {
+static int make_dz_shadow(const float *g, const float *gp, const int *mask, const float *y, const float *yp, float *dbias, int NB, int C,
+                          int H, int W, int act, int ns, NhwcShadow &out) {
     out.NB = NB; out.H = H; out.W = W; out.C = C; out.Cp = (C + 7) / 8 * 8;
     size_t bytes = (size_t)NB * H * W * out.Cp * 2;
     for (int i = 0; i < ns; i++) { out.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!out.p[i]) return SEERA_E_OOM; }
@@ -653,9 +662,9 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
     if (dbias) { partial = (float *)scratch_alloc((size_t)splits * C * sizeof(float)); if (!partial) return SEERA_E_OOM; }
     dim3 grid((unsigned)splits, (unsigned)cchunks);
     cudaStream_t st = rt().stream;
-    if (ns == 1) dz_shadow_kernel<1><<<grid, 256, 0, st>>>(g, gp, mask, y, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
-    else if (ns == 2) dz_shadow_kernel<2><<<grid, 256, 0, st>>>(g, gp, mask, y, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
-    else dz_shadow_kernel<3><<<grid, 256, 0, st>>>(g, gp, mask, y, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+    if (ns == 1) dz_shadow_kernel<1><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+    else if (ns == 2) dz_shadow_kernel<2><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+    else dz_shadow_kernel<3><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess && dbias) {
@@ -668,7 +677,7 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
 }
 
 int seera_conv2d_act_bwd(const float *Wt, const float *X, const float *y, const float *g, const float *gp, const int *pool_mask,
-                         float *dX, float *dW, float *dbias, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw,
+                         const float *y_pooled, float *dX, float *dW, float *dbias, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw,
                          int ph, int pw, int act, seera_shadow_t *x_shadow) {
     SEERA_ENSURE();
     if (!conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) || !X || !Wt || (g == nullptr) == (gp == nullptr) || (gp && !pool_mask) ||
@@ -681,13 +690,14 @@ int seera_conv2d_act_bwd(const float *Wt, const float *X, const float *y, const 
     if (keeps_shadows(NB, C, H, W, F, R, S, sh, sw, ph, pw) &&
         (sh == 1 && sw == 1 ? true : phases_supported(H, W, OH, OW, R, S, sh, sw, ph, pw) || !dX)) {
         seera_shadow dz{NhwcShadow{}, precision_copies()};
-        int s = make_dz_shadow(g, gp, pool_mask, y, dbias, NB, F, OH, OW, act, dz.ns, dz.s);
+        int s = make_dz_shadow(g, gp, pool_mask, y, gp ? y_pooled : nullptr, dbias, NB, F, OH, OW, act, dz.ns, dz.s);
         if (!s) s = tma_conv2d_bwd_kept(Wt, X, nullptr, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw, x_shadow, &dz);
         free_nhwc(dz.s);
         return s;
     }
     if (rt().precision && rt().conv_tma && conv_first_applies(C, R, S) && !dX && dW && (!dbias || conv_first_fuses_bias(C, R, S)))
-        return conv_first_act_wgrad(X, y, g, gp, pool_mask, dW, dbias, NB, C, H, W, F, R, S, sh, sw, ph, pw, act, "conv2d_act_bwd");
+        return conv_first_act_wgrad(X, y, g, gp, pool_mask, gp ? y_pooled : nullptr, dW, dbias, NB, C, H, W, F, R, S, sh, sw, ph, pw, act,
+                                    "conv2d_act_bwd");
     // composition of the separate entries
     float *dy_full = nullptr, *dz = nullptr;
     int s = SEERA_OK;

@@ -44,8 +44,9 @@ bool conv_first_applies(int C, int R, int S);
 int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F, int R, int S,
                    int ph, int pw, int sh, int sw, int act, const char *name);
 bool conv_first_fuses_bias(int C, int R, int S);
-int conv_first_act_wgrad(const float *X, const float *y, const float *g, const float *gp, const int *mask, float *dW, float *dbias,
-                         int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw, int act, const char *name);
+int conv_first_act_wgrad(const float *X, const float *y, const float *g, const float *gp, const int *mask, const float *y_pooled,
+                         float *dW, float *dbias, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw,
+                         int act, const char *name);
 int conv_first_wgrad(const float *X, const float *dY, float *dW, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw,
                      int ph, int pw, const char *name);
 }

@@ -195,9 +195,10 @@ PYBIND11_MODULE(seera_cuda, m) {
         ck(seera_maxpool2x2_fwd_s(P<const F>(x), P<F>(o), P<int>(mask), N, C, H, W, &keep));
         return reinterpret_cast<uptr>(keep); });
     m.def("shadow_free", [](uptr h) { seera_shadow_free(P<seera_shadow_t>(h)); });
-    m.def("conv2d_act_bwd", [](uptr w, uptr x, uptr y, uptr g, uptr gp, uptr mask, uptr dx, uptr dw, uptr db, int N, int C, int H, int W,
-                               int Fo, int R, int S, int sh, int sw, int ph, int pw, int act, uptr x_shadow) {
-        ck(seera_conv2d_act_bwd(P<const F>(w), P<const F>(x), P<const F>(y), P<const F>(g), P<const F>(gp), P<const int>(mask), P<F>(dx),
+    m.def("conv2d_act_bwd", [](uptr w, uptr x, uptr y, uptr g, uptr gp, uptr mask, uptr yp, uptr dx, uptr dw, uptr db, int N, int C, int H,
+                               int W, int Fo, int R, int S, int sh, int sw, int ph, int pw, int act, uptr x_shadow) {
+        ck(seera_conv2d_act_bwd(P<const F>(w), P<const F>(x), P<const F>(y), P<const F>(g), P<const F>(gp), P<const int>(mask),
+                                P<const F>(yp), P<F>(dx),
                                 P<F>(dw), P<F>(db), N, C, H, W, Fo, R, S, sh, sw, ph, pw, act, P<seera_shadow_t>(x_shadow))); });
     m.def("act_bias_bwd", [](uptr dy, uptr y, uptr dz, uptr db, int n, int ch, int inner, int act) {
         ck(seera_act_bias_bwd(P<const F>(dy), P<const F>(y), P<F>(dz), P<F>(db), n, ch, inner, act)); });

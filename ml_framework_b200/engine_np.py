@@ -164,7 +164,7 @@ def conv2d_bias_act(X, W, bias, sh, sw, ph, pw, act):
         return d.down(o, (N, F, OH, OW))
 
 
-def conv2d_layer_roundtrip(X, W, bias, sh, sw, ph, pw, act, g=None, gp=None, need_dx=True, keep=True):
+def conv2d_layer_roundtrip(X, W, bias, sh, sw, ph, pw, act, g=None, gp=None, need_dx=True, keep=True, pass_pooled=True):
     """Forward y = act(conv2d(X, W) + bias) with the input's copies kept, then seera_conv2d_act_bwd from g (gradient of
     y) or gp (gradient of maxpool2x2(y); the pool runs here to get its mask).  Returns y, pooled, dX, dW, dbias."""
     X, W = np.asarray(X, np.float32), np.asarray(W, np.float32)
@@ -186,7 +186,8 @@ def conv2d_layer_roundtrip(X, W, bias, sh, sw, ph, pw, act, g=None, gp=None, nee
         dw, db = d.new(W.size), d.new(F)
         try:
             capi.check(L.seera_conv2d_act_bwd(wd, xd, y, d.up(g) if g is not None else None, d.up(gp) if gp is not None else None,
-                                              mask, dx, dw, db, N, C, H, Wi, F, KH, KW, sh, sw, ph, pw, act, kept))
+                                              mask, pooled if pass_pooled else None, dx, dw, db, N, C, H, Wi, F, KH, KW, sh, sw,
+                                              ph, pw, act, kept))
         finally:
             L.seera_shadow_free(kept)
         return (d.down(y, (N, F, OH, OW)), d.down(pooled, (N, F, OH // 2, OW // 2)) if gp is not None else None,

@@ -136,10 +136,10 @@ class _PooledGrad:
     """Gradient of a 2x2 / stride-2 max-pool output, kept in pooled form with the pool's argmax mask.  A consumer that
     can route it itself (Conv2D backward: one kernel forms dz from it) takes it as is; anything else materialises the
     full-resolution gradient with cuda_maxpool_bwd."""
-    __slots__ = ("gp", "mask", "shape")
+    __slots__ = ("gp", "mask", "shape", "pooled")
 
-    def __init__(self, gp, mask, shape):
-        self.gp, self.mask, self.shape = gp, mask, tuple(shape)
+    def __init__(self, gp, mask, shape, pooled=None):
+        self.gp, self.mask, self.shape, self.pooled = gp, mask, tuple(shape), pooled
 
     def materialize(self):
         N, C, H, W = self.shape
@@ -420,10 +420,10 @@ class Conv2D(_ParamLayer):
             dw = self.weights._grad_target()
             dx = _new(xv.shape) if need_dx else None
             if isinstance(g, _PooledGrad):
-                gptr, gpptr, mptr = 0, g.gp.main_ptr, g.mask.main_ptr
+                gptr, gpptr, mptr, ypptr = 0, g.gp.main_ptr, g.mask.main_ptr, g.pooled.main_ptr if g.pooled is not None else 0
             else:
-                gptr, gpptr, mptr = g.main_ptr, 0, 0
-            sc.conv2d_act_bwd(W.main_ptr, xv.main_ptr, y.main_ptr, gptr, gpptr, mptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
+                gptr, gpptr, mptr, ypptr = g.main_ptr, 0, 0, 0
+            sc.conv2d_act_bwd(W.main_ptr, xv.main_ptr, y.main_ptr, gptr, gpptr, mptr, ypptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
                               db.main_ptr, N, C, H, Wd, F, KH, KW, sh, sw, ph, pw, code, kept.h or (given.h if given else 0))
             kept.release()
             if given:
@@ -524,7 +524,7 @@ class MaxPool2D(Layer):
 
         def backward(g):
             if tiles_exactly and getattr(x, "_takes_pooled", False):
-                x._accumulate(_PooledGrad(g, mask, xv.shape))      # the producer routes it through the mask itself
+                x._accumulate(_PooledGrad(g, mask, xv.shape, y))   # the producer routes it through the mask itself
                 return
             dx = _new(xv.shape)
             sc.cuda_maxpool_bwd(g.main_ptr, mask.main_ptr, dx.main_ptr, N, C, H, W, KH, KW, ph, pw, sh, sw)

@@ -308,7 +308,7 @@ def maxpool2x2_fwd_s(x, o, mask, N, C, H, W):
 def shadow_free(h): pass
 
 
-def conv2d_act_bwd(w, x, y, g, gp, mask, dx, dw, db, N, C, H, W, Fo, R, S, sh, sw, ph, pw, act, x_shadow):
+def conv2d_act_bwd(w, x, y, g, gp, mask, yp, dx, dw, db, N, C, H, W, Fo, R, S, sh, sw, ph, pw, act, x_shadow):
     OH, OW = (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1
     n = N * Fo * OH * OW
     full = np.empty(n, np.float32)
