@@ -292,7 +292,11 @@ def run_gpu(args, work):
     peaks = _peaks()
     sc.profile_enable(1 if rank == 0 else 0)
     for _ in range(min(args.steps, 5)):             # every rank steps (collectives), rank 0 records
+        # hold the stream for about two steps first: the step's launches then queue up and run back to back, so the
+        # events around each contraction time the kernel and not the host's gaps between eager launches
+        sc.stream_delay(int(min(100000, max(2000, 2000 * ms / args.steps))))
         tr.step(Xd, Yd)
+        sc.stream_synchronize()
     sc.stream_synchronize()
     cnt, pms, pfl = sc.profile_read()
     sc.profile_enable(0)

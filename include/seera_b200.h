@@ -110,6 +110,9 @@ int   seera_upload(void *dev, const void *host, size_t n_bytes);      /* upload 
  * runs).  Host memory must be page-locked (seera_host_alloc_pinned).  The two fences order "everything queued so
  * far" on one stream before everything queued later on the other.  Not usable while a graph is being captured.
  * No counterpart in the reference, which copies synchronously on the default stream (cuda_bindings.cpp:98-170). */
+/* Measurement aid: occupies the compute stream for about `microseconds` (0..100000) with a one-thread kernel, so that
+ * work enqueued right after it queues up and runs back to back; bench.py uses it before its per-kernel event pass. */
+int   seera_stream_delay(int microseconds);
 int   seera_copy_upload(void *dev, const void *pinned_host, size_t n_bytes);
 int   seera_copy_download(void *pinned_host, const void *dev, size_t n_bytes);
 int   seera_copy_wait_compute(void);     /* later copy-stream work waits for the compute stream's current tail */

@@ -337,6 +337,23 @@ int seera_upload(void *dev, const void *host, size_t n_bytes) {
     // `host` at once; from pinned memory the copy is asynchronous and ordered on the stream.
     return check_cuda(cudaMemcpyAsync(dev, host, n_bytes, cudaMemcpyHostToDevice, rt().stream), "cudaMemcpyAsync h2d");
 }
+// ---- measurement aid: hold the stream for a while so that the launches that follow queue up behind it ---------
+// Events recorded around a kernel in an eagerly launched sequence otherwise also time the host's gaps between launches.
+__global__ void stream_delay_kernel(long long clocks) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < clocks) {}          // bounded by `clocks` (at most 0.1 s worth, see below)
+}
+int seera_stream_delay(int microseconds) {
+    SEERA_ENSURE();
+    if (microseconds < 0 || microseconds > 100000) return fail(SEERA_E_ARG, "stream_delay: 0..100000 microseconds");
+    if (rt().capturing) return fail(SEERA_E_ARG, "stream_delay: not allowed while a graph is being captured");
+    int khz = 0;
+    if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, rt().device) != cudaSuccess || khz <= 0) { cudaGetLastError(); khz = 1500000; }
+    stream_delay_kernel<<<1, 1, 0, rt().stream>>>((long long)microseconds * khz / 1000);
+    SEERA_LAUNCH_CHECK("stream_delay");
+    return SEERA_OK;
+}
+
 // ---- copy stream: host<->device transfers that overlap the compute stream -----------------------------------
 // One extra non-blocking stream per process.  Ordering against the compute stream is explicit: each fence records an
 // event at the current tail of one stream and makes the other wait for it, so "everything queued so far" is the unit.

@@ -166,6 +166,7 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("pool_bytes_reserved", []() { return seera_pool_bytes_reserved(); });
     m.def("upload_f32", [](uptr dst, arr_f a) { ck(seera_upload(P<void>(dst), a.data(), (size_t)a.size() * 4)); });
     m.def("upload_from_host_ptr", [](uptr dst, uptr host, size_t nbytes) { ck(seera_upload(P<void>(dst), P<const void>(host), nbytes)); });
+    m.def("stream_delay", [](int us) { ck(seera_stream_delay(us)); });
     m.def("copy_upload", [](uptr dst, uptr host, size_t nbytes) { ck(seera_copy_upload(P<void>(dst), P<const void>(host), nbytes)); });
     m.def("copy_download", [](uptr host, uptr src, size_t nbytes) { ck(seera_copy_download(P<void>(host), P<const void>(src), nbytes)); });
     m.def("copy_wait_compute", []() { ck(seera_copy_wait_compute()); });
