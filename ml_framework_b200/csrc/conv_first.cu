@@ -340,7 +340,9 @@ static int resident_blocks(K kernel) {
 // Every mbarrier wait is bounded (status word as for the other tensor-core kernels).
 constexpr int FT_PRODUCERS = 512;         // 16 producer warps: with one warp per scheduler the gathers' latency was the whole cost
 constexpr int FTC_THREADS = FT_PRODUCERS + 32 + 128;      // forward: warps 0-15 producers, 16 MMA, 17-20 epilogue
-constexpr int FTW_THREADS = FT_PRODUCERS + 32;            // dW: warps 0-15 producers, 16 MMA; warps 0-3 drain the accumulator at the end
+constexpr int FTW_PRODUCERS = 768;        // dW: 24 producer warps (the conversion work per pixel is several times the forward's)
+constexpr int FTW_THREADS = FTW_PRODUCERS + 32;           // warps 0-23 producers, 24 MMA; warps 0-3 drain the accumulator at the end
+constexpr int FTW_SLOTS = FTW_PRODUCERS / 64;             // pixel-ordered producers: job slots per pixel
 
 __device__ __forceinline__ uint32_t sw128_offset(int row, int chunk) {        // 16-byte chunk `chunk` of 128-byte row `row`
     return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
@@ -509,11 +511,12 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
     constexpr uint32_t A_BYTES = 16384, B_BYTES = 8192;              // dz: two boxes of 64 filters; patches: one box of 64 values
     const uint32_t stage_bytes = (uint32_t)NS * (A_BYTES + B_BYTES);
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[8]), done = smem_u32(&bars[16]);
+    constexpr int MMA_WARP = FTW_PRODUCERS / 32;
 
     if (t == 0) {
         abort_flag = 0;
-        // by_window: one group of 4 producer warps per stage; otherwise all 16 warps fill every stage
-        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, by_window ? 4 : FT_PRODUCERS / 32); mbar_init(empty0 + 8 * s, 1); }
+        // by_window: two groups of 4 producer warps per stage (dz rows, patch rows); otherwise all producer warps fill every stage
+        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, by_window ? 8 : FTW_PRODUCERS / 32); mbar_init(empty0 + 8 * s, 1); }
         mbar_init(done, 1);
         fence_mbar_init();
     }
@@ -521,7 +524,6 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
     // chunks that no producer ever writes (filters past F, patch values past K) must read as zero
     for (uint32_t e = t; e < (uint32_t)stages * stage_bytes / 16; e += FTW_THREADS) reinterpret_cast<uint4 *>(smem)[e] = make_uint4(0, 0, 0, 0);
     fence_async_smem();
-    constexpr int MMA_WARP = FT_PRODUCERS / 32;
     if (warp == MMA_WARP) tmem_alloc(smem_u32(&tmem_base_slot), 64);
     tc_fence_before();
     __syncthreads();
@@ -537,102 +539,101 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
     if (warp < MMA_WARP && by_window) {
         // ---------------- producers, pooled gradient: a step is 16 pool windows = 64 pixels, row = 4 * window + position ----------------
         // A window's gradient, argmax index and pooled output are loaded ONCE for its four pixels (dz is zero at the other
-        // three), and each group of 4 warps works on its own step, so up to `stages` steps' loads are in flight per SM.
-        const int group = t >> 7, tg = t & 127;
+        // three).  Stage s is filled by producer groups 2s (dz rows) and 2s + 1 (patch rows), 4 warps each, so up to
+        // `stages` steps are being loaded and converted at once: a single warp converts slowly (dependent ALU chains), the
+        // throughput comes from having many of them (at most 3 stages x 2 groups = 24 warps).
+        const int group = t >> 7, tg = t & 127, s = group >> 1;
         const long long windows = (long long)g.NB * Pq;
-        const bool slope = src.act != SEERA_ACT_NONE;
-        const int wl = tg & 15, fcg = tg >> 4;                      // dz job: window of the step, filter chunks fcg and fcg + 8
-        const int pr = tg & 63, kq = tg >> 6;                       // patch jobs: row of the step, patch chunks kq, kq + 2, ...
-        int off[2][8], wr[2][8], ws[2][8];
-#pragma unroll
-        for (int h = 0; h < 2; h++)
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int kc = kq + 2 * h, k = (kc * 8 + i) & 63, rs = kc < kchunks ? krs[k] : -1;
-                off[h][i] = koff[k];
-                wr[h][i] = rs >= 0 ? (rs >> 16) : -(1 << 20);
-                ws[h][i] = rs == -2 ? -2 : (rs & 0xffff);
-            }
-        if (group < stages) {
-            for (int it = group;; it += stages) {
+        if (s < stages && (group & 1) == 0) {
+            // ---- dz rows: thread = (window of the step, filter chunks fcg and fcg + 8) ----
+            const bool slope = src.act != SEERA_ACT_NONE;
+            const int wl = tg & 15, fcg = tg >> 4;
+            for (int it = s;; it += stages) {
                 const long long step = blockIdx.x + (long long)it * gridDim.x;
                 if (step >= nsteps) break;
-                const int s = group;                                // it % stages
                 if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
-                unsigned char *a_stage = smem + (size_t)s * stage_bytes, *b_stage = a_stage + (size_t)NS * A_BYTES;
-                // ---- patch rows ----
-                {
-                    const long long wi = step * 16 + (pr >> 2);
-                    const bool live = wi < windows;
-                    const int img = live ? (int)(wi / Pq) : 0, wrem = live ? (int)(wi - (long long)img * Pq) : 0;
-                    const int ohq = wrem / OWq, owq = wrem - ohq * OWq;
-                    const int oh = 2 * ohq + ((pr >> 1) & 1), ow = 2 * owq + (pr & 1);
-                    const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
-                    const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
-                    float v0[8], v1[8];
+                unsigned char *a_stage = smem + (size_t)s * stage_bytes;
+                const long long wj = step * 16 + wl;
+                const bool wlive = wj < windows;
+                const int wimg = wlive ? (int)(wj / Pq) : 0, wwrem = wlive ? (int)(wj - (long long)wimg * Pq) : 0;
+                const long long wbase = (long long)wimg * g.F * Pq + wwrem;
+                for (int fc = fcg; fc < fchunks; fc += 8) {
+                    float gv[8], pv[8];
+                    int mk[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {        // every load of the chunk is issued before any is used
+                        const long long q = wbase + (long long)min(fc * 8 + i, g.F - 1) * Pq;
+                        gv[i] = __ldg(src.gp + q);
+                        mk[i] = __ldg(src.mask + q);
+                        pv[i] = slope ? __ldg(src.yp + q) : 1.f;
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
-                        const bool ok = (unsigned)(ih0 + wr[0][i]) < (unsigned)g.H && (unsigned)(iw0 + ws[0][i]) < (unsigned)g.W && ws[0][i] != -2;
-                        v0[i] = ok ? __ldg(xb + off[0][i]) : ((ws[0][i] == -2 && live) ? 1.f : 0.f);
+                        const float dz = slope ? gv[i] * first_slope(pv[i], src.act) : gv[i];
+                        gv[i] = (wlive && fc * 8 + i < g.F) ? dz : 0.f;
                     }
-                    if (kq + 2 < kchunks) {
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            const bool ok = (unsigned)(ih0 + wr[1][i]) < (unsigned)g.H && (unsigned)(iw0 + ws[1][i]) < (unsigned)g.W && ws[1][i] != -2;
-                            v1[i] = ok ? __ldg(xb + off[1][i]) : ((ws[1][i] == -2 && live) ? 1.f : 0.f);
-                        }
-                    }
-                    // ---- dz rows of this thread's window: loads first ----
-                    const long long wj = step * 16 + wl;
-                    const bool wlive = wj < windows;
-                    const int wimg = wlive ? (int)(wj / Pq) : 0, wwrem = wlive ? (int)(wj - (long long)wimg * Pq) : 0;
-                    const long long wbase = (long long)wimg * g.F * Pq + wwrem;
-                    float gv[2][8], pv[2][8];
-                    int mk[2][8];
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int fc = fcg + 8 * h;
-                        if (fc < fchunks) {
-#pragma unroll
-                            for (int i = 0; i < 8; i++) {
-                                const long long q = wbase + (long long)min(fc * 8 + i, g.F - 1) * Pq;
-                                gv[h][i] = __ldg(src.gp + q);
-                                mk[h][i] = __ldg(src.mask + q);
-                                pv[h][i] = slope ? __ldg(src.yp + q) : 1.f;
-                            }
-                        }
-                    }
-                    if (kq < kchunks) store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kq), v0);
-                    if (kq + 2 < kchunks) store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kq + 2), v1);
-                    for (int kc = kq + 4; kc < kchunks; kc += 2) {          // patches longer than 32 values: tables from shared memory
+                    for (int pos = 0; pos < 4; pos++) {
                         float v[8];
 #pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            const int k = kc * 8 + i, rs = krs[k];
-                            const int ih = ih0 + (rs >> 16), iw = iw0 + (rs & 0xffff);
-                            const bool ok = live && rs >= 0 && (unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W;
-                            v[i] = ok ? __ldg(xb + koff[k]) : ((rs == -2 && live) ? 1.f : 0.f);
-                        }
-                        store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kc), v);
+                        for (int i = 0; i < 8; i++) v[i] = mk[i] == pos ? gv[i] : 0.f;
+                        store_copies<NS>(a_stage, A_BYTES, (uint32_t)(fc >> 3) * 8192u + sw128_offset(4 * wl + pos, fc & 7), v);
                     }
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full0 + 8 * s);
+            }
+        } else if (s < stages) {
+            // ---- patch rows: thread = (row of the step, patch chunks kq, kq + 2, ...) ----
+            const int pr = tg & 63, kq = tg >> 6;
+            int off[2][8], wr[2][8], ws[2][8];
 #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int fc = fcg + 8 * h;
-                        if (fc < fchunks) {
+            for (int h = 0; h < 2; h++)
 #pragma unroll
-                            for (int i = 0; i < 8; i++) {
-                                float dz = slope ? gv[h][i] * first_slope(pv[h][i], src.act) : gv[h][i];
-                                gv[h][i] = (wlive && fc * 8 + i < g.F) ? dz : 0.f;
-                            }
+                for (int i = 0; i < 8; i++) {
+                    const int kc = kq + 2 * h, k = (kc * 8 + i) & 63, rs = kc < kchunks ? krs[k] : -1;
+                    off[h][i] = koff[k];
+                    wr[h][i] = rs >= 0 ? (rs >> 16) : -(1 << 20);
+                    ws[h][i] = rs == -2 ? -2 : (rs & 0xffff);
+                }
+            for (int it = s;; it += stages) {
+                const long long step = blockIdx.x + (long long)it * gridDim.x;
+                if (step >= nsteps) break;
+                if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
+                unsigned char *b_stage = smem + (size_t)s * stage_bytes + (size_t)NS * A_BYTES;
+                const long long wi = step * 16 + (pr >> 2);
+                const bool live = wi < windows;
+                const int img = live ? (int)(wi / Pq) : 0, wrem = live ? (int)(wi - (long long)img * Pq) : 0;
+                const int ohq = wrem / OWq, owq = wrem - ohq * OWq;
+                const int oh = 2 * ohq + ((pr >> 1) & 1), ow = 2 * owq + (pr & 1);
+                const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
+                const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
+                float v0[8], v1[8];
 #pragma unroll
-                            for (int pos = 0; pos < 4; pos++) {
-                                float v[8];
+                for (int i = 0; i < 8; i++) {
+                    const bool ok = (unsigned)(ih0 + wr[0][i]) < (unsigned)g.H && (unsigned)(iw0 + ws[0][i]) < (unsigned)g.W && ws[0][i] != -2;
+                    v0[i] = ok ? __ldg(xb + off[0][i]) : ((ws[0][i] == -2 && live) ? 1.f : 0.f);
+                }
+                if (kq + 2 < kchunks) {
 #pragma unroll
-                                for (int i = 0; i < 8; i++) v[i] = mk[h][i] == pos ? gv[h][i] : 0.f;
-                                store_copies<NS>(a_stage, A_BYTES, (uint32_t)(fc >> 3) * 8192u + sw128_offset(4 * wl + pos, fc & 7), v);
-                            }
-                        }
+                    for (int i = 0; i < 8; i++) {
+                        const bool ok = (unsigned)(ih0 + wr[1][i]) < (unsigned)g.H && (unsigned)(iw0 + ws[1][i]) < (unsigned)g.W && ws[1][i] != -2;
+                        v1[i] = ok ? __ldg(xb + off[1][i]) : ((ws[1][i] == -2 && live) ? 1.f : 0.f);
                     }
+                }
+                if (kq < kchunks) store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kq), v0);
+                if (kq + 2 < kchunks) store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kq + 2), v1);
+                for (int kc = kq + 4; kc < kchunks; kc += 2) {          // patches longer than 32 values: tables from shared memory
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int k = kc * 8 + i, rs = krs[k];
+                        const int ih = ih0 + (rs >> 16), iw = iw0 + (rs & 0xffff);
+                        const bool ok = live && rs >= 0 && (unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W;
+                        v[i] = ok ? __ldg(xb + koff[k]) : ((rs == -2 && live) ? 1.f : 0.f);
+                    }
+                    store_copies<NS>(b_stage, B_BYTES, sw128_offset(pr, kc), v);
                 }
                 fence_async_smem();
                 __syncwarp();
@@ -640,25 +641,12 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
             }
         }
     } else if (warp < MMA_WARP) {
-        // ---------------- producers: thread = (pixel of the step, job slot); jobs = filter chunks of dz, then patch chunks ----------------
-        const int p = t & 63, slot = t >> 6;                          // 8 slots, jobs slot and slot + 8
+        // ---------------- producers, stored or full-resolution gradient: thread = (pixel of the step, job slot) ----------------
+        // Jobs per pixel: the 8-filter chunks of dz first, then the 8-value chunks of the patch; slot takes jobs slot, slot + 12, ...
+        const int p = t & 63, slot = t >> 6;
         const int mode = src.dz ? 0 : (src.gp ? 2 : 1);               // stored dz | full-resolution gradient | pooled gradient
         const float *grad = src.dz ? src.dz : (src.gp ? src.gp : src.g);
         const bool slope = mode != 0 && src.act != SEERA_ACT_NONE;
-        // what this thread produces is the same at every step: job slot (and slot + 8) -> a filter chunk of dz or a patch chunk
-        const int job0 = slot, job1 = slot + 8;
-        const int fc0 = job0 < fchunks ? job0 : -1, fc1 = job1 < fchunks ? job1 : -1;
-        const int kc0 = (job0 >= fchunks && job0 - fchunks < kchunks) ? job0 - fchunks : -1;
-        const int kc1 = (job1 >= fchunks && job1 - fchunks < kchunks) ? job1 - fchunks : -1;
-        const int kc = kc0 >= 0 ? kc0 : kc1;                          // at most one patch chunk per thread (kchunks <= 8)
-        int off[8], wr[8], ws[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int k = (kc < 0 ? 0 : kc) * 8 + i, rs = kc < 0 ? -1 : krs[k];
-            off[i] = koff[k];
-            wr[i] = rs >= 0 ? (rs >> 16) : -(1 << 20);
-            ws[i] = rs == -2 ? -2 : (rs & 0xffff);                    // -2: the column of ones
-        }
         int it = 0;
         for (int step = blockIdx.x; step < nsteps; step += gridDim.x, it++) {
             const int s = it % stages;
@@ -668,42 +656,43 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
             const bool live = pix < (int)pixels;
             const int img = live ? pix / P : 0, rem = live ? pix - img * P : 0;
             const int oh = rem / g.OW, ow = rem - oh * g.OW;
-            const int win = (oh >> 1) * OWq + (ow >> 1), loc = ((oh & 1) << 1) | (ow & 1);
-            const long long ybase = (long long)img * g.F * P + rem;                       // + f * P
-            const long long gbase = mode == 2 ? (long long)img * g.F * Pq + win : ybase;   // + f * (Pq or P)
-            const int gstride = mode == 2 ? Pq : P;
+            for (int job = slot; job < fchunks + kchunks; job += FTW_SLOTS) {
+                if (job < fchunks) {
+                    const int fc = job;
+                    const int win = (oh >> 1) * OWq + (ow >> 1), loc = ((oh & 1) << 1) | (ow & 1);
+                    const long long ybase = (long long)img * g.F * P + rem;                       // + f * P
+                    const long long gbase = mode == 2 ? (long long)img * g.F * Pq + win : ybase;   // + f * (Pq or P)
+                    const int gstride = mode == 2 ? Pq : P;
+                    float dy[8], yv[8];
+                    int mk[8];
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
-                const int fc = h ? fc1 : fc0;
-                if (fc < 0) continue;
-                // dz chunk: 8 filters of this pixel; every load of the chunk is issued before any is used
-                float dy[8], yv[8];
-                int mk[8];
+                    for (int i = 0; i < 8; i++) {            // every load of the chunk is issued before any is used
+                        const int f = min(fc * 8 + i, g.F - 1);
+                        dy[i] = __ldg(grad + gbase + (long long)f * gstride);
+                        mk[i] = mode == 2 ? __ldg(src.mask + gbase + (long long)f * gstride) : loc;
+                        yv[i] = slope ? __ldg(src.y + ybase + (long long)f * P) : 1.f;
+                    }
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const int f = min(fc * 8 + i, g.F - 1);
-                    dy[i] = __ldg(grad + gbase + (long long)f * gstride);
-                    mk[i] = mode == 2 ? __ldg(src.mask + gbase + (long long)f * gstride) : loc;
-                    yv[i] = slope ? __ldg(src.y + ybase + (long long)f * P) : 1.f;
+                    for (int i = 0; i < 8; i++) {
+                        float dz = mk[i] == loc ? dy[i] : 0.f;
+                        if (slope) dz *= first_slope(yv[i], src.act);
+                        dy[i] = (live && fc * 8 + i < g.F) ? dz : 0.f;
+                    }
+                    store_copies<NS>(a_stage, A_BYTES, (uint32_t)(fc >> 3) * 8192u + sw128_offset(p, fc & 7), dy);
+                } else {
+                    const int kc = job - fchunks;
+                    const int ih0 = oh * g.sh - g.ph, iw0 = ow * g.sw - g.pw;
+                    const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
+                    float v[8];
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int k = kc * 8 + i, rs = krs[k];
+                        const int ih = ih0 + (rs >> 16), iw = iw0 + (rs & 0xffff);
+                        const bool ok = live && rs >= 0 && (unsigned)ih < (unsigned)g.H && (unsigned)iw < (unsigned)g.W;
+                        v[i] = ok ? __ldg(xb + koff[k]) : ((rs == -2 && live) ? 1.f : 0.f);
+                    }
+                    store_copies<NS>(b_stage, B_BYTES, sw128_offset(p, kc), v);
                 }
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    float dz = mk[i] == loc ? dy[i] : 0.f;
-                    if (slope) dz *= first_slope(yv[i], src.act);
-                    dy[i] = (live && fc * 8 + i < g.F) ? dz : 0.f;
-                }
-                store_copies<NS>(a_stage, A_BYTES, (uint32_t)(fc >> 3) * 8192u + sw128_offset(p, fc & 7), dy);
-            }
-            if (kc >= 0) {
-                const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
-                const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const bool ok = (unsigned)(ih0 + wr[i]) < (unsigned)g.H && (unsigned)(iw0 + ws[i]) < (unsigned)g.W && ws[i] != -2;
-                    v[i] = ok ? __ldg(xb + off[i]) : ((ws[i] == -2 && live) ? 1.f : 0.f);
-                }
-                store_copies<NS>(b_stage, B_BYTES, sw128_offset(p, kc), v);
             }
             fence_async_smem();
             __syncwarp();
@@ -773,8 +762,7 @@ static cudaError_t raise_smem_limit(K kernel, int *done_flags) {
 
 static bool first_tc_fwd_ok(const FirstGeom &g) { return rt().precision >= 1 && g.F <= 128 && (long long)g.NB * g.OH * g.OW < (1LL << 31) - 256; }
 static bool first_tc_wgrad_ok(const FirstGeom &g, bool want_bias) {
-    // 16 producer jobs per pixel: the 8-filter chunks of dz plus the 8-value chunks of the patch
-    return rt().precision >= 1 && (g.F + 7) / 8 + (g.K + (want_bias ? 1 : 0) + 7) / 8 <= 16 && (!want_bias || g.K < 64) && (long long)g.NB * g.OH * g.OW < (1LL << 31) - 256;
+    return rt().precision >= 1 && g.F <= 128 && (!want_bias || g.K < 64) && (long long)g.NB * g.OH * g.OW < (1LL << 31) - 256;
 }
 
 static int first_tc_fwd(const float *X, const float *Wt, const float *bias, float *Y, const FirstGeom &g, int act, const char *name) {
@@ -812,7 +800,7 @@ static int first_tc_wgrad(const float *X, const DzSource &src, float *dW, float 
     const int nsteps = by_window ? (int)(((long long)g.NB * (g.OH / 2) * (g.OW / 2) + 15) / 16) : (int)((pixels + 63) / 64);
     const size_t stage = (size_t)ns * (16384 + 8192);
     int stages = (int)((220 * 1024) / stage);
-    if (stages > 4) stages = 4;
+    if (stages > (by_window ? 3 : 4)) stages = by_window ? 3 : 4;       // by window: two groups of 4 producer warps per stage, 24 warps
     const size_t smem = stage * stages + 1024;
     const int nblocks = nsteps < rt().sm_count ? nsteps : rt().sm_count;
     const int boxes = (g.F + 63) / 64;

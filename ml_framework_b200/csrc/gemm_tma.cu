@@ -37,7 +37,7 @@ int seera_tma_matmul_bias_act(const float *A, const float *B, const float *bias,
     Shadow sa, sb;
     int s = make_shadow(A, (int)rows, K, ns, sa);
     if (!s) s = make_shadow(B, K, N, ns, sb);
-    if (!s) s = run_tma_gemm(sa, 0, sb, 1, StoreDense{C, N}, (int)rows, N, K, false, "cuda_matmul", bias, act);
+    if (!s) s = run_tma_gemm(sa, 0, sb, 1, StoreDense{C, N}, (int)rows, N, K, true, "cuda_matmul", bias, act);
     free_shadow(sa); free_shadow(sb);
     return s;
 }
@@ -52,7 +52,7 @@ int seera_tma_matmul_bwd(const float *A, const float *B, const float *dC, float 
     int s = make_shadow(dC, (int)rows, N, ns, sd);
     if (!s && dA) {      // dA[rows,K] = dC[rows,N] * B[K,N]^T : contraction over N, both operands read along their rows
         s = make_shadow(B, K, N, ns, sb);
-        if (!s) s = run_tma_gemm(sd, 0, sb, 0, StoreDense{dA, K}, (int)rows, K, N, false, "cuda_matmul_bwd(dA)");
+        if (!s) s = run_tma_gemm(sd, 0, sb, 0, StoreDense{dA, K}, (int)rows, K, N, true, "cuda_matmul_bwd(dA)");
     }
     if (!s && dB) {      // dB[K,N] = A[rows,K]^T * dC[rows,N] : contraction over rows, both operands read along their columns
         s = make_shadow(A, (int)rows, K, ns, sa);

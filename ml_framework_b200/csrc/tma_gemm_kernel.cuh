@@ -423,7 +423,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
         for (long long sp = 1; sp <= maxs || sp == 1; sp++) {
             long long per = (ksteps + sp - 1) / sp, eff = (ksteps + per - 1) / per;
             long long rounds = (tiles * eff + sms - 1) / sms;
-            long long cost = rounds * (per + 4);
+            long long cost = rounds * (per + 4) + (sp > 1 ? 8 : 0);     // a split also pays for the reduce launch
             if (best < 0 || cost < best) { best = cost; splits = (int)eff; }
         }
     }
