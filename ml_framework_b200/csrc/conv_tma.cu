@@ -349,7 +349,7 @@ __device__ __forceinline__ float slope_from_output(float y, int act) {
     }
 }
 template <int NS>
-__global__ void __launch_bounds__(256) dz_shadow_kernel(const float *__restrict__ g, const float *__restrict__ gp, const int *__restrict__ mask,
+__global__ void __launch_bounds__(256, 4) dz_shadow_kernel(const float *__restrict__ g, const float *__restrict__ gp, const int *__restrict__ mask,
                                                         const float *__restrict__ y, const float *__restrict__ yp, int C, int H, int W,
                                                         int Cp, int items, int ptiles,
                                                         int act, __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
@@ -418,6 +418,64 @@ __global__ void __launch_bounds__(256) dz_shadow_kernel(const float *__restrict_
         }
     }
 }
+// The same for a pooled gradient with the pool's output at hand, organised by pool window: lane = window, so the
+// quarter-resolution tensors (gradient, argmax index, pooled output) are read as full 128-byte lines, once per window
+// instead of once per pixel, and each thread writes the channels-last chunks of its window's four pixels.
+template <int NS>
+__global__ void __launch_bounds__(256, 4) dz_shadow_window_kernel(const float *__restrict__ gp, const int *__restrict__ mask,
+                                                                  const float *__restrict__ yp, int C, int H, int W, int Cp, int items,
+                                                                  int wtiles, int act, __nv_bfloat16 *__restrict__ d0,
+                                                                  __nv_bfloat16 *__restrict__ d1, __nv_bfloat16 *__restrict__ d2,
+                                                                  float *__restrict__ partial) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cb = blockIdx.y * 64 + warp * 8;
+    const int P = H * W, Wq = W >> 1, Pq = (H >> 1) * Wq;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+    if (cb < Cp) {
+        for (int item = blockIdx.x; item < items; item += gridDim.x) {
+            const int img = item / wtiles, q = (item - img * wtiles) * 32 + lane;
+            if (q >= Pq) continue;
+            float val[8], pv[8];
+            int mk[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const long long o = ((long long)img * C + min(cb + i, C - 1)) * Pq + q;
+                val[i] = __ldg(gp + o);
+                mk[i] = __ldg(mask + o);
+                pv[i] = act != SEERA_ACT_NONE ? __ldg(yp + o) : 1.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (act != SEERA_ACT_NONE) val[i] *= slope_from_output(pv[i], act);
+                if (cb + i >= C) val[i] = 0.f;
+                acc[i] += ((unsigned)mk[i] < 4u) ? val[i] : 0.f;
+            }
+            const int ohq = q / Wq, owq = q - ohq * Wq;
+#pragma unroll
+            for (int pos = 0; pos < 4; pos++) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = mk[i] == pos ? val[i] : 0.f;
+                const int p = (2 * ohq + (pos >> 1)) * W + 2 * owq + (pos & 1);
+                const long long o = ((long long)img * P + p) * Cp + cb;
+                *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
+                if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
+                if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+            }
+        }
+    }
+    if (partial) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float t = acc[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (lane == 0 && cb + i < C) partial[(long long)blockIdx.x * C + cb + i] = t;
+        }
+    }
+}
 // out[c] = sum over splits of partial[s][c]: one warp per channel, lanes stride over the splits, then a shuffle tree.
 __global__ void __launch_bounds__(256) dz_bias_sum_kernel(const float *__restrict__ partial, float *__restrict__ out, int channels, int splits) {
     const int lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -433,7 +491,7 @@ __global__ void __launch_bounds__(256) dz_bias_sum_kernel(const float *__restric
 // Same thread layout as dz_shadow_kernel (warp = 8 channels, lane = output pixel).  The scan order and the strict
 // comparison match cuda_maxpool_fwd, so values and window-local argmax indices are the same bit for bit.
 template <int NS>
-__global__ void __launch_bounds__(256) pool2x2_shadow_kernel(const float *__restrict__ y, float *__restrict__ out, int *__restrict__ mask,
+__global__ void __launch_bounds__(256, 4) pool2x2_shadow_kernel(const float *__restrict__ y, float *__restrict__ out, int *__restrict__ mask,
                                                              int C, int H, int W, int Cp, int items, int ptiles,
                                                              __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
                                                              __nv_bfloat16 *__restrict__ d2) {
@@ -631,7 +689,7 @@ int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, 
     size_t bytes = (size_t)N * Pq * sh.Cp * 2;
     for (int i = 0; i < ns; i++) { sh.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!sh.p[i]) { free_nhwc(sh); return SEERA_E_OOM; } }
     const int cchunks = (sh.Cp + 63) / 64;
-    int blocks = rt().sm_count * 8 / cchunks;
+    int blocks = rt().sm_count * 4 / cchunks;           // one round of resident blocks (4 per SM)
     if (blocks < 1) blocks = 1;
     if (blocks > items) blocks = (int)items;
     dim3 grid((unsigned)blocks, (unsigned)cchunks);
@@ -652,9 +710,10 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
     out.NB = NB; out.H = H; out.W = W; out.C = C; out.Cp = (C + 7) / 8 * 8;
     size_t bytes = (size_t)NB * H * W * out.Cp * 2;
     for (int i = 0; i < ns; i++) { out.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!out.p[i]) return SEERA_E_OOM; }
-    const int P = H * W, ptiles = (P + 31) / 32, cchunks = (out.Cp + 63) / 64;
+    const bool by_window = gp && (yp || act == SEERA_ACT_NONE);
+    const int P = H * W, ptiles = by_window ? ((H / 2) * (W / 2) + 31) / 32 : (P + 31) / 32, cchunks = (out.Cp + 63) / 64;
     const long long items = (long long)NB * ptiles;
-    int splits = rt().sm_count * 8 / cchunks;
+    int splits = rt().sm_count * 4 / cchunks;           // one round of resident blocks (4 per SM)
     if (splits < 1) splits = 1;
     if (splits > items) splits = (int)items;
     if (items > 0x7fffffff || cchunks > 65535) return fail(SEERA_E_LIMIT, "activation backward: tensor too large");
@@ -662,6 +721,11 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
     if (dbias) { partial = (float *)scratch_alloc((size_t)splits * C * sizeof(float)); if (!partial) return SEERA_E_OOM; }
     dim3 grid((unsigned)splits, (unsigned)cchunks);
     cudaStream_t st = rt().stream;
+    if (by_window) {
+        if (ns == 1) dz_shadow_window_kernel<1><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+        else if (ns == 2) dz_shadow_window_kernel<2><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+        else dz_shadow_window_kernel<3><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+    } else
     if (ns == 1) dz_shadow_kernel<1><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
     else if (ns == 2) dz_shadow_kernel<2><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
     else dz_shadow_kernel<3><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
