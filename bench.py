@@ -129,7 +129,8 @@ def run_reference(args, work):
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic (seeded, shapes and value ranges of the configuration)",
-            "config": {"workload": work.name, "step_sample": sample, "note": "each step is a %d-sample slice of the workload" % sample},
+            "config": {"workload": work.name, "per_gpu_batch": work.batch_size, "global_batch": work.batch_size * args.gpus, "optimizer": work.opt["kind"],
+                       "step_sample": sample, "note": "each step is a %d-sample slice of the workload" % sample},
             "cpu_baseline": {"value": v, "unit": "samples/s", "cores": cores, "kind": kind,
                              "sample": "%d steps of %d samples; %s" % (args.steps, sample, how)},
             "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -313,7 +314,7 @@ def run_gpu(args, work):
         if world == 1 and not args.no_cpu:
             cores = os.cpu_count()
             sample = CPU_SAMPLE[args.workload]
-            v, cms, kind, how = cpu_steps(work, sample, 3 if args.workload in ("c3", "c4") else 10, 1)
+            v, cms, kind, how = cpu_steps(work, sample, {"c3": 8, "c4": 12}.get(args.workload, 10), 1)      # about 10 s of CPU work
             cpu = {"value": v, "unit": "samples/s", "cores": cores, "kind": kind,
                    "sample": "%d-sample steps, %.0f ms each; %s" % (sample, cms, how)}
         line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
