@@ -73,6 +73,9 @@ int         seera_get_precision(void);
  *   "dense_tma" (default 1): in precision modes 1-3 the Dense GEMMs convert their operands to bf16 shadows once
  *       and feed the tensor cores by TMA; 0 selects the kernel that converts inside its producer warps.
  *   "conv_tma" (default 1): the same choice for the convolution family (TMA im2col).
+ *   "pool_short_patch" (default 0): let seera_conv2d_bias_act_pool_fwd_s also serve short-patch convolutions
+ *       (C*R*S <= 64).  Correct, but that kernel is bound by its epilogue warps and runs slower with the pool folded in
+ *       than followed by a separate pool.
  *   "tile_n_cap2" / "tile_n_cap3" (64, 128 or 256; defaults 128 / 128): widest accumulator tile used with two /
  *       three bf16 copies per operand; wider tiles raise the arithmetic per byte loaded but leave fewer stages. */
 int         seera_set_option(const char *name, int value);
@@ -240,6 +243,18 @@ int seera_conv2d_bias_act_fwd_s(const float *image, const float *kernel, const f
  * copies of its OUTPUT in *out_shadow for the convolution that consumes it (pass them as x_in).  Same values
  * and mask as cuda_maxpool_fwd.  *out_shadow is NULL when no copies were made (exact-fp32 mode). */
 int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, int H, int W, seera_shadow_t **out_shadow);
+/* Convolution + bias + activation + the 2x2 / stride-2 max-pool of the result in ONE launch: the tensor-core epilogue
+ * reduces each window with warp shuffles and stores only `pooled` [N,F,OH/2,OW/2], the pool's `mask` (as
+ * cuda_maxpool_fwd) and, when pooled_copies is non-NULL, the channels-last copies of `pooled` for the next convolution.
+ * The full-resolution layer output never reaches HBM; seera_conv2d_act_bwd accepts y == NULL when it is given gp, the
+ * mask and y_pooled.  Values and mask equal seera_conv2d_bias_act_fwd followed by cuda_maxpool_fwd bit for bit.
+ * Available when seera_conv2d_pool_fusable(...) returns 1 (tensor-core modes; even OH and OW; OW in {2,4,8,16}; with
+ * the option "pool_short_patch" also short patches C*R*S <= 64 with at most 128 filters); otherwise SEERA_E_LIMIT.  Replaces Conv2D.forward +
+ * MaxPool2D.forward of the reference (Seera.py:235-259, :471-480). */
+int seera_conv2d_pool_fusable(int batchN, int C, int H, int W, int F, int R, int S, int stride_h, int stride_w, int pad_h, int pad_w);
+int seera_conv2d_bias_act_pool_fwd_s(const float *image, const float *kernel, const float *bias, float *pooled, int *mask, int batchN,
+                                     int C, int H, int W, int F, int R, int S, int pad_h, int pad_w, int stride_h, int stride_w, int act,
+                                     seera_shadow_t *x_in, seera_shadow_t **x_keep, seera_shadow_t **pooled_copies);
 /* Backward of y = act(conv2d(X, W) + bias) in one call (Conv2D backward: Seera_Engine.py:571-583 activation,
  * :43-65 bias, :67-115 convolution; with gp also MaxPool2D backward, :117-131).  The gradient arrives either
  * as g = dL/dy [N,F,OH,OW] or as gp = dL/d(maxpool2x2(y)) [N,F,OH/2,OW/2] with that pool's mask from

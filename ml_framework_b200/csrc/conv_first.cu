@@ -357,7 +357,7 @@ __device__ __forceinline__ void store_copies(unsigned char *base, uint32_t copy_
 template <int NS>
 __global__ void __launch_bounds__(FTC_THREADS, 1)
 first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, StorePixelRows cs, FirstGeom g,
-                    const float *__restrict__ bias, int act, int bn, int stages, int nslices, int *status) {
+                    const float *__restrict__ bias, int act, int bn, int stages, int nslices, int pool_on, PoolOut po, int *status) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * 8 + 4];      // full[8], empty[8], tfull[2], tempty[2]
     __shared__ uint32_t tmem_base_slot;
@@ -400,7 +400,10 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
 
     const int P = g.OH * g.OW;
     const long long pixels = (long long)g.NB * P;
+    // with the pool folded in, a tile is 32 pool windows and row = 4 * window + position inside the window (the number
+    // of rows is the same: OH and OW are even)
     const int tiles = (int)((pixels + TC_BM - 1) / TC_BM);
+    const int OWq = g.OW >> 1, Pq = P >> 2;
 
     if (warp < MMA_WARP) {
         // ---------------- producers: thread = (tile row = pixel, quarter of the row's chunks) ----------------
@@ -424,8 +427,15 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
             if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
             const int pix = tile * TC_BM + row;                  // the launcher keeps the pixel count below 2^31
             const bool live = pix < (int)pixels;
-            const int img = live ? pix / P : 0, rem = live ? pix - img * P : 0;
-            const int oh = rem / g.OW, ow = rem - oh * g.OW;
+            int img, oh, ow;
+            if (pool_on) {
+                const int wi = live ? pix >> 2 : 0, wimg = wi / Pq, wrem = wi - wimg * Pq, ohq = wrem / OWq, owq = wrem - ohq * OWq;
+                img = wimg; oh = 2 * ohq + ((row >> 1) & 1); ow = 2 * owq + (row & 1);
+            } else {
+                img = live ? pix / P : 0;
+                const int rem = live ? pix - img * P : 0;
+                oh = rem / g.OW; ow = rem - oh * g.OW;
+            }
             const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
             const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
             unsigned char *a_stage = a_base + (size_t)s * NS * a_bytes;
@@ -484,8 +494,12 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
             const int buf = it & 1;
             if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)it >> 1) & 1u, abortp, status, 3)) break;
             tc_fence_after();
-            drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), tile * TC_BM + q * 32, 0, 0, bn,
-                              (int)pixels, g.F, cs, nullptr, 0, stage, bias, act);
+            if (pool_on)
+                drain_accumulator_pooled(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), tile * TC_BM + q * 32, 0, bn,
+                                         (int)pixels, g.F, bias, act, po, stage);
+            else
+                drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), tile * TC_BM + q * 32, 0, 0, bn,
+                                  (int)pixels, g.F, cs, nullptr, 0, stage, bias, act);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
@@ -765,7 +779,8 @@ static bool first_tc_wgrad_ok(const FirstGeom &g, bool want_bias) {
     return rt().precision >= 1 && g.F <= 128 && (!want_bias || g.K < 64) && (long long)g.NB * g.OH * g.OW < (1LL << 31) - 256;
 }
 
-static int first_tc_fwd(const float *X, const float *Wt, const float *bias, float *Y, const FirstGeom &g, int act, const char *name) {
+static int first_tc_fwd(const float *X, const float *Wt, const float *bias, float *Y, const FirstGeom &g, int act, const char *name,
+                        const PoolOut *pool = nullptr) {
     const int ns = precision_copies();
     const int bn = g.F <= 32 ? 32 : (g.F <= 64 ? 64 : 128);
     const int nslices = (g.K + 15) / 16;
@@ -778,13 +793,16 @@ static int first_tc_fwd(const float *X, const float *Wt, const float *bias, floa
     const size_t smem = fixed + (size_t)stages * ns * TC_BM * 128;
     const dim3 grid((unsigned)(tiles < rt().sm_count ? tiles : rt().sm_count));
     StorePixelRows cs{Y, g.F, g.OH * g.OW};
+    PoolOut po{};
+    const int pool_on = pool ? 1 : 0;
+    if (pool) { po = *pool; po.P = g.OH * g.OW; po.OW = g.OW; po.window_major = 1; }
     cudaStream_t st = rt().stream;
     cudaError_t e;
     static int f1[64], f2[64], f3[64];
     profile_begin();
-    if (ns == 1) { e = raise_smem_limit(first_tc_fwd_kernel<1>, f1); if (e == cudaSuccess) first_tc_fwd_kernel<1><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, tc_status_word()); }
-    else if (ns == 2) { e = raise_smem_limit(first_tc_fwd_kernel<2>, f2); if (e == cudaSuccess) first_tc_fwd_kernel<2><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, tc_status_word()); }
-    else { e = raise_smem_limit(first_tc_fwd_kernel<3>, f3); if (e == cudaSuccess) first_tc_fwd_kernel<3><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, tc_status_word()); }
+    if (ns == 1) { e = raise_smem_limit(first_tc_fwd_kernel<1>, f1); if (e == cudaSuccess) first_tc_fwd_kernel<1><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, pool_on, po, tc_status_word()); }
+    else if (ns == 2) { e = raise_smem_limit(first_tc_fwd_kernel<2>, f2); if (e == cudaSuccess) first_tc_fwd_kernel<2><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, pool_on, po, tc_status_word()); }
+    else { e = raise_smem_limit(first_tc_fwd_kernel<3>, f3); if (e == cudaSuccess) first_tc_fwd_kernel<3><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, pool_on, po, tc_status_word()); }
     count_launch();
     if (e == cudaSuccess) e = cudaGetLastError();
     profile_end(2.0 * pixels * (double)g.F * g.K);
@@ -833,6 +851,19 @@ static bool first_geom(FirstGeom &g, int NB, int C, int H, int W, int F, int R, 
 }
 
 bool conv_first_applies(int C, int R, int S) { return C * R * S <= 64; }
+
+// The forward with the 2x2 max-pool of its output folded into the epilogue (tensor-core variant only).
+bool conv_first_pool_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
+    FirstGeom g;
+    return first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw) && first_tc_fwd_ok(g) && g.OH >= 2 && g.OW >= 2 && !(g.OH & 1) && !(g.OW & 1);
+}
+int conv_first_pool_fwd(const float *X, const float *Wt, const float *bias, const PoolOut &pool, int NB, int C, int H, int W, int F, int R,
+                        int S, int ph, int pw, int sh, int sw, int act, const char *name) {
+    if (!conv_first_pool_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the fused pool path", name);
+    FirstGeom g;
+    first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw);
+    return first_tc_fwd(X, Wt, bias, nullptr, g, act, name, &pool);
+}
 
 int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F, int R, int S,
                    int ph, int pw, int sh, int sw, int act, const char *name) {
@@ -921,7 +952,8 @@ int conv_first_act_wgrad(const float *X, const float *y, const float *g, const f
                          int act, const char *name) {
     FirstGeom geo;
     if (!first_geom(geo, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
-    if ((g == nullptr) == (gp == nullptr) || (gp && (!mask || (geo.OH & 1) || (geo.OW & 1))) || (act != SEERA_ACT_NONE && !y))
+    if ((g == nullptr) == (gp == nullptr) || (gp && (!mask || (geo.OH & 1) || (geo.OW & 1))) ||
+        (act != SEERA_ACT_NONE && !y && !(gp && y_pooled && first_tc_wgrad_ok(geo, dbias != nullptr))))
         return fail(SEERA_E_ARG, "%s: bad argument", name);
     return first_wgrad_run(X, DzSource{nullptr, g, gp, mask, y, act, y_pooled}, dW, dbias, geo, name);
 }

@@ -209,9 +209,10 @@ struct StoreWgrad {
 
 // Y[NB, F, OH, OW] = conv(X_nhwc, weights Wk[F][tap][Cp]) with window R x S, stride, lower padding.
 static int tma_fprop(const NhwcShadow &x, const Shadow &wk, float *Y, int F, int R, int S, int sh, int sw, int ph, int pw,
-                     int OH, int OW, int ns, const char *name, const float *bias = nullptr, int act = 0) {
+                     int OH, int OW, int ns, const char *name, const float *bias = nullptr, int act = 0, const PoolOut *pool = nullptr) {
     TmaGemmParams p{};
     p.bias = bias; p.act = act;
+    if (pool) { p.pool_on = 1; p.pool = *pool; p.pool.P = OH * OW; p.pool.OW = OW; p.pool.window_major = 0; }
     p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
     p.M = x.NB * OH * OW; p.N = F;
     p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
@@ -704,6 +705,60 @@ int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, 
     return SEERA_OK;
 }
 
+// ---- convolution + bias + activation + 2x2 max-pool in one launch ----------------------------------------------------
+// In raster row order a 2x2 window must lie inside one epilogue warp's 32 rows: OW a power of two <= 16 and an even OH.
+static bool pool_in_epilogue_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
+    if (!rt().precision || !rt().conv_tma || !conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw)) return false;
+    if (conv_first_applies(C, R, S)) return rt().pool_short_patch && conv_first_pool_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw);
+    if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return false;
+    const int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
+    return OH >= 2 && !(OH & 1) && (OW == 2 || OW == 4 || OW == 8 || OW == 16);
+}
+int seera_conv2d_pool_fusable(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
+    if (ensure_init()) return 0;
+    return pool_in_epilogue_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) ? 1 : 0;
+}
+
+int seera_conv2d_bias_act_pool_fwd_s(const float *X, const float *Wt, const float *bias, float *pooled, int *mask, int NB, int C, int H,
+                                     int W, int F, int R, int S, int ph, int pw, int sh, int sw, int act, seera_shadow_t *x_in,
+                                     seera_shadow_t **x_keep, seera_shadow_t **pooled_copies) {
+    SEERA_ENSURE();
+    if (x_keep) *x_keep = nullptr;
+    if (pooled_copies) *pooled_copies = nullptr;
+    if (!X || !Wt || !pooled || !mask) return fail(SEERA_E_ARG, "conv2d_pool_fwd: bad argument");
+    if (!pool_in_epilogue_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw))
+        return fail(SEERA_E_LIMIT, "conv2d_pool_fwd: this shape or mode does not fold the pool in (see seera_conv2d_pool_fusable)");
+    const int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
+    const int ns = precision_copies();
+    PoolOut po{};
+    po.pooled = pooled; po.mask = mask;
+    NhwcShadow pc;                                     // copies of the pooled tensor, when the caller wants them
+    if (pooled_copies) {
+        pc.NB = NB; pc.H = OH / 2; pc.W = OW / 2; pc.C = F; pc.Cp = (F + 7) / 8 * 8;
+        size_t bytes = (size_t)NB * pc.H * pc.W * pc.Cp * 2;
+        for (int i = 0; i < ns; i++) { pc.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!pc.p[i]) { free_nhwc(pc); return SEERA_E_OOM; } }
+        for (int i = 0; i < 3; i++) po.copy[i] = pc.p[i];
+        po.ns = ns; po.Cp = pc.Cp;
+    }
+    int s;
+    if (conv_first_applies(C, R, S)) {
+        s = conv_first_pool_fwd(X, Wt, bias, po, NB, C, H, W, F, R, S, ph, pw, sh, sw, act, "conv2d_pool_fwd");
+    } else {
+        NhwcShadow local; Shadow wk;
+        const NhwcShadow *xs = usable(x_in, ns, NB, C, H, W);
+        s = SEERA_OK;
+        if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, local); xs = &local; }
+        if (!s) s = make_weight_shadow(Wt, F, C, R * S, (long long)C * R * S, R * S, 0, ns, wk);
+        if (!s) s = tma_fprop(*xs, wk, nullptr, F, R, S, sh, sw, ph, pw, OH, OW, ns, "conv2d_pool_fwd", bias, act, &po);
+        free_shadow(wk);
+        if (!s && x_keep && xs == &local) *x_keep = new seera_shadow{local, ns};
+        else free_nhwc(local);
+    }
+    if (!s && pooled_copies) *pooled_copies = new seera_shadow{pc, ns};
+    else free_nhwc(pc);
+    return s;
+}
+
 // dz = dy * act'(y) as channels-last copies plus dbias; dy = g, or gp through a 2x2 / stride-2 max-pool mask.
 static int make_dz_shadow(const float *g, const float *gp, const int *mask, const float *y, const float *yp, float *dbias, int NB, int C,
                           int H, int W, int act, int ns, NhwcShadow &out) {
@@ -745,7 +800,7 @@ int seera_conv2d_act_bwd(const float *Wt, const float *X, const float *y, const 
                          int ph, int pw, int act, seera_shadow_t *x_shadow) {
     SEERA_ENSURE();
     if (!conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw) || !X || !Wt || (g == nullptr) == (gp == nullptr) || (gp && !pool_mask) ||
-        (act != SEERA_ACT_NONE && !y))
+        (act != SEERA_ACT_NONE && !y && !(gp && y_pooled)))
         return fail(SEERA_E_ARG, "conv2d_act_bwd: bad argument");
     int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
     if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "conv2d_act_bwd: kernel larger than padded input");
@@ -763,21 +818,30 @@ int seera_conv2d_act_bwd(const float *Wt, const float *X, const float *y, const 
         return conv_first_act_wgrad(X, y, g, gp, pool_mask, gp ? y_pooled : nullptr, dW, dbias, NB, C, H, W, F, R, S, sh, sw, ph, pw, act,
                                     "conv2d_act_bwd");
     // composition of the separate entries
-    float *dy_full = nullptr, *dz = nullptr;
+    if (act != SEERA_ACT_NONE && !y && !(gp && y_pooled)) return fail(SEERA_E_ARG, "conv2d_act_bwd: this shape needs the layer output");
+    float *dy_full = nullptr, *dz = nullptr, *gq = nullptr;
     int s = SEERA_OK;
-    if (gp) {
-        dy_full = (float *)scratch_alloc((size_t)out_elems * sizeof(float));
-        if (!dy_full) return SEERA_E_OOM;
-        s = seera_cuda_maxpool_bwd(gp, pool_mask, dy_full, NB, F, OH, OW, 2, 2, 0, 0, 2, 2);
+    dz = (float *)scratch_alloc((size_t)out_elems * sizeof(float));
+    if (!dz) return SEERA_E_OOM;
+    if (gp && (y_pooled || act == SEERA_ACT_NONE)) {
+        // slope and bias sums at pooled resolution (the pool's output is y wherever the routed gradient is not zero),
+        // then the pool backward spreads the result
+        gq = (float *)scratch_alloc((size_t)(out_elems / 4) * sizeof(float));
+        if (!gq) s = SEERA_E_OOM;
+        if (!s) s = seera_act_bias_bwd(gp, y_pooled, gq, dbias, (int)(out_elems / 4), F, (OH / 2) * (OW / 2), act);
+        if (!s) s = seera_cuda_maxpool_bwd(gq, pool_mask, dz, NB, F, OH, OW, 2, 2, 0, 0, 2, 2);
+    } else {
+        if (gp) {
+            dy_full = (float *)scratch_alloc((size_t)out_elems * sizeof(float));
+            if (!dy_full) s = SEERA_E_OOM;
+            if (!s) s = seera_cuda_maxpool_bwd(gp, pool_mask, dy_full, NB, F, OH, OW, 2, 2, 0, 0, 2, 2);
+        }
+        if (!s) s = seera_act_bias_bwd(gp ? dy_full : g, y, dz, dbias, (int)out_elems, F, OH * OW, act);
     }
-    if (!s) {
-        dz = (float *)scratch_alloc((size_t)out_elems * sizeof(float));
-        if (!dz) s = SEERA_E_OOM;
-    }
-    if (!s) s = seera_act_bias_bwd(gp ? dy_full : g, y, dz, dbias, (int)out_elems, F, OH * OW, act);
     if (!s) s = seera_cuda_conv2d_bwd(Wt, X, dz, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw);
     if (dy_full) scratch_free(dy_full);
-    if (dz) scratch_free(dz);
+    if (gq) scratch_free(gq);
+    scratch_free(dz);
     return s;
 }
 

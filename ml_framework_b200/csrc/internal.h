@@ -38,7 +38,11 @@ int seera_tc_convT_bwd(const float *Wt, const float *X, const float *dY, float *
                        int Cout, int KH, int KW, int sh, int sw, int ph, int pw);
 }
 
+#include "tc_epilogue.cuh"
 namespace seera {
+bool conv_first_pool_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw);
+int conv_first_pool_fwd(const float *X, const float *Wt, const float *bias, const PoolOut &pool, int NB, int C, int H, int W, int F, int R,
+                        int S, int ph, int pw, int sh, int sw, int act, const char *name);
 // Direct fp32 kernels for convolutions with C*R*S <= 64 (conv_first.cu); bias may be null.
 bool conv_first_applies(int C, int R, int S);
 int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F, int R, int S,

@@ -8,6 +8,7 @@
 // No compute happens here.
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
+#include <utility>
 #include <pybind11/stl.h>
 
 #include <stdexcept>
@@ -195,6 +196,14 @@ PYBIND11_MODULE(seera_cuda, m) {
         seera_shadow_t *keep = nullptr;
         ck(seera_maxpool2x2_fwd_s(P<const F>(x), P<F>(o), P<int>(mask), N, C, H, W, &keep));
         return reinterpret_cast<uptr>(keep); });
+    m.def("conv2d_pool_fusable", [](int N, int C, int H, int W, int Fo, int R, int S, int sh, int sw, int ph, int pw) {
+        return seera_conv2d_pool_fusable(N, C, H, W, Fo, R, S, sh, sw, ph, pw) != 0; });
+    m.def("conv2d_bias_act_pool_fwd_s", [](uptr x, uptr w, uptr b, uptr pooled, uptr mask, int N, int C, int H, int W, int Fo, int R, int S,
+                                           int ph, int pw, int sh, int sw, int act, uptr x_in, bool want_copies) {
+        seera_shadow_t *keep = nullptr, *pc = nullptr;
+        ck(seera_conv2d_bias_act_pool_fwd_s(P<const F>(x), P<const F>(w), P<const F>(b), P<F>(pooled), P<int>(mask), N, C, H, W, Fo, R, S,
+                                            ph, pw, sh, sw, act, P<seera_shadow_t>(x_in), &keep, want_copies ? &pc : nullptr));
+        return std::make_pair(reinterpret_cast<uptr>(keep), reinterpret_cast<uptr>(pc)); });
     m.def("shadow_free", [](uptr h) { seera_shadow_free(P<seera_shadow_t>(h)); });
     m.def("conv2d_act_bwd", [](uptr w, uptr x, uptr y, uptr g, uptr gp, uptr mask, uptr yp, uptr dx, uptr dw, uptr db, int N, int C, int H,
                                int W, int Fo, int R, int S, int sh, int sw, int ph, int pw, int act, uptr x_shadow) {

@@ -102,4 +102,130 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, 
     }
 }
 
+// ---- epilogue with a 2x2 / stride-2 max-pool folded in --------------------------------------------------------------
+// The accumulator rows are output pixels of y = act(conv + bias); instead of storing y, each warp reduces the 2x2
+// windows that lie inside its 32 rows with shuffles and stores only the pooled value, the window-local argmax (scan
+// order (0,0), (0,1), (1,0), (1,1), strict comparison: the first maximum wins, as in cuda_maxpool_fwd) and the bf16
+// channels-last copies of the pooled tensor for the next convolution.  y itself never reaches HBM.
+// Row order: raster (row = pixel index; needs OW a power of two <= 16 so that a window's rows are lanes l, l^1, l^OW,
+// l^(OW+1)) or window-major (row = 4 * window + position; partners are lanes l^1, l^2, l^3).
+struct PoolOut {
+    float *pooled;                 // [NB, F, OH/2, OW/2]
+    int *mask;                     // same shape
+    __nv_bfloat16 *copy[3];        // [NB, (OH/2)*(OW/2), Cp] or null
+    int ns, Cp;
+    int P, OW;                     // pixels per image and width of y
+    int window_major;
+};
+
+__device__ __forceinline__ void drain_accumulator_pooled(uint32_t taddr, int row_base, int col_base, int ncols, int M, int N,
+                                                         const float *bias, int act, const PoolOut &po, float *stage) {
+    // The warp's 32 rows hold exactly 8 windows.  Each 32-column chunk gets bias + activation while lanes still hold rows,
+    // then goes through the warp's 32 x 33 staging buffer so that lanes hold COLUMNS (filters): a lane reads the four
+    // values of a window from shared memory (no shuffles), and the 8 windows of its filter are 8 consecutive floats of the
+    // pooled plane.
+    const int lane = threadIdx.x & 31;
+    const int Pq = po.P >> 2, OWq = po.OW >> 1;
+    const int d2 = po.window_major ? 2 : po.OW;
+    // first row of window w inside the warp's rows, its image and its index inside the image (the same for every lane)
+    int r0[8], wimg[8], wrem[8];
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        if (po.window_major) {
+            r0[w] = 4 * w;
+            const int wi = (row_base >> 2) + w;
+            wimg[w] = wi / Pq; wrem[w] = wi - wimg[w] * Pq;
+        } else {
+            const int wr = w / OWq, wc = w - wr * OWq;            // window row / column inside the warp's rows
+            r0[w] = 2 * wr * po.OW + 2 * wc;
+            const int m = row_base + r0[w], img = m / po.P, rem = m - img * po.P, oh = rem / po.OW, ow = rem - oh * po.OW;
+            wimg[w] = img; wrem[w] = (oh >> 1) * OWq + (ow >> 1);
+        }
+    }
+    // runs of four windows that are four consecutive floats of one pooled plane are stored as one 16-byte vector
+    bool run[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++)
+        run[h] = wimg[4 * h + 3] == wimg[4 * h] && wrem[4 * h + 3] == wrem[4 * h] + 3 && (wrem[4 * h] & 3) == 0 && (Pq & 3) == 0 &&
+                 row_base + r0[4 * h + 3] < M;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(po.pooled) | reinterpret_cast<uintptr_t>(po.mask)) & 15) == 0;
+    for (int c = 0; c < ncols; c += 32) {
+        float v[32];
+        tmem_ld32(taddr + (uint32_t)c, v);
+        const int n = col_base + c + lane;                          // this lane's filter once lanes hold columns
+        __syncwarp();
+        stage[lane] = (bias && n < N) ? __ldg(bias + n) : 0.f;
+        __syncwarp();
+        if (act == 1) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 b4 = *reinterpret_cast<const float4 *>(stage + j);
+                float z;
+                z = v[j] + b4.x; v[j] = z > 0.f ? z : 0.f;
+                z = v[j + 1] + b4.y; v[j + 1] = z > 0.f ? z : 0.f;
+                z = v[j + 2] + b4.z; v[j + 2] = z > 0.f ? z : 0.f;
+                z = v[j + 3] + b4.w; v[j + 3] = z > 0.f ? z : 0.f;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 b4 = *reinterpret_cast<const float4 *>(stage + j);
+                v[j] = epilogue_act(v[j] + b4.x, act); v[j + 1] = epilogue_act(v[j + 1] + b4.y, act);
+                v[j + 2] = epilogue_act(v[j + 2] + b4.z, act); v[j + 3] = epilogue_act(v[j + 3] + b4.w, act);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; j++) stage[lane * 33 + j] = v[j];
+        __syncwarp();
+        float mx[8];
+        int ix[8];
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const float a0 = stage[r0[w] * 33 + lane], a1 = stage[(r0[w] + 1) * 33 + lane];
+            const float a2 = stage[(r0[w] + d2) * 33 + lane], a3 = stage[(r0[w] + d2 + 1) * 33 + lane];
+            float m = -3.402823466e+38f; int id = 0;               // -FLT_MAX, strict comparisons: the first maximum wins
+            if (a0 > m) { m = a0; id = 0; }
+            if (a1 > m) { m = a1; id = 1; }
+            if (a2 > m) { m = a2; id = 2; }
+            if (a3 > m) { m = a3; id = 3; }
+            mx[w] = m; ix[w] = id;
+        }
+        if (n < N) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const long long o = ((long long)wimg[4 * h] * N + n) * Pq + wrem[4 * h];
+                if (run[h] && aligned) {
+                    *reinterpret_cast<float4 *>(po.pooled + o) = make_float4(mx[4 * h], mx[4 * h + 1], mx[4 * h + 2], mx[4 * h + 3]);
+                    *reinterpret_cast<int4 *>(po.mask + o) = make_int4(ix[4 * h], ix[4 * h + 1], ix[4 * h + 2], ix[4 * h + 3]);
+                } else {
+#pragma unroll
+                    for (int w = 4 * h; w < 4 * h + 4; w++) {
+                        if (row_base + r0[w] >= M) continue;
+                        const long long q = ((long long)wimg[w] * N + n) * Pq + wrem[w];
+                        po.pooled[q] = mx[w];
+                        po.mask[q] = ix[w];
+                    }
+                }
+            }
+        }
+        if (po.copy[0] && n < po.Cp) {                              // channels-last copies: lanes = consecutive channels
+#pragma unroll
+            for (int w = 0; w < 8; w++) {
+                if (row_base + r0[w] >= M) continue;
+                float r = n < N ? mx[w] : 0.f;
+                const long long o = ((long long)wimg[w] * Pq + wrem[w]) * po.Cp + n;
+                const __nv_bfloat16 h0 = __float2bfloat16_rn(r);
+                po.copy[0][o] = h0;
+                if (po.ns >= 2) {
+                    r -= __bfloat162float(h0);
+                    const __nv_bfloat16 h1 = __float2bfloat16_rn(r);
+                    po.copy[1][o] = h1;
+                    if (po.ns >= 3) { r -= __bfloat162float(h1); po.copy[2][o] = __float2bfloat16_rn(r); }
+                }
+            }
+        }
+    }
+}
+
 }  // namespace seera

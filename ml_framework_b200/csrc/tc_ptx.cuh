@@ -94,4 +94,18 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t packed, int odd) {
+    return __uint_as_float(odd ? (packed & 0xFFFF0000u) : (packed << 16));
+}
+// Rounds 8 values to bf16 and returns them as one 16-byte chunk; `v` is replaced by the residuals, so calling it again
+// yields the next copy of a split (hi, then mid, then lo).
+__device__ __forceinline__ uint4 split_chunk(float *v) {
+    uint4 h;
+    h.x = pack_bf16x2(v[0], v[1]); h.y = pack_bf16x2(v[2], v[3]); h.z = pack_bf16x2(v[4], v[5]); h.w = pack_bf16x2(v[6], v[7]);
+    const uint32_t w[4] = {h.x, h.y, h.z, h.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] -= bf16_bits_to_float(w[i >> 1], i & 1);
+    return h;
+}
+
 }  // namespace seera

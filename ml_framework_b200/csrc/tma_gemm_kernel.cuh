@@ -49,19 +49,6 @@ inline int make_map_2d(CUtensorMap *m, const void *base, int rows, int cols, int
 
 // ---- fp32 -> bf16 shadows -----------------------------------------------------------------------------------
 // NS = 1: hi = bf16(x).  NS = 2: plus lo = bf16(x - hi).  NS = 3: plus lo2 = bf16(x - hi - lo) (24 mantissa bits).
-__device__ __forceinline__ float bf16_bits_to_float(uint32_t packed, int odd) {
-    return __uint_as_float(odd ? (packed & 0xFFFF0000u) : (packed << 16));
-}
-// Rounds 8 values to bf16 and writes them as one 16-byte chunk; `v` is replaced by the residuals.
-__device__ __forceinline__ uint4 split_chunk(float *v) {
-    uint4 h;
-    h.x = pack_bf16x2(v[0], v[1]); h.y = pack_bf16x2(v[2], v[3]); h.z = pack_bf16x2(v[4], v[5]); h.w = pack_bf16x2(v[6], v[7]);
-    const uint32_t w[4] = {h.x, h.y, h.z, h.w};
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] -= bf16_bits_to_float(w[i >> 1], i & 1);
-    return h;
-}
-
 struct Shadow {
     __nv_bfloat16 *p[3] = {nullptr, nullptr, nullptr};
     int rows = 0, cols = 0, ld = 0;
@@ -170,6 +157,8 @@ struct TmaGemmParams {
     int *status;
     const float *bias;       // per-column bias added before the store, or null
     int act;                 // activation applied before the store (0 = none)
+    int pool_on;             // 1: rows are pixels of a layer output that is only consumed through a 2x2 max-pool: store that instead
+    PoolOut pool;
 };
 
 constexpr int TG_THREADS = 192;
@@ -358,8 +347,12 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             const int buf = local & 1;
             if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)local >> 1) & 1u, abortp, p.status, 3)) break;
             tc_fence_after();
-            drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, 0, bn, p.M, p.N, cs,
-                              p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act);
+            if (p.pool_on)
+                drain_accumulator_pooled(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, bn, p.M, p.N,
+                                         p.bias, p.act, p.pool, stage);
+            else
+                drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, 0, bn, p.M, p.N, cs,
+                                  p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);

@@ -132,6 +132,12 @@ class Tensor:
 tensor = Tensor
 
 
+# Conv2D followed by a 2x2 / stride-2 MaxPool2D runs as one launch (pool in the convolution's epilogue) where the engine
+# can do it; the convolution's own full-resolution output is then never materialised.  Set to False to keep every
+# layer's output in memory.
+FUSE_POOL = True
+
+
 class _PooledGrad:
     """Gradient of a 2x2 / stride-2 max-pool output, kept in pooled form with the pool's argmax mask.  A consumer that
     can route it itself (Conv2D backward: one kernel forms dz from it) takes it as is; anything else materialises the
@@ -408,13 +414,30 @@ class Conv2D(_ParamLayer):
         N, C, H, Wd = xv.shape
         F, (KH, KW), (sh, sw), (ph, pw) = self.out_channels, self.kernel_size, self.stride, self.zero_padding
         OH, OW = (H + 2 * ph - KH) // sh + 1, (Wd + 2 * pw - KW) // sw + 1
-        z = _new((N, F, OH, OW))
         kept = _KeptCopies()
         given = getattr(x, "_copies", None) if x.value is xv else None       # copies made by the producer of x
+        pool = getattr(self, "_pool_consumer", None)
+        self._fused = None
+        if (FUSE_POOL and pool is not None and self.layeract != "softmax"
+                and sc.conv2d_pool_fusable(N, C, H, Wd, F, KH, KW, sh, sw, ph, pw)):
+            # the pool is folded into this layer's epilogue: z stays a shape without memory
+            z = cuten._wrap(0, (N, F, OH, OW))
+            z._owns_memory = False
+            pooled = _new((N, F, OH // 2, OW // 2))
+            pmask = cuten._wrap(sc.cuda_malloc_i32(N * F * (OH // 2) * (OW // 2)), (N, F, OH // 2, OW // 2), "int32")
+            pcopies = _KeptCopies()
 
-        def product(bias, code):
-            kept.h = sc.conv2d_bias_act_fwd_s(xv.main_ptr, W.main_ptr, bias, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw, code,
-                                              given.h if given else 0)
+            def product(bias, code):
+                kept.h, pcopies.h = sc.conv2d_bias_act_pool_fwd_s(xv.main_ptr, W.main_ptr, bias, pooled.main_ptr, pmask.main_ptr, N, C, H,
+                                                                  Wd, F, KH, KW, ph, pw, sh, sw, code, given.h if given else 0,
+                                                                  bool(getattr(pool, "_feeds_conv", False)))
+            self._fused = (pooled, pmask, pcopies)
+        else:
+            z = _new((N, F, OH, OW))
+
+            def product(bias, code):
+                kept.h = sc.conv2d_bias_act_fwd_s(xv.main_ptr, W.main_ptr, bias, z.main_ptr, N, C, H, Wd, F, KH, KW, ph, pw, sh, sw,
+                                                  code, given.h if given else 0)
 
         def fused_backward(g, y, code, db, need_dx=not x.is_leaf):
             dw = self.weights._grad_target()
@@ -497,6 +520,8 @@ class MaxPool2D(Layer):
         if not isinstance(input_layer, Layer):
             raise TypeError("Input must be a Layer instance.")
         self.inpobj = input_layer
+        if (tuple(self.pool_size), self.stride, self.padding) == ((2, 2), (2, 2), (0, 0)):
+            input_layer._pool_consumer = self     # a Conv2D producer may fold this pool into its own launch
         return self
 
     def forward(self):
@@ -507,13 +532,20 @@ class MaxPool2D(Layer):
         N, C, H, W = xv.shape
         (KH, KW), (sh, sw), (ph, pw) = self.pool_size, self.stride, self.padding
         OH, OW = (H + 2 * ph - KH) // sh + 1, (W + 2 * pw - KW) // sw + 1
-        y = _new((N, C, OH, OW))
-        mask = cuten._wrap(sc.cuda_malloc_i32(N * C * OH * OW), (N, C, OH, OW), "int32")
         if OH * OW > H * W:
             raise ValueError("[cuTen]: maxpool2d with more outputs than inputs is not supported")
         tiles_exactly = (KH, KW, sh, sw, ph, pw) == (2, 2, 2, 2, 0, 0) and H % 2 == 0 and W % 2 == 0
-        copies = _KeptCopies()
-        if tiles_exactly and getattr(self, "_feeds_conv", False):   # also leaves the channels-last copies of y for that convolution
+        fused = getattr(self.inpobj, "_fused", None)
+        if fused is not None:                     # the producing convolution already pooled its output
+            y, mask, copies = fused
+            self.inpobj._fused = None
+        else:
+            y = _new((N, C, OH, OW))
+            mask = cuten._wrap(sc.cuda_malloc_i32(N * C * OH * OW), (N, C, OH, OW), "int32")
+            copies = _KeptCopies()
+        if fused is not None:
+            pass
+        elif tiles_exactly and getattr(self, "_feeds_conv", False):   # also leaves the channels-last copies of y for that convolution
             copies.h = sc.maxpool2x2_fwd_s(xv.main_ptr, y.main_ptr, mask.main_ptr, N, C, H, W)
         else:
             sc.cuda_maxpool_fwd(xv.main_ptr, y.main_ptr, mask.main_ptr, N, C, H, W, KH, KW, ph, pw, sh, sw)

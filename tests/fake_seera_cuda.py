@@ -305,12 +305,31 @@ def maxpool2x2_fwd_s(x, o, mask, N, C, H, W):
     return 0
 
 
+def conv2d_pool_fusable(N, C, H, W, Fo, R, S, sh, sw, ph, pw):
+    OH, OW = (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1
+    return OH % 2 == 0 and OW % 2 == 0 and (OW in (2, 4, 8, 16) or C * R * S <= 64)
+
+
+def conv2d_bias_act_pool_fwd_s(x, w, b, pooled, mask, N, C, H, W, Fo, R, S, ph, pw, sh, sw, act, x_in, want_copies):
+    OH, OW = (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1
+    tmp = _alloc(N * Fo * OH * OW * 4)
+    conv2d_bias_act_fwd(x, w, b, tmp, N, C, H, W, Fo, R, S, ph, pw, sh, sw, act)
+    cuda_maxpool_fwd(tmp, pooled, mask, N, Fo, OH, OW, 2, 2, 0, 0, 2, 2)
+    cuda_free(tmp)
+    return 0, 0
+
+
 def shadow_free(h): pass
 
 
 def conv2d_act_bwd(w, x, y, g, gp, mask, yp, dx, dw, db, N, C, H, W, Fo, R, S, sh, sw, ph, pw, act, x_shadow):
     OH, OW = (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1
     n = N * Fo * OH * OW
+    ytmp = 0
+    if not y and act:            # only the pool's output is at hand: it is y wherever the routed gradient is not zero
+        ytmp = y = _alloc(n * 4)
+        up = np.repeat(np.repeat(F(yp, (N, Fo, OH // 2, OW // 2)), 2, axis=2), 2, axis=3)
+        _view(y, n)[:] = up.ravel()
     full = np.empty(n, np.float32)
     if gp:
         tmp = _alloc(n * 4)
@@ -324,6 +343,8 @@ def conv2d_act_bwd(w, x, y, g, gp, mask, yp, dx, dw, db, N, C, H, W, Fo, R, S, s
     act_bias_bwd(tmp, y, tmp, db, n, Fo, OH * OW, act)
     cuda_conv2d_bwd(w, x, tmp, dx, dw, N, C, H, W, Fo, R, S, sh, sw, ph, pw)
     cuda_free(tmp)
+    if ytmp:
+        cuda_free(ytmp)
 
 
 def act_bias_bwd(dy, y, dz, db, n, ch, inner, act):

@@ -240,6 +240,77 @@ def test_pool_hands_its_copies_to_the_next_convolution(E, mode):
             L.seera_cuda_free(p)
 
 
+POOL_FUSED = [(3, 16, 16, 16, 24, 3, 3, 1, 1, 1, 1), (2, 70, 8, 8, 130, 3, 3, 1, 1, 1, 1), (5, 8, 4, 4, 16, 3, 3, 1, 1, 1, 1),
+              (4, 8, 8, 8, 8, 3, 3, 2, 2, 1, 1), (4, 3, 32, 32, 64, 3, 3, 1, 1, 1, 1), (3, 1, 28, 28, 20, 5, 5, 1, 1, 2, 2),
+              (1, 2, 6, 6, 3, 1, 1, 1, 1, 0, 0)]
+
+
+@pytest.mark.parametrize("mode", [2, 3])
+@pytest.mark.parametrize("shape", POOL_FUSED)
+def test_pool_folded_into_the_convolution_epilogue(E, mode, shape):
+    """seera_conv2d_bias_act_pool_fwd_s against the separate calls: pooled values and mask bit-equal; the copies it returns
+    feed the next convolution to a bit-equal result; backward from (gp, mask, pooled) with y = NULL equals backward with y."""
+    import ctypes
+    from ml_framework_b200 import capi
+    L = capi.load()
+    _prep(mode)
+    N, C, H, W, F, KH, KW, sh, sw, ph, pw = shape
+    OH, OW = (H + 2 * ph - KH) // sh + 1, (W + 2 * pw - KW) // sw + 1
+    short = C * KH * KW <= 64
+    assert L.seera_conv2d_pool_fusable(N, C, H, W, F, KH, KW, sh, sw, ph, pw) == (0 if short else 1)
+    capi.check(L.seera_set_option(b"pool_short_patch", 1))            # off by default (slower), still has to be right
+    assert L.seera_conv2d_pool_fusable(N, C, H, W, F, KH, KW, sh, sw, ph, pw) == 1
+    rs = np.random.RandomState(sum(shape) + mode)
+    X, Wt, b = (rs.standard_normal(s).astype(np.float32) for s in ((N, C, H, W), (F, C, KH, KW), (F,)))
+    W2 = rs.standard_normal((9, F, 3, 3)).astype(np.float32)
+    gp = rs.standard_normal((N, F, OH // 2, OW // 2)).astype(np.float32)
+    up = lambda a: L.seera_to_device(np.ascontiguousarray(a).ctypes.data_as(ctypes.c_void_p), a.nbytes)
+    def down(p, shape, dt=np.float32):
+        a = np.empty(shape, dt)
+        capi.check(L.seera_to_host(a.ctypes.data_as(ctypes.c_void_p), p, a.nbytes))
+        return a
+    xd, wd, bd, w2d, gpd = up(X), up(Wt), up(b), up(W2), up(gp)
+    nq = N * F * (OH // 2) * (OW // 2)
+    for act in (1, 2):
+        # separate calls
+        y = L.seera_cuda_malloc(N * F * OH * OW * 4)
+        p1, m1 = L.seera_cuda_malloc(nq * 4), L.seera_cuda_malloc(nq * 4)
+        capi.check(L.seera_conv2d_bias_act_fwd(xd, wd, bd, y, N, C, H, W, F, KH, KW, ph, pw, sh, sw, act))
+        capi.check(L.seera_cuda_maxpool_fwd(y, p1, m1, N, F, OH, OW, 2, 2, 0, 0, 2, 2))
+        # one call
+        p2, m2 = L.seera_cuda_malloc(nq * 4), L.seera_cuda_malloc(nq * 4)
+        keep, pc = ctypes.c_void_p(), ctypes.c_void_p()
+        capi.check(L.seera_conv2d_bias_act_pool_fwd_s(xd, wd, bd, p2, m2, N, C, H, W, F, KH, KW, ph, pw, sh, sw, act, None,
+                                                      ctypes.byref(keep), ctypes.byref(pc)))
+        shp = (N, F, OH // 2, OW // 2)
+        assert np.array_equal(down(p1, shp), down(p2, shp)) and np.array_equal(down(m1, shp, np.int32), down(m2, shp, np.int32))
+        # the returned copies of the pooled tensor feed the next convolution
+        if F * 9 > 64:
+            res = []
+            for x_in in (pc, None):
+                zd = L.seera_cuda_malloc(N * 9 * (OH // 2) * (OW // 2) * 4)
+                capi.check(L.seera_conv2d_bias_act_fwd_s(p2, w2d, None, zd, N, F, OH // 2, OW // 2, 9, 3, 3, 1, 1, 1, 1, 0, x_in, None))
+                res.append(down(zd, (N, 9, OH // 2, OW // 2)))
+                L.seera_cuda_free(zd)
+            assert np.array_equal(res[0], res[1])
+        # backward without the full-resolution output
+        outs = []
+        for yy in (y, None):
+            dw, db, dx = L.seera_cuda_malloc(Wt.size * 4), L.seera_cuda_malloc(F * 4), L.seera_cuda_malloc(X.size * 4)
+            capi.check(L.seera_conv2d_act_bwd(wd, xd, yy, None, gpd, m2, p2, dx, dw, db, N, C, H, W, F, KH, KW, sh, sw, ph, pw, act, keep))
+            outs.append((down(dw, Wt.shape), down(db, (F,)), down(dx, X.shape)))
+            for p in (dw, db, dx):
+                L.seera_cuda_free(p)
+        for a, bb in zip(*outs):
+            assert np.array_equal(a, bb)
+        L.seera_shadow_free(keep); L.seera_shadow_free(pc)
+        for p in (y, p1, m1, p2, m2):
+            L.seera_cuda_free(p)
+    for p in (xd, wd, bd, w2d, gpd):
+        L.seera_cuda_free(p)
+    capi.check(L.seera_set_option(b"pool_short_patch", 0))
+
+
 def test_c5_conv_backward_point_bf16(E):
     """One point of the Conv2D-backward sweep at reduced batch (C = K = 64, 56x56, 3x3 s1 p1), bf16 operands."""
     X, Wt, dY = wl.c5_conv_bwd(64, 56, n=4)
