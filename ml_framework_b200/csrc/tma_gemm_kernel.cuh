@@ -410,7 +410,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
     const long long ksteps = (p.K + TC_BK - 1) / TC_BK;
     if (allow_split) {
         const long long sms = rt().sm_count;
-        long long maxs = ksteps / 4;
+        long long maxs = ksteps / 2;                  // at least two k-steps per item
         if (maxs > 256) maxs = 256;
         long long best = -1;
         for (long long sp = 1; sp <= maxs || sp == 1; sp++) {
