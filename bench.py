@@ -163,9 +163,9 @@ def setup_data_parallel(model, world, local_rank):
     full = torch.as_tensor(_ArenaView(model.grads.main_ptr, model.n_arena), device="cuda")
     from ml_framework_b200 import dp
     model._arena_allreduce = lambda: dist.all_reduce(full, op=dist.ReduceOp.SUM)     # whole arena, stream-ordered
-    dp.attach(model, world,
-              reduce_range=lambda b, e: dist.all_reduce(full[b:e], op=dist.ReduceOp.SUM, async_op=True),
-              wait=lambda w: w.wait())
+    model._reduce_range = lambda b, e: dist.all_reduce(full[b:e], op=dist.ReduceOp.SUM, async_op=True)
+    model._reduce_wait = lambda w: w.wait()
+    dp.attach(model, world, reduce_range=model._reduce_range, wait=model._reduce_wait)
     return dist, torch
 
 
@@ -217,7 +217,9 @@ def run_gpu(args, work):
     use_graph = not args.no_graph
     eager_ms = None
     if use_graph and dist is not None:
-        loss_t = tr.capture_data_parallel(Xd, Yd, tr.model._arena_allreduce)
+        from ml_framework_b200 import dp
+        loss_t = tr.capture_data_parallel(Xd, Yd, tr.model._arena_allreduce, buckets=dp.plan_buckets(tr.model, 4),
+                                          reduce_range=tr.model._reduce_range, wait=tr.model._reduce_wait)
         for _ in range(args.warmup):
             tr.replay_data_parallel()
         run_step = tr.replay_data_parallel
@@ -332,7 +334,7 @@ def run_gpu(args, work):
                         "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
                 "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": launches_per_step, "final_loss": last,
                 "step_mode": ("eager launches, bucketed all-reduce overlapping backward" if not use_graph else
-                              "CUDA graph replay of forward+backward, one NCCL all-reduce of the gradient arena, fused optimizer"
+                              "CUDA graphs of forward+backward cut at the gradient buckets, each bucket's NCCL all-reduce overlapping the next graph, fused optimizer"
                               if dist is not None else "CUDA graph replay of the captured step"),
                 "eager_ms_per_step": eager_ms,
                 "algorithmic_gflop_per_step": work.flops_per_sample() * n * world / 1e9,

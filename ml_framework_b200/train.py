@@ -100,14 +100,31 @@ class Trainer:
         sc.graph_launch(self._graph)
         return self._graph_keep[2]
 
-    def capture_data_parallel(self, X, Y, allreduce_arena):
-        """Data-parallel variant: records forward + loss + backward (gradients gathered in the arena) as one graph;
-        `replay_data_parallel` then launches it, calls `allreduce_arena()` (one in-place sum of the whole gradient
-        arena over the ranks, enqueued on the engine's stream) and enqueues the optimizer.  The bucketed overlap of
-        the eager path is traded for a step without per-kernel launch cost; the arena is a few MB."""
+    def capture_data_parallel(self, X, Y, allreduce_arena=None, buckets=None, reduce_range=None, wait=None):
+        """Data-parallel variant: records forward + loss + backward (gradients gathered in the arena) as CUDA graphs and
+        leaves the collectives and the optimizer outside them.
+
+        Without `buckets`: one graph, then `allreduce_arena()` (one in-place sum of the whole gradient arena over the ranks,
+        enqueued on the engine's stream), then the optimizer.
+        With `buckets` (arena ranges from dp.plan_buckets, last layers first), `reduce_range(begin, end) -> handle` (an
+        asynchronous in-place sum) and `wait(handle)`: the recording is cut each time backward has written the last
+        gradient of a bucket, so a replay is  graph 0, reduce(bucket 0), graph 1, reduce(bucket 1), ..., wait all,
+        optimizer - the sums of the late layers' gradients (most of the parameters) travel while the early layers'
+        backward still runs."""
         if not (isinstance(X, S.Tensor) and isinstance(Y, S.Tensor)):
             raise TypeError("capture needs device-resident Tensors")
         hook, self.model._on_grad_ready = self.model._on_grad_ready, None
+        plan, nxt = [], [0]
+        if buckets:
+            def cut_at(t):
+                # backward runs from the last layer to the first: once parameter t's gradient sits in the arena every
+                # slot at or above its offset is final
+                while nxt[0] < len(buckets) - 1 and t._arena_off <= buckets[nxt[0]][0]:
+                    plan.append(("graph", sc.graph_end()))
+                    plan.append(("reduce",) + tuple(buckets[nxt[0]]))
+                    nxt[0] += 1
+                    sc.graph_begin()
+            self.model._on_grad_ready = cut_at
         sc.graph_begin()
         try:
             loss = self.forward_backward(X, Y)
@@ -117,16 +134,34 @@ class Trainer:
                 sc.graph_end()
             except Exception:
                 pass
+            for item in plan:
+                if item[0] == "graph":
+                    sc.graph_destroy(item[1])
             self.model._on_grad_ready = hook
             raise
-        self._graph = sc.graph_end()
+        plan.append(("graph", sc.graph_end()))
+        if buckets:
+            plan.extend(("reduce",) + tuple(bk) for bk in buckets[nxt[0]:])
+        self.model._on_grad_ready = None
+        self._graph = plan[0][1]
+        self._graph_plan = plan
         self._graph_keep = (X, Y, loss, self.pred, hook)
         self._graph_allreduce = allreduce_arena
+        self._graph_reduce = (reduce_range, wait)
         return loss
 
     def replay_data_parallel(self):
-        sc.graph_launch(self._graph)
-        self._graph_allreduce()
+        reduce_range, wait = self._graph_reduce
+        works = []
+        for item in self._graph_plan:
+            if item[0] == "graph":
+                sc.graph_launch(item[1])
+            else:
+                works.append(reduce_range(item[1], item[2]))
+        if not works:
+            self._graph_allreduce()
+        for w in works:
+            wait(w)
         self.opt.advance()
         self.opt._enqueue()
         return self._graph_keep[2]
@@ -174,6 +209,13 @@ class Trainer:
         return losses
 
     def release_graph(self):
+        plan = getattr(self, "_graph_plan", None)
+        if plan:
+            for item in plan:
+                if item[0] == "graph":
+                    sc.graph_destroy(item[1])
+            self._graph_plan, self._graph, self._graph_keep = None, None, None
+            return
         g = getattr(self, "_graph", None)
         if g:
             sc.graph_destroy(g)

@@ -185,3 +185,36 @@ def test_streamed_batches_match_step_by_step_uploads(T):
         sc.host_free_pinned(hx); sc.host_free_pinned(hy)
     a.release_graph(); b.release_graph()
     sc.set_precision(0)
+
+
+def test_step_recorded_in_segments_at_the_gradient_buckets(T):
+    """capture_data_parallel with buckets cuts the recording where backward has finished a bucket of the gradient arena;
+    with a do-nothing collective (one rank) the replayed weights equal eager steps bit for bit, and the cuts and the
+    reduce calls come in arena order (last layers first)."""
+    from ml_framework_b200 import seera as S, seera_cuda as sc, dp
+    sc.set_precision(2)
+    work = wl.WORKLOADS["c3"]()
+    X, Y = work.batch(16, 9)
+    a, b = T.Trainer(work, seed=4), T.Trainer(work, seed=4)
+    Xa, Ya = S.Tensor(X, is_leaf=True), S.Tensor(Y, is_leaf=True)
+    Xb, Yb = S.Tensor(X, is_leaf=True), S.Tensor(Y, is_leaf=True)
+    for _ in range(2):
+        a.step(Xa, Ya)
+        b.step(Xb, Yb)
+    for _ in range(3):
+        la = a.step(Xa, Ya)
+    buckets = dp.plan_buckets(b.model, 4)
+    assert len(buckets) >= 2 and buckets[0][1] == b.model.n_arena and buckets[-1][0] == 0
+    calls = []
+    b.capture_data_parallel(Xb, Yb, buckets=buckets, reduce_range=lambda lo, hi: calls.append((lo, hi)), wait=lambda w: None)
+    kinds = [item[0] for item in b._graph_plan]
+    assert kinds.count("graph") == len(buckets) and kinds[0] == "graph" and kinds[-1] == "reduce"
+    for _ in range(3):
+        lb = b.replay_data_parallel()
+    assert calls == list(buckets) * 3
+    assert float(la.value.to_host_f32()[0]) == float(lb.value.to_host_f32()[0])
+    for Pa, Pb in zip(a.host_params(), b.host_params()):
+        if Pa is not None:
+            assert np.array_equal(Pa[0], Pb[0]) and np.array_equal(Pa[1], Pb[1])
+    b.release_graph()
+    sc.set_precision(0)
