@@ -306,8 +306,11 @@ def run_gpu(args, work):
     if rank == 0:
         if cnt and pms > 0:
             ach = pfl / (pms / 1e3) / 1e12
+            # DRAM bytes per contraction launch from the ncu launch list of this workload (profiles/bench_c3_launch_list.txt:
+            # dram__bytes_read.sum + dram__bytes_write.sum of the 17 contraction launches of a C3 step = 620.9 MB)
+            traffic = 36.5e6 if (args.workload == "c3" and args.precision == "3/2") else None
             roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": ach / peaks["tensor"],
-                    "traffic": None, "kernel": "contraction (Dense/Conv fwd, dX, dW)", "launches_per_step": cnt / min(args.steps, 5),
+                    "traffic": traffic, "kernel": "contraction (Dense/Conv fwd, dX, dW)", "launches_per_step": cnt / min(args.steps, 5),
                     "ms_per_step_in_kernel": pms / min(args.steps, 5), "peak_source": peaks["src"] + " sustained bf16",
                     "share_of_step": (pms / min(args.steps, 5)) / (ms / args.steps)}
 
