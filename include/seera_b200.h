@@ -73,6 +73,9 @@ int         seera_get_precision(void);
  *   "dense_tma" (default 1): in precision modes 1-3 the Dense GEMMs convert their operands to bf16 shadows once
  *       and feed the tensor cores by TMA; 0 selects the kernel that converts inside its producer warps.
  *   "conv_tma" (default 1): the same choice for the convolution family (TMA im2col).
+ *   "sm_reserve" (default 0): the persistent kernels size their grids for that many SMs fewer than the device has.
+ *       They hold one CTA with ~214 KB of shared memory per SM for their whole duration, so a kernel of another
+ *       stream (a collective that should overlap them) otherwise finds no SM until they end.
  *   "pool_short_patch" (default 0): let seera_conv2d_bias_act_pool_fwd_s also serve short-patch convolutions
  *       (C*R*S <= 64).  Correct, but that kernel is bound by its epilogue warps and runs slower with the pool folded in
  *       than followed by a separate pool.

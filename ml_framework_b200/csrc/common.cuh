@@ -9,7 +9,8 @@ namespace seera {
 
 struct Runtime {
     int device = -1;
-    int sm_count = 148;
+    int sm_count = 148;                 // SMs the kernels size their grids for (physical count minus the "sm_reserve" option)
+    int sm_physical = 148;
     cudaStream_t stream = nullptr;      // the stream every kernel is enqueued on
     cudaStream_t own_stream = nullptr;
     int precision = 0;

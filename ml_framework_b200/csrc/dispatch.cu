@@ -16,6 +16,11 @@ int seera_set_option(const char *name, int value) {
     if (!strcmp(name, "dense_tma")) { rt().dense_tma = value != 0; return SEERA_OK; }
     if (!strcmp(name, "conv_tma")) { rt().conv_tma = value != 0; return SEERA_OK; }
     if (!strcmp(name, "pool_short_patch")) { rt().pool_short_patch = value != 0; return SEERA_OK; }
+    if (!strcmp(name, "sm_reserve")) {
+        if (value < 0 || value >= rt().sm_physical) return fail(SEERA_E_ARG, "set_option: sm_reserve must be in [0, %d)", rt().sm_physical);
+        rt().sm_count = rt().sm_physical - value;
+        return SEERA_OK;
+    }
     if (!strcmp(name, "tile_n_cap2") || !strcmp(name, "tile_n_cap3")) {
         if (value != 64 && value != 128 && value != 256) return fail(SEERA_E_ARG, "set_option: %s must be 64, 128 or 256", name);
         (name[10] == '2' ? rt().tile_n_cap2 : rt().tile_n_cap3) = value;

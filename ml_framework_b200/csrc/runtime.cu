@@ -103,7 +103,7 @@ int seera_init(int device) {
     if (int s = check_cuda(cudaSetDevice(device), "cudaSetDevice")) return s;
     cudaDeviceProp p;
     if (int s = check_cuda(cudaGetDeviceProperties(&p, device), "cudaGetDeviceProperties")) return s;
-    r.sm_count = p.multiProcessorCount;
+    r.sm_count = r.sm_physical = p.multiProcessorCount;
     if (!r.own_stream)
         if (int s = check_cuda(cudaStreamCreateWithFlags(&r.own_stream, cudaStreamNonBlocking), "cudaStreamCreate")) return s;
     r.stream = r.own_stream;
