@@ -116,6 +116,10 @@ int   seera_upload(void *dev, const void *host, size_t n_bytes);      /* upload 
  * runs).  Host memory must be page-locked (seera_host_alloc_pinned).  The two fences order "everything queued so
  * far" on one stream before everything queued later on the other.  Not usable while a graph is being captured.
  * No counterpart in the reference, which copies synchronously on the default stream (cuda_bindings.cpp:98-170). */
+/* One-hot rows on the device: out[i, c] = (labels[i] == c) as float, n x classes.  Lets a training loop upload 4 bytes
+ * of label per sample instead of a one-hot row (Sequential.fit of the reference takes host one-hot arrays and uploads
+ * them batch by batch, Seera.py:748-755). */
+int   seera_onehot_f32(const int *labels, float *out, int n, int classes);
 /* Measurement aid: occupies the compute stream for about `microseconds` (0..100000) with a one-thread kernel, so that
  * work enqueued right after it queues up and runs back to back; bench.py uses it before its per-kernel event pass. */
 int   seera_stream_delay(int microseconds);

@@ -155,6 +155,14 @@ __global__ void __launch_bounds__(256) sum_partials_kernel(const float *__restri
     out[c] = t;
 }
 
+// out[i][c] = (labels[i] == c): labels outside [0, classes) give an all-zero row
+__global__ void __launch_bounds__(256) onehot_kernel(const int *__restrict__ labels, float *__restrict__ out, int total, int classes) {
+    for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
+        const int i = e / classes, c = e - i * classes;
+        out[e] = __ldg(labels + i) == c ? 1.f : 0.f;
+    }
+}
+
 // ---- row softmax: one warp per row --------------------------------------------------------------------
 __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float *__restrict__ x, float *__restrict__ out, int N, int C) {
     int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -437,6 +445,16 @@ int seera_cuda_softmax_vjp(const float *s, const float *dout, float *dx, int N, 
     if (N == 0) return SEERA_OK;
     softmax_vjp_kernel<<<stride_grid((long long)N * 32), 256, 0, rt().stream>>>(s, dout, dx, N, C);
     SEERA_LAUNCH_CHECK("cuda_softmax_vjp");
+    return SEERA_OK;
+}
+
+int seera_onehot_f32(const int *labels, float *out, int n, int classes) {
+    SEERA_ENSURE();
+    if (n < 0 || classes < 1 || (n > 0 && (!labels || !out)) || (long long)n * classes > 0x7fffffffLL)
+        return fail(SEERA_E_ARG, "onehot_f32: bad argument");
+    if (n == 0) return SEERA_OK;
+    onehot_kernel<<<stride_grid((long long)n * classes), 256, 0, rt().stream>>>(labels, out, n * classes, classes);
+    SEERA_LAUNCH_CHECK("onehot_f32");
     return SEERA_OK;
 }
 

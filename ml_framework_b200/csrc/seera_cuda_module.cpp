@@ -167,12 +167,16 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("pool_bytes_reserved", []() { return seera_pool_bytes_reserved(); });
     m.def("upload_f32", [](uptr dst, arr_f a) { ck(seera_upload(P<void>(dst), a.data(), (size_t)a.size() * 4)); });
     m.def("upload_from_host_ptr", [](uptr dst, uptr host, size_t nbytes) { ck(seera_upload(P<void>(dst), P<const void>(host), nbytes)); });
+    m.def("onehot_f32", [](uptr labels, uptr out, int n, int classes) { ck(seera_onehot_f32(P<const int>(labels), P<F>(out), n, classes)); });
     m.def("stream_delay", [](int us) { ck(seera_stream_delay(us)); });
     m.def("copy_upload", [](uptr dst, uptr host, size_t nbytes) { ck(seera_copy_upload(P<void>(dst), P<const void>(host), nbytes)); });
     m.def("copy_download", [](uptr host, uptr src, size_t nbytes) { ck(seera_copy_download(P<void>(host), P<const void>(src), nbytes)); });
     m.def("copy_wait_compute", []() { ck(seera_copy_wait_compute()); });
     m.def("compute_wait_copy", []() { ck(seera_compute_wait_copy()); });
     m.def("copy_synchronize", []() { ck(seera_copy_synchronize()); });
+    m.def("host_view", [](uptr p, size_t nbytes) {
+        // NumPy view (uint8) of page-locked memory from host_alloc_pinned; the caller keeps the allocation alive
+        return py::array_t<unsigned char>({nbytes}, {sizeof(unsigned char)}, P<unsigned char>(p), py::none()); });
     m.def("host_alloc_pinned", [](size_t n) { return ckp(seera_host_alloc_pinned(n)); });
     m.def("host_free_pinned", [](uptr p) { ck(seera_host_free_pinned(P<void>(p))); });
     m.def("bias_act_fwd", [](uptr z, uptr b, uptr y, int n, int ch, int inner, int act) {

@@ -716,7 +716,85 @@ class Sequential:
                 sc.cuda_memcopy_devicetodevice(dst, g.main_ptr, t._arena_n)
                 t.grad = self._grad_view(t)
 
-    def fit(self, X_train, y, Optimizer, Loss, Epochs, batch_size=1, Loss_interval=20):
+    def fit(self, X_train, y, Optimizer, Loss, Epochs, batch_size=1, Loss_interval=20, num_classes=None):
+        """Training loop with the reference's signature, shuffling and history (Seera.py:715-788).  The input side is a
+        pipeline: each batch is gathered straight into one of two page-locked staging buffers and uploaded on the copy
+        stream while the previous step runs, and the loss of a step is read back one step later, so the compute stream
+        never waits for a transfer.  `y` may be the reference's one-hot / target array, or, with `num_classes`, a 1-D
+        integer label array: 4 bytes per sample cross PCIe and the one-hot rows are formed on the device."""
+        X_train = np.ascontiguousarray(X_train, np.float32)
+        labels = num_classes is not None and np.ndim(y) == 1
+        y = np.ascontiguousarray(y, np.int32 if labels else np.float32)
+        n = X_train.shape[0]
+        bs = int(batch_size)
+        xrow, yrow = int(np.prod(X_train.shape[1:])), int(np.prod(y.shape[1:]))
+        # two sets of staging / device buffers, sized for a full batch
+        stage = []
+        for _ in range(2):
+            hx, hy = sc.host_alloc_pinned(bs * xrow * 4), sc.host_alloc_pinned(bs * yrow * 4)
+            stage.append({"hx": hx, "hy": hy, "vx": sc.host_view(hx, bs * xrow * 4).view(np.float32),
+                          "vy": sc.host_view(hy, bs * yrow * 4).view(np.int32 if labels else np.float32),
+                          "dx": _new((bs,) + X_train.shape[1:]), "dy": _new((bs,) + y.shape[1:]) if not labels else None,
+                          "dl": cuten._wrap(sc.cuda_malloc_i32(bs), (bs,), "int32") if labels else None})
+        hl = sc.host_alloc_pinned(8)
+        slots = sc.host_view(hl, 8).view(np.float32)
+        history = []
+        try:
+            for epoch in range(Epochs):
+                perm = np.random.permutation(n)
+                starts = list(range(0, n, bs))
+
+                def upload(k):                      # batch k -> staging set k % 2 -> its device buffers (copy stream)
+                    st, idx = stage[k & 1], perm[starts[k]:starts[k] + bs]
+                    m = len(idx)
+                    np.take(X_train.reshape(n, xrow), idx, axis=0, out=st["vx"][:m * xrow].reshape(m, xrow))
+                    np.take(y.reshape(n, yrow), idx, axis=0, out=st["vy"][:m * yrow].reshape(m, yrow))
+                    sc.copy_upload(st["dx"].main_ptr, st["hx"], m * xrow * 4)
+                    sc.copy_upload((st["dl"] if labels else st["dy"]).main_ptr, st["hy"], m * yrow * 4)
+                    return m
+                total, pending = 0.0, None          # pending: loss tensor of the previous step, not read back yet
+                sc.copy_wait_compute()              # whatever still reads the staging sets comes first
+                sizes = {0: upload(0)}
+                for k in range(len(starts)):
+                    st, m = stage[k & 1], sizes[k]
+                    sc.compute_wait_copy()          # batch k has landed
+                    sc.copy_wait_compute()          # set (k + 1) % 2 is free once step k - 1 has run
+                    xb = Tensor(cuten._wrap(st["dx"].main_ptr, (m,) + X_train.shape[1:]), is_leaf=True)
+                    xb.value._owns_memory = False
+                    if labels:
+                        yv = _new((m, int(num_classes)))
+                        sc.onehot_f32(st["dl"].main_ptr, yv.main_ptr, m, int(num_classes))
+                    else:
+                        yv = cuten._wrap(st["dy"].main_ptr, (m,) + y.shape[1:])
+                        yv._owns_memory = False
+                    loss = Loss(self.forward(xb), Tensor(yv, is_leaf=True))
+                    self.zero_grad()
+                    autograd4nn(loss)
+                    Optimizer.step()
+                    if pending is not None:         # the device is already busy with step k
+                        sc.copy_synchronize()
+                        total += float(slots[(k - 1) & 1])
+                    if k + 1 < len(starts):
+                        sizes[k + 1] = upload(k + 1)
+                    sc.copy_wait_compute()          # the loss is final once step k has run
+                    sc.copy_download(hl + 4 * (k & 1), loss.value.main_ptr, 4)
+                    pending = loss
+                sc.copy_synchronize()
+                total += float(slots[(len(starts) - 1) & 1])
+                history.append(total / len(starts))
+                if epoch % Loss_interval == 0 or epoch == Epochs - 1:
+                    print(f"Epoch {epoch + 1}/{Epochs} — Loss: {history[-1]:.6f}")
+        finally:
+            sc.stream_synchronize()
+            sc.copy_synchronize()
+            for st in stage:
+                sc.host_free_pinned(st["hx"]); sc.host_free_pinned(st["hy"])
+            sc.host_free_pinned(hl)
+        return np.array(history)
+
+    def _fit_unpipelined(self, X_train, y, Optimizer, Loss, Epochs, batch_size=1):
+        """The same loop with a synchronous upload and loss read per step (the reference's structure); kept as the
+        yardstick for fit()."""
         history = []
         n = X_train.shape[0]
         for epoch in range(Epochs):
@@ -733,8 +811,6 @@ class Sequential:
                 total += float(loss.value.to_host_f32().ravel()[0])
                 batches += 1
             history.append(total / batches)
-            if epoch % Loss_interval == 0 or epoch == Epochs - 1:
-                print(f"Epoch {epoch + 1}/{Epochs} — Loss: {history[-1]:.6f}")
         return np.array(history)
 
     # checkpoint: layer configs + host copies of the weights (same record layout as Seera.py:790-860)

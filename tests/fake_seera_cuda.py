@@ -322,6 +322,37 @@ def conv2d_bias_act_pool_fwd_s(x, w, b, pooled, mask, N, C, H, W, Fo, R, S, ph, 
 def shadow_free(h): pass
 
 
+# transfers: the stand-in has one "stream", so the copy-stream calls are plain copies and the fences do nothing
+def host_alloc_pinned(n):
+    return _alloc(n)
+
+
+def host_free_pinned(p):
+    cuda_free(p)
+
+
+def host_view(p, nbytes):
+    return _view(p, nbytes, np.uint8)
+
+
+def copy_upload(dst, host, nbytes):
+    _view(dst, nbytes, np.uint8)[:] = _view(host, nbytes, np.uint8)
+
+
+def copy_download(host, src, nbytes):
+    _view(host, nbytes, np.uint8)[:] = _view(src, nbytes, np.uint8)
+
+
+def copy_wait_compute(): pass
+def compute_wait_copy(): pass
+def copy_synchronize(): pass
+
+
+def onehot_f32(labels, out, n, classes):
+    lab = _view(labels, n, np.int32)
+    F(out, (n, classes))[:] = (lab[:, None] == np.arange(classes)[None, :]).astype(np.float32)
+
+
 def conv2d_act_bwd(w, x, y, g, gp, mask, yp, dx, dw, db, N, C, H, W, Fo, R, S, sh, sw, ph, pw, act, x_shadow):
     OH, OW = (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1
     n = N * Fo * OH * OW

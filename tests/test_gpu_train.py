@@ -218,3 +218,36 @@ def test_step_recorded_in_segments_at_the_gradient_buckets(T):
             assert np.array_equal(Pa[0], Pb[0]) and np.array_equal(Pa[1], Pb[1])
     b.release_graph()
     sc.set_precision(0)
+
+
+def test_fit_pipeline_matches_the_synchronous_loop_on_the_device(T):
+    """Sequential.fit with staging buffers, copy-stream uploads and late loss reads equals the synchronous loop bit for
+    bit (history and weights), with host one-hot targets and with integer labels expanded by seera_onehot_f32."""
+    from ml_framework_b200 import seera as S, seera_cuda as sc
+    sc.set_precision(0)
+    rs = np.random.RandomState(3)
+    X = rs.standard_normal((150, 1, 12, 12)).astype(np.float32)
+    lab = rs.randint(0, 7, 150).astype(np.int32)
+    Y = np.eye(7, dtype=np.float32)[lab]
+
+    def make():
+        np.random.seed(11)
+        m = S.Sequential([S.Input((1, 12, 12)), S.Conv2D(8, 1, (3, 3), "relu", stride=1, zero_padding=1), S.MaxPool2D((2, 2), stride=2),
+                          S.Flatten(), S.Dense(288, 7, activation="softmax")], device="cuda")
+        return m, S.Adam(m, lr=1e-2), S.Loss().categorical_cross_entropy
+    runs = []
+    for mode in ("sync", "pipe", "labels"):
+        m, opt, loss = make()
+        np.random.seed(5)
+        if mode == "sync":
+            h = m._fit_unpipelined(X, Y, opt, loss, Epochs=2, batch_size=32)
+        elif mode == "pipe":
+            h = m.fit(X, Y, opt, loss, Epochs=2, batch_size=32, Loss_interval=100)
+        else:
+            h = m.fit(X, lab, opt, loss, Epochs=2, batch_size=32, Loss_interval=100, num_classes=7)
+        runs.append((h, [(l.weights.to_numpy(), l.bais.to_numpy()) for l in m.model if isinstance(l, S._ParamLayer)]))
+    assert runs[0][0][-1] < runs[0][0][0]                       # it trains
+    for h, ws in runs[1:]:
+        assert np.array_equal(h, runs[0][0])
+        for (w, b), (w0, b0) in zip(ws, runs[0][1]):
+            assert np.array_equal(w, w0) and np.array_equal(b, b0)

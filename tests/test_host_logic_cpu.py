@@ -172,6 +172,37 @@ def test_save_load_round_trip(host, tmp_path):
     assert np.array_equal(a, b)
 
 
+def test_fit_pipeline_matches_the_synchronous_loop(host):
+    """Sequential.fit (double-buffered staging, loss read one step late, last batch ragged) gives the history and the
+    weights of the synchronous loop; integer labels expanded on the device give the same as host one-hot rows."""
+    S = host.seera
+    rs = np.random.RandomState(3)
+    X = rs.standard_normal((37, 1, 6, 6)).astype(np.float32)
+    lab = rs.randint(0, 5, 37).astype(np.int32)
+    Y = np.eye(5, dtype=np.float32)[lab]
+
+    def make():
+        np.random.seed(11)
+        m = S.Sequential([S.Input((1, 6, 6)), S.Conv2D(4, 1, (3, 3), "relu", stride=1, zero_padding=1), S.MaxPool2D((2, 2), stride=2),
+                          S.Flatten(), S.Dense(36, 5, activation="softmax")], device="cuda")
+        return m, S.Adam(m, lr=1e-2), S.Loss().categorical_cross_entropy
+    runs = []
+    for mode in ("sync", "pipe", "labels"):
+        m, opt, loss = make()
+        np.random.seed(5)                               # the epoch shuffles
+        if mode == "sync":
+            h = m._fit_unpipelined(X, Y, opt, loss, Epochs=2, batch_size=8)
+        elif mode == "pipe":
+            h = m.fit(X, Y, opt, loss, Epochs=2, batch_size=8, Loss_interval=100)
+        else:
+            h = m.fit(X, lab, opt, loss, Epochs=2, batch_size=8, Loss_interval=100, num_classes=5)
+        runs.append((h, [(l.weights.to_numpy(), l.bais.to_numpy()) for l in m.model if isinstance(l, S._ParamLayer)]))
+    for h, ws in runs[1:]:
+        assert np.array_equal(h, runs[0][0])
+        for (w, b), (w0, b0) in zip(ws, runs[0][1]):
+            assert np.array_equal(w, w0) and np.array_equal(b, b0)
+
+
 @pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="reference checkout not present")
 def test_unmodified_reference_python_layer_runs_on_this_cuten(host, golden_dir):
     """Drop-in check of the tensor class: the reference's own Seera.py / Seera_init.py /
