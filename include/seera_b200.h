@@ -116,6 +116,17 @@ int   seera_upload(void *dev, const void *host, size_t n_bytes);      /* upload 
  * runs).  Host memory must be page-locked (seera_host_alloc_pinned).  The two fences order "everything queued so
  * far" on one stream before everything queued later on the other.  Not usable while a graph is being captured.
  * No counterpart in the reference, which copies synchronously on the default stream (cuda_bindings.cpp:98-170). */
+/* Batch normalisation on the device for x[N, C, S] (S = H*W; 1 for the 1-D layer).  The reference computes this layer
+ * on the host even in its GPU path (Seera_init.py:870-921, Seera_Engine.py:381-415, engine/src/batchnorm_ops.cpp:12-138);
+ * same arithmetic: per-channel mean, biased variance from the differences to that mean, std_inv = 1/sqrt(var + eps),
+ * y = gamma * x_hat + beta; training != 0 also moves running_mean / running_var by `momentum`, training == 0
+ * normalises with them.  mean_out and std_inv_out (C floats each) are what the backward needs; x_hat is recomputed
+ * there from x.  Backward: dgamma = sum dy * x_hat, dbeta = sum dy,
+ * dx = (1/M) * std_inv * (M * dxh - sum dxh - x_hat * sum dxh * x_hat) with dxh = dy * gamma, M = N * S. */
+int   seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta, float *running_mean, float *running_var, float *y,
+                          float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training);
+int   seera_batchnorm_bwd(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
+                          float *dgamma, float *dbeta, int N, int C, int S);
 /* One-hot rows on the device: out[i, c] = (labels[i] == c) as float, n x classes.  Lets a training loop upload 4 bytes
  * of label per sample instead of a one-hot row (Sequential.fit of the reference takes host one-hot arrays and uploads
  * them batch by batch, Seera.py:748-755). */

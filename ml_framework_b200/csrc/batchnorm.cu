@@ -1,0 +1,246 @@
+// Batch normalisation, forward and backward, for [N, C] and [N, C, H, W] tensors.
+//
+// The reference runs this layer on the CPU only, even in its GPU path (Seera_init.py:870-921 forward,
+// Seera_Engine.py:381-415 backward, engine/src/batchnorm_ops.cpp:12-138 the arithmetic): every batch goes device -> host
+// -> device around it.  Here it is four bandwidth-bound passes forward (sum, squared differences to the mean, a
+// C-thread finalise that also moves the running statistics, normalise) and three backward (sums of dout and
+// dout * x_hat, finalise, dx).  The statistics are two-pass like the reference (mean first, then the variance from the
+// differences), and every reduction has a fixed order: per-thread strided partials, a block tree, then the partial rows
+// summed in split order.  x_hat is not stored: the backward recomputes it from the layer input, the saved mean and
+// 1/std (one multiply-add against a second activation-sized buffer of traffic).
+//
+// Layout [N, C, S] with S = H*W (1 for the 1-D form).  S > 1: a block owns one channel and a stripe of images and reads
+// its planes contiguously.  S == 1: a block owns 32 adjacent channels x a stripe of rows, so warps read rows contiguously.
+#include "common.cuh"
+
+namespace seera {
+
+constexpr int BN_MAX_SPLITS = 64;
+
+__device__ __forceinline__ float bn_block_sum(float v, float *sm /* 8 floats */) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) r += sm[w];
+    return r;
+}
+// sum over the split rows of a [splits, C] partial table, in split order
+__device__ __forceinline__ float bn_sum_partials(const float *partial, int c, int C, int splits) {
+    float t = 0.f;
+    for (int s = 0; s < splits; s++) t += partial[(long long)s * C + c];
+    return t;
+}
+
+// What a reduction pass accumulates per channel:
+//   0  sum x                                   -> out0
+//   1  sum (x - mean)^2, mean from `in0`       -> out0          (in0 = the [splits, C] sums of pass 0)
+//   2  sum dy and sum dy * x_hat               -> out0, out1    (x_hat = (x - mean[c]) * std_inv[c])
+template <int MODE>
+__global__ void __launch_bounds__(256) bn_reduce_planes_kernel(const float *__restrict__ x, const float *__restrict__ dy,
+                                                               const float *__restrict__ in0, const float *__restrict__ mean,
+                                                               const float *__restrict__ std_inv, float *__restrict__ out0,
+                                                               float *__restrict__ out1, int N, int C, int S, int splits) {
+    __shared__ float sm[8];
+    const int c = blockIdx.x, split = blockIdx.y;
+    float mu = 0.f, si = 0.f;
+    if (MODE == 1) mu = bn_sum_partials(in0, c, C, splits) / (float)((long long)N * S);
+    if (MODE == 2) { mu = mean[c]; si = std_inv[c]; }
+    float a0 = 0.f, a1 = 0.f;
+    for (int n = split; n < N; n += splits) {
+        const long long base = ((long long)n * C + c) * S;
+        for (int s = threadIdx.x; s < S; s += 256) {
+            const float v = __ldg(x + base + s);
+            if (MODE == 0) a0 += v;
+            if (MODE == 1) { const float d = v - mu; a0 += d * d; }
+            if (MODE == 2) { const float g = __ldg(dy + base + s); a0 += g; a1 += g * ((v - mu) * si); }
+        }
+    }
+    a0 = bn_block_sum(a0, sm);
+    if (MODE == 2) a1 = bn_block_sum(a1, sm);
+    if (threadIdx.x == 0) {
+        out0[(long long)split * C + c] = a0;
+        if (MODE == 2) out1[(long long)split * C + c] = a1;
+    }
+}
+template <int MODE>
+__global__ void __launch_bounds__(256) bn_reduce_rows_kernel(const float *__restrict__ x, const float *__restrict__ dy,
+                                                             const float *__restrict__ in0, const float *__restrict__ mean,
+                                                             const float *__restrict__ std_inv, float *__restrict__ out0,
+                                                             float *__restrict__ out1, int N, int C, int splits) {
+    __shared__ float s0[8][32], s1[8][32];
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx, split = blockIdx.y;
+    const bool live = c < C;
+    float mu = 0.f, si = 0.f;
+    if (MODE == 1 && live) mu = bn_sum_partials(in0, c, C, splits) / (float)N;
+    if (MODE == 2 && live) { mu = mean[c]; si = std_inv[c]; }
+    float a0 = 0.f, a1 = 0.f;
+    if (live) {
+        for (int n = split * 8 + ry; n < N; n += splits * 8) {
+            const float v = __ldg(x + (long long)n * C + c);
+            if (MODE == 0) a0 += v;
+            if (MODE == 1) { const float d = v - mu; a0 += d * d; }
+            if (MODE == 2) { const float g = __ldg(dy + (long long)n * C + c); a0 += g; a1 += g * ((v - mu) * si); }
+        }
+    }
+    s0[ry][cx] = a0; s1[ry][cx] = a1;
+    __syncthreads();
+    if (ry == 0 && live) {
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; r++) { t0 += s0[r][cx]; t1 += s1[r][cx]; }
+        out0[(long long)split * C + c] = t0;
+        if (MODE == 2) out1[(long long)split * C + c] = t1;
+    }
+}
+
+// mean, 1/std and the running statistics of every channel (training), or the running statistics as they are (inference)
+__global__ void __launch_bounds__(256) bn_finalize_fwd_kernel(const float *__restrict__ sums, const float *__restrict__ sqs,
+                                                              float *__restrict__ running_mean, float *__restrict__ running_var,
+                                                              float *__restrict__ mean_out, float *__restrict__ std_inv_out, int C,
+                                                              int splits, float M, float momentum, float eps, int training) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    if (training) {
+        const float mu = bn_sum_partials(sums, c, C, splits) / M;
+        const float var = bn_sum_partials(sqs, c, C, splits) / M;
+        mean_out[c] = mu;
+        std_inv_out[c] = 1.0f / sqrtf(var + eps);
+        running_mean[c] = (1.0f - momentum) * running_mean[c] + momentum * mu;
+        running_var[c] = (1.0f - momentum) * running_var[c] + momentum * var;
+    } else {
+        mean_out[c] = running_mean[c];
+        std_inv_out[c] = 1.0f / sqrtf(running_var[c] + eps);
+    }
+}
+__global__ void __launch_bounds__(256) bn_finalize_bwd_kernel(const float *__restrict__ p0, const float *__restrict__ p1,
+                                                              float *__restrict__ dbeta, float *__restrict__ dgamma, int C, int splits) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    dbeta[c] = bn_sum_partials(p0, c, C, splits);
+    dgamma[c] = bn_sum_partials(p1, c, C, splits);
+}
+
+// y = gamma * (x - mean) * std_inv + beta
+__global__ void __launch_bounds__(256) bn_normalize_kernel(const float *__restrict__ x, const float *__restrict__ mean,
+                                                           const float *__restrict__ std_inv, const float *__restrict__ gamma,
+                                                           const float *__restrict__ beta, float *__restrict__ y, long long total, int C,
+                                                           int S) {
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    if (total < (1LL << 31)) {                  // 32-bit index arithmetic: the 64-bit divisions cost more than the traffic
+        for (unsigned e = (unsigned)tid; e < (unsigned)total; e += (unsigned)nthr) {
+            const unsigned c = (e / (unsigned)S) % (unsigned)C;
+            y[e] = __ldg(gamma + c) * ((__ldg(x + e) - __ldg(mean + c)) * __ldg(std_inv + c)) + __ldg(beta + c);
+        }
+        return;
+    }
+    for (long long e = tid; e < total; e += nthr) {
+        const int c = (int)((e / S) % C);
+        y[e] = __ldg(gamma + c) * ((__ldg(x + e) - __ldg(mean + c)) * __ldg(std_inv + c)) + __ldg(beta + c);
+    }
+}
+// dx = (1/M) * std_inv * (M * dxh - sum dxh - x_hat * sum dxh * x_hat), dxh = dy * gamma; the sums are gamma * dbeta and gamma * dgamma
+__global__ void __launch_bounds__(256) bn_dx_kernel(const float *__restrict__ dy, const float *__restrict__ x, const float *__restrict__ mean,
+                                                    const float *__restrict__ std_inv, const float *__restrict__ gamma,
+                                                    const float *__restrict__ dbeta, const float *__restrict__ dgamma,
+                                                    float *__restrict__ dx, long long total, int C, int S, float M) {
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    const float inv_M = 1.0f / M;
+    const bool small = total < (1LL << 31);
+    for (long long e = tid; e < total; e += nthr) {
+        const int c = small ? (int)(((unsigned)e / (unsigned)S) % (unsigned)C) : (int)((e / S) % C);
+        const float g = __ldg(gamma + c), si = __ldg(std_inv + c);
+        const float xh = (__ldg(x + e) - __ldg(mean + c)) * si;
+        const float dxh = __ldg(dy + e) * g;
+        dx[e] = inv_M * si * (M * dxh - g * __ldg(dbeta + c) - xh * (g * __ldg(dgamma + c)));
+    }
+}
+
+static int bn_splits(int N, int C, int S) {
+    long long blocks = S > 1 ? C : (C + 31) / 32;
+    long long rows = S > 1 ? N : (N + 7) / 8;
+    long long s = ((long long)rt().sm_count * 4 + blocks - 1) / blocks;
+    if (s > rows) s = rows;
+    if (s > BN_MAX_SPLITS) s = BN_MAX_SPLITS;
+    return s < 1 ? 1 : (int)s;
+}
+template <int MODE>
+static cudaError_t bn_reduce(const float *x, const float *dy, const float *in0, const float *mean, const float *std_inv, float *out0,
+                             float *out1, int N, int C, int S, int splits) {
+    cudaStream_t st = rt().stream;
+    if (S > 1) bn_reduce_planes_kernel<MODE><<<dim3(C, splits), 256, 0, st>>>(x, dy, in0, mean, std_inv, out0, out1, N, C, S, splits);
+    else bn_reduce_rows_kernel<MODE><<<dim3((C + 31) / 32, splits), 256, 0, st>>>(x, dy, in0, mean, std_inv, out0, out1, N, C, splits);
+    count_launch();
+    return cudaGetLastError();
+}
+
+}  // namespace seera
+
+using namespace seera;
+
+extern "C" {
+
+int seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta, float *running_mean, float *running_var, float *y,
+                        float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training) {
+    SEERA_ENSURE();
+    if (N < 1 || C < 1 || S < 1 || C > 65535 || !x || !gamma || !beta || !running_mean || !running_var || !y || !mean_out || !std_inv_out)
+        return fail(SEERA_E_ARG, "batchnorm_fwd: bad argument");
+    const long long total = (long long)N * C * S;
+    cudaStream_t st = rt().stream;
+    cudaError_t e = cudaSuccess;
+    float *sums = nullptr, *sqs = nullptr;
+    int splits = 1;
+    if (training) {
+        splits = bn_splits(N, C, S);
+        sums = (float *)scratch_alloc((size_t)2 * splits * C * sizeof(float));
+        if (!sums) return SEERA_E_OOM;
+        sqs = sums + (size_t)splits * C;
+        e = bn_reduce<0>(x, nullptr, nullptr, nullptr, nullptr, sums, nullptr, N, C, S, splits);
+        if (e == cudaSuccess) e = bn_reduce<1>(x, nullptr, sums, nullptr, nullptr, sqs, nullptr, N, C, S, splits);
+    }
+    if (e == cudaSuccess) {
+        bn_finalize_fwd_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, sqs, running_mean, running_var, mean_out, std_inv_out, C, splits,
+                                                                (float)((long long)N * S), momentum, eps, training);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) {
+        bn_normalize_kernel<<<stride_grid(total), 256, 0, st>>>(x, mean_out, std_inv_out, gamma, beta, y, total, C, S);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    if (sums) scratch_free(sums);
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, "batchnorm_fwd");
+}
+
+int seera_batchnorm_bwd(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
+                        float *dgamma, float *dbeta, int N, int C, int S) {
+    SEERA_ENSURE();
+    if (N < 1 || C < 1 || S < 1 || C > 65535 || !dy || !x || !mean || !std_inv || !gamma || !dx || !dgamma || !dbeta)
+        return fail(SEERA_E_ARG, "batchnorm_bwd: bad argument");
+    const long long total = (long long)N * C * S;
+    const int splits = bn_splits(N, C, S);
+    float *p0 = (float *)scratch_alloc((size_t)2 * splits * C * sizeof(float));
+    if (!p0) return SEERA_E_OOM;
+    float *p1 = p0 + (size_t)splits * C;
+    cudaStream_t st = rt().stream;
+    cudaError_t e = bn_reduce<2>(x, dy, nullptr, mean, std_inv, p0, p1, N, C, S, splits);
+    if (e == cudaSuccess) {
+        bn_finalize_bwd_kernel<<<(C + 255) / 256, 256, 0, st>>>(p0, p1, dbeta, dgamma, C, splits);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) {
+        bn_dx_kernel<<<stride_grid(total), 256, 0, st>>>(dy, x, mean, std_inv, gamma, dbeta, dgamma, dx, total, C, S, (float)((long long)N * S));
+        count_launch();
+        e = cudaGetLastError();
+    }
+    scratch_free(p0);
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, "batchnorm_bwd");
+}
+
+}  // extern "C"

@@ -167,6 +167,13 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("pool_bytes_reserved", []() { return seera_pool_bytes_reserved(); });
     m.def("upload_f32", [](uptr dst, arr_f a) { ck(seera_upload(P<void>(dst), a.data(), (size_t)a.size() * 4)); });
     m.def("upload_from_host_ptr", [](uptr dst, uptr host, size_t nbytes) { ck(seera_upload(P<void>(dst), P<const void>(host), nbytes)); });
+    m.def("batchnorm_fwd", [](uptr x, uptr g, uptr b, uptr rm, uptr rv, uptr y, uptr mean, uptr si, int N, int C, int S, float momentum,
+                              float eps, bool training) {
+        ck(seera_batchnorm_fwd(P<const F>(x), P<const F>(g), P<const F>(b), P<F>(rm), P<F>(rv), P<F>(y), P<F>(mean), P<F>(si), N, C, S,
+                               momentum, eps, training ? 1 : 0)); });
+    m.def("batchnorm_bwd", [](uptr dy, uptr x, uptr mean, uptr si, uptr g, uptr dx, uptr dg, uptr db, int N, int C, int S) {
+        ck(seera_batchnorm_bwd(P<const F>(dy), P<const F>(x), P<const F>(mean), P<const F>(si), P<const F>(g), P<F>(dx), P<F>(dg),
+                               P<F>(db), N, C, S)); });
     m.def("onehot_f32", [](uptr labels, uptr out, int n, int classes) { ck(seera_onehot_f32(P<const int>(labels), P<F>(out), n, classes)); });
     m.def("stream_delay", [](int us) { ck(seera_stream_delay(us)); });
     m.def("copy_upload", [](uptr dst, uptr host, size_t nbytes) { ck(seera_copy_upload(P<void>(dst), P<const void>(host), nbytes)); });

@@ -509,6 +509,103 @@ class ConvTranspose2D(_ParamLayer):
                 f"stride={self.stride}, act={self.layeract})")
 
 
+class _BatchNorm(_ParamLayer):
+    """Batch normalisation on the device (the reference computes it on the host even in its GPU path: Seera.py:511-623,
+    Seera_init.py:870-921, Seera_Engine.py:381-415).  gamma / beta are the layer's `weights` / `bais` (as in the reference)
+    and live in the model's parameter arena; the running statistics are device buffers, readable as NumPy arrays through
+    `running_mean` / `running_var`.  In a data-parallel run each rank normalises with the statistics of its own shard."""
+
+    def __init__(self, num, momentum=0.1, eps=1e-5):
+        super().__init__()
+        self.momentum, self.eps, self.training = momentum, eps, True
+        self._w_init = np.ones((num,), np.float32)
+        self._b_init = np.zeros((num,), np.float32)
+        self.weights = Tensor(self._w_init, is_leaf=True)
+        self.bais = Tensor(self._b_init, is_leaf=True)
+        self._rm = cuten(np.zeros(num, np.float32))
+        self._rv = cuten(np.ones(num, np.float32))
+        self._num = num
+
+    gamma = property(lambda self: self.weights)
+    beta = property(lambda self: self.bais)
+
+    @property
+    def running_mean(self):
+        return self._rm.to_host_f32().copy()
+
+    @running_mean.setter
+    def running_mean(self, v):
+        sc.upload_f32(self._rm.main_ptr, np.ascontiguousarray(v, np.float32).reshape(self._num))
+
+    @property
+    def running_var(self):
+        return self._rv.to_host_f32().copy()
+
+    @running_var.setter
+    def running_var(self, v):
+        sc.upload_f32(self._rv.main_ptr, np.ascontiguousarray(v, np.float32).reshape(self._num))
+
+    def _shape_ok(self, shape):
+        raise NotImplementedError
+
+    def forward(self):
+        x = self.inputs = self.inpobj.outputs
+        xv = x.value
+        self._shape_ok(xv.shape)
+        N, C = xv.shape[0], xv.shape[1]
+        S = 1
+        for d in xv.shape[2:]:
+            S *= d
+        g, b = self.weights, self.bais
+        y, mean, si = _new(xv.shape), _new((C,)), _new((C,))
+        sc.batchnorm_fwd(xv.main_ptr, g.value.main_ptr, b.value.main_ptr, self._rm.main_ptr, self._rv.main_ptr, y.main_ptr,
+                         mean.main_ptr, si.main_ptr, N, C, S, float(self.momentum), float(self.eps), bool(self.training))
+        out = Tensor(y)
+        out._parents = (x, g, b)
+
+        def backward(dy, need_dx=not x.is_leaf):
+            dg, db = g._grad_target(), b._grad_target()
+            dx = _new(xv.shape)
+            sc.batchnorm_bwd(dy.main_ptr, xv.main_ptr, mean.main_ptr, si.main_ptr, g.value.main_ptr, dx.main_ptr, dg.main_ptr,
+                             db.main_ptr, N, C, S)
+            g._accumulate(dg)
+            b._accumulate(db)
+            hook = getattr(getattr(self, "_model", None), "_on_grad_ready", None)
+            if hook is not None and g.grad is g._grad_slot and b.grad is b._grad_slot:
+                hook(g)
+            if need_dx:
+                x._accumulate(dx)
+        out._backward = backward
+        self.outputs = out
+        return out
+
+
+class BatchNorm1d(_BatchNorm):
+    def __init__(self, num_features, momentum=0.1, eps=1e-5):
+        super().__init__(num_features, momentum, eps)
+        self.num_features = num_features
+
+    def _shape_ok(self, shape):
+        if len(shape) != 2 or shape[1] != self.num_features:
+            raise ValueError(f"BatchNorm1d({self.num_features}) expects (N, {self.num_features}), got {tuple(shape)}")
+
+    def __repr__(self):
+        return f"BatchNorm1d({self.num_features})"
+
+
+class BatchNorm2d(_BatchNorm):
+    def __init__(self, num_channels, momentum=0.1, eps=1e-5):
+        super().__init__(num_channels, momentum, eps)
+        self.num_channels = num_channels
+
+    def _shape_ok(self, shape):
+        if len(shape) != 4 or shape[1] != self.num_channels:
+            raise ValueError(f"BatchNorm2d({self.num_channels}) expects (N, {self.num_channels}, H, W), got {tuple(shape)}")
+
+    def __repr__(self):
+        return f"BatchNorm2d({self.num_channels})"
+
+
 class MaxPool2D(Layer):
     def __init__(self, pool_size=(2, 2), stride=1, padding=0):
         super().__init__()
@@ -688,7 +785,17 @@ class Sequential:
         return out
 
     def predict(self, X):
-        return self.forward(X)
+        """Forward in evaluation mode: BatchNorm layers normalise with their running statistics (Seera.py:690-700)."""
+        self._set_mode(False)
+        try:
+            return self.forward(X)
+        finally:
+            self._set_mode(True)
+
+    def _set_mode(self, training=True):
+        for l in self.model:
+            if hasattr(l, "training"):
+                l.training = training
 
     def zero_grad(self):
         """Parameter gradients restart from zero: the next backward writes them instead of adding."""
@@ -827,6 +934,9 @@ class Sequential:
                                   "layeract": l.layeract, "stride": l.stride, "zero_padding": l.zero_padding}
             elif isinstance(l, MaxPool2D):
                 info["config"] = {"pool_size": l.pool_size, "stride": l.stride, "padding": l.padding}
+            elif isinstance(l, _BatchNorm):
+                info["config"] = {"num_features" if isinstance(l, BatchNorm1d) else "num_channels": l._num, "momentum": l.momentum,
+                                  "eps": l.eps, "running_mean": l.running_mean, "running_var": l.running_var}
             elif isinstance(l, Unpool2D_Nearest):
                 info["config"] = {"size": l.size}
             if isinstance(l, _ParamLayer):
@@ -852,6 +962,10 @@ class Sequential:
                                                                  zero_padding=c.get("zero_padding", 0))
             elif k == "MaxPool2D":
                 l = MaxPool2D(pool_size=c["pool_size"], stride=c["stride"], padding=c["padding"])
+            elif k in ("BatchNorm1d", "BatchNorm2d"):
+                l = BatchNorm1d(c["num_features"], c["momentum"], c["eps"]) if k == "BatchNorm1d" else \
+                    BatchNorm2d(c["num_channels"], c["momentum"], c["eps"])
+                l.running_mean, l.running_var = c["running_mean"], c["running_var"]
             elif k in ("Unpool2D_Nearest", "UpSampling2D_Nearest"):
                 l = Unpool2D_Nearest(size=c["size"])
             elif k == "Flatten":

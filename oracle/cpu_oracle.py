@@ -276,3 +276,26 @@ def mul(A, B):
     o = np.empty_like(A)
     lib().so_mul(_p(A), _p(B), _p(o), A.size)
     return o
+
+
+# ---- batch normalisation ---------------------------------------------------------
+def batchnorm_forward(X, gamma, beta, running_mean, running_var, momentum, eps, training):
+    """Returns (y, x_hat, mean, std_inv); running_mean / running_var (fp32 arrays) are updated in place when training."""
+    X = _f(X)
+    N, C = X.shape[0], X.shape[1]
+    S = int(np.prod(X.shape[2:])) if X.ndim > 2 else 1
+    out, xh = np.empty_like(X), np.empty_like(X)
+    mean, si = np.empty(C, np.float32), np.empty(C, np.float32)
+    assert running_mean.dtype == np.float32 and running_var.dtype == np.float32
+    lib().so_batchnorm_fwd(_p(X), _p(_f(gamma)), _p(_f(beta)), _p(running_mean), _p(running_var), _p(out), _p(xh), _p(mean), _p(si),
+                           N, C, S, _cf(momentum), _cf(eps), int(bool(training)))
+    return out, xh, mean, si
+
+
+def batchnorm_backward(dout, x_hat, std_inv, gamma):
+    dout, x_hat = _f(dout), _f(x_hat)
+    N, C = dout.shape[0], dout.shape[1]
+    S = int(np.prod(dout.shape[2:])) if dout.ndim > 2 else 1
+    dx, dg, db = np.empty_like(dout), np.empty(C, np.float32), np.empty(C, np.float32)
+    lib().so_batchnorm_bwd(_p(dout), _p(x_hat), _p(_f(std_inv)), _p(_f(gamma)), _p(dx), _p(dg), _p(db), N, C, S)
+    return dx, dg, db

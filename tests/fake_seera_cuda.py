@@ -348,6 +348,28 @@ def compute_wait_copy(): pass
 def copy_synchronize(): pass
 
 
+def batchnorm_fwd(x, g, b, rm, rv, y, mean, si, N, C, S, momentum, eps, training):
+    _count("batchnorm_fwd")
+    shape = (N, C, S)
+    rmv, rvv = _view(rm, C).copy(), _view(rv, C).copy()
+    yy, _, mu, s = co.batchnorm_forward(F(x, shape), _view(g, C), _view(b, C), rmv, rvv, momentum, eps, training)
+    F(y, shape)[:] = yy
+    _view(mean, C)[:] = mu
+    _view(si, C)[:] = s
+    _view(rm, C)[:] = rmv
+    _view(rv, C)[:] = rvv
+
+
+def batchnorm_bwd(dy, x, mean, si, g, dx, dg, db, N, C, S):
+    _count("batchnorm_bwd")
+    shape = (N, C, S)
+    xh = ((F(x, shape) - _view(mean, C).reshape(1, C, 1)) * _view(si, C).reshape(1, C, 1)).astype(np.float32)
+    a, b, c = co.batchnorm_backward(F(dy, shape), xh, _view(si, C), _view(g, C))
+    F(dx, shape)[:] = a
+    _view(dg, C)[:] = b
+    _view(db, C)[:] = c
+
+
 def onehot_f32(labels, out, n, classes):
     lab = _view(labels, n, np.int32)
     F(out, (n, classes))[:] = (lab[:, None] == np.arange(classes)[None, :]).astype(np.float32)

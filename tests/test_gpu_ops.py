@@ -294,3 +294,40 @@ def test_bad_arguments_return_status_not_crash(E):
     assert L.seera_broadcast_add_4d(1, 1, 1, 1, 2, 3, 4, 1, 5, 3, 4) == 2
     L.seera_clear_status()
     assert L.seera_last_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(7, 5), (64, 300), (4, 6, 3, 5), (16, 33, 14, 14), (3, 1, 1, 1), (512, 64)])
+def test_batchnorm_forward_and_backward(shape):
+    """seera_batchnorm_fwd / _bwd against the oracle (training and inference statistics, running-statistics update)."""
+    import ctypes
+    from ml_framework_b200 import capi
+    L = capi.load()
+    capi.check(L.seera_init(capi.default_device()))
+    rs = np.random.RandomState(sum(shape))
+    X = (rs.standard_normal(shape) * 2 + 1).astype(np.float32)
+    N, C = shape[0], shape[1]
+    S = int(np.prod(shape[2:])) if len(shape) > 2 else 1
+    g, b = rs.standard_normal(C).astype(np.float32), rs.standard_normal(C).astype(np.float32)
+    d = rs.standard_normal(shape).astype(np.float32)
+    up = lambda a: L.seera_to_device(np.ascontiguousarray(a).ctypes.data_as(ctypes.c_void_p), a.nbytes)
+    def down(p, shp):
+        a = np.empty(shp, np.float32)
+        capi.check(L.seera_to_host(a.ctypes.data_as(ctypes.c_void_p), p, a.nbytes))
+        return a
+    for training in (1, 0):
+        rm, rv = rs.standard_normal(C).astype(np.float32), (rs.rand(C) + 0.5).astype(np.float32)
+        rm0, rv0 = rm.copy(), rv.copy()
+        y_ref, xh_ref, mu_ref, si_ref = co.batchnorm_forward(X, g, b, rm0, rv0, 0.1, 1e-5, training)
+        dx_ref, dg_ref, db_ref = co.batchnorm_backward(d, xh_ref, si_ref, g)
+        xd, gd, bd, rmd, rvd, dd = up(X), up(g), up(b), up(rm), up(rv), up(d)
+        yd, mud, sid = L.seera_cuda_malloc(X.nbytes), L.seera_cuda_malloc(4 * C), L.seera_cuda_malloc(4 * C)
+        dxd, dgd, dbd = L.seera_cuda_malloc(X.nbytes), L.seera_cuda_malloc(4 * C), L.seera_cuda_malloc(4 * C)
+        capi.check(L.seera_batchnorm_fwd(xd, gd, bd, rmd, rvd, yd, mud, sid, N, C, S, 0.1, 1e-5, training))
+        capi.check(L.seera_batchnorm_bwd(dd, xd, mud, sid, gd, dxd, dgd, dbd, N, C, S))
+        assert rel_l2(down(yd, shape), y_ref) < 1e-5 and rel_l2(down(sid, (C,)), si_ref) < 1e-5
+        assert np.allclose(down(mud, (C,)), mu_ref, rtol=1e-5, atol=1e-6)
+        assert np.allclose(down(rmd, (C,)), rm0, rtol=1e-5, atol=1e-6) and np.allclose(down(rvd, (C,)), rv0, rtol=1e-5, atol=1e-6)
+        assert rel_l2(down(dxd, shape), dx_ref) < 2e-5
+        assert np.allclose(down(dgd, (C,)), dg_ref, rtol=1e-4, atol=1e-4) and np.allclose(down(dbd, (C,)), db_ref, rtol=1e-4, atol=1e-4)
+        for p in (xd, gd, bd, rmd, rvd, dd, yd, mud, sid, dxd, dgd, dbd):
+            L.seera_cuda_free(p)

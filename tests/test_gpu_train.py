@@ -251,3 +251,12 @@ def test_fit_pipeline_matches_the_synchronous_loop_on_the_device(T):
         assert np.array_equal(h, runs[0][0])
         for (w, b), (w0, b0) in zip(ws, runs[0][1]):
             assert np.array_equal(w, w0) and np.array_equal(b, b0)
+
+
+def test_batchnorm_model_against_reference_golden(T, golden_dir):
+    """BatchNorm2d / BatchNorm1d on the device inside a small CNN: two SGD steps (loss, predictions, every gradient and
+    weight, running statistics) and an evaluation-mode prediction against the unmodified reference (host BatchNorm)."""
+    from ml_framework_b200 import seera as S, seera_cuda as sc
+    from test_host_logic_cpu import _bn_model_against_golden
+    sc.set_precision(0)
+    _bn_model_against_golden(S, golden_dir, 2e-4)

@@ -172,6 +172,50 @@ def test_save_load_round_trip(host, tmp_path):
     assert np.array_equal(a, b)
 
 
+def _bn_model_against_golden(S, golden_dir, tol):
+    """Two SGD steps and an evaluation-mode prediction of the BatchNorm model against the unmodified reference."""
+    sys.path.insert(0, golden_dir)
+    import bn_case
+    gold = np.load(os.path.join(golden_dir, "bn_two_steps.npz"))
+    lays = bn_case.layers(S)
+    for i, (W, B) in bn_case.weights().items():
+        lays[i].set_weights(W, B)
+    model = S.Sequential(lays, device="cuda")
+    opt = S.SGD(model, lr=bn_case.LR, momentum=bn_case.MOMENTUM)
+    lossf = S.Loss().categorical_cross_entropy
+    X, Y = bn_case.data()
+    rel = lambda a, b: float(np.linalg.norm(np.asarray(a, np.float64).ravel() - np.asarray(b, np.float64).ravel()) /
+                             max(np.linalg.norm(np.asarray(b, np.float64).ravel()), 1e-12))
+    plist = [l for l in model.model if isinstance(l, S._ParamLayer)]
+    for s in range(bn_case.STEPS):
+        yp = model.forward(S.Tensor(X, is_leaf=True))
+        loss = lossf(yp, S.Tensor(Y, is_leaf=True))
+        model.zero_grad()
+        S.autograd4nn(loss)
+        assert abs(float(loss.value.to_host_f32().ravel()[0]) - float(gold["loss%d" % s])) < tol * max(1.0, float(gold["loss%d" % s]))
+        if s == 0:
+            assert rel(yp.to_numpy(), gold["pred0"]) < tol
+            model.gather_grads()
+            for k, l in enumerate(plist):
+                assert rel(l.weights.grad.to_host_f32(), gold["dW%d" % k]) < tol, ("dW", k)
+                if k in (0, 2):     # a bias that feeds a BatchNorm: its gradient is zero up to rounding noise on every engine
+                    assert np.max(np.abs(l.bais.grad.to_host_f32().ravel() - gold["db%d" % k].ravel())) < 1e-6, ("db", k)
+                else:
+                    assert rel(l.bais.grad.to_host_f32(), gold["db%d" % k]) < tol, ("db", k)
+        opt.step()
+        for k, l in enumerate(plist):
+            assert rel(l.weights.to_numpy(), gold["W%d_s%d" % (k, s)]) < tol, ("W", k, s)
+            assert rel(l.bais.to_numpy(), gold["b%d_s%d" % (k, s)]) < tol, ("b", k, s)
+    assert rel(lays[2].running_mean, gold["rm2"]) < tol and rel(lays[2].running_var, gold["rv2"]) < tol
+    assert rel(lays[6].running_mean, gold["rm6"]) < tol and rel(lays[6].running_var, gold["rv6"]) < tol
+    assert rel(model.predict(S.Tensor(X, is_leaf=True)).to_numpy(), gold["pred_eval"]) < tol
+    assert lays[2].training and lays[6].training                      # predict() restores training mode
+
+
+def test_batchnorm_layers_against_reference_golden(host, golden_dir):
+    _bn_model_against_golden(host.seera, golden_dir, 2e-5)
+
+
 def test_fit_pipeline_matches_the_synchronous_loop(host):
     """Sequential.fit (double-buffered staging, loss read one step late, last batch ragged) gives the history and the
     weights of the synchronous loop; integer labels expanded on the device give the same as host one-hot rows."""

@@ -126,3 +126,40 @@ def test_c1_two_steps_against_reference(name, E, golden_dir):
 def test_small_configs_two_steps_against_reference(name, E, case, golden_dir):
     work, n = cases.small_cases()[case]
     _check_steps(work, n, 2, np.load(golden_dir + "/%s_two_steps.npz" % case), E, 2e-5)
+
+
+def test_batchnorm_restatement_matches_the_reference_engine_and_numpy():
+    """so_batchnorm_fwd / _bwd against the compiled reference engine (bit for bit, same loops) and against the NumPy
+    formulas of the reference's fallback (Seera_init.py:893-912, Seera_Engine.py:401-412)."""
+    rs = np.random.RandomState(0)
+    for shape in [(7, 5), (4, 6, 3, 5), (1, 3, 2, 2)]:
+        X = (rs.standard_normal(shape) * 2 + 1).astype(np.float32)
+        C = shape[1]
+        g, b = rs.standard_normal(C).astype(np.float32), rs.standard_normal(C).astype(np.float32)
+        axes = (0, 2, 3) if len(shape) == 4 else (0,)
+        bs = (1, -1, 1, 1) if len(shape) == 4 else (1, -1)
+        for training in (True, False):
+            rm, rv = rs.standard_normal(C).astype(np.float32), (rs.rand(C) + 0.5).astype(np.float32)
+            rm0, rv0 = rm.copy(), rv.copy()
+            y, xh, mu, si = co.batchnorm_forward(X, g, b, rm, rv, 0.1, 1e-5, training)
+            m_np, v_np = (X.mean(axis=axes), X.var(axis=axes)) if training else (rm0, rv0)
+            xh_np = (X - m_np.reshape(bs)) / np.sqrt(v_np.reshape(bs) + 1e-5)
+            assert np.allclose(xh, xh_np, rtol=2e-5, atol=2e-5) and np.allclose(y, g.reshape(bs) * xh_np + b.reshape(bs), rtol=2e-5, atol=2e-5)
+            if training:
+                assert np.allclose(rm, 0.9 * rm0 + 0.1 * m_np, atol=1e-6) and np.allclose(rv, 0.9 * rv0 + 0.1 * v_np, atol=1e-6)
+            else:
+                assert np.array_equal(rm, rm0) and np.array_equal(rv, rv0)
+            d = rs.standard_normal(shape).astype(np.float32)
+            dx, dg, db = co.batchnorm_backward(d, xh, si, g)
+            M = X.size // C
+            dxh = d * g.reshape(bs)
+            dx_np = (1.0 / M) * si.reshape(bs) * (M * dxh - dxh.sum(axis=axes).reshape(bs) - xh * (dxh * xh).sum(axis=axes).reshape(bs))
+            assert np.allclose(dx, dx_np, rtol=1e-4, atol=1e-5) and np.allclose(dg, (d * xh).sum(axis=axes), rtol=1e-4, atol=1e-5)
+            assert np.allclose(db, d.sum(axis=axes), rtol=1e-4, atol=1e-5)
+            if REF is not None:
+                rm2, rv2 = rm0.copy(), rv0.copy()
+                y2, xh2, si2 = REF.batchnorm_forward(X, g, b, rm2, rv2, 0.1, 1e-5, training, len(shape) == 4)
+                assert np.array_equal(y, y2) and np.array_equal(xh, xh2) and np.array_equal(si, si2)
+                assert np.array_equal(rm, rm2) and np.array_equal(rv, rv2)
+                r = REF.batchnorm_backward(d, xh2, si2, g, M, len(shape) == 4)
+                assert all(np.array_equal(p, q) for p, q in zip((dx, dg, db), r))
