@@ -127,6 +127,11 @@ int   seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta,
                           float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training);
 int   seera_batchnorm_bwd(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
                           float *dgamma, float *dbeta, int N, int C, int S);
+/* Concatenation of two tensors along axis 1 ([N, n1] and [N, n2] rows, n = C*H*W of each sample) and the backward
+ * split of the joined gradient, one launch each.  Replaces the per-sample cudaMemcpy loops of cuten.concatenate2D /
+ * concatenate1D and their backward forms (cuTen.py:688-796, used by Seera_init.py:764-779, Seera_Engine.py:418-429). */
+int   seera_concat_fwd(const float *a, const float *b, float *out, int N, int n1, int n2);
+int   seera_concat_bwd(const float *dout, float *da, float *db, int N, int n1, int n2);
 /* One-hot rows on the device: out[i, c] = (labels[i] == c) as float, n x classes.  Lets a training loop upload 4 bytes
  * of label per sample instead of a one-hot row (Sequential.fit of the reference takes host one-hot arrays and uploads
  * them batch by batch, Seera.py:748-755). */

@@ -170,6 +170,22 @@ int launch_broadcast(const float *A, const float *B, float *C, const int a[4], c
 
 using namespace seera;
 
+// element e of the joined [N, n1 + n2] matrix lives in part a (column < n1) or part b; JOIN copies parts -> joined, else joined -> parts
+template <bool JOIN, class V>
+__global__ void __launch_bounds__(256) concat_kernel(const float *a_, const float *b_, float *joined_, long long total, int n1, int n2) {
+    V *a = reinterpret_cast<V *>(const_cast<float *>(a_)), *b = reinterpret_cast<V *>(const_cast<float *>(b_));
+    V *joined = reinterpret_cast<V *>(joined_);
+    const int n = n1 + n2;
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    for (long long e = tid; e < total; e += nthr) {
+        const long long row = e / n;
+        const int col = (int)(e - row * n);
+        V *part = col < n1 ? a + row * n1 + col : b + row * n2 + (col - n1);
+        if (JOIN) joined[e] = *part;
+        else *part = joined[e];
+    }
+}
+
 extern "C" {
 int seera_cuda_relu_fwd(const float *x, float *o, float *g, int n)    { return launch_unary(x, o, g, n, OpRelu{}, "cuda_relu_fwd"); }
 int seera_cuda_sigmoid_fwd(const float *x, float *o, float *g, int n) { return launch_unary(x, o, g, n, OpSigmoid{}, "cuda_sigmoid_fwd"); }
@@ -200,4 +216,30 @@ int seera_broadcast_mul_4d(const float *A, const float *B, float *C, int aN, int
     int a[4] = {aN, aC, aH, aW}, b[4] = {bN, bC, bH, bW};
     return launch_broadcast(A, B, C, a, b, BMul{}, "broadcast_mul_4d");
 }
+
+// ---- concatenation along axis 1 of [N, n1] and [N, n2] rows (n = C*H*W per sample), and its backward split ---------
+// The reference issues two cudaMemcpy per sample from a Python loop (cuTen.py:688-796); here each direction is one launch.
+int seera_concat_fwd(const float *a, const float *b, float *out, int N, int n1, int n2) {
+    SEERA_ENSURE();
+    if (N < 0 || n1 < 0 || n2 < 0 || (N > 0 && ((n1 > 0 && !a) || (n2 > 0 && !b) || !out))) return fail(SEERA_E_ARG, "concat_fwd: bad argument");
+    const long long total = (long long)N * (n1 + n2);
+    if (total == 0) return SEERA_OK;
+    const bool v4 = n1 % 4 == 0 && n2 % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(out);
+    if (v4) concat_kernel<true, float4><<<stride_grid(total / 4), 256, 0, rt().stream>>>(a, b, out, total / 4, n1 / 4, n2 / 4);
+    else concat_kernel<true, float><<<stride_grid(total), 256, 0, rt().stream>>>(a, b, out, total, n1, n2);
+    SEERA_LAUNCH_CHECK("concat_fwd");
+    return SEERA_OK;
+}
+int seera_concat_bwd(const float *dout, float *da, float *db, int N, int n1, int n2) {
+    SEERA_ENSURE();
+    if (N < 0 || n1 < 0 || n2 < 0 || (N > 0 && ((n1 > 0 && !da) || (n2 > 0 && !db) || !dout))) return fail(SEERA_E_ARG, "concat_bwd: bad argument");
+    const long long total = (long long)N * (n1 + n2);
+    if (total == 0) return SEERA_OK;
+    const bool v4 = n1 % 4 == 0 && n2 % 4 == 0 && aligned16(da) && aligned16(db) && aligned16(dout);
+    if (v4) concat_kernel<false, float4><<<stride_grid(total / 4), 256, 0, rt().stream>>>(da, db, const_cast<float *>(dout), total / 4, n1 / 4, n2 / 4);
+    else concat_kernel<false, float><<<stride_grid(total), 256, 0, rt().stream>>>(da, db, const_cast<float *>(dout), total, n1, n2);
+    SEERA_LAUNCH_CHECK("concat_bwd");
+    return SEERA_OK;
+}
+
 }  // extern "C"

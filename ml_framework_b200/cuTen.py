@@ -411,25 +411,12 @@ class cuten:
                                            strideh, stridew, padh, padw)
         return cuten._wrap(p, (N, Cout, Ho, Wo))
 
-    # ---- concatenation along axis 1: per-sample device-to-device copies ------------------------------------------------
-    @staticmethod
-    def _concatenate(ptr1, ptr2, ptr3, n1, n2):
-        seera_cuda.cuda_memcopy_devicetodevice(ptr3, ptr1, n1)
-        seera_cuda.cuda_memcopy_devicetodevice(ptr3 + n1 * 4, ptr2, n2)
-        return ptr3
-
-    @staticmethod
-    def _concatenate_backward(ptr_out, ptr1, ptr2, n1, n2):
-        seera_cuda.cuda_memcopy_devicetodevice(ptr1, ptr_out, n1)
-        seera_cuda.cuda_memcopy_devicetodevice(ptr2, ptr_out + n1 * 4, n2)
-
+    # ---- concatenation along axis 1: one strided-copy launch each way (the reference loops over the samples) ---------------
     def _concat(self, other, out_shape):
         N = self.shape[0]
         n1, n2 = self.size // N, other.size // N
-        a, b = self.main_ptr, other.main_ptr
         p = seera_cuda.cuda_malloc_f32(self.size + other.size)
-        for i in range(N):
-            cuten._concatenate(a + n1 * i * 4, b + n2 * i * 4, p + (n1 + n2) * i * 4, n1, n2)
+        seera_cuda.concat_fwd(self.main_ptr, other.main_ptr, p, N, n1, n2)
         return cuten._wrap(p, out_shape)
 
     def concatenate2D(self, other):
@@ -451,10 +438,8 @@ class cuten:
             raise ValueError("[cuTen]: Batch mismatch in backward")
         N = a.shape[0]
         n1, n2 = a.size // N, b.size // N
-        src = dout.main_ptr
         p1, p2 = seera_cuda.cuda_malloc_f32(a.size), seera_cuda.cuda_malloc_f32(b.size)
-        for i in range(N):
-            cls._concatenate_backward(src + (n1 + n2) * i * 4, p1 + n1 * i * 4, p2 + n2 * i * 4, n1, n2)
+        seera_cuda.concat_bwd(dout.main_ptr, p1, p2, N, n1, n2)
         return cls._wrap(p1, a.shape), cls._wrap(p2, b.shape)
 
     @classmethod

@@ -606,6 +606,37 @@ class BatchNorm2d(_BatchNorm):
         return f"BatchNorm2d({self.num_channels})"
 
 
+class Concatenate(Layer):
+    """Joins the outputs of two layers along axis 1 (Seera.py:486-505); one strided-copy launch forward, one backward."""
+
+    def __call__(self, *input_layers):
+        if len(input_layers) != 2:
+            raise ValueError("Only 2 layers supported for concatenation.")
+        for l in input_layers:
+            if not isinstance(l, Layer):
+                raise TypeError("All inputs must be Layer instances.")
+        self.input_layers = input_layers
+        return self
+
+    def forward(self):
+        a, b = self.inputs = [l.outputs for l in self.input_layers]
+        av, bv = a.value, b.value
+        y = av.concatenate2D(bv) if len(av.shape) >= 4 else av.concatenate1D(bv)
+        out = Tensor(y)
+        out._parents = (a, b)
+
+        def backward(g):
+            da, db = cuten._concat_backward(g, av, bv)
+            a._accumulate(da)
+            b._accumulate(db)
+        out._backward = backward
+        self.outputs = out
+        return out
+
+    def __repr__(self):
+        return "Concatenate Layer"
+
+
 class MaxPool2D(Layer):
     def __init__(self, pool_size=(2, 2), stride=1, padding=0):
         super().__init__()
@@ -970,6 +1001,8 @@ class Sequential:
                 l = Unpool2D_Nearest(size=c["size"])
             elif k == "Flatten":
                 l = Flatten()
+            elif k == "Concatenate":
+                l = Concatenate()
             else:
                 raise ValueError(f"Unknown layer type: {k}")
             if "weights" in info:

@@ -370,6 +370,18 @@ def batchnorm_bwd(dy, x, mean, si, g, dx, dg, db, N, C, S):
     _view(db, C)[:] = c
 
 
+def concat_fwd(a, b, out, N, n1, n2):
+    _count("concat_fwd")
+    F(out, (N, n1 + n2))[:] = np.concatenate([F(a, (N, n1)), F(b, (N, n2))], axis=1)
+
+
+def concat_bwd(dout, da, db, N, n1, n2):
+    _count("concat_bwd")
+    d = F(dout, (N, n1 + n2))
+    F(da, (N, n1))[:] = d[:, :n1]
+    F(db, (N, n2))[:] = d[:, n1:]
+
+
 def onehot_f32(labels, out, n, classes):
     lab = _view(labels, n, np.int32)
     F(out, (n, classes))[:] = (lab[:, None] == np.arange(classes)[None, :]).astype(np.float32)

@@ -331,3 +331,28 @@ def test_batchnorm_forward_and_backward(shape):
         assert np.allclose(down(dgd, (C,)), dg_ref, rtol=1e-4, atol=1e-4) and np.allclose(down(dbd, (C,)), db_ref, rtol=1e-4, atol=1e-4)
         for p in (xd, gd, bd, rmd, rvd, dd, yd, mud, sid, dxd, dgd, dbd):
             L.seera_cuda_free(p)
+
+
+@pytest.mark.parametrize("N,n1,n2", [(1, 1, 1), (5, 7, 3), (16, 64 * 14 * 14, 32 * 14 * 14), (3, 4, 13), (257, 1000, 24)])
+def test_concatenate_forward_and_backward(N, n1, n2):
+    """seera_concat_fwd / _bwd (vector and scalar paths, offset pointers) against NumPy."""
+    from ml_framework_b200 import capi
+    L = capi.load()
+    capi.check(L.seera_init(capi.default_device()))
+    rs = np.random.RandomState(N + n1 + n2)
+    A, B = rs.standard_normal((N, n1)).astype(np.float32), rs.standard_normal((N, n2)).astype(np.float32)
+    up = lambda a: L.seera_to_device(np.ascontiguousarray(a).ctypes.data_as(ctypes.c_void_p), a.nbytes)
+    def down(p, shp):
+        a = np.empty(shp, np.float32)
+        capi.check(L.seera_to_host(a.ctypes.data_as(ctypes.c_void_p), p, a.nbytes))
+        return a
+    ad, bd = up(A), up(B)
+    od = L.seera_cuda_malloc(4 * N * (n1 + n2))
+    capi.check(L.seera_concat_fwd(ad, bd, od, N, n1, n2))
+    J = np.concatenate([A, B], axis=1)
+    assert np.array_equal(down(od, (N, n1 + n2)), J)
+    da, db = L.seera_cuda_malloc(4 * N * n1), L.seera_cuda_malloc(4 * N * n2)
+    capi.check(L.seera_concat_bwd(od, da, db, N, n1, n2))
+    assert np.array_equal(down(da, (N, n1)), A) and np.array_equal(down(db, (N, n2)), B)
+    for p in (ad, bd, od, da, db):
+        L.seera_cuda_free(p)

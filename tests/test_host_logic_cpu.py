@@ -216,6 +216,29 @@ def test_batchnorm_layers_against_reference_golden(host, golden_dir):
     _bn_model_against_golden(host.seera, golden_dir, 2e-5)
 
 
+def test_concatenate_layer_joins_and_splits(host):
+    """Concatenate of two branches (4-D and 2-D): forward equals np.concatenate along axis 1, backward hands each branch
+    its slice of the gradient; one concat launch per direction."""
+    S, ct = host.seera, host.cuTen.cuten
+    rs = np.random.RandomState(0)
+    for sa, sb in (((3, 2, 4, 4), (3, 5, 4, 4)), ((6, 7), (6, 3))):
+        A, B = rs.standard_normal(sa).astype(np.float32), rs.standard_normal(sb).astype(np.float32)
+        la, lb = S.Input(sa[1:]), S.Input(sb[1:])
+        la.inputs, lb.inputs = S.Tensor(A), S.Tensor(B)          # not leaves: they take gradients
+        la.forward(); lb.forward()
+        cat = S.Concatenate()(la, lb)
+        before = dict(host.fake.CALLS)
+        out = cat.forward()
+        assert np.array_equal(out.to_numpy(), np.concatenate([A, B], axis=1))
+        G = rs.standard_normal(out.shape).astype(np.float32)
+        out._backward(ct(G))
+        assert np.array_equal(la.outputs.grad.to_host_f32(), G[:, :sa[1]]) and np.array_equal(lb.outputs.grad.to_host_f32(), G[:, sa[1]:])
+        assert host.fake.CALLS.get("concat_fwd", 0) - before.get("concat_fwd", 0) == 1
+        assert host.fake.CALLS.get("concat_bwd", 0) - before.get("concat_bwd", 0) == 1
+    with pytest.raises(ValueError):
+        S.Concatenate()(la)
+
+
 def test_fit_pipeline_matches_the_synchronous_loop(host):
     """Sequential.fit (double-buffered staging, loss read one step late, last batch ragged) gives the history and the
     weights of the synchronous loop; integer labels expanded on the device give the same as host one-hot rows."""
