@@ -2,8 +2,8 @@
 layer list, seeded initial weights and data."""
 import numpy as np
 
-# SGD, not Adam: a bias that feeds a BatchNorm has a gradient of zero up to rounding noise, and Adam would turn that noise
-# into steps of size lr in a noise-given direction, which no two engines share.
+# SGD, not Adam: Adam divides every gradient entry by its own magnitude, so entries near zero (there are some behind the
+# normalisation layers) turn rounding differences between engines into steps of size lr.
 N, CLASSES, STEPS, LR, MOMENTUM = 12, 5, 2, 5e-2, 0.9
 
 

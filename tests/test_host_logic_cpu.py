@@ -198,10 +198,7 @@ def _bn_model_against_golden(S, golden_dir, tol):
             model.gather_grads()
             for k, l in enumerate(plist):
                 assert rel(l.weights.grad.to_host_f32(), gold["dW%d" % k]) < tol, ("dW", k)
-                if k in (0, 2):     # a bias that feeds a BatchNorm: its gradient is zero up to rounding noise on every engine
-                    assert np.max(np.abs(l.bais.grad.to_host_f32().ravel() - gold["db%d" % k].ravel())) < 1e-6, ("db", k)
-                else:
-                    assert rel(l.bais.grad.to_host_f32(), gold["db%d" % k]) < tol, ("db", k)
+                assert rel(l.bais.grad.to_host_f32(), gold["db%d" % k]) < tol, ("db", k)
         opt.step()
         for k, l in enumerate(plist):
             assert rel(l.weights.to_numpy(), gold["W%d_s%d" % (k, s)]) < tol, ("W", k, s)
