@@ -952,7 +952,14 @@ class Sequential:
         return np.array(history)
 
     # checkpoint: layer configs + host copies of the weights (same record layout as Seera.py:790-860)
-    def save(self, filepath):
+    def save(self, filepath, optimizer=None, rank=None):
+        """Layer records as the reference writes them (Seera.py:790-860).  With `optimizer`, a last record of class
+        "__optimizer__" carries its kind, hyper-parameters, step count and state arenas (Adam m / v, SGD velocity), so
+        that training resumes exactly; the reference drops that state.  In a data-parallel run only rank 0 writes
+        (`rank`, else the RANK environment variable): the ranks hold identical weights and optimizer state."""
+        import os
+        if int(os.environ.get("RANK", "0") if rank is None else rank) != 0:
+            return
         data = []
         for l in self.model:
             info = {"class": l.__class__.__name__, "config": {}}
@@ -973,16 +980,23 @@ class Sequential:
             if isinstance(l, _ParamLayer):
                 info["weights"], info["bais"] = l.weights.to_numpy(), l.bais.to_numpy()
             data.append(info)
+        if optimizer is not None:
+            data.append({"class": "__optimizer__", "config": optimizer.state_dict()})
         with open(filepath, "wb") as f:
             pickle.dump(data, f)
 
     @classmethod
-    def load(cls, filepath):
+    def load(cls, filepath, with_optimizer=False):
+        """Rebuilds the model; with_optimizer=True returns (model, optimizer) with the saved optimizer state restored
+        (optimizer is None when the file holds none)."""
         with open(filepath, "rb") as f:
             data = pickle.load(f)
-        layers = []
+        layers, opt_state = [], None
         for info in data:
             c, k = info["config"], info["class"]
+            if k == "__optimizer__":
+                opt_state = c
+                continue
             if k == "Input":
                 l = Input(c["shape"])
             elif k == "Dense":
@@ -1009,7 +1023,10 @@ class Sequential:
                 l._w_init = np.ascontiguousarray(info["weights"], np.float32)
                 l._b_init = np.ascontiguousarray(info["bais"], np.float32)
             layers.append(l)
-        return cls(layers)
+        model = cls(layers)
+        if not with_optimizer:
+            return model
+        return model, (_Optimizer.from_state(model, opt_state) if opt_state is not None else None)
 
 
 # ─────────────────────────────────────────────────────────────────────────────────────────────
@@ -1091,6 +1108,22 @@ class _Optimizer:
         h[:len(values)] = np.asarray(values, np.float32)
         sc.upload_f32(self._hyper.main_ptr, h)
 
+    @staticmethod
+    def from_state(model, state):
+        if state["kind"] == "adam":
+            o = Adam(model, lr=state["lr"], beta1=state["beta1"], beta2=state["beta2"], eps=state["eps"])
+            o.t = state["t"]
+            arenas = (("m", o.m), ("v", o.v))
+        else:
+            o = SGD(model, lr=state["lr"], momentum=state["momentum"])
+            arenas = (("velocity", o.velocity),)
+        for name, dst in arenas:
+            a = np.ascontiguousarray(state[name], np.float32)
+            if a.size != dst.size:
+                raise ValueError(f"optimizer state '{name}' has {a.size} values, the model's arena {dst.size}")
+            sc.upload_f32(dst.main_ptr, a)
+        return o
+
     def step(self):
         """One update.  Outside a capture this also refreshes the device scalars and advances the step count."""
         if not sc.is_capturing():
@@ -1110,6 +1143,9 @@ class SGD(_Optimizer):
     def advance(self):
         self._upload([self.lr, self.momentum, self._grad_scale()])
 
+    def state_dict(self):
+        return {"kind": "sgd", "lr": self.lr, "momentum": self.momentum, "velocity": self.velocity.to_host_f32().copy()}
+
     def _enqueue(self):
         m = self.model
         sc.cuda_sgd_step_dev(m.params.main_ptr, m.grads.main_ptr, self.velocity.main_ptr, m.n_arena, self._hyper.main_ptr)
@@ -1127,6 +1163,10 @@ class Adam(_Optimizer):
         b1, b2 = self.beta1, self.beta2
         self._upload([self.lr, b1, 1 - b1, b2, 1 - b2, self.eps, 1 - b1 ** self.t, 1 - b2 ** self.t, self._grad_scale()])
         self.t += 1
+
+    def state_dict(self):
+        return {"kind": "adam", "lr": self.lr, "beta1": self.beta1, "beta2": self.beta2, "eps": self.eps, "t": self.t,
+                "m": self.m.to_host_f32().copy(), "v": self.v.to_host_f32().copy()}
 
     def _enqueue(self):
         md = self.model

@@ -253,6 +253,50 @@ def test_fit_pipeline_matches_the_synchronous_loop_on_the_device(T):
             assert np.array_equal(w, w0) and np.array_equal(b, b0)
 
 
+@pytest.mark.parametrize("kind", ["adam", "sgd"])
+def test_checkpoint_with_optimizer_state_resumes_exactly_on_the_device(T, tmp_path, kind):
+    """fit two epochs, save with the optimizer, load, fit one more == three epochs straight, bit for bit (weights,
+    BatchNorm running statistics, Adam moments / SGD velocity and the step count)."""
+    from ml_framework_b200 import seera as S, seera_cuda as sc
+    sc.set_precision(0)
+    rs = np.random.RandomState(3)
+    X = rs.standard_normal((96, 1, 12, 12)).astype(np.float32)
+    Y = np.eye(7, dtype=np.float32)[rs.randint(0, 7, 96)]
+
+    def make():
+        np.random.seed(11)
+        m = S.Sequential([S.Input((1, 12, 12)), S.Conv2D(8, 1, (3, 3), "relu", stride=1, zero_padding=1), S.BatchNorm2d(8),
+                          S.MaxPool2D((2, 2), stride=2), S.Flatten(), S.Dense(288, 7, activation="softmax")], device="cuda")
+        return m, (S.Adam(m, lr=1e-2) if kind == "adam" else S.SGD(m, lr=1e-2, momentum=0.9))
+    loss = S.Loss().categorical_cross_entropy
+    f = str(tmp_path / "ck.pkl")
+    a, oa = make()
+    b, ob = make()
+    for e in range(3):                                          # fit shuffles from numpy's global stream: seed per epoch
+        np.random.seed(100 + e)
+        a.fit(X, Y, oa, loss, Epochs=1, batch_size=32, Loss_interval=100)
+    for e in range(2):
+        np.random.seed(100 + e)
+        b.fit(X, Y, ob, loss, Epochs=1, batch_size=32, Loss_interval=100)
+    b.save(f, optimizer=ob)
+    c, oc = S.Sequential.load(f, with_optimizer=True)
+    np.random.seed(102)
+    c.fit(X, Y, oc, loss, Epochs=1, batch_size=32, Loss_interval=100)
+    assert type(oc) is type(oa)
+    pa = [l for l in a.model if isinstance(l, S._ParamLayer)]
+    pc = [l for l in c.model if isinstance(l, S._ParamLayer)]
+    assert len(pa) == len(pc) > 0
+    for la, lc in zip(pa, pc):
+        assert np.array_equal(la.weights.to_numpy(), lc.weights.to_numpy()) and np.array_equal(la.bais.to_numpy(), lc.bais.to_numpy())
+    bna = [l for l in a.model if isinstance(l, S.BatchNorm2d)][0]
+    bnc = [l for l in c.model if isinstance(l, S.BatchNorm2d)][0]
+    assert np.array_equal(np.asarray(bna.running_mean), np.asarray(bnc.running_mean))
+    assert np.array_equal(np.asarray(bna.running_var), np.asarray(bnc.running_var))
+    sa, sb = oa.state_dict(), oc.state_dict()
+    for k in sa:
+        assert np.array_equal(sa[k], sb[k]), k
+
+
 def test_batchnorm_model_against_reference_golden(T, golden_dir):
     """BatchNorm2d / BatchNorm1d on the device inside a small CNN: two SGD steps (loss, predictions, every gradient and
     weight, running statistics) and an evaluation-mode prediction against the unmodified reference (host BatchNorm)."""

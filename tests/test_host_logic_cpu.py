@@ -213,6 +213,41 @@ def test_batchnorm_layers_against_reference_golden(host, golden_dir):
     _bn_model_against_golden(host.seera, golden_dir, 2e-5)
 
 
+@pytest.mark.parametrize("kind", ["adam", "sgd"])
+def test_checkpoint_with_optimizer_state_resumes_exactly(host, tmp_path, kind):
+    """Two steps, save with the optimizer, load, one more step == three steps straight (weights bit-equal); a non-zero
+    rank writes nothing."""
+    S = host.seera
+    work, n = cases.small_cases()["c3s"]
+    X, Y = work.batch(n, 4)
+
+    def make():
+        m = host.train.build_model(work, work.params(6))
+        return m, (S.Adam(m, lr=1e-3) if kind == "adam" else S.SGD(m, lr=1e-2, momentum=0.9))
+
+    def step(m, o):
+        loss = S.Loss().categorical_cross_entropy(m.forward(S.Tensor(X, is_leaf=True)), S.Tensor(Y, is_leaf=True))
+        m.zero_grad()
+        S.autograd4nn(loss)
+        o.step()
+    a, oa = make()
+    for _ in range(3):
+        step(a, oa)
+    b, ob = make()
+    for _ in range(2):
+        step(b, ob)
+    f = str(tmp_path / "ck.pkl")
+    b.save(str(tmp_path / "none.pkl"), optimizer=ob, rank=1)
+    assert not os.path.exists(str(tmp_path / "none.pkl"))
+    b.save(f, optimizer=ob)
+    c, oc = S.Sequential.load(f, with_optimizer=True)
+    assert type(oc) is type(ob)
+    step(c, oc)
+    for la, lc in zip(a.param_layers, c.param_layers):
+        assert np.array_equal(la.weights.to_numpy(), lc.weights.to_numpy()) and np.array_equal(la.bais.to_numpy(), lc.bais.to_numpy())
+    assert S.Sequential.load(f).n_arena == a.n_arena                   # plain load ignores the optimizer record
+
+
 def test_concatenate_layer_joins_and_splits(host):
     """Concatenate of two branches (4-D and 2-D): forward equals np.concatenate along axis 1, backward hands each branch
     its slice of the gradient; one concat launch per direction."""
