@@ -145,6 +145,25 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t addr, uint32_t b
 //                 two boxes of 64 channels (MN-major).  B is then [pixels, N] read along its columns.
 enum { TMA_A_ROWS = 0, TMA_A_COLS = 1, TMA_A_IM2COL = 2, TMA_A_TAPS = 3 };
 
+// Division by a launch constant as one wide multiply and a shift: the producer and the MMA issuer are single threads
+// with nothing to hide an integer division's ~100 dependent clocks behind, and they divide several times per k-step.
+// Exact for 0 <= n < 2^31 (shift = 31 + ceil(log2 d), mul = ceil(2^shift / d) < 2^32).
+struct FastDiv {
+    uint32_t mul, shift;
+    int d;
+    __device__ __forceinline__ int div(int n) const { return (int)(((unsigned long long)(uint32_t)n * mul) >> shift); }
+};
+inline FastDiv fast_div(int d) {
+    if (d < 1) d = 1;
+    uint32_t l = 0;
+    while ((1ll << l) < d) l++;
+    FastDiv f;
+    f.shift = 31 + l;
+    f.mul = (uint32_t)(((1ull << f.shift) + (unsigned long long)d - 1) / (unsigned long long)d);
+    f.d = d;
+    return f;
+}
+
 struct TmaGemmParams {
     int M, N, K, kchunk, splits, bn, stages;
     int a_mode, b_mn;        // b_mn = 1: B read along its contiguous row index (MN-major)
@@ -159,6 +178,7 @@ struct TmaGemmParams {
     int act;                 // activation applied before the store (0 = none)
     int pool_on;             // 1: rows are pixels of a layer output that is only consumed through a 2x2 max-pool: store that instead
     PoolOut pool;
+    FastDiv by_mtiles, by_ntiles, by_OHW, by_OW, by_S, by_cchunks;      // filled by launch_tma_gemm
 };
 
 constexpr int TG_THREADS = 192;
@@ -208,8 +228,9 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
 
     // tile id -> origin and K range
     auto tile_origin = [&](int id, int &m0, int &n0, int &kbeg, int &ktiles, int &z) {
-        int mt = id % mtiles, rest = id / mtiles, nt = rest % ntiles;
-        z = rest / ntiles;
+        int rest = p.by_mtiles.div(id), mt = id - rest * mtiles;
+        z = p.by_ntiles.div(rest);
+        int nt = rest - z * ntiles;
         m0 = mt * TC_BM; n0 = nt * bn;
         kbeg = z * p.kchunk;
         int kend = min(p.K, kbeg + p.kchunk);
@@ -221,6 +242,8 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         const CUtensorMap *mA[3] = {&mapA0, &mapA1, &mapA2};
         const CUtensorMap *mB[3] = {&mapB0, &mapB1, &mapB2};
         int it = 0, issued_from = 0;
+        int s = 0;                                            // ring slot and its phase, carried across tiles
+        uint32_t ph = 0;
         bool alive = true;
         for (int id = blockIdx.x; id < total_tiles && alive; id += gridDim.x) {
             int m0, n0, kbeg, ktiles, z;
@@ -228,8 +251,8 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             // im2col, M = pixels: window corner of this tile's first output pixel
             int pix_img = 0, pix_w = 0, pix_h = 0;
             if (p.a_mode == TMA_A_IM2COL) {
-                pix_img = m0 / p.OHW;
-                int rem = m0 - pix_img * p.OHW, oh = rem / p.OW, ow = rem - oh * p.OW;
+                pix_img = p.by_OHW.div(m0);
+                int rem = m0 - pix_img * p.OHW, oh = p.by_OW.div(rem), ow = rem - oh * p.OW;
                 pix_w = ow * p.sw - p.pw; pix_h = oh * p.sh - p.ph;
             }
             // im2col, M = (tap, channel): the two 64-channel boxes of this tile
@@ -239,15 +262,13 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             if (p.a_mode == TMA_A_TAPS) {
                 int c64 = p.cchunks * 64;
                 for (int b = 0; b < 2; b++) {
-                    int mb = m0 + 64 * b, tap = mb / c64;
+                    int mb = m0 + 64 * b, tap = p.by_cchunks.div(mb >> 6);
                     box_ok[b] = tap < p.taps;
-                    box_c[b] = mb - tap * c64; box_r[b] = tap / p.S; box_s[b] = tap - box_r[b] * p.S;
+                    box_c[b] = mb - tap * c64; box_r[b] = p.by_S.div(tap); box_s[b] = tap - box_r[b] * p.S;
                     if (!box_ok[b]) tx_bytes -= (uint32_t)NS * 8192u;
                 }
             }
             for (int kt = 0; kt < ktiles; kt++, it++) {
-                int s = it % stages;
-                uint32_t ph = (uint32_t)(it / stages) & 1u;
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, p.status, 1)) { alive = false; break; }
                 int k0 = kbeg + kt * TC_BK;
                 uint32_t bar = full0 + 8 * s;
@@ -261,13 +282,13 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
                     for (int i = 0; i < NS; i++)
                         for (int b = 0; b < 2; b++) tma_load_2d(a_tile(s, i) + b * 8192, mA[i], m0 + 64 * b, k0, bar);
                 } else if (p.a_mode == TMA_A_IM2COL) {
-                    int ktile = k0 >> 6, tap = ktile / p.cchunks, c0 = (ktile - tap * p.cchunks) * 64;
-                    int r = tap / p.S, sx = tap - r * p.S;
+                    int ktile = k0 >> 6, tap = p.by_cchunks.div(ktile), c0 = (ktile - tap * p.cchunks) * 64;
+                    int r = p.by_S.div(tap), sx = tap - r * p.S;
 #pragma unroll
                     for (int i = 0; i < NS; i++) tma_load_im2col(a_tile(s, i), mA[i], c0, pix_w, pix_h, pix_img, sx, r, bar);
                     bk = tap * p.cpad + c0;
                 } else {
-                    int img = k0 / p.OHW, rem = k0 - img * p.OHW, oh = rem / p.OW, ow = rem - oh * p.OW;
+                    int img = p.by_OHW.div(k0), rem = k0 - img * p.OHW, oh = p.by_OW.div(rem), ow = rem - oh * p.OW;
                     int w = ow * p.sw - p.pw, h = oh * p.sh - p.ph;
 #pragma unroll
                     for (int i = 0; i < NS; i++)
@@ -282,6 +303,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
 #pragma unroll
                     for (int i = 0; i < NS; i++) tma_load_2d(b_tile(s, i), mB[i], bk, n0, bar);
                 }
+                if (++s == stages) { s = 0; ph ^= 1u; }
             }
         }
         if (*abortp) {
@@ -300,7 +322,15 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
         const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
         bool alive = true;
-        int it = 0, local = 0;
+        int local = 0;
+        int s = 0;                                            // ring slot and its phase, carried across tiles
+        uint32_t ph = 0;
+        // descriptors of copy 0 / slice 0 in slot 0; the others differ only in the start-address field (16-byte units),
+        // which never carries out of its 14 bits for addresses inside the CTA's shared memory
+        const uint64_t da0 = a_mn ? umma_desc_sw128_mn(a_tile(0, 0), 8192) : umma_desc_sw128(a_tile(0, 0));
+        const uint64_t db0 = p.b_mn ? umma_desc_sw128_mn(b_tile(0, 0), 8192) : umma_desc_sw128(b_tile(0, 0));
+        const uint32_t a_step16 = a_step >> 4, b_step16 = b_step >> 4, a_copy16 = a_bytes >> 4, b_copy16 = b_bytes >> 4;
+        const uint32_t stage16 = stage_bytes >> 4;
         for (int id = blockIdx.x; id < total_tiles && alive; id += gridDim.x, local++) {
             int m0, n0, kbeg, ktiles, z;
             tile_origin(id, m0, n0, kbeg, ktiles, z);
@@ -311,20 +341,18 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
             uint32_t acc = 0;
-            for (int kt = 0; kt < ktiles && alive; kt++, it++) {
-                int s = it % stages;
-                uint32_t ph = (uint32_t)(it / stages) & 1u;
+            for (int kt = 0; kt < ktiles && alive; kt++) {
                 alive = mbar_wait(full0 + 8 * s, ph, abortp, p.status, 2);
                 if (!alive) break;
                 tc_fence_after();
+                const uint64_t das = da0 + (uint32_t)s * stage16, dbs = db0 + (uint32_t)s * stage16;
 #pragma unroll
                 for (int j = 0; j < TC_BK / 16; j++) {
                     uint64_t da[NS], db[NS];
 #pragma unroll
                     for (int i = 0; i < NS; i++) {
-                        uint32_t aa = a_tile(s, i) + j * a_step, ba = b_tile(s, i) + j * b_step;
-                        da[i] = a_mn ? umma_desc_sw128_mn(aa, 8192) : umma_desc_sw128(aa);
-                        db[i] = p.b_mn ? umma_desc_sw128_mn(ba, 8192) : umma_desc_sw128(ba);
+                        da[i] = das + (uint32_t)i * a_copy16 + (uint32_t)j * a_step16;
+                        db[i] = dbs + (uint32_t)i * b_copy16 + (uint32_t)j * b_step16;
                     }
 #pragma unroll
                     for (int q = 0; q < NPROD; q++) {
@@ -333,6 +361,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
                     }
                 }
                 umma_commit(empty0 + 8 * s);
+                if (++s == stages) { s = 0; ph ^= 1u; }
             }
             if (alive) umma_commit(tfull0 + 8 * buf);        // accumulator of this tile complete
         }
@@ -424,6 +453,8 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
     splits = (p.K + p.kchunk - 1) / p.kchunk;
     p.splits = splits;
     p.stages = stages;
+    p.by_mtiles = fast_div((p.M + TC_BM - 1) / TC_BM); p.by_ntiles = fast_div((p.N + p.bn - 1) / p.bn);
+    p.by_OHW = fast_div(p.OHW); p.by_OW = fast_div(p.OW); p.by_S = fast_div(p.S); p.by_cchunks = fast_div(p.cchunks);
     p.status = tc_status_word();
     p.partial = nullptr;
     if (splits > 1) {
