@@ -23,6 +23,7 @@ namespace seera {
 
 struct FirstGeom {
     int NB, C, H, W, F, R, S, sh, sw, ph, pw, OH, OW, K;
+    FastDiv by_P, by_OW, by_Pq, by_OWq;      // pixels per image, output width, and the same counted in 2x2 windows
 };
 
 __device__ __forceinline__ float first_act(float z, int act) {
@@ -421,20 +422,20 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
                 ws[h][i] = rs & 0xffff;
             }
         const bool second = cg + 4 < chunks;
-        int it = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, it++) {
-            const int s = it % stages;
-            if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
+        int s = 0;
+        uint32_t ph = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, status, 1)) break;
             const int pix = tile * TC_BM + row;                  // the launcher keeps the pixel count below 2^31
             const bool live = pix < (int)pixels;
             int img, oh, ow;
             if (pool_on) {
-                const int wi = live ? pix >> 2 : 0, wimg = wi / Pq, wrem = wi - wimg * Pq, ohq = wrem / OWq, owq = wrem - ohq * OWq;
+                const int wi = live ? pix >> 2 : 0, wimg = g.by_Pq.div(wi), wrem = wi - wimg * Pq, ohq = g.by_OWq.div(wrem), owq = wrem - ohq * OWq;
                 img = wimg; oh = 2 * ohq + ((row >> 1) & 1); ow = 2 * owq + (row & 1);
             } else {
-                img = live ? pix / P : 0;
+                img = live ? g.by_P.div(pix) : 0;
                 const int rem = live ? pix - img * P : 0;
-                oh = rem / g.OW; ow = rem - oh * g.OW;
+                oh = g.by_OW.div(rem); ow = rem - oh * g.OW;
             }
             const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
             const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
@@ -457,17 +458,19 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
             fence_async_smem();                      // generic-proxy stores -> visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mbar_arrive(full0 + 8 * s);        // one arrival per warp: 512 arrivals on one barrier serialise
+            if (++s == stages) { s = 0; ph ^= 1u; }
         }
     } else if (warp == MMA_WARP && lane == 0) {
         // ---------------- MMA issuer ----------------
         const uint32_t idesc = umma_idesc_bf16(bn);
         constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
         const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
-        int it = 0;
+        int it = 0, s = 0;
+        uint32_t ph = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, it++) {
-            const int s = it % stages, buf = it & 1;
+            const int buf = it & 1;
             if (!mbar_wait(tempty0 + 8 * buf, (((uint32_t)it >> 1) & 1u) ^ 1u, abortp, status, 4)) break;
-            if (!mbar_wait(full0 + 8 * s, ((uint32_t)(it / stages)) & 1u, abortp, status, 2)) break;
+            if (!mbar_wait(full0 + 8 * s, ph, abortp, status, 2)) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
             const uint32_t a0 = smem_u32(a_base + (size_t)s * NS * a_bytes), b0 = smem_u32(b_base);
@@ -484,6 +487,7 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
             }
             umma_commit(empty0 + 8 * s);
             umma_commit(tfull0 + 8 * buf);
+            if (++s == stages) { s = 0; ph ^= 1u; }
         }
     } else if (warp > MMA_WARP) {
         // ---------------- epilogue: warp w drains TMEM lane quarter w % 4 ----------------
@@ -562,14 +566,15 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
             // ---- dz rows: thread = (window of the step, filter chunks fcg and fcg + 8) ----
             const bool slope = src.act != SEERA_ACT_NONE;
             const int wl = tg & 15, fcg = tg >> 4;
-            for (int it = s;; it += stages) {
+            uint32_t ph = 0;                                   // it advances by `stages`: the slot's phase flips every iteration
+            for (int it = s;; it += stages, ph ^= 1u) {
                 const long long step = blockIdx.x + (long long)it * gridDim.x;
                 if (step >= nsteps) break;
-                if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, status, 1)) break;
                 unsigned char *a_stage = smem + (size_t)s * stage_bytes;
                 const long long wj = step * 16 + wl;
                 const bool wlive = wj < windows;
-                const int wimg = wlive ? (int)(wj / Pq) : 0, wwrem = wlive ? (int)(wj - (long long)wimg * Pq) : 0;
+                const int wimg = wlive ? g.by_Pq.div((int)wj) : 0, wwrem = wlive ? (int)(wj - (long long)wimg * Pq) : 0;
                 const long long wbase = (long long)wimg * g.F * Pq + wwrem;
                 for (int fc = fcg; fc < fchunks; fc += 8) {
                     float gv[8], pv[8];
@@ -611,15 +616,16 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
                     wr[h][i] = rs >= 0 ? (rs >> 16) : -(1 << 20);
                     ws[h][i] = rs == -2 ? -2 : (rs & 0xffff);
                 }
-            for (int it = s;; it += stages) {
+            uint32_t ph = 0;                                   // it advances by `stages`: the slot's phase flips every iteration
+            for (int it = s;; it += stages, ph ^= 1u) {
                 const long long step = blockIdx.x + (long long)it * gridDim.x;
                 if (step >= nsteps) break;
-                if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, status, 1)) break;
                 unsigned char *b_stage = smem + (size_t)s * stage_bytes + (size_t)NS * A_BYTES;
                 const long long wi = step * 16 + (pr >> 2);
                 const bool live = wi < windows;
-                const int img = live ? (int)(wi / Pq) : 0, wrem = live ? (int)(wi - (long long)img * Pq) : 0;
-                const int ohq = wrem / OWq, owq = wrem - ohq * OWq;
+                const int img = live ? g.by_Pq.div((int)wi) : 0, wrem = live ? (int)(wi - (long long)img * Pq) : 0;
+                const int ohq = g.by_OWq.div(wrem), owq = wrem - ohq * OWq;
                 const int oh = 2 * ohq + ((pr >> 1) & 1), ow = 2 * owq + (pr & 1);
                 const int ih0 = live ? oh * g.sh - g.ph : -(1 << 20), iw0 = ow * g.sw - g.pw;
                 const float *xb = X + (long long)img * g.C * g.H * g.W + (long long)ih0 * g.W + iw0;
@@ -661,15 +667,15 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
         const int mode = src.dz ? 0 : (src.gp ? 2 : 1);               // stored dz | full-resolution gradient | pooled gradient
         const float *grad = src.dz ? src.dz : (src.gp ? src.gp : src.g);
         const bool slope = mode != 0 && src.act != SEERA_ACT_NONE;
-        int it = 0;
-        for (int step = blockIdx.x; step < nsteps; step += gridDim.x, it++) {
-            const int s = it % stages;
-            if (!mbar_wait(empty0 + 8 * s, (((uint32_t)(it / stages)) & 1u) ^ 1u, abortp, status, 1)) break;
+        int s = 0;
+        uint32_t ph = 0;
+        for (int step = blockIdx.x; step < nsteps; step += gridDim.x, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+            if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, status, 1)) break;
             unsigned char *a_stage = smem + (size_t)s * stage_bytes, *b_stage = a_stage + (size_t)NS * A_BYTES;
             const int pix = step * 64 + p;
             const bool live = pix < (int)pixels;
-            const int img = live ? pix / P : 0, rem = live ? pix - img * P : 0;
-            const int oh = rem / g.OW, ow = rem - oh * g.OW;
+            const int img = live ? g.by_P.div(pix) : 0, rem = live ? pix - img * P : 0;
+            const int oh = g.by_OW.div(rem), ow = rem - oh * g.OW;
             for (int job = slot; job < fchunks + kchunks; job += FTW_SLOTS) {
                 if (job < fchunks) {
                     const int fc = job;
@@ -718,11 +724,11 @@ first_tc_wgrad_kernel(const float *__restrict__ X, DzSource src, float *__restri
         constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
         const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
         uint32_t acc = 0;
-        int it = 0;
+        int s = 0;
+        uint32_t ph = 0;
         bool alive = true;
-        for (int step = blockIdx.x; step < nsteps && alive; step += gridDim.x, it++) {
-            const int s = it % stages;
-            alive = mbar_wait(full0 + 8 * s, ((uint32_t)(it / stages)) & 1u, abortp, status, 2);
+        for (int step = blockIdx.x; step < nsteps && alive; step += gridDim.x, s = (s + 1 == stages ? 0 : s + 1), ph ^= (s == 0 ? 1u : 0u)) {
+            alive = mbar_wait(full0 + 8 * s, ph, abortp, status, 2);
             if (!alive) break;
             tc_fence_after();
             const uint32_t a0 = smem_u32(smem + (size_t)s * stage_bytes), b0 = a0 + (uint32_t)NS * A_BYTES;
@@ -847,6 +853,8 @@ static int first_tc_wgrad(const float *X, const DzSource &src, float *dW, float 
 
 static bool first_geom(FirstGeom &g, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     g = FirstGeom{NB, C, H, W, F, R, S, sh, sw, ph, pw, (H + 2 * ph - R) / sh + 1, (W + 2 * pw - S) / sw + 1, C * R * S};
+    g.by_P = fast_div(g.OH * g.OW); g.by_OW = fast_div(g.OW);
+    g.by_Pq = fast_div((g.OH * g.OW) >> 2); g.by_OWq = fast_div(g.OW >> 1);
     return g.K <= 64 && R < 32768 && S < 32768 && (F + FIRST_FC - 1) / FIRST_FC <= 65535;
 }
 
