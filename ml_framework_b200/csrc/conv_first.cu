@@ -340,7 +340,9 @@ static int resident_blocks(K kernel) {
 //             patch matrix yields the bias gradient.  Per-CTA partial tiles are reduced in block order.
 // Every mbarrier wait is bounded (status word as for the other tensor-core kernels).
 constexpr int FT_PRODUCERS = 512;         // 16 producer warps: with one warp per scheduler the gathers' latency was the whole cost
-constexpr int FTC_THREADS = FT_PRODUCERS + 32 + 128;      // forward: warps 0-15 producers, 16 MMA, 17-20 epilogue
+constexpr int FT_EPI_WARPS = 8;           // two per TMEM lane quarter, each draining half of the tile's columns: the epilogue
+                                          // shares its schedulers with the producers and was the slower side with four
+constexpr int FTC_THREADS = FT_PRODUCERS + 32 + 32 * FT_EPI_WARPS;      // forward: warps 0-15 producers, 16 MMA, 17-24 epilogue
 constexpr int FTW_PRODUCERS = 768;        // dW: 24 producer warps (the conversion work per pixel is several times the forward's)
 constexpr int FTW_THREADS = FTW_PRODUCERS + 32;           // warps 0-23 producers, 24 MMA; warps 0-3 drain the accumulator at the end
 constexpr int FTW_SLOTS = FTW_PRODUCERS / 64;             // pixel-ordered producers: job slots per pixel
@@ -378,7 +380,7 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
     if (t == 0) {
         abort_flag = 0;
         for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, FT_PRODUCERS / 32); mbar_init(empty0 + 8 * s, 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, FT_EPI_WARPS); }
         fence_mbar_init();
     }
     fill_patch_table(koff, krs, g, 64);
@@ -490,20 +492,22 @@ first_tc_fwd_kernel(const float *__restrict__ X, const float *__restrict__ Wt, S
             if (++s == stages) { s = 0; ph ^= 1u; }
         }
     } else if (warp > MMA_WARP) {
-        // ---------------- epilogue: warp w drains TMEM lane quarter w % 4 ----------------
-        const int q = warp & 3;
-        float *stage = reinterpret_cast<float *>(epi_smem + (size_t)(warp - MMA_WARP - 1) * EPI_WARP_SMEM);
+        // ---------------- epilogue: warp w drains TMEM lane quarter w % 4, columns of its half ----------------
+        const int q = warp & 3, ew = warp - MMA_WARP - 1;
+        const int half = bn >= 64 ? bn / 2 : bn;                  // a 32-column tile is not split: the second set of warps only arrives
+        const int c0 = (ew >> 2) * half, c1 = min(bn, c0 + half);
+        float *stage = reinterpret_cast<float *>(epi_smem + (size_t)ew * EPI_WARP_SMEM);
         int it = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, it++) {
             const int buf = it & 1;
             if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)it >> 1) & 1u, abortp, status, 3)) break;
             tc_fence_after();
-            if (pool_on)
-                drain_accumulator_pooled(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), tile * TC_BM + q * 32, 0, bn,
-                                         (int)pixels, g.F, bias, act, po, stage);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn + c0);
+            if (c0 >= bn) {}
+            else if (pool_on)
+                drain_accumulator_pooled(taddr, tile * TC_BM + q * 32, c0, c1 - c0, (int)pixels, g.F, bias, act, po, stage);
             else
-                drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), tile * TC_BM + q * 32, 0, 0, bn,
-                                  (int)pixels, g.F, cs, nullptr, 0, stage, bias, act);
+                drain_accumulator(taddr, tile * TC_BM + q * 32, 0, c0, c1, (int)pixels, g.F, cs, nullptr, 0, stage, bias, act);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
@@ -792,7 +796,7 @@ static int first_tc_fwd(const float *X, const float *Wt, const float *bias, floa
     const int nslices = (g.K + 15) / 16;
     const long long pixels = (long long)g.NB * g.OH * g.OW;
     const int tiles = (int)((pixels + TC_BM - 1) / TC_BM);
-    const size_t fixed = (size_t)ns * bn * 128 + 4 * EPI_WARP_SMEM + 1024;
+    const size_t fixed = (size_t)ns * bn * 128 + FT_EPI_WARPS * EPI_WARP_SMEM + 1024;
     int stages = (int)((225 * 1024 - fixed) / ((size_t)ns * TC_BM * 128));
     if (stages > 4) stages = 4;
     if (stages < 2) return fail(SEERA_E_LIMIT, "%s: tile does not fit shared memory", name);
@@ -801,7 +805,7 @@ static int first_tc_fwd(const float *X, const float *Wt, const float *bias, floa
     StorePixelRows cs{Y, g.F, g.OH * g.OW};
     PoolOut po{};
     const int pool_on = pool ? 1 : 0;
-    if (pool) { po = *pool; po.P = g.OH * g.OW; po.OW = g.OW; po.window_major = 1; }
+    if (pool) { po = *pool; pool_out_geometry(po, g.OH * g.OW, g.OW, 1); }
     cudaStream_t st = rt().stream;
     cudaError_t e;
     static int f1[64], f2[64], f3[64];

@@ -212,7 +212,7 @@ static int tma_fprop(const NhwcShadow &x, const Shadow &wk, float *Y, int F, int
                      int OH, int OW, int ns, const char *name, const float *bias = nullptr, int act = 0, const PoolOut *pool = nullptr) {
     TmaGemmParams p{};
     p.bias = bias; p.act = act;
-    if (pool) { p.pool_on = 1; p.pool = *pool; p.pool.P = OH * OW; p.pool.OW = OW; p.pool.window_major = 0; }
+    if (pool) { p.pool_on = 1; p.pool = *pool; pool_out_geometry(p.pool, OH * OW, OW, 0); }
     p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
     p.M = x.NB * OH * OW; p.N = F;
     p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;

@@ -116,7 +116,12 @@ struct PoolOut {
     int ns, Cp;
     int P, OW;                     // pixels per image and width of y
     int window_major;
+    FastDiv by_P, by_OW, by_Pq;    // set by pool_out_geometry
 };
+inline void pool_out_geometry(PoolOut &po, int P, int OW, int window_major) {
+    po.P = P; po.OW = OW; po.window_major = window_major;
+    po.by_P = fast_div(P); po.by_OW = fast_div(OW); po.by_Pq = fast_div(P >> 2);
+}
 
 __device__ __forceinline__ void drain_accumulator_pooled(uint32_t taddr, int row_base, int col_base, int ncols, int M, int N,
                                                          const float *bias, int act, const PoolOut &po, float *stage) {
@@ -134,11 +139,11 @@ __device__ __forceinline__ void drain_accumulator_pooled(uint32_t taddr, int row
         if (po.window_major) {
             r0[w] = 4 * w;
             const int wi = (row_base >> 2) + w;
-            wimg[w] = wi / Pq; wrem[w] = wi - wimg[w] * Pq;
+            wimg[w] = po.by_Pq.div(wi); wrem[w] = wi - wimg[w] * Pq;
         } else {
             const int wr = w / OWq, wc = w - wr * OWq;            // window row / column inside the warp's rows
             r0[w] = 2 * wr * po.OW + 2 * wc;
-            const int m = row_base + r0[w], img = m / po.P, rem = m - img * po.P, oh = rem / po.OW, ow = rem - oh * po.OW;
+            const int m = row_base + r0[w], img = po.by_P.div(m), rem = m - img * po.P, oh = po.by_OW.div(rem), ow = rem - oh * po.OW;
             wimg[w] = img; wrem[w] = (oh >> 1) * OWq + (ow >> 1);
         }
     }

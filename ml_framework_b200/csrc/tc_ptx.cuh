@@ -9,6 +9,25 @@ namespace seera {
 constexpr int TC_BM = 128, TC_BK = 64, TC_PRODUCERS = 256, TC_THREADS = 288;
 constexpr unsigned long long TC_WAIT_CLOCKS = 4000000000ull;      // ~2 s at 2 GHz
 
+// Division by a launch constant as one wide multiply and a shift: the producer and the MMA issuer are single threads
+// with nothing to hide an integer division's ~100 dependent clocks behind, and they divide several times per k-step.
+// Exact for 0 <= n < 2^31 (shift = 31 + ceil(log2 d), mul = ceil(2^shift / d) < 2^32).
+struct FastDiv {
+    uint32_t mul, shift;
+    int d;
+    __device__ __forceinline__ int div(int n) const { return (int)(((unsigned long long)(uint32_t)n * mul) >> shift); }
+};
+inline FastDiv fast_div(int d) {
+    if (d < 1) d = 1;
+    uint32_t l = 0;
+    while ((1ll << l) < d) l++;
+    FastDiv f;
+    f.shift = 31 + l;
+    f.mul = (uint32_t)(((1ull << f.shift) + (unsigned long long)d - 1) / (unsigned long long)d);
+    f.d = d;
+    return f;
+}
+
 // ---- PTX wrappers ----------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

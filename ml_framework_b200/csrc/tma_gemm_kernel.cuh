@@ -145,25 +145,6 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t addr, uint32_t b
 //                 two boxes of 64 channels (MN-major).  B is then [pixels, N] read along its columns.
 enum { TMA_A_ROWS = 0, TMA_A_COLS = 1, TMA_A_IM2COL = 2, TMA_A_TAPS = 3 };
 
-// Division by a launch constant as one wide multiply and a shift: the producer and the MMA issuer are single threads
-// with nothing to hide an integer division's ~100 dependent clocks behind, and they divide several times per k-step.
-// Exact for 0 <= n < 2^31 (shift = 31 + ceil(log2 d), mul = ceil(2^shift / d) < 2^32).
-struct FastDiv {
-    uint32_t mul, shift;
-    int d;
-    __device__ __forceinline__ int div(int n) const { return (int)(((unsigned long long)(uint32_t)n * mul) >> shift); }
-};
-inline FastDiv fast_div(int d) {
-    if (d < 1) d = 1;
-    uint32_t l = 0;
-    while ((1ll << l) < d) l++;
-    FastDiv f;
-    f.shift = 31 + l;
-    f.mul = (uint32_t)(((1ull << f.shift) + (unsigned long long)d - 1) / (unsigned long long)d);
-    f.d = d;
-    return f;
-}
-
 struct TmaGemmParams {
     int M, N, K, kchunk, splits, bn, stages;
     int a_mode, b_mn;        // b_mn = 1: B read along its contiguous row index (MN-major)
