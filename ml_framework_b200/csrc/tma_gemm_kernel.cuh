@@ -414,19 +414,25 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
     long long tiles = (long long)((p.M + TC_BM - 1) / TC_BM) * ((p.N + p.bn - 1) / p.bn);
     // Split of the contraction: every (tile, split) item is one pass of a persistent CTA, so the launch takes
     // ceil(items / SMs) rounds of ceil(ksteps / splits) k-steps each, plus a fixed cost per item (pipeline fill, the
-    // partial tile written out, worth about four k-steps).  Take the split count with the smallest such estimate;
-    // ties go to fewer splits (less partial traffic).
+    // partial tile written out, worth about four k-steps).  A split also pays for the reduce launch (eight k-steps) and
+    // for moving the partial sums: splits x M x N floats written and read back, M x N written, priced at 5 TB/s against
+    // a k-step of about 0.25 us per product at N = 128 (small outputs stay in L2 and cost nothing; a 4096 x 4096 output
+    // split in two would cost more than the idle SMs it fills).  Take the split count with the smallest such estimate;
+    // ties go to fewer splits.
     int splits = 1;
     const long long ksteps = (p.K + TC_BK - 1) / TC_BK;
     if (allow_split) {
         const long long sms = rt().sm_count;
+        const double kstep_us = 0.25 * (ns == 1 ? 1 : (ns == 2 ? 3 : 6)) * p.bn / 128.0;
+        const double partial_ksteps = (double)p.M * p.N * 4.0 / 5e6 / kstep_us;      // one pass over M x N floats, in k-steps
         long long maxs = ksteps / 2;                  // at least two k-steps per item
         if (maxs > 256) maxs = 256;
         long long best = -1;
         for (long long sp = 1; sp <= maxs || sp == 1; sp++) {
             long long per = (ksteps + sp - 1) / sp, eff = (ksteps + per - 1) / per;
             long long rounds = (tiles * eff + sms - 1) / sms;
-            long long cost = rounds * (per + 4) + (sp > 1 ? 8 : 0);     // a split also pays for the reduce launch
+            long long cost = rounds * (per + 4);
+            if (sp > 1) cost += 8 + (long long)((2.0 * eff + 1.0) * partial_ksteps);
             if (best < 0 || cost < best) { best = cost; splits = (int)eff; }
         }
     }
