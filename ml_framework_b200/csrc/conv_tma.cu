@@ -860,6 +860,8 @@ int seera_tma_convT_bias_act_fwd(const float *X, const float *Wt, const float *b
     if (!conv_ok(NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw) || Ho < 1 || Wo < 1 || !X || !Wt || !out)
         return fail(SEERA_E_ARG, "cuda_conv2DTranpose_fwd: bad argument");
     const bool unit = sh == 1 && sw == 1;
+    if (unit && conv_few_applies(NB, Cin, Cout, KH, KW, Ho, Wo))        // a few output channels: a stencil, not a GEMM
+        return conv_few_fwd(X, Wt, bias, out, NB, Cin, H, W, Cout, KH, KW, KH - 1 - ph, KW - 1 - pw, Ho, Wo, act, 1, "cuda_conv2DTranpose_fwd");
     if (!tma_conv_supported(NB, KH, KW, sh, sw, ph, pw) || (!unit && !phases_supported(Ho, Wo, H, W, KH, KW, sh, sw, ph, pw)) ||
         (!unit && (bias || act) && (sh > KH || sw > KW))) {
         int s = seera_tc_convT_fwd(X, Wt, out, NB, Cin, H, W, Cout, KH, KW, sh, sw, ph, pw);

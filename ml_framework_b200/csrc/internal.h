@@ -43,6 +43,10 @@ namespace seera {
 bool conv_first_pool_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw);
 int conv_first_pool_fwd(const float *X, const float *Wt, const float *bias, const PoolOut &pool, int NB, int C, int H, int W, int F, int R,
                         int S, int ph, int pw, int sh, int sw, int act, const char *name);
+// Direct fp32 kernel for unit-stride (transposed) convolutions with 1, 2 or 4 output channels (conv_few.cu); bias may be null.
+bool conv_few_applies(int NB, int C, int F, int R, int S, int OH, int OW);
+int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F, int R, int S, int PH,
+                 int PW, int OH, int OW, int act, int transposed, const char *name);
 // Direct fp32 kernels for convolutions with C*R*S <= 64 (conv_first.cu); bias may be null.
 bool conv_first_applies(int C, int R, int S);
 int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F, int R, int S,

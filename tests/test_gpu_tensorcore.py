@@ -200,6 +200,27 @@ def test_conv_layer_backward_in_one_call(E, mode, shape):
                     assert rel_l2(dX, rX) < 3e-5
 
 
+# Unit-stride transposed convolutions with 1, 2 or 4 output channels run a direct fp32 stencil kernel (the last layer of the
+# autoencoder configuration): 3x3 and other filter sizes, zero / full padding, widths that are no multiple of anything.
+FEW_FILTER_CONVT = [(3, 32, 16, 16, 1, 3, 3, 1, 1), (2, 5, 9, 13, 1, 3, 3, 0, 0), (2, 7, 6, 10, 2, 3, 3, 2, 2), (2, 3, 7, 5, 4, 3, 3, 1, 0),
+                    (2, 6, 8, 8, 1, 4, 4, 1, 2), (1, 4, 5, 11, 2, 5, 2, 2, 0), (2, 40, 12, 12, 4, 3, 3, 1, 1)]
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3])
+def test_few_filter_transposed_convolution(E, mode):
+    """Forward with bias and every activation against the oracle at fp32 accuracy (the kernel is exact fp32 in every tensor-core
+    mode), and the layer's backward through the usual entry."""
+    rs = np.random.RandomState(40 + mode)
+    _prep(mode)
+    for (N, Ci, H, W, Co, KH, KW, ph, pw) in FEW_FILTER_CONVT:
+        X, Wt, b = (rs.standard_normal(s).astype(np.float32) for s in ((N, Ci, H, W), (Ci, Co, KH, KW), (Co,)))
+        R = co.conv_transpose2d_forward(X, Wt, 1, 1, ph, pw)
+        assert rel_l2(E.conv_transpose2d_forward(X, Wt, 1, 1, ph, pw), R) < 2e-6
+        for act in (0, 1, 2, 3):
+            got = E.conv_transpose2d_bias_act(X, Wt, b, 1, 1, ph, pw, act)
+            assert got.shape == R.shape and rel_l2(got, _act_ref(R + b.reshape(1, Co, 1, 1), act)) < 2e-6
+
+
 @pytest.mark.parametrize("mode", [1, 2, 3])
 def test_pool_hands_its_copies_to_the_next_convolution(E, mode):
     """seera_maxpool2x2_fwd_s: pooled values and mask bit-equal to the oracle; a convolution fed the returned copies gives
