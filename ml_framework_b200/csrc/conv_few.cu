@@ -94,4 +94,111 @@ int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, i
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 
+// ---- weight gradient of a convolution with ONE input channel and at most nine taps ----------------------------------
+// dW[f][tap] = sum over (n, oh, ow) of dY[n, f, oh, ow] * A[n, 0, oh*sh - ph + r, ow*sw - pw + s]
+// (also the weight gradient of a transposed convolution to one channel, with the roles of the two tensors exchanged, which
+// is how cuda_conv2DTranspose_bwd calls it).  Per pixel this is 9 * F multiply-adds on 9 + F loaded values: a stencil
+// reduction, far below what staging it for the tensor cores costs.  A warp owns four filters (36 running sums per lane)
+// and walks 32-pixel tiles, lanes = consecutive pixels, so the F-channel tensor is read in place, once, in coalesced lines
+// and the nine one-channel neighbours come from L1.  Sums are reduced in a fixed order (lanes by shuffle tree, then
+// warps by a second kernel), so the result is deterministic.
+constexpr int C1_FPW = 4;                // filters per warp
+constexpr int C1_TAPS = 9;
+
+__global__ void __launch_bounds__(256) wgrad_c1_kernel(const float *__restrict__ A, const float *__restrict__ dY, float *__restrict__ partial,
+                                                       int NB, int H, int W, int F, int OH, int OW, int R, int S, int sh, int sw, int ph,
+                                                       int pw, int ngroups, FastDiv by_plane, FastDiv by_OW, FastDiv by_S) {
+    const int lane = threadIdx.x & 31;
+    const int gw = blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = gridDim.x * 8;          // gridDim.x is a multiple of ngroups
+    const int g = gw % ngroups, f0 = g * C1_FPW, taps = R * S;
+    const int plane = OH * OW;
+    const long long total = (long long)NB * plane;
+    const long long tiles = (total + 31) / 32;
+    float acc[C1_FPW][C1_TAPS];
+#pragma unroll
+    for (int i = 0; i < C1_FPW; i++)
+#pragma unroll
+        for (int t = 0; t < C1_TAPS; t++) acc[i][t] = 0.f;
+    // tap -> (r, s), the same for every pixel
+    int tr[C1_TAPS], ts[C1_TAPS];
+#pragma unroll
+    for (int t = 0; t < C1_TAPS; t++) { tr[t] = by_S.div(t); ts[t] = t - tr[t] * S; }
+    for (long long tile = gw / ngroups; tile < tiles; tile += nwarps / ngroups) {
+        const long long p = tile * 32 + lane;
+        if (p < total) {
+            const int n = by_plane.div((int)p), rem = (int)(p - (long long)n * plane), oh = by_OW.div(rem), ow = rem - oh * OW;
+            const float *a = A + (long long)n * H * W;
+            const int ih0 = oh * sh - ph, iw0 = ow * sw - pw;
+            float av[C1_TAPS];
+#pragma unroll
+            for (int t = 0; t < C1_TAPS; t++) {
+                const int ih = ih0 + tr[t], iw = iw0 + ts[t];
+                av[t] = (t < taps && (unsigned)ih < (unsigned)H && (unsigned)iw < (unsigned)W) ? __ldg(a + ih * W + iw) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < C1_FPW; i++) {
+                const float d = f0 + i < F ? __ldg(dY + ((long long)n * F + f0 + i) * plane + rem) : 0.f;
+#pragma unroll
+                for (int t = 0; t < C1_TAPS; t++) acc[i][t] = fmaf(d, av[t], acc[i][t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < C1_FPW; i++)
+#pragma unroll
+        for (int t = 0; t < C1_TAPS; t++) {
+            float v = acc[i][t];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) partial[(long long)gw * (C1_FPW * C1_TAPS) + i * C1_TAPS + t] = v;
+        }
+}
+
+// dW[f][t] = sum over the warps of group f / 4, in warp order: one warp per output, lanes stride over the group's warps.
+__global__ void __launch_bounds__(256) wgrad_c1_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dW, int F, int taps,
+                                                              int ngroups, int nwarps) {
+    const int lane = threadIdx.x & 31, o = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (o >= F * taps) return;
+    const int f = o / taps, t = o - f * taps, g = f / C1_FPW, i = f - g * C1_FPW;
+    float v = 0.f;
+    for (int w = g + lane * ngroups; w < nwarps; w += 32 * ngroups) v += partial[(long long)w * (C1_FPW * C1_TAPS) + i * C1_TAPS + t];
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    if (lane == 0) dW[o] = v;
+}
+
+bool wgrad_c1_applies(int NB, int C, int F, int R, int S, int OH, int OW) {
+    return C == 1 && R * S <= C1_TAPS && F >= 1 && (long long)NB * OH * OW < (1ll << 31);
+}
+
+int wgrad_c1(const float *A, const float *dY, float *dW, int NB, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw,
+             const char *name) {
+    const int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
+    const int ngroups = (F + C1_FPW - 1) / C1_FPW;
+    const long long tiles = ((long long)NB * OH * OW + 31) / 32;
+    // about four resident blocks per SM, rounded to a multiple of the group count; no more warps per group than tiles
+    int blocks = rt().sm_count * 4 / ngroups;
+    const long long need = (tiles + 7) / 8;
+    if (blocks > need) blocks = (int)need;
+    if (blocks < 1) blocks = 1;
+    blocks *= ngroups;
+    const int nwarps = blocks * 8;
+    float *partial = (float *)scratch_alloc((size_t)nwarps * C1_FPW * C1_TAPS * sizeof(float));
+    if (!partial) return SEERA_E_OOM;
+    cudaStream_t st = rt().stream;
+    profile_begin();
+    wgrad_c1_kernel<<<blocks, 256, 0, st>>>(A, dY, partial, NB, H, W, F, OH, OW, R, S, sh, sw, ph, pw, ngroups, fast_div(OH * OW), fast_div(OW),
+                                            fast_div(S));
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) {
+        wgrad_c1_reduce_kernel<<<(F * R * S + 7) / 8, 256, 0, st>>>(partial, dW, F, R * S, ngroups, nwarps);
+        count_launch();
+        e = cudaGetLastError();
+    }
+    profile_end(2.0 * NB * OH * OW * (double)F * R * S);
+    scratch_free(partial);
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
+}
+
 }  // namespace seera

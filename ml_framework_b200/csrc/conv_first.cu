@@ -948,6 +948,8 @@ int conv_first_wgrad(const float *X, const float *dY, float *dW, int NB, int C, 
                      int ph, int pw, const char *name) {
     FirstGeom g;
     if (!first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
+    if (wgrad_c1_applies(NB, C, F, R, S, g.OH, g.OW))          // one input channel, <= 9 taps: a stencil reduction in fp32
+        return wgrad_c1(X, dY, dW, NB, H, W, F, R, S, sh, sw, ph, pw, name);
     return first_wgrad_run(X, DzSource{dY, nullptr, nullptr, nullptr, nullptr, SEERA_ACT_NONE, nullptr}, dW, nullptr, g, name);
 }
 

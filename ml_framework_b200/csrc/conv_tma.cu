@@ -620,6 +620,8 @@ int seera_tma_conv2d_bias_act_fwd(const float *X, const float *Wt, const float *
     if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: kernel larger than padded input");
     if (conv_first_applies(C, R, S))  // short patch: direct fp32 kernel
         return conv_first_fwd(X, Wt, bias, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw, act, "cuda_conv2d_fwd");
+    if (sh == 1 && sw == 1 && conv_few_applies(NB, C, F, R, S, OH, OW))       // a few filters: a stencil, not a GEMM
+        return conv_few_fwd(X, Wt, bias, Y, NB, C, H, W, F, R, S, ph, pw, OH, OW, act, 0, "cuda_conv2d_fwd");
     if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) {
         int s = seera_tc_conv2d_fwd(X, Wt, Y, NB, C, H, W, F, R, S, ph, pw, sh, sw);
         if (!s && (bias || act)) s = seera_bias_act_fwd(Y, bias, Y, NB * F * OH * OW, F, OH * OW, act);
@@ -660,6 +662,8 @@ int seera_conv2d_bias_act_fwd_s(const float *X, const float *Wt, const float *bi
     if (!X || !Wt || !Y) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: bad argument");
     int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
     if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_conv2d_fwd: kernel larger than padded input");
+    if (sh == 1 && sw == 1 && conv_few_applies(NB, C, F, R, S, OH, OW))       // reads X in place: no copies made, none kept
+        return conv_few_fwd(X, Wt, bias, Y, NB, C, H, W, F, R, S, ph, pw, OH, OW, act, 0, "cuda_conv2d_fwd");
     int ns = precision_copies();
     NhwcShadow local; Shadow wk;
     const NhwcShadow *xs = usable(x_in, ns, NB, C, H, W);

@@ -219,6 +219,20 @@ def test_few_filter_transposed_convolution(E, mode):
         for act in (0, 1, 2, 3):
             got = E.conv_transpose2d_bias_act(X, Wt, b, 1, 1, ph, pw, act)
             assert got.shape == R.shape and rel_l2(got, _act_ref(R + b.reshape(1, Co, 1, 1), act)) < 2e-6
+        if Co == 1 and KH * KW <= 9:      # the weight gradient of a one-channel output is a direct fp32 kernel as well
+            dY = rs.standard_normal(R.shape).astype(np.float32)
+            dX, dW = E.conv_transpose2d_backward(dY, X, Wt, 1, 1, ph, pw)
+            rX, rW = co.conv_transpose2d_backward(dY, X, Wt, 1, 1, ph, pw)
+            assert rel_l2(dW, rW) < 2e-6 and rel_l2(dX, rX) < 3e-3
+        # the same kernel serves a unit-stride convolution with few filters (patch longer than 64, or it is a short-patch layer)
+        if Ci * KH * KW > 64:
+            Wc = rs.standard_normal((Co, Ci, KH, KW)).astype(np.float32)
+            Rc = co.conv2d_forward(X, Wc, 1, 1, ph, pw) + b.reshape(1, Co, 1, 1)
+            assert rel_l2(E.conv2d_bias_act(X, Wc, b, 1, 1, ph, pw, 2), _act_ref(Rc, 2)) < 2e-6
+            dY = rs.standard_normal(Rc.shape).astype(np.float32)
+            dX, dW = E.conv2d_backward(dY, X, Wc, 1, 1, ph, pw)
+            rX, rW = co.conv2d_backward(dY, X, Wc, 1, 1, ph, pw)
+            assert rel_l2(dX, rX) < 3e-3 and rel_l2(dW, rW) < 3e-3
 
 
 @pytest.mark.parametrize("mode", [1, 2, 3])
