@@ -881,6 +881,8 @@ int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y,
                    int ph, int pw, int sh, int sw, int act, const char *name) {
     FirstGeom g;
     if (!first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the short-patch kernel", name);
+    if (conv_c1_fwd_applies(X, Y, NB, C, H, W, F, R, S, sh, sw, ph, pw))       // one input channel, "same" 3 x 3: output-bound stencil
+        return conv_c1_fwd(X, Wt, bias, Y, NB, H, W, F, ph, act, name);
     if (first_tc_fwd_ok(g)) return first_tc_fwd(X, Wt, bias, Y, g, act, name);
     long long pixels = (long long)NB * g.OH * g.OW;
     unsigned chunks = (unsigned)((F + FIRST_FC - 1) / FIRST_FC);

@@ -98,7 +98,8 @@ def _act_ref(z, act):
 # of 8 or 64 and beyond 128 (CUDA-core variant), pixel counts that are not multiples of the tile.
 SHORT = [(2, 1, 28, 28, 8, 3, 3, 1, 1, 1, 1), (3, 3, 32, 32, 64, 3, 3, 1, 1, 1, 1), (2, 1, 9, 11, 70, 5, 5, 2, 1, 2, 0),
          (2, 3, 13, 9, 5, 4, 4, 2, 3, 1, 2), (5, 4, 7, 7, 130, 4, 4, 1, 1, 0, 0), (64, 3, 32, 32, 64, 3, 3, 1, 1, 1, 1),
-         (1, 2, 6, 6, 3, 1, 1, 1, 1, 0, 0), (9, 4, 10, 10, 100, 4, 4, 1, 1, 1, 1)]
+         (1, 2, 6, 6, 3, 1, 1, 1, 1, 0, 0), (9, 4, 10, 10, 100, 4, 4, 1, 1, 1, 1),
+         (3, 1, 8, 64, 33, 3, 3, 1, 1, 1, 1), (2, 1, 10, 16, 5, 3, 3, 1, 1, 0, 1), (70, 1, 4, 4, 2, 3, 3, 1, 1, 2, 1)]
 SHORT_TOL = {1: 1e-5, 2: 2e-5, 3: 5e-6}
 
 
@@ -203,7 +204,8 @@ def test_conv_layer_backward_in_one_call(E, mode, shape):
 # Unit-stride transposed convolutions with 1, 2 or 4 output channels run a direct fp32 stencil kernel (the last layer of the
 # autoencoder configuration): 3x3 and other filter sizes, zero / full padding, widths that are no multiple of anything.
 FEW_FILTER_CONVT = [(3, 32, 16, 16, 1, 3, 3, 1, 1), (2, 5, 9, 13, 1, 3, 3, 0, 0), (2, 7, 6, 10, 2, 3, 3, 2, 2), (2, 3, 7, 5, 4, 3, 3, 1, 0),
-                    (2, 6, 8, 8, 1, 4, 4, 1, 2), (1, 4, 5, 11, 2, 5, 2, 2, 0), (2, 40, 12, 12, 4, 3, 3, 1, 1)]
+                    (2, 6, 8, 8, 1, 4, 4, 1, 2), (1, 4, 5, 11, 2, 5, 2, 2, 0), (2, 40, 12, 12, 4, 3, 3, 1, 1),
+                    (2, 9, 8, 64, 2, 3, 3, 1, 1), (1, 8, 4, 4, 1, 3, 3, 1, 1), (3, 8, 5, 136, 1, 3, 3, 0, 1), (37, 3, 6, 8, 1, 3, 3, 2, 1)]
 
 
 @pytest.mark.parametrize("mode", [1, 2, 3])
