@@ -175,28 +175,44 @@ __global__ void __launch_bounds__(256) conv_few3x3v_kernel(const float *__restri
 #pragma unroll
             for (int q = 0; q < 4; q++) acc[f][q] = b[f];
         const float *xp = x + (long long)n * C * H * W + (long long)ih0 * W + ow0;
-        for (int c = 0; c < C; c++, xp += (long long)H * W) {
-            float w[9][F];
+        // Channels go in groups of four: all twelve row vectors of a group (and the edge lanes' outer columns) are requested
+        // before the first is used.  One channel at a time, every channel costs the thread a full trip to HBM.
+        constexpr int CG = 4;
+        for (int c0 = 0; c0 < C; c0 += CG, xp += (long long)CG * H * W) {
+            float4 m[CG][3];
+            float edge[CG][3];
 #pragma unroll
-            for (int t = 0; t < 9; t++)
+            for (int k = 0; k < CG; k++)
 #pragma unroll
-                for (int f = 0; f < F; f++) w[t][f] = wk[(c * 9 + t) * F + f];
+                for (int r = 0; r < 3; r++) {
+                    const bool ok = rowok[r] && c0 + k < C;
+                    const float *row = xp + (long long)k * H * W + r * W;
+                    m[k][r] = ok ? __ldg(reinterpret_cast<const float4 *>(row)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    edge[k][r] = (ok && lane == 0 && has_left) ? __ldg(row - 1) : ((ok && lane == 31 && has_right) ? __ldg(row + 4) : 0.f);
+                }
 #pragma unroll
-            for (int r = 0; r < 3; r++) {
-                const float *row = xp + r * W;
-                const float4 m = rowok[r] ? __ldg(reinterpret_cast<const float4 *>(row)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                float left = __shfl_up_sync(0xffffffffu, m.w, 1), right = __shfl_down_sync(0xffffffffu, m.x, 1);
-                if (lane == 0) left = (rowok[r] && has_left) ? __ldg(row - 1) : 0.f;
-                if (lane == 31) right = (rowok[r] && has_right) ? __ldg(row + 4) : 0.f;
-                if (!has_left) left = 0.f;
-                if (!has_right) right = 0.f;
-                const float v[6] = {left, m.x, m.y, m.z, m.w, right};
+            for (int k = 0; k < CG; k++) {
+                const int c = min(c0 + k, C - 1);                 // past the last channel the inputs are zero: any weights do
+                float w[9][F];
 #pragma unroll
-                for (int s = 0; s < 3; s++)
+                for (int t = 0; t < 9; t++)
 #pragma unroll
-                    for (int q = 0; q < 4; q++)
+                    for (int f = 0; f < F; f++) w[t][f] = wk[(c * 9 + t) * F + f];
 #pragma unroll
-                        for (int f = 0; f < F; f++) acc[f][q] = fmaf(v[q + s], w[r * 3 + s][f], acc[f][q]);
+                for (int r = 0; r < 3; r++) {
+                    float left = __shfl_up_sync(0xffffffffu, m[k][r].w, 1), right = __shfl_down_sync(0xffffffffu, m[k][r].x, 1);
+                    if (lane == 0) left = edge[k][r];
+                    if (lane == 31) right = edge[k][r];
+                    if (!has_left) left = 0.f;
+                    if (!has_right) right = 0.f;
+                    const float v[6] = {left, m[k][r].x, m[k][r].y, m[k][r].z, m[k][r].w, right};
+#pragma unroll
+                    for (int s = 0; s < 3; s++)
+#pragma unroll
+                        for (int q = 0; q < 4; q++)
+#pragma unroll
+                            for (int f = 0; f < F; f++) acc[f][q] = fmaf(v[q + s], w[r * 3 + s][f], acc[f][q]);
+                }
             }
         }
         if (live) {
