@@ -17,7 +17,8 @@ struct Runtime {
     bool dense_tma = true;              // Dense GEMMs in modes 1/2: TMA-fed kernel (false: in-kernel conversion kernel)
     int tile_n_cap2 = 128;              // widest accumulator tile with two operand copies per stage (bf16x3)
     int tile_n_cap3 = 128;              // ... with three (bf16x6)
-    bool pool_short_patch = false;      // fold a 2x2 max-pool into the short-patch forward kernel too (its epilogue warps become the bottleneck: off)
+    bool pool_short_patch = false;      // fold a 2x2 max-pool into the tensor-core short-patch forward kernel too (its epilogue warps become the
+                                        // bottleneck: off; 3 x 3 unit-stride layers fold it into the fp32 stencil kernel regardless)
     bool conv_tma = true;               // convolutions in modes 1-3: TMA im2col kernel (false: in-kernel gather kernel)
     bool capturing = false;             // a stream capture (seera_graph_begin) is open
     bool tc_used = false;               // a tensor-core kernel ran since the status word was last read

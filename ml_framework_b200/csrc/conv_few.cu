@@ -271,6 +271,112 @@ int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, i
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 
+// ---- 3 x 3 unit-stride convolution with a few input channels + bias + activation + 2x2 / stride-2 max-pool ------------------
+// The first layer of an image network (3 -> 64 channels): 27 multiply-adds per output, which the tensor-core path can only
+// reach by gathering and splitting patches in producer warps.  Here a lane owns one pool window (2 x 2 outputs, a 4 x 4 input
+// patch per channel, read once with row / column validity worked out once) and a warp owns eight filters, whose 72 weights
+// per channel come from shared memory as broadcast 16-byte reads.  The layer output is never stored: pooled values, the
+// window-local argmax (scan order (0,0), (0,1), (1,0), (1,1), strict comparison: the first maximum wins, as in
+// cuda_maxpool_fwd) and the channels-last bf16 copies of the pooled tensor for the next convolution are.  Exact fp32.
+__global__ void __launch_bounds__(256) conv3x3_pool_kernel(const float *__restrict__ x, const float *__restrict__ Wt,
+                                                           const float *__restrict__ bias, PoolOut po, int NB, int C, int H, int W,
+                                                           int F, int OH, int OW, int ph, int pw, int act, FastDiv by_Pq,
+                                                           FastDiv by_OWq) {
+    extern __shared__ float wk[];                         // [C][9][F], then [F] biases
+    for (int e = threadIdx.x; e < C * 9 * F; e += blockDim.x) {
+        const int f = e % F, k = e / F;                   // k = c * 9 + t
+        wk[e] = __ldg(Wt + (long long)f * C * 9 + k);
+    }
+    for (int e = threadIdx.x; e < F; e += blockDim.x) wk[C * 9 * F + e] = bias ? __ldg(bias + e) : 0.f;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int OWq = OW >> 1, Pq = (OH >> 1) * OWq;
+    const long long windows = (long long)NB * Pq;
+    const long long tiles = (windows + 31) / 32;
+    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const long long wl = tile * 32 + lane;
+        if (wl >= windows) continue;
+        const int wi = (int)wl, n = by_Pq.div(wi), wrem = wi - n * Pq, ohq = by_OWq.div(wrem), owq = wrem - ohq * OWq;
+        const int ih0 = 2 * ohq - ph, iw0 = 2 * owq - pw;
+        bool rowok[4], colok[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) { rowok[i] = (unsigned)(ih0 + i) < (unsigned)H; colok[i] = (unsigned)(iw0 + i) < (unsigned)W; }
+        const float *xn = x + (long long)n * C * H * W + (long long)ih0 * W + iw0;
+        for (int fg = warp; fg * 8 < F; fg += 8) {
+            const int f0 = fg * 8;
+            float acc[4][8];
+#pragma unroll
+            for (int p = 0; p < 4; p++)
+#pragma unroll
+                for (int f = 0; f < 8; f++) acc[p][f] = 0.f;
+            for (int c = 0; c < C; c++) {
+                const float *xc = xn + (long long)c * H * W;
+                float v[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) v[i][j] = (rowok[i] && colok[j]) ? __ldg(xc + i * W + j) : 0.f;
+#pragma unroll
+                for (int t = 0; t < 9; t++) {
+                    const float4 wa = *reinterpret_cast<const float4 *>(wk + (c * 9 + t) * F + f0);
+                    const float4 wb = *reinterpret_cast<const float4 *>(wk + (c * 9 + t) * F + f0 + 4);
+                    const float w8[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+                    const int r = t / 3, s = t - r * 3;
+#pragma unroll
+                    for (int p = 0; p < 4; p++) {
+                        const float a = v[(p >> 1) + r][(p & 1) + s];
+#pragma unroll
+                        for (int f = 0; f < 8; f++) acc[p][f] = fmaf(a, w8[f], acc[p][f]);
+                    }
+                }
+            }
+            float mx[8];
+#pragma unroll
+            for (int f = 0; f < 8; f++) {
+                const float b = wk[C * 9 * F + f0 + f];
+                float m = -3.402823466e+38f;
+                int id = 0;
+#pragma unroll
+                for (int p = 0; p < 4; p++) {
+                    const float z = epilogue_act(acc[p][f] + b, act);
+                    if (z > m) { m = z; id = p; }
+                }
+                const long long q = ((long long)n * F + f0 + f) * Pq + wrem;
+                po.pooled[q] = m;
+                po.mask[q] = id;
+                mx[f] = m;
+            }
+            if (po.copy[0]) {
+                const long long o = ((long long)n * Pq + wrem) * po.Cp + f0;
+                *reinterpret_cast<uint4 *>(po.copy[0] + o) = split_chunk(mx);
+                if (po.ns >= 2) *reinterpret_cast<uint4 *>(po.copy[1] + o) = split_chunk(mx);
+                if (po.ns >= 3) *reinterpret_cast<uint4 *>(po.copy[2] + o) = split_chunk(mx);
+            }
+        }
+    }
+}
+
+bool conv_pool_simt_applies(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
+    const int OH = H + 2 * ph - 2, OW = W + 2 * pw - 2;
+    return R == 3 && S == 3 && sh == 1 && sw == 1 && C >= 1 && C <= 7 && (F & 7) == 0 && F <= 512 && OH >= 2 && OW >= 2 && !(OH & 1) && !(OW & 1) &&
+           (long long)NB * OH * OW < (1ll << 31) && (size_t)(C * 9 + 1) * F * sizeof(float) <= 40 * 1024;
+}
+
+int conv_pool_simt(const float *X, const float *Wt, const float *bias, const PoolOut &pool, int NB, int C, int H, int W, int F, int ph, int pw,
+                   int act, const char *name) {
+    const int OH = H + 2 * ph - 2, OW = W + 2 * pw - 2, Pq = (OH / 2) * (OW / 2);
+    const long long tiles = ((long long)NB * Pq + 31) / 32;
+    const int grid = (int)(tiles < (long long)rt().sm_count * 8 ? tiles : (long long)rt().sm_count * 8);
+    cudaStream_t st = rt().stream;
+    profile_begin();
+    conv3x3_pool_kernel<<<grid, 256, (size_t)(C * 9 + 1) * F * sizeof(float), st>>>(X, Wt, bias, pool, NB, C, H, W, F, OH, OW, ph, pw, act,
+                                                                               fast_div(Pq), fast_div(OW / 2));
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    profile_end(2.0 * NB * OH * OW * (double)F * C * 9);
+    return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
+}
+
 // ---- forward of a "same" 3 x 3 convolution with ONE input channel (a grey image into F filters; the data gradient of a
 // transposed convolution to one channel) --------------------------------------------------------------------------------
 // All output, almost no input: a lane reads the 3 x 6 inputs of its four pixels once (16-byte vector + neighbour shuffles,

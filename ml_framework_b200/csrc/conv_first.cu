@@ -867,11 +867,14 @@ bool conv_first_applies(int C, int R, int S) { return C * R * S <= 64; }
 // The forward with the 2x2 max-pool of its output folded into the epilogue (tensor-core variant only).
 bool conv_first_pool_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     FirstGeom g;
+    if (conv_pool_simt_applies(NB, C, H, W, F, R, S, sh, sw, ph, pw)) return true;
     return first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw) && first_tc_fwd_ok(g) && g.OH >= 2 && g.OW >= 2 && !(g.OH & 1) && !(g.OW & 1);
 }
 int conv_first_pool_fwd(const float *X, const float *Wt, const float *bias, const PoolOut &pool, int NB, int C, int H, int W, int F, int R,
                         int S, int ph, int pw, int sh, int sw, int act, const char *name) {
     if (!conv_first_pool_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw)) return fail(SEERA_E_LIMIT, "%s: shape outside the fused pool path", name);
+    if (conv_pool_simt_applies(NB, C, H, W, F, R, S, sh, sw, ph, pw))       // 3 x 3, unit stride: fp32 stencil with the pool folded in
+        return conv_pool_simt(X, Wt, bias, pool, NB, C, H, W, F, ph, pw, act, name);
     FirstGeom g;
     first_geom(g, NB, C, H, W, F, R, S, sh, sw, ph, pw);
     return first_tc_fwd(X, Wt, bias, nullptr, g, act, name, &pool);

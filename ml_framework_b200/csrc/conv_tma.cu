@@ -713,7 +713,8 @@ int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, 
 // In raster row order a 2x2 window must lie inside one epilogue warp's 32 rows: OW a power of two <= 16 and an even OH.
 static bool pool_in_epilogue_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw) {
     if (!rt().precision || !rt().conv_tma || !conv_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw)) return false;
-    if (conv_first_applies(C, R, S)) return rt().pool_short_patch && conv_first_pool_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw);
+    if (conv_first_applies(C, R, S))       // the fp32 stencil kernel always; the tensor-core short-patch kernel's pooled epilogue only on request
+        return conv_pool_simt_applies(NB, C, H, W, F, R, S, sh, sw, ph, pw) || (rt().pool_short_patch && conv_first_pool_ok(NB, C, H, W, F, R, S, sh, sw, ph, pw));
     if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return false;
     const int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
     return OH >= 2 && !(OH & 1) && (OW == 2 || OW == 4 || OW == 8 || OW == 16);

@@ -47,6 +47,10 @@ int conv_first_pool_fwd(const float *X, const float *Wt, const float *bias, cons
 bool conv_few_applies(int NB, int C, int F, int R, int S, int OH, int OW);
 int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F, int R, int S, int PH,
                  int PW, int OH, int OW, int act, int transposed, const char *name);
+// 3 x 3 unit-stride convolution with at most seven input channels + bias + activation + 2x2 max-pool, direct fp32 (conv_few.cu).
+bool conv_pool_simt_applies(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw);
+int conv_pool_simt(const float *X, const float *Wt, const float *bias, const PoolOut &pool, int NB, int C, int H, int W, int F, int ph, int pw,
+                   int act, const char *name);
 // Forward of a "same" 3 x 3 unit-stride convolution with one input channel, direct fp32 (conv_few.cu); bias may be null.
 bool conv_c1_fwd_applies(const float *X, const float *Y, int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw);
 int conv_c1_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int H, int W, int F, int ph, int act, const char *name);

@@ -294,7 +294,10 @@ def test_pool_folded_into_the_convolution_epilogue(E, mode, shape):
     N, C, H, W, F, KH, KW, sh, sw, ph, pw = shape
     OH, OW = (H + 2 * ph - KH) // sh + 1, (W + 2 * pw - KW) // sw + 1
     short = C * KH * KW <= 64
-    assert L.seera_conv2d_pool_fusable(N, C, H, W, F, KH, KW, sh, sw, ph, pw) == (0 if short else 1)
+    # 3 x 3 unit-stride short-patch layers with a multiple of 8 filters run an exact-fp32 kernel when the pool is folded in: the
+    # separate calls (tensor-core products) then agree with it to rounding, not bit for bit
+    exact = short and (KH, KW, sh, sw) == (3, 3, 1, 1) and C <= 7 and F % 8 == 0
+    assert L.seera_conv2d_pool_fusable(N, C, H, W, F, KH, KW, sh, sw, ph, pw) == (0 if short and not exact else 1)
     capi.check(L.seera_set_option(b"pool_short_patch", 1))            # off by default (slower), still has to be right
     assert L.seera_conv2d_pool_fusable(N, C, H, W, F, KH, KW, sh, sw, ph, pw) == 1
     rs = np.random.RandomState(sum(shape) + mode)
@@ -320,7 +323,13 @@ def test_pool_folded_into_the_convolution_epilogue(E, mode, shape):
         capi.check(L.seera_conv2d_bias_act_pool_fwd_s(xd, wd, bd, p2, m2, N, C, H, W, F, KH, KW, ph, pw, sh, sw, act, None,
                                                       ctypes.byref(keep), ctypes.byref(pc)))
         shp = (N, F, OH // 2, OW // 2)
-        assert np.array_equal(down(p1, shp), down(p2, shp)) and np.array_equal(down(m1, shp, np.int32), down(m2, shp, np.int32))
+        if exact:
+            ref = _act_ref(co.conv2d_forward(X, Wt, sh, sw, ph, pw) + b.reshape(1, F, 1, 1), act).astype(np.float32)
+            want, want_mask = co.maxpool2d_forward(ref, 2, 2, 2, 2, 0, 0)
+            assert rel_l2(down(p2, shp), want) < 2e-6 and rel_l2(down(p2, shp), down(p1, shp)) < 2e-5
+            assert (down(m2, shp, np.int32) == want_mask).mean() > 0.999          # ties within rounding may pick another tap
+        else:
+            assert np.array_equal(down(p1, shp), down(p2, shp)) and np.array_equal(down(m1, shp, np.int32), down(m2, shp, np.int32))
         # the returned copies of the pooled tensor feed the next convolution
         if F * 9 > 64:
             res = []
@@ -339,7 +348,7 @@ def test_pool_folded_into_the_convolution_epilogue(E, mode, shape):
             for p in (dw, db, dx):
                 L.seera_cuda_free(p)
         for a, bb in zip(*outs):
-            assert np.array_equal(a, bb)
+            assert rel_l2(a, bb) < 1e-4 if exact else np.array_equal(a, bb)
         L.seera_shadow_free(keep); L.seera_shadow_free(pc)
         for p in (y, p1, m1, p2, m2):
             L.seera_cuda_free(p)
