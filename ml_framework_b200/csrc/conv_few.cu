@@ -278,7 +278,7 @@ int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, i
 // per channel come from shared memory as broadcast 16-byte reads.  The layer output is never stored: pooled values, the
 // window-local argmax (scan order (0,0), (0,1), (1,0), (1,1), strict comparison: the first maximum wins, as in
 // cuda_maxpool_fwd) and the channels-last bf16 copies of the pooled tensor for the next convolution are.  Exact fp32.
-__global__ void __launch_bounds__(256) conv3x3_pool_kernel(const float *__restrict__ x, const float *__restrict__ Wt,
+__global__ void __launch_bounds__(256, 3) conv3x3_pool_kernel(const float *__restrict__ x, const float *__restrict__ Wt,
                                                            const float *__restrict__ bias, PoolOut po, int NB, int C, int H, int W,
                                                            int F, int OH, int OW, int ph, int pw, int act, FastDiv by_Pq,
                                                            FastDiv by_OWq) {
