@@ -225,7 +225,7 @@ def run_gpu(args, work):
     eager_ms = None
     if use_graph and dist is not None:
         from ml_framework_b200 import dp
-        loss_t = tr.capture_data_parallel(Xd, Yd, tr.model._arena_allreduce, buckets=dp.plan_buckets(tr.model, 4),
+        loss_t = tr.capture_data_parallel(Xd, Yd, tr.model._arena_allreduce, buckets=dp.plan_buckets(tr.model, args.buckets),
                                           reduce_range=tr.model._reduce_range, wait=tr.model._reduce_wait)
         for _ in range(args.warmup):
             tr.replay_data_parallel()
@@ -422,6 +422,7 @@ def main():
                          "3/2 for the fp32 configurations")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="engine option for seera_set_option (repeatable), e.g. tile_n_cap3=128")
+    ap.add_argument("--buckets", type=int, default=4, help="data parallel: gradient buckets (all-reduces) per step")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a captured step")
     args = ap.parse_args()
