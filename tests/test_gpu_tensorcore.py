@@ -163,7 +163,8 @@ def _dact_ref(y, act):
 # (N, C, H, W, F, KH, KW, sh, sw, ph, pw): tensor-core shapes (kept copies, dz never stored), short-patch shapes (the
 # bias gradient rides in a spare patch column; none spare when C*KH*KW is 16) and a strided one.
 LAYER_BWD = [(4, 16, 8, 8, 24, 3, 3, 1, 1, 1, 1), (2, 70, 12, 12, 130, 3, 3, 1, 1, 1, 1), (3, 8, 16, 16, 16, 3, 3, 2, 2, 1, 1),
-             (4, 3, 16, 16, 20, 3, 3, 1, 1, 1, 1), (2, 1, 12, 12, 6, 4, 4, 1, 1, 2, 2), (2, 1, 8, 8, 70, 3, 3, 1, 1, 1, 1)]
+             (4, 3, 16, 16, 20, 3, 3, 1, 1, 1, 1), (2, 1, 12, 12, 6, 4, 4, 1, 1, 2, 2), (2, 1, 8, 8, 70, 3, 3, 1, 1, 1, 1),
+             (3, 3, 16, 16, 64, 3, 3, 1, 1, 1, 1), (2, 1, 8, 12, 128, 3, 3, 1, 1, 1, 1), (70, 2, 6, 6, 64, 3, 3, 1, 1, 1, 1)]
 
 
 @pytest.mark.parametrize("mode", [2, 3])
