@@ -428,44 +428,68 @@ __global__ void __launch_bounds__(256, 4) dz_shadow_window_kernel(const float *_
                                                                   int wtiles, int act, __nv_bfloat16 *__restrict__ d0,
                                                                   __nv_bfloat16 *__restrict__ d1, __nv_bfloat16 *__restrict__ d2,
                                                                   float *__restrict__ partial) {
+    // Tile = 32 windows x 64 channels.  Read side: lane = window, warp = 8 channels (full lines of the channel-major pooled
+    // tensors).  Write side: the tile goes through shared memory so that 8 consecutive lanes write the 128 bytes one pixel owns
+    // in the channels-last copies (a lane-per-window store touches 32 different lines per instruction).
+    __shared__ __align__(16) float sval[32][64 + 4];
+    __shared__ __align__(16) int smk[32][64 + 4];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int cb = blockIdx.y * 64 + warp * 8;
     const int P = H * W, Wq = W >> 1, Pq = (H >> 1) * Wq;
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[i] = 0.f;
-    if (cb < Cp) {
-        for (int item = blockIdx.x; item < items; item += gridDim.x) {
-            const int img = item / wtiles, q = (item - img * wtiles) * 32 + lane;
-            if (q >= Pq) continue;
-            float val[8], pv[8];
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int img = item / wtiles, q0 = (item - img * wtiles) * 32, q = q0 + lane;
+        if (cb < Cp) {
+            float val[8];
             int mk[8];
+            if (q < Pq) {
+                float pv[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const long long o = ((long long)img * C + min(cb + i, C - 1)) * Pq + q;
-                val[i] = __ldg(gp + o);
-                mk[i] = __ldg(mask + o);
-                pv[i] = act != SEERA_ACT_NONE ? __ldg(yp + o) : 1.f;
-            }
+                for (int i = 0; i < 8; i++) {
+                    const long long o = ((long long)img * C + min(cb + i, C - 1)) * Pq + q;
+                    val[i] = __ldg(gp + o);
+                    mk[i] = __ldg(mask + o);
+                    pv[i] = act != SEERA_ACT_NONE ? __ldg(yp + o) : 1.f;
+                }
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                if (act != SEERA_ACT_NONE) val[i] *= slope_from_output(pv[i], act);
-                if (cb + i >= C) val[i] = 0.f;
-                acc[i] += ((unsigned)mk[i] < 4u) ? val[i] : 0.f;
+                for (int i = 0; i < 8; i++) {
+                    if (act != SEERA_ACT_NONE) val[i] *= slope_from_output(pv[i], act);
+                    if (cb + i >= C) val[i] = 0.f;
+                    acc[i] += ((unsigned)mk[i] < 4u) ? val[i] : 0.f;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) { val[i] = 0.f; mk[i] = -1; }
             }
-            const int ohq = q / Wq, owq = q - ohq * Wq;
+            *reinterpret_cast<float4 *>(&sval[lane][warp * 8]) = make_float4(val[0], val[1], val[2], val[3]);
+            *reinterpret_cast<float4 *>(&sval[lane][warp * 8 + 4]) = make_float4(val[4], val[5], val[6], val[7]);
+            *reinterpret_cast<int4 *>(&smk[lane][warp * 8]) = make_int4(mk[0], mk[1], mk[2], mk[3]);
+            *reinterpret_cast<int4 *>(&smk[lane][warp * 8 + 4]) = make_int4(mk[4], mk[5], mk[6], mk[7]);
+        }
+        __syncthreads();
+        // thread = (window w, 8-channel chunk ch): its window's four pixels, 16 bytes of each copy per pixel
+        const int ch = threadIdx.x & 7, c8 = blockIdx.y * 64 + ch * 8, w = threadIdx.x >> 3, qq = q0 + w;
+        if (c8 < Cp && qq < Pq) {
+            const float4 a = *reinterpret_cast<const float4 *>(&sval[w][ch * 8]), b = *reinterpret_cast<const float4 *>(&sval[w][ch * 8 + 4]);
+            const int4 ma = *reinterpret_cast<const int4 *>(&smk[w][ch * 8]), mb = *reinterpret_cast<const int4 *>(&smk[w][ch * 8 + 4]);
+            const float vv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            const int mm[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+            const int ohq = qq / Wq, owq = qq - ohq * Wq;
 #pragma unroll
             for (int pos = 0; pos < 4; pos++) {
                 float v[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) v[i] = mk[i] == pos ? val[i] : 0.f;
+                for (int i = 0; i < 8; i++) v[i] = mm[i] == pos ? vv[i] : 0.f;
                 const int p = (2 * ohq + (pos >> 1)) * W + 2 * owq + (pos & 1);
-                const long long o = ((long long)img * P + p) * Cp + cb;
+                const long long o = ((long long)img * P + p) * Cp + c8;
                 *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
                 if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
                 if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
             }
         }
+        __syncthreads();
     }
     if (partial) {
 #pragma unroll
