@@ -315,7 +315,7 @@ def run_gpu(args, work):
             ach = pfl / (pms / 1e3) / 1e12
             # DRAM bytes per contraction launch from the ncu launch list of this workload (profiles/bench_c3_launch_list.txt:
             # dram__bytes_read.sum + dram__bytes_write.sum of the 17 contraction launches of a C3 step = 620.9 MB)
-            traffic = 36.5e6 if (args.workload == "c3" and args.precision == "3/2") else None
+            traffic = 35.4e6 if (args.workload == "c3" and args.precision == "3/2") else None
             roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": ach / peaks["tensor"],
                     "traffic": traffic, "kernel": "contraction (Dense/Conv fwd, dX, dW)", "launches_per_step": cnt / min(args.steps, 5),
                     "ms_per_step_in_kernel": pms / min(args.steps, 5), "peak_source": peaks["src"] + " sustained bf16",
