@@ -355,20 +355,25 @@ __global__ void __launch_bounds__(256, 4) dz_shadow_kernel(const float *__restri
                                                         int Cp, int items, int ptiles,
                                                         int act, __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
                                                         __nv_bfloat16 *__restrict__ d2, float *__restrict__ partial) {
-    // warp = group of 8 consecutive channels, lane = pixel: every load is one 128-byte line of a channel plane and each
-    // thread ends up with the 8 channels of its pixel, i.e. one 16-byte chunk of the channels-last row: no transpose.
+    // Read side: warp = group of 8 consecutive channels, lane = pixel: every load is one 128-byte line of a channel plane.
+    // Write side: the 32-pixel x 64-channel tile goes through shared memory so that 8 consecutive lanes write the 128 bytes one
+    // pixel owns in the channels-last copies and a warp writes four whole pixels per store.
+    __shared__ __align__(16) float sdz[32][64 + 4];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int cb = blockIdx.y * 64 + warp * 8;
     const int P = H * W, Wq = W >> 1, Pq = (H >> 1) * Wq;
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[i] = 0.f;
-    if (cb < Cp) {
-        for (int item = blockIdx.x; item < items; item += gridDim.x) {
-            const int img = item / ptiles, p = (item - img * ptiles) * 32 + lane;
-            if (p >= P) continue;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int img = item / ptiles, p0 = (item - img * ptiles) * 32, p = p0 + lane;
+        if (cb < Cp) {
             float dy[8], yv[8];
             bool sloped = false;
+            if (p >= P) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) dy[i] = 0.f;
+            } else {
             if (gp) {
                 const int h = p / W, w = p - h * W;
                 const int win = (h >> 1) * Wq + (w >> 1), loc = ((h & 1) << 1) | (w & 1);
@@ -403,11 +408,22 @@ __global__ void __launch_bounds__(256, 4) dz_shadow_kernel(const float *__restri
                 if (cb + i >= C) dy[i] = 0.f;          // padding channels of the last group
                 acc[i] += dy[i];
             }
-            const long long o = ((long long)img * P + p) * Cp + cb;
-            *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(dy);
-            if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(dy);
-            if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(dy);
+            }
+            *reinterpret_cast<float4 *>(&sdz[lane][warp * 8]) = make_float4(dy[0], dy[1], dy[2], dy[3]);
+            *reinterpret_cast<float4 *>(&sdz[lane][warp * 8 + 4]) = make_float4(dy[4], dy[5], dy[6], dy[7]);
         }
+        __syncthreads();
+        const int ch = threadIdx.x & 7, c8 = blockIdx.y * 64 + ch * 8, pp = p0 + (threadIdx.x >> 3);
+        if (c8 < Cp && pp < P) {
+            const float4 a = *reinterpret_cast<const float4 *>(&sdz[threadIdx.x >> 3][ch * 8]);
+            const float4 b = *reinterpret_cast<const float4 *>(&sdz[threadIdx.x >> 3][ch * 8 + 4]);
+            float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            const long long o = ((long long)img * P + pp) * Cp + c8;
+            *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
+            if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
+            if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+        }
+        __syncthreads();
     }
     if (partial) {
 #pragma unroll
