@@ -433,7 +433,9 @@ def main():
         return
     work = wl.WORKLOADS[args.workload]()
     if args.precision is None:
-        args.precision = "1" if work.precision == "bf16" else "3/2"
+        from ml_framework_b200.train import POLICY          # the policy the parity gates are checked at
+        f, b = POLICY[work.precision]
+        args.precision = str(f) if f == b else "%d/%d" % (f, b)
     if args.impl == "reference":
         run_reference(args, work)
     else:

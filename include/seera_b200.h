@@ -42,7 +42,7 @@ enum {
 };
 
 /* ---- runtime ------------------------------------------------------------------ */
-int         seera_init(int device);                 /* selects the device, creates the stream; idempotent */
+int         seera_init(int device);                 /* selects the device, creates the stream; idempotent for the same device, SEERA_E_ARG for another (one device per process) */
 int         seera_synchronize(void);                /* waits for the engine's stream                     */
 int         seera_set_stream(void *cuda_stream);    /* adopt an external cudaStream_t (NULL = own stream) */
 void       *seera_get_stream(void);
@@ -56,11 +56,19 @@ void       *seera_event_create(void);
 int         seera_event_record(void *event);
 float       seera_event_elapsed_ms(void *start, void *stop);   /* waits for `stop`; < 0 on error */
 int         seera_event_destroy(void *event);
-/* Contraction profile: while enabled, every GEMM / convolution launch of this library is bracketed by
- * events; seera_profile_read() waits for them and returns their count, summed device time and summed
- * algorithmic FLOPs (2*M*N*K each), then clears the record. */
+/* Launch profile: while enabled, every GEMM / convolution launch of this library and every bandwidth-bound pass
+ * (optimizer, activation backward, pooling, loss heads, operand copies) is bracketed by events on the engine's
+ * stream.  Enabling starts an empty table.  seera_profile_read() waits for the events and returns the
+ * contractions' count, summed device time and summed algorithmic FLOPs (2*M*N*K each), then clears the table.
+ * seera_profile_read_kinds() gives the same three figures split by kind (index 0 forward products, 1 data
+ * gradients dX / dA, 2 weight gradients dW / dB) and leaves the table alone.  seera_profile_report() writes one
+ * line per tag, "tag<TAB>kind<TAB>launches<TAB>ms<TAB>work<NEWLINE>" (kind 0-2: work = FLOPs; kind 3: work =
+ * algorithmic bytes of a bandwidth-bound pass), and leaves the table alone.  Nothing is recorded during a
+ * stream capture.  No counterpart in the reference. */
 int         seera_profile_enable(int on);
 int         seera_profile_read(uint64_t *launches, double *ms, double *flops);
+int         seera_profile_read_kinds(uint64_t *launches3, double *ms3, double *flops3);
+int         seera_profile_report(char *buf, size_t size);
 /* Precision of the GEMM / convolution contractions:
  *   0 fp32 CUDA-core tiles (bit-for-bit fp32 products, default for the fp32 configurations)
  *   1 bf16 operands, fp32 accumulate on the tensor cores (one pass)
@@ -137,7 +145,7 @@ int   seera_concat_bwd(const float *dout, float *da, float *db, int N, int n1, i
  * them batch by batch, Seera.py:748-755). */
 int   seera_onehot_f32(const int *labels, float *out, int n, int classes);
 /* Measurement aid: occupies the compute stream for about `microseconds` (0..100000) with a one-thread kernel, so that
- * work enqueued right after it queues up and runs back to back; bench.py uses it before its per-kernel event pass. */
+ * work enqueued right after it queues up and runs back to back (used before a per-kernel event pass). */
 int   seera_stream_delay(int microseconds);
 int   seera_copy_upload(void *dev, const void *pinned_host, size_t n_bytes);
 int   seera_copy_download(void *pinned_host, const void *dev, size_t n_bytes);
@@ -252,8 +260,8 @@ int seera_conv2DTranspose_bias_act_fwd(const float *X, const float *W, const flo
 /* Channels-last bf16 copies of one NCHW activation tensor, as the tensor-core convolutions read them.  A forward call
  * can hand the copies of its input to the matching backward call instead of producing them twice.  Opaque; owned
  * by the caller once returned; release with seera_shadow_free (stream-ordered, NULL allowed).
- * No counterpart in the reference, whose convolutions re-run im2col in every call (engine_cuda/src/conv_fwd.cu,
- * conv_bwd.cu). */
+ * No counterpart in the reference, whose convolutions re-run im2col in every call
+ * (engine_cuda/src/convolution.cu:15-453). */
 typedef struct seera_shadow seera_shadow_t;
 void seera_shadow_free(seera_shadow_t *s);
 /* seera_conv2d_bias_act_fwd with kept copies: x_in (may be NULL) are copies of `image` from an earlier call;
@@ -302,8 +310,7 @@ int seera_act_bias_bwd(const float *dy, const float *y, float *dz, float *dbias,
  * replay.  The regular entry takes its partial-sum scratch from the pool; this one uses a fixed 256 KiB device
  * array built into the library (present on every GPU that loads it, until exit) and never calls cudaMalloc,
  * cudaFree or the pool.  Same arguments and results as seera_act_bias_bwd, with these limits:
- *   - channels <= 65536; when splits * channels would not fit, fewer and longer partial sums are used (dbias
- *     then differs from the regular entry only by summation order); more channels -> SEERA_E_LIMIT.
+ *   - channels <= 65536 (the array holds one partial sum per channel and split); more -> SEERA_E_LIMIT.
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
  *     first call before any stream capture begins.
  *   - all calls share the one array: two calls whose kernels overlap on the GPU (different streams or
@@ -324,6 +331,13 @@ int seera_softmax_cce_fwd_bwd(const float *z, const float *onehot, float *p, flo
 int seera_mse_partials(int size);
 int seera_mse_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp,
                       int size, float inv_count);
+/* Mean absolute error (Seera.py:947-949; the gradient of |d| is sign(d) with 0 at 0, as abs_fwd of
+ * engine/src/activation_ops.cpp:50-56) and binary cross-entropy -y log(p+eps) - (1-y) log(1-p+eps)
+ * (Seera.py:951-953), same calling convention and scratch as seera_mse_fwd_bwd. */
+int seera_mae_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp,
+                      int size, float inv_count);
+int seera_bce_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp,
+                      int size, float inv_count, float eps);
 
 /* Adam (Seera.py:1069-1084) and SGD with momentum (Seera.py:1006-1008) in one pass, in place.
  * The caller passes the fp32-rounded scalars omb1 = 1-beta1, omb2 = 1-beta2, c1 = 1-beta1^t,
@@ -336,6 +350,45 @@ int seera_sgd_step(float *w, const float *g, float *vel, int n, float lr, float 
  * for Adam, {lr, momentum, grad_scale} for SGD. */
 int seera_adam_step_dev(float *w, const float *g, float *m, float *v, int n, const float *hyper);
 int seera_sgd_step_dev(float *w, const float *g, float *vel, int n, const float *hyper);
+
+/* ---- data parallel: the gradient exchange of a batch sharded over the GPUs of one node -----------------------------
+ * No counterpart in the reference (single GPU only).  One process per GPU; every rank holds the same weights and
+ * trains its shard; the weight-gradient arena is summed over the ranks with NCCL over NVLink / NVSwitch and the
+ * optimizer divides by the world size (grad_scale).  NCCL is opened with dlopen by seera_dp_init: a single-GPU
+ * caller never loads it.
+ *   seera_dp_unique_id   rank 0 makes the communicator id (seera_dp_unique_id_bytes() bytes) and hands it to the
+ *                        other ranks by any means (a file, a socket, the launcher's store)
+ *   seera_dp_init        joins the communicator on the device chosen by seera_init; collective over the ranks
+ *   seera_dp_alloc/free  device memory the collectives use in place (ncclMemAlloc, registered with the
+ *                        communicator: no staging copy, in-switch reduction where NVSwitch offers it); zeroed
+ *   seera_dp_allreduce   in-place sum (op 0), max (1) or min (2) of n floats on the COMPUTE stream
+ *   seera_dp_broadcast   in-place broadcast from `root` on the compute stream
+ *   seera_dp_reduce_range  in-place sum of floats [begin, end) of `arena` on the engine's COMMUNICATION stream,
+ *                        ordered after everything the compute stream holds so far; returns at once, so the
+ *                        backward kernels of earlier layers overlap the exchange
+ *   seera_dp_join        the compute stream waits for every range enqueued since the last join
+ *                        (reduce_range and join are event edges: a step recorded with seera_graph_begin/end
+ *                        carries its collectives inside the one graph)
+ *   seera_dp_poll        NCCL's asynchronous error state as a status
+ *   seera_dp_wait_host   host-side wait for both streams with a deadline in milliseconds (< 0: none); on expiry
+ *                        or on an NCCL error the communicator is aborted and an error status returned - a peer
+ *                        that left becomes a status code on the host, never a wait inside a kernel
+ *   seera_dp_finalize    destroys the communicator and frees seera_dp_alloc blocks still held */
+int   seera_dp_unique_id_bytes(void);
+int   seera_dp_unique_id(void *out, int size);
+int   seera_dp_init(int rank, int world, const void *unique_id, int size);
+int   seera_dp_rank(void);
+int   seera_dp_world(void);
+int   seera_dp_nccl_version(void);
+void *seera_dp_alloc(size_t bytes);
+int   seera_dp_free(void *p);
+int   seera_dp_allreduce(float *buf, long long n, int op);
+int   seera_dp_broadcast(float *buf, long long n, int root);
+int   seera_dp_reduce_range(float *arena, long long begin, long long end);
+int   seera_dp_join(void);
+int   seera_dp_poll(void);
+int   seera_dp_wait_host(int timeout_ms);
+int   seera_dp_finalize(void);
 
 #ifdef __cplusplus
 }

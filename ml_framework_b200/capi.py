@@ -15,7 +15,7 @@ LIB_PATH = os.path.join(PKG, "libseera_b200.so")
 
 _CT = {
     "int": ctypes.c_int, "float": ctypes.c_float, "size_t": ctypes.c_size_t, "uint64_t": ctypes.c_uint64,
-    "void": None,
+    "long long": ctypes.c_longlong, "void": None,
 }
 
 

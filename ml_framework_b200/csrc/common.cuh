@@ -59,7 +59,16 @@ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // Contraction profile (seera_profile_enable): bracket a launch sequence with events and book its FLOPs.
 void profile_begin();
-void profile_end(double flops);
+void profile_end_bytes(double bytes, const char *tag);      // a bandwidth-bound pass: its algorithmic bytes
+void profile_end(double flops, const char *name = nullptr);    // name ending in (dX)/(dA) or (dW)/(dB) books the launch as a backward product
+
+// Brackets the launches of a bandwidth-bound pass for the profile: constructed before them, destroyed after them.
+struct ProfBytes {
+    double bytes;
+    const char *tag;
+    ProfBytes(double b, const char *t) : bytes(b), tag(t) { profile_begin(); }
+    ~ProfBytes() { profile_end_bytes(bytes, tag); }
+};
 
 // Pool-backed scratch for internal use (split-K partials, operand shadows).
 void *scratch_alloc(size_t bytes);

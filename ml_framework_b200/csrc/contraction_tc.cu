@@ -248,7 +248,7 @@ int run_tc(const AL &al, const BL &bl, const CS &cs, int M, int N, int K, bool a
         e = cudaGetLastError();
     }
     if (partial) scratch_free(partial);
-    profile_end(2.0 * M * N * (double)K);
+    profile_end(2.0 * M * N * (double)K, name);
     rt().tc_used = true;
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }

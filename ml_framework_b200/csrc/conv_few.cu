@@ -247,7 +247,7 @@ int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, i
 #undef SEERA_FEW3V
         count_launch();
         cudaError_t e3 = cudaGetLastError();
-        profile_end(2.0 * total * (double)F * C * R * S);
+        profile_end(2.0 * total * (double)F * C * R * S, name);
         return e3 == cudaSuccess ? SEERA_OK : check_cuda(e3, name);
     }
     if (R == 3 && S == 3) {
@@ -259,7 +259,7 @@ int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, i
 #undef SEERA_FEW3
         count_launch();
         cudaError_t e3 = cudaGetLastError();
-        profile_end(2.0 * total * (double)F * C * R * S);
+        profile_end(2.0 * total * (double)F * C * R * S, name);
         return e3 == cudaSuccess ? SEERA_OK : check_cuda(e3, name);
     }
 #define SEERA_FEW(FV, KV) conv_few_kernel<FV, KV><<<grid, 256, smem, st>>>(X, Wt, bias, Y, NB, C, H, W, OH, OW, R, S, PH, PW, act, transposed, by_plane, by_OW)
@@ -267,7 +267,7 @@ int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, i
 #undef SEERA_FEW
     count_launch();
     cudaError_t e = cudaGetLastError();
-    profile_end(2.0 * total * (double)F * C * R * S);
+    profile_end(2.0 * total * (double)F * C * R * S, name);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 
@@ -373,7 +373,7 @@ int conv_pool_simt(const float *X, const float *Wt, const float *bias, const Poo
                                                                                fast_div(Pq), fast_div(OW / 2));
     count_launch();
     cudaError_t e = cudaGetLastError();
-    profile_end(2.0 * NB * OH * OW * (double)F * C * 9);
+    profile_end(2.0 * NB * OH * OW * (double)F * C * 9, name);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 
@@ -445,7 +445,7 @@ int conv_c1_fwd(const float *X, const float *Wt, const float *bias, float *Y, in
                                                                                      fast_div(OH * (W / 4)), fast_div(W / 4));
     count_launch();
     cudaError_t e = cudaGetLastError();
-    profile_end(2.0 * NB * OH * W * (double)F * 9);
+    profile_end(2.0 * NB * OH * W * (double)F * 9, name);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 
@@ -622,7 +622,7 @@ int wgrad_c1(const float *A, const float *dY, float *dW, int NB, int H, int W, i
         count_launch();
         e = cudaGetLastError();
     }
-    profile_end(2.0 * NB * OH * OW * (double)F * R * S);
+    profile_end(2.0 * NB * OH * OW * (double)F * R * S, name);
     scratch_free(partial);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }

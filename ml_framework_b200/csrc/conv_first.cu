@@ -815,7 +815,7 @@ static int first_tc_fwd(const float *X, const float *Wt, const float *bias, floa
     else { e = raise_smem_limit(first_tc_fwd_kernel<3>, f3); if (e == cudaSuccess) first_tc_fwd_kernel<3><<<grid, FTC_THREADS, smem, st>>>(X, Wt, cs, g, bias, act, bn, stages, nslices, pool_on, po, tc_status_word()); }
     count_launch();
     if (e == cudaSuccess) e = cudaGetLastError();
-    profile_end(2.0 * pixels * (double)g.F * g.K);
+    profile_end(2.0 * pixels * (double)g.F * g.K, name);
     rt().tc_used = true;
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
@@ -849,7 +849,7 @@ static int first_tc_wgrad(const float *X, const DzSource &src, float *dW, float 
         count_launch();
         e = cudaGetLastError();
     }
-    profile_end(2.0 * pixels * (double)g.F * g.K);
+    profile_end(2.0 * pixels * (double)g.F * g.K, name);
     scratch_free(partial);
     rt().tc_used = true;
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
@@ -910,7 +910,7 @@ int conv_first_fwd(const float *X, const float *Wt, const float *bias, float *Y,
     }
     count_launch();
     cudaError_t e = cudaGetLastError();
-    profile_end(2.0 * pixels * (double)F * g.K);
+    profile_end(2.0 * pixels * (double)F * g.K, name);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 
@@ -944,7 +944,7 @@ static int first_wgrad_run(const float *X, const DzSource &src, float *dW, float
         count_launch();
         e = cudaGetLastError();
     }
-    profile_end(2.0 * pixels * (double)g.F * g.K);
+    profile_end(2.0 * pixels * (double)g.F * g.K, name);
     scratch_free(partial);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }

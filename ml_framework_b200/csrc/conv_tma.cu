@@ -68,8 +68,11 @@ static int make_map_im2col_box(CUtensorMap *m, const void *base, int NB, int H, 
     if (r != CUDA_SUCCESS)
         return fail(SEERA_E_CUDA, "cuTensorMapEncodeIm2col failed (%d) for %dx%dx%dx%d window %dx%d stride %d,%d pad %d,%d", (int)r, NB, H, W,
                     Cp, R, S, sh, sw, ph, pw);
-    // Drivers up to CUDA 13.1 mis-encode one descriptor bit for tensors smaller than 128 KiB; clear it as the vendor's
-    // own templates do for the same driver range.
+    // Known driver defect, documented in the CUTLASS sources (include/cute/atom/copy_traits_sm90_im2col.hpp, the note beside
+    // cuTensorMapEncodeIm2col): drivers up to CUDA 13.1 set bit 21 of the second 64-bit word of an IM2COL descriptor when the
+    // whole tensor is smaller than 128 KiB, and a load through such a descriptor returns wrong pixels.  Clearing the bit is
+    // the published remedy for that driver range.  tests/test_gpu_tensorcore.py::test_im2col_maps_of_tensors_below_128_kib
+    // runs convolutions on both sides of the 128 KiB boundary.
     int drv = 0;
     if (cudaDriverGetVersion(&drv) == cudaSuccess && drv <= 13010 && (size_t)NB * H * W * Cp * 2 < 131072)
         reinterpret_cast<uint64_t *>(m)[1] &= ~(1ull << 21);
@@ -120,6 +123,7 @@ static int make_nhwc(const float *src, int NB, int C, int H, int W, int ns, Nhwc
     dim3 grid((P + 31) / 32, (s.Cp + 63) / 64, NB);
     if (grid.z > 65535 || grid.y > 65535) return fail(SEERA_E_LIMIT, "channels-last shadow: batch or channel count too large");
     cudaStream_t st = rt().stream;
+    ProfBytes pb(4.0 * NB * C * P + (double)ns * bytes, "shadow_nhwc");
     if (ns == 1) shadow_nhwc_kernel<1><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
     else if (ns == 2) shadow_nhwc_kernel<2><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
     else shadow_nhwc_kernel<3><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
@@ -739,6 +743,8 @@ int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, 
     if (blocks > items) blocks = (int)items;
     dim3 grid((unsigned)blocks, (unsigned)cchunks);
     cudaStream_t st = rt().stream;
+    // input read once; pooled values and argmax mask written; ns channels-last copies of the pooled tensor written
+    ProfBytes pb(4.0 * N * C * H * W + 8.0 * N * C * Pq + (double)ns * bytes, "pool2x2_shadow");
     if (ns == 1) pool2x2_shadow_kernel<1><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
     else if (ns == 2) pool2x2_shadow_kernel<2><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
     else pool2x2_shadow_kernel<3><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
@@ -821,6 +827,11 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
     if (dbias) { partial = (float *)scratch_alloc((size_t)splits * C * sizeof(float)); if (!partial) return SEERA_E_OOM; }
     dim3 grid((unsigned)splits, (unsigned)cchunks);
     cudaStream_t st = rt().stream;
+    // by window: pooled gradient + mask (+ pooled output) read at a quarter of the layer's resolution; otherwise the
+    // full-resolution gradient (or pooled gradient + mask) and the layer output; ns copies of dz written either way
+    const double in_bytes = by_window ? 4.0 * NB * C * (P / 4) * (2 + (yp ? 1 : 0))
+                                      : 4.0 * NB * C * ((g ? (double)P : 2.0 * (P / 4)) + (act ? (double)P : 0.0));
+    ProfBytes pb(in_bytes + (double)ns * bytes, by_window ? "dz_shadow_window" : "dz_shadow");
     if (by_window) {
         if (ns == 1) dz_shadow_window_kernel<1><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
         else if (ns == 2) dz_shadow_window_kernel<2><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);

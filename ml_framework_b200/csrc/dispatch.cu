@@ -1,6 +1,8 @@
 // Public GEMM / convolution entries: choose the contraction engine by the precision mode.
-//   mode 0    fp32 CUDA-core tiles (gemm_conv_simt.cu)
-//   mode 1/2  tcgen05 tensor-core tiles (contraction_tc.cu): bf16 single pass / bf16x3
+//   mode 0      fp32 CUDA-core tiles (gemm_conv_simt.cu)
+//   mode 1/2/3  tcgen05 tensor-core tiles fed by TMA (gemm_tma.cu, conv_tma.cu; short patches conv_first.cu, few channels
+//               conv_few.cu): bf16 single pass / bf16x3 / bf16x6.  The in-kernel-gather kernel of contraction_tc.cu is the
+//               fallback for geometries a tensor map cannot express and is selectable with the "dense_tma" / "conv_tma" options.
 // Argument validation is shared: the CUDA-core entry checks are repeated by the tensor-core path through
 // the same geometry tests before any launch.
 #include "common.cuh"

@@ -237,16 +237,30 @@ __global__ void __launch_bounds__(256) scaled_sum_kernel(const float *__restrict
     if (threadIdx.x == 0) *out = t * scale;
 }
 
-__global__ void __launch_bounds__(256) mse_kernel(const float *__restrict__ p, const float *__restrict__ y,
-                                                  float *__restrict__ partials, float *__restrict__ dp,
-                                                  long long n, float inv_count) {
+// Element-wise losses with their gradient in the same pass.  KIND 0: (p-y)^2 (Seera.py:943-945); 1: |p-y| with the sign
+// convention of abs_fwd, 0 at 0 (Seera.py:947-949, engine/src/activation_ops.cpp:50-56); 2: binary cross-entropy
+// -y log(p+eps) - (1-y) log(1-p+eps) (Seera.py:951-953).  dp = dloss/dp * inv_count; per-block sums go to `partials`.
+template <int KIND>
+__global__ void __launch_bounds__(256) elem_loss_kernel(const float *__restrict__ p, const float *__restrict__ y,
+                                                        float *__restrict__ partials, float *__restrict__ dp,
+                                                        long long n, float inv_count, float eps) {
     __shared__ float sm[8];
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
     float acc = 0.f;
     for (long long i = tid; i < n; i += nthr) {
-        float d = p[i] + y[i] * -1.0f;
-        acc += d * d;
-        dp[i] = (2.0f * d) * inv_count;
+        if (KIND == 0) {
+            float d = p[i] + y[i] * -1.0f;
+            acc += d * d;
+            dp[i] = (2.0f * d) * inv_count;
+        } else if (KIND == 1) {
+            float d = p[i] + y[i] * -1.0f;
+            acc += fabsf(d);
+            dp[i] = (d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f)) * inv_count;
+        } else {
+            const float pv = p[i], yv = y[i], a = pv + eps, b = (1.f - pv) + eps;
+            acc += -yv * logf(a) - (1.f - yv) * logf(b);
+            dp[i] = (-yv / a + (1.f - yv) / b) * inv_count;
+        }
     }
     float t = block_sum_256(acc, sm);
     if (threadIdx.x == 0) partials[blockIdx.x] = t;
@@ -263,10 +277,11 @@ __device__ __forceinline__ void adam_one(float &w, float g, float &m, float &v, 
     w -= (a.lr * mh) / (sqrtf(vh) + a.eps);
 }
 
-__global__ void __launch_bounds__(256) adam_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ m,
-                                                   float *__restrict__ v, long long n, bool vec, AdamArgs a) {
+template <class Args>
+__device__ __forceinline__ void adam_range(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ m,
+                                           float *__restrict__ v, long long n, bool vec, const Args &a) {
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
-    if (vec) {
+    if (vec) {                 // 128-bit accesses: 28 bytes per parameter move as 7 vector transactions per 4 parameters
         long long n4 = n >> 2;
         float4 *w4 = reinterpret_cast<float4 *>(w), *m4 = reinterpret_cast<float4 *>(m), *v4 = reinterpret_cast<float4 *>(v);
         const float4 *g4 = reinterpret_cast<const float4 *>(g);
@@ -281,22 +296,8 @@ __global__ void __launch_bounds__(256) adam_kernel(float *__restrict__ w, const 
         for (long long i = tid; i < n; i += nthr) adam_one(w[i], g[i], m[i], v[i], a);
     }
 }
-
-__global__ void __launch_bounds__(256) adam_dev_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ m,
-                                                       float *__restrict__ v, long long n, const float *__restrict__ h) {
-    AdamArgs a{h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8]};
-    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
-    for (long long i = tid; i < n; i += nthr) adam_one(w[i], g[i], m[i], v[i], a);
-}
-__global__ void __launch_bounds__(256) sgd_dev_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ vel,
-                                                      long long n, const float *__restrict__ h) {
-    float lr = h[0], mu = h[1], gs = h[2];
-    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
-    for (long long i = tid; i < n; i += nthr) { vel[i] = mu * vel[i] + lr * (g[i] * gs); w[i] -= vel[i]; }
-}
-
-__global__ void __launch_bounds__(256) sgd_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ vel,
-                                                  long long n, bool vec, float lr, float mu, float gs) {
+__device__ __forceinline__ void sgd_range(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ vel, long long n,
+                                          bool vec, float lr, float mu, float gs) {
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
     if (vec) {
         long long n4 = n >> 2;
@@ -315,6 +316,26 @@ __global__ void __launch_bounds__(256) sgd_kernel(float *__restrict__ w, const f
     }
 }
 
+__global__ void __launch_bounds__(256) adam_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ m,
+                                                   float *__restrict__ v, long long n, bool vec, AdamArgs a) {
+    adam_range(w, g, m, v, n, vec, a);
+}
+// The same update with its scalars read from device memory, so that a captured step graph can be replayed with a new
+// step count (the host refreshes the nine floats before each replay).
+__global__ void __launch_bounds__(256) adam_dev_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ m,
+                                                       float *__restrict__ v, long long n, bool vec, const float *__restrict__ h) {
+    AdamArgs a{h[0], h[1], h[2], h[3], h[4], h[5], h[6], h[7], h[8]};
+    adam_range(w, g, m, v, n, vec, a);
+}
+__global__ void __launch_bounds__(256) sgd_dev_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ vel,
+                                                      long long n, bool vec, const float *__restrict__ h) {
+    sgd_range(w, g, vel, n, vec, h[0], h[1], h[2]);
+}
+__global__ void __launch_bounds__(256) sgd_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ vel,
+                                                  long long n, bool vec, float lr, float mu, float gs) {
+    sgd_range(w, g, vel, n, vec, lr, mu, gs);
+}
+
 }  // namespace seera
 
 using namespace seera;
@@ -330,6 +351,7 @@ int seera_bias_act_fwd(const float *z, const float *bias, float *y, int size, in
         if (inner % 4 == 0) mode = 1;
         else if (inner == 1 && channels % 4 == 0 && (!bias || aligned16(bias))) mode = 2;
     }
+    ProfBytes pb(8.0 * size, "bias_act_fwd");
     bias_act_kernel<<<stride_grid(mode ? size / 4 : size), 256, 0, rt().stream>>>(z, bias, y, size, channels, inner, act, mode);
     SEERA_LAUNCH_CHECK("bias_act_fwd");
     return SEERA_OK;
@@ -355,6 +377,8 @@ static int act_bias_splits(int outer, int channels, int inner) {
 // (splits * channels floats of scratch owned by the caller of this helper).
 static int act_bias_bwd_launch(const float *dy, const float *y, float *dz, float *dbias, float *partial, int outer, int channels,
                                int inner, int act, int splits) {
+    // dy and (with an activation) y read, dz written unless it is dy itself
+    ProfBytes pb(4.0 * outer * channels * inner * (1 + (act ? 1 : 0) + (dz != dy ? 1 : 0)), "act_bias_bwd");
     if (inner == 1) {
         int colblocks = (channels + 31) / 32;
         act_bias_bwd_rows_kernel<<<dim3(colblocks, splits), 256, 0, rt().stream>>>(dy, y, dz, partial, outer, channels, act);
@@ -372,8 +396,9 @@ static int act_bias_bwd_launch(const float *dy, const float *y, float *dz, float
 }
 
 static int act_bias_bwd_check(const float *dy, const float *y, float *dz, int size, int channels, int inner, int act, const char *name) {
+    const long long per_outer = (long long)channels * inner;      // in 64 bits: channels * inner may not fit an int
     if (size < 0 || channels < 1 || inner < 1 || (size > 0 && (!dy || !dz)) || (act != SEERA_ACT_NONE && !y) ||
-        size % (channels * inner) != 0)
+        per_outer > 0x7fffffffLL || (long long)size % per_outer != 0)
         return fail(SEERA_E_ARG, "%s: bad argument", name);
     return SEERA_OK;
 }
@@ -422,7 +447,7 @@ int seera_act_bias_bwd_noalloc(const float *dy, const float *y, float *dz, float
     if (channels > SEERA_STATIC_PARTIALS)
         return fail(SEERA_E_LIMIT, "act_bias_bwd_noalloc: %d channels exceed the fixed scratch of %d partial sums", channels, SEERA_STATIC_PARTIALS);
     int splits = act_bias_splits(outer, channels, inner);
-    if ((long long)splits * channels > SEERA_STATIC_PARTIALS) splits = SEERA_STATIC_PARTIALS / channels;   // fewer, longer partial sums
+    if ((long long)splits * channels > SEERA_STATIC_PARTIALS) splits = SEERA_STATIC_PARTIALS / channels;   // (not reached with 148 SMs)
     int st = SEERA_OK;
     float *partial = dbias ? static_partials_for_current_device(&st) : nullptr;
     if (dbias && !partial) return st;
@@ -463,6 +488,7 @@ int seera_softmax_cce_fwd_bwd(const float *z, const float *onehot, float *p, flo
     SEERA_ENSURE();
     if (N < 1 || C < 1 || !z || !onehot || !p || !loss_rows || !loss_mean || !dz)
         return fail(SEERA_E_ARG, "softmax_cce_fwd_bwd: bad argument");
+    ProfBytes pb(16.0 * N * C, "softmax_cce");
     softmax_cce_kernel<<<stride_grid((long long)N * 32), 256, 0, rt().stream>>>(z, onehot, p, loss_rows, dz, N, C, eps, inv_count);
     SEERA_LAUNCH_CHECK("softmax_cce");
     scaled_sum_kernel<<<1, 256, 0, rt().stream>>>(loss_rows, loss_mean, N, inv_count);
@@ -475,15 +501,30 @@ int seera_mse_partials(int size) {
     return g;
 }
 
-int seera_mse_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp, int size, float inv_count) {
+static int elem_loss(int kind, const float *p, const float *y, float *partials, float *loss_mean, float *dp, int size,
+                     float inv_count, float eps, const char *name) {
     SEERA_ENSURE();
-    if (size < 1 || !p || !y || !partials || !loss_mean || !dp) return fail(SEERA_E_ARG, "mse_fwd_bwd: bad argument");
+    if (size < 1 || !p || !y || !partials || !loss_mean || !dp) return fail(SEERA_E_ARG, "%s: bad argument", name);
     int g = stride_grid(size);
-    mse_kernel<<<g, 256, 0, rt().stream>>>(p, y, partials, dp, size, inv_count);
-    SEERA_LAUNCH_CHECK("mse");
-    scaled_sum_kernel<<<1, 256, 0, rt().stream>>>(partials, loss_mean, g, inv_count);
-    SEERA_LAUNCH_CHECK("mse(sum)");
+    cudaStream_t st = rt().stream;
+    ProfBytes pb(12.0 * size, name);
+    if (kind == 0) elem_loss_kernel<0><<<g, 256, 0, st>>>(p, y, partials, dp, size, inv_count, eps);
+    else if (kind == 1) elem_loss_kernel<1><<<g, 256, 0, st>>>(p, y, partials, dp, size, inv_count, eps);
+    else elem_loss_kernel<2><<<g, 256, 0, st>>>(p, y, partials, dp, size, inv_count, eps);
+    SEERA_LAUNCH_CHECK(name);
+    scaled_sum_kernel<<<1, 256, 0, st>>>(partials, loss_mean, g, inv_count);
+    SEERA_LAUNCH_CHECK(name);
     return SEERA_OK;
+}
+int seera_mse_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp, int size, float inv_count) {
+    return elem_loss(0, p, y, partials, loss_mean, dp, size, inv_count, 0.f, "mse_fwd_bwd");
+}
+int seera_mae_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp, int size, float inv_count) {
+    return elem_loss(1, p, y, partials, loss_mean, dp, size, inv_count, 0.f, "mae_fwd_bwd");
+}
+int seera_bce_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp, int size, float inv_count,
+                      float eps) {
+    return elem_loss(2, p, y, partials, loss_mean, dp, size, inv_count, eps, "bce_fwd_bwd");
 }
 
 int seera_adam_step(float *w, const float *g, float *m, float *v, int n, float lr, float beta1, float omb1,
@@ -493,6 +534,7 @@ int seera_adam_step(float *w, const float *g, float *m, float *v, int n, float l
     if (n == 0) return SEERA_OK;
     bool vec = aligned16(w) && aligned16(g) && aligned16(m) && aligned16(v);
     AdamArgs a{lr, beta1, omb1, beta2, omb2, eps, c1, c2, grad_scale};
+    ProfBytes pb(28.0 * n, "adam");
     adam_kernel<<<stride_grid(vec ? (n + 3) / 4 : n), 256, 0, rt().stream>>>(w, g, m, v, n, vec, a);
     SEERA_LAUNCH_CHECK("adam_step");
     return SEERA_OK;
@@ -502,7 +544,9 @@ int seera_adam_step_dev(float *w, const float *g, float *m, float *v, int n, con
     SEERA_ENSURE();
     if (n < 0 || (n > 0 && (!w || !g || !m || !v || !hyper))) return fail(SEERA_E_ARG, "adam_step_dev: bad argument");
     if (n == 0) return SEERA_OK;
-    adam_dev_kernel<<<stride_grid(n), 256, 0, rt().stream>>>(w, g, m, v, n, hyper);
+    bool vec = aligned16(w) && aligned16(g) && aligned16(m) && aligned16(v);
+    ProfBytes pb(28.0 * n, "adam");
+    adam_dev_kernel<<<stride_grid(vec ? (n + 3) / 4 : n), 256, 0, rt().stream>>>(w, g, m, v, n, vec, hyper);
     SEERA_LAUNCH_CHECK("adam_step_dev");
     return SEERA_OK;
 }
@@ -510,7 +554,9 @@ int seera_sgd_step_dev(float *w, const float *g, float *vel, int n, const float 
     SEERA_ENSURE();
     if (n < 0 || (n > 0 && (!w || !g || !vel || !hyper))) return fail(SEERA_E_ARG, "sgd_step_dev: bad argument");
     if (n == 0) return SEERA_OK;
-    sgd_dev_kernel<<<stride_grid(n), 256, 0, rt().stream>>>(w, g, vel, n, hyper);
+    bool vec = aligned16(w) && aligned16(g) && aligned16(vel);
+    ProfBytes pb(20.0 * n, "sgd");
+    sgd_dev_kernel<<<stride_grid(vec ? (n + 3) / 4 : n), 256, 0, rt().stream>>>(w, g, vel, n, vec, hyper);
     SEERA_LAUNCH_CHECK("sgd_step_dev");
     return SEERA_OK;
 }
@@ -520,6 +566,7 @@ int seera_sgd_step(float *w, const float *g, float *vel, int n, float lr, float 
     if (n < 0 || (n > 0 && (!w || !g || !vel))) return fail(SEERA_E_ARG, "sgd_step: bad argument");
     if (n == 0) return SEERA_OK;
     bool vec = aligned16(w) && aligned16(g) && aligned16(vel);
+    ProfBytes pb(20.0 * n, "sgd");
     sgd_kernel<<<stride_grid(vec ? (n + 3) / 4 : n), 256, 0, rt().stream>>>(w, g, vel, n, vec, lr, momentum, grad_scale);
     SEERA_LAUNCH_CHECK("sgd_step");
     return SEERA_OK;

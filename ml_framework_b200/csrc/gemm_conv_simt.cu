@@ -165,7 +165,7 @@ int run_contraction(const AL &al, const BL &bl, const CS &cs, int M, int N, int 
         e = cudaGetLastError();
     }
     if (partial) scratch_free(partial);
-    profile_end(2.0 * M * N * (double)K);
+    profile_end(2.0 * M * N * (double)K, name);
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }
 

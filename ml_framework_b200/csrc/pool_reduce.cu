@@ -325,6 +325,7 @@ int seera_cuda_maxpool_fwd(const float *X, float *out, int *mask, int N, int C, 
     if ((long long)OH * OW > (long long)H * W)
         return fail(SEERA_E_ARG, "cuda_maxpool_fwd: %dx%d outputs do not fit the caller's %dx%d mask buffer", OH, OW, H, W);
     long long total = (long long)N * C * OH * OW;
+    ProfBytes pb(4.0 * N * C * H * W + 8.0 * total, "maxpool_fwd");
     if (R == 2 && S == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && H % 2 == 0 && W % 4 == 0 &&
         aligned16(X) && aligned16(out) && aligned16(mask)) {
         long long pairs = total / 2;
@@ -344,6 +345,7 @@ int seera_cuda_maxpool_bwd(const float *dout, const int *mask, float *dX, int N,
         return fail(SEERA_E_ARG, "cuda_maxpool_bwd: bad argument");
     int OH = (H + 2 * ph - R) / sh + 1, OW = (W + 2 * pw - S) / sw + 1;
     if (OH < 1 || OW < 1) return fail(SEERA_E_ARG, "cuda_maxpool_bwd: window larger than padded input");
+    ProfBytes pb(4.0 * N * C * H * W + 8.0 * N * C * OH * OW, "maxpool_bwd");
     if (R == 2 && S == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && H % 2 == 0 && W % 4 == 0 &&
         aligned16(dX) && aligned16(dout) && aligned16(mask)) {
         long long pairs = (long long)N * C * OH * OW / 2;
@@ -361,6 +363,7 @@ int seera_cuda_unpooling_fwd(const float *inp, float *out, int N, int C, int H, 
     SEERA_ENSURE();
     if (N < 1 || C < 1 || H < 1 || W < 1 || sh < 1 || sw < 1 || !inp || !out) return fail(SEERA_E_ARG, "cuda_unpooling_fwd: bad argument");
     long long total = (long long)N * C * H * sh * W * sw;
+    ProfBytes pb(4.0 * N * C * H * W + 4.0 * total, "unpool_fwd");
     if (total < (1LL << 31)) {
         const bool v4 = (W * sw) % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
         unsigned items = (unsigned)(v4 ? total / 4 : total);
@@ -376,6 +379,7 @@ int seera_cuda_unpooling_bwd(const float *dout, float *dx, int N, int C, int H, 
     SEERA_ENSURE();
     if (N < 1 || C < 1 || H < 1 || W < 1 || sh < 1 || sw < 1 || !dout || !dx) return fail(SEERA_E_ARG, "cuda_unpooling_bwd: bad argument");
     long long total = (long long)N * C * H * W;
+    ProfBytes pb(4.0 * total + 4.0 * total * sh * sw, "unpool_bwd");
     if (total * sh * sw < (1LL << 31)) unpool_bwd32_kernel<<<stride_grid(total), 256, 0, rt().stream>>>(dout, dx, (unsigned)total, H, W, sh, sw);
     else unpool_bwd_kernel<<<stride_grid(total), 256, 0, rt().stream>>>(dout, dx, total, H, W, sh, sw);
     SEERA_LAUNCH_CHECK("cuda_unpooling_bwd");

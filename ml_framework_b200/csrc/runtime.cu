@@ -9,6 +9,7 @@
 #include "common.cuh"
 #include <cstdarg>
 #include <cstring>
+#include <string>
 #include <map>
 #include <unordered_map>
 #include <vector>
@@ -63,8 +64,13 @@ size_t round_size(size_t n) {
 }
 }  // namespace
 
-struct ProfRec { cudaEvent_t a, b; double flops; };
-struct Prof { bool on = false; std::vector<ProfRec> recs; cudaEvent_t pending = nullptr; };
+// Per-launch profile (seera_profile_enable): launches bracketed by profile_begin / profile_end[_bytes] are timed with
+// events on the engine's stream and booked under a tag.  Contractions book FLOPs and a kind (0 forward, 1 data gradient,
+// 2 weight gradient, from the entry name's "(dX)" / "(dW)" suffix); bandwidth-bound passes book their algorithmic bytes
+// (kind 3).  Nothing is recorded while a graph is being captured.
+struct ProfRec { cudaEvent_t a, b; double work; int kind; const char *tag; };
+struct ProfAgg { int kind = 0; uint64_t n = 0; double ms = 0, work = 0; };
+struct Prof { bool on = false; std::vector<ProfRec> recs; cudaEvent_t pending = nullptr; std::map<std::string, ProfAgg> table; };
 static Prof &prof() { static Prof p; return p; }
 
 void profile_begin() {
@@ -73,14 +79,39 @@ void profile_begin() {
     cudaEventCreate(&p.pending);
     cudaEventRecord(p.pending, rt().stream);
 }
-void profile_end(double flops) {
+static int profile_kind(const char *name) {
+    if (!name) return 0;
+    size_t n = strlen(name);
+    if (n >= 4 && name[n - 1] == ')' && name[n - 4] == '(' && name[n - 3] == 'd') {
+        char c = name[n - 2];
+        return (c == 'X' || c == 'A') ? 1 : ((c == 'W' || c == 'B') ? 2 : 0);
+    }
+    return strcmp(name, "conv2d_act_bwd") == 0 ? 2 : 0;       // the short-patch layer backward forms only the weight gradient
+}
+static void profile_close(double work, int kind, const char *tag) {
     Prof &p = prof();
     if (!p.on || !p.pending) return;
-    ProfRec r{p.pending, nullptr, flops};
+    ProfRec r{p.pending, nullptr, work, kind, tag ? tag : "?"};
     cudaEventCreate(&r.b);
     cudaEventRecord(r.b, rt().stream);
     p.recs.push_back(r);
     p.pending = nullptr;
+}
+void profile_end(double flops, const char *name) { profile_close(flops, profile_kind(name), name); }
+void profile_end_bytes(double bytes, const char *tag) { profile_close(bytes, 3, tag); }
+
+// Resolves the recorded events into the per-tag table (waits for them).
+static void profile_collect() {
+    Prof &p = prof();
+    for (auto &r : p.recs) {
+        float e = 0.f;
+        cudaEventSynchronize(r.b);
+        cudaEventElapsedTime(&e, r.a, r.b);
+        ProfAgg &g = p.table[std::string(r.tag)];
+        g.kind = r.kind; g.n++; g.ms += e; g.work += r.work;
+        cudaEventDestroy(r.a); cudaEventDestroy(r.b);
+    }
+    p.recs.clear();
 }
 
 void *scratch_alloc(size_t bytes) { return seera_cuda_malloc(bytes); }
@@ -95,6 +126,10 @@ extern "C" {
 int seera_init(int device) {
     Runtime &r = rt();
     if (r.device == device && r.stream) return SEERA_OK;
+    // one device per process: the stream, the memory pool, the tensor-core status word and the profiler events all belong to
+    // the device of the first call
+    if (r.device >= 0 && r.device != device)
+        return fail(SEERA_E_ARG, "seera_init: this process already runs on device %d (one device per process; asked for %d)", r.device, device);
     int n = 0;
     cudaError_t e = cudaGetDeviceCount(&n);
     if (e != cudaSuccess || n == 0)
@@ -149,24 +184,50 @@ float seera_event_elapsed_ms(void *a, void *b) {
 int seera_event_destroy(void *ev) { return ev ? check_cuda(cudaEventDestroy((cudaEvent_t)ev), "cudaEventDestroy") : SEERA_OK; }
 
 int seera_profile_enable(int on) {
-    seera::prof().on = on != 0;
+    auto &p = seera::prof();
+    if (on && !p.on) { seera::profile_collect(); p.table.clear(); }      // a new session starts from an empty table
+    p.on = on != 0;
+    return SEERA_OK;
+}
+int seera_profile_read_kinds(uint64_t *launches3, double *ms3, double *flops3) {
+    SEERA_ENSURE();
+    seera::profile_collect();
+    uint64_t n[3] = {0, 0, 0};
+    double t[3] = {0, 0, 0}, f[3] = {0, 0, 0};
+    for (auto &kv : seera::prof().table) {
+        const auto &g = kv.second;
+        if (g.kind > 2) continue;
+        n[g.kind] += g.n; t[g.kind] += g.ms; f[g.kind] += g.work;
+    }
+    for (int k = 0; k < 3; k++) {
+        if (launches3) launches3[k] = n[k];
+        if (ms3) ms3[k] = t[k];
+        if (flops3) flops3[k] = f[k];
+    }
     return SEERA_OK;
 }
 int seera_profile_read(uint64_t *launches, double *ms, double *flops) {
+    uint64_t n[3];
+    double t[3], f[3];
+    if (int s = seera_profile_read_kinds(n, t, f)) return s;
+    if (launches) *launches = n[0] + n[1] + n[2];
+    if (ms) *ms = t[0] + t[1] + t[2];
+    if (flops) *flops = f[0] + f[1] + f[2];
+    seera::prof().table.clear();
+    return SEERA_OK;
+}
+int seera_profile_report(char *buf, size_t size) {
     SEERA_ENSURE();
-    auto &p = seera::prof();
-    double t = 0, f = 0;
-    for (auto &r : p.recs) {
-        float e = 0.f;
-        cudaEventSynchronize(r.b);
-        cudaEventElapsedTime(&e, r.a, r.b);
-        t += e; f += r.flops;
-        cudaEventDestroy(r.a); cudaEventDestroy(r.b);
+    if (!buf || size < 2) return fail(SEERA_E_ARG, "profile_report: no buffer");
+    seera::profile_collect();
+    size_t off = 0;
+    buf[0] = 0;
+    for (auto &kv : seera::prof().table) {
+        const auto &g = kv.second;
+        int w = snprintf(buf + off, size - off, "%s\t%d\t%llu\t%.6f\t%.6e\n", kv.first.c_str(), g.kind, (unsigned long long)g.n, g.ms, g.work);
+        if (w < 0 || (size_t)w >= size - off) { buf[off] = 0; return fail(SEERA_E_LIMIT, "profile_report: buffer of %zu bytes is too small", size); }
+        off += (size_t)w;
     }
-    if (launches) *launches = p.recs.size();
-    if (ms) *ms = t;
-    if (flops) *flops = f;
-    p.recs.clear();
     return SEERA_OK;
 }
 

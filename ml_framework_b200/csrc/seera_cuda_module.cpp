@@ -149,6 +149,29 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("event_elapsed_ms", [](uptr a, uptr b) { return seera_event_elapsed_ms(P<void>(a), P<void>(b)); });
     m.def("event_destroy", [](uptr e) { ck(seera_event_destroy(P<void>(e))); });
     m.def("profile_enable", [](int on) { ck(seera_profile_enable(on)); });
+    m.def("profile_read_kinds", []() {
+        uint64_t n[3]; double ms[3], fl[3];
+        ck(seera_profile_read_kinds(n, ms, fl));
+        py::list out;
+        for (int k = 0; k < 3; k++) out.append(py::make_tuple(n[k], ms[k], fl[k]));
+        return out; });
+    m.def("profile_report", []() {
+        std::string buf(1 << 16, '\0');
+        ck(seera_profile_report(&buf[0], buf.size()));
+        py::list rows;
+        size_t pos = 0, end = buf.find('\0');
+        std::string text = buf.substr(0, end);
+        while (pos < text.size()) {
+            size_t nl = text.find('\n', pos);
+            if (nl == std::string::npos) break;
+            std::string line = text.substr(pos, nl - pos);
+            pos = nl + 1;
+            size_t t1 = line.find('\t'), t2 = line.find('\t', t1 + 1), t3 = line.find('\t', t2 + 1), t4 = line.find('\t', t3 + 1);
+            rows.append(py::make_tuple(line.substr(0, t1), std::stoi(line.substr(t1 + 1, t2 - t1 - 1)),
+                                       std::stoull(line.substr(t2 + 1, t3 - t2 - 1)), std::stod(line.substr(t3 + 1, t4 - t3 - 1)),
+                                       std::stod(line.substr(t4 + 1))));
+        }
+        return rows; });
     m.def("profile_read", []() { uint64_t n = 0; double ms = 0, fl = 0; ck(seera_profile_read(&n, &ms, &fl)); return py::make_tuple(n, ms, fl); });
     m.def("set_precision", [](int mode) { ck(seera_set_precision(mode)); });
     m.def("graph_begin", []() { ck(seera_graph_begin()); });
@@ -230,9 +253,35 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("mse_partials", [](int n) { return seera_mse_partials(n); });
     m.def("mse_fwd_bwd", [](uptr p, uptr y, uptr part, uptr loss, uptr dp, int n, float inv) {
         ck(seera_mse_fwd_bwd(P<const F>(p), P<const F>(y), P<F>(part), P<F>(loss), P<F>(dp), n, inv)); });
+    m.def("mae_fwd_bwd", [](uptr p, uptr y, uptr part, uptr loss, uptr dp, int n, float inv) {
+        ck(seera_mae_fwd_bwd(P<const F>(p), P<const F>(y), P<F>(part), P<F>(loss), P<F>(dp), n, inv)); });
+    m.def("bce_fwd_bwd", [](uptr p, uptr y, uptr part, uptr loss, uptr dp, int n, float inv, float eps) {
+        ck(seera_bce_fwd_bwd(P<const F>(p), P<const F>(y), P<F>(part), P<F>(loss), P<F>(dp), n, inv, eps)); });
     m.def("cuda_adam_step", [](uptr w, uptr g, uptr mm, uptr v, int n, float lr, float b1, float omb1, float b2, float omb2,
                                float eps, float c1, float c2, float gs) {
         ck(seera_adam_step(P<F>(w), P<const F>(g), P<F>(mm), P<F>(v), n, lr, b1, omb1, b2, omb2, eps, c1, c2, gs)); });
     m.def("cuda_sgd_step", [](uptr w, uptr g, uptr vel, int n, float lr, float mu, float gs) {
         ck(seera_sgd_step(P<F>(w), P<const F>(g), P<F>(vel), n, lr, mu, gs)); });
+
+    // ---- data parallel (NCCL inside the engine) ----
+    m.def("dp_unique_id", []() {
+        std::string id((size_t)seera_dp_unique_id_bytes(), '\0');
+        ck(seera_dp_unique_id(&id[0], (int)id.size()));
+        return py::bytes(id); });
+    m.def("dp_init", [](int rank, int world, py::bytes id) {
+        std::string s = id;
+        py::gil_scoped_release nogil;           // collective over the ranks: may wait for the others
+        ck(seera_dp_init(rank, world, s.data(), (int)s.size())); });
+    m.def("dp_rank", []() { return seera_dp_rank(); });
+    m.def("dp_world", []() { return seera_dp_world(); });
+    m.def("dp_nccl_version", []() { return seera_dp_nccl_version(); });
+    m.def("dp_alloc", [](size_t bytes) { return ckp(seera_dp_alloc(bytes)); });
+    m.def("dp_free", [](uptr p) { ck(seera_dp_free(P<void>(p))); });
+    m.def("dp_allreduce", [](uptr p, long long n, int op) { ck(seera_dp_allreduce(P<F>(p), n, op)); });
+    m.def("dp_broadcast", [](uptr p, long long n, int root) { ck(seera_dp_broadcast(P<F>(p), n, root)); });
+    m.def("dp_reduce_range", [](uptr p, long long b, long long e) { ck(seera_dp_reduce_range(P<F>(p), b, e)); });
+    m.def("dp_join", []() { ck(seera_dp_join()); });
+    m.def("dp_poll", []() { ck(seera_dp_poll()); });
+    m.def("dp_wait_host", [](int timeout_ms) { py::gil_scoped_release nogil; ck(seera_dp_wait_host(timeout_ms)); });
+    m.def("dp_finalize", []() { ck(seera_dp_finalize()); });
 }

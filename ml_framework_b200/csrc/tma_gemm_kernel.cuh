@@ -98,6 +98,7 @@ inline int make_shadow(const float *src, int rows, int cols, int ns, Shadow &s) 
     long long groups = (long long)rows * (s.ld / 8);
     int grid = stride_grid(groups);
     cudaStream_t st = rt().stream;
+    ProfBytes pb(4.0 * rows * cols + 2.0 * ns * rows * s.ld, "shadow_rows");
     if (ns == 1) shadow_rows_kernel<1><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
     else if (ns == 2) shadow_rows_kernel<2><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
     else shadow_rows_kernel<3><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
@@ -477,7 +478,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
         e = cudaGetLastError();
     }
     if (p.partial) scratch_free(p.partial);
-    profile_end(flops);
+    profile_end(flops, name);
     rt().tc_used = true;
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, name);
 }

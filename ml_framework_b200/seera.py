@@ -1033,9 +1033,8 @@ class Sequential:
 # Losses
 # ─────────────────────────────────────────────────────────────────────────────────────────────
 class Loss:
-    """inv_scale: set by a data-parallel driver so that each rank's loss is divided by the GLOBAL
-    batch (the ranks' gradient sum is then the gradient of the global mean)."""
-    world = 1
+    """Each loss is the mean over the batch THIS process holds.  In a data-parallel run the ranks' gradients are averaged
+    by the optimizer (dp.attach sets the 1/world factor there), so no scale is applied here."""
 
     def categorical_cross_entropy(self, y_pred, y, epsilon=1e-7):
         """mean over the batch of -sum(y * log(clip(y_pred, eps, 1-eps)))  (Seera.py:955-969)."""
@@ -1048,32 +1047,37 @@ class Loss:
             raise ValueError(f"[cuTen]: Shapes {tuple(yv.shape)} and {(N, C)} not broadcastable")
         rows, loss, dz = _new((N,)), _new((1,)), _new((N, C))
         sc.softmax_cce_fwd_bwd(z.main_ptr, yv.main_ptr, y_pred.value.main_ptr, rows.main_ptr, loss.main_ptr, dz.main_ptr,
-                               N, C, float(epsilon), float(f32(1.0 / (N * Loss.world))))
+                               N, C, float(epsilon), float(f32(1.0 / N)))
         out = Tensor(loss)
         out._parents = (logits,)
         out._keep = (rows, yv)
         out._backward = lambda g: logits._accumulate(dz)       # g is the all-ones seed of a scalar loss
         return out
 
-    def mse(self, y_pred, y):
-        """mean((y_pred - y)^2) over all elements (Seera.py:943-945)."""
+    def _elementwise(self, kernel, y_pred, y, *extra):
         p, yv = y_pred.value, y.value
         if p.size != yv.size:
             raise ValueError(f"[cuTen]: Shapes {tuple(p.shape)} and {tuple(yv.shape)} not broadcastable")
         part, loss, dp = _new((sc.mse_partials(p.size),)), _new((1,)), _new(p.shape)
-        sc.mse_fwd_bwd(p.main_ptr, yv.main_ptr, part.main_ptr, loss.main_ptr, dp.main_ptr, p.size,
-                       float(f32(1.0 / (p.size * Loss.world))))
+        kernel(p.main_ptr, yv.main_ptr, part.main_ptr, loss.main_ptr, dp.main_ptr, p.size,
+               float(f32(1.0 / p.size)), *extra)
         out = Tensor(loss)
         out._parents = (y_pred,)
         out._keep = (part, yv)
         out._backward = lambda g: y_pred._accumulate(dp)
         return out
 
+    def mse(self, y_pred, y):
+        """mean((y_pred - y)^2) over all elements (Seera.py:943-945)."""
+        return self._elementwise(sc.mse_fwd_bwd, y_pred, y)
+
     def mae(self, y_pred, y):
-        raise NotImplementedError("mae is outside the accelerated training path")
+        """mean(|y_pred - y|) over all elements (Seera.py:947-949)."""
+        return self._elementwise(sc.mae_fwd_bwd, y_pred, y)
 
     def binary_cross_entropy(self, y_pred, y, epsilon=1e-15):
-        raise NotImplementedError("binary_cross_entropy is outside the accelerated training path")
+        """mean(-y log(p + eps) - (1 - y) log(1 - p + eps)) over all elements (Seera.py:951-953)."""
+        return self._elementwise(sc.bce_fwd_bwd, y_pred, y, float(epsilon))
 
 
 # ─────────────────────────────────────────────────────────────────────────────────────────────

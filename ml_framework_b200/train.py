@@ -11,6 +11,16 @@ from . import seera_cuda as sc
 from .cuTen import cuten
 
 
+# Precision policy (forward mode, backward mode) per kind of configuration: what the benchmark times and what the
+# parity gates are checked at.  fp32 configurations run split products on the tensor cores; the bf16 configuration
+# a single bf16 pass.
+POLICY = {"fp32": (3, 2), "bf16": (1, 1)}
+
+
+def policy_for(work):
+    return POLICY[work.precision]
+
+
 def build_model(work, params=None):
     layers = [S.Input(tuple(work.in_shape))]
     for L in work.layers:

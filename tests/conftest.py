@@ -3,6 +3,10 @@ import sys
 
 import pytest
 
+# The reference's CPU engine calls a pthread OpenBLAS inside OpenMP loops (engine/src/conv_ops.cpp:109-175): one BLAS thread
+# per OpenMP thread keeps its summation order fixed and stops the two thread pools from fighting over the cores.
+os.environ.setdefault("OPENBLAS_NUM_THREADS", "1")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 for p in (ROOT, os.path.join(ROOT, "tests", "golden")):
     if p not in sys.path:

@@ -2,7 +2,7 @@
 
 Function names and argument orders are those of the reference's CPU engine binding
 (engine/src/bindings.cpp:14-248: matmul, relu, ..., conv2d_forward, conv2d_backward,
-maxpool2d_forward, ...), so a script written against `seera_cpp` runs against this module
+maxpool2d_forward, ...), so the parity tests read like calls into `seera_cpp`
 with host arrays: each call uploads its operands, enqueues the device kernels of
 include/seera_b200.h, and downloads the result.  Meant for checks and small experiments;
 training keeps tensors resident (see ml_framework_b200.seera).
@@ -11,7 +11,7 @@ import ctypes
 
 import numpy as np
 
-from . import capi
+from ml_framework_b200 import capi
 
 
 class _Dev:

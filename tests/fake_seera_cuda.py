@@ -443,6 +443,21 @@ def mse_fwd_bwd(p, y, part, loss, dp, n, inv):
     _view(dp, n)[:] = 2 * d * np.float32(inv)
 
 
+def mae_fwd_bwd(p, y, part, loss, dp, n, inv):
+    _count("mae")
+    d = _view(p, n) - _view(y, n)
+    _view(loss, 1)[:] = np.abs(d).sum() * np.float32(inv)
+    _view(dp, n)[:] = np.sign(d) * np.float32(inv)
+
+
+def bce_fwd_bwd(p, y, part, loss, dp, n, inv, eps):
+    _count("bce")
+    P, Y, e = _view(p, n), _view(y, n), np.float32(eps)
+    a, b = P + e, (np.float32(1) - P) + e
+    _view(loss, 1)[:] = (-Y * np.log(a) - (1 - Y) * np.log(b)).sum() * np.float32(inv)
+    _view(dp, n)[:] = (-Y / a + (1 - Y) / b) * np.float32(inv)
+
+
 def cuda_adam_step(w, g, m, v, n, lr, b1, omb1, b2, omb2, eps, c1, c2, gs):
     _count("adam")
     f = np.float32

@@ -1,4 +1,4 @@
-"""GPU parity, op by op, through the C ABI (ml_framework_b200.engine_np -> ctypes -> libseera_b200.so)
+"""GPU parity, op by op, through the C ABI (tests/engine_np.py -> ctypes -> libseera_b200.so)
 against the CPU oracle and the golden vectors of the unmodified reference engine.
 Integer results (max-pool masks, argmax/argmin) and pure data movement must be bit-exact; floating
 point contractions must agree to rel-L2 <= 2e-5 in fp32 mode (summation order only)."""
@@ -19,7 +19,8 @@ FP32_TOL = 2e-5
 
 @pytest.fixture(scope="module")
 def E():
-    from ml_framework_b200 import engine_np, capi
+    from ml_framework_b200 import capi
+    import engine_np
     L = capi.load()
     capi.check(L.seera_init(capi.default_device()))
     capi.check(L.seera_set_precision(0))
@@ -188,7 +189,7 @@ def test_argmax_ties_take_first_index(E):
 def _dev_call(fn_name, arrays, scalars, outs):
     """Runs a raw C-ABI entry on uploaded arrays; `outs` lists (index, shape, dtype) to download."""
     from ml_framework_b200 import capi
-    from ml_framework_b200.engine_np import _Dev
+    from engine_np import _Dev
     with _Dev() as d:
         ptrs = [None if a is None else d.up(a, a.dtype) for a in arrays]
         capi.check(getattr(d.L, fn_name)(*ptrs, *scalars))
@@ -276,7 +277,7 @@ def test_fused_optimizers_match_the_oracle(E, n):
 def test_elementwise_on_unaligned_addresses(E):
     """Callers do byte arithmetic on device addresses (concatenate); kernels must accept 4-byte alignment."""
     from ml_framework_b200 import capi
-    from ml_framework_b200.engine_np import _Dev
+    from engine_np import _Dev
     a = np.arange(1001, dtype=np.float32)
     with _Dev() as d:
         pa, pc = d.up(a), d.new(1001)
@@ -356,3 +357,23 @@ def test_concatenate_forward_and_backward(N, n1, n2):
     assert np.array_equal(down(da, (N, n1)), A) and np.array_equal(down(db, (N, n2)), B)
     for p in (ad, bd, od, da, db):
         L.seera_cuda_free(p)
+
+
+@pytest.mark.parametrize("n", [(7,), (64, 10), (256, 1, 64, 64)])
+def test_mae_and_binary_cross_entropy_losses(E, n):
+    """Loss.mae and Loss.binary_cross_entropy (Seera.py:947-953) with their gradients in one pass, against the formulas
+    evaluated in double precision; |d| has gradient 0 at d = 0 (engine/src/activation_ops.cpp:50-56)."""
+    from ml_framework_b200 import seera as S
+    rs = np.random.RandomState(len(n))
+    p = rs.uniform(0.02, 0.98, n).astype(np.float32)
+    y = (rs.uniform(0, 1, n) > 0.5).astype(np.float32)
+    p.ravel()[0] = y.ravel()[0]                              # one exact zero difference
+    P, Y = p.astype(np.float64), y.astype(np.float64)
+    for name, want, grad in (("mae", np.abs(P - Y).mean(), np.sign(P - Y) / P.size),
+                             ("binary_cross_entropy", (-Y * np.log(P + 1e-15) - (1 - Y) * np.log(1 - P + 1e-15)).mean(),
+                              (-Y / (P + 1e-15) + (1 - Y) / (1 - P + 1e-15)) / P.size)):
+        pt, yt = S.Tensor(p, is_leaf=True), S.Tensor(y, is_leaf=True)
+        loss = getattr(S.Loss(), name)(pt, yt)
+        S.autograd4nn(loss)
+        assert abs(loss.item() - want) < 2e-6 * max(1.0, abs(want)), name
+        assert rel_l2(pt.grad.to_host_f32(), grad) < 1e-6, name

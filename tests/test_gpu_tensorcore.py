@@ -20,7 +20,8 @@ TOL = {1: 1e-5, 2: 2e-5}
 
 @pytest.fixture(scope="module")
 def E():
-    from ml_framework_b200 import engine_np, capi
+    from ml_framework_b200 import capi
+    import engine_np
     L = capi.load()
     capi.check(L.seera_init(capi.default_device()))
     yield engine_np
@@ -67,6 +68,19 @@ def test_conv2d(E, mode, shape):
     dX, dW = E.conv2d_backward(dY, X, Wt, sh, sw, ph, pw)
     rX, rW = co.conv2d_backward(dY, X, Wt, sh, sw, ph, pw)
     assert rel_l2(dX, rX) < TOL[mode] and rel_l2(dW, rW) < TOL[mode]
+
+
+# channels-last bf16 copy of the input = N*H*W*Cp*2 bytes: 64 KiB, 127.5 KiB (just below), 128 KiB (at) and 256 KiB (above)
+# the size under which drivers up to CUDA 13.1 need one bit of the IM2COL descriptor cleared (conv_tma.cu, make_map_im2col)
+@pytest.mark.parametrize("N,C,H,W", [(2, 64, 16, 16), (1, 8, 51, 160), (4, 64, 16, 16), (8, 64, 16, 16)])
+def test_im2col_maps_of_tensors_below_128_kib(E, N, C, H, W):
+    rs = np.random.RandomState(N * C + H)
+    X, Wt = _prep(1, rs.standard_normal((N, C, H, W)).astype(np.float32), rs.standard_normal((64, C, 3, 3)).astype(np.float32))
+    assert rel_l2(E.conv2d_forward(X, Wt, 1, 1, 1, 1), co.conv2d_forward(X, Wt, 1, 1, 1, 1)) < TOL[1]
+    dY, = _prep(1, rs.standard_normal((N, 64, H, W)).astype(np.float32))
+    dX, dW = E.conv2d_backward(dY, X, Wt, 1, 1, 1, 1)
+    rX, rW = co.conv2d_backward(dY, X, Wt, 1, 1, 1, 1)
+    assert rel_l2(dX, rX) < TOL[1] and rel_l2(dW, rW) < TOL[1]
 
 
 CONVT = [(1, 1, 4, 4, 1, 3, 3, 1, 1, 0, 0), (2, 4, 5, 6, 3, 4, 3, 2, 2, 1, 0), (8, 64, 16, 16, 32, 4, 4, 2, 2, 1, 1),

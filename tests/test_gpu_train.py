@@ -304,3 +304,29 @@ def test_batchnorm_model_against_reference_golden(T, golden_dir):
     from test_host_logic_cpu import _bn_model_against_golden
     sc.set_precision(0)
     _bn_model_against_golden(S, golden_dir, 2e-4)
+
+
+def test_fit_history_matches_the_reference_fit_on_the_device(T, golden_dir):
+    """`Sequential.fit` on the device against the loss history of the reference's own `fit` (Seera.py:729-788): same data,
+    initial weights and shuffling seed; golden written by tests/golden/make_golden_fit.py."""
+    from ml_framework_b200 import seera as S
+    import fit_case
+    gold = np.load(golden_dir + "/fit_c1.npz")
+    m = fit_case.build(S, device="cuda")
+    X, Y = fit_case.data()
+    np.random.seed(fit_case.SHUFFLE_SEED)
+    h = m.fit(X, Y, S.Adam(m, lr=fit_case.LR), S.Loss().categorical_cross_entropy, Epochs=fit_case.EPOCHS,
+              batch_size=fit_case.BATCH, Loss_interval=100)
+    assert np.max(np.abs(h - gold["history"])) < 1e-4, (h, gold["history"])
+    assert rel_l2(m.forward(X[:fit_case.BATCH]).to_numpy(), gold["pred"]) < 1e-4
+
+
+def test_checkpoint_written_by_the_reference_loads_and_predicts_on_the_device(T, golden_dir):
+    """A pickle written by the reference's `Sequential.save` (Seera.py:790-860) loads unchanged on the device and predicts
+    what the reference's trained model predicted."""
+    from ml_framework_b200 import seera as S
+    import fit_case
+    gold = np.load(golden_dir + "/fit_c1.npz")
+    m = S.Sequential.load(golden_dir + "/ref_c1_checkpoint.pkl")
+    X, _ = fit_case.data()
+    assert rel_l2(m.predict(X[:fit_case.BATCH]).to_numpy(), gold["pred"]) < 1e-5

@@ -14,7 +14,7 @@ from oracle import cpu_oracle as co
 from oracle.train_oracle import RefNet
 import cases
 
-REFERENCE = "/root/reference"
+REFERENCE = os.environ.get("SEERA_REFERENCE", "/root/reference")
 
 
 @pytest.fixture(scope="module")
@@ -300,6 +300,33 @@ def test_fit_pipeline_matches_the_synchronous_loop(host):
         assert np.array_equal(h, runs[0][0])
         for (w, b), (w0, b0) in zip(ws, runs[0][1]):
             assert np.array_equal(w, w0) and np.array_equal(b, b0)
+
+
+def test_fit_history_matches_the_reference_fit(host, golden_dir):
+    """`Sequential.fit` against the loss history of the reference's own `fit` (Seera.py:729-788) on the same data, initial
+    weights and shuffling seed (tests/golden/make_golden_fit.py)."""
+    import fit_case
+    gold = np.load(golden_dir + "/fit_c1.npz")
+    S = host.seera
+    m = fit_case.build(S, device="cuda")
+    X, Y = fit_case.data()
+    np.random.seed(fit_case.SHUFFLE_SEED)
+    h = m.fit(X, Y, S.Adam(m, lr=fit_case.LR), S.Loss().categorical_cross_entropy, Epochs=fit_case.EPOCHS,
+              batch_size=fit_case.BATCH, Loss_interval=100)
+    assert np.max(np.abs(h - gold["history"])) < 1e-4, (h, gold["history"])
+    assert rel_l2(m.forward(X[:fit_case.BATCH]).to_numpy(), gold["pred"]) < 1e-4
+
+
+def test_checkpoint_written_by_the_reference_loads_and_predicts(host, golden_dir):
+    """A pickle written by the reference's `Sequential.save` (Seera.py:790-860) loads unchanged and predicts what the
+    reference's trained model predicted."""
+    import fit_case
+    gold = np.load(golden_dir + "/fit_c1.npz")
+    S = host.seera
+    m = S.Sequential.load(golden_dir + "/ref_c1_checkpoint.pkl")
+    X, _ = fit_case.data()
+    assert [l.__class__.__name__ for l in m.model] == ["Input", "Conv2D", "MaxPool2D", "Conv2D", "MaxPool2D", "Flatten", "Dense"]
+    assert rel_l2(m.predict(X[:fit_case.BATCH]).to_numpy(), gold["pred"]) < 1e-5
 
 
 @pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="reference checkout not present")
