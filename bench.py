@@ -1,23 +1,36 @@
 #!/usr/bin/env python
 """Benchmark of the Seera training hot path (forward + loss + backward + optimizer) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2|c3|c4|c5] [--impl reference] [--scaling weak|strong]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Prints ONE JSON line (rank 0).  `value` is whole-job training samples/s with the batch already
-resident in HBM; `e2e` is the same through the public Python API with the batch copied from pinned
-host memory every step and the loss read back every step.  `roofline` covers the contraction
-kernels (Dense / convolution forward, dX, dW), timed live with CUDA events in a separate profiled
-pass; `cpu_baseline` is the reference's own CPU engine on this box's host cores on a bounded sample.
+Prints ONE JSON line (rank 0).  `value` is whole-job training samples/s with the batches already resident in HBM
+(a captured step graph replayed on four rotating device batches); `e2e` is the same through the public Python API
+with every batch copied from pinned host memory and every loss read back.  Both are the median over `--repeats`
+timed regions of K steps each; the spread is printed beside them.  `roofline` covers the contraction kernels
+(Dense / convolution forward, dX, dW, each with its own sub-record) and lists the bandwidth-bound passes with their
+algorithmic bytes against the HBM peak; all of it is timed live with CUDA events in a separate profiled pass.
+`cpu_baseline` is the reference's own CPU engine on this box's host cores on a bounded sample.
 
-With N > 1 the batch is sharded: every rank trains `batch` samples per step (weak scaling), the
-gradient arena is all-reduced with NCCL in buckets that overlap the rest of backward, and the
-optimizer divides by the world size.  `--impl reference` times the reference CPU engine
-(oracle/_ref, else the C restatement) driven op for op as the reference's CPU path runs.
+With N > 1 the batch is sharded: every rank trains `batch` samples per step (weak scaling; `--scaling strong` splits
+the configuration's batch over the ranks instead), the gradient arena is summed over the ranks by the engine's own
+NCCL data plane in buckets that overlap the rest of backward - inside the captured step graph - and the optimizer
+divides by the world size.  After the timed steps the ranks' weights are compared (`dp_check`).
+`--impl reference` times the reference CPU engine (oracle/_ref, else the C restatement) driven op for op as the
+reference's CPU path runs, with the thread layout stated in its line.
 """
-import argparse
-import json
 import os
+
+# The reference's CPU engine calls a pthread OpenBLAS inside `omp parallel for` loops (engine/src/conv_ops.cpp:109-175):
+# with both pools at the core count, cores^2 threads fight.  Pin one level before either library loads (a launcher that
+# presets OMP_NUM_THREADS=1 must not change the CPU arm); `cpu_threads` below switches layouts at run time.
+_CORES = os.cpu_count() or 1
+os.environ["OMP_NUM_THREADS"] = str(_CORES)
+os.environ["OPENBLAS_NUM_THREADS"] = "1"
+
+import argparse
+import ctypes
+import json
 import subprocess
 import sys
 import threading
@@ -99,19 +112,57 @@ def cpu_engine():
     return cpu_oracle, "port", "C restatement of the reference CPU engine (oracle/seera_oracle.c)"
 
 
-def cpu_steps(work, sample, steps, warmup):
-    """Times `steps` training steps of `sample` samples on the CPU engine; returns (samples/s, ms/step)."""
-    from oracle.train_oracle import RefNet
-    E, kind, how = cpu_engine()
-    net = RefNet(work.layers, work.params(0), work.loss, work.opt, E)
-    X, Y = work.batch(sample, 0)
+def cpu_threads(omp, blas):
+    """Sets the OpenMP and OpenBLAS thread counts of the libraries already loaded in this process."""
+    done = []
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(int(omp))
+        done.append("omp=%d" % omp)
+    except OSError:
+        pass
+    try:
+        with open("/proc/self/maps") as f:
+            libs = sorted({line.split()[-1] for line in f if "openblas" in line.split()[-1]})
+        for path in libs:
+            if "opencv" not in path:            # the engine links the OpenBLAS inside the opencv wheel; NumPy's own copy is not on this path
+                continue
+            lib = ctypes.CDLL(path)
+            for name in ("openblas_set_num_threads", "openblas_set_num_threads64_"):
+                if hasattr(lib, name):
+                    getattr(lib, name)(int(blas))
+                    done.append("blas=%d" % blas)
+                    break
+    except OSError:
+        pass
+    return " ".join(done)
+
+
+def cpu_time_steps(net, X, Y, steps, warmup):
     for _ in range(warmup):
         net.step(X, Y)
     t0 = time.perf_counter()
     for _ in range(steps):
         net.step(X, Y)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    return sample / dt, dt * 1e3, kind, how
+    return (time.perf_counter() - t0) / max(steps, 1)
+
+
+def cpu_steps(work, sample, steps, warmup):
+    """Times training steps of `sample` samples on the CPU engine under both thread layouts (all cores to the OpenMP loops
+    with one BLAS thread each, and all cores to BLAS with one OpenMP thread), keeps the faster for the `steps` timed steps.
+    Returns (samples/s, ms/step, kind, description)."""
+    from oracle.train_oracle import RefNet
+    E, kind, how = cpu_engine()
+    net = RefNet(work.layers, work.params(0), work.loss, work.opt, E)
+    X, Y = work.batch(sample, 0)
+    trial = {}
+    for name, (omp, blas) in (("omp%d_blas1" % _CORES, (_CORES, 1)), ("omp1_blas%d" % _CORES, (1, _CORES))):
+        set_to = cpu_threads(omp, blas)
+        trial[name] = (cpu_time_steps(net, X, Y, 2, 1), omp, blas, set_to)
+    best = min(trial, key=lambda k: trial[k][0])
+    cpu_threads(trial[best][1], trial[best][2])
+    dt = cpu_time_steps(net, X, Y, steps, warmup)
+    layout = "threads %s (chosen from %s)" % (best, ", ".join("%s %.0f ms/step" % (k, v[0] * 1e3) for k, v in trial.items()))
+    return sample / dt, dt * 1e3, kind, how + "; " + layout
 
 
 CPU_SAMPLE = {"c1": 64, "c2": 512, "c3": 32, "c4": 16}
@@ -121,17 +172,14 @@ def run_reference(args, work):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count()
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
-    os.environ.setdefault("OPENBLAS_NUM_THREADS", str(cores))
     sample = CPU_SAMPLE[args.workload]
     v, ms, kind, how = cpu_steps(work, sample, args.steps, args.warmup)
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "samples/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "f32", "data": "synthetic (seeded, shapes and value ranges of the configuration)",
             "config": {"workload": work.name, "per_gpu_batch": work.batch_size, "global_batch": work.batch_size * args.gpus, "optimizer": work.opt["kind"],
                        "step_sample": sample, "note": "each step is a %d-sample slice of the workload" % sample},
-            "cpu_baseline": {"value": v, "unit": "samples/s", "cores": cores, "kind": kind,
+            "cpu_baseline": {"value": v, "unit": "samples/s", "cores": _CORES, "kind": kind,
                              "sample": "%d steps of %d samples; %s" % (args.steps, sample, how)},
             "e2e": {"value": v, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -141,218 +189,269 @@ def run_reference(args, work):
 # ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
-class _ArenaView:
-    """Exposes a device range to torch (for NCCL) without copying."""
-
-    def __init__(self, ptr, n):
-        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
-
-
-def setup_data_parallel(model, world, local_rank):
-    """Bucketed, overlapped all-reduce of the gradient arena through torch.distributed (NCCL)."""
-    import torch
-    import torch.distributed as dist
-    from ml_framework_b200 import seera_cuda as sc, seera as S
-    import datetime
-    torch.cuda.set_device(local_rank)
-    opts = None
-    if os.environ.get("SEERA_NCCL_HIGH_PRIORITY", "1") != "0":
-        # the bucket sums run beside persistent kernels that fill every SM: let the collective's blocks go first
-        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=120),
-                            pg_options=opts)
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
-    sc.stream_synchronize()                         # uploads enqueued so far ran on the engine's own stream
-    sc.set_stream(stream.cuda_stream)               # the engine enqueues on the stream NCCL orders against
-    full = torch.as_tensor(_ArenaView(model.grads.main_ptr, model.n_arena), device="cuda")
-    from ml_framework_b200 import dp
-    model._arena_allreduce = lambda: dist.all_reduce(full, op=dist.ReduceOp.SUM)     # whole arena, stream-ordered
-    model._reduce_range = lambda b, e: dist.all_reduce(full[b:e], op=dist.ReduceOp.SUM, async_op=True)
-    model._reduce_wait = lambda w: w.wait()
-    dp.attach(model, world, reduce_range=model._reduce_range, wait=model._reduce_wait)
-    return dist, torch
-
-
 def _apply_options(sc, args):
     for item in args.option:
         name, _, value = item.partition("=")
         sc.set_option(name, int(value))
 
 
+def _median(v):
+    return float(np.median(np.asarray(v, np.float64)))
+
+
+def _traffic_from_profile(workload, precision):
+    """DRAM bytes per contraction launch, from the committed ncu launch list of this workload if it carries the line
+    `roofline.traffic_bytes_per_launch: <number> (precision <mode>)`; None otherwise (never a typed-in constant)."""
+    path = os.path.join(ROOT, "profiles", "bench_%s_launch_list.txt" % workload)
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.startswith("roofline.traffic_bytes_per_launch:"):
+                    rest = line.split(":", 1)[1].split()
+                    if "(precision" in line and precision not in line:
+                        return None, None
+                    return float(rest[0]), os.path.relpath(path, ROOT)
+    except OSError:
+        pass
+    return None, None
+
+
+def _dp_step_equals_joined_batch(work, rank, world, buckets, per_rank=16):
+    """One sharded step against the single-process step on the joined batch, in exact-fp32 mode: every rank computes the
+    gradients of its shard, the engine sums them over the ranks, and the mean is compared with the gradient arena of the same
+    model run on all `world * per_rank` samples by this rank alone."""
+    from ml_framework_b200 import train, dp, seera_cuda as sc
+    X, Y = work.batch(per_rank * world, seed=4242)
+    joined = train.Trainer(work, seed=7, precision=(0, 0))
+    joined.forward_backward(X, Y)
+    joined.model.gather_grads()
+    want = joined.model.grads.to_host_f32().astype(np.float64)[:joined.model.n_arena]
+    sharded = train.Trainer(work, seed=7, precision=(0, 0))
+    dp.attach_nccl(sharded.model, buckets)
+    sl = slice(rank * per_rank, (rank + 1) * per_rank)
+    sharded.forward_backward(X[sl], Y[sl])
+    sharded.model.gather_grads()
+    sharded.model._allreduce(sharded.model.grads)
+    got = sharded.model.grads.to_host_f32().astype(np.float64)[:sharded.model.n_arena] / world
+    den = np.linalg.norm(want)
+    return {"sharded_vs_joined_batch_grad_rel_l2": float(np.linalg.norm(got - want) / den) if den > 0 else 0.0,
+            "sharded_vs_joined_batch_samples": per_rank * world}
+
+
 def run_gpu(args, work):
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    from ml_framework_b200 import seera_cuda as sc, seera as S, train
+    from ml_framework_b200 import seera_cuda as sc, seera as S, train, dp
     sc.init(local)
     _apply_options(sc, args)
     prec = tuple(int(v) for v in args.precision.split("/"))
     prec = prec if len(prec) == 2 else (prec[0], prec[0])
+    multi = world > 1 or bool(os.environ.get("SEERA_BENCH_FORCE_DP"))     # the variable exercises the collective path on one rank
+    if multi:
+        dp.init_from_env()
     tr = train.Trainer(work, seed=0, precision=prec)
-    dist = torch = None
-    if world > 1 or os.environ.get("SEERA_BENCH_FORCE_DP"):      # the variable exercises the collective path on one rank
-        dist, torch = setup_data_parallel(tr.model, world, local)
-        # ("--option sm_reserve=R" leaves R SMs to the overlapped all-reduce; measured at 2 GPUs it only costs: 1.122 ms per step
-        # with R = 0, 1.157 / 1.170 / 1.185 with R = 4 / 8 / 16)
-    n = work.batch_size                                  # per-rank batch: weak scaling
-    X, Y = work.batch(n, seed=100 + rank)
-    Xd, Yd = S.Tensor(X, is_leaf=True), S.Tensor(Y, is_leaf=True)
+    buckets = dp.attach_nccl(tr.model, args.buckets) if multi else []
+    n = work.batch_size if args.scaling == "weak" else max(1, work.batch_size // world)     # per-rank batch
+    NB = 4                                                # distinct batches rotated through the step's input buffers
+    host = [work.batch(n, seed=100 + 17 * rank + i) for i in range(NB)]
+    dev = [(S.Tensor(x, is_leaf=True), S.Tensor(y, is_leaf=True)) for x, y in host]
+    X, Y = host[0]
+    Xd, Yd = S.Tensor(X.copy(), is_leaf=True), S.Tensor(Y.copy(), is_leaf=True)   # the buffers the captured step reads
+    scratch = S.cuten(np.zeros(4, np.float32)) if multi else None
 
     def barrier():
         sc.stream_synchronize()
-        if dist is not None:
-            dist.barrier()
+        if multi:
+            sc.dp_allreduce(scratch.main_ptr, 1, 0)
             sc.stream_synchronize()
 
     def reduce_max(ms):
-        if dist is None:
+        if not multi:
             return ms
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        sc.upload_f32(scratch.main_ptr, np.array([ms, 0, 0, 0], np.float32))
+        sc.dp_allreduce(scratch.main_ptr, 1, 1)
+        return float(scratch.to_host_f32()[0])
 
-    # ---- warm-up: eager steps until the memory pool has stopped growing, then (single process) capture the step
-    # (with several ranks every rank must run the SAME number of steps: each step holds collectives)
+    def load_batch(i):                                    # device-to-device: the batch is already resident in HBM
+        xb, yb = dev[i % NB]
+        sc.cuda_memcopy_devicetodevice(Xd.value.main_ptr, xb.value.main_ptr, xb.value.size)
+        sc.cuda_memcopy_devicetodevice(Yd.value.main_ptr, yb.value.main_ptr, yb.value.size)
+
+    # ---- warm-up: eager steps until the memory pool has stopped growing, then capture the step.  With several ranks
+    # every rank runs the SAME number of steps (each step holds collectives; NCCL sets its channels up lazily).
     reserved = -1
-    for i in range(max(args.warmup, 3) + (17 if dist is not None else 8)):      # NCCL sets its channels up lazily
+    for i in range(max(args.warmup, 3) + (9 if multi else 8)):
+        load_batch(i)
         tr.step(Xd, Yd)
         sc.stream_synchronize()
         r = sc.pool_bytes_reserved()
-        if dist is None and i + 1 >= max(args.warmup, 3) and r == reserved:
+        if not multi and i + 1 >= max(args.warmup, 3) and r == reserved:
             break
         reserved = r
     use_graph = not args.no_graph
     eager_ms = None
-    if use_graph and dist is not None:
-        from ml_framework_b200 import dp
-        loss_t = tr.capture_data_parallel(Xd, Yd, tr.model._arena_allreduce, buckets=dp.plan_buckets(tr.model, args.buckets),
-                                          reduce_range=tr.model._reduce_range, wait=tr.model._reduce_wait)
-        for _ in range(args.warmup):
-            tr.replay_data_parallel()
-        run_step = tr.replay_data_parallel
-    elif use_graph:
+    if use_graph:
         e0, e1 = sc.event_create(), sc.event_create()
         sc.event_record(e0)
-        for _ in range(5):
+        for i in range(5):
+            load_batch(i)
             tr.step(Xd, Yd)
         sc.event_record(e1)
         eager_ms = sc.event_elapsed_ms(e0, e1) / 5
-        loss_t = tr.capture(Xd, Yd)
-        for _ in range(args.warmup):
-            tr.replay()
-        run_step = tr.replay
+        tr.capture(Xd, Yd)
+        step_fn = tr.replay
     else:
-        run_step = lambda: tr.step(Xd, Yd)
+        step_fn = lambda: tr.step(Xd, Yd)
 
-    # ---- kernel-path throughput: inputs resident in HBM ------------------------------------------
-    barrier()
+    def run_step(i):
+        load_batch(i)
+        return step_fn()
+    for i in range(args.warmup):
+        run_step(i)
+
+    # ---- kernel-path throughput: batches resident in HBM; `repeats` timed regions of exactly K steps --------------
     e0, e1 = sc.event_create(), sc.event_create()
-    l0 = sc.launch_count()
+    times, launches = [], 0
     with ClockSampler(local) as clk:
-        t_wall = time.perf_counter()
-        sc.event_record(e0)
-        for _ in range(args.steps):
-            loss = run_step()
-        sc.event_record(e1)
-        barrier()
-        ms = reduce_max(sc.event_elapsed_ms(e0, e1))
+        for rep in range(args.repeats):
+            barrier()
+            l0 = sc.launch_count()
+            sc.event_record(e0)
+            for i in range(args.steps):
+                run_step(i)
+            sc.event_record(e1)
+            barrier()
+            launches = sc.launch_count() - l0
+            times.append(reduce_max(sc.event_elapsed_ms(e0, e1)))
+        ms = _median(times)
         # keep the device busy for about a second so the 200 ms clock sampler sees it under load; the count is
         # derived from the rank-reduced time, so every rank runs the same number of extra steps
-        extra = int(min(5000, max(0.0, 1000.0 - ms) / max(ms / args.steps, 1e-3)))
-        for _ in range(extra):
-            run_step()
+        extra = int(min(5000, max(0.0, 1000.0 - sum(times)) / max(ms / args.steps, 1e-3)))
+        for i in range(extra):
+            run_step(i)
         sc.stream_synchronize()
-    launches = (sc.launch_count() - l0)
     value = n * world * args.steps / (ms / 1e3)
     clocks = clk.summary()
-    launches_per_step = None
 
-    # ---- end to end: pinned host batch -> device every step, loss read back every step ---------------
-    import ctypes
-    hx, hy = sc.host_alloc_pinned(X.nbytes), sc.host_alloc_pinned(Y.nbytes)
-    ctypes.memmove(hx, X.ctypes.data, X.nbytes)
-    ctypes.memmove(hy, Y.ctypes.data, Y.nbytes)
+    # ---- end to end: a pinned host batch -> device every step, the loss read back every step --------------------
+    pinned = []
+    for x, y in host:
+        hx, hy = sc.host_alloc_pinned(x.nbytes), sc.host_alloc_pinned(y.nbytes)
+        ctypes.memmove(hx, x.ctypes.data, x.nbytes)
+        ctypes.memmove(hy, y.ctypes.data, y.nbytes)
+        pinned.append((hx, hy))
 
     # Graph mode streams the batches (Trainer.fit_stream: upload of batch i+1 and read-back of loss i-1 on the copy
     # stream while step i runs); eager mode uploads, steps and reads the loss in turn.
     def e2e_run(k):
         if use_graph:
-            return tr.fit_stream(((hx, hy) for _ in range(k)), data_parallel=dist is not None)[-1]
+            return tr.fit_stream((pinned[i % NB] for i in range(k)))[-1]
         last = 0.0
-        for _ in range(k):
+        for i in range(k):
+            hx, hy = pinned[i % NB]
             sc.upload_from_host_ptr(Xd.value.main_ptr, hx, X.nbytes)
             sc.upload_from_host_ptr(Yd.value.main_ptr, hy, Y.nbytes)
-            last = float(run_step().value.to_host_f32()[0])
+            last = float(step_fn().value.to_host_f32()[0])
         return last
     e2e_run(3)
-    barrier()
-    l1 = sc.launch_count()
-    sc.event_record(e0)
-    last = e2e_run(args.steps)
-    sc.event_record(e1)
-    barrier()
-    launches_per_step = (sc.launch_count() - l1) / args.steps
-    ms_e2e = reduce_max(sc.event_elapsed_ms(e0, e1))
+    e2e_times, last, e2e_launches = [], 0.0, 0
+    for rep in range(max(3, args.repeats // 2 + 1)):
+        barrier()
+        l1 = sc.launch_count()
+        sc.event_record(e0)
+        last = e2e_run(args.steps)
+        sc.event_record(e1)
+        barrier()
+        e2e_launches = sc.launch_count() - l1
+        e2e_times.append(reduce_max(sc.event_elapsed_ms(e0, e1)))
+    ms_e2e = _median(e2e_times)
     e2e = n * world * args.steps / (ms_e2e / 1e3)
     if use_graph:
         tr.release_graph()
 
-    # ---- roofline of the contraction kernels: a separate profiled pass (events around each launch) -----
+    # ---- data parallel: the ranks must hold the same weights after all those steps ---------------------------------
+    dp_check = None
+    if multi:
+        dp_check = {"weights_max_abs_diff_across_ranks": dp.replicas_differ_by(tr.model)}
+        dp_check.update(_dp_step_equals_joined_batch(work, rank, world, args.buckets))
+
+    # ---- roofline: a separate profiled pass (events around each launch), eager so that every launch is bracketed ----
     roof = None
     peaks = _peaks()
+    psteps = min(args.steps, 5)
     sc.profile_enable(1 if rank == 0 else 0)
-    for _ in range(min(args.steps, 5)):             # every rank steps (collectives), rank 0 records
+    for i in range(psteps):                         # every rank steps (collectives), rank 0 records
+        load_batch(i)
         # hold the stream for about two steps first: the step's launches then queue up and run back to back, so the
-        # events around each contraction time the kernel and not the host's gaps between eager launches
+        # events around each launch time the kernel and not the host's gaps between eager launches
         sc.stream_delay(int(min(100000, max(2000, 2000 * ms / args.steps))))
         tr.step(Xd, Yd)
         sc.stream_synchronize()
-    sc.stream_synchronize()
-    cnt, pms, pfl = sc.profile_read()
+    kinds = sc.profile_read_kinds()
+    table = sc.profile_report()
     sc.profile_enable(0)
-    if rank == 0:
-        if cnt and pms > 0:
-            ach = pfl / (pms / 1e3) / 1e12
-            # DRAM bytes per contraction launch from the ncu launch list of this workload (profiles/bench_c3_launch_list.txt:
-            # dram__bytes_read.sum + dram__bytes_write.sum of the 17 contraction launches of a C3 step = 620.9 MB)
-            traffic = 35.4e6 if (args.workload == "c3" and args.precision == "3/2") else None
-            roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": ach / peaks["tensor"],
-                    "traffic": traffic, "kernel": "contraction (Dense/Conv fwd, dX, dW)", "launches_per_step": cnt / min(args.steps, 5),
-                    "ms_per_step_in_kernel": pms / min(args.steps, 5), "peak_source": peaks["src"] + " sustained bf16",
-                    "share_of_step": (pms / min(args.steps, 5)) / (ms / args.steps)}
+    if rank == 0 and sum(k[0] for k in kinds) and sum(k[1] for k in kinds) > 0:
+        cnt, pms, pfl = (sum(k[j] for k in kinds) for j in range(3))
+        ach = pfl / (pms / 1e3) / 1e12
+        traffic, traffic_src = _traffic_from_profile(args.workload, args.precision)
+        sub = {}
+        for name, (kn, kms, kfl) in zip(("forward", "dX", "dW"), kinds):
+            if kn and kms > 0:
+                t = kfl / (kms / 1e3) / 1e12
+                sub[name] = {"launches_per_step": kn / psteps, "ms_per_step": kms / psteps, "gflop_per_step": kfl / psteps / 1e9,
+                             "achieved": t, "frac": t / peaks["tensor"]}
+        hbm = []
+        for tag, kind, kn, kms, work_bytes in table:
+            if kind == 3 and kms > 0:
+                g = work_bytes / (kms / 1e3) / 1e9
+                hbm.append({"pass": tag, "launches_per_step": kn / psteps, "ms_per_step": kms / psteps,
+                            "algorithmic_mb_per_step": work_bytes / psteps / 1e6, "achieved": g, "frac": g / peaks["hbm"]})
+        hbm.sort(key=lambda r: -r["ms_per_step"])
+        roof = {"bound": "tensor", "achieved": ach, "peak": peaks["tensor"], "unit": "TFLOP/s", "frac": ach / peaks["tensor"],
+                "traffic": traffic, "traffic_source": traffic_src, "kernel": "contraction (Dense/Conv forward, dX, dW)",
+                "launches_per_step": cnt / psteps, "ms_per_step_in_kernel": pms / psteps, "peak_source": peaks["src"] + " sustained bf16",
+                "share_of_step": (pms / psteps) / (ms / args.steps), "by_kind": sub,
+                "backward": None, "hbm_bound_passes": {"peak": peaks["hbm"], "unit": "GB/s", "peak_source": peaks["src"], "passes": hbm}}
+        bkn, bms, bfl = (kinds[1][j] + kinds[2][j] for j in range(3))
+        if bkn and bms > 0:
+            t = bfl / (bms / 1e3) / 1e12
+            roof["backward"] = {"achieved": t, "frac": t / peaks["tensor"], "ms_per_step": bms / psteps}
 
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu:
-            cores = os.cpu_count()
             sample = CPU_SAMPLE[args.workload]
-            v, cms, kind, how = cpu_steps(work, sample, {"c3": 8, "c4": 12}.get(args.workload, 10), 1)      # about 10 s of CPU work
-            cpu = {"value": v, "unit": "samples/s", "cores": cores, "kind": kind,
+            v, cms, kind, how = cpu_steps(work, sample, {"c3": 40, "c4": 30, "c2": 20}.get(args.workload, 50), 1)   # 10-30 s of CPU work
+            cpu = {"value": v, "unit": "samples/s", "cores": _CORES, "kind": kind,
                    "sample": "%d-sample steps, %.0f ms each; %s" % (sample, cms, how)}
+        dtype = {"0": "f32", "1": "bf16 (f32 accumulate)", "2": "bf16x3 (f32 accumulate)", "3": "bf16x6 (f32 accumulate)",
+                 "3/2": "bf16 split products, f32 accumulate (forward 6-term, backward 3-term)"}.get(args.precision, args.precision)
         line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": {"0": "f32", "1": "bf16 (f32 accumulate)", "2": "bf16x3 (f32 accumulate)", "3": "bf16x6 (f32 accumulate)",
-                          "3/2": "bf16 split products, f32 accumulate (forward 6-term, backward 3-term)"}.get(args.precision, args.precision),
-                "data": "synthetic (seeded, shapes and value ranges of the configuration)",
+                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
+                "dtype": dtype, "data": "synthetic (seeded, shapes and value ranges of the configuration)",
                 "config": {"workload": work.name, "per_gpu_batch": n, "global_batch": n * world,
                            "parallelism": "dp%d" % world if world > 1 else "single",
-                           "optimizer": work.opt["kind"], "precision_mode": args.precision,
+                           "optimizer": work.opt["kind"], "precision_mode": args.precision, "distinct_batches": NB,
                            "l2": "activations per step exceed the 126 MB L2; no explicit flush" if args.workload in ("c2", "c3", "c4")
                                  else "working set fits L2 (latency-bound configuration)"},
+                "repeats": {"n": len(times), "ms_per_step_median": ms / args.steps, "ms_per_step_min": min(times) / args.steps,
+                            "ms_per_step_max": max(times) / args.steps},
                 "clocks": clocks,
                 "e2e": {"value": e2e, "unit": "samples/s", "h2d_bytes_per_step": int(X.nbytes + Y.nbytes) * world,
-                        "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
-                "gpu_launches": int(launches_per_step * args.steps), "launches_per_step": launches_per_step, "final_loss": last,
-                "step_mode": ("eager launches, bucketed all-reduce overlapping backward" if not use_graph else
-                              "CUDA graphs of forward+backward cut at the gradient buckets, each bucket's NCCL all-reduce overlapping the next graph, fused optimizer"
-                              if dist is not None else "CUDA graph replay of the captured step"),
+                        "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps,
+                        "ms_per_step_min": min(e2e_times) / args.steps, "ms_per_step_max": max(e2e_times) / args.steps,
+                        "repeats": len(e2e_times)},
+                "gpu_launches": int(e2e_launches), "launches_per_step": launches / args.steps, "final_loss": last,
+                "step_mode": ("eager launches" if not use_graph else "CUDA graph replay of the captured step") +
+                             (", gradient buckets summed by NCCL on the engine's communication stream inside the step, overlapping "
+                              "the rest of backward (%d buckets)" % len(buckets) if multi else ""),
                 "eager_ms_per_step": eager_ms,
                 "algorithmic_gflop_per_step": work.flops_per_sample() * n * world / 1e9,
-                "roofline": roof, "cpu_baseline": cpu}
+                "dp_check": dp_check, "roofline": roof, "cpu_baseline": cpu}
         print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    if multi:
+        barrier()
+        dp.finalize()
 
 
 def run_c5(args):
@@ -422,7 +521,10 @@ def main():
                          "3/2 for the fp32 configurations")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="engine option for seera_set_option (repeatable), e.g. tile_n_cap3=128")
-    ap.add_argument("--buckets", type=int, default=4, help="data parallel: gradient buckets (all-reduces) per step")
+    ap.add_argument("--buckets", type=int, default=3, help="data parallel: gradient buckets (all-reduces) per step")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1: weak = the configuration's batch on every GPU; strong = that batch split over the GPUs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a captured step")
     args = ap.parse_args()

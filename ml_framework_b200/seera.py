@@ -800,6 +800,16 @@ class Sequential:
         v._owns_memory, v._base = False, self.grads
         return v
 
+    def rehome_grads(self, ptr):
+        """Use the caller's device block (at least n_arena floats, zeroed, kept alive by the caller) as the gradient arena
+        from now on - e.g. memory registered with a communicator, so that collectives work on it in place."""
+        g = cuten._wrap(int(ptr), (max(self.n_arena, 1),))
+        g._owns_memory = False
+        self.grads = g
+        for t in self.parameters():
+            t._grad_slot = self._grad_view(t)
+            t.grad = None
+
     def parameters(self):
         return [t for l in self.param_layers for t in (l.weights, l.bais)]
 

@@ -85,13 +85,16 @@ class Trainer:
 
     # ---- whole-step CUDA graph -------------------------------------------------------------------
     def capture(self, X, Y):
-        """Records forward + loss + backward + optimizer on the device tensors X, Y into a CUDA graph.
+        """Records forward + loss + backward + optimizer on the device tensors X, Y into a CUDA graph.  In a data-parallel
+        run over the engine's own collectives (dp.attach_nccl) the bucket sums are part of the recording: they fork onto
+        the communication stream and join before the optimizer, all inside the one graph.
         Run `step` eagerly at least twice first.  Afterwards `replay()` re-runs the recorded step on
         whatever X and Y hold at that moment; the loss tensor returned here is rewritten by every replay."""
         if not (isinstance(X, S.Tensor) and isinstance(Y, S.Tensor)):
             raise TypeError("capture needs device-resident Tensors")
-        if self.model._allreduce is not None:
-            raise RuntimeError("capture is for single-process training; the data-parallel step runs eagerly")
+        if self.model._allreduce is not None and not getattr(self.model, "_collectives_capturable", False):
+            raise RuntimeError("capture needs collectives that can be recorded (dp.attach_nccl); with other collectives use "
+                               "capture_data_parallel")
         sc.graph_begin()
         try:
             loss = self.step(X, Y)
