@@ -21,7 +21,9 @@ on the reference's CPU path (Seera_Engine.py:30-39, Seera_init.py:476, :514).
 `quant` (optional) is applied to every GEMM / convolution operand before the engine call:
 with ml_framework_b200.workloads.bf16_round it gives the "matched quantisation" oracle for
 the bf16 configurations - the arithmetic stays the engine's fp32, only its inputs carry
-the rounding the tensor-core path applies.
+the rounding the tensor-core path applies.  With `quant_forward=False` only the backward products' operands are
+rounded: the oracle of a policy that runs the forward pass in fp32-class split products and the backward GEMMs in
+one bf16 pass.
 """
 import numpy as np
 
@@ -31,9 +33,10 @@ def _pair(v):
 
 
 class RefNet:
-    def __init__(self, layers, params, loss, opt, engine, quant=None):
+    def __init__(self, layers, params, loss, opt, engine, quant=None, quant_forward=True):
         self.layers, self.loss_kind, self.opt, self.E = layers, loss, dict(opt), engine
         self.q = quant or (lambda a: a)
+        self.qf = self.q if quant_forward else (lambda a: a)      # forward operands: rounded too, or left in fp32
         self.params = [None if p is None else [p[0].copy(), p[1].copy()] for p in params]
         self.state = [None if p is None else [np.zeros_like(p[0]), np.zeros_like(p[1]),
                                               np.zeros_like(p[0]), np.zeros_like(p[1])] for p in params]
@@ -56,7 +59,7 @@ class RefNet:
         raise ValueError(kind)
 
     def forward(self, X):
-        E, q = self.E, self.q
+        E, q = self.E, self.qf
         x = np.ascontiguousarray(X, dtype=np.float32)
         tape = []
         for L, P in zip(self.layers, self.params):
