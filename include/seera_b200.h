@@ -74,7 +74,14 @@ int         seera_profile_report(char *buf, size_t size);
  *   1 bf16 operands, fp32 accumulate on the tensor cores (one pass)
  *   2 bf16x3: a_hi*b_hi + a_hi*b_lo + a_lo*b_hi on the tensor cores (16 mantissa bits per operand, ~5e-6)
  *   3 bf16x6: three-way split hi+lo+lo2, six products (24 mantissa bits per operand, fp32-class); on the
- *     TMA-fed kernels; the kernel that gathers in its producer warps runs mode 3 as mode 2 */
+ *     TMA-fed kernels; the kernel that gathers in its producer warps runs mode 3 as mode 2
+ *   4 fp16x3: two-way split into fp16 copies (11 + 11 mantissa bits), three products - the accuracy of mode 3
+ *     (the dropped lo*lo term is 2^-22 of a product) at the cost of mode 2.  fp16 has a 5-bit exponent, so the
+ *     copies carry a power-of-two factor by class of tensor, taken out again exactly in the epilogue:
+ *     activations x 2^4 (saturate at 4094), weights x 2^8 (at 255.9), gradients x 2^12 (at 15.99); magnitudes
+ *     down to 2^-7 / 2^-11 / 2^-15 keep all 22 bits, smaller ones an absolute error of 2^-29 / 2^-33 / 2^-37.
+ *     Conversion saturates, it never produces infinities.  Data outside these ranges belongs in modes 2 / 3.
+ *     Kernels that convert inside their producer warps (short patches, the gather fallback) run mode 4 as mode 2. */
 int         seera_set_precision(int mode);
 int         seera_get_precision(void);
 /* Engine options by name.

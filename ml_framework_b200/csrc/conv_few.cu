@@ -348,9 +348,9 @@ __global__ void __launch_bounds__(256, 3) conv3x3_pool_kernel(const float *__res
             }
             if (po.copy[0]) {
                 const long long o = ((long long)n * Pq + wrem) * po.Cp + f0;
-                *reinterpret_cast<uint4 *>(po.copy[0] + o) = split_chunk(mx);
-                if (po.ns >= 2) *reinterpret_cast<uint4 *>(po.copy[1] + o) = split_chunk(mx);
-                if (po.ns >= 3) *reinterpret_cast<uint4 *>(po.copy[2] + o) = split_chunk(mx);
+                if (po.ns == 1) store_split8<1>(mx, po.enc, po.copy[0] + o, nullptr, nullptr);
+                else if (po.ns == 2) store_split8<2>(mx, po.enc, po.copy[0] + o, po.copy[1] + o, nullptr);
+                else store_split8<3>(mx, po.enc, po.copy[0] + o, po.copy[1] + o, po.copy[2] + o);
             }
         }
     }

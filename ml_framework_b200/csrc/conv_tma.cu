@@ -85,7 +85,7 @@ static int make_map_im2col_box(CUtensorMap *m, const void *base, int NB, int H, 
 template <int NS>
 __global__ void __launch_bounds__(256) shadow_nhwc_kernel(const float *__restrict__ src, int C, int P, int Cp,
                                                           __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
-                                                          __nv_bfloat16 *__restrict__ d2) {
+                                                          __nv_bfloat16 *__restrict__ d2, Enc enc) {
     __shared__ float tile[64][33];
     const int img = blockIdx.z, c0 = blockIdx.y * 64, p0 = blockIdx.x * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -102,21 +102,21 @@ __global__ void __launch_bounds__(256) shadow_nhwc_kernel(const float *__restric
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = tile[cg * 8 + i][pl];
         long long o = ((long long)img * P + p) * Cp + c;
-        *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
-        if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
-        if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+        store_split8<NS>(v, enc, d0 + o, d1 + o, d2 + o);
     }
 }
 
 struct NhwcShadow {
     __nv_bfloat16 *p[3] = {nullptr, nullptr, nullptr};
     int NB = 0, H = 0, W = 0, C = 0, Cp = 0;
+    Enc enc{0, 1.f};
 };
 static void free_nhwc(NhwcShadow &s) {
     for (int i = 0; i < 3; i++) { if (s.p[i]) scratch_free(s.p[i]); s.p[i] = nullptr; }
 }
-static int make_nhwc(const float *src, int NB, int C, int H, int W, int ns, NhwcShadow &s) {
+static int make_nhwc(const float *src, int NB, int C, int H, int W, int ns, NhwcShadow &s, int cls) {
     s.NB = NB; s.H = H; s.W = W; s.C = C; s.Cp = (C + 7) / 8 * 8;
+    s.enc = enc_for(cls);
     size_t bytes = (size_t)NB * H * W * s.Cp * 2;
     for (int i = 0; i < ns; i++) { s.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!s.p[i]) return SEERA_E_OOM; }
     int P = H * W;
@@ -124,9 +124,9 @@ static int make_nhwc(const float *src, int NB, int C, int H, int W, int ns, Nhwc
     if (grid.z > 65535 || grid.y > 65535) return fail(SEERA_E_LIMIT, "channels-last shadow: batch or channel count too large");
     cudaStream_t st = rt().stream;
     ProfBytes pb(4.0 * NB * C * P + (double)ns * bytes, "shadow_nhwc");
-    if (ns == 1) shadow_nhwc_kernel<1><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
-    else if (ns == 2) shadow_nhwc_kernel<2><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
-    else shadow_nhwc_kernel<3><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2]);
+    if (ns == 1) shadow_nhwc_kernel<1><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2], s.enc);
+    else if (ns == 2) shadow_nhwc_kernel<2><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2], s.enc);
+    else shadow_nhwc_kernel<3><<<grid, 256, 0, st>>>(src, C, P, s.Cp, s.p[0], s.p[1], s.p[2], s.enc);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, "shadow_nhwc");
@@ -136,29 +136,27 @@ static int make_nhwc(const float *src, int NB, int C, int H, int W, int ns, Nhwc
 template <int NS>
 __global__ void __launch_bounds__(256) shadow_weight_kernel(const float *__restrict__ Wt, int O, int I, int Ip, int taps, long long so,
                                                             long long si, int flip, __nv_bfloat16 *__restrict__ d0,
-                                                            __nv_bfloat16 *__restrict__ d1, __nv_bfloat16 *__restrict__ d2) {
+                                                            __nv_bfloat16 *__restrict__ d1, __nv_bfloat16 *__restrict__ d2, Enc enc) {
     long long total = (long long)O * taps * Ip;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
     for (long long e = tid; e < total; e += nthr) {
         int i = (int)(e % Ip); long long t2 = e / Ip;
         int tap = (int)(t2 % taps); int o = (int)(t2 / taps);
         float v = i < I ? __ldg(Wt + o * so + i * si + (flip ? taps - 1 - tap : tap)) : 0.f;
-        __nv_bfloat16 h = __float2bfloat16_rn(v);
-        d0[e] = h;
-        if (NS >= 2) { v -= __bfloat162float(h); __nv_bfloat16 l = __float2bfloat16_rn(v); d1[e] = l;
-                       if (NS >= 3) { v -= __bfloat162float(l); d2[e] = __float2bfloat16_rn(v); } }
+        store_split1(v, NS, enc, d0 + e, d1 + e, d2 + e);
     }
 }
 // Result is a row-major matrix [O, taps*Ip] (Shadow with ld = cols).
 static int make_weight_shadow(const float *Wt, int O, int I, int taps, long long so, long long si, int flip, int ns, Shadow &s) {
     int Ip = (I + 7) / 8 * 8;
     if (int e = alloc_shadow(s, O, taps * Ip, ns)) return e;
+    s.enc = enc_for(CLS_WEIGHT);
     long long total = (long long)O * taps * Ip;
     int grid = stride_grid(total);
     cudaStream_t st = rt().stream;
-    if (ns == 1) shadow_weight_kernel<1><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2]);
-    else if (ns == 2) shadow_weight_kernel<2><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2]);
-    else shadow_weight_kernel<3><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2]);
+    if (ns == 1) shadow_weight_kernel<1><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2], s.enc);
+    else if (ns == 2) shadow_weight_kernel<2><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2], s.enc);
+    else shadow_weight_kernel<3><<<grid, 256, 0, st>>>(Wt, O, I, Ip, taps, so, si, flip, s.p[0], s.p[1], s.p[2], s.enc);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, "shadow_weight");
@@ -170,7 +168,7 @@ template <int NS>
 __global__ void __launch_bounds__(256) shadow_weight_phase_kernel(const float *__restrict__ Wt, int O, int I, int Ip, long long so, long long si,
                                                                   int S, int r0, int sh, int Ta, int s0, int sw, int Ub,
                                                                   __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
-                                                                  __nv_bfloat16 *__restrict__ d2) {
+                                                                  __nv_bfloat16 *__restrict__ d2, Enc enc) {
     const int taps = Ta * Ub;
     long long total = (long long)O * taps * Ip;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
@@ -180,10 +178,7 @@ __global__ void __launch_bounds__(256) shadow_weight_phase_kernel(const float *_
         int tp = tap / Ub, up = tap - tp * Ub;
         int r = r0 + sh * (Ta - 1 - tp), sx = s0 + sw * (Ub - 1 - up);
         float v = i < I ? __ldg(Wt + o * so + i * si + r * S + sx) : 0.f;
-        __nv_bfloat16 h = __float2bfloat16_rn(v);
-        d0[e] = h;
-        if (NS >= 2) { v -= __bfloat162float(h); __nv_bfloat16 l = __float2bfloat16_rn(v); d1[e] = l;
-                       if (NS >= 3) { v -= __bfloat162float(l); d2[e] = __float2bfloat16_rn(v); } }
+        store_split1(v, NS, enc, d0 + e, d1 + e, d2 + e);
     }
 }
 
@@ -218,6 +213,7 @@ static int tma_fprop(const NhwcShadow &x, const Shadow &wk, float *Y, int F, int
     p.bias = bias; p.act = act;
     if (pool) { p.pool_on = 1; p.pool = *pool; pool_out_geometry(p.pool, OH * OW, OW, 0); }
     p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
+    p.a_fp16 = x.enc.fmt; p.b_fp16 = wk.enc.fmt; p.out_scale = 1.f / (x.enc.scale * wk.enc.scale);
     p.M = x.NB * OH * OW; p.N = F;
     p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
     p.K = p.taps * p.cchunks * 64;
@@ -239,6 +235,7 @@ static int tma_wgrad(const NhwcShadow &x, const NhwcShadow &dy, float *dW, int R
     const int OH = dy.H, OW = dy.W, F = dy.C;
     TmaGemmParams p{};
     p.a_mode = TMA_A_TAPS; p.b_mn = 1;
+    p.a_fp16 = x.enc.fmt; p.b_fp16 = dy.enc.fmt; p.out_scale = 1.f / (x.enc.scale * dy.enc.scale);
     p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
     p.M = p.taps * p.cchunks * 64; p.N = F;
     p.K = x.NB * OH * OW;
@@ -305,11 +302,12 @@ static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, 
             Shadow wk;
             const int taps = y.T * x.T;
             if (int e = alloc_shadow(wk, Nch, taps * Ip, ns)) return e;
+            wk.enc = enc_for(CLS_WEIGHT);
             long long total = (long long)Nch * taps * Ip;
             int grid = stride_grid(total);
-            if (ns == 1) shadow_weight_phase_kernel<1><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2]);
-            else if (ns == 2) shadow_weight_phase_kernel<2><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2]);
-            else shadow_weight_phase_kernel<3><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2]);
+            if (ns == 1) shadow_weight_phase_kernel<1><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2], wk.enc);
+            else if (ns == 2) shadow_weight_phase_kernel<2><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2], wk.enc);
+            else shadow_weight_phase_kernel<3><<<grid, 256, 0, st>>>(Wt, Nch, g.C, Ip, so, si, S, y.r0, sh, y.T, x.r0, sw, x.T, wk.p[0], wk.p[1], wk.p[2], wk.enc);
             count_launch();
             cudaError_t ce = cudaGetLastError();
             if (ce != cudaSuccess) { free_shadow(wk); return check_cuda(ce, "shadow_weight_phase"); }
@@ -317,6 +315,7 @@ static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, 
             TmaGemmParams p{};
             p.bias = bias; p.act = act;
             p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
+            p.a_fp16 = g.enc.fmt; p.b_fp16 = wk.enc.fmt; p.out_scale = 1.f / (g.enc.scale * wk.enc.scale);
             p.M = g.NB * y.G * x.G; p.N = Nch;
             p.cchunks = (g.Cp + 63) / 64; p.cpad = g.Cp; p.taps = taps; p.S = x.T;
             p.K = p.taps * p.cchunks * 64;
@@ -358,7 +357,7 @@ __global__ void __launch_bounds__(256, 4) dz_shadow_kernel(const float *__restri
                                                         const float *__restrict__ y, const float *__restrict__ yp, int C, int H, int W,
                                                         int Cp, int items, int ptiles,
                                                         int act, __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
-                                                        __nv_bfloat16 *__restrict__ d2, float *__restrict__ partial) {
+                                                        __nv_bfloat16 *__restrict__ d2, float *__restrict__ partial, Enc enc) {
     // Read side: warp = group of 8 consecutive channels, lane = pixel: every load is one 128-byte line of a channel plane.
     // Write side: the 32-pixel x 64-channel tile goes through shared memory so that 8 consecutive lanes write the 128 bytes one
     // pixel owns in the channels-last copies and a warp writes four whole pixels per store.
@@ -423,9 +422,7 @@ __global__ void __launch_bounds__(256, 4) dz_shadow_kernel(const float *__restri
             const float4 b = *reinterpret_cast<const float4 *>(&sdz[threadIdx.x >> 3][ch * 8 + 4]);
             float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
             const long long o = ((long long)img * P + pp) * Cp + c8;
-            *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
-            if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
-            if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+            store_split8<NS>(v, enc, d0 + o, d1 + o, d2 + o);
         }
         __syncthreads();
     }
@@ -447,7 +444,7 @@ __global__ void __launch_bounds__(256, 4) dz_shadow_window_kernel(const float *_
                                                                   const float *__restrict__ yp, int C, int H, int W, int Cp, int items,
                                                                   int wtiles, int act, __nv_bfloat16 *__restrict__ d0,
                                                                   __nv_bfloat16 *__restrict__ d1, __nv_bfloat16 *__restrict__ d2,
-                                                                  float *__restrict__ partial) {
+                                                                  float *__restrict__ partial, Enc enc) {
     // Tile = 32 windows x 64 channels.  Read side: lane = window, warp = 8 channels (full lines of the channel-major pooled
     // tensors).  Write side: the tile goes through shared memory so that 8 consecutive lanes write the 128 bytes one pixel owns
     // in the channels-last copies (a lane-per-window store touches 32 different lines per instruction).
@@ -504,9 +501,7 @@ __global__ void __launch_bounds__(256, 4) dz_shadow_window_kernel(const float *_
                 for (int i = 0; i < 8; i++) v[i] = mm[i] == pos ? vv[i] : 0.f;
                 const int p = (2 * ohq + (pos >> 1)) * W + 2 * owq + (pos & 1);
                 const long long o = ((long long)img * P + p) * Cp + c8;
-                *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
-                if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
-                if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+                store_split8<NS>(v, enc, d0 + o, d1 + o, d2 + o);
             }
         }
         __syncthreads();
@@ -539,7 +534,7 @@ template <int NS>
 __global__ void __launch_bounds__(256, 4) pool2x2_shadow_kernel(const float *__restrict__ y, float *__restrict__ out, int *__restrict__ mask,
                                                              int C, int H, int W, int Cp, int items, int ptiles,
                                                              __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
-                                                             __nv_bfloat16 *__restrict__ d2) {
+                                                             __nv_bfloat16 *__restrict__ d2, Enc enc) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int cb = blockIdx.y * 64 + warp * 8;
     const int OW = W >> 1, Pq = (H >> 1) * OW;
@@ -568,9 +563,7 @@ __global__ void __launch_bounds__(256, 4) pool2x2_shadow_kernel(const float *__r
             v[i] = cb + i < C ? m : 0.f;
         }
         const long long o = ((long long)img * Pq + q) * Cp + cb;
-        *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
-        if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
-        if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+        store_split8<NS>(v, enc, d0 + o, d1 + o, d2 + o);
     }
 }
 
@@ -595,8 +588,10 @@ struct seera_shadow {
 
 namespace seera {
 
-static const NhwcShadow *usable(const seera_shadow *h, int ns, int NB, int C, int H, int W) {
-    if (!h || h->ns < ns || h->s.NB != NB || h->s.C != C || h->s.H != H || h->s.W != W) return nullptr;
+static const NhwcShadow *usable(const seera_shadow *h, int ns, int NB, int C, int H, int W, int cls) {
+    const Enc want = enc_for(cls);            // copies made under another encoding (bf16 against fp16) cannot be mixed in
+    if (!h || h->ns < ns || h->s.NB != NB || h->s.C != C || h->s.H != H || h->s.W != W || h->s.enc.fmt != want.fmt ||
+        h->s.enc.scale != want.scale) return nullptr;
     return &h->s;
 }
 
@@ -615,11 +610,11 @@ static int tma_conv2d_bwd_kept(const float *Wt, const float *X, const float *dY,
     if (!tma_conv_supported(NB, R, S, sh, sw, ph, pw)) return seera_tc_conv2d_bwd(Wt, X, dY, dX, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw);
     int ns = precision_copies();
     NhwcShadow dys_local, xs_local; Shadow wd;
-    const NhwcShadow *dys = usable(dyk, ns, NB, F, OH, OW), *xs = usable(xk, ns, NB, C, H, W);
+    const NhwcShadow *dys = usable(dyk, ns, NB, F, OH, OW, CLS_GRAD), *xs = usable(xk, ns, NB, C, H, W, CLS_ACT);
     int s = SEERA_OK;
     if (!dys && (dX || (dW && !first))) {
         if (!dY) return fail(SEERA_E_ARG, "cuda_conv2d_bwd: kept gradient copies do not fit this call and no fp32 gradient was given");
-        s = make_nhwc(dY, NB, F, OH, OW, ns, dys_local);
+        s = make_nhwc(dY, NB, F, OH, OW, ns, dys_local, CLS_GRAD);
         dys = &dys_local;
     }
     if (!s && dX) {
@@ -636,7 +631,7 @@ static int tma_conv2d_bwd_kept(const float *Wt, const float *X, const float *dY,
         if (first) {                  // short patch: direct fp32 kernel on the NCHW tensors
             s = conv_first_wgrad(X, dY, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw, "cuda_conv2d_bwd(dW)");
         } else {
-            if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, xs_local); xs = &xs_local; }
+            if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, xs_local, CLS_ACT); xs = &xs_local; }
             if (!s) s = tma_wgrad(*xs, *dys, dW, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dW)");
         }
     }
@@ -673,7 +668,7 @@ int seera_tma_conv2d_bias_act_fwd(const float *X, const float *Wt, const float *
     }
     int ns = precision_copies();
     NhwcShadow xs; Shadow wk;
-    int s = make_nhwc(X, NB, C, H, W, ns, xs);
+    int s = make_nhwc(X, NB, C, H, W, ns, xs, CLS_ACT);
     if (!s) s = make_weight_shadow(Wt, F, C, R * S, (long long)C * R * S, R * S, 0, ns, wk);
     if (!s) s = tma_fprop(xs, wk, Y, F, R, S, sh, sw, ph, pw, OH, OW, ns, "cuda_conv2d_fwd", bias, act);
     free_nhwc(xs); free_shadow(wk);
@@ -710,9 +705,9 @@ int seera_conv2d_bias_act_fwd_s(const float *X, const float *Wt, const float *bi
         return conv_few_fwd(X, Wt, bias, Y, NB, C, H, W, F, R, S, ph, pw, OH, OW, act, 0, "cuda_conv2d_fwd");
     int ns = precision_copies();
     NhwcShadow local; Shadow wk;
-    const NhwcShadow *xs = usable(x_in, ns, NB, C, H, W);
+    const NhwcShadow *xs = usable(x_in, ns, NB, C, H, W, CLS_ACT);
     int s = SEERA_OK;
-    if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, local); xs = &local; }
+    if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, local, CLS_ACT); xs = &local; }
     if (!s) s = make_weight_shadow(Wt, F, C, R * S, (long long)C * R * S, R * S, 0, ns, wk);
     if (!s) s = tma_fprop(*xs, wk, Y, F, R, S, sh, sw, ph, pw, OH, OW, ns, "cuda_conv2d_fwd", bias, act);
     free_shadow(wk);
@@ -735,6 +730,7 @@ int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, 
     const int ns = precision_copies();
     NhwcShadow sh;
     sh.NB = N; sh.H = H / 2; sh.W = W / 2; sh.C = C; sh.Cp = (C + 7) / 8 * 8;
+    sh.enc = enc_for(CLS_ACT);
     size_t bytes = (size_t)N * Pq * sh.Cp * 2;
     for (int i = 0; i < ns; i++) { sh.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!sh.p[i]) { free_nhwc(sh); return SEERA_E_OOM; } }
     const int cchunks = (sh.Cp + 63) / 64;
@@ -745,9 +741,9 @@ int seera_maxpool2x2_fwd_s(const float *X, float *out, int *mask, int N, int C, 
     cudaStream_t st = rt().stream;
     // input read once; pooled values and argmax mask written; ns channels-last copies of the pooled tensor written
     ProfBytes pb(4.0 * N * C * H * W + 8.0 * N * C * Pq + (double)ns * bytes, "pool2x2_shadow");
-    if (ns == 1) pool2x2_shadow_kernel<1><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
-    else if (ns == 2) pool2x2_shadow_kernel<2><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
-    else pool2x2_shadow_kernel<3><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2]);
+    if (ns == 1) pool2x2_shadow_kernel<1><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2], sh.enc);
+    else if (ns == 2) pool2x2_shadow_kernel<2><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2], sh.enc);
+    else pool2x2_shadow_kernel<3><<<grid, 256, 0, st>>>(X, out, mask, C, H, W, sh.Cp, (int)items, ptiles, sh.p[0], sh.p[1], sh.p[2], sh.enc);
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { free_nhwc(sh); return check_cuda(e, "maxpool2x2_fwd"); }
@@ -786,19 +782,20 @@ int seera_conv2d_bias_act_pool_fwd_s(const float *X, const float *Wt, const floa
     NhwcShadow pc;                                     // copies of the pooled tensor, when the caller wants them
     if (pooled_copies) {
         pc.NB = NB; pc.H = OH / 2; pc.W = OW / 2; pc.C = F; pc.Cp = (F + 7) / 8 * 8;
+        pc.enc = enc_for(CLS_ACT);
         size_t bytes = (size_t)NB * pc.H * pc.W * pc.Cp * 2;
         for (int i = 0; i < ns; i++) { pc.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!pc.p[i]) { free_nhwc(pc); return SEERA_E_OOM; } }
         for (int i = 0; i < 3; i++) po.copy[i] = pc.p[i];
-        po.ns = ns; po.Cp = pc.Cp;
+        po.ns = ns; po.Cp = pc.Cp; po.enc = pc.enc;
     }
     int s;
     if (conv_first_applies(C, R, S)) {
         s = conv_first_pool_fwd(X, Wt, bias, po, NB, C, H, W, F, R, S, ph, pw, sh, sw, act, "conv2d_pool_fwd");
     } else {
         NhwcShadow local; Shadow wk;
-        const NhwcShadow *xs = usable(x_in, ns, NB, C, H, W);
+        const NhwcShadow *xs = usable(x_in, ns, NB, C, H, W, CLS_ACT);
         s = SEERA_OK;
-        if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, local); xs = &local; }
+        if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, local, CLS_ACT); xs = &local; }
         if (!s) s = make_weight_shadow(Wt, F, C, R * S, (long long)C * R * S, R * S, 0, ns, wk);
         if (!s) s = tma_fprop(*xs, wk, nullptr, F, R, S, sh, sw, ph, pw, OH, OW, ns, "conv2d_pool_fwd", bias, act, &po);
         free_shadow(wk);
@@ -814,6 +811,7 @@ int seera_conv2d_bias_act_pool_fwd_s(const float *X, const float *Wt, const floa
 static int make_dz_shadow(const float *g, const float *gp, const int *mask, const float *y, const float *yp, float *dbias, int NB, int C,
                           int H, int W, int act, int ns, NhwcShadow &out) {
     out.NB = NB; out.H = H; out.W = W; out.C = C; out.Cp = (C + 7) / 8 * 8;
+    out.enc = enc_for(CLS_GRAD);
     size_t bytes = (size_t)NB * H * W * out.Cp * 2;
     for (int i = 0; i < ns; i++) { out.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!out.p[i]) return SEERA_E_OOM; }
     const bool by_window = gp && (yp || act == SEERA_ACT_NONE);
@@ -833,13 +831,13 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
                                       : 4.0 * NB * C * ((g ? (double)P : 2.0 * (P / 4)) + (act ? (double)P : 0.0));
     ProfBytes pb(in_bytes + (double)ns * bytes, by_window ? "dz_shadow_window" : "dz_shadow");
     if (by_window) {
-        if (ns == 1) dz_shadow_window_kernel<1><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
-        else if (ns == 2) dz_shadow_window_kernel<2><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
-        else dz_shadow_window_kernel<3><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+        if (ns == 1) dz_shadow_window_kernel<1><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
+        else if (ns == 2) dz_shadow_window_kernel<2><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
+        else dz_shadow_window_kernel<3><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
     } else
-    if (ns == 1) dz_shadow_kernel<1><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
-    else if (ns == 2) dz_shadow_kernel<2><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
-    else dz_shadow_kernel<3><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial);
+    if (ns == 1) dz_shadow_kernel<1><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
+    else if (ns == 2) dz_shadow_kernel<2><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
+    else dz_shadow_kernel<3><<<grid, 256, 0, st>>>(g, gp, mask, y, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess && dbias) {
@@ -927,7 +925,7 @@ int seera_tma_convT_bias_act_fwd(const float *X, const float *Wt, const float *b
     int ns = precision_copies();
     NhwcShadow xs; Shadow wd;
     int taps = KH * KW;
-    int s = make_nhwc(X, NB, Cin, H, W, ns, xs);
+    int s = make_nhwc(X, NB, Cin, H, W, ns, xs, CLS_ACT);
     if (!s && unit) {
         s = make_weight_shadow(Wt, Cout, Cin, taps, taps, (long long)Cout * taps, 1, ns, wd);
         if (!s) s = tma_fprop(xs, wd, out, Cout, KH, KW, 1, 1, KH - 1 - ph, KW - 1 - pw, Ho, Wo, ns, "cuda_conv2DTranpose_fwd", bias, act);
@@ -957,13 +955,13 @@ int seera_tma_convT_bwd(const float *Wt, const float *X, const float *dY, float 
     int ns = precision_copies();
     int taps = KH * KW;
     NhwcShadow dys, xs; Shadow wk;
-    int s = make_nhwc(dY, NB, Cout, Ho, Wo, ns, dys);
+    int s = make_nhwc(dY, NB, Cout, Ho, Wo, ns, dys, CLS_GRAD);
     if (!s && dX) {      // dX[NB,Cin,H,W] = convolution of dY with Wt read as [F = Cin][C = Cout][KH][KW]
         s = make_weight_shadow(Wt, Cin, Cout, taps, (long long)Cout * taps, taps, 0, ns, wk);
         if (!s) s = tma_fprop(dys, wk, dX, Cin, KH, KW, sh, sw, ph, pw, H, W, ns, "cuda_conv2DTranspose_bwd(dX)");
     }
     if (!s && dW) {      // dW[Cin][Cout][KH][KW]: weight gradient of that convolution with dY as its input and X as its output gradient
-        s = make_nhwc(X, NB, Cin, H, W, ns, xs);
+        s = make_nhwc(X, NB, Cin, H, W, ns, xs, CLS_ACT);
         if (!s) s = tma_wgrad(dys, xs, dW, KH, KW, sh, sw, ph, pw, ns, "cuda_conv2DTranspose_bwd(dW)");
     }
     free_nhwc(dys); free_nhwc(xs); free_shadow(wk);

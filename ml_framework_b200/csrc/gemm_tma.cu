@@ -35,8 +35,8 @@ int seera_tma_matmul_bias_act(const float *A, const float *B, const float *bias,
     if (rows > 0x7fffffff) return fail(SEERA_E_LIMIT, "cuda_matmul: batch*M too large");
     int ns = precision_copies();
     Shadow sa, sb;
-    int s = make_shadow(A, (int)rows, K, ns, sa);
-    if (!s) s = make_shadow(B, K, N, ns, sb);
+    int s = make_shadow(A, (int)rows, K, ns, sa, CLS_ACT);
+    if (!s) s = make_shadow(B, K, N, ns, sb, CLS_WEIGHT);
     if (!s) s = run_tma_gemm(sa, 0, sb, 1, StoreDense{C, N}, (int)rows, N, K, true, "cuda_matmul", bias, act);
     free_shadow(sa); free_shadow(sb);
     return s;
@@ -49,13 +49,13 @@ int seera_tma_matmul_bwd(const float *A, const float *B, const float *dC, float 
     if (rows > 0x7fffffff) return fail(SEERA_E_LIMIT, "cuda_matmul_bwd: batch*M too large");
     int ns = precision_copies();
     Shadow sd, sa, sb;
-    int s = make_shadow(dC, (int)rows, N, ns, sd);
+    int s = make_shadow(dC, (int)rows, N, ns, sd, CLS_GRAD);
     if (!s && dA) {      // dA[rows,K] = dC[rows,N] * B[K,N]^T : contraction over N, both operands read along their rows
-        s = make_shadow(B, K, N, ns, sb);
+        s = make_shadow(B, K, N, ns, sb, CLS_WEIGHT);
         if (!s) s = run_tma_gemm(sd, 0, sb, 0, StoreDense{dA, K}, (int)rows, K, N, true, "cuda_matmul_bwd(dA)");
     }
     if (!s && dB) {      // dB[K,N] = A[rows,K]^T * dC[rows,N] : contraction over rows, both operands read along their columns
-        s = make_shadow(A, (int)rows, K, ns, sa);
+        s = make_shadow(A, (int)rows, K, ns, sa, CLS_ACT);
         if (!s) s = run_tma_gemm(sa, 1, sd, 1, StoreDense{dB, N}, K, N, (int)rows, true, "cuda_matmul_bwd(dB)");
     }
     free_shadow(sd); free_shadow(sa); free_shadow(sb);

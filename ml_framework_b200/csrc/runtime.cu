@@ -232,7 +232,7 @@ int seera_profile_report(char *buf, size_t size) {
 }
 
 int seera_set_precision(int mode) {
-    if (mode < 0 || mode > 3) return fail(SEERA_E_ARG, "seera_set_precision: mode %d", mode);
+    if (mode < 0 || mode > 4) return fail(SEERA_E_ARG, "seera_set_precision: mode %d", mode);
     rt().precision = mode;
     return SEERA_OK;
 }

@@ -26,7 +26,7 @@ template <class CS>
 __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, int col_base, int c_begin, int c_end,
                                                   int M, int N, const CS &cs, float *partial, long long partial_off,
                                                   float *stage /* EPI_WARP_SMEM bytes, this warp's own */,
-                                                  const float *bias = nullptr, int act = 0) {
+                                                  const float *bias = nullptr, int act = 0, float scale = 1.f) {
     const int lane = threadIdx.x & 31;
     const bool transpose = partial != nullptr || !CS::kMContiguous;
     const long long sn = cs.nstride();
@@ -36,6 +36,10 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, 
     for (int c = c_begin; c < c_end; c += 32) {
         float v[32];
         tmem_ld32(taddr + (uint32_t)(c - c_begin), v);
+        if (scale != 1.f && !partial) {            // operand copies carried power-of-two factors: take them out (exact)
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] *= scale;
+        }
         const bool fuse = !partial && (bias || act);
         if (!transpose) {
             if (fuse) {            // lanes hold rows here: the 32 column biases go through this warp's staging buffer
@@ -114,6 +118,7 @@ struct PoolOut {
     int *mask;                     // same shape
     __nv_bfloat16 *copy[3];        // [NB, (OH/2)*(OW/2), Cp] or null
     int ns, Cp;
+    Enc enc;                       // encoding of the copies
     int P, OW;                     // pixels per image and width of y
     int window_major;
     FastDiv by_P, by_OW, by_Pq;    // set by pool_out_geometry
@@ -124,7 +129,7 @@ inline void pool_out_geometry(PoolOut &po, int P, int OW, int window_major) {
 }
 
 __device__ __forceinline__ void drain_accumulator_pooled(uint32_t taddr, int row_base, int col_base, int ncols, int M, int N,
-                                                         const float *bias, int act, const PoolOut &po, float *stage) {
+                                                         const float *bias, int act, const PoolOut &po, float *stage, float scale = 1.f) {
     // The warp's 32 rows hold exactly 8 windows.  Each 32-column chunk gets bias + activation while lanes still hold rows,
     // then goes through the warp's 32 x 33 staging buffer so that lanes hold COLUMNS (filters): a lane reads the four
     // values of a window from shared memory (no shuffles), and the 8 windows of its filter are 8 consecutive floats of the
@@ -157,6 +162,10 @@ __device__ __forceinline__ void drain_accumulator_pooled(uint32_t taddr, int row
     for (int c = 0; c < ncols; c += 32) {
         float v[32];
         tmem_ld32(taddr + (uint32_t)c, v);
+        if (scale != 1.f) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] *= scale;
+        }
         const int n = col_base + c + lane;                          // this lane's filter once lanes hold columns
         __syncwarp();
         stage[lane] = (bias && n < N) ? __ldg(bias + n) : 0.f;
@@ -220,14 +229,7 @@ __device__ __forceinline__ void drain_accumulator_pooled(uint32_t taddr, int row
                 if (row_base + r0[w] >= M) continue;
                 float r = n < N ? mx[w] : 0.f;
                 const long long o = ((long long)wimg[w] * Pq + wrem[w]) * po.Cp + n;
-                const __nv_bfloat16 h0 = __float2bfloat16_rn(r);
-                po.copy[0][o] = h0;
-                if (po.ns >= 2) {
-                    r -= __bfloat162float(h0);
-                    const __nv_bfloat16 h1 = __float2bfloat16_rn(r);
-                    po.copy[1][o] = h1;
-                    if (po.ns >= 3) { r -= __bfloat162float(h1); po.copy[2][o] = __float2bfloat16_rn(r); }
-                }
+                store_split1(r, po.ns, po.enc, po.copy[0] + o, po.copy[1] + o, po.copy[2] + o);
             }
         }
     }

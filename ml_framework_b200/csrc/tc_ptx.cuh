@@ -2,6 +2,7 @@
 // tcgen05.mma / commit / ld, shared-memory matrix descriptors and the instruction descriptor.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cstdint>
 
 namespace seera {
@@ -107,6 +108,10 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
 __device__ __forceinline__ uint32_t umma_idesc_bf16(int bn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
 }
+// The same with the operand formats chosen: field value 1 = bf16, 0 = fp16 (bits 7-9 for A, 10-12 for B).
+__device__ __forceinline__ uint32_t umma_idesc_16bit(int bn, int a_fp16, int b_fp16) {
+    return (1u << 4) | ((a_fp16 ? 0u : 1u) << 7) | ((b_fp16 ? 0u : 1u) << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -115,6 +120,24 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t packed, int odd) {
     return __uint_as_float(odd ? (packed & 0xFFFF0000u) : (packed << 16));
+}
+// How a tensor's 16-bit operand copies are encoded.  fmt 0: bf16 (fp32's exponent range, 8-bit mantissa).  fmt 1: fp16
+// (11-bit mantissa, so a two-copy split carries 22 bits and three products give an fp32-class result where bf16 needs six)
+// with the values multiplied by `scale`, a power of two chosen per class of tensor so that the SECOND copy - 2^-11 of the
+// first - stays in fp16's normal range for the values that matter; conversion saturates instead of producing infinities.
+// The product's epilogue multiplies by 1 / (scale_a * scale_b), which is exact.
+struct Enc {
+    int fmt;
+    float scale;
+};
+
+__device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ float f16_bits_to_float(uint32_t packed, int odd) {
+    return __half2float(__ushort_as_half((unsigned short)(odd ? (packed >> 16) : (packed & 0xFFFFu))));
 }
 // Rounds 8 values to bf16 and returns them as one 16-byte chunk; `v` is replaced by the residuals, so calling it again
 // yields the next copy of a split (hi, then mid, then lo).
@@ -125,6 +148,50 @@ __device__ __forceinline__ uint4 split_chunk(float *v) {
 #pragma unroll
     for (int i = 0; i < 8; i++) v[i] -= bf16_bits_to_float(w[i >> 1], i & 1);
     return h;
+}
+__device__ __forceinline__ uint4 split_chunk_f16(float *v) {
+    uint4 h;
+    h.x = pack_f16x2_sat(v[0], v[1]); h.y = pack_f16x2_sat(v[2], v[3]); h.z = pack_f16x2_sat(v[4], v[5]); h.w = pack_f16x2_sat(v[6], v[7]);
+    const uint32_t w[4] = {h.x, h.y, h.z, h.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] -= f16_bits_to_float(w[i >> 1], i & 1);
+    return h;
+}
+// Writes the NS copies of 8 consecutive values (16-byte chunks at d0, d1, d2) in the encoding `e`; v is consumed.
+template <int NS>
+__device__ __forceinline__ void store_split8(float *v, const Enc &e, void *d0, void *d1, void *d2) {
+    if (e.fmt) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] *= e.scale;
+        *reinterpret_cast<uint4 *>(d0) = split_chunk_f16(v);
+        if (NS >= 2) *reinterpret_cast<uint4 *>(d1) = split_chunk_f16(v);
+        if (NS >= 3) *reinterpret_cast<uint4 *>(d2) = split_chunk_f16(v);
+    } else {
+        *reinterpret_cast<uint4 *>(d0) = split_chunk(v);
+        if (NS >= 2) *reinterpret_cast<uint4 *>(d1) = split_chunk(v);
+        if (NS >= 3) *reinterpret_cast<uint4 *>(d2) = split_chunk(v);
+    }
+}
+// The same for one value (ns known at run time).
+__device__ __forceinline__ void store_split1(float v, int ns, const Enc &e, __nv_bfloat16 *d0, __nv_bfloat16 *d1, __nv_bfloat16 *d2) {
+    unsigned short *u0 = reinterpret_cast<unsigned short *>(d0), *u1 = reinterpret_cast<unsigned short *>(d1),
+                   *u2 = reinterpret_cast<unsigned short *>(d2);
+    if (e.fmt) {
+        v *= e.scale;
+        uint32_t p = pack_f16x2_sat(v, 0.f);
+        *u0 = (unsigned short)p;
+        if (ns >= 2) {
+            v -= f16_bits_to_float(p, 0); p = pack_f16x2_sat(v, 0.f); *u1 = (unsigned short)p;
+            if (ns >= 3) { v -= f16_bits_to_float(p, 0); *u2 = (unsigned short)pack_f16x2_sat(v, 0.f); }
+        }
+    } else {
+        __nv_bfloat16 h = __float2bfloat16_rn(v);
+        *d0 = h;
+        if (ns >= 2) {
+            v -= __bfloat162float(h); h = __float2bfloat16_rn(v); *d1 = h;
+            if (ns >= 3) { v -= __bfloat162float(h); *d2 = __float2bfloat16_rn(v); }
+        }
+    }
 }
 
 }  // namespace seera

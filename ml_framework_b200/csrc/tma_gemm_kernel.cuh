@@ -50,14 +50,22 @@ inline int make_map_2d(CUtensorMap *m, const void *base, int rows, int cols, int
 // ---- fp32 -> bf16 shadows -----------------------------------------------------------------------------------
 // NS = 1: hi = bf16(x).  NS = 2: plus lo = bf16(x - hi).  NS = 3: plus lo2 = bf16(x - hi - lo) (24 mantissa bits).
 struct Shadow {
-    __nv_bfloat16 *p[3] = {nullptr, nullptr, nullptr};
+    __nv_bfloat16 *p[3] = {nullptr, nullptr, nullptr};      // 16-bit containers: bf16 or fp16 by `enc`
     int rows = 0, cols = 0, ld = 0;
+    Enc enc{0, 1.f};
 };
+
+// Classes of tensor, for the scale of an fp16 encoding: activations are O(1) after He / Glorot initialisation, weights a
+// few hundredths, gradients of a batch-mean loss 1e-6 .. 1e-2.  With the factors 2^4 / 2^8 / 2^12 the second copy of a
+// value stays a normal fp16 number down to a magnitude of 2^-7 / 2^-11 / 2^-15 (below that its absolute error is
+// 2^-29 / 2^-33 / 2^-37, far under the products' own rounding); values saturate at 4094 / 255.9 / 15.99 - data beyond
+// that belongs in the bf16 modes 2 and 3, which keep fp32's exponent range.
+enum { CLS_ACT = 0, CLS_WEIGHT = 1, CLS_GRAD = 2 };
 
 template <int NS>
 __global__ void __launch_bounds__(256) shadow_rows_kernel(const float *__restrict__ src, long long src_ld, int rows, int cols,
                                                           __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
-                                                          __nv_bfloat16 *__restrict__ d2, int ld) {
+                                                          __nv_bfloat16 *__restrict__ d2, int ld, Enc enc) {
     // one thread per 8 consecutive elements of a row; ld is a multiple of 8 so the 16-byte stores are aligned
     long long groups_per_row = ld >> 3, total = (long long)rows * groups_per_row;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
@@ -73,13 +81,17 @@ __global__ void __launch_bounds__(256) shadow_rows_kernel(const float *__restric
             for (int i = 0; i < 8; i++) v[i] = (c0 + i < cols) ? __ldg(s + i) : 0.f;
         }
         long long o = (long long)r * ld + c0;
-        *reinterpret_cast<uint4 *>(d0 + o) = split_chunk(v);
-        if (NS >= 2) *reinterpret_cast<uint4 *>(d1 + o) = split_chunk(v);
-        if (NS >= 3) *reinterpret_cast<uint4 *>(d2 + o) = split_chunk(v);
+        store_split8<NS>(v, enc, d0 + o, d1 + o, d2 + o);
     }
 }
 
-inline int precision_copies() { int m = rt().precision; return m < 1 ? 1 : (m > 3 ? 3 : m); }
+// Precision modes 1 / 2 / 3: one, two, three bf16 copies (1, 3, 6 products).  Mode 4: two fp16 copies (3 products).
+inline int precision_copies() { int m = rt().precision; return m == 4 ? 2 : (m < 1 ? 1 : (m > 3 ? 3 : m)); }
+inline Enc enc_for(int cls) {
+    if (rt().precision != 4) return Enc{0, 1.f};
+    static const float scale[3] = {16.f, 256.f, 4096.f};
+    return Enc{1, scale[cls]};
+}
 
 inline int alloc_shadow(Shadow &s, int rows, int cols, int ns) {
     s.rows = rows; s.cols = cols; s.ld = (cols + 7) / 8 * 8;
@@ -93,15 +105,16 @@ inline void free_shadow(Shadow &s) {
     for (int i = 0; i < 3; i++) { if (s.p[i]) scratch_free(s.p[i]); s.p[i] = nullptr; }
 }
 // Row-major fp32 [rows, cols] -> bf16 shadows of the same layout (pitch rounded up to 8 elements).
-inline int make_shadow(const float *src, int rows, int cols, int ns, Shadow &s) {
+inline int make_shadow(const float *src, int rows, int cols, int ns, Shadow &s, int cls) {
     if (int e = alloc_shadow(s, rows, cols, ns)) return e;
+    s.enc = enc_for(cls);
     long long groups = (long long)rows * (s.ld / 8);
     int grid = stride_grid(groups);
     cudaStream_t st = rt().stream;
     ProfBytes pb(4.0 * rows * cols + 2.0 * ns * rows * s.ld, "shadow_rows");
-    if (ns == 1) shadow_rows_kernel<1><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
-    else if (ns == 2) shadow_rows_kernel<2><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
-    else shadow_rows_kernel<3><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld);
+    if (ns == 1) shadow_rows_kernel<1><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc);
+    else if (ns == 2) shadow_rows_kernel<2><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc);
+    else shadow_rows_kernel<3><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc);
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, "shadow_rows");
@@ -156,6 +169,8 @@ struct TmaGemmParams {
     int cpad, cchunks;       // channel pitch of the weight rows / channels rounded up to 64, in chunks of 64
     float *partial;
     int *status;
+    float out_scale;         // the accumulator is multiplied by this before bias / activation / store: 1 / (scale_a * scale_b)
+    int a_fp16, b_fp16;      // operand formats: 0 bf16, 1 fp16
     const float *bias;       // per-column bias added before the store, or null
     int act;                 // activation applied before the store (0 = none)
     int pool_on;             // 1: rows are pixels of a layer output that is only consumed through a 2x2 max-pool: store that instead
@@ -298,7 +313,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         }
     } else if (warp == 1 && lane == 0) {
         // ---------------- MMA issuer ----------------
-        const uint32_t idesc = umma_idesc_bf16(bn) | ((uint32_t)(a_mn ? 1 : 0) << 15) | ((uint32_t)p.b_mn << 16);
+        const uint32_t idesc = umma_idesc_16bit(bn, p.a_fp16, p.b_fp16) | ((uint32_t)(a_mn ? 1 : 0) << 15) | ((uint32_t)p.b_mn << 16);
         const uint32_t a_step = a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;   // bytes per K=16 slice
         // split products kept: hi*hi | + hi*lo, lo*hi | + hi*lo2, lo2*hi, lo*lo
         constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
@@ -360,10 +375,10 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             tc_fence_after();
             if (p.pool_on)
                 drain_accumulator_pooled(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, bn, p.M, p.N,
-                                         p.bias, p.act, p.pool, stage);
+                                         p.bias, p.act, p.pool, stage, p.out_scale);
             else
                 drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, 0, bn, p.M, p.N, cs,
-                                  p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act);
+                                  p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act, p.out_scale);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
@@ -376,12 +391,13 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
 
 template <class CS>
 __global__ void __launch_bounds__(256) tma_splitk_reduce_kernel(const float *__restrict__ partial, CS cs, int M, int N, int splits,
-                                                                const float *__restrict__ bias, int act) {
+                                                                const float *__restrict__ bias, int act, float scale) {
     long long total = (long long)M * N;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
     for (long long i = tid; i < total; i += nthr) {
         float s = 0.f;
         for (int z = 0; z < splits; z++) s += partial[(long long)z * total + i];
+        s *= scale;
         const int n = (int)(i % N);
         if (bias) s += __ldg(bias + n);
         cs((int)(i / N), n, epilogue_act(s, act));
@@ -473,7 +489,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
 #undef SEERA_TMA_LAUNCH
     count_launch();
     if (e == cudaSuccess && p.partial) {
-        tma_splitk_reduce_kernel<<<stride_grid((long long)p.M * p.N), 256, 0, st>>>(p.partial, cs, p.M, p.N, splits, p.bias, p.act);
+        tma_splitk_reduce_kernel<<<stride_grid((long long)p.M * p.N), 256, 0, st>>>(p.partial, cs, p.M, p.N, splits, p.bias, p.act, p.out_scale);
         count_launch();
         e = cudaGetLastError();
     }
@@ -491,6 +507,7 @@ int run_tma_gemm(const Shadow &sa, int a_mn, const Shadow &sb, int b_mn, const C
     TmaGemmParams p{};
     p.bias = bias; p.act = act;
     p.M = M; p.N = N; p.K = K; p.a_mode = a_mn ? TMA_A_COLS : TMA_A_ROWS; p.b_mn = b_mn;
+    p.a_fp16 = sa.enc.fmt; p.b_fp16 = sb.enc.fmt; p.out_scale = 1.f / (sa.enc.scale * sb.enc.scale);
     p.bn = tma_pick_bn(N, ns, b_mn);
     TmaMaps maps;
     for (int i = 0; i < 3; i++) {

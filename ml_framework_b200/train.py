@@ -16,7 +16,8 @@ from .cuTen import cuten
 # slope and max-pool argmax, and a decision that differs from the reference's changes a gradient entry by O(1) - with
 # forward values rounded to bf16 (2^-9) a few per mille of them would.  The backward products only add their own rounding:
 # two-way split for the fp32 configurations, ONE bf16 pass for the bf16 configuration (its subject: dA = dC B^T, dB = A^T dC).
-POLICY = {"fp32": (3, 2), "bf16": (3, 1)}
+# Mode 4 is the two-way fp16 split: three products with the accuracy the three-way bf16 split (mode 3) needs six for.
+POLICY = {"fp32": (4, 4), "bf16": (4, 1)}
 
 
 def policy_for(work):

@@ -3,7 +3,11 @@
 Mode 1 (bf16 operands, fp32 accumulate) is compared with the CPU oracle fed the SAME bf16-rounded
 operands ("matched quantisation": products of bf16 values are exact in fp32, so only the summation
 order differs): rel-L2 <= 1e-5.  Mode 2 (bf16x3 split) is compared with the untouched fp32 oracle:
-rel-L2 <= 2e-5 (observed ~5e-6), far inside the 2e-3 gate of the training configurations."""
+rel-L2 <= 2e-5 (observed ~5e-6), far inside the 2e-3 gate of the training configurations.  Mode 4 (fp16x3 split with
+power-of-two scales) likewise against the fp32 oracle: rel-L2 <= 1e-5.  Its arithmetic would allow 7e-8 (the dropped lo*lo
+term is 2^-22 of a product); observed on N(0,1) operands is 1e-7 for short contractions and 3.7e-6 at K = 1024 in one
+accumulation chain - the tensor core keeps fewer low-order bits of a 22-bit fp16 product than of a 16-bit bf16 product when
+it aligns the addends, and that truncation adds up along the chain."""
 import numpy as np
 import pytest
 
@@ -15,7 +19,7 @@ import cases
 
 pytestmark = pytest.mark.gpu
 
-TOL = {1: 1e-5, 2: 2e-5}
+TOL = {1: 1e-5, 2: 2e-5, 4: 1e-5}
 
 
 @pytest.fixture(scope="module")
@@ -38,7 +42,7 @@ def _prep(mode, *arrays):
 MATMUL = [(1, 3, 2), (5, 7, 3), (128, 64, 32), (129, 65, 33), (64, 784, 10), (300, 10, 1024), (257, 1000, 255), (4096, 1024, 1024)]
 
 
-@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mode", [1, 2, 4])
 @pytest.mark.parametrize("M,K,N", MATMUL)
 def test_matmul_and_backward(E, mode, M, K, N):
     rs = np.random.RandomState(M + K + N)
@@ -56,7 +60,7 @@ CONV = [(1, 1, 5, 5, 1, 3, 3, 1, 1, 0, 0), (2, 3, 8, 8, 4, 3, 3, 1, 1, 1, 1), (3
         (2, 3, 9, 9, 4, 1, 1, 2, 2, 0, 0), (2, 8, 32, 32, 8, 3, 3, 2, 2, 0, 0), (2, 16, 15, 17, 12, 4, 4, 3, 2, 2, 1)]
 
 
-@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mode", [1, 2, 4])
 @pytest.mark.parametrize("shape", CONV)
 def test_conv2d(E, mode, shape):
     N, C, H, W, F, KH, KW, sh, sw, ph, pw = shape
@@ -88,7 +92,7 @@ CONVT = [(1, 1, 4, 4, 1, 3, 3, 1, 1, 0, 0), (2, 4, 5, 6, 3, 4, 3, 2, 2, 1, 0), (
          (2, 4, 5, 5, 3, 2, 2, 3, 3, 0, 0), (16, 128, 8, 8, 64, 4, 4, 2, 2, 1, 1)]
 
 
-@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mode", [1, 2, 4])
 @pytest.mark.parametrize("shape", CONVT)
 def test_conv_transpose2d(E, mode, shape):
     N, Ci, H, W, Co, KH, KW, sh, sw, ph, pw = shape
