@@ -326,7 +326,7 @@ def run_gpu(args, work):
         ms = _median(times)
         # keep the device busy for about a second so the 200 ms clock sampler sees it under load; the count is
         # derived from the rank-reduced time, so every rank runs the same number of extra steps
-        extra = int(min(5000, max(0.0, 1000.0 - sum(times)) / max(ms / args.steps, 1e-3)))
+        extra = 0 if args.no_clock_fill else int(min(5000, max(0.0, 1000.0 - sum(times)) / max(ms / args.steps, 1e-3)))
         for i in range(extra):
             run_step(i)
         sc.stream_synchronize()
@@ -528,6 +528,9 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="N > 1: weak = the configuration's batch on every GPU; strong = that batch split over the GPUs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-clock-fill", action="store_true",
+                    help="do not keep the device busy for a second after the timed regions (the clock sampler then sees few samples); "
+                         "for runs under a profiler")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel eagerly instead of replaying a captured step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

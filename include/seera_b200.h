@@ -94,6 +94,12 @@ int         seera_get_precision(void);
  *   "pool_short_patch" (default 0): let seera_conv2d_bias_act_pool_fwd_s also serve short-patch convolutions
  *       (C*R*S <= 64).  Correct, but that kernel is bound by its epilogue warps and runs slower with the pool folded in
  *       than followed by a separate pool.
+ *   "tc_wait_ms" (1..60000, default 2000; also SEERA_TC_WAIT_MS): budget of every wait inside the TMA-fed tensor-core
+ *       kernel, in milliseconds at ~2 GHz.  A wait that runs out makes the kernel record its code in the status word
+ *       (seera_tc_device_status), let the copies already in flight land (bounded), free its TMEM and return.
+ *   "tc_test_skip_load" (k-step index, -1 off): TEST HOOK for that path.  The next TMA-fed launch's first CTA leaves out
+ *       the loads of that k-step, so the MMA issuer's wait for the stage runs out.  Nothing faults, traps or spins
+ *       without a bound; the result of that one launch is garbage and the status word reads 2.  Clears itself.
  *   "tile_n_cap2" / "tile_n_cap3" (64, 128 or 256; defaults 128 / 128): widest accumulator tile used with two /
  *       three bf16 copies per operand; wider tiles raise the arithmetic per byte loaded but leave fewer stages. */
 int         seera_set_option(const char *name, int value);

@@ -13,7 +13,9 @@ struct Runtime {
     int sm_physical = 148;
     cudaStream_t stream = nullptr;      // the stream every kernel is enqueued on
     cudaStream_t own_stream = nullptr;
-    int precision = 0;
+    int precision = 0;                  // set from SEERA_PRECISION (default 3) when the runtime is created
+    unsigned long long tc_wait_clocks = 4000000000ull;      // budget of a bounded wait inside a tensor-core kernel (~2 s)
+    int tc_test_skip_load = -1;         // test hook ("tc_test_skip_load" option): see TmaGemmParams::skip_load
     bool dense_tma = true;              // Dense GEMMs in modes 1/2: TMA-fed kernel (false: in-kernel conversion kernel)
     int tile_n_cap2 = 128;              // widest accumulator tile with two operand copies per stage (bf16x3)
     int tile_n_cap3 = 128;              // ... with three (bf16x6)

@@ -17,6 +17,12 @@ int seera_set_option(const char *name, int value) {
     if (!name) return fail(SEERA_E_ARG, "set_option: null name");
     if (!strcmp(name, "dense_tma")) { rt().dense_tma = value != 0; return SEERA_OK; }
     if (!strcmp(name, "conv_tma")) { rt().conv_tma = value != 0; return SEERA_OK; }
+    if (!strcmp(name, "tc_wait_ms")) {
+        if (value < 1 || value > 60000) return fail(SEERA_E_ARG, "set_option: tc_wait_ms must be in [1, 60000]");
+        rt().tc_wait_clocks = (unsigned long long)value * 2000000ull;
+        return SEERA_OK;
+    }
+    if (!strcmp(name, "tc_test_skip_load")) { rt().tc_test_skip_load = value; return SEERA_OK; }
     if (!strcmp(name, "pool_short_patch")) { rt().pool_short_patch = value != 0; return SEERA_OK; }
     if (!strcmp(name, "sm_reserve")) {
         if (value < 0 || value >= rt().sm_physical) return fail(SEERA_E_ARG, "set_option: sm_reserve must be in [0, %d)", rt().sm_physical);

@@ -8,6 +8,7 @@
 // by the next allocation without waiting: every kernel that still reads it was enqueued earlier.
 #include "common.cuh"
 #include <cstdarg>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <map>
@@ -16,7 +17,26 @@
 
 namespace seera {
 
-Runtime &rt() { static Runtime r; return r; }
+// Configuration by environment, read once when the library is first used:
+//   SEERA_PRECISION   0..4   initial precision mode of the contractions (default 3: bf16x6 on the tensor cores - fp32-class
+//                            products over fp32's whole exponent range, so that a caller who never heard of
+//                            seera_set_precision still runs on tcgen05 kernels and still matches the fp32 reference)
+//   SEERA_SM_RESERVE  n      SMs the persistent kernels leave free (the "sm_reserve" option)
+//   SEERA_TC_WAIT_MS  n      budget of the bounded waits inside the tensor-core kernels, in milliseconds (default 2000)
+static Runtime make_runtime() {
+    Runtime r;
+    r.precision = 3;
+    if (const char *e = getenv("SEERA_PRECISION")) {
+        int m = atoi(e);
+        if (m >= 0 && m <= 4 && e[0] >= '0' && e[0] <= '4') r.precision = m;
+    }
+    if (const char *e = getenv("SEERA_TC_WAIT_MS")) {
+        long long ms = atoll(e);
+        if (ms > 0) r.tc_wait_clocks = (unsigned long long)ms * 2000000ull;      // ~2e6 clocks per millisecond
+    }
+    return r;
+}
+Runtime &rt() { static Runtime r = make_runtime(); return r; }
 
 int fail(int code, const char *fmt, ...) {
     Runtime &r = rt();
@@ -143,6 +163,10 @@ int seera_init(int device) {
         if (int s = check_cuda(cudaStreamCreateWithFlags(&r.own_stream, cudaStreamNonBlocking), "cudaStreamCreate")) return s;
     r.stream = r.own_stream;
     r.device = device;
+    if (const char *e = getenv("SEERA_SM_RESERVE")) {
+        int n = atoi(e);
+        if (n > 0 && n < r.sm_physical) r.sm_count = r.sm_physical - n;
+    }
     return SEERA_OK;
 }
 

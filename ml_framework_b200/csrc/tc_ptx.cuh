@@ -44,13 +44,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the budget ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+// Bounded wait: false when the budget (in clocks) ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                          unsigned long long budget = TC_WAIT_CLOCKS) {
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
         if (*abort_flag) return false;
-        if (clock64() - t0 > TC_WAIT_CLOCKS) {
+        if (clock64() - t0 > budget) {
             *abort_flag = 1;
             if (status) atomicCAS(status, 0, code);
             return false;

@@ -169,6 +169,9 @@ struct TmaGemmParams {
     int cpad, cchunks;       // channel pitch of the weight rows / channels rounded up to 64, in chunks of 64
     float *partial;
     int *status;
+    unsigned long long wait_clocks;   // budget of every bounded wait in the kernel
+    int skip_load;           // test hook: the producer of CTA 0 leaves out the loads of this k-step (-1: none), so that the
+                             // waits downstream of it run out and the kernel has to report and unwind
     float out_scale;         // the accumulator is multiplied by this before bias / activation / store: 1 / (scale_a * scale_b)
     int a_fp16, b_fp16;      // operand formats: 0 bf16, 1 fp16
     const float *bias;       // per-column bias added before the store, or null
@@ -266,9 +269,13 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
                 }
             }
             for (int kt = 0; kt < ktiles; kt++, it++) {
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, p.status, 1)) { alive = false; break; }
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, p.status, 1, p.wait_clocks)) { alive = false; break; }
                 int k0 = kbeg + kt * TC_BK;
                 uint32_t bar = full0 + 8 * s;
+                if (p.skip_load >= 0 && blockIdx.x == 0 && it == p.skip_load) {      // test hook: this stage never fills
+                    if (++s == stages) { s = 0; ph ^= 1u; }
+                    continue;
+                }
                 mbar_expect_tx(bar, tx_bytes);
                 int bk = k0;                                  // B's coordinate along the contraction
                 if (p.a_mode == TMA_A_ROWS) {
@@ -308,7 +315,8 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             issued_from = it - stages < 0 ? 0 : it - stages;
             for (int k = issued_from; k < it; k++) {
                 unsigned long long t0 = clock64();
-                while (!mbar_try_wait(full0 + 8 * (k % stages), (uint32_t)(k / stages) & 1u) && clock64() - t0 < TC_WAIT_CLOCKS) {}
+                if (p.skip_load >= 0 && blockIdx.x == 0 && k == p.skip_load) continue;      // nothing was issued for it
+                while (!mbar_try_wait(full0 + 8 * (k % stages), (uint32_t)(k / stages) & 1u) && clock64() - t0 < p.wait_clocks) {}
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -333,13 +341,13 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             tile_origin(id, m0, n0, kbeg, ktiles, z);
             const int buf = local & 1;
             // the epilogue must have drained this accumulator buffer (two tiles ago)
-            alive = mbar_wait(tempty0 + 8 * buf, (((uint32_t)local >> 1) & 1u) ^ 1u, abortp, p.status, 4);
+            alive = mbar_wait(tempty0 + 8 * buf, (((uint32_t)local >> 1) & 1u) ^ 1u, abortp, p.status, 4, p.wait_clocks);
             if (!alive) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
             uint32_t acc = 0;
             for (int kt = 0; kt < ktiles && alive; kt++) {
-                alive = mbar_wait(full0 + 8 * s, ph, abortp, p.status, 2);
+                alive = mbar_wait(full0 + 8 * s, ph, abortp, p.status, 2, p.wait_clocks);
                 if (!alive) break;
                 tc_fence_after();
                 const uint64_t das = da0 + (uint32_t)s * stage16, dbs = db0 + (uint32_t)s * stage16;
@@ -371,7 +379,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             int m0, n0, kbeg, ktiles, z;
             tile_origin(id, m0, n0, kbeg, ktiles, z);
             const int buf = local & 1;
-            if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)local >> 1) & 1u, abortp, p.status, 3)) break;
+            if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)local >> 1) & 1u, abortp, p.status, 3, p.wait_clocks)) break;
             tc_fence_after();
             if (p.pool_on)
                 drain_accumulator_pooled(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, bn, p.M, p.N,
@@ -460,6 +468,9 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
     p.by_mtiles = fast_div((p.M + TC_BM - 1) / TC_BM); p.by_ntiles = fast_div((p.N + p.bn - 1) / p.bn);
     p.by_OHW = fast_div(p.OHW); p.by_OW = fast_div(p.OW); p.by_S = fast_div(p.S); p.by_cchunks = fast_div(p.cchunks);
     p.status = tc_status_word();
+    p.wait_clocks = rt().tc_wait_clocks;
+    p.skip_load = rt().tc_test_skip_load;
+    rt().tc_test_skip_load = -1;                 // one launch only
     p.partial = nullptr;
     if (splits > 1) {
         p.partial = (float *)scratch_alloc((size_t)splits * p.M * p.N * sizeof(float));
