@@ -427,6 +427,7 @@ def run_gpu(args, work):
         dtype = {"0": "f32", "1": "bf16 (f32 accumulate)", "2": "bf16x3 (f32 accumulate)", "3": "bf16x6 (f32 accumulate)",
                  "4": "fp16x3 split products (two fp16 copies per operand, three products), f32 accumulate",
                  "4/1": "forward fp16x3 split products, backward one bf16 pass; f32 accumulate",
+                 "4/5": "forward fp16x3 split products (two fp16 copies, three products), backward one fp16 pass; f32 accumulate",
                  "3/2": "bf16 split products, f32 accumulate (forward 6-term, backward 3-term)"}.get(args.precision, args.precision)
         line = {"metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,

@@ -81,7 +81,11 @@ int         seera_profile_report(char *buf, size_t size);
  *     activations x 2^4 (saturate at 4094), weights x 2^8 (at 255.9), gradients x 2^12 (at 15.99); magnitudes
  *     down to 2^-7 / 2^-11 / 2^-15 keep all 22 bits, smaller ones an absolute error of 2^-29 / 2^-33 / 2^-37.
  *     Conversion saturates, it never produces infinities.  Data outside these ranges belongs in modes 2 / 3.
- *     Kernels that convert inside their producer warps (short patches, the gather fallback) run mode 4 as mode 2. */
+ *     Kernels that convert inside their producer warps (short patches, the gather fallback) run mode 4 as mode 2.
+ *   5 fp16: ONE fp16 copy per operand with the scales of mode 4, one product (11 mantissa bits per operand, 2^-12
+ *     rounding: eight times finer than mode 1).  It is the first copy of a mode-4 set, so a forward pass in mode 4
+ *     followed by a backward pass in mode 5 converts nothing twice.  Meant for backward products: they take no
+ *     decisions, so their rounding (2e-4 per contraction) stays a rounding.  Producer-warp kernels run it as mode 2. */
 int         seera_set_precision(int mode);
 int         seera_get_precision(void);
 /* Engine options by name.
@@ -94,6 +98,10 @@ int         seera_get_precision(void);
  *   "pool_short_patch" (default 0): let seera_conv2d_bias_act_pool_fwd_s also serve short-patch convolutions
  *       (C*R*S <= 64).  Correct, but that kernel is bound by its epilogue warps and runs slower with the pool folded in
  *       than followed by a separate pool.
+ *   "wgrad_single" (default 1): in precision mode 4 a weight gradient (conv dW, Dense dB) is formed from the FIRST fp16
+ *       copy of each operand alone - one product instead of three.  Its 2^-12 rounding stays inside that one tensor
+ *       (nothing downstream in the backward pass reads dW); measured on the VGG configuration it moves no dW error
+ *       by more than 3e-5.  Data gradients keep all three products: their rounding would compound layer by layer.
  *   "tc_wait_ms" (1..60000, default 2000; also SEERA_TC_WAIT_MS): budget of every wait inside the TMA-fed tensor-core
  *       kernel, in milliseconds at ~2 GHz.  A wait that runs out makes the kernel record its code in the status word
  *       (seera_tc_device_status), let the copies already in flight land (bounded), free its TMEM and return.
@@ -351,6 +359,18 @@ int seera_mae_fwd_bwd(const float *p, const float *y, float *partials, float *lo
                       int size, float inv_count);
 int seera_bce_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp,
                       int size, float inv_count, float eps);
+
+/* Dynamic factor of the fp16 gradient copies of precision modes 4 and 5.  Gradients have no fixed magnitude - they
+ * shrink by orders of magnitude as training converges - so a loss head calls this on the gradient it hands to the
+ * backward pass (n floats at g): two small launches find its largest |entry| and set a power-of-two factor, kept in
+ * device memory, under which that entry lands in [128, 256) after the static 2^12 of the gradient class.  Every
+ * gradient copy made until the next call uses it and every product's epilogue takes it out again (exactly).
+ * Stream-ordered and capturable; in the other modes the factor is never read.  Without any call it is 1.
+ * The entries that are handed an fp32 gradient tensor (seera_cuda_matmul_bwd, seera_cuda_conv2d_bwd,
+ * seera_cuda_conv2DTranspose_bwd) call it on that tensor themselves; a caller of the fused layer-backward entries
+ * (seera_conv2d_act_bwd with a pooled gradient) calls it once per backward pass on the loss gradient.
+ * No counterpart in the reference. */
+int seera_grad_scale_update(const float *g, long long n);
 
 /* Adam (Seera.py:1069-1084) and SGD with momentum (Seera.py:1006-1008) in one pass, in place.
  * The caller passes the fp32-rounded scalars omb1 = 1-beta1, omb2 = 1-beta2, c1 = 1-beta1^t,

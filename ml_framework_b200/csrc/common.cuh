@@ -21,6 +21,7 @@ struct Runtime {
     int tile_n_cap3 = 128;              // ... with three (bf16x6)
     bool pool_short_patch = false;      // fold a 2x2 max-pool into the tensor-core short-patch forward kernel too (its epilogue warps become the
                                         // bottleneck: off; 3 x 3 unit-stride layers fold it into the fp32 stencil kernel regardless)
+    bool wgrad_single = true;           // precision mode 4: weight gradients from the first fp16 copy of each operand alone
     bool conv_tma = true;               // convolutions in modes 1-3: TMA im2col kernel (false: in-kernel gather kernel)
     bool capturing = false;             // a stream capture (seera_graph_begin) is open
     bool tc_used = false;               // a tensor-core kernel ran since the status word was last read
@@ -71,6 +72,9 @@ struct ProfBytes {
     ProfBytes(double b, const char *t) : bytes(b), tag(t) { profile_begin(); }
     ~ProfBytes() { profile_end_bytes(bytes, tag); }
 };
+
+// Device float[2]: {dynamic factor of the fp16 gradient copies, its inverse}; both 1 until a loss head sets them (fused.cu).
+float *grad_scale_words();
 
 // Pool-backed scratch for internal use (split-K partials, operand shadows).
 void *scratch_alloc(size_t bytes);

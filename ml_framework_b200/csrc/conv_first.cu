@@ -791,7 +791,7 @@ static bool first_tc_wgrad_ok(const FirstGeom &g, bool want_bias) {
 
 static int first_tc_fwd(const float *X, const float *Wt, const float *bias, float *Y, const FirstGeom &g, int act, const char *name,
                         const PoolOut *pool = nullptr) {
-    const int ns = precision_copies();
+    const int ns = rt().precision == 5 ? 2 : precision_copies();   // these kernels split into bf16 themselves: the fp16 modes 4 and 5 run as bf16x3
     const int bn = g.F <= 32 ? 32 : (g.F <= 64 ? 64 : 128);
     const int nslices = (g.K + 15) / 16;
     const long long pixels = (long long)g.NB * g.OH * g.OW;
@@ -821,7 +821,7 @@ static int first_tc_fwd(const float *X, const float *Wt, const float *bias, floa
 }
 
 static int first_tc_wgrad(const float *X, const DzSource &src, float *dW, float *dbias, const FirstGeom &g, const char *name) {
-    const int ns = precision_copies();
+    const int ns = rt().precision == 5 ? 2 : precision_copies();   // these kernels split into bf16 themselves: the fp16 modes 4 and 5 run as bf16x3
     const long long pixels = (long long)g.NB * g.OH * g.OW;
     // pooled gradient with the pool's output at hand: steps of 16 pool windows, one producer group per stage
     const int by_window = (src.gp && (src.yp || src.act == SEERA_ACT_NONE)) ? 1 : 0;

@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(256) shadow_nhwc_kernel(const float *__restric
 struct NhwcShadow {
     __nv_bfloat16 *p[3] = {nullptr, nullptr, nullptr};
     int NB = 0, H = 0, W = 0, C = 0, Cp = 0;
-    Enc enc{0, 1.f};
+    Enc enc{0, 1.f, nullptr};
 };
 static void free_nhwc(NhwcShadow &s) {
     for (int i = 0; i < 3; i++) { if (s.p[i]) scratch_free(s.p[i]); s.p[i] = nullptr; }
@@ -117,6 +117,8 @@ static void free_nhwc(NhwcShadow &s) {
 static int make_nhwc(const float *src, int NB, int C, int H, int W, int ns, NhwcShadow &s, int cls) {
     s.NB = NB; s.H = H; s.W = W; s.C = C; s.Cp = (C + 7) / 8 * 8;
     s.enc = enc_for(cls);
+    if (s.enc.dscale)          // an fp32 gradient tensor handed in from outside: its own largest entry sets the dynamic factor
+        if (int e = seera_grad_scale_update(src, (long long)NB * C * H * W)) return e;
     size_t bytes = (size_t)NB * H * W * s.Cp * 2;
     for (int i = 0; i < ns; i++) { s.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!s.p[i]) return SEERA_E_OOM; }
     int P = H * W;
@@ -213,7 +215,7 @@ static int tma_fprop(const NhwcShadow &x, const Shadow &wk, float *Y, int F, int
     p.bias = bias; p.act = act;
     if (pool) { p.pool_on = 1; p.pool = *pool; pool_out_geometry(p.pool, OH * OW, OW, 0); }
     p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
-    p.a_fp16 = x.enc.fmt; p.b_fp16 = wk.enc.fmt; p.out_scale = 1.f / (x.enc.scale * wk.enc.scale);
+    p.a_fp16 = x.enc.fmt; p.b_fp16 = wk.enc.fmt; p.out_scale = 1.f / (x.enc.scale * wk.enc.scale); p.dinv = enc_dinv(x.enc, wk.enc);
     p.M = x.NB * OH * OW; p.N = F;
     p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
     p.K = p.taps * p.cchunks * 64;
@@ -235,7 +237,7 @@ static int tma_wgrad(const NhwcShadow &x, const NhwcShadow &dy, float *dW, int R
     const int OH = dy.H, OW = dy.W, F = dy.C;
     TmaGemmParams p{};
     p.a_mode = TMA_A_TAPS; p.b_mn = 1;
-    p.a_fp16 = x.enc.fmt; p.b_fp16 = dy.enc.fmt; p.out_scale = 1.f / (x.enc.scale * dy.enc.scale);
+    p.a_fp16 = x.enc.fmt; p.b_fp16 = dy.enc.fmt; p.out_scale = 1.f / (x.enc.scale * dy.enc.scale); p.dinv = enc_dinv(x.enc, dy.enc);
     p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
     p.M = p.taps * p.cchunks * 64; p.N = F;
     p.K = x.NB * OH * OW;
@@ -315,7 +317,7 @@ static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, 
             TmaGemmParams p{};
             p.bias = bias; p.act = act;
             p.a_mode = TMA_A_IM2COL; p.b_mn = 0;
-            p.a_fp16 = g.enc.fmt; p.b_fp16 = wk.enc.fmt; p.out_scale = 1.f / (g.enc.scale * wk.enc.scale);
+            p.a_fp16 = g.enc.fmt; p.b_fp16 = wk.enc.fmt; p.out_scale = 1.f / (g.enc.scale * wk.enc.scale); p.dinv = enc_dinv(g.enc, wk.enc);
             p.M = g.NB * y.G * x.G; p.N = Nch;
             p.cchunks = (g.Cp + 63) / 64; p.cpad = g.Cp; p.taps = taps; p.S = x.T;
             p.K = p.taps * p.cchunks * 64;
@@ -591,7 +593,7 @@ namespace seera {
 static const NhwcShadow *usable(const seera_shadow *h, int ns, int NB, int C, int H, int W, int cls) {
     const Enc want = enc_for(cls);            // copies made under another encoding (bf16 against fp16) cannot be mixed in
     if (!h || h->ns < ns || h->s.NB != NB || h->s.C != C || h->s.H != H || h->s.W != W || h->s.enc.fmt != want.fmt ||
-        h->s.enc.scale != want.scale) return nullptr;
+        h->s.enc.scale != want.scale || h->s.enc.dscale != want.dscale) return nullptr;
     return &h->s;
 }
 
@@ -632,7 +634,7 @@ static int tma_conv2d_bwd_kept(const float *Wt, const float *X, const float *dY,
             s = conv_first_wgrad(X, dY, dW, NB, C, H, W, F, R, S, sh, sw, ph, pw, "cuda_conv2d_bwd(dW)");
         } else {
             if (!xs) { s = make_nhwc(X, NB, C, H, W, ns, xs_local, CLS_ACT); xs = &xs_local; }
-            if (!s) s = tma_wgrad(*xs, *dys, dW, R, S, sh, sw, ph, pw, ns, "cuda_conv2d_bwd(dW)");
+            if (!s) s = tma_wgrad(*xs, *dys, dW, R, S, sh, sw, ph, pw, wgrad_copies(ns), "cuda_conv2d_bwd(dW)");
         }
     }
     free_nhwc(dys_local); free_nhwc(xs_local); free_shadow(wd);
@@ -962,7 +964,7 @@ int seera_tma_convT_bwd(const float *Wt, const float *X, const float *dY, float 
     }
     if (!s && dW) {      // dW[Cin][Cout][KH][KW]: weight gradient of that convolution with dY as its input and X as its output gradient
         s = make_nhwc(X, NB, Cin, H, W, ns, xs, CLS_ACT);
-        if (!s) s = tma_wgrad(dys, xs, dW, KH, KW, sh, sw, ph, pw, ns, "cuda_conv2DTranspose_bwd(dW)");
+        if (!s) s = tma_wgrad(dys, xs, dW, KH, KW, sh, sw, ph, pw, wgrad_copies(ns), "cuda_conv2DTranspose_bwd(dW)");
     }
     free_nhwc(dys); free_nhwc(xs); free_shadow(wk);
     return s;

@@ -336,6 +336,46 @@ __global__ void __launch_bounds__(256) sgd_kernel(float *__restrict__ w, const f
     sgd_range(w, g, vel, n, vec, lr, mu, gs);
 }
 
+// ---- dynamic factor of the fp16 gradient copies -------------------------------------------------------------------
+__global__ void grad_scale_reset_kernel(float *w) {
+    if (threadIdx.x == 0) { w[0] = 1.f; w[1] = 1.f; reinterpret_cast<unsigned *>(w)[2] = 0u; w[3] = 0.f; }
+}
+__global__ void __launch_bounds__(256) grad_amax_kernel(const float *__restrict__ g, long long n, unsigned *__restrict__ amax_bits) {
+    long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    float m = 0.f;
+    for (long long i = tid; i < n; i += nthr) {
+        const float a = fabsf(g[i]);
+        if (a < 3.0e38f) m = fmaxf(m, a);              // infinities and NaNs do not steer the scale
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax_bits, __float_as_uint(m));
+}
+// factor = 2^(-4 - e) with amax = m * 2^e, m in [0.5, 1): together with the static 2^12 of the gradient class the largest
+// entry of the loss gradient lands in [128, 256) - eight binades of headroom below fp16's maximum for gradients that grow
+// on the way down the network, twenty-one binades of normal range below it for those that shrink.
+__global__ void grad_scale_finalize_kernel(float *w) {
+    if (threadIdx.x != 0) return;
+    unsigned *bits = reinterpret_cast<unsigned *>(w) + 2;
+    const float amax = __uint_as_float(*bits);
+    *bits = 0u;
+    int e = 0;
+    if (amax > 0.f) frexpf(amax, &e);
+    e = max(-100, min(30, e));
+    w[0] = amax > 0.f ? ldexpf(1.f, -4 - e) : 1.f;
+    w[1] = amax > 0.f ? ldexpf(1.f, 4 + e) : 1.f;
+}
+
+float *grad_scale_words() {
+    static float *w = nullptr;
+    if (!w) {
+        if (cudaMalloc(&w, 4 * sizeof(float)) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        grad_scale_reset_kernel<<<1, 32, 0, rt().stream>>>(w);
+        count_launch();
+    }
+    return w;
+}
+
 }  // namespace seera
 
 using namespace seera;
@@ -525,6 +565,22 @@ int seera_mae_fwd_bwd(const float *p, const float *y, float *partials, float *lo
 int seera_bce_fwd_bwd(const float *p, const float *y, float *partials, float *loss_mean, float *dp, int size, float inv_count,
                       float eps) {
     return elem_loss(2, p, y, partials, loss_mean, dp, size, inv_count, eps, "bce_fwd_bwd");
+}
+
+// ---- dynamic factor of the fp16 gradient copies (precision modes 4 and 5) -------------------------------------------
+// words[0] = factor, words[1] = 1 / factor, words[2] = bits of the running maximum |g| (as an unsigned: positive floats
+// order like their bit patterns).
+int seera_grad_scale_update(const float *g, long long n) {
+    SEERA_ENSURE();
+    if (n < 0 || (n > 0 && !g)) return fail(SEERA_E_ARG, "grad_scale_update: bad argument");
+    float *w = grad_scale_words();
+    if (!w) return fail(SEERA_E_OOM, "grad_scale_update: no device memory for the scale words");
+    if (n == 0) return SEERA_OK;
+    grad_amax_kernel<<<stride_grid(n), 256, 0, rt().stream>>>(g, n, reinterpret_cast<unsigned *>(w) + 2);
+    SEERA_LAUNCH_CHECK("grad_scale_update(amax)");
+    grad_scale_finalize_kernel<<<1, 32, 0, rt().stream>>>(w);
+    SEERA_LAUNCH_CHECK("grad_scale_update");
+    return SEERA_OK;
 }
 
 int seera_adam_step(float *w, const float *g, float *m, float *v, int n, float lr, float beta1, float omb1,

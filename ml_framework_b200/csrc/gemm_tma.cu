@@ -56,7 +56,7 @@ int seera_tma_matmul_bwd(const float *A, const float *B, const float *dC, float 
     }
     if (!s && dB) {      // dB[K,N] = A[rows,K]^T * dC[rows,N] : contraction over rows, both operands read along their columns
         s = make_shadow(A, (int)rows, K, ns, sa, CLS_ACT);
-        if (!s) s = run_tma_gemm(sa, 1, sd, 1, StoreDense{dB, N}, K, N, (int)rows, true, "cuda_matmul_bwd(dB)");
+        if (!s) s = run_tma_gemm(sa, 1, sd, 1, StoreDense{dB, N}, K, N, (int)rows, true, "cuda_matmul_bwd(dB)", nullptr, 0, wgrad_copies(ns));
     }
     free_shadow(sd); free_shadow(sa); free_shadow(sb);
     return s;

@@ -18,7 +18,7 @@
 namespace seera {
 
 // Configuration by environment, read once when the library is first used:
-//   SEERA_PRECISION   0..4   initial precision mode of the contractions (default 3: bf16x6 on the tensor cores - fp32-class
+//   SEERA_PRECISION   0..5   initial precision mode of the contractions (default 3: bf16x6 on the tensor cores - fp32-class
 //                            products over fp32's whole exponent range, so that a caller who never heard of
 //                            seera_set_precision still runs on tcgen05 kernels and still matches the fp32 reference)
 //   SEERA_SM_RESERVE  n      SMs the persistent kernels leave free (the "sm_reserve" option)
@@ -28,7 +28,7 @@ static Runtime make_runtime() {
     r.precision = 3;
     if (const char *e = getenv("SEERA_PRECISION")) {
         int m = atoi(e);
-        if (m >= 0 && m <= 4 && e[0] >= '0' && e[0] <= '4') r.precision = m;
+        if (m >= 0 && m <= 5 && e[0] >= '0' && e[0] <= '5') r.precision = m;
     }
     if (const char *e = getenv("SEERA_TC_WAIT_MS")) {
         long long ms = atoll(e);
@@ -256,7 +256,7 @@ int seera_profile_report(char *buf, size_t size) {
 }
 
 int seera_set_precision(int mode) {
-    if (mode < 0 || mode > 4) return fail(SEERA_E_ARG, "seera_set_precision: mode %d", mode);
+    if (mode < 0 || mode > 5) return fail(SEERA_E_ARG, "seera_set_precision: mode %d", mode);
     rt().precision = mode;
     return SEERA_OK;
 }

@@ -253,6 +253,7 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("mse_partials", [](int n) { return seera_mse_partials(n); });
     m.def("mse_fwd_bwd", [](uptr p, uptr y, uptr part, uptr loss, uptr dp, int n, float inv) {
         ck(seera_mse_fwd_bwd(P<const F>(p), P<const F>(y), P<F>(part), P<F>(loss), P<F>(dp), n, inv)); });
+    m.def("grad_scale_update", [](uptr g, long long n) { ck(seera_grad_scale_update(P<const F>(g), n)); });
     m.def("mae_fwd_bwd", [](uptr p, uptr y, uptr part, uptr loss, uptr dp, int n, float inv) {
         ck(seera_mae_fwd_bwd(P<const F>(p), P<const F>(y), P<F>(part), P<F>(loss), P<F>(dp), n, inv)); });
     m.def("bce_fwd_bwd", [](uptr p, uptr y, uptr part, uptr loss, uptr dp, int n, float inv, float eps) {

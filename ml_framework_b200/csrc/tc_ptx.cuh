@@ -127,10 +127,15 @@ __device__ __forceinline__ float bf16_bits_to_float(uint32_t packed, int odd) {
 // with the values multiplied by `scale`, a power of two chosen per class of tensor so that the SECOND copy - 2^-11 of the
 // first - stays in fp16's normal range for the values that matter; conversion saturates instead of producing infinities.
 // The product's epilogue multiplies by 1 / (scale_a * scale_b), which is exact.
+// Gradients have no fixed magnitude (they shrink by orders of magnitude as training converges), so their factor has a
+// second, dynamic part: `dscale` points at a power of two in device memory that the loss head refreshes every step from
+// the largest entry of the loss gradient (seera_grad_scale_update); null means 1.
 struct Enc {
     int fmt;
     float scale;
+    const float *dscale;
 };
+__device__ __forceinline__ float enc_factor(const Enc &e) { return e.dscale ? e.scale * __ldg(e.dscale) : e.scale; }
 
 __device__ __forceinline__ uint32_t pack_f16x2_sat(float lo, float hi) {
     uint32_t r;
@@ -162,8 +167,9 @@ __device__ __forceinline__ uint4 split_chunk_f16(float *v) {
 template <int NS>
 __device__ __forceinline__ void store_split8(float *v, const Enc &e, void *d0, void *d1, void *d2) {
     if (e.fmt) {
+        const float f = enc_factor(e);
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] *= e.scale;
+        for (int i = 0; i < 8; i++) v[i] *= f;
         *reinterpret_cast<uint4 *>(d0) = split_chunk_f16(v);
         if (NS >= 2) *reinterpret_cast<uint4 *>(d1) = split_chunk_f16(v);
         if (NS >= 3) *reinterpret_cast<uint4 *>(d2) = split_chunk_f16(v);
@@ -178,7 +184,7 @@ __device__ __forceinline__ void store_split1(float v, int ns, const Enc &e, __nv
     unsigned short *u0 = reinterpret_cast<unsigned short *>(d0), *u1 = reinterpret_cast<unsigned short *>(d1),
                    *u2 = reinterpret_cast<unsigned short *>(d2);
     if (e.fmt) {
-        v *= e.scale;
+        v *= enc_factor(e);
         uint32_t p = pack_f16x2_sat(v, 0.f);
         *u0 = (unsigned short)p;
         if (ns >= 2) {

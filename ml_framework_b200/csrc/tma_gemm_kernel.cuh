@@ -52,7 +52,7 @@ inline int make_map_2d(CUtensorMap *m, const void *base, int rows, int cols, int
 struct Shadow {
     __nv_bfloat16 *p[3] = {nullptr, nullptr, nullptr};      // 16-bit containers: bf16 or fp16 by `enc`
     int rows = 0, cols = 0, ld = 0;
-    Enc enc{0, 1.f};
+    Enc enc{0, 1.f, nullptr};
 };
 
 // Classes of tensor, for the scale of an fp16 encoding: activations are O(1) after He / Glorot initialisation, weights a
@@ -86,12 +86,19 @@ __global__ void __launch_bounds__(256) shadow_rows_kernel(const float *__restric
 }
 
 // Precision modes 1 / 2 / 3: one, two, three bf16 copies (1, 3, 6 products).  Mode 4: two fp16 copies (3 products).
-inline int precision_copies() { int m = rt().precision; return m == 4 ? 2 : (m < 1 ? 1 : (m > 3 ? 3 : m)); }
+// Mode 5: one fp16 copy (1 product) - the first copy of a mode-4 set, so copies kept by a mode-4 forward serve a mode-5 backward.
+inline int precision_copies() { int m = rt().precision; return m == 4 ? 2 : (m == 5 ? 1 : (m < 1 ? 1 : (m > 3 ? 3 : m))); }
 inline Enc enc_for(int cls) {
-    if (rt().precision != 4) return Enc{0, 1.f};
+    if (rt().precision != 4 && rt().precision != 5) return Enc{0, 1.f, nullptr};
     static const float scale[3] = {16.f, 256.f, 4096.f};
-    return Enc{1, scale[cls]};
+    return Enc{1, scale[cls], cls == CLS_GRAD ? grad_scale_words() : nullptr};
 }
+// Copies a weight-gradient product uses.  Its rounding stays in that one tensor (nothing downstream of dW in the backward
+// pass reads it), so with the "wgrad_single" option the fp16 split mode forms dW from the first copy of each operand alone:
+// one product instead of three, 2e-4 of rounding in dW.
+inline int wgrad_copies(int ns) { return (rt().wgrad_single && rt().precision == 4) ? 1 : ns; }
+// The inverse of an operand's dynamic factor, for the epilogue (null: none).
+inline const float *enc_dinv(const Enc &a, const Enc &b) { return (a.dscale || b.dscale) ? grad_scale_words() + 1 : nullptr; }
 
 inline int alloc_shadow(Shadow &s, int rows, int cols, int ns) {
     s.rows = rows; s.cols = cols; s.ld = (cols + 7) / 8 * 8;
@@ -108,6 +115,8 @@ inline void free_shadow(Shadow &s) {
 inline int make_shadow(const float *src, int rows, int cols, int ns, Shadow &s, int cls) {
     if (int e = alloc_shadow(s, rows, cols, ns)) return e;
     s.enc = enc_for(cls);
+    if (s.enc.dscale)          // an fp32 gradient tensor handed in from outside: its own largest entry sets the dynamic factor
+        if (int e = seera_grad_scale_update(src, (long long)rows * cols)) return e;
     long long groups = (long long)rows * (s.ld / 8);
     int grid = stride_grid(groups);
     cudaStream_t st = rt().stream;
@@ -172,6 +181,7 @@ struct TmaGemmParams {
     unsigned long long wait_clocks;   // budget of every bounded wait in the kernel
     int skip_load;           // test hook: the producer of CTA 0 leaves out the loads of this k-step (-1: none), so that the
                              // waits downstream of it run out and the kernel has to report and unwind
+    const float *dinv;       // device word holding the inverse of the gradient operand's dynamic factor (null: none)
     float out_scale;         // the accumulator is multiplied by this before bias / activation / store: 1 / (scale_a * scale_b)
     int a_fp16, b_fp16;      // operand formats: 0 bf16, 1 fp16
     const float *bias;       // per-column bias added before the store, or null
@@ -374,6 +384,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         // ---------------- epilogue: warp w drains TMEM lane quarter w % 4 ----------------
         const int q = warp & 3;
         float *stage = reinterpret_cast<float *>(epi_smem + (size_t)(warp - 2) * EPI_WARP_SMEM);
+        const float out_scale = p.dinv ? p.out_scale * __ldg(p.dinv) : p.out_scale;
         int local = 0;
         for (int id = blockIdx.x; id < total_tiles; id += gridDim.x, local++) {
             int m0, n0, kbeg, ktiles, z;
@@ -383,10 +394,10 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             tc_fence_after();
             if (p.pool_on)
                 drain_accumulator_pooled(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, bn, p.M, p.N,
-                                         p.bias, p.act, p.pool, stage, p.out_scale);
+                                         p.bias, p.act, p.pool, stage, out_scale);
             else
                 drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, 0, bn, p.M, p.N, cs,
-                                  p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act, p.out_scale);
+                                  p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act, out_scale);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
@@ -399,7 +410,9 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
 
 template <class CS>
 __global__ void __launch_bounds__(256) tma_splitk_reduce_kernel(const float *__restrict__ partial, CS cs, int M, int N, int splits,
-                                                                const float *__restrict__ bias, int act, float scale) {
+                                                                const float *__restrict__ bias, int act, float scale,
+                                                                const float *__restrict__ dinv) {
+    if (dinv) scale *= __ldg(dinv);
     long long total = (long long)M * N;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
     for (long long i = tid; i < total; i += nthr) {
@@ -500,7 +513,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
 #undef SEERA_TMA_LAUNCH
     count_launch();
     if (e == cudaSuccess && p.partial) {
-        tma_splitk_reduce_kernel<<<stride_grid((long long)p.M * p.N), 256, 0, st>>>(p.partial, cs, p.M, p.N, splits, p.bias, p.act, p.out_scale);
+        tma_splitk_reduce_kernel<<<stride_grid((long long)p.M * p.N), 256, 0, st>>>(p.partial, cs, p.M, p.N, splits, p.bias, p.act, p.out_scale, p.dinv);
         count_launch();
         e = cudaGetLastError();
     }
@@ -513,12 +526,13 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
 // Dense: A operand shadow `sa`; a_mn = 0: sa is [M, K] (read along its rows); a_mn = 1: sa is [K, M].  Likewise B with N.
 template <class CS>
 int run_tma_gemm(const Shadow &sa, int a_mn, const Shadow &sb, int b_mn, const CS &cs, int M, int N, int K,
-                 bool allow_split, const char *name, const float *bias = nullptr, int act = 0) {
-    const int ns = precision_copies();
+                 bool allow_split, const char *name, const float *bias = nullptr, int act = 0, int copies = 0) {
+    const int ns = copies ? copies : precision_copies();
     TmaGemmParams p{};
     p.bias = bias; p.act = act;
     p.M = M; p.N = N; p.K = K; p.a_mode = a_mn ? TMA_A_COLS : TMA_A_ROWS; p.b_mn = b_mn;
     p.a_fp16 = sa.enc.fmt; p.b_fp16 = sb.enc.fmt; p.out_scale = 1.f / (sa.enc.scale * sb.enc.scale);
+    p.dinv = enc_dinv(sa.enc, sb.enc);
     p.bn = tma_pick_bn(N, ns, b_mn);
     TmaMaps maps;
     for (int i = 0; i < 3; i++) {

@@ -1042,6 +1042,13 @@ class Sequential:
 # ─────────────────────────────────────────────────────────────────────────────────────────────
 # Losses
 # ─────────────────────────────────────────────────────────────────────────────────────────────
+def _scale_gradients(g):
+    """In the fp16 precision modes the backward pass scales its gradient copies by a power of two taken from the largest
+    entry of the loss gradient (fp16's exponent range is 2^-14 .. 2^16; a converging run's gradients leave it downwards)."""
+    if sc.get_precision() in (4, 5):
+        sc.grad_scale_update(g.main_ptr, g.size)
+
+
 class Loss:
     """Each loss is the mean over the batch THIS process holds.  In a data-parallel run the ranks' gradients are averaged
     by the optimizer (dp.attach sets the 1/world factor there), so no scale is applied here."""
@@ -1061,7 +1068,7 @@ class Loss:
         out = Tensor(loss)
         out._parents = (logits,)
         out._keep = (rows, yv)
-        out._backward = lambda g: logits._accumulate(dz)       # g is the all-ones seed of a scalar loss
+        out._backward = lambda g: (_scale_gradients(dz), logits._accumulate(dz))       # g is the all-ones seed of a scalar loss
         return out
 
     def _elementwise(self, kernel, y_pred, y, *extra):
@@ -1074,7 +1081,7 @@ class Loss:
         out = Tensor(loss)
         out._parents = (y_pred,)
         out._keep = (part, yv)
-        out._backward = lambda g: y_pred._accumulate(dp)
+        out._backward = lambda g: (_scale_gradients(dp), y_pred._accumulate(dp))
         return out
 
     def mse(self, y_pred, y):

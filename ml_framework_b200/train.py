@@ -17,7 +17,7 @@ from .cuTen import cuten
 # forward values rounded to bf16 (2^-9) a few per mille of them would.  The backward products only add their own rounding:
 # two-way split for the fp32 configurations, ONE bf16 pass for the bf16 configuration (its subject: dA = dC B^T, dB = A^T dC).
 # Mode 4 is the two-way fp16 split: three products with the accuracy the three-way bf16 split (mode 3) needs six for.
-POLICY = {"fp32": (4, 4), "bf16": (4, 1)}
+POLICY = {"fp32": (4, 4), "bf16": (4, 5)}
 
 
 def policy_for(work):

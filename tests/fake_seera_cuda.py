@@ -443,6 +443,9 @@ def mse_fwd_bwd(p, y, part, loss, dp, n, inv):
     _view(dp, n)[:] = 2 * d * np.float32(inv)
 
 
+def grad_scale_update(g, n): _count("grad_scale")
+
+
 def mae_fwd_bwd(p, y, part, loss, dp, n, inv):
     _count("mae")
     d = _view(p, n) - _view(y, n)

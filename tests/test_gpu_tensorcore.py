@@ -28,7 +28,9 @@ def E():
     import engine_np
     L = capi.load()
     capi.check(L.seera_init(capi.default_device()))
+    capi.check(L.seera_set_option(b"wgrad_single", 0))        # mode 4 at its full three products, weight gradients included
     yield engine_np
+    capi.check(L.seera_set_option(b"wgrad_single", 1))
     assert L.seera_tc_device_status() == 0            # no bounded wait ever expired
     L.seera_set_precision(0)
 
@@ -85,6 +87,29 @@ def test_im2col_maps_of_tensors_below_128_kib(E, N, C, H, W):
     dX, dW = E.conv2d_backward(dY, X, Wt, 1, 1, 1, 1)
     rX, rW = co.conv2d_backward(dY, X, Wt, 1, 1, 1, 1)
     assert rel_l2(dX, rX) < TOL[1] and rel_l2(dW, rW) < TOL[1]
+
+
+def test_mode_4_weight_gradients_from_one_fp16_copy(E):
+    """The default of mode 4 ("wgrad_single"): dW / dB from the first fp16 copy of each operand - one product, 2^-12 rounding
+    per operand (a few 1e-4 here, where nothing averages; 3e-5 and less on the training configurations) - while the data
+    gradient keeps its three products."""
+    from ml_framework_b200 import capi
+    L = capi.load()
+    rs = np.random.RandomState(77)
+    A, B, dC = (rs.standard_normal(s).astype(np.float32) for s in ((512, 300), (300, 200), (512, 200)))
+    X, Wt = rs.standard_normal((8, 64, 12, 12)).astype(np.float32), rs.standard_normal((96, 64, 3, 3)).astype(np.float32)
+    dY = rs.standard_normal((8, 96, 12, 12)).astype(np.float32)
+    _prep(4)
+    try:
+        capi.check(L.seera_set_option(b"wgrad_single", 1))
+        dA, dB = E.matmul_backward(A, B, dC)
+        assert rel_l2(dA, dC.astype(np.float64) @ B.T) < TOL[4]
+        assert 1e-5 < rel_l2(dB, A.T.astype(np.float64) @ dC) < 5e-4
+        dX, dW = E.conv2d_backward(dY, X, Wt, 1, 1, 1, 1)
+        rX, rW = co.conv2d_backward(dY, X, Wt, 1, 1, 1, 1)
+        assert rel_l2(dX, rX) < TOL[4] and 1e-5 < rel_l2(dW, rW) < 5e-4
+    finally:
+        capi.check(L.seera_set_option(b"wgrad_single", 0))
 
 
 CONVT = [(1, 1, 4, 4, 1, 3, 3, 1, 1, 0, 0), (2, 4, 5, 6, 3, 4, 3, 2, 2, 1, 0), (8, 64, 16, 16, 32, 4, 4, 2, 2, 1, 1),
