@@ -98,6 +98,12 @@ int         seera_get_precision(void);
  *   "pool_short_patch" (default 0): let seera_conv2d_bias_act_pool_fwd_s also serve short-patch convolutions
  *       (C*R*S <= 64).  Correct, but that kernel is bound by its epilogue warps and runs slower with the pool folded in
  *       than followed by a separate pool.
+ *   "pair_tiles" (default 0; also SEERA_PAIR_TILES): run the TMA-fed GEMMs as clusters of two CTAs on 256-row tiles
+ *       (tcgen05 cta_group::2: each CTA stages its own 128 rows of A and half of B's columns, the even CTA issues the
+ *       MMAs for both, completion of both CTAs' plain tensor copies is counted on its barrier; no multicast load).
+ *       It cuts the operand bytes per CTA and k-step by a quarter to a third.  Bit-for-bit the same results; measured
+ *       3-8 % SLOWER on every configuration here (C3 dgrad 51.3 -> 53.2 us, wgrad 41.2 -> 51.1 us), because these
+ *       kernels are bound by the MMA issue rate at accumulator widths of 64-128 columns, not by the operand stream.
  *   "wgrad_single" (default 1): in precision mode 4 a weight gradient (conv dW, Dense dB) is formed from the FIRST fp16
  *       copy of each operand alone - one product instead of three.  Its 2^-12 rounding stays inside that one tensor
  *       (nothing downstream in the backward pass reads dW); measured on the VGG configuration it moves no dW error

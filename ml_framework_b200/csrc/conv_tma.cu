@@ -220,12 +220,12 @@ static int tma_fprop(const NhwcShadow &x, const Shadow &wk, float *Y, int F, int
     p.cchunks = (x.Cp + 63) / 64; p.cpad = x.Cp; p.taps = R * S; p.S = S;
     p.K = p.taps * p.cchunks * 64;
     p.OW = OW; p.OHW = OH * OW; p.sw = sw; p.sh = sh; p.pw = pw; p.ph = ph;
-    p.bn = tma_pick_bn(F, ns, 0);
+    tma_plan(p, ns, false);
     TmaMaps maps;
     for (int i = 0; i < 3; i++) {
         int j = i < ns ? i : 0;
         if (int s = make_map_im2col(&maps.a[i], x.p[j], x.NB, x.H, x.W, x.Cp, R, S, sh, sw, ph, pw, 64, TC_BM)) return s;
-        if (int s = make_map_2d(&maps.b[i], wk.p[j], wk.rows, wk.cols, wk.ld, 64, p.bn)) return s;
+        if (int s = make_map_2d(&maps.b[i], wk.p[j], wk.rows, wk.cols, wk.ld, 64, p.pair ? p.bn / 2 : p.bn)) return s;
     }
     double flops = 2.0 * p.M * (double)F * x.C * R * S;
     return launch_tma_gemm(maps, p, StorePixelRows{Y, F, OH * OW}, ns, false, flops, name);
@@ -242,7 +242,7 @@ static int tma_wgrad(const NhwcShadow &x, const NhwcShadow &dy, float *dW, int R
     p.M = p.taps * p.cchunks * 64; p.N = F;
     p.K = x.NB * OH * OW;
     p.OW = OW; p.OHW = OH * OW; p.sw = sw; p.sh = sh; p.pw = pw; p.ph = ph;
-    p.bn = tma_pick_bn(F, ns, 1);
+    tma_plan(p, ns, true);
     TmaMaps maps;
     for (int i = 0; i < 3; i++) {
         int j = i < ns ? i : 0;
@@ -322,13 +322,13 @@ static int tma_dgrad_phases(const NhwcShadow &g, const float *Wt, long long so, 
             p.cchunks = (g.Cp + 63) / 64; p.cpad = g.Cp; p.taps = taps; p.S = x.T;
             p.K = p.taps * p.cchunks * 64;
             p.OW = x.G; p.OHW = y.G * x.G; p.sw = 1; p.sh = 1; p.pw = -x.lower; p.ph = -y.lower;
-            p.bn = tma_pick_bn(Nch, ns, 0);
+            tma_plan(p, ns, false);
             TmaMaps maps;
             int e = SEERA_OK;
             for (int i = 0; i < 3 && !e; i++) {
                 int j = i < ns ? i : 0;
                 e = make_map_im2col_box(&maps.a[i], g.p[j], g.NB, g.H, g.W, g.Cp, 1, 1, x.lower, y.lower, x.upper, y.upper, 64, TC_BM);
-                if (!e) e = make_map_2d(&maps.b[i], wk.p[j], wk.rows, wk.cols, wk.ld, 64, p.bn);
+                if (!e) e = make_map_2d(&maps.b[i], wk.p[j], wk.rows, wk.cols, wk.ld, 64, p.pair ? p.bn / 2 : p.bn);
             }
             double flops = 2.0 * p.M * (double)Nch * g.C * taps;
             if (!e) e = launch_tma_gemm(maps, p, StorePhaseRows{out, Nch, H, W, y.G, x.G, a, b, sh, sw}, ns, false, flops, name);

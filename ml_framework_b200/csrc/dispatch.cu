@@ -17,6 +17,7 @@ int seera_set_option(const char *name, int value) {
     if (!name) return fail(SEERA_E_ARG, "set_option: null name");
     if (!strcmp(name, "dense_tma")) { rt().dense_tma = value != 0; return SEERA_OK; }
     if (!strcmp(name, "conv_tma")) { rt().conv_tma = value != 0; return SEERA_OK; }
+    if (!strcmp(name, "pair_tiles")) { rt().pair_tiles = value != 0; return SEERA_OK; }
     if (!strcmp(name, "wgrad_single")) { rt().wgrad_single = value != 0; return SEERA_OK; }
     if (!strcmp(name, "tc_wait_ms")) {
         if (value < 1 || value > 60000) return fail(SEERA_E_ARG, "set_option: tc_wait_ms must be in [1, 60000]");

@@ -21,6 +21,7 @@ namespace seera {
 //   SEERA_PRECISION   0..5   initial precision mode of the contractions (default 3: bf16x6 on the tensor cores - fp32-class
 //                            products over fp32's whole exponent range, so that a caller who never heard of
 //                            seera_set_precision still runs on tcgen05 kernels and still matches the fp32 reference)
+//   SEERA_PAIR_TILES  0|1    the "pair_tiles" option (TMA-fed GEMMs as clusters of two CTAs on 256-row tiles)
 //   SEERA_SM_RESERVE  n      SMs the persistent kernels leave free (the "sm_reserve" option)
 //   SEERA_TC_WAIT_MS  n      budget of the bounded waits inside the tensor-core kernels, in milliseconds (default 2000)
 static Runtime make_runtime() {
@@ -30,6 +31,7 @@ static Runtime make_runtime() {
         int m = atoi(e);
         if (m >= 0 && m <= 5 && e[0] >= '0' && e[0] <= '5') r.precision = m;
     }
+    if (const char *e = getenv("SEERA_PAIR_TILES")) r.pair_tiles = atoi(e) != 0;
     if (const char *e = getenv("SEERA_TC_WAIT_MS")) {
         long long ms = atoll(e);
         if (ms > 0) r.tc_wait_clocks = (unsigned long long)ms * 2000000ull;      // ~2e6 clocks per millisecond

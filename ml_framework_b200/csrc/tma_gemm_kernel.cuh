@@ -147,6 +147,60 @@ __device__ __forceinline__ void tma_load_im2col(uint32_t dst_smem, const CUtenso
                    "h"((unsigned short)off_w), "h"((unsigned short)off_h) : "memory");
 }
 
+// ---- CTA pairs (tcgen05 cta_group::2): two CTAs of a cluster share one 256-row accumulator tile -------------------------
+// Each CTA stages its own 128 rows of A and its own half of B's columns; the MMA, issued by the even CTA alone, reads the
+// shared memory of both, and each CTA's TMEM receives its 128 rows of the result.  Per CTA and k-step that is
+// (128 + N/2) operand rows loaded for 128 x N of output instead of (128 + N): the L2 -> shared-memory stream, which bounds
+// the split-product kernels, shrinks by a quarter to a third.  No multicast load is involved: every CTA issues plain
+// tensor copies into its own shared memory; only their completion is counted on the even CTA's barrier, and the
+// tcgen05.commit that frees a stage or publishes an accumulator arrives on both CTAs' barriers.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();        // the single-thread roles left their warps diverged
+    asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// shared::cluster address of the same variable in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far have finished
+__device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+// tensor copies of a CTA of a pair: into its own shared memory, completion counted on `bar`, a shared::cluster address
+__device__ __forceinline__ void tma2_load_2d(uint32_t dst_smem, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma2_load_im2col(uint32_t dst_smem, const CUtensorMap *map, int c, int w, int h, int n,
+                                                 int off_w, int off_h, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6], {%7, %8};"
+                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(map)), "r"(c), "r"(w), "r"(h), "r"(n), "r"(bar),
+                   "h"((unsigned short)off_w), "h"((unsigned short)off_h) : "memory");
+}
+
 // MN-major operand tile: 64 contiguous row-index elements (128 bytes) per k line, 8 k lines per 1024-byte
 // atom; atoms of the next 64 row indices start box_bytes later.
 __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t addr, uint32_t box_bytes) {
@@ -171,6 +225,7 @@ enum { TMA_A_ROWS = 0, TMA_A_COLS = 1, TMA_A_IM2COL = 2, TMA_A_TAPS = 3 };
 struct TmaGemmParams {
     int M, N, K, kchunk, splits, bn, stages;
     int a_mode, b_mn;        // b_mn = 1: B read along its contiguous row index (MN-major)
+    int pair;                // 1: launched as clusters of two CTAs sharing 256-row tiles (tcgen05 cta_group::2)
     // convolution geometry for the im2col modes
     int OW, OHW;             // output width and pixels per image of the traversal
     int sw, sh, pw, ph;      // window stride and lower padding
@@ -196,7 +251,7 @@ constexpr int TG_THREADS = 192;
 // Persistent kernel: each CTA walks tiles  id = blockIdx.x, blockIdx.x + gridDim.x, ...  (m-tile fastest, then n-tile,
 // then K split).  The operand ring keeps streaming across tile boundaries and the accumulator is double-buffered in
 // TMEM (2 x bn columns), so the epilogue of tile i overlaps the main loop of tile i+1.
-template <int NS, class CS>
+template <int NS, class CS, bool PAIR>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
                 const __grid_constant__ CUtensorMap mapA2, const __grid_constant__ CUtensorMap mapB0,
@@ -208,12 +263,17 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
 
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int bn = p.bn, stages = p.stages;
-    const int mtiles = (p.M + TC_BM - 1) / TC_BM, ntiles = (p.N + bn - 1) / bn;
+    // PAIR: the two CTAs of a cluster work on one tile of 256 rows; `rank` 0 (the even CTA) issues its MMAs
+    constexpr int TM = PAIR ? 2 * TC_BM : TC_BM;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, nworkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int bh = PAIR ? bn >> 1 : bn;                       // columns of B this CTA stages
+    const int mtiles = (p.M + TM - 1) / TM, ntiles = (p.N + bn - 1) / bn;
     const int total_tiles = mtiles * ntiles * p.splits;
     const bool a_mn = p.a_mode == TMA_A_COLS || p.a_mode == TMA_A_TAPS;
 
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const uint32_t a_bytes = TC_BM * 128, b_bytes = (uint32_t)bn * 128;
+    const uint32_t a_bytes = TC_BM * 128, b_bytes = (uint32_t)bh * 128;
     const uint32_t stage_bytes = (uint32_t)NS * (a_bytes + b_bytes);
     const uint32_t smem0 = smem_u32(smem);
     auto a_tile = [&](int s, int i) { return smem0 + (uint32_t)s * stage_bytes + (uint32_t)i * a_bytes; };
@@ -225,13 +285,13 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
     if (t == 0) {
         abort_flag = 0;
         for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, PAIR ? 8 : 4); }
         fence_mbar_init();
         fence_async_smem();
     }
-    if (warp == 1) tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols);
+    if (warp == 1) { if (PAIR) tmem_alloc2(smem_u32(&tmem_base_slot), tmem_cols); else tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols); }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all(); else __syncthreads();        // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int *abortp = &abort_flag;
@@ -241,7 +301,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         int rest = p.by_mtiles.div(id), mt = id - rest * mtiles;
         z = p.by_ntiles.div(rest);
         int nt = rest - z * ntiles;
-        m0 = mt * TC_BM; n0 = nt * bn;
+        m0 = mt * TM + (int)rank * TC_BM; n0 = nt * bn;         // this CTA's own 128 rows
         kbeg = z * p.kchunk;
         int kend = min(p.K, kbeg + p.kchunk);
         ktiles = (kend - kbeg + TC_BK - 1) / TC_BK;
@@ -251,13 +311,20 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         // ---------------- TMA producer ----------------
         const CUtensorMap *mA[3] = {&mapA0, &mapA1, &mapA2};
         const CUtensorMap *mB[3] = {&mapB0, &mapB1, &mapB2};
+        auto ld2d = [&](uint32_t dst, const CUtensorMap *m, int x, int y, uint32_t bar) {
+            if (PAIR) tma2_load_2d(dst, m, x, y, bar); else tma_load_2d(dst, m, x, y, bar);
+        };
+        auto ldim = [&](uint32_t dst, const CUtensorMap *m, int c, int w, int h, int n, int ow, int oh, uint32_t bar) {
+            if (PAIR) tma2_load_im2col(dst, m, c, w, h, n, ow, oh, bar); else tma_load_im2col(dst, m, c, w, h, n, ow, oh, bar);
+        };
         int it = 0, issued_from = 0;
         int s = 0;                                            // ring slot and its phase, carried across tiles
         uint32_t ph = 0;
         bool alive = true;
-        for (int id = blockIdx.x; id < total_tiles && alive; id += gridDim.x) {
+        for (int id = worker; id < total_tiles && alive; id += nworkers) {
             int m0, n0, kbeg, ktiles, z;
             tile_origin(id, m0, n0, kbeg, ktiles, z);
+            const int nb0 = n0 + (int)rank * bh;               // this CTA's own columns of B
             // im2col, M = pixels: window corner of this tile's first output pixel
             int pix_img = 0, pix_w = 0, pix_h = 0;
             if (p.a_mode == TMA_A_IM2COL) {
@@ -268,7 +335,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             // im2col, M = (tap, channel): the two 64-channel boxes of this tile
             int box_c[2] = {0, 0}, box_s[2] = {0, 0}, box_r[2] = {0, 0};
             bool box_ok[2] = {true, true};
-            uint32_t tx_bytes = stage_bytes;
+            uint32_t tx_bytes = PAIR ? 2u * stage_bytes : stage_bytes;     // a pair counts both CTAs' bytes on the even CTA's barrier
             if (p.a_mode == TMA_A_TAPS) {
                 int c64 = p.cchunks * 64;
                 for (int b = 0; b < 2; b++) {
@@ -277,29 +344,35 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
                     box_c[b] = mb - tap * c64; box_r[b] = p.by_S.div(tap); box_s[b] = tap - box_r[b] * p.S;
                     if (!box_ok[b]) tx_bytes -= (uint32_t)NS * 8192u;
                 }
+                if (PAIR && rank == 0) {                       // the peer's boxes beyond the last tap are not loaded either
+                    for (int b = 0; b < 2; b++) {
+                        int mb = m0 + TC_BM + 64 * b, tap = p.by_cchunks.div(mb >> 6);
+                        if (tap >= p.taps) tx_bytes -= (uint32_t)NS * 8192u;
+                    }
+                }
             }
             for (int kt = 0; kt < ktiles; kt++, it++) {
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abortp, p.status, 1, p.wait_clocks)) { alive = false; break; }
                 int k0 = kbeg + kt * TC_BK;
-                uint32_t bar = full0 + 8 * s;
+                const uint32_t bar = PAIR ? mapa_rank(full0 + 8 * s, 0) : full0 + 8 * s;
                 if (p.skip_load >= 0 && blockIdx.x == 0 && it == p.skip_load) {      // test hook: this stage never fills
                     if (++s == stages) { s = 0; ph ^= 1u; }
                     continue;
                 }
-                mbar_expect_tx(bar, tx_bytes);
+                if (rank == 0) mbar_expect_tx(full0 + 8 * s, tx_bytes);
                 int bk = k0;                                  // B's coordinate along the contraction
                 if (p.a_mode == TMA_A_ROWS) {
 #pragma unroll
-                    for (int i = 0; i < NS; i++) tma_load_2d(a_tile(s, i), mA[i], k0, m0, bar);
+                    for (int i = 0; i < NS; i++) ld2d(a_tile(s, i), mA[i], k0, m0, bar);
                 } else if (p.a_mode == TMA_A_COLS) {
 #pragma unroll
                     for (int i = 0; i < NS; i++)
-                        for (int b = 0; b < 2; b++) tma_load_2d(a_tile(s, i) + b * 8192, mA[i], m0 + 64 * b, k0, bar);
+                        for (int b = 0; b < 2; b++) ld2d(a_tile(s, i) + b * 8192, mA[i], m0 + 64 * b, k0, bar);
                 } else if (p.a_mode == TMA_A_IM2COL) {
                     int ktile = k0 >> 6, tap = p.by_cchunks.div(ktile), c0 = (ktile - tap * p.cchunks) * 64;
                     int r = p.by_S.div(tap), sx = tap - r * p.S;
 #pragma unroll
-                    for (int i = 0; i < NS; i++) tma_load_im2col(a_tile(s, i), mA[i], c0, pix_w, pix_h, pix_img, sx, r, bar);
+                    for (int i = 0; i < NS; i++) ldim(a_tile(s, i), mA[i], c0, pix_w, pix_h, pix_img, sx, r, bar);
                     bk = tap * p.cpad + c0;
                 } else {
                     int img = p.by_OHW.div(k0), rem = k0 - img * p.OHW, oh = p.by_OW.div(rem), ow = rem - oh * p.OW;
@@ -307,20 +380,20 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
 #pragma unroll
                     for (int i = 0; i < NS; i++)
                         for (int b = 0; b < 2; b++)
-                            if (box_ok[b]) tma_load_im2col(a_tile(s, i) + b * 8192, mA[i], box_c[b], w, h, img, box_s[b], box_r[b], bar);
+                            if (box_ok[b]) ldim(a_tile(s, i) + b * 8192, mA[i], box_c[b], w, h, img, box_s[b], box_r[b], bar);
                 }
                 if (p.b_mn) {
 #pragma unroll
                     for (int i = 0; i < NS; i++)
-                        for (int b = 0; b < bn / 64; b++) tma_load_2d(b_tile(s, i) + b * 8192, mB[i], n0 + 64 * b, bk, bar);
+                        for (int b = 0; b < bh / 64; b++) ld2d(b_tile(s, i) + b * 8192, mB[i], nb0 + 64 * b, bk, bar);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < NS; i++) tma_load_2d(b_tile(s, i), mB[i], bk, n0, bar);
+                    for (int i = 0; i < NS; i++) ld2d(b_tile(s, i), mB[i], bk, nb0, bar);
                 }
                 if (++s == stages) { s = 0; ph ^= 1u; }
             }
         }
-        if (*abortp) {
+        if (*abortp && rank == 0) {
             // give copies already in flight a bounded chance to land before the CTA's shared memory goes away
             issued_from = it - stages < 0 ? 0 : it - stages;
             for (int k = issued_from; k < it; k++) {
@@ -329,9 +402,10 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
                 while (!mbar_try_wait(full0 + 8 * (k % stages), (uint32_t)(k / stages) & 1u) && clock64() - t0 < p.wait_clocks) {}
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---------------- MMA issuer ----------------
-        const uint32_t idesc = umma_idesc_16bit(bn, p.a_fp16, p.b_fp16) | ((uint32_t)(a_mn ? 1 : 0) << 15) | ((uint32_t)p.b_mn << 16);
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---------------- MMA issuer (the even CTA of a pair) ----------------
+        uint32_t idesc = umma_idesc_16bit(bn, p.a_fp16, p.b_fp16) | ((uint32_t)(a_mn ? 1 : 0) << 15) | ((uint32_t)p.b_mn << 16);
+        if (PAIR) idesc = (idesc & ~(31u << 24)) | ((uint32_t)(TM >> 4) << 24);          // M = 256 over the two CTAs
         const uint32_t a_step = a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;   // bytes per K=16 slice
         // split products kept: hi*hi | + hi*lo, lo*hi | + hi*lo2, lo2*hi, lo*lo
         constexpr int NPROD = NS == 1 ? 1 : (NS == 2 ? 3 : 6);
@@ -346,7 +420,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         const uint64_t db0 = p.b_mn ? umma_desc_sw128_mn(b_tile(0, 0), 8192) : umma_desc_sw128(b_tile(0, 0));
         const uint32_t a_step16 = a_step >> 4, b_step16 = b_step >> 4, a_copy16 = a_bytes >> 4, b_copy16 = b_bytes >> 4;
         const uint32_t stage16 = stage_bytes >> 4;
-        for (int id = blockIdx.x; id < total_tiles && alive; id += gridDim.x, local++) {
+        for (int id = worker; id < total_tiles && alive; id += nworkers, local++) {
             int m0, n0, kbeg, ktiles, z;
             tile_origin(id, m0, n0, kbeg, ktiles, z);
             const int buf = local & 1;
@@ -371,14 +445,14 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
                     }
 #pragma unroll
                     for (int q = 0; q < NPROD; q++) {
-                        umma_bf16(d_tmem, da[pa[q]], db[pb[q]], idesc, acc);
+                        if (PAIR) umma2_bf16(d_tmem, da[pa[q]], db[pb[q]], idesc, acc); else umma_bf16(d_tmem, da[pa[q]], db[pb[q]], idesc, acc);
                         acc = 1;
                     }
                 }
-                umma_commit(empty0 + 8 * s);
+                if (PAIR) umma2_commit_both(empty0 + 8 * s); else umma_commit(empty0 + 8 * s);
                 if (++s == stages) { s = 0; ph ^= 1u; }
             }
-            if (alive) umma_commit(tfull0 + 8 * buf);        // accumulator of this tile complete
+            if (alive) { if (PAIR) umma2_commit_both(tfull0 + 8 * buf); else umma_commit(tfull0 + 8 * buf); }   // accumulator complete
         }
     } else if (warp >= 2) {
         // ---------------- epilogue: warp w drains TMEM lane quarter w % 4 ----------------
@@ -386,7 +460,8 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         float *stage = reinterpret_cast<float *>(epi_smem + (size_t)(warp - 2) * EPI_WARP_SMEM);
         const float out_scale = p.dinv ? p.out_scale * __ldg(p.dinv) : p.out_scale;
         int local = 0;
-        for (int id = blockIdx.x; id < total_tiles; id += gridDim.x, local++) {
+        const uint32_t tempty_at = PAIR ? mapa_rank(tempty0, 0) : tempty0;      // the even CTA's barrier counts both epilogues
+        for (int id = worker; id < total_tiles; id += nworkers, local++) {
             int m0, n0, kbeg, ktiles, z;
             tile_origin(id, m0, n0, kbeg, ktiles, z);
             const int buf = local & 1;
@@ -400,12 +475,12 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
                                   p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act, out_scale);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+            if (lane == 0) { if (PAIR) mbar_arrive_cluster(tempty_at + 8 * buf); else mbar_arrive(tempty0 + 8 * buf); }
         }
     }
     tc_fence_before();
-    __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, tmem_cols);
+    if (PAIR) cluster_sync_all(); else __syncthreads();        // neither CTA's shared memory or TMEM goes away while the other still uses it
+    if (warp == 1) { if (PAIR) tmem_dealloc2(tmem_base, tmem_cols); else tmem_dealloc(tmem_base, tmem_cols); }
 }
 
 template <class CS>
@@ -439,17 +514,34 @@ inline int tma_pick_bn(int N, int ns, int b_mn) {
     return bn;
 }
 
+// Chooses the accumulator width and whether the launch runs as CTA pairs; sets p.bn and p.pair from p.M, p.N, p.b_mn.
+// Pairs pay when the operand stream bounds the kernel (the split modes: per CTA and k-step 128 + N/2 operand rows instead of
+// 128 + N) and there are enough 256-row tiles to keep 74 pairs busy; a launch that may split its contraction always has.
+inline void tma_plan(TmaGemmParams &p, int ns, bool allow_split) {
+    p.bn = tma_pick_bn(p.N, ns, p.b_mn);
+    p.pair = 0;
+    if (!rt().pair_tiles || ns > 2 || rt().sm_count < 4) return;
+    int bn = p.bn;
+    if (ns == 2 && p.N > 128) bn = 256;               // a pair stages half of B per CTA: 2 x (16 + 16) KB per stage, three stages
+    if (bn < 64 || (p.b_mn && bn < 128) || p.M < 2 * TC_BM) return;
+    const long long pair_tiles = (long long)((p.M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((p.N + bn - 1) / bn);
+    if (!allow_split && pair_tiles < rt().sm_count / 2) return;
+    p.bn = bn;
+    p.pair = 1;
+}
+
 // Launches the kernel on prepared tensor maps.  p.M, p.N, p.K (contraction length in elements), a_mode, b_mn, bn
 // and the geometry fields must be set; kchunk, stages, partial and status are filled here.
 template <class CS>
 int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, bool allow_split, double flops, const char *name) {
-    size_t stage = (size_t)ns * (TC_BM * 128 + (size_t)p.bn * 128);
+    const int tm = p.pair ? 2 * TC_BM : TC_BM;
+    size_t stage = (size_t)ns * (TC_BM * 128 + (size_t)(p.pair ? p.bn / 2 : p.bn) * 128);
     // 227 KB per CTA on sm_100a; keep 2 KB for the kernel's static shared memory and alignment slack
     int stages = (int)((225 * 1024 - 4 * EPI_WARP_SMEM - 1024) / stage);
     if (stages > 8) stages = 8;
     if (stages < 2) return fail(SEERA_E_LIMIT, "%s: tile does not fit shared memory", name);
     size_t smem = stage * stages + 4 * EPI_WARP_SMEM + 1024;
-    long long tiles = (long long)((p.M + TC_BM - 1) / TC_BM) * ((p.N + p.bn - 1) / p.bn);
+    long long tiles = (long long)((p.M + tm - 1) / tm) * ((p.N + p.bn - 1) / p.bn);
     // Split of the contraction: every (tile, split) item is one pass of a persistent CTA, so the launch takes
     // ceil(items / SMs) rounds of ceil(ksteps / splits) k-steps each, plus a fixed cost per item (pipeline fill, the
     // partial tile written out, worth about four k-steps).  A split also pays for the reduce launch (eight k-steps) and
@@ -460,7 +552,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
     int splits = 1;
     const long long ksteps = (p.K + TC_BK - 1) / TC_BK;
     if (allow_split) {
-        const long long sms = rt().sm_count;
+        const long long sms = p.pair ? rt().sm_count / 2 : rt().sm_count;      // workers: CTAs, or pairs of them
         const double kstep_us = 0.25 * (ns == 1 ? 1 : (ns == 2 ? 3 : 6)) * p.bn / 128.0;
         const double partial_ksteps = (double)p.M * p.N * 4.0 / 5e6 / kstep_us;      // one pass over M x N floats, in k-steps
         long long maxs = ksteps / 2;                  // at least two k-steps per item
@@ -478,7 +570,7 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
     splits = (p.K + p.kchunk - 1) / p.kchunk;
     p.splits = splits;
     p.stages = stages;
-    p.by_mtiles = fast_div((p.M + TC_BM - 1) / TC_BM); p.by_ntiles = fast_div((p.N + p.bn - 1) / p.bn);
+    p.by_mtiles = fast_div((p.M + tm - 1) / tm); p.by_ntiles = fast_div((p.N + p.bn - 1) / p.bn);
     p.by_OHW = fast_div(p.OHW); p.by_OW = fast_div(p.OW); p.by_S = fast_div(p.S); p.by_cchunks = fast_div(p.cchunks);
     p.status = tc_status_word();
     p.wait_clocks = rt().tc_wait_clocks;
@@ -490,13 +582,14 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
         if (!p.partial) return SEERA_E_OOM;
     }
     long long all_tiles = tiles * splits;
-    dim3 grid((unsigned)(all_tiles < rt().sm_count ? all_tiles : rt().sm_count));     // persistent: one CTA per SM at most
+    const long long workers = p.pair ? rt().sm_count / 2 : rt().sm_count;
+    dim3 grid((unsigned)((all_tiles < workers ? all_tiles : workers) * (p.pair ? 2 : 1)));     // persistent: one CTA per SM at most
     cudaStream_t st = rt().stream;
     cudaError_t e;
     profile_begin();
-#define SEERA_TMA_LAUNCH(NSV)                                                                                              \
+#define SEERA_TMA_LAUNCH(NSV, PAIRV)                                                                                       \
     {                                                                                                                      \
-        auto kern = tma_gemm_kernel<NSV, CS>;                                                                              \
+        auto kern = tma_gemm_kernel<NSV, CS, PAIRV>;                                                                       \
         static int smem_set[64];                     /* per instantiation and device: raise the limit once */              \
         const int dev = rt().device & 63;                                                                                  \
         e = cudaSuccess;                                                                                                   \
@@ -505,11 +598,18 @@ int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, 
             if (e == cudaSuccess) smem_set[dev] = 1;                                                                       \
         }                                                                                                                  \
         if (e == cudaSuccess) {                                                                                            \
-            kern<<<grid, TG_THREADS, smem, st>>>(maps.a[0], maps.a[1], maps.a[2], maps.b[0], maps.b[1], maps.b[2], cs, p); \
-            e = cudaGetLastError();                                                                                        \
+            cudaLaunchConfig_t cfg = {};                                                                                   \
+            cfg.gridDim = grid; cfg.blockDim = dim3(TG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;             \
+            cudaLaunchAttribute attr[1];                                                                                   \
+            attr[0].id = cudaLaunchAttributeClusterDimension;                                                              \
+            attr[0].val.clusterDim.x = PAIRV ? 2 : 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;          \
+            cfg.attrs = attr; cfg.numAttrs = PAIRV ? 1 : 0;                                                                \
+            e = cudaLaunchKernelEx(&cfg, kern, maps.a[0], maps.a[1], maps.a[2], maps.b[0], maps.b[1], maps.b[2], cs, p);   \
+            if (e == cudaSuccess) e = cudaGetLastError();                                                                  \
         }                                                                                                                  \
     }
-    if (ns == 1) SEERA_TMA_LAUNCH(1) else if (ns == 2) SEERA_TMA_LAUNCH(2) else SEERA_TMA_LAUNCH(3)
+    if (p.pair) { if (ns == 1) SEERA_TMA_LAUNCH(1, true) else SEERA_TMA_LAUNCH(2, true) }
+    else if (ns == 1) SEERA_TMA_LAUNCH(1, false) else if (ns == 2) SEERA_TMA_LAUNCH(2, false) else SEERA_TMA_LAUNCH(3, false)
 #undef SEERA_TMA_LAUNCH
     count_launch();
     if (e == cudaSuccess && p.partial) {
@@ -533,13 +633,13 @@ int run_tma_gemm(const Shadow &sa, int a_mn, const Shadow &sb, int b_mn, const C
     p.M = M; p.N = N; p.K = K; p.a_mode = a_mn ? TMA_A_COLS : TMA_A_ROWS; p.b_mn = b_mn;
     p.a_fp16 = sa.enc.fmt; p.b_fp16 = sb.enc.fmt; p.out_scale = 1.f / (sa.enc.scale * sb.enc.scale);
     p.dinv = enc_dinv(sa.enc, sb.enc);
-    p.bn = tma_pick_bn(N, ns, b_mn);
+    tma_plan(p, ns, allow_split);
     TmaMaps maps;
     for (int i = 0; i < 3; i++) {
         int j = i < ns ? i : 0;
         // K-major: inner dimension = K (cols of the shadow), box 64 x rows-of-tile; MN-major: inner = M/N, box 64 x 64 k lines
         if (int s = make_map_2d(&maps.a[i], sa.p[j], sa.rows, sa.cols, sa.ld, 64, a_mn ? 64 : TC_BM)) return s;
-        if (int s = make_map_2d(&maps.b[i], sb.p[j], sb.rows, sb.cols, sb.ld, 64, b_mn ? 64 : p.bn)) return s;
+        if (int s = make_map_2d(&maps.b[i], sb.p[j], sb.rows, sb.cols, sb.ld, 64, b_mn ? 64 : (p.pair ? p.bn / 2 : p.bn))) return s;
     }
     return launch_tma_gemm(maps, p, cs, ns, allow_split, 2.0 * M * N * (double)K, name);
 }

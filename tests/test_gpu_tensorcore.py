@@ -89,6 +89,35 @@ def test_im2col_maps_of_tensors_below_128_kib(E, N, C, H, W):
     assert rel_l2(dX, rX) < TOL[1] and rel_l2(dW, rW) < TOL[1]
 
 
+@pytest.mark.parametrize("mode", [1, 4])
+def test_cta_pair_tiles_give_the_same_results(E, mode):
+    """The "pair_tiles" option (clusters of two CTAs on 256-row tiles, tcgen05 cta_group::2) against the single-CTA kernel:
+    Dense forward / dA / dB and convolution forward / dX / dW, shapes with full, partial and odd tiles."""
+    from ml_framework_b200 import capi
+    L = capi.load()
+    rs = np.random.RandomState(5 + mode)
+    cases = []
+    for (M, K, N) in ((512, 256, 256), (1000, 520, 130), (2048, 64, 64), (4096, 1024, 1024)):
+        A, B, dC = _prep(mode, *(rs.standard_normal(s).astype(np.float32) for s in ((M, K), (K, N), (M, N))))
+        cases.append(lambda A=A, B=B, dC=dC: (E.matmul(A, B),) + tuple(E.matmul_backward(A, B, dC)))
+    for shape in ((64, 64, 16, 16, 128, 3, 3, 1, 1, 1, 1), (32, 128, 8, 8, 256, 3, 3, 1, 1, 1, 1), (40, 32, 33, 31, 72, 3, 3, 2, 2, 1, 1)):
+        N, C, H, W, F, KH, KW, sh, sw, ph, pw = shape
+        X, Wt = _prep(mode, rs.standard_normal((N, C, H, W)).astype(np.float32), rs.standard_normal((F, C, KH, KW)).astype(np.float32))
+        OH, OW = (H + 2 * ph - KH) // sh + 1, (W + 2 * pw - KW) // sw + 1
+        dY, = _prep(mode, rs.standard_normal((N, F, OH, OW)).astype(np.float32))
+        cases.append(lambda X=X, Wt=Wt, dY=dY, g=(sh, sw, ph, pw): (E.conv2d_forward(X, Wt, *g),) + tuple(E.conv2d_backward(dY, X, Wt, *g)))
+    try:
+        for run in cases:
+            capi.check(L.seera_set_option(b"pair_tiles", 0))
+            want = run()
+            capi.check(L.seera_set_option(b"pair_tiles", 1))
+            got = run()
+            for a, b in zip(got, want):
+                assert rel_l2(a, b) < 2e-6          # same products; split-K chunking may differ, hence not bit-equal
+    finally:
+        capi.check(L.seera_set_option(b"pair_tiles", 0))
+
+
 def test_mode_4_weight_gradients_from_one_fp16_copy(E):
     """The default of mode 4 ("wgrad_single"): dW / dB from the first fp16 copy of each operand - one product, 2^-12 rounding
     per operand (a few 1e-4 here, where nothing averages; 3e-5 and less on the training configurations) - while the data
