@@ -291,6 +291,12 @@ int seera_conv2DTranspose_bias_act_fwd(const float *X, const float *W, const flo
  * (engine_cuda/src/convolution.cu:15-453). */
 typedef struct seera_shadow seera_shadow_t;
 void seera_shadow_free(seera_shadow_t *s);
+/* The same for Dense layers: row-major 16-bit copies of one [rows, cols] matrix (a layer's input, its weight matrix, or
+ * its output).  Opaque; owned by the caller once returned; release with seera_rows_free (stream-ordered, NULL allowed).
+ * No counterpart in the reference, whose cuda_matmul_bwd transposes both operands through HBM on every call
+ * (engine_cuda/src/GEMM.cu:164-225). */
+typedef struct seera_rows seera_rows_t;
+void seera_rows_free(seera_rows_t *r);
 /* seera_conv2d_bias_act_fwd with kept copies: x_in (may be NULL) are copies of `image` from an earlier call;
  * *x_keep (x_keep may be NULL) receives the copies this call produced, or NULL when it produced none (x_in was
  * used, or the shape does not run on copies: exact-fp32 mode, short patches, unsupported geometry). */
@@ -330,6 +336,18 @@ int seera_conv2d_act_bwd(const float *W, const float *X, const float *y, const f
  * stored local gradient plus broadcast_mul_4d + three cuda_sum_fwd (Seera_Engine.py:571-583, :43-65). */
 int seera_act_bias_bwd(const float *dy, const float *y, float *dz, float *dbias,
                        int size, int channels, int inner, int act);
+/* A Dense layer as two calls that convert nothing twice (tensor-core modes; in mode 0 they compose the plain entries).
+ * Forward: C = act(A B + bias) (Seera.py:133-138).  `a_in` (may be NULL): copies of A made by the layer before;
+ * `*a_keep`, `*w_keep` (may be NULL pointers): the copies of A and of B this call made, for the backward call;
+ * `*c_copies` (may be a NULL pointer): copies of C written by the same epilogue that stores C, for the next Dense layer.
+ * Backward of that layer (replaces Seera_Engine.py:571-583 + GEMM.cu:164-225): dz = g * act'(y) is formed straight into
+ * 16-bit copies together with dbias (no fp32 dz, no separate conversion of it), then dA = dz B^T and dB = A^T dz read
+ * those and the kept copies.  dA, dB or dbias may be NULL.  In the fp16 modes the gradient copies use the dynamic
+ * factor of the current backward pass (seera_grad_scale_update on the loss gradient). */
+int seera_matmul_bias_act_fwd_s(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, int act,
+                                seera_rows_t *a_in, seera_rows_t **a_keep, seera_rows_t **w_keep, seera_rows_t **c_copies);
+int seera_matmul_act_bwd(const float *A, const float *B, const float *y, const float *g, float *dA, float *dB,
+                         float *dbias, int M, int N, int K, int act, seera_rows_t *a_keep, seera_rows_t *w_keep);
 /* seera_act_bias_bwd for callers that must not allocate.  No counterpart in the reference.
  * Some hosts of this library cannot let a call reach cudaMalloc: code that runs between fixed memory budgets
  * (an inference server or a plugin that was handed its device memory up front), code on a latency path where a

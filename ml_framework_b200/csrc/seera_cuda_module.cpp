@@ -241,6 +241,17 @@ PYBIND11_MODULE(seera_cuda, m) {
                                             ph, pw, sh, sw, act, P<seera_shadow_t>(x_in), &keep, want_copies ? &pc : nullptr));
         return std::make_pair(reinterpret_cast<uptr>(keep), reinterpret_cast<uptr>(pc)); });
     m.def("shadow_free", [](uptr h) { seera_shadow_free(P<seera_shadow_t>(h)); });
+    m.def("rows_free", [](uptr h) { seera_rows_free(P<seera_rows_t>(h)); });
+    // Dense forward that keeps / hands on its operand copies: returns (a_keep, w_keep, c_copies) handles (0: none)
+    m.def("matmul_bias_act_fwd_s", [](uptr a, uptr b, uptr bias, uptr c, int M, int N, int K, int act, uptr a_in, bool want_c_copies) {
+        seera_rows_t *ak = nullptr, *wk = nullptr, *cc = nullptr;
+        ck(seera_matmul_bias_act_fwd_s(P<const F>(a), P<const F>(b), P<const F>(bias), P<F>(c), M, N, K, act, P<seera_rows_t>(a_in), &ak, &wk,
+                                       want_c_copies ? &cc : nullptr));
+        return py::make_tuple(reinterpret_cast<uptr>(ak), reinterpret_cast<uptr>(wk), reinterpret_cast<uptr>(cc)); });
+    m.def("matmul_act_bwd", [](uptr a, uptr b, uptr y, uptr g, uptr da, uptr db, uptr dbias, int M, int N, int K, int act, uptr a_keep,
+                               uptr w_keep) {
+        ck(seera_matmul_act_bwd(P<const F>(a), P<const F>(b), P<const F>(y), P<const F>(g), P<F>(da), P<F>(db), P<F>(dbias), M, N, K, act,
+                                P<seera_rows_t>(a_keep), P<seera_rows_t>(w_keep))); });
     m.def("conv2d_act_bwd", [](uptr w, uptr x, uptr y, uptr g, uptr gp, uptr mask, uptr yp, uptr dx, uptr dw, uptr db, int N, int C, int H,
                                int W, int Fo, int R, int S, int sh, int sw, int ph, int pw, int act, uptr x_shadow) {
         ck(seera_conv2d_act_bwd(P<const F>(w), P<const F>(x), P<const F>(y), P<const F>(g), P<const F>(gp), P<const int>(mask),

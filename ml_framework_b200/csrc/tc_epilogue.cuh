@@ -22,6 +22,14 @@ __device__ __forceinline__ float epilogue_act(float z, int act) {
     }
 }
 
+// Output functors that also keep 16-bit copies of what they store expose copy_out(m, n, value); the others do not.
+template <class CS>
+__device__ __forceinline__ auto maybe_copy_out(const CS &cs, int m, int n, float v, int) -> decltype(cs.copy_out(m, n, v), void()) {
+    cs.copy_out(m, n, v);
+}
+template <class CS>
+__device__ __forceinline__ void maybe_copy_out(const CS &, int, int, float, long) {}
+
 template <class CS>
 __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, int col_base, int c_begin, int c_end,
                                                   int M, int N, const CS &cs, float *partial, long long partial_off,
@@ -96,7 +104,8 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, 
                     for (int r = 0; r < 32; r++) {
                         if (row_base + r < M) {
                             float *rp = cs.row(row_base + r);
-                            if (rp) rp[n * sn] = fuse ? epilogue_act(stage[r * 33 + lane] + b, act) : stage[r * 33 + lane];
+                            const float val = fuse ? epilogue_act(stage[r * 33 + lane] + b, act) : stage[r * 33 + lane];
+                            if (rp) { rp[n * sn] = val; maybe_copy_out(cs, row_base + r, n, val, 0); }
                         }
                     }
                 }

@@ -136,6 +136,12 @@ tensor = Tensor
 # can do it; the convolution's own full-resolution output is then never materialised.  Set to False to keep every
 # layer's output in memory.
 FUSE_POOL = True
+# A Dense layer that feeds another Dense layer can have its GEMM epilogue write the 16-bit copies of its output that the next
+# layer's GEMM reads (seera_matmul_bias_act_fwd_s, c_copies).  Off: at the sizes measured (4096 x 1024 outputs, one tile per
+# CTA) the two-byte stores lengthen an epilogue that nothing overlaps by more than the next layer's vectorised conversion
+# launch costs (MLP configuration: step 0.317 ms with it, 0.287 ms without).
+import os as _os
+DENSE_EPILOGUE_COPIES = _os.environ.get("SEERA_DENSE_EPILOGUE_COPIES", "0") != "0"
 
 
 class _PooledGrad:
@@ -164,6 +170,21 @@ class _KeptCopies:
     def release(self):
         if self.h:
             sc.shadow_free(self.h)
+            self.h = 0
+
+    __del__ = release
+
+
+class _KeptRows:
+    """Owner of row-major operand copies a Dense forward call kept or handed on (0: none)."""
+    __slots__ = ("h",)
+
+    def __init__(self):
+        self.h = 0
+
+    def release(self):
+        if self.h:
+            sc.rows_free(self.h)
             self.h = 0
 
     __del__ = release
@@ -289,7 +310,7 @@ class _ParamLayer(Layer):
             sc.cuda_elemadd(t.value.main_ptr, neg.main_ptr, t.value.main_ptr, t.value.size)
 
     # fused epilogue / prologue shared by Dense, Conv2D, ConvTranspose2D
-    def _finish_forward(self, x, z, channels, inner, product, contraction_backward, fused_backward=None):
+    def _finish_forward(self, x, z, channels, inner, product, contraction_backward, fused_backward=None, takes_pooled=False):
         """product(bias_ptr, act_code) fills z with act(contraction + bias) in one call; this wraps z as the layer's
         output Tensor and attaches the backward closure."""
         act = self.layeract
@@ -318,7 +339,7 @@ class _ParamLayer(Layer):
             node = out
         node._parents = (x, W, b)
 
-        node._takes_pooled = fused_backward is not None
+        node._takes_pooled = takes_pooled and fused_backward is not None
 
         def layer_backward(g, y=node.value, code=code):
             db = b._grad_target()
@@ -362,6 +383,11 @@ class Dense(_ParamLayer):
         self.weights = Tensor(self._w_init, is_leaf=True)
         self.bais = Tensor(self._b_init, is_leaf=True)
 
+    def __call__(self, input_layer):
+        super().__call__(input_layer)
+        input_layer._feeds_dense = True       # a Dense producer then also emits the row-major copies of its output this layer reads
+        return self
+
     def forward(self):
         x = self.inputs = self.inpobj.outputs
         xv, W = x.value, self.weights.value
@@ -369,16 +395,34 @@ class Dense(_ParamLayer):
             raise ValueError(f"[cuTen]: matmul: inner dimensions must agree, got {xv.shape} @ {W.shape}")
         M, K, N = xv.shape[0], self.in_units, self.out_units
         z = _new((M, N))
+        kept = {"a": _KeptRows(), "w": _KeptRows()}
+        given = getattr(x, "_rows", None) if x.value is xv else None        # copies written by the Dense layer before
+        out_rows = _KeptRows()
+        want_out = DENSE_EPILOGUE_COPIES and bool(getattr(self, "_feeds_dense", False)) and self.layeract != "softmax"
 
         def product(bias, code):
-            sc.matmul_bias_act_fwd(xv.main_ptr, W.main_ptr, bias, z.main_ptr, M, N, K, code)
+            kept["a"].h, kept["w"].h, out_rows.h = sc.matmul_bias_act_fwd_s(xv.main_ptr, W.main_ptr, bias, z.main_ptr, M, N, K, code,
+                                                                             given.h if given else 0, want_out)
+
+        def fused_backward(g, y, code, db, need_dx=not x.is_leaf):
+            # activation slope, bias gradient, dA and dB in one call; it reads the copies the forward call kept
+            dw = self.weights._grad_target()
+            dx = _new(xv.shape) if need_dx else None
+            sc.matmul_act_bwd(xv.main_ptr, W.main_ptr, y.main_ptr if code else 0, g.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
+                              db.main_ptr, M, N, K, code, kept["a"].h or (given.h if given else 0), kept["w"].h)
+            kept["a"].release(); kept["w"].release()
+            if given:
+                given.release()
+            return dx, dw
 
         def contraction_backward(dz, need_dx=not x.is_leaf):
             dw = self.weights._grad_target()
             dx = _new(xv.shape) if need_dx else None
             sc.cuda_matmul_bwd(xv.main_ptr, W.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr, M, N, K, 1)
             return dx, dw
-        self.outputs = self._finish_forward(x, z, N, 1, product, contraction_backward)
+        self.outputs = self._finish_forward(x, z, N, 1, product, contraction_backward, fused_backward)
+        if want_out:
+            self.outputs._rows = out_rows
         return self.outputs
 
     def __repr__(self):
@@ -459,7 +503,7 @@ class Conv2D(_ParamLayer):
             sc.cuda_conv2d_bwd(W.main_ptr, xv.main_ptr, dz.main_ptr, dx.main_ptr if need_dx else 0, dw.main_ptr,
                                N, C, H, Wd, F, KH, KW, sh, sw, ph, pw)
             return dx, dw
-        self.outputs = self._finish_forward(x, z, F, OH * OW, product, contraction_backward, fused_backward)
+        self.outputs = self._finish_forward(x, z, F, OH * OW, product, contraction_backward, fused_backward, takes_pooled=True)
         return self.outputs
 
     def __repr__(self):
