@@ -430,6 +430,7 @@ int seera_sgd_step_dev(float *w, const float *g, float *vel, int n, const float 
  *   seera_dp_wait_host   host-side wait for both streams with a deadline in milliseconds (< 0: none); on expiry
  *                        or on an NCCL error the communicator is aborted and an error status returned - a peer
  *                        that left becomes a status code on the host, never a wait inside a kernel
+ *   seera_dp_abort       drops the communicator without talking to the peers (one of them is known to be gone)
  *   seera_dp_finalize    destroys the communicator and frees seera_dp_alloc blocks still held */
 int   seera_dp_unique_id_bytes(void);
 int   seera_dp_unique_id(void *out, int size);
@@ -445,6 +446,7 @@ int   seera_dp_reduce_range(float *arena, long long begin, long long end);
 int   seera_dp_join(void);
 int   seera_dp_poll(void);
 int   seera_dp_wait_host(int timeout_ms);
+int   seera_dp_abort(void);
 int   seera_dp_finalize(void);
 
 #ifdef __cplusplus

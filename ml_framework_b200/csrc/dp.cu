@@ -306,6 +306,19 @@ int seera_dp_wait_host(int timeout_ms) {
     return status;
 }
 
+/* Drops the communicator without talking to the peers (ncclCommAbort): the way out when one of them is known to be gone.
+ * Blocks seera_dp_alloc handed out stay allocated until the process ends. */
+int seera_dp_abort(void) {
+    Dp &d = dp();
+    if (!d.comm) return SEERA_OK;
+    d.api.CommAbort(d.comm);
+    d.comm = nullptr;
+    d.pending = false;
+    d.regs.clear();
+    d.world = 1; d.rank = 0;
+    return SEERA_OK;
+}
+
 int seera_dp_finalize(void) {
     Dp &d = dp();
     if (!d.comm) return SEERA_OK;

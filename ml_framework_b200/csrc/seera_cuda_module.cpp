@@ -295,5 +295,6 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("dp_join", []() { ck(seera_dp_join()); });
     m.def("dp_poll", []() { ck(seera_dp_poll()); });
     m.def("dp_wait_host", [](int timeout_ms) { py::gil_scoped_release nogil; ck(seera_dp_wait_host(timeout_ms)); });
+    m.def("dp_abort", []() { ck(seera_dp_abort()); });
     m.def("dp_finalize", []() { ck(seera_dp_finalize()); });
 }

@@ -203,6 +203,14 @@ def replicas_differ_by(model):
         sc.cuda_free(lo)
 
 
+def abort():
+    """Leave the job without talking to the peers: for a rank that has learnt (Rendezvous.check) that one of them is gone."""
+    global _group
+    from . import seera_cuda as sc
+    sc.dp_abort()
+    _group = None
+
+
 def finalize():
     global _group
     from . import seera_cuda as sc
