@@ -108,6 +108,11 @@ int         seera_get_precision(void);
  *       copy of each operand alone - one product instead of three.  Its 2^-12 rounding stays inside that one tensor
  *       (nothing downstream in the backward pass reads dW); measured on the VGG configuration it moves no dW error
  *       by more than 3e-5.  Data gradients keep all three products: their rounding would compound layer by layer.
+ *   "skinny_gemm" (default 1): in precision modes 1-5 a Dense product of at most 16 output columns (a classifier head: the
+ *       forward, dA and dB of seera_cuda_matmul[_bwd] and of the fused Dense entries) runs as plain fp32 on the CUDA cores,
+ *       one small launch each, reading the fp32 operands in place: no conversion passes, no pipeline fill for a tile that is
+ *       mostly padding.  Results are fp32-exact (operands are not rounded to 16 bits) and bit-reproducible; the Dense entries
+ *       keep no 16-bit copies for such a layer.  0 sends these products to the tensor cores like any other.
  *   "tc_wait_ms" (1..60000, default 2000; also SEERA_TC_WAIT_MS): budget of every wait inside the TMA-fed tensor-core
  *       kernel, in milliseconds at ~2 GHz.  A wait that runs out makes the kernel record its code in the status word
  *       (seera_tc_device_status), let the copies already in flight land (bounded), free its TMEM and return.

@@ -518,6 +518,85 @@ __global__ void __launch_bounds__(256, 4) dz_shadow_window_kernel(const float *_
         }
     }
 }
+
+// The same for layers whose pooled image holds fewer than 32 windows (a power of two of them: 4 x 4, 2 x 2, 4 x 2 ... pooled
+// images deep in a network).  With lane = window most lanes of the kernel above would idle.  Here a tile is 32 / Pq whole images
+// x 64 channels: per image those are 64 * Pq CONSECUTIVE floats of each quarter-resolution tensor, read flat (fully coalesced),
+// turned to (window, channel) order in shared memory and written like above.  The bias gradient is summed on the write side.
+template <int NS>
+__global__ void __launch_bounds__(256, 3) dz_shadow_window_small_kernel(const float *__restrict__ gp, const int *__restrict__ mask,
+                                                                        const float *__restrict__ yp, int NB, int C, int H, int W, int Cp,
+                                                                        int items, int lgPq, int act, __nv_bfloat16 *__restrict__ d0,
+                                                                        __nv_bfloat16 *__restrict__ d1, __nv_bfloat16 *__restrict__ d2,
+                                                                        float *__restrict__ partial, Enc enc) {
+    __shared__ __align__(16) float sval[32][64 + 4];
+    __shared__ __align__(16) int smk[32][64 + 4];
+    const int P = H * W, Wq = W >> 1, Pq = 1 << lgPq, ipt = 32 >> lgPq, cb0 = blockIdx.y * 64;
+    const int ch = threadIdx.x & 7, c8 = cb0 + ch * 8, w = threadIdx.x >> 3;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.f;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        float val[8], pv[8];
+        int mk[8];
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int e = it * 256 + threadIdx.x, q = e & (Pq - 1), cl = (e >> lgPq) & 63, img = item * ipt + (e >> (lgPq + 6));
+            const bool ok = img < NB && cb0 + cl < C;
+            const long long o = ((long long)min(img, NB - 1) * C + min(cb0 + cl, C - 1)) * Pq + q;
+            val[it] = ok ? __ldg(gp + o) : 0.f;
+            mk[it] = ok ? __ldg(mask + o) : -1;
+            pv[it] = (ok && act != SEERA_ACT_NONE) ? __ldg(yp + o) : 1.f;
+        }
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int e = it * 256 + threadIdx.x, q = e & (Pq - 1), cl = (e >> lgPq) & 63, il = e >> (lgPq + 6);
+            if (act != SEERA_ACT_NONE) val[it] *= slope_from_output(pv[it], act);
+            sval[il * Pq + q][cl] = val[it];
+            smk[il * Pq + q][cl] = mk[it];
+        }
+        __syncthreads();
+        const int img = item * ipt + (w >> lgPq), qq = w & (Pq - 1);
+        if (c8 < Cp && img < NB) {
+            const float4 a = *reinterpret_cast<const float4 *>(&sval[w][ch * 8]), b = *reinterpret_cast<const float4 *>(&sval[w][ch * 8 + 4]);
+            const int4 ma = *reinterpret_cast<const int4 *>(&smk[w][ch * 8]), mb = *reinterpret_cast<const int4 *>(&smk[w][ch * 8 + 4]);
+            const float vv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            const int mm[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+            const int ohq = qq / Wq, owq = qq - ohq * Wq;
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[i] += ((unsigned)mm[i] < 4u) ? vv[i] : 0.f;
+#pragma unroll
+            for (int pos = 0; pos < 4; pos++) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = mm[i] == pos ? vv[i] : 0.f;
+                const int p = (2 * ohq + (pos >> 1)) * W + 2 * owq + (pos & 1);
+                const long long o = ((long long)img * P + p) * Cp + c8;
+                store_split8<NS>(v, enc, d0 + o, d1 + o, d2 + o);
+            }
+        }
+        __syncthreads();
+    }
+    if (partial) {
+        // threads with the same ch hold sums of the same eight channels: lanes ch, ch + 8, ch + 16, ch + 24 of each warp
+        float *red = &sval[0][0];                      // [8 warps][8 chunks][8 channels]
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float t = acc[i];
+            t += __shfl_xor_sync(0xffffffffu, t, 8);
+            t += __shfl_xor_sync(0xffffffffu, t, 16);
+            if (lane < 8) red[(warp * 8 + lane) * 8 + i] = t;
+        }
+        __syncthreads();
+        if (threadIdx.x < 64) {
+            float t = 0.f;
+#pragma unroll
+            for (int wv = 0; wv < 8; wv++) t += red[wv * 64 + threadIdx.x];
+            if (cb0 + threadIdx.x < C) partial[(long long)blockIdx.x * C + cb0 + threadIdx.x] = t;
+        }
+    }
+}
 // out[c] = sum over splits of partial[s][c]: one warp per channel, lanes stride over the splits, then a shuffle tree.
 __global__ void __launch_bounds__(256) dz_bias_sum_kernel(const float *__restrict__ partial, float *__restrict__ out, int channels, int splits) {
     const int lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -817,8 +896,12 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
     size_t bytes = (size_t)NB * H * W * out.Cp * 2;
     for (int i = 0; i < ns; i++) { out.p[i] = (__nv_bfloat16 *)scratch_alloc(bytes); if (!out.p[i]) return SEERA_E_OOM; }
     const bool by_window = gp && (yp || act == SEERA_ACT_NONE);
-    const int P = H * W, ptiles = by_window ? ((H / 2) * (W / 2) + 31) / 32 : (P + 31) / 32, cchunks = (out.Cp + 63) / 64;
-    const long long items = (long long)NB * ptiles;
+    const int Pq = (H / 2) * (W / 2);
+    const bool small = by_window && Pq >= 1 && Pq < 32 && (Pq & (Pq - 1)) == 0;     // several whole images per 32-window tile
+    int lgPq = 0;
+    while (small && (1 << lgPq) < Pq) lgPq++;
+    const int P = H * W, ptiles = by_window ? (Pq + 31) / 32 : (P + 31) / 32, cchunks = (out.Cp + 63) / 64;
+    const long long items = small ? (NB + (32 / Pq) - 1) / (32 / Pq) : (long long)NB * ptiles;
     int splits = rt().sm_count * 4 / cchunks;           // one round of resident blocks (4 per SM)
     if (splits < 1) splits = 1;
     if (splits > items) splits = (int)items;
@@ -832,7 +915,11 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
     const double in_bytes = by_window ? 4.0 * NB * C * (P / 4) * (2 + (yp ? 1 : 0))
                                       : 4.0 * NB * C * ((g ? (double)P : 2.0 * (P / 4)) + (act ? (double)P : 0.0));
     ProfBytes pb(in_bytes + (double)ns * bytes, by_window ? "dz_shadow_window" : "dz_shadow");
-    if (by_window) {
+    if (small) {
+        if (ns == 1) dz_shadow_window_small_kernel<1><<<grid, 256, 0, st>>>(gp, mask, yp, NB, C, H, W, out.Cp, (int)items, lgPq, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
+        else if (ns == 2) dz_shadow_window_small_kernel<2><<<grid, 256, 0, st>>>(gp, mask, yp, NB, C, H, W, out.Cp, (int)items, lgPq, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
+        else dz_shadow_window_small_kernel<3><<<grid, 256, 0, st>>>(gp, mask, yp, NB, C, H, W, out.Cp, (int)items, lgPq, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
+    } else if (by_window) {
         if (ns == 1) dz_shadow_window_kernel<1><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
         else if (ns == 2) dz_shadow_window_kernel<2><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);
         else dz_shadow_window_kernel<3><<<grid, 256, 0, st>>>(gp, mask, yp, C, H, W, out.Cp, (int)items, ptiles, act, out.p[0], out.p[1], out.p[2], partial, out.enc);

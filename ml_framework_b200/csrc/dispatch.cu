@@ -15,6 +15,7 @@ extern "C" {
 
 int seera_set_option(const char *name, int value) {
     if (!name) return fail(SEERA_E_ARG, "set_option: null name");
+    if (!strcmp(name, "skinny_gemm")) { rt().skinny_gemm = value != 0; return SEERA_OK; }
     if (!strcmp(name, "dense_tma")) { rt().dense_tma = value != 0; return SEERA_OK; }
     if (!strcmp(name, "conv_tma")) { rt().conv_tma = value != 0; return SEERA_OK; }
     if (!strcmp(name, "pair_tiles")) { rt().pair_tiles = value != 0; return SEERA_OK; }
@@ -39,10 +40,16 @@ int seera_set_option(const char *name, int value) {
     return fail(SEERA_E_ARG, "set_option: unknown option '%s'", name);
 }
 
+// a product of at most 16 output columns runs as exact fp32 on the CUDA cores in every mode (gemm_skinny.cu)
+static bool skinny_ok(const void *a, const void *b, const void *c, int M, int N, int K, int Nbatch) {
+    return a && b && c && M >= 1 && Nbatch >= 1 && !seera::ensure_init() && seera::skinny_applies(M, N, K, Nbatch);
+}
 int seera_cuda_matmul(const float *A, const float *B, float *C, int M, int N, int K, int Nbatch) {
+    if (skinny_ok(A, B, C, M, N, K, Nbatch)) return seera::skinny_fwd(A, B, nullptr, C, M * Nbatch, N, K, SEERA_ACT_NONE, "cuda_matmul");
     return rt().precision ? (rt().dense_tma ? seera_tma_matmul(A, B, C, M, N, K, Nbatch) : seera_tc_matmul(A, B, C, M, N, K, Nbatch)) : seera_simt_matmul(A, B, C, M, N, K, Nbatch);
 }
 int seera_cuda_matmul_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB, int M, int N, int K, int Nbatch) {
+    if (skinny_ok(A, B, dC, M, N, K, Nbatch)) return seera::skinny_bwd(A, B, dC, dA, dB, nullptr, M * Nbatch, N, K);
     return rt().precision ? (rt().dense_tma ? seera_tma_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch) : seera_tc_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch)) : seera_simt_matmul_bwd(A, B, dC, dA, dB, M, N, K, Nbatch);
 }
 int seera_cuda_conv2d_fwd(const float *image, const float *kernel, float *out, int batchN, int C, int H, int W, int F, int R, int S,
@@ -70,6 +77,7 @@ static int bias_act_after(int s, float *y, const float *bias, long long size, in
     return seera_bias_act_fwd(y, bias, y, (int)size, channels, inner, act);
 }
 int seera_matmul_bias_act_fwd(const float *A, const float *B, const float *bias, float *C, int M, int N, int K, int act) {
+    if (skinny_ok(A, B, C, M, N, K, 1)) return seera::skinny_fwd(A, B, bias, C, M, N, K, act, "cuda_matmul");
     if (rt().precision && rt().dense_tma) return seera_tma_matmul_bias_act(A, B, bias, C, M, N, K, 1, act);
     return bias_act_after(seera_cuda_matmul(A, B, C, M, N, K, 1), C, bias, (long long)M * N, N, 1, act);
 }

@@ -182,7 +182,7 @@ int seera_matmul_bias_act_fwd_s(const float *A, const float *B, const float *bia
     if (a_keep) *a_keep = nullptr;
     if (w_keep) *w_keep = nullptr;
     if (c_copies) *c_copies = nullptr;
-    if (!dense_keeps()) return seera_matmul_bias_act_fwd(A, B, bias, C, M, N, K, act);
+    if (!dense_keeps() || skinny_applies(M, N, K, 1)) return seera_matmul_bias_act_fwd(A, B, bias, C, M, N, K, act);
     if (M < 1 || N < 1 || K < 1 || !A || !B || !C) return fail(SEERA_E_ARG, "matmul_bias_act_fwd: bad argument");
     const int ns = precision_copies();
     Shadow sa_local, sb, sc;
@@ -216,7 +216,8 @@ int seera_matmul_act_bwd(const float *A, const float *B, const float *y, const f
     SEERA_ENSURE();
     if (M < 1 || N < 1 || K < 1 || !A || !B || !g || (act != SEERA_ACT_NONE && !y))
         return fail(SEERA_E_ARG, "matmul_act_bwd: bad argument");
-    if (!dense_keeps()) {          // composition of the separate entries
+    if (act == SEERA_ACT_NONE && skinny_applies(M, N, K, 1)) return skinny_bwd(A, B, g, dA, dB, dbias, M, N, K);
+    if (!dense_keeps() || skinny_applies(M, N, K, 1)) {          // composition of the separate entries
         float *dz = (float *)scratch_alloc((size_t)M * N * sizeof(float));
         if (!dz) return SEERA_E_OOM;
         int s = seera_act_bias_bwd(g, y, dz, dbias, M * N, N, 1, act);

@@ -43,6 +43,11 @@ namespace seera {
 bool conv_first_pool_ok(int NB, int C, int H, int W, int F, int R, int S, int sh, int sw, int ph, int pw);
 int conv_first_pool_fwd(const float *X, const float *Wt, const float *bias, const PoolOut &pool, int NB, int C, int H, int W, int F, int R,
                         int S, int ph, int pw, int sh, int sw, int act, const char *name);
+// Dense products of at most 16 output columns, exact fp32 on the CUDA cores (gemm_skinny.cu).  rows = M * batch; bias, dA, dB and
+// dbias may be null (dbias = the column sums of dC).
+bool skinny_applies(int M, int N, int K, int Nbatch);
+int skinny_fwd(const float *A, const float *B, const float *bias, float *C, int rows, int N, int K, int act, const char *name);
+int skinny_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB, float *dbias, int rows, int N, int K);
 // Direct fp32 kernel for unit-stride (transposed) convolutions with 1, 2 or 4 output channels (conv_few.cu); bias may be null.
 bool conv_few_applies(int NB, int C, int F, int R, int S, int OH, int OW);
 int conv_few_fwd(const float *X, const float *Wt, const float *bias, float *Y, int NB, int C, int H, int W, int F, int R, int S, int PH,

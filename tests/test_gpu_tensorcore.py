@@ -29,8 +29,10 @@ def E():
     L = capi.load()
     capi.check(L.seera_init(capi.default_device()))
     capi.check(L.seera_set_option(b"wgrad_single", 0))        # mode 4 at its full three products, weight gradients included
+    capi.check(L.seera_set_option(b"skinny_gemm", 0))         # products of few output columns on the tensor cores too
     yield engine_np
     capi.check(L.seera_set_option(b"wgrad_single", 1))
+    capi.check(L.seera_set_option(b"skinny_gemm", 1))
     assert L.seera_tc_device_status() == 0            # no bounded wait ever expired
     L.seera_set_precision(0)
 
@@ -54,6 +56,53 @@ def test_matmul_and_backward(E, mode, M, K, N):
     dA, dB = E.matmul_backward(A, B, dC)
     assert rel_l2(dA, dC.astype(np.float64) @ B.T.astype(np.float64)) < TOL[mode]
     assert rel_l2(dB, A.T.astype(np.float64) @ dC.astype(np.float64)) < TOL[mode]
+
+
+@pytest.mark.parametrize("mode", [1, 4])
+@pytest.mark.parametrize("M,K,N,batch", [(1, 1, 1, 1), (5, 7, 3, 1), (64, 784, 10, 1), (512, 256, 10, 1), (4096, 1024, 10, 1), (33, 300, 16, 3),
+                                         (1000, 513, 7, 1), (70000, 24, 2, 1)])
+def test_products_of_few_output_columns_are_exact_fp32_in_every_mode(E, mode, M, K, N, batch):
+    """By default a product of at most 16 output columns (a classifier head) runs as fp32 on the CUDA cores whatever the precision
+    mode: the plain entries, the fused forward and the one-call backward with its bias gradient all agree with double precision
+    to fp32 rounding, the operands are NOT rounded to the mode's 16-bit type, and two runs give the same bits."""
+    import ctypes
+    from ml_framework_b200 import capi
+    from engine_np import _Dev
+    L = capi.load()
+    L.seera_set_precision(mode)
+    capi.check(L.seera_set_option(b"skinny_gemm", 1))
+    try:
+        rs = np.random.RandomState(M + K + N)
+        A = rs.standard_normal((batch, M, K)).astype(np.float32)
+        B = (rs.standard_normal((K, N)) * 0.1).astype(np.float32)
+        bias, g = rs.standard_normal(N).astype(np.float32), rs.standard_normal((batch, M, N)).astype(np.float32)
+        A64, B64, g64 = A.reshape(-1, K).astype(np.float64), B.astype(np.float64), g.reshape(-1, N).astype(np.float64)
+        with _Dev() as d:
+            pa, pb, pbias, pg = d.up(A), d.up(B), d.up(bias), d.up(g)
+            c, da, db, dbias = d.new(batch * M * N), d.new(batch * M * K), d.new(K * N), d.new(N)
+            capi.check(L.seera_cuda_matmul(pa, pb, c, M, N, K, batch))
+            assert rel_l2(d.down(c, (batch * M, N)), A64 @ B64) < 2e-6
+            capi.check(L.seera_cuda_matmul_bwd(pa, pb, pg, da, db, M, N, K, batch))
+            first = d.down(db, (K, N)).copy()
+            assert rel_l2(d.down(da, (batch * M, K)), g64 @ B64.T) < 2e-6
+            assert rel_l2(first, A64.T @ g64) < 2e-6
+            capi.check(L.seera_cuda_matmul_bwd(pa, pb, pg, da, db, M, N, K, batch))
+            assert np.array_equal(first, d.down(db, (K, N)))
+            if batch == 1:
+                capi.check(L.seera_matmul_bias_act_fwd(pa, pb, pbias, c, M, N, K, 1))
+                y = d.down(c, (M, N))
+                assert rel_l2(y, np.maximum(A64 @ B64 + bias, 0)) < 2e-6
+                ak, wk = ctypes.c_void_p(), ctypes.c_void_p()
+                capi.check(L.seera_matmul_bias_act_fwd_s(pa, pb, pbias, c, M, N, K, 1, None, ctypes.byref(ak), ctypes.byref(wk), None))
+                assert not ak.value and not wk.value and np.array_equal(y, d.down(c, (M, N)))
+                for act, slope in ((0, np.ones((M, N))), (1, (y > 0).astype(np.float64))):
+                    capi.check(L.seera_matmul_act_bwd(pa, pb, c, pg, da, db, dbias, M, N, K, act, None, None))
+                    dz = g64 * slope
+                    assert rel_l2(d.down(dbias, (N,)), dz.sum(axis=0)) < 1e-5
+                    assert rel_l2(d.down(da, (M, K)), dz @ B64.T) < 2e-6
+                    assert rel_l2(d.down(db, (K, N)), A64.T @ dz) < 2e-6
+    finally:
+        capi.check(L.seera_set_option(b"skinny_gemm", 0))
 
 
 CONV = [(1, 1, 5, 5, 1, 3, 3, 1, 1, 0, 0), (2, 3, 8, 8, 4, 3, 3, 1, 1, 1, 1), (3, 5, 9, 7, 6, 3, 3, 2, 1, 1, 2),
@@ -233,10 +282,12 @@ def _dact_ref(y, act):
 
 
 # (N, C, H, W, F, KH, KW, sh, sw, ph, pw): tensor-core shapes (kept copies, dz never stored), short-patch shapes (the
-# bias gradient rides in a spare patch column; none spare when C*KH*KW is 16) and a strided one.
+# bias gradient rides in a spare patch column; none spare when C*KH*KW is 16), a strided one and tiny pooled images.
 LAYER_BWD = [(4, 16, 8, 8, 24, 3, 3, 1, 1, 1, 1), (2, 70, 12, 12, 130, 3, 3, 1, 1, 1, 1), (3, 8, 16, 16, 16, 3, 3, 2, 2, 1, 1),
              (4, 3, 16, 16, 20, 3, 3, 1, 1, 1, 1), (2, 1, 12, 12, 6, 4, 4, 1, 1, 2, 2), (2, 1, 8, 8, 70, 3, 3, 1, 1, 1, 1),
-             (3, 3, 16, 16, 64, 3, 3, 1, 1, 1, 1), (2, 1, 8, 12, 128, 3, 3, 1, 1, 1, 1), (70, 2, 6, 6, 64, 3, 3, 1, 1, 1, 1)]
+             (3, 3, 16, 16, 64, 3, 3, 1, 1, 1, 1), (2, 1, 8, 12, 128, 3, 3, 1, 1, 1, 1), (70, 2, 6, 6, 64, 3, 3, 1, 1, 1, 1),
+             # pooled images of 4, 1 and 8 windows: several whole images per tile of the pooled-gradient kernel, ragged at the end
+             (13, 16, 4, 4, 130, 3, 3, 1, 1, 1, 1), (37, 16, 2, 2, 72, 3, 3, 1, 1, 1, 1), (3, 32, 4, 8, 24, 3, 3, 1, 1, 1, 1)]
 
 
 @pytest.mark.parametrize("mode", [2, 3])
