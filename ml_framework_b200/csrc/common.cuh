@@ -47,6 +47,33 @@ inline int stride_grid(long long work_items, int threads = 256) {
 
 inline void count_launch(int n = 1) { rt().launches += n; }
 
+// out[c] = sum over s < splits of partial[s * n + c], added in a fixed order (the same bits on every run).  A block owns 32
+// consecutive columns; its eight warps take the splits w, w + 8, ... (128-byte coalesced reads, splits / 8 dependent loads
+// instead of `splits`), then the eight sums are added in warp order.  Columns at or beyond n_first go to out2 (may be null).
+static __global__ void __launch_bounds__(256) sum_splits_kernel(const float *__restrict__ partial, float *__restrict__ out,
+                                                                float *__restrict__ out2, int n_first, int n, int splits) {
+    __shared__ float sm[8][33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, c = blockIdx.x * 32 + lane;
+    float t = 0.f;
+    if (c < n) {
+#pragma unroll 4
+        for (int s = warp; s < splits; s += 8) t += __ldg(partial + (long long)s * n + c);
+    }
+    sm[warp][lane] = t;
+    __syncthreads();
+    if (warp == 0 && c < n) {
+        float r = sm[0][lane];
+#pragma unroll
+        for (int w = 1; w < 8; w++) r += sm[w][lane];
+        if (c < n_first) out[c] = r;
+        else if (out2) out2[c - n_first] = r;
+    }
+}
+inline void launch_sum_splits(const float *partial, float *out, int n, int splits, cudaStream_t st, float *out2 = nullptr, int n_first = -1) {
+    sum_splits_kernel<<<(n + 31) / 32, 256, 0, st>>>(partial, out, out2, n_first < 0 ? n : n_first, n, splits);
+    count_launch();
+}
+
 #define SEERA_ENSURE()                      \
     do {                                    \
         int _s = seera::ensure_init();      \

@@ -597,17 +597,6 @@ __global__ void __launch_bounds__(256, 3) dz_shadow_window_small_kernel(const fl
         }
     }
 }
-// out[c] = sum over splits of partial[s][c]: one warp per channel, lanes stride over the splits, then a shuffle tree.
-__global__ void __launch_bounds__(256) dz_bias_sum_kernel(const float *__restrict__ partial, float *__restrict__ out, int channels, int splits) {
-    const int lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (c >= channels) return;
-    float t = 0.f;
-    for (int s = lane; s < splits; s += 32) t += partial[(long long)s * channels + c];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (lane == 0) out[c] = t;
-}
-
 // ---- 2x2 / stride-2 max-pool that also writes the channels-last copies of its output ---------------------------
 // Same thread layout as dz_shadow_kernel (warp = 8 channels, lane = output pixel).  The scan order and the strict
 // comparison match cuda_maxpool_fwd, so values and window-local argmax indices are the same bit for bit.
@@ -930,8 +919,7 @@ static int make_dz_shadow(const float *g, const float *gp, const int *mask, cons
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess && dbias) {
-        dz_bias_sum_kernel<<<(C + 7) / 8, 256, 0, st>>>(partial, dbias, C, splits);
-        count_launch();
+        launch_sum_splits(partial, dbias, C, splits, st);
         e = cudaGetLastError();
     }
     if (partial) scratch_free(partial);

@@ -146,15 +146,6 @@ __global__ void __launch_bounds__(256) act_bias_bwd_rows_kernel(const float *__r
     }
 }
 
-__global__ void __launch_bounds__(256) sum_partials_kernel(const float *__restrict__ partial, float *__restrict__ out,
-                                                           int channels, int splits) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= channels) return;
-    float t = 0.f;
-    for (int s = 0; s < splits; s++) t += partial[(long long)s * channels + c];
-    out[c] = t;
-}
-
 // out[i][c] = (labels[i] == c): labels outside [0, classes) give an all-zero row
 __global__ void __launch_bounds__(256) onehot_kernel(const int *__restrict__ labels, float *__restrict__ out, int total, int classes) {
     for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
@@ -232,6 +223,7 @@ __global__ void __launch_bounds__(256) softmax_cce_kernel(const float *__restric
 __global__ void __launch_bounds__(256) scaled_sum_kernel(const float *__restrict__ v, float *__restrict__ out, int n, float scale) {
     __shared__ float sm[8];
     float acc = 0.f;
+#pragma unroll 8
     for (int i = threadIdx.x; i < n; i += blockDim.x) acc += v[i];
     float t = block_sum_256(acc, sm);
     if (threadIdx.x == 0) *out = t * scale;
@@ -429,8 +421,9 @@ static int act_bias_bwd_launch(const float *dy, const float *y, float *dz, float
         SEERA_LAUNCH_CHECK("act_bias_bwd(nchw)");
     }
     if (dbias) {
-        sum_partials_kernel<<<(channels + 255) / 256, 256, 0, rt().stream>>>(partial, dbias, channels, splits);
-        SEERA_LAUNCH_CHECK("act_bias_bwd(sum)");
+        launch_sum_splits(partial, dbias, channels, splits, rt().stream);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return check_cuda(e, "act_bias_bwd(sum)");
     }
     return SEERA_OK;
 }

@@ -189,17 +189,6 @@ __global__ void __launch_bounds__(256) skinny_dB_kernel(const float *__restrict_
     }
 }
 
-__global__ void __launch_bounds__(256) skinny_dB_reduce_kernel(const float *__restrict__ partial, float *__restrict__ dB, float *__restrict__ dbias,
-                                                               int kn, int n, int splits) {
-    const int e = blockIdx.x * 256 + threadIdx.x, outputs = kn + n;
-    if (e >= outputs) return;
-    float t = 0.f;
-#pragma unroll 8
-    for (int z = 0; z < splits; z++) t += __ldg(partial + (long long)z * outputs + e);
-    if (e < kn) dB[e] = t;
-    else if (dbias) dbias[e - kn] = t;
-}
-
 bool skinny_applies(int M, int N, int K, int Nbatch) {
     return rt().precision != 0 && rt().skinny_gemm && N >= 1 && N <= SK_MAXN && K >= 1 && (long long)M * Nbatch < (1ll << 31) &&
            (long long)M * Nbatch * K < (1ll << 40);
@@ -255,8 +244,7 @@ int skinny_bwd(const float *A, const float *B, const float *dC, float *dA, float
         SK_DISPATCH(N, (skinny_dB_kernel<NN><<<dim3(kblocks, splits), 256, 0, st>>>(A, dC, db_out, dbias, partial, rows, K)))
         count_launch();
         if (splits > 1) {
-            skinny_dB_reduce_kernel<<<(K * N + N + 255) / 256, 256, 0, st>>>(partial, db_out, dbias, K * N, N, splits);
-            count_launch();
+            launch_sum_splits(partial, db_out, (K + 1) * N, splits, st, dbias, K * N);
         }
         profile_end(2.0 * rows * N * (double)K, "cuda_matmul_bwd(dB)");
         e = cudaGetLastError();

@@ -108,14 +108,6 @@ __global__ void __launch_bounds__(256) dz_rows_kernel(const float *__restrict__ 
         }
     }
 }
-__global__ void __launch_bounds__(256) dz_rows_sum_kernel(const float *__restrict__ partial, float *__restrict__ out, int cols, int splits) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols) return;
-    float t = 0.f;
-    for (int s = 0; s < splits; s++) t += partial[(long long)s * cols + c];
-    out[c] = t;
-}
-
 static const Shadow *rows_usable(const seera_rows *h, int ns, int rows, int cols, int cls) {
     const Enc want = enc_for(cls);
     if (!h || h->ns < ns || h->s.rows != rows || h->s.cols != cols || h->s.enc.fmt != want.fmt || h->s.enc.scale != want.scale ||
@@ -247,8 +239,7 @@ int seera_matmul_act_bwd(const float *A, const float *B, const float *y, const f
             count_launch();
             cudaError_t e = cudaGetLastError();
             if (e == cudaSuccess && dbias) {
-                dz_rows_sum_kernel<<<(N + 255) / 256, 256, 0, st>>>(partial, dbias, N, splits);
-                count_launch();
+                launch_sum_splits(partial, dbias, N, splits, st);
                 e = cudaGetLastError();
             }
             if (e != cudaSuccess) s = check_cuda(e, "matmul_act_bwd(dz)");
