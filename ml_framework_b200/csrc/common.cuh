@@ -23,6 +23,7 @@ struct Runtime {
                                         // bottleneck: off; 3 x 3 unit-stride layers fold it into the fp32 stencil kernel regardless)
     bool wgrad_single = true;           // precision mode 4: weight gradients from the first fp16 copy of each operand alone
     bool skinny_gemm = true;            // Dense products of at most 16 output columns: exact fp32 on the CUDA cores in every mode
+    int mma_issuers = 0;                // cap on the MMA-issuing threads of the TMA-fed GEMM kernel (0: none; 1 or 2)
     bool pair_tiles = false;            // TMA-fed GEMMs as clusters of two CTAs on 256-row tiles where the plan finds it pays
     bool conv_tma = true;               // convolutions in modes 1-3: TMA im2col kernel (false: in-kernel gather kernel)
     bool capturing = false;             // a stream capture (seera_graph_begin) is open

@@ -15,6 +15,11 @@ extern "C" {
 
 int seera_set_option(const char *name, int value) {
     if (!name) return fail(SEERA_E_ARG, "set_option: null name");
+    if (!strcmp(name, "mma_issuers")) {
+        if (value != 0 && value != 1 && value != 2) return fail(SEERA_E_ARG, "set_option: mma_issuers must be 0, 1 or 2");
+        rt().mma_issuers = value;
+        return SEERA_OK;
+    }
     if (!strcmp(name, "skinny_gemm")) { rt().skinny_gemm = value != 0; return SEERA_OK; }
     if (!strcmp(name, "dense_tma")) { rt().dense_tma = value != 0; return SEERA_OK; }
     if (!strcmp(name, "conv_tma")) { rt().conv_tma = value != 0; return SEERA_OK; }

@@ -34,7 +34,8 @@ template <class CS>
 __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, int col_base, int c_begin, int c_end,
                                                   int M, int N, const CS &cs, float *partial, long long partial_off,
                                                   float *stage /* EPI_WARP_SMEM bytes, this warp's own */,
-                                                  const float *bias = nullptr, int act = 0, float scale = 1.f) {
+                                                  const float *bias = nullptr, int act = 0, float scale = 1.f,
+                                                  int nacc = 1, uint32_t acc_stride = 0 /* partial accumulators to add up */) {
     const int lane = threadIdx.x & 31;
     const bool transpose = partial != nullptr || !CS::kMContiguous;
     const long long sn = cs.nstride();
@@ -43,7 +44,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int row_base, 
     float *own = (!transpose && m_own < M) ? cs.row(m_own) : nullptr;
     for (int c = c_begin; c < c_end; c += 32) {
         float v[32];
-        tmem_ld32(taddr + (uint32_t)(c - c_begin), v);
+        tmem_ld32_sum(taddr + (uint32_t)(c - c_begin), v, nacc, acc_stride);
         if (scale != 1.f && !partial) {            // operand copies carried power-of-two factors: take them out (exact)
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] *= scale;
@@ -138,7 +139,8 @@ inline void pool_out_geometry(PoolOut &po, int P, int OW, int window_major) {
 }
 
 __device__ __forceinline__ void drain_accumulator_pooled(uint32_t taddr, int row_base, int col_base, int ncols, int M, int N,
-                                                         const float *bias, int act, const PoolOut &po, float *stage, float scale = 1.f) {
+                                                         const float *bias, int act, const PoolOut &po, float *stage, float scale = 1.f,
+                                                         int nacc = 1, uint32_t acc_stride = 0) {
     // The warp's 32 rows hold exactly 8 windows.  Each 32-column chunk gets bias + activation while lanes still hold rows,
     // then goes through the warp's 32 x 33 staging buffer so that lanes hold COLUMNS (filters): a lane reads the four
     // values of a window from shared memory (no shuffles), and the 8 windows of its filter are 8 consecutive floats of the
@@ -170,7 +172,7 @@ __device__ __forceinline__ void drain_accumulator_pooled(uint32_t taddr, int row
     const bool aligned = ((reinterpret_cast<uintptr_t>(po.pooled) | reinterpret_cast<uintptr_t>(po.mask)) & 15) == 0;
     for (int c = 0; c < ncols; c += 32) {
         float v[32];
-        tmem_ld32(taddr + (uint32_t)c, v);
+        tmem_ld32_sum(taddr + (uint32_t)c, v, nacc, acc_stride);
         if (scale != 1.f) {
 #pragma unroll
             for (int j = 0; j < 32; j++) v[j] *= scale;

@@ -92,6 +92,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The same over `nacc` accumulators that sit `acc_stride` columns apart and hold partial sums of one tile (one per MMA-issuing
+// thread): their sum, added in index order.
+__device__ __forceinline__ void tmem_ld32_sum(uint32_t taddr, float *v, int nacc, uint32_t acc_stride) {
+    tmem_ld32(taddr, v);
+    for (int i = 1; i < nacc; i++) {
+        float w[32];
+        tmem_ld32(taddr + (uint32_t)i * acc_stride, w);
+#pragma unroll
+        for (int j = 0; j < 32; j++) v[j] += w[j];
+    }
+}
 
 // Shared-memory matrix descriptor: K-major tile whose rows are 128 bytes (64 bf16) with the 128-byte
 // swizzle; 8-row groups are 1024 bytes apart.  `addr` must be 1024-byte aligned plus a multiple of 32

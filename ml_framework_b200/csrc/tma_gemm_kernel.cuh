@@ -226,6 +226,8 @@ struct TmaGemmParams {
     int M, N, K, kchunk, splits, bn, stages;
     int a_mode, b_mn;        // b_mn = 1: B read along its contiguous row index (MN-major)
     int pair;                // 1: launched as clusters of two CTAs sharing 256-row tiles (tcgen05 cta_group::2)
+    int issuers;             // 1 or 2 threads issue the MMAs of a k-step (the K = 16 slices dealt round robin), each into its own
+                             // accumulator; the epilogue adds the accumulators up
     // convolution geometry for the im2col modes
     int OW, OHW;             // output width and pixels per image of the traversal
     int sw, sh, pw, ph;      // window stride and lower padding
@@ -246,11 +248,21 @@ struct TmaGemmParams {
     FastDiv by_mtiles, by_ntiles, by_OHW, by_OW, by_S, by_cchunks;      // filled by launch_tma_gemm
 };
 
-constexpr int TG_THREADS = 192;
+// warp 0: TMA producer; warps 1-2: MMA issuers (the first p.issuers of them); warp 3 allocates TMEM; warps 4-7: epilogue.
+// (Eight warps: with a ninth the register file would be shared out as for twelve, 168 registers per thread, and the epilogue spills.)
+constexpr int TG_THREADS = 256, TG_EPI_WARP0 = 4;
 
 // Persistent kernel: each CTA walks tiles  id = blockIdx.x, blockIdx.x + gridDim.x, ...  (m-tile fastest, then n-tile,
 // then K split).  The operand ring keeps streaming across tile boundaries and the accumulator is double-buffered in
-// TMEM (2 x bn columns), so the epilogue of tile i overlaps the main loop of tile i+1.
+// TMEM, so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// One thread can issue a tcgen05.mma only every 80-90 clocks, whatever the instruction's size (measured: 88 clocks per MMA at
+// N = 64 from one thread, the same MMAs from two threads at twice the rate), while a 128 x N x 16 instruction occupies the
+// tensor pipe for N / 2 clocks.  With N <= 128 a single issuing thread therefore leaves the pipe idle half of the time or more.
+// So two threads (lane 0 of warps 1 and 2) issue where the accumulators fit: they wait for the same stage, take the K = 16 slices
+// of the k-step alternately, each into an accumulator of its own (MMAs of different threads are not ordered among themselves), and each commits
+// to the stage's "empty" barrier and to the tile's "accumulator full" barrier, which count `issuers` arrivals.  TMEM holds
+// 2 buffers x issuers x bn columns (at most 512); the epilogue adds the accumulators of a buffer while it drains them.
 template <int NS, class CS, bool PAIR>
 __global__ void __launch_bounds__(TG_THREADS, 1)
 tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
@@ -280,16 +292,17 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
     auto b_tile = [&](int s, int i) { return smem0 + (uint32_t)s * stage_bytes + (uint32_t)NS * a_bytes + (uint32_t)i * b_bytes; };
     unsigned char *epi_smem = smem + (size_t)stages * stage_bytes;   // 4 x EPI_WARP_SMEM after the ring
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[8]), tfull0 = smem_u32(&bars[16]), tempty0 = smem_u32(&bars[18]);
-    const uint32_t tmem_cols = (uint32_t)(2 * bn < 32 ? 32 : 2 * bn);
+    const int issuers = PAIR ? 1 : p.issuers;
+    const uint32_t tmem_cols = (uint32_t)(2 * issuers * bn < 32 ? 32 : 2 * issuers * bn);
 
     if (t == 0) {
         abort_flag = 0;
-        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, PAIR ? 8 : 4); }
+        for (int s = 0; s < stages; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, issuers); }
+        for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, issuers); mbar_init(tempty0 + 8 * b, PAIR ? 8 : 4); }
         fence_mbar_init();
         fence_async_smem();
     }
-    if (warp == 1) { if (PAIR) tmem_alloc2(smem_u32(&tmem_base_slot), tmem_cols); else tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols); }
+    if (warp == 3) { if (PAIR) tmem_alloc2(smem_u32(&tmem_base_slot), tmem_cols); else tmem_alloc(smem_u32(&tmem_base_slot), tmem_cols); }
     tc_fence_before();
     if (PAIR) cluster_sync_all(); else __syncthreads();        // the peer's barriers exist before anything arrives on them
     tc_fence_after();
@@ -402,8 +415,9 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
                 while (!mbar_try_wait(full0 + 8 * (k % stages), (uint32_t)(k / stages) & 1u) && clock64() - t0 < p.wait_clocks) {}
             }
         }
-    } else if (warp == 1 && lane == 0 && rank == 0) {
-        // ---------------- MMA issuer (the even CTA of a pair) ----------------
+    } else if (warp >= 1 && warp <= issuers && lane == 0 && rank == 0) {
+        // ---------------- MMA issuers (in the even CTA of a pair) ----------------
+        const int me = warp - 1;
         uint32_t idesc = umma_idesc_16bit(bn, p.a_fp16, p.b_fp16) | ((uint32_t)(a_mn ? 1 : 0) << 15) | ((uint32_t)p.b_mn << 16);
         if (PAIR) idesc = (idesc & ~(31u << 24)) | ((uint32_t)(TM >> 4) << 24);          // M = 256 over the two CTAs
         const uint32_t a_step = a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;   // bytes per K=16 slice
@@ -416,9 +430,9 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
         uint32_t ph = 0;
         // descriptors of copy 0 / slice 0 in slot 0; the others differ only in the start-address field (16-byte units),
         // which never carries out of its 14 bits for addresses inside the CTA's shared memory
-        const uint64_t da0 = a_mn ? umma_desc_sw128_mn(a_tile(0, 0), 8192) : umma_desc_sw128(a_tile(0, 0));
-        const uint64_t db0 = p.b_mn ? umma_desc_sw128_mn(b_tile(0, 0), 8192) : umma_desc_sw128(b_tile(0, 0));
         const uint32_t a_step16 = a_step >> 4, b_step16 = b_step >> 4, a_copy16 = a_bytes >> 4, b_copy16 = b_bytes >> 4;
+        const uint64_t da0 = (a_mn ? umma_desc_sw128_mn(a_tile(0, 0), 8192) : umma_desc_sw128(a_tile(0, 0))) + (uint32_t)me * a_step16;
+        const uint64_t db0 = (p.b_mn ? umma_desc_sw128_mn(b_tile(0, 0), 8192) : umma_desc_sw128(b_tile(0, 0))) + (uint32_t)me * b_step16;
         const uint32_t stage16 = stage_bytes >> 4;
         for (int id = worker; id < total_tiles && alive; id += nworkers, local++) {
             int m0, n0, kbeg, ktiles, z;
@@ -428,36 +442,41 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             alive = mbar_wait(tempty0 + 8 * buf, (((uint32_t)local >> 1) & 1u) ^ 1u, abortp, p.status, 4, p.wait_clocks);
             if (!alive) break;
             tc_fence_after();
-            const uint32_t d_tmem = tmem_base + (uint32_t)(buf * bn);
+            const uint32_t d_tmem = tmem_base + (uint32_t)((buf * issuers + me) * bn);
             uint32_t acc = 0;
             for (int kt = 0; kt < ktiles && alive; kt++) {
                 alive = mbar_wait(full0 + 8 * s, ph, abortp, p.status, 2, p.wait_clocks);
                 if (!alive) break;
                 tc_fence_after();
                 const uint64_t das = da0 + (uint32_t)s * stage16, dbs = db0 + (uint32_t)s * stage16;
-#pragma unroll
-                for (int j = 0; j < TC_BK / 16; j++) {
+                // the K = 16 slices of this thread (da0 / db0 already point at its first one), fully unrolled either way: the
+                // issuing thread's own instruction stream is what limits the MMA rate
+                auto slice = [&](uint64_t dsa, uint64_t dsb) {
                     uint64_t da[NS], db[NS];
 #pragma unroll
-                    for (int i = 0; i < NS; i++) {
-                        da[i] = das + (uint32_t)i * a_copy16 + (uint32_t)j * a_step16;
-                        db[i] = dbs + (uint32_t)i * b_copy16 + (uint32_t)j * b_step16;
-                    }
+                    for (int i = 0; i < NS; i++) { da[i] = dsa + (uint32_t)i * a_copy16; db[i] = dsb + (uint32_t)i * b_copy16; }
 #pragma unroll
                     for (int q = 0; q < NPROD; q++) {
                         if (PAIR) umma2_bf16(d_tmem, da[pa[q]], db[pb[q]], idesc, acc); else umma_bf16(d_tmem, da[pa[q]], db[pb[q]], idesc, acc);
                         acc = 1;
                     }
+                };
+                if (issuers == 2) {
+#pragma unroll
+                    for (int jj = 0; jj < TC_BK / 32; jj++) slice(das + (uint32_t)(2 * jj) * a_step16, dbs + (uint32_t)(2 * jj) * b_step16);
+                } else {
+#pragma unroll
+                    for (int jj = 0; jj < TC_BK / 16; jj++) slice(das + (uint32_t)jj * a_step16, dbs + (uint32_t)jj * b_step16);
                 }
                 if (PAIR) umma2_commit_both(empty0 + 8 * s); else umma_commit(empty0 + 8 * s);
                 if (++s == stages) { s = 0; ph ^= 1u; }
             }
             if (alive) { if (PAIR) umma2_commit_both(tfull0 + 8 * buf); else umma_commit(tfull0 + 8 * buf); }   // accumulator complete
         }
-    } else if (warp >= 2) {
+    } else if (warp >= TG_EPI_WARP0) {
         // ---------------- epilogue: warp w drains TMEM lane quarter w % 4 ----------------
         const int q = warp & 3;
-        float *stage = reinterpret_cast<float *>(epi_smem + (size_t)(warp - 2) * EPI_WARP_SMEM);
+        float *stage = reinterpret_cast<float *>(epi_smem + (size_t)(warp - TG_EPI_WARP0) * EPI_WARP_SMEM);
         const float out_scale = p.dinv ? p.out_scale * __ldg(p.dinv) : p.out_scale;
         int local = 0;
         const uint32_t tempty_at = PAIR ? mapa_rank(tempty0, 0) : tempty0;      // the even CTA's barrier counts both epilogues
@@ -468,11 +487,11 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
             if (!mbar_wait(tfull0 + 8 * buf, ((uint32_t)local >> 1) & 1u, abortp, p.status, 3, p.wait_clocks)) break;
             tc_fence_after();
             if (p.pool_on)
-                drain_accumulator_pooled(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, bn, p.M, p.N,
-                                         p.bias, p.act, p.pool, stage, out_scale);
+                drain_accumulator_pooled(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * issuers * bn), m0 + q * 32, n0, bn, p.M, p.N,
+                                         p.bias, p.act, p.pool, stage, out_scale, issuers, (uint32_t)bn);
             else
-                drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * bn), m0 + q * 32, n0, 0, bn, p.M, p.N, cs,
-                                  p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act, out_scale);
+                drain_accumulator(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * issuers * bn), m0 + q * 32, n0, 0, bn, p.M, p.N, cs,
+                                  p.partial, (long long)z * p.M * p.N, stage, p.bias, p.act, out_scale, issuers, (uint32_t)bn);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) { if (PAIR) mbar_arrive_cluster(tempty_at + 8 * buf); else mbar_arrive(tempty0 + 8 * buf); }
@@ -480,7 +499,7 @@ tma_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant
     }
     tc_fence_before();
     if (PAIR) cluster_sync_all(); else __syncthreads();        // neither CTA's shared memory or TMEM goes away while the other still uses it
-    if (warp == 1) { if (PAIR) tmem_dealloc2(tmem_base, tmem_cols); else tmem_dealloc(tmem_base, tmem_cols); }
+    if (warp == 3) { if (PAIR) tmem_dealloc2(tmem_base, tmem_cols); else tmem_dealloc(tmem_base, tmem_cols); }
 }
 
 template <class CS>
@@ -520,6 +539,10 @@ inline int tma_pick_bn(int N, int ns, int b_mn) {
 inline void tma_plan(TmaGemmParams &p, int ns, bool allow_split) {
     p.bn = tma_pick_bn(p.N, ns, p.b_mn);
     p.pair = 0;
+    // MMA-issuing threads: two where TMEM has room for their accumulators (2 buffers x issuers x bn <= 512 columns); one thread
+    // keeps up with 256-column instructions by itself
+    p.issuers = p.bn <= 128 ? 2 : 1;
+    if (rt().mma_issuers && rt().mma_issuers < p.issuers) p.issuers = rt().mma_issuers;
     if (!rt().pair_tiles || ns > 2 || rt().sm_count < 4) return;
     int bn = p.bn;
     if (ns == 2 && p.N > 128) bn = 256;               // a pair stages half of B per CTA: 2 x (16 + 16) KB per stage, three stages
@@ -534,6 +557,7 @@ inline void tma_plan(TmaGemmParams &p, int ns, bool allow_split) {
 // and the geometry fields must be set; kchunk, stages, partial and status are filled here.
 template <class CS>
 int launch_tma_gemm(const TmaMaps &maps, TmaGemmParams p, const CS &cs, int ns, bool allow_split, double flops, const char *name) {
+    if (p.issuers != 2 || p.pair || 4 * p.bn > 512) p.issuers = 1;      // TMEM has 512 columns
     const int tm = p.pair ? 2 * TC_BM : TC_BM;
     size_t stage = (size_t)ns * (TC_BM * 128 + (size_t)(p.pair ? p.bn / 2 : p.bn) * 128);
     // 227 KB per CTA on sm_100a; keep 2 KB for the kernel's static shared memory and alignment slack
