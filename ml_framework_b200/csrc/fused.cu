@@ -220,10 +220,10 @@ __global__ void __launch_bounds__(256) softmax_cce_kernel(const float *__restric
 }
 
 // Deterministic single-block sum of n floats times scale.
-__global__ void __launch_bounds__(256) scaled_sum_kernel(const float *__restrict__ v, float *__restrict__ out, int n, float scale) {
-    __shared__ float sm[8];
+__global__ void __launch_bounds__(1024) scaled_sum_kernel(const float *__restrict__ v, float *__restrict__ out, int n, float scale) {
+    __shared__ float sm[32];
     float acc = 0.f;
-#pragma unroll 8
+#pragma unroll 4
     for (int i = threadIdx.x; i < n; i += blockDim.x) acc += v[i];
     float t = block_sum_256(acc, sm);
     if (threadIdx.x == 0) *out = t * scale;
@@ -524,7 +524,7 @@ int seera_softmax_cce_fwd_bwd(const float *z, const float *onehot, float *p, flo
     ProfBytes pb(16.0 * N * C, "softmax_cce");
     softmax_cce_kernel<<<stride_grid((long long)N * 32), 256, 0, rt().stream>>>(z, onehot, p, loss_rows, dz, N, C, eps, inv_count);
     SEERA_LAUNCH_CHECK("softmax_cce");
-    scaled_sum_kernel<<<1, 256, 0, rt().stream>>>(loss_rows, loss_mean, N, inv_count);
+    scaled_sum_kernel<<<1, N > 1024 ? 1024 : 256, 0, rt().stream>>>(loss_rows, loss_mean, N, inv_count);
     SEERA_LAUNCH_CHECK("softmax_cce(sum)");
     return SEERA_OK;
 }
@@ -545,7 +545,7 @@ static int elem_loss(int kind, const float *p, const float *y, float *partials, 
     else if (kind == 1) elem_loss_kernel<1><<<g, 256, 0, st>>>(p, y, partials, dp, size, inv_count, eps);
     else elem_loss_kernel<2><<<g, 256, 0, st>>>(p, y, partials, dp, size, inv_count, eps);
     SEERA_LAUNCH_CHECK(name);
-    scaled_sum_kernel<<<1, 256, 0, st>>>(partials, loss_mean, g, inv_count);
+    scaled_sum_kernel<<<1, g > 1024 ? 1024 : 256, 0, st>>>(partials, loss_mean, g, inv_count);
     SEERA_LAUNCH_CHECK(name);
     return SEERA_OK;
 }

@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(256) skinny_fwd_kernel(const float *__restrict
             float acc0[N], acc1[N];
 #pragma unroll
             for (int n = 0; n < N; n++) { acc0[n] = 0.f; acc1[n] = 0.f; }
-#pragma unroll 4
+#pragma unroll 8
             for (int k = lane; k < kc; k += 32) {
                 const float x0 = __ldg(a0 + k), x1 = __ldg(a1 + k);
 #pragma unroll
