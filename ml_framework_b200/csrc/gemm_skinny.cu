@@ -19,7 +19,7 @@ constexpr int SK_MAXN = 16;
 
 // k-extent of the slice of B a block keeps in shared memory: N * sk_kc(N) floats, at most 48 KB
 __host__ __device__ constexpr int sk_kc(int n) { return n <= 12 ? 1024 : 768; }
-constexpr int SK_ROWS = 64;          // rows of dC a block stages at a time in the two backward kernels
+constexpr int SK_ROWS = 64;          // most rows of dC a block stages at a time in the two backward kernels
 
 // C = act(A B + bias).  A block keeps B^T (slice by slice when K exceeds it) in shared memory as bt[n][k], so that lane = k reads
 // it without bank conflicts; a warp forms two rows of C at a time: lanes stride over k (coalesced reads of A), 2 * N running
@@ -106,15 +106,15 @@ struct SkinnyRows {
 // of its group: N multiply-adds per element against broadcast reads of the staged dC rows, stores coalesced over k.
 template <int N>
 __global__ void __launch_bounds__(256) skinny_dA_kernel(const float *__restrict__ dC, const float *__restrict__ B, float *__restrict__ dA,
-                                                        int rows, int K) {
+                                                        int rows, int K, int chunk_rows) {
     __shared__ __align__(16) SkinnyRows<N> sd;
     constexpr int NP = SkinnyRows<N>::NP;
     const int k = blockIdx.x * 256 + threadIdx.x;
     float b[N];
 #pragma unroll
     for (int n = 0; n < N; n++) b[n] = k < K ? __ldg(B + (long long)k * N + n) : 0.f;
-    for (int m0 = blockIdx.y * SK_ROWS; m0 < rows; m0 += gridDim.y * SK_ROWS) {
-        const int nrows = min(SK_ROWS, rows - m0);
+    for (int m0 = blockIdx.y * chunk_rows; m0 < rows; m0 += gridDim.y * chunk_rows) {
+        const int nrows = min(chunk_rows, rows - m0);
         __syncthreads();
         sd.stage(dC, m0, nrows);
         __syncthreads();
@@ -137,17 +137,17 @@ __global__ void __launch_bounds__(256) skinny_dA_kernel(const float *__restrict_
 // small kernel, so the result is the same on every run.
 template <int N>
 __global__ void __launch_bounds__(256) skinny_dB_kernel(const float *__restrict__ A, const float *__restrict__ dC, float *__restrict__ dB,
-                                                        float *__restrict__ dbias, float *__restrict__ partial, int rows, int K) {
+                                                        float *__restrict__ dbias, float *__restrict__ partial, int rows, int K, int chunk_rows) {
     __shared__ __align__(16) SkinnyRows<N> sd;
     constexpr int NP = SkinnyRows<N>::NP;
     const int k = blockIdx.x * 256 + threadIdx.x, s = blockIdx.y, splits = gridDim.y;
-    const int chunks = (rows + SK_ROWS - 1) / SK_ROWS, per = (chunks + splits - 1) / splits;
-    const int m_begin = min(rows, s * per * SK_ROWS), m_end = min(rows, (s + 1) * per * SK_ROWS);
+    const int chunks = (rows + chunk_rows - 1) / chunk_rows, per = (chunks + splits - 1) / splits;
+    const int m_begin = (int)min((long long)rows, (long long)s * per * chunk_rows), m_end = (int)min((long long)rows, (long long)(s + 1) * per * chunk_rows);
     float acc[N], colsum = 0.f;
 #pragma unroll
     for (int n = 0; n < N; n++) acc[n] = 0.f;
-    for (int m0 = m_begin; m0 < m_end; m0 += SK_ROWS) {
-        const int nrows = min(SK_ROWS, m_end - m0);
+    for (int m0 = m_begin; m0 < m_end; m0 += chunk_rows) {
+        const int nrows = min(chunk_rows, m_end - m0);
         __syncthreads();
         sd.stage(dC, m0, nrows);
         __syncthreads();
@@ -222,13 +222,17 @@ int skinny_fwd(const float *A, const float *B, const float *bias, float *C, int 
 int skinny_bwd(const float *A, const float *B, const float *dC, float *dA, float *dB, float *dbias, int rows, int N, int K) {
     cudaStream_t st = rt().stream;
     cudaError_t e = cudaSuccess;
-    const int kblocks = (K + 255) / 256, chunks = (rows + SK_ROWS - 1) / SK_ROWS;
+    const int kblocks = (K + 255) / 256;
     int groups = (rt().sm_count * 4 + kblocks - 1) / kblocks;            // about four blocks per SM
+    // rows staged at a time: few where the rows are few, so that a small problem still spreads over many blocks (8 ... SK_ROWS)
+    int chunk_rows = ((rows + groups - 1) / groups + 7) / 8 * 8;
+    if (chunk_rows > SK_ROWS) chunk_rows = SK_ROWS;
+    const int chunks = (rows + chunk_rows - 1) / chunk_rows;
     if (groups > chunks) groups = chunks;
     if (groups > 65535) groups = 65535;
     if (dA) {
         profile_begin();
-        SK_DISPATCH(N, (skinny_dA_kernel<NN><<<dim3(kblocks, groups), 256, 0, st>>>(dC, B, dA, rows, K)))
+        SK_DISPATCH(N, (skinny_dA_kernel<NN><<<dim3(kblocks, groups), 256, 0, st>>>(dC, B, dA, rows, K, chunk_rows)))
         count_launch();
         profile_end(2.0 * rows * N * (double)K, "cuda_matmul_bwd(dA)");
         e = cudaGetLastError();
@@ -241,7 +245,7 @@ int skinny_bwd(const float *A, const float *B, const float *dC, float *dA, float
         if (!partial) return SEERA_E_OOM;
         if (!dB) { tmp = (float *)scratch_alloc((size_t)K * N * sizeof(float)); if (!tmp) { scratch_free(partial); return SEERA_E_OOM; } db_out = tmp; }
         profile_begin();
-        SK_DISPATCH(N, (skinny_dB_kernel<NN><<<dim3(kblocks, splits), 256, 0, st>>>(A, dC, db_out, dbias, partial, rows, K)))
+        SK_DISPATCH(N, (skinny_dB_kernel<NN><<<dim3(kblocks, splits), 256, 0, st>>>(A, dC, db_out, dbias, partial, rows, K, chunk_rows)))
         count_launch();
         if (splits > 1) {
             launch_sum_splits(partial, db_out, (K + 1) * N, splits, st, dbias, K * N);
