@@ -5,7 +5,8 @@
 // of k-steps into a 32-column tile that is two thirds padding, and a split-K reduce - about 15 us per launch, three launches per
 // layer and step - for well under a microsecond of arithmetic.  Here each of the three products of a layer (reference:
 // engine_cuda/src/GEMM.cu:95-103 forward, :164-225 backward) is one or two small launches that read the fp32 operands in place:
-//   C  = act(A B + bias)   one warp per row of A, lanes stride over k, N running sums per lane, shuffle reduction
+//   C  = act(A B + bias)   a warp per pair of rows (a block per pair where rows are few), lanes stride over k, N running sums
+//                          per lane and row, shuffle reduction
 //   dA = dC B^T            one thread per element of dA, N multiply-adds
 //   dB = A^T dC (+ dbias)  one thread per row of dB walks its share of the M rows; the shares are summed in a fixed order by a
 //                          second small kernel, so the result does not depend on scheduling
@@ -78,6 +79,55 @@ __global__ void __launch_bounds__(256) skinny_fwd_kernel(const float *__restrict
                 *c0 = v0;
                 if (two) c0[N] = v1;
             }
+        }
+    }
+}
+
+// The same for few rows (at most a few blocks' worth per SM): one block per pair of rows, its eight warps take interleaved
+// 32-wide pieces of k, B read in place (a warp's reads of B cover 32 * N consecutive floats over its n loop, served by L1), the
+// warps' sums added in warp order through shared memory.  No staging of B, and a long contraction (a flattened feature map into
+// ten classes) is spread over eight warps instead of walked by one.
+template <int N>
+__global__ void __launch_bounds__(256) skinny_fwd_small_kernel(const float *__restrict__ A, const float *__restrict__ B,
+                                                               const float *__restrict__ bias, float *__restrict__ C, int rows, int K, int act) {
+    __shared__ float red[8][2][N];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int m = blockIdx.x * 2;
+    const bool two = m + 1 < rows;
+    const float *a0 = A + (long long)m * K, *a1 = a0 + (two ? K : 0);
+    float acc0[N], acc1[N];
+#pragma unroll
+    for (int n = 0; n < N; n++) { acc0[n] = 0.f; acc1[n] = 0.f; }
+#pragma unroll 2
+    for (int k = warp * 32 + lane; k < K; k += 256) {
+        const float x0 = __ldg(a0 + k), x1 = __ldg(a1 + k);
+        const float *b = B + (long long)k * N;
+#pragma unroll
+        for (int n = 0; n < N; n++) {
+            const float bv = __ldg(b + n);
+            acc0[n] = fmaf(x0, bv, acc0[n]);
+            acc1[n] = fmaf(x1, bv, acc1[n]);
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < N; n++) {
+        float t0 = acc0[n], t1 = acc1[n];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            t0 += __shfl_xor_sync(0xffffffffu, t0, o);
+            t1 += __shfl_xor_sync(0xffffffffu, t1, o);
+        }
+        if (lane == 0) { red[warp][0][n] = t0; red[warp][1][n] = t1; }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * N) {
+        const int r = threadIdx.x / N, n = threadIdx.x - r * N;
+        if (r == 0 || two) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) v += red[w][r][n];
+            if (bias) v += __ldg(bias + n);
+            C[(long long)(m + r) * N + n] = epilogue_act(v, act);
         }
     }
 }
@@ -211,7 +261,10 @@ int skinny_fwd(const float *A, const float *B, const float *bias, float *C, int 
     int grid = (rows + 15) / 16;
     if (grid > rt().sm_count * 2) grid = rt().sm_count * 2;
     const size_t smem = (size_t)N * sk_kc(N) * sizeof(float);
+    const bool small = (rows + 1) / 2 <= rt().sm_count * 4;             // a block per pair of rows still fits a wave or so
     profile_begin();
+    if (small) { SK_DISPATCH(N, (skinny_fwd_small_kernel<NN><<<(rows + 1) / 2, 256, 0, st>>>(A, B, bias, C, rows, K, act))) }
+    else
     SK_DISPATCH(N, (skinny_fwd_kernel<NN><<<grid, 256, smem, st>>>(A, B, bias, C, rows, K, act)))
     count_launch();
     profile_end(2.0 * rows * N * (double)K, name);

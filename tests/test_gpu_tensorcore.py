@@ -60,7 +60,7 @@ def test_matmul_and_backward(E, mode, M, K, N):
 
 @pytest.mark.parametrize("mode", [1, 4])
 @pytest.mark.parametrize("M,K,N,batch", [(1, 1, 1, 1), (5, 7, 3, 1), (64, 784, 10, 1), (512, 256, 10, 1), (4096, 1024, 10, 1), (33, 300, 16, 3),
-                                         (1000, 513, 7, 1), (70000, 24, 2, 1)])
+                                         (1000, 513, 7, 1), (70000, 24, 2, 1), (64, 3136, 10, 1), (2000, 1500, 3, 1), (1300, 2100, 13, 1)])
 def test_products_of_few_output_columns_are_exact_fp32_in_every_mode(E, mode, M, K, N, batch):
     """By default a product of at most 16 output columns (a classifier head) runs as fp32 on the CUDA cores whatever the precision
     mode: the plain entries, the fused forward and the one-call backward with its bias gradient all agree with double precision
