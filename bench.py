@@ -510,12 +510,110 @@ def run_c5(args):
                       "gpu_launches": int(sc.launch_count() - l0)}), flush=True)
 
 
+def run_adjacent(args):
+    """The device passes of the rows next to the training step - BatchNorm forward / backward, Concatenate forward / backward,
+    one-hot labels - each timed alone with CUDA events on operands resident in HBM: algorithmic bytes / time against the
+    measured HBM peak, and the same call on the CPU engine (a bounded sample of the rows) beside it.  One JSON line."""
+    import time
+    from ml_framework_b200 import seera_cuda as sc
+    from oracle import cpu_oracle as co
+    sc.init(int(os.environ.get("LOCAL_RANK", "0")))
+    _apply_options(sc, args)
+    peaks = _peaks()
+    rs = np.random.RandomState(7)
+    l0 = sc.launch_count()
+
+    def dev(a):
+        return sc.to_device_f32(np.ascontiguousarray(a, np.float32).ravel())
+
+    def timed(call):
+        for _ in range(max(args.warmup, 3)):
+            call()
+        sc.stream_synchronize()
+        e0, e1 = sc.event_create(), sc.event_create()
+        sc.event_record(e0)
+        for _ in range(args.steps):
+            call()
+        sc.event_record(e1)
+        ms = sc.event_elapsed_ms(e0, e1) / args.steps
+        sc.event_destroy(e0), sc.event_destroy(e1)
+        return ms
+
+    def cpu_timed(call, reps=3):
+        call()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            call()
+        return (time.perf_counter() - t0) / reps * 1e3
+
+    passes = []
+
+    def add(name, shape, nbytes, ms, cpu_ms, cpu_bytes, note):
+        g = nbytes / (ms / 1e3) / 1e9
+        passes.append({"pass": name, "shape": shape, "algorithmic_mb": nbytes / 1e6, "ms": ms, "achieved": g, "frac": g / peaks["hbm"],
+                       "cpu_gbs": cpu_bytes / (cpu_ms / 1e3) / 1e9, "cpu_sample": note})
+
+    # BatchNorm2d (512, 64, 32, 32) and BatchNorm1d (4096, 1024): read x + write y; backward read dy, x + write dx
+    for tag, (N, C, S) in (("batchnorm2d", (512, 64, 1024)), ("batchnorm1d", (4096, 1024, 1))):
+        x = rs.standard_normal((N, C, S)).astype(np.float32)
+        gam, bet = rs.uniform(0.5, 1.5, C).astype(np.float32), rs.standard_normal(C).astype(np.float32)
+        xd, gd, bd, yd, dxd = dev(x), dev(gam), dev(bet), sc.cuda_malloc_f32(x.size), sc.cuda_malloc_f32(x.size)
+        rm, rv, mean, si, dg, db = (dev(np.zeros(C)), dev(np.ones(C)), sc.cuda_malloc_f32(C), sc.cuda_malloc_f32(C),
+                                    sc.cuda_malloc_f32(C), sc.cuda_malloc_f32(C))
+        ms_f = timed(lambda: sc.batchnorm_fwd(xd, gd, bd, rm, rv, yd, mean, si, N, C, S, 0.1, 1e-5, 1))
+        ms_b = timed(lambda: sc.batchnorm_bwd(yd, xd, mean, si, gd, dxd, dg, db, N, C, S))
+        ns = max(1, N // 16)                                    # CPU: a sixteenth of the rows
+        xs = x[:ns].reshape((ns, C, S) if S > 1 else (ns, C))
+        r0, r1 = np.zeros(C, np.float32), np.ones(C, np.float32)
+        c_f = cpu_timed(lambda: co.batchnorm_forward(xs, gam, bet, r0, r1, 0.1, 1e-5, True))
+        _, xh, _, sinv = co.batchnorm_forward(xs, gam, bet, r0, r1, 0.1, 1e-5, True)
+        c_b = cpu_timed(lambda: co.batchnorm_backward(xs, xh, sinv, gam))
+        add(tag + "_fwd", [N, C, S], 8.0 * x.size, ms_f, c_f, 8.0 * xs.size, "%d of %d rows" % (ns, N))
+        add(tag + "_bwd", [N, C, S], 12.0 * x.size, ms_b, c_b, 12.0 * xs.size, "%d of %d rows" % (ns, N))
+        for p in (xd, gd, bd, yd, dxd, rm, rv, mean, si, dg, db):
+            sc.cuda_free(p)
+    # Concatenate two (512, 64*32*32) tensors along axis 1 and split the joined gradient
+    N, n1, n2 = 512, 65536, 65536
+    a, b = rs.standard_normal((N, n1)).astype(np.float32), rs.standard_normal((N, n2)).astype(np.float32)
+    ad, bd, od = dev(a), dev(b), sc.cuda_malloc_f32(N * (n1 + n2))
+    ms_f = timed(lambda: sc.concat_fwd(ad, bd, od, N, n1, n2))
+    ms_b = timed(lambda: sc.concat_bwd(od, ad, bd, N, n1, n2))
+    ns = N // 16
+    c_f = cpu_timed(lambda: np.concatenate([a[:ns], b[:ns]], axis=1))
+    joined = np.concatenate([a[:ns], b[:ns]], axis=1)
+    c_b = cpu_timed(lambda: (np.ascontiguousarray(joined[:, :n1]), np.ascontiguousarray(joined[:, n1:])))
+    add("concat_fwd", [N, n1, n2], 8.0 * N * (n1 + n2), ms_f, c_f, 8.0 * ns * (n1 + n2), "%d of %d rows, numpy" % (ns, N))
+    add("concat_bwd", [N, n1, n2], 8.0 * N * (n1 + n2), ms_b, c_b, 8.0 * ns * (n1 + n2), "%d of %d rows, numpy" % (ns, N))
+    for p in (ad, bd, od):
+        sc.cuda_free(p)
+    # one-hot rows from integer labels
+    n, classes = 1 << 20, 10
+    labels = rs.randint(0, classes, n).astype(np.int32)
+    ld, oh = sc.to_device_i32(labels), sc.cuda_malloc_f32(n * classes)
+    ms_o = timed(lambda: sc.onehot_f32(ld, oh, n, classes))
+    c_o = cpu_timed(lambda: np.eye(classes, dtype=np.float32)[labels[: n // 16]])
+    add("onehot", [n, classes], 4.0 * n * (1 + classes), ms_o, c_o, 4.0 * (n // 16) * (1 + classes), "%d of %d labels, numpy" % (n // 16, n))
+    sc.cuda_free(ld), sc.cuda_free(oh)
+
+    gm = float(np.exp(np.mean([np.log(p["achieved"]) for p in passes])))
+    top = max(passes, key=lambda p: p["ms"])
+    print(json.dumps({"metric": "adjacent device passes (BatchNorm, Concatenate, one-hot): algorithmic GB/s, geometric mean", "value": gm,
+                      "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True,
+                      "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+                      "config": {"workload": "rows next to the training step, each pass timed alone on operands in HBM", "passes": passes,
+                                 "l2": "operands of 134-268 MB exceed the 126 MB L2 except batchnorm1d (17 MB) and one-hot (46 MB)"},
+                      "roofline": {"bound": "hbm", "achieved": top["achieved"], "peak": peaks["hbm"], "unit": "GB/s", "frac": top["frac"],
+                                   "traffic": None, "kernel": top["pass"], "peak_source": peaks["src"]},
+                      "gpu_launches": int(sc.launch_count() - l0)}), flush=True)
+
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="c3", choices=sorted(wl.WORKLOADS) + ["c5"])
+    ap.add_argument("--workload", default="c3", choices=sorted(wl.WORKLOADS) + ["c5", "adjacent"])
     ap.add_argument("--c5-shape", default=None, help="C,HW of one point of the C5 sweep (default: the four diagonal shapes)")
     ap.add_argument("--c5-batch", type=int, default=256)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
@@ -538,6 +636,10 @@ def main():
     if args.workload == "c5":
         if int(os.environ.get("RANK", "0")) == 0:
             run_c5(args)
+        return
+    if args.workload == "adjacent":
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_adjacent(args)
         return
     work = wl.WORKLOADS[args.workload]()
     if args.precision is None:

@@ -2,12 +2,18 @@
 //
 // The reference runs this layer on the CPU only, even in its GPU path (Seera_init.py:870-921 forward,
 // Seera_Engine.py:381-415 backward, engine/src/batchnorm_ops.cpp:12-138 the arithmetic): every batch goes device -> host
-// -> device around it.  Here it is four bandwidth-bound passes forward (sum, squared differences to the mean, a
-// C-thread finalise that also moves the running statistics, normalise) and three backward (sums of dout and
-// dout * x_hat, finalise, dx).  The statistics are two-pass like the reference (mean first, then the variance from the
-// differences), and every reduction has a fixed order: per-thread strided partials, a block tree, then the partial rows
-// summed in split order.  x_hat is not stored: the backward recomputes it from the layer input, the saved mean and
-// 1/std (one multiply-add against a second activation-sized buffer of traffic).
+// -> device around it.  Here it is two bandwidth-bound passes over the tensor forward (statistics, normalise) and two backward
+// (sums of dout and dout * x_hat, dx), each with a C-thread finalise between them.
+//
+// Statistics.  The reference takes the mean first and the variance from the differences to it (two passes over x).  Here every
+// thread walks its share of a channel ONCE, accumulating sum (x - K) and sum (x - K)^2 around the first value K it meets - a
+// sample of the same distribution, so the subtraction in  M2 = s2 - s1^2 / n  cancels a few bits at most - and the per-thread
+// triples (n, mean, M2) are merged pairwise with Chan's update  mean = mean_a + d * n_b / n,  M2 = M2_a + M2_b + d^2 * n_a * n_b / n
+// (d = mean_b - mean_a) in a fixed order: lanes, warps, then the split rows.  That is as accurate as the two-pass form (both are
+// within a few ulp of the fp64 result; the parity tests hold the outputs to 1e-5 of the CPU engine's) for one read less.
+// Every other reduction has a fixed order too: per-thread strided partials, a block tree, then the partial rows summed in split
+// order.  x_hat is not stored: the backward recomputes it from the layer input, the saved mean and 1/std (one multiply-add
+// against a second activation-sized buffer of traffic).
 //
 // Layout [N, C, S] with S = H*W (1 for the 1-D form).  S > 1: a block owns one channel and a stripe of images and reads
 // its planes contiguously.  S == 1: a block owns 32 adjacent channels x a stripe of rows, so warps read rows contiguously.
@@ -35,7 +41,85 @@ __device__ __forceinline__ float bn_sum_partials(const float *partial, int c, in
     return t;
 }
 
-// What a reduction pass accumulates per channel:
+// ---- one-pass statistics -------------------------------------------------------------------------------------------
+struct BnMoments { float n, mean, m2; };
+__device__ __forceinline__ BnMoments bn_merge(const BnMoments &a, const BnMoments &b) {
+    const float n = a.n + b.n;
+    if (n == 0.f) return BnMoments{0.f, 0.f, 0.f};
+    const float d = b.mean - a.mean, w = b.n / n;
+    return BnMoments{n, a.mean + d * w, a.m2 + b.m2 + d * d * a.n * w};
+}
+struct BnShifted {                 // a thread's running sums around its first value
+    float k, s1, s2, n;
+    __device__ __forceinline__ void add(float v) {
+        if (n == 0.f) k = v;
+        const float d = v - k;
+        s1 += d; s2 += d * d; n += 1.f;
+    }
+    __device__ __forceinline__ BnMoments done() const {
+        if (n == 0.f) return BnMoments{0.f, 0.f, 0.f};
+        return BnMoments{n, k + s1 / n, fmaxf(s2 - s1 * s1 / n, 0.f)};
+    }
+};
+__device__ __forceinline__ BnMoments bn_warp_merge(BnMoments m) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {              // lane l merges (l, l ^ o) with the lower lane first: every lane ends with the same bits
+        BnMoments other{__shfl_xor_sync(0xffffffffu, m.n, o), __shfl_xor_sync(0xffffffffu, m.mean, o), __shfl_xor_sync(0xffffffffu, m.m2, o)};
+        m = ((threadIdx.x & o) == 0) ? bn_merge(m, other) : bn_merge(other, m);
+    }
+    return m;
+}
+// partial[(split * C + c) * 3 + {0, 1, 2}] = (n, mean, M2) of channel c over the images split, split + splits, ...
+__global__ void __launch_bounds__(256) bn_stats_planes_kernel(const float *__restrict__ x, float *__restrict__ partial, int N, int C, int S,
+                                                              int splits, int vec) {
+    __shared__ float sm[8][3];
+    const int c = blockIdx.x, split = blockIdx.y;
+    BnShifted acc{0.f, 0.f, 0.f, 0.f};
+    for (int n = split; n < N; n += splits) {
+        const float *plane = x + ((long long)n * C + c) * S;
+        if (vec) {
+            const float4 *p4 = reinterpret_cast<const float4 *>(plane);
+            for (int s = threadIdx.x; s < (S >> 2); s += 256) {
+                const float4 v = __ldg(p4 + s);
+                acc.add(v.x); acc.add(v.y); acc.add(v.z); acc.add(v.w);
+            }
+        } else {
+            for (int s = threadIdx.x; s < S; s += 256) acc.add(__ldg(plane + s));
+        }
+    }
+    BnMoments m = bn_warp_merge(acc.done());
+    if ((threadIdx.x & 31) == 0) { sm[threadIdx.x >> 5][0] = m.n; sm[threadIdx.x >> 5][1] = m.mean; sm[threadIdx.x >> 5][2] = m.m2; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        BnMoments t{sm[0][0], sm[0][1], sm[0][2]};
+#pragma unroll
+        for (int w = 1; w < 8; w++) t = bn_merge(t, BnMoments{sm[w][0], sm[w][1], sm[w][2]});
+        float *o = partial + ((long long)split * C + c) * 3;
+        o[0] = t.n; o[1] = t.mean; o[2] = t.m2;
+    }
+}
+// [N, C] rows: a block owns 32 adjacent channels and the rows split * 8 + ry, + splits * 8, ...
+__global__ void __launch_bounds__(256) bn_stats_rows_kernel(const float *__restrict__ x, float *__restrict__ partial, int N, int C, int splits) {
+    __shared__ float sm[8][32][3];
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx, split = blockIdx.y;
+    BnShifted acc{0.f, 0.f, 0.f, 0.f};
+    if (c < C)
+        for (int n = split * 8 + ry; n < N; n += splits * 8) acc.add(__ldg(x + (long long)n * C + c));
+    const BnMoments m = acc.done();
+    sm[ry][cx][0] = m.n; sm[ry][cx][1] = m.mean; sm[ry][cx][2] = m.m2;
+    __syncthreads();
+    if (ry == 0 && c < C) {
+        BnMoments t{sm[0][cx][0], sm[0][cx][1], sm[0][cx][2]};
+#pragma unroll
+        for (int r = 1; r < 8; r++) t = bn_merge(t, BnMoments{sm[r][cx][0], sm[r][cx][1], sm[r][cx][2]});
+        float *o = partial + ((long long)split * C + c) * 3;
+        o[0] = t.n; o[1] = t.mean; o[2] = t.m2;
+    }
+}
+
+// What a reduction pass accumulates per channel (the backward uses mode 2; modes 0 and 1 are the two-pass statistics the forward
+// used before the one-pass form above and are not launched any more):
 //   0  sum x                                   -> out0
 //   1  sum (x - mean)^2, mean from `in0`       -> out0          (in0 = the [splits, C] sums of pass 0)
 //   2  sum dy and sum dy * x_hat               -> out0, out1    (x_hat = (x - mean[c]) * std_inv[c])
@@ -50,8 +134,18 @@ __global__ void __launch_bounds__(256) bn_reduce_planes_kernel(const float *__re
     if (MODE == 1) mu = bn_sum_partials(in0, c, C, splits) / (float)((long long)N * S);
     if (MODE == 2) { mu = mean[c]; si = std_inv[c]; }
     float a0 = 0.f, a1 = 0.f;
+    const bool vec = MODE == 2 && (S & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0;
     for (int n = split; n < N; n += splits) {
         const long long base = ((long long)n * C + c) * S;
+        if (vec) {
+            const float4 *x4 = reinterpret_cast<const float4 *>(x + base), *g4 = reinterpret_cast<const float4 *>(dy + base);
+            for (int s = threadIdx.x; s < (S >> 2); s += 256) {
+                const float4 v = __ldg(x4 + s), g = __ldg(g4 + s);
+                a0 += (g.x + g.y) + (g.z + g.w);
+                a1 += (g.x * ((v.x - mu) * si) + g.y * ((v.y - mu) * si)) + (g.z * ((v.z - mu) * si) + g.w * ((v.w - mu) * si));
+            }
+            continue;
+        }
         for (int s = threadIdx.x; s < S; s += 256) {
             const float v = __ldg(x + base + s);
             if (MODE == 0) a0 += v;
@@ -98,16 +192,21 @@ __global__ void __launch_bounds__(256) bn_reduce_rows_kernel(const float *__rest
     }
 }
 
-// mean, 1/std and the running statistics of every channel (training), or the running statistics as they are (inference)
-__global__ void __launch_bounds__(256) bn_finalize_fwd_kernel(const float *__restrict__ sums, const float *__restrict__ sqs,
-                                                              float *__restrict__ running_mean, float *__restrict__ running_var,
-                                                              float *__restrict__ mean_out, float *__restrict__ std_inv_out, int C,
-                                                              int splits, float M, float momentum, float eps, int training) {
+// mean, 1/std and the running statistics of every channel (training: the split rows' moments merged in split order), or the
+// running statistics as they are (inference)
+__global__ void __launch_bounds__(256) bn_finalize_fwd_kernel(const float *__restrict__ moments, float *__restrict__ running_mean,
+                                                              float *__restrict__ running_var, float *__restrict__ mean_out,
+                                                              float *__restrict__ std_inv_out, int C, int splits, float M, float momentum,
+                                                              float eps, int training) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
     if (training) {
-        const float mu = bn_sum_partials(sums, c, C, splits) / M;
-        const float var = bn_sum_partials(sqs, c, C, splits) / M;
+        BnMoments t{0.f, 0.f, 0.f};
+        for (int s = 0; s < splits; s++) {
+            const float *p = moments + ((long long)s * C + c) * 3;
+            t = bn_merge(t, BnMoments{p[0], p[1], p[2]});
+        }
+        const float mu = t.mean, var = t.m2 / M;
         mean_out[c] = mu;
         std_inv_out[c] = 1.0f / sqrtf(var + eps);
         running_mean[c] = (1.0f - momentum) * running_mean[c] + momentum * mu;
@@ -160,6 +259,49 @@ __global__ void __launch_bounds__(256) bn_dx_kernel(const float *__restrict__ dy
     }
 }
 
+// The same two passes for planes of at least 256 floats (a multiple of 4, 16-byte aligned): a block takes whole planes, reads the
+// channel's scalars once per plane and moves 128-bit words - no division per element.
+__global__ void __launch_bounds__(256) bn_normalize_planes_kernel(const float *__restrict__ x, const float *__restrict__ mean,
+                                                                  const float *__restrict__ std_inv, const float *__restrict__ gamma,
+                                                                  const float *__restrict__ beta, float *__restrict__ y, long long planes,
+                                                                  int C, int S) {
+    for (long long p = blockIdx.x; p < planes; p += gridDim.x) {
+        const int c = (int)(p % C);
+        const float mu = __ldg(mean + c), g = __ldg(gamma + c), si = __ldg(std_inv + c), b = __ldg(beta + c);
+        const float4 *x4 = reinterpret_cast<const float4 *>(x + p * S);
+        float4 *y4 = reinterpret_cast<float4 *>(y + p * S);
+        for (int s = threadIdx.x; s < (S >> 2); s += 256) {
+            const float4 v = __ldg(x4 + s);
+            y4[s] = make_float4(g * ((v.x - mu) * si) + b, g * ((v.y - mu) * si) + b, g * ((v.z - mu) * si) + b, g * ((v.w - mu) * si) + b);
+        }
+    }
+}
+__global__ void __launch_bounds__(256) bn_dx_planes_kernel(const float *__restrict__ dy, const float *__restrict__ x, const float *__restrict__ mean,
+                                                           const float *__restrict__ std_inv, const float *__restrict__ gamma,
+                                                           const float *__restrict__ dbeta, const float *__restrict__ dgamma,
+                                                           float *__restrict__ dx, long long planes, int C, int S, float M) {
+    const float inv_M = 1.0f / M;
+    for (long long p = blockIdx.x; p < planes; p += gridDim.x) {
+        const int c = (int)(p % C);
+        const float g = __ldg(gamma + c), si = __ldg(std_inv + c), mu = __ldg(mean + c);
+        const float sb = g * __ldg(dbeta + c), sg = g * __ldg(dgamma + c);
+        const float4 *x4 = reinterpret_cast<const float4 *>(x + p * S), *g4 = reinterpret_cast<const float4 *>(dy + p * S);
+        float4 *d4 = reinterpret_cast<float4 *>(dx + p * S);
+        for (int s = threadIdx.x; s < (S >> 2); s += 256) {
+            const float4 v = __ldg(x4 + s), u = __ldg(g4 + s);
+            float4 o;
+            o.x = inv_M * si * (M * (u.x * g) - sb - ((v.x - mu) * si) * sg);
+            o.y = inv_M * si * (M * (u.y * g) - sb - ((v.y - mu) * si) * sg);
+            o.z = inv_M * si * (M * (u.z * g) - sb - ((v.z - mu) * si) * sg);
+            o.w = inv_M * si * (M * (u.w * g) - sb - ((v.w - mu) * si) * sg);
+            d4[s] = o;
+        }
+    }
+}
+static bool bn_planes_ok(int S, const void *a, const void *b, const void *c) {
+    return S >= 256 && (S & 3) == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
+}
+
 static int bn_splits(int N, int C, int S) {
     long long blocks = S > 1 ? C : (C + 31) / 32;
     long long rows = S > 1 ? N : (N + 7) / 8;
@@ -192,24 +334,34 @@ int seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta, f
     const long long total = (long long)N * C * S;
     cudaStream_t st = rt().stream;
     cudaError_t e = cudaSuccess;
-    float *sums = nullptr, *sqs = nullptr;
+    float *sums = nullptr;                 // [splits, C, 3] moments of the split rows
     int splits = 1;
     if (training) {
         splits = bn_splits(N, C, S);
-        sums = (float *)scratch_alloc((size_t)2 * splits * C * sizeof(float));
+        sums = (float *)scratch_alloc((size_t)3 * splits * C * sizeof(float));
         if (!sums) return SEERA_E_OOM;
-        sqs = sums + (size_t)splits * C;
-        e = bn_reduce<0>(x, nullptr, nullptr, nullptr, nullptr, sums, nullptr, N, C, S, splits);
-        if (e == cudaSuccess) e = bn_reduce<1>(x, nullptr, sums, nullptr, nullptr, sqs, nullptr, N, C, S, splits);
+        if (S > 1) {
+            const int vec = (S & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+            bn_stats_planes_kernel<<<dim3(C, splits), 256, 0, st>>>(x, sums, N, C, S, splits, vec);
+        } else {
+            bn_stats_rows_kernel<<<dim3((C + 31) / 32, splits), 256, 0, st>>>(x, sums, N, C, splits);
+        }
+        count_launch();
+        e = cudaGetLastError();
     }
     if (e == cudaSuccess) {
-        bn_finalize_fwd_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, sqs, running_mean, running_var, mean_out, std_inv_out, C, splits,
+        bn_finalize_fwd_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, running_mean, running_var, mean_out, std_inv_out, C, splits,
                                                                 (float)((long long)N * S), momentum, eps, training);
         count_launch();
         e = cudaGetLastError();
     }
     if (e == cudaSuccess) {
-        bn_normalize_kernel<<<stride_grid(total), 256, 0, st>>>(x, mean_out, std_inv_out, gamma, beta, y, total, C, S);
+        if (bn_planes_ok(S, x, y, x)) {
+            const long long planes = (long long)N * C;
+            bn_normalize_planes_kernel<<<stride_grid(planes * 256), 256, 0, st>>>(x, mean_out, std_inv_out, gamma, beta, y, planes, C, S);
+        } else {
+            bn_normalize_kernel<<<stride_grid(total), 256, 0, st>>>(x, mean_out, std_inv_out, gamma, beta, y, total, C, S);
+        }
         count_launch();
         e = cudaGetLastError();
     }
@@ -235,7 +387,12 @@ int seera_batchnorm_bwd(const float *dy, const float *x, const float *mean, cons
         e = cudaGetLastError();
     }
     if (e == cudaSuccess) {
-        bn_dx_kernel<<<stride_grid(total), 256, 0, st>>>(dy, x, mean, std_inv, gamma, dbeta, dgamma, dx, total, C, S, (float)((long long)N * S));
+        if (bn_planes_ok(S, x, dy, dx)) {
+            const long long planes = (long long)N * C;
+            bn_dx_planes_kernel<<<stride_grid(planes * 256), 256, 0, st>>>(dy, x, mean, std_inv, gamma, dbeta, dgamma, dx, planes, C, S, (float)((long long)N * S));
+        } else {
+            bn_dx_kernel<<<stride_grid(total), 256, 0, st>>>(dy, x, mean, std_inv, gamma, dbeta, dgamma, dx, total, C, S, (float)((long long)N * S));
+        }
         count_launch();
         e = cudaGetLastError();
     }

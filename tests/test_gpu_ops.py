@@ -297,7 +297,8 @@ def test_bad_arguments_return_status_not_crash(E):
     assert L.seera_last_status() == 0
 
 
-@pytest.mark.parametrize("shape", [(7, 5), (64, 300), (4, 6, 3, 5), (16, 33, 14, 14), (3, 1, 1, 1), (512, 64)])
+@pytest.mark.parametrize("shape", [(7, 5), (64, 300), (4, 6, 3, 5), (16, 33, 14, 14), (3, 1, 1, 1), (512, 64), (6, 10, 16, 16), (3, 5, 32, 24),
+                                   (70, 3, 20, 20)])
 def test_batchnorm_forward_and_backward(shape):
     """seera_batchnorm_fwd / _bwd against the oracle (training and inference statistics, running-statistics update)."""
     import ctypes
@@ -332,6 +333,37 @@ def test_batchnorm_forward_and_backward(shape):
         assert np.allclose(down(dgd, (C,)), dg_ref, rtol=1e-4, atol=1e-4) and np.allclose(down(dbd, (C,)), db_ref, rtol=1e-4, atol=1e-4)
         for p in (xd, gd, bd, rmd, rvd, dd, yd, mud, sid, dxd, dgd, dbd):
             L.seera_cuda_free(p)
+
+
+@pytest.mark.parametrize("shape", [(256, 40), (32, 8, 16, 16)])
+def test_batchnorm_statistics_of_data_far_from_zero(shape):
+    """The one-pass statistics (sums around a sample of the data, Chan merges) on inputs whose mean is 1000 standard deviations
+    from zero: mean and 1 / std as close to the fp64 values as the CPU engine's two-pass form, or closer."""
+    import ctypes
+    from ml_framework_b200 import capi
+    L = capi.load()
+    capi.check(L.seera_init(capi.default_device()))
+    rs = np.random.RandomState(5)
+    X = (rs.standard_normal(shape) * 0.05 + 50.0).astype(np.float32)
+    N, C = shape[0], shape[1]
+    S = int(np.prod(shape[2:])) if len(shape) > 2 else 1
+    g, b = np.ones(C, np.float32), np.zeros(C, np.float32)
+    rm, rv = np.zeros(C, np.float32), np.ones(C, np.float32)
+    _, _, mu_ref, si_ref = co.batchnorm_forward(X, g, b, rm.copy(), rv.copy(), 0.1, 1e-5, True)
+    axes = (0,) + tuple(range(2, X.ndim))
+    X64 = X.astype(np.float64)
+    mu64, si64 = X64.mean(axis=axes), 1.0 / np.sqrt(X64.var(axis=axes) + 1e-5)
+    up = lambda a: L.seera_to_device(np.ascontiguousarray(a).ctypes.data_as(ctypes.c_void_p), a.nbytes)
+    xd, gd, bd, rmd, rvd = up(X), up(g), up(b), up(rm), up(rv)
+    yd, mud, sid = L.seera_cuda_malloc(X.nbytes), L.seera_cuda_malloc(4 * C), L.seera_cuda_malloc(4 * C)
+    capi.check(L.seera_batchnorm_fwd(xd, gd, bd, rmd, rvd, yd, mud, sid, N, C, S, 0.1, 1e-5, 1))
+    mu, si = np.empty(C, np.float32), np.empty(C, np.float32)
+    capi.check(L.seera_to_host(mu.ctypes.data_as(ctypes.c_void_p), mud, 4 * C))
+    capi.check(L.seera_to_host(si.ctypes.data_as(ctypes.c_void_p), sid, 4 * C))
+    for p in (xd, gd, bd, rmd, rvd, yd, mud, sid):
+        L.seera_cuda_free(p)
+    assert np.max(np.abs(mu - mu64)) <= 2 * np.max(np.abs(mu_ref - mu64)) + 8e-6         # a few ulp of 50
+    assert rel_l2(si, si64) <= 2 * rel_l2(si_ref, si64) + 2e-5
 
 
 @pytest.mark.parametrize("N,n1,n2", [(1, 1, 1), (5, 7, 3), (16, 64 * 14 * 14, 32 * 14 * 14), (3, 4, 13), (257, 1000, 24)])
