@@ -250,7 +250,7 @@ def run_gpu(args, work):
     if multi:
         dp.init_from_env()
     tr = train.Trainer(work, seed=0, precision=prec)
-    buckets = dp.attach_nccl(tr.model, args.buckets) if multi else []
+    buckets = dp.attach_nccl(tr.model, args.buckets, optimizer=None if args.whole_arena_update else tr.opt) if multi else []
     n = work.batch_size if args.scaling == "weak" else max(1, work.batch_size // world)     # per-rank batch
     NB = 4                                                # distinct batches rotated through the step's input buffers
     host = [work.batch(n, seed=100 + 17 * rank + i) for i in range(NB)]
@@ -447,7 +447,9 @@ def run_gpu(args, work):
                 "gpu_launches": int(e2e_launches), "launches_per_step": launches / args.steps, "final_loss": last,
                 "step_mode": ("eager launches" if not use_graph else "CUDA graph replay of the captured step") +
                              (", gradient buckets summed by NCCL on the engine's communication stream inside the step, overlapping "
-                              "the rest of backward (%d buckets)" % len(buckets) if multi else ""),
+                              "the rest of backward (%d buckets)%s" % (len(buckets), "" if args.whole_arena_update else
+                                                                       ", each bucket's optimizer update enqueued behind its sum")
+                              if multi else ""),
                 "eager_ms_per_step": eager_ms,
                 "algorithmic_gflop_per_step": work.flops_per_sample() * n * world / 1e9,
                 "dp_check": dp_check, "roofline": roof, "cpu_baseline": cpu}
@@ -622,7 +624,10 @@ def main():
                          "3/2 for the fp32 configurations")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="engine option for seera_set_option (repeatable), e.g. tile_n_cap3=128")
-    ap.add_argument("--buckets", type=int, default=3, help="data parallel: gradient buckets (all-reduces) per step")
+    ap.add_argument("--buckets", type=int, default=5, help="data parallel: target number of gradient buckets (all-reduces) per step")
+    ap.add_argument("--whole-arena-update", action="store_true",
+                    help="data parallel: one optimizer launch over the whole arena after the last sum, instead of each bucket's update "
+                         "on the communication stream right behind its sum")
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="N > 1: weak = the configuration's batch on every GPU; strong = that batch split over the GPUs")

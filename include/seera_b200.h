@@ -429,6 +429,10 @@ int seera_sgd_step_dev(float *w, const float *g, float *vel, int n, const float 
  *                        ordered after everything the compute stream holds so far; returns at once, so the
  *                        backward kernels of earlier layers overlap the exchange
  *   seera_dp_join        the compute stream waits for every range enqueued since the last join
+ *   seera_dp_side_begin / _end   between the two, every launch of this library goes to the communication stream, behind the
+ *                        sums enqueued there and behind what the compute stream held at the call; meant for the optimizer's
+ *                        update of a bucket right behind that bucket's sum (entries that take pool scratch must not run
+ *                        there).  seera_dp_join covers these launches too and ends a window left open.
  *                        (reduce_range and join are event edges: a step recorded with seera_graph_begin/end
  *                        carries its collectives inside the one graph)
  *   seera_dp_poll        NCCL's asynchronous error state as a status
@@ -449,6 +453,8 @@ int   seera_dp_allreduce(float *buf, long long n, int op);
 int   seera_dp_broadcast(float *buf, long long n, int root);
 int   seera_dp_reduce_range(float *arena, long long begin, long long end);
 int   seera_dp_join(void);
+int   seera_dp_side_begin(void);
+int   seera_dp_side_end(void);
 int   seera_dp_poll(void);
 int   seera_dp_wait_host(int timeout_ms);
 int   seera_dp_abort(void);

@@ -107,6 +107,8 @@ struct ProfBytes {
 float *grad_scale_words();
 
 // Pool-backed scratch for internal use (split-K partials, operand shadows).
+void graph_note_collective();              // runtime.cu: the open capture records a collective
+void graphs_with_collectives_release();     // runtime.cu: destroy the executable graphs that hold collectives (before the communicator goes)
 void *scratch_alloc(size_t bytes);
 void scratch_free(void *p);
 

@@ -19,9 +19,11 @@
 #include <nccl.h>
 
 #include <chrono>
+#include <cstdio>
 #include <cstring>
 #include <thread>
 #include <unordered_map>
+#include <vector>
 
 #include "common.cuh"
 
@@ -56,7 +58,11 @@ struct Dp {
     cudaStream_t comm_stream = nullptr;
     cudaEvent_t fork_ev = nullptr, done_ev = nullptr;
     bool pending = false;                     // a range was enqueued since the last join
+    cudaStream_t main_stream = nullptr;       // the compute stream while launches are diverted (seera_dp_side_begin)
+    bool side = false;
     std::unordered_map<void *, Registration> regs;
+    std::vector<void *> reg_order;            // blocks in the order they were registered: window (de)registration is collective
+                                              // over the ranks, so every rank must walk its blocks in the same order
 };
 Dp &dp() { static Dp d; return d; }
 
@@ -174,6 +180,7 @@ void *seera_dp_alloc(size_t bytes) {
     }
     cudaMemsetAsync(p, 0, bytes, rt().stream);
     d.regs[p] = reg;
+    d.reg_order.push_back(p);
     return p;
 }
 
@@ -190,6 +197,8 @@ int seera_dp_free(void *p) {
     }
     d.api.MemFree(p);
     d.regs.erase(it);
+    for (size_t i = 0; i < d.reg_order.size(); i++)
+        if (d.reg_order[i] == p) { d.reg_order.erase(d.reg_order.begin() + (long)i); break; }
     return SEERA_OK;
 }
 
@@ -212,6 +221,7 @@ int seera_dp_allreduce(float *buf, long long n, int op) {
     if (int s = red_op(op, &o)) return s;
     Dp &d = dp();
     SEERA_NCCL(d.api.AllReduce(buf, buf, (size_t)n, ncclFloat, o, d.comm, rt().stream), "ncclAllReduce");
+    graph_note_collective();
     count_launch();
     return SEERA_OK;
 }
@@ -223,6 +233,7 @@ int seera_dp_broadcast(float *buf, long long n, int root) {
     if (n == 0) return SEERA_OK;
     Dp &d = dp();
     SEERA_NCCL(d.api.Broadcast(buf, buf, (size_t)n, ncclFloat, root, d.comm, rt().stream), "ncclBroadcast");
+    graph_note_collective();
     count_launch();
     return SEERA_OK;
 }
@@ -238,8 +249,35 @@ int seera_dp_reduce_range(float *arena, long long begin, long long end) {
     if (int s = check_cuda(cudaEventRecord(d.fork_ev, rt().stream), "cudaEventRecord")) return s;
     if (int s = check_cuda(cudaStreamWaitEvent(d.comm_stream, d.fork_ev, 0), "cudaStreamWaitEvent")) return s;
     SEERA_NCCL(d.api.AllReduce(arena + begin, arena + begin, (size_t)(end - begin), ncclFloat, ncclSum, d.comm, d.comm_stream), "ncclAllReduce");
+    graph_note_collective();
     count_launch();
     d.pending = true;
+    return SEERA_OK;
+}
+
+/* Between seera_dp_side_begin() and seera_dp_side_end() every launch of this library goes to the communication stream, behind
+ * the collectives already enqueued there and behind what the compute stream held at the call: the optimizer's update of a
+ * bucket follows that bucket's sum without waiting for the rest of backward, and seera_dp_join() covers it like the sums.
+ * Only for entries that take no scratch memory from the pool (the optimizer steps): the pool recycles blocks in the order
+ * of ONE stream. */
+int seera_dp_side_begin(void) {
+    SEERA_ENSURE();
+    if (int s = need_comm("dp_side_begin")) return s;
+    Dp &d = dp();
+    if (d.side) return fail(SEERA_E_ARG, "dp_side_begin: already diverted");
+    if (int s = check_cuda(cudaEventRecord(d.fork_ev, rt().stream), "cudaEventRecord")) return s;
+    if (int s = check_cuda(cudaStreamWaitEvent(d.comm_stream, d.fork_ev, 0), "cudaStreamWaitEvent")) return s;
+    d.main_stream = rt().stream;
+    rt().stream = d.comm_stream;
+    d.side = true;
+    d.pending = true;
+    return SEERA_OK;
+}
+int seera_dp_side_end(void) {
+    Dp &d = dp();
+    if (!d.side) return SEERA_OK;
+    rt().stream = d.main_stream;
+    d.side = false;
     return SEERA_OK;
 }
 
@@ -247,6 +285,7 @@ int seera_dp_reduce_range(float *arena, long long begin, long long end) {
 int seera_dp_join(void) {
     SEERA_ENSURE();
     Dp &d = dp();
+    if (d.side) seera_dp_side_end();
     if (!d.comm || !d.pending) return SEERA_OK;
     if (int s = check_cuda(cudaEventRecord(d.done_ev, d.comm_stream), "cudaEventRecord")) return s;
     if (int s = check_cuda(cudaStreamWaitEvent(rt().stream, d.done_ev, 0), "cudaStreamWaitEvent")) return s;
@@ -302,6 +341,7 @@ int seera_dp_wait_host(int timeout_ms) {
         d.comm = nullptr;
         d.pending = false;
         d.regs.clear();                    // the registrations went with the communicator; the memory stays allocated
+        d.reg_order.clear();
     }
     return status;
 }
@@ -310,26 +350,33 @@ int seera_dp_wait_host(int timeout_ms) {
  * Blocks seera_dp_alloc handed out stay allocated until the process ends. */
 int seera_dp_abort(void) {
     Dp &d = dp();
+    seera_dp_side_end();
     if (!d.comm) return SEERA_OK;
     d.api.CommAbort(d.comm);
     d.comm = nullptr;
     d.pending = false;
     d.regs.clear();
+    d.reg_order.clear();
     d.world = 1; d.rank = 0;
     return SEERA_OK;
 }
 
 int seera_dp_finalize(void) {
     Dp &d = dp();
+    seera_dp_side_end();
     if (!d.comm) return SEERA_OK;
     cudaStreamSynchronize(rt().stream);
     cudaStreamSynchronize(d.comm_stream);
-    for (auto &kv : d.regs) {
-        if (kv.second.win && d.api.CommWindowDeregister) d.api.CommWindowDeregister(d.comm, kv.second.win);
-        if (kv.second.handle) d.api.CommDeregister(d.comm, kv.second.handle);
-        d.api.MemFree(kv.first);
+    graphs_with_collectives_release();         // recordings that hold this communicator's launches go first
+    for (void *p : d.reg_order) {              // registration order, the same on every rank (not the map's hash order)
+        auto it = d.regs.find(p);
+        if (it == d.regs.end()) continue;
+        if (it->second.win && d.api.CommWindowDeregister) d.api.CommWindowDeregister(d.comm, it->second.win);
+        if (it->second.handle) d.api.CommDeregister(d.comm, it->second.handle);
+        d.api.MemFree(p);
     }
     d.regs.clear();
+    d.reg_order.clear();
     d.api.CommDestroy(d.comm);
     d.comm = nullptr;
     if (d.comm_stream) { cudaStreamDestroy(d.comm_stream); d.comm_stream = nullptr; }

@@ -66,7 +66,9 @@ struct GraphRec {
     std::vector<std::pair<void *, size_t>> blocks;      // every block handed out while the graph was captured
     uint64_t kernels = 0;                               // kernel launches recorded in the graph
     uint64_t launches_at_begin = 0;
+    bool collectives = false;                           // the recording holds launches of the data-parallel communicator
 };
+static std::vector<GraphRec *> &live_graphs() { static std::vector<GraphRec *> v; return v; }
 struct Pool {
     std::map<size_t, std::vector<void *>> free_lists;   // rounded size -> cached blocks
     std::unordered_map<void *, size_t> live;            // every block handed out -> rounded size
@@ -139,6 +141,25 @@ static void profile_collect() {
 void *scratch_alloc(size_t bytes) { return seera_cuda_malloc(bytes); }
 void scratch_free(void *p) { seera_cuda_free(p); }
 
+}  // namespace seera
+
+namespace seera {
+// dp.cu: a collective is being recorded into the open capture
+void graph_note_collective() {
+    Pool &p = pool();
+    if (p.capturing && p.cur) p.cur->collectives = true;
+}
+// dp.cu, before the communicator goes away: the library that runs the collectives keeps per-recording state alive as long as a
+// recording that holds its launches exists, and tearing the communicator down waits for that state.  The executable graphs are
+// destroyed here; their handles stay valid for seera_graph_destroy, and seera_graph_launch on them reports an error.
+void graphs_with_collectives_release() {
+    if (rt().stream) cudaStreamSynchronize(rt().stream);
+    for (GraphRec *g : live_graphs()) {
+        if (!g->collectives) continue;
+        if (g->exec) { cudaGraphExecDestroy(g->exec); g->exec = nullptr; }
+        if (g->graph) { cudaGraphDestroy(g->graph); g->graph = nullptr; }
+    }
+}
 }  // namespace seera
 
 using namespace seera;
@@ -364,13 +385,14 @@ void *seera_graph_end(void) {
         seera_graph_destroy(g);
         return nullptr;
     }
+    live_graphs().push_back(g);
     return g;
 }
 
 int seera_graph_launch(void *graph) {
     SEERA_ENSURE();
     GraphRec *g = static_cast<GraphRec *>(graph);
-    if (!g || !g->exec) return fail(SEERA_E_ARG, "graph_launch: not a captured graph");
+    if (!g || !g->exec) return fail(SEERA_E_ARG, "graph_launch: not a captured graph (or one whose communicator has been finalized)");
     rt().launches += g->kernels;
     return check_cuda(cudaGraphLaunch(g->exec, rt().stream), "cudaGraphLaunch");
 }
@@ -386,6 +408,9 @@ int seera_graph_destroy(void *graph) {
         p.owner.erase(b.first);
         if (!p.live.count(b.first)) p.free_lists[b.second].push_back(b.first);   // idle: back to the general pool
     }
+    auto &lg = live_graphs();
+    for (size_t i = 0; i < lg.size(); i++)
+        if (lg[i] == g) { lg.erase(lg.begin() + (long)i); break; }
     delete g;
     return SEERA_OK;
 }

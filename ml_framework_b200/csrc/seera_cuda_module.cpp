@@ -293,6 +293,8 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("dp_broadcast", [](uptr p, long long n, int root) { ck(seera_dp_broadcast(P<F>(p), n, root)); });
     m.def("dp_reduce_range", [](uptr p, long long b, long long e) { ck(seera_dp_reduce_range(P<F>(p), b, e)); });
     m.def("dp_join", []() { ck(seera_dp_join()); });
+    m.def("dp_side_begin", []() { ck(seera_dp_side_begin()); });
+    m.def("dp_side_end", []() { ck(seera_dp_side_end()); });
     m.def("dp_poll", []() { ck(seera_dp_poll()); });
     m.def("dp_wait_host", [](int timeout_ms) { py::gil_scoped_release nogil; ck(seera_dp_wait_host(timeout_ms)); });
     m.def("dp_abort", []() { ck(seera_dp_abort()); });

@@ -38,17 +38,22 @@ def plan_buckets(model, target_buckets=3):
     return buckets
 
 
-def attach(model, world, reduce_range, wait, target_buckets=3, join=None):
+def attach(model, world, reduce_range, wait, target_buckets=3, join=None, after_reduce=None):
     """Installs the hooks on `model`; returns the bucket list.  `reduce_range(begin, end) -> handle` starts an in-place
     sum over the ranks of floats [begin, end) of the model's gradient arena; `wait(handle)` completes one; `join()`
-    (optional) is called once after all waits."""
+    (optional) is called once after all waits.  `after_reduce(handle, begin, end)` (optional) runs right after a range's
+    sum has been started - the place to enqueue the optimizer's update of that range behind the sum (see
+    `update_in_buckets`)."""
     buckets = plan_buckets(model, target_buckets)
     state = {"works": [], "next": 0}
 
     def fire_upto(offset):
         while state["next"] < len(buckets) and offset <= buckets[state["next"]][0]:
             b, e = buckets[state["next"]]
-            state["works"].append(reduce_range(b, e))
+            h = reduce_range(b, e)
+            state["works"].append(h)
+            if after_reduce is not None:
+                after_reduce(h, b, e)
             state["next"] += 1
 
     def on_grad_ready(t):
@@ -172,17 +177,43 @@ def init_from_env(timeout_s=120.0, directory=None):
     return rv
 
 
-def attach_nccl(model, target_buckets=3):
+def update_in_buckets(optimizer, complete=None):
+    """An `after_reduce` callback that applies `optimizer`'s update to a bucket as soon as its sum is under way, instead of one
+    update of the whole arena after the last sum.  `complete(handle)` makes the sum's result visible first where enqueueing
+    order does not (host-memory collectives); with the engine's collectives the update is enqueued on the communication
+    stream right behind the sum (seera_dp_side_begin / _end), so the weights of the late layers are updated while backward
+    still runs through the early ones and only the last, small bucket's sum and update remain after backward."""
+    optimizer.updates_by_bucket = True
+
+    def after(handle, b, e):
+        if complete is not None:
+            complete(handle)
+        optimizer.update_range(b, e)
+    return after
+
+
+def attach_nccl(model, target_buckets=3, optimizer=None):
     """Moves the model's gradient arena into memory registered with the communicator and installs the bucket hooks over
-    the engine's collectives.  Returns the bucket list."""
+    the engine's collectives.  With `optimizer`, each bucket is updated on the communication stream right behind its sum
+    (`update_in_buckets`).  Returns the bucket list."""
     from . import seera_cuda as sc
     world = sc.dp_world()
     ptr = sc.dp_alloc(4 * max(model.n_arena, 1))
     model.rehome_grads(ptr)
     arena = model.grads.main_ptr
     model._collectives_capturable = True
+    after = None
+    if optimizer is not None:
+        inner = update_in_buckets(optimizer)
+
+        def after(handle, b, e):
+            sc.dp_side_begin()
+            try:
+                inner(handle, b, e)
+            finally:
+                sc.dp_side_end()
     return attach(model, world, reduce_range=lambda b, e: sc.dp_reduce_range(arena, b, e), wait=lambda h: None,
-                  target_buckets=target_buckets, join=sc.dp_join)
+                  target_buckets=target_buckets, join=sc.dp_join, after_reduce=after)
 
 
 def replicas_differ_by(model):

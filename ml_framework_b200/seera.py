@@ -1154,6 +1154,10 @@ class _Optimizer:
         self.model = model
         self.use_gpu = True
         self._hyper = cuten(np.zeros(16, np.float32))
+        # data parallel: the bucket hooks apply the update range by range behind each bucket's sum (dp.update_in_buckets);
+        # step() then only completes the sums
+        self.updates_by_bucket = False
+        self._advanced = False
 
     def _state(self):
         n = max(self.model.n_arena, 1)
@@ -1189,12 +1193,29 @@ class _Optimizer:
             sc.upload_f32(dst.main_ptr, a)
         return o
 
+    def begin_step(self):
+        """Call before backward when the update runs bucket by bucket during it: the step's scalars must be on the device before
+        the first bucket's update is enqueued.  A no-op otherwise and inside a capture (replays refresh the scalars themselves)."""
+        if self.updates_by_bucket and not sc.is_capturing() and not self._advanced:
+            self.advance()
+            self._advanced = True
+
+    def update_range(self, begin, end):
+        """The update of arena slots [begin, end) alone (the same arithmetic as the whole-arena launch)."""
+        if not sc.is_capturing() and not self._advanced:        # first range of a step whose caller did not call begin_step()
+            self.advance()
+            self._advanced = True
+        if end > begin:
+            self._enqueue(begin, end)
+
     def step(self):
         """One update.  Outside a capture this also refreshes the device scalars and advances the step count."""
-        if not sc.is_capturing():
+        if not sc.is_capturing() and not self._advanced:
             self.advance()
+        self._advanced = False
         self._grads_ready()
-        self._enqueue()
+        if not (self.updates_by_bucket and self.model._allreduce is not None):
+            self._enqueue()
 
 
 class SGD(_Optimizer):
@@ -1211,9 +1232,11 @@ class SGD(_Optimizer):
     def state_dict(self):
         return {"kind": "sgd", "lr": self.lr, "momentum": self.momentum, "velocity": self.velocity.to_host_f32().copy()}
 
-    def _enqueue(self):
+    def _enqueue(self, begin=0, end=None):
         m = self.model
-        sc.cuda_sgd_step_dev(m.params.main_ptr, m.grads.main_ptr, self.velocity.main_ptr, m.n_arena, self._hyper.main_ptr)
+        end = m.n_arena if end is None else end
+        o = 4 * begin
+        sc.cuda_sgd_step_dev(m.params.main_ptr + o, m.grads.main_ptr + o, self.velocity.main_ptr + o, end - begin, self._hyper.main_ptr)
 
 
 class Adam(_Optimizer):
@@ -1233,7 +1256,9 @@ class Adam(_Optimizer):
         return {"kind": "adam", "lr": self.lr, "beta1": self.beta1, "beta2": self.beta2, "eps": self.eps, "t": self.t,
                 "m": self.m.to_host_f32().copy(), "v": self.v.to_host_f32().copy()}
 
-    def _enqueue(self):
+    def _enqueue(self, begin=0, end=None):
         md = self.model
-        sc.cuda_adam_step_dev(md.params.main_ptr, md.grads.main_ptr, self.m.main_ptr, self.v.main_ptr, md.n_arena,
+        end = md.n_arena if end is None else end
+        o = 4 * begin
+        sc.cuda_adam_step_dev(md.params.main_ptr + o, md.grads.main_ptr + o, self.m.main_ptr + o, self.v.main_ptr + o, end - begin,
                               self._hyper.main_ptr)

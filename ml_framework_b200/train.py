@@ -82,6 +82,7 @@ class Trainer:
         return loss
 
     def step(self, X, Y):
+        self.opt.begin_step()
         loss = self.forward_backward(X, Y)
         self.opt.step()
         return loss

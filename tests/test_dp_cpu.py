@@ -10,7 +10,7 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, case, out_dir):
+def _worker(rank, world, port, case, out_dir, by_bucket=False):
     sys.path[:0] = [ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "tests", "golden")]
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import torch
@@ -33,23 +33,29 @@ def _worker(rank, world, port, case, out_dir):
         t = torch.from_numpy(view)
         order.append((b, e))
         return dist.all_reduce(t, op=dist.ReduceOp.SUM, async_op=True)
-    buckets = dp.attach(tr.model, world, reduce_range, lambda w: w.wait(), target_buckets=3)
+    # by_bucket: the optimizer updates each bucket right after its sum (completed first: host memory has no stream order)
+    after = dp.update_in_buckets(tr.opt, complete=lambda w: w.wait()) if by_bucket else None
+    buckets = dp.attach(tr.model, world, reduce_range, lambda w: w.wait(), target_buckets=3, after_reduce=after)
     for _ in range(2):
         tr.step(X[shard], Y[shard])
     assert order[:len(buckets)] == buckets and len(order) == 2 * len(buckets)
+    if by_bucket:
+        n_updates = fake.CALLS.get("adam", 0) + fake.CALLS.get("sgd", 0)
+        assert n_updates == 2 * len(buckets), (n_updates, len(buckets))
     np.savez(os.path.join(out_dir, "rank%d.npz" % rank), *[p for P in tr.host_params() if P is not None for p in P])
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("by_bucket", [False, True])
 @pytest.mark.parametrize("case", ["c2s", "c3s"])
-def test_two_ranks_match_the_single_process_step(case, tmp_path):
+def test_two_ranks_match_the_single_process_step(case, by_bucket, tmp_path):
     import torch.multiprocessing as mp
     from oracle import cpu_oracle as co
     from oracle.train_oracle import RefNet
     from conftest import rel_l2
     import cases
     port = 29500 + (os.getpid() % 2000)
-    mp.spawn(_worker, args=(2, port, case, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, case, str(tmp_path), by_bucket), nprocs=2, join=True)
     work, n = cases.small_cases()[case]
     X, Y = work.batch(n, 2)
     ref = RefNet(work.layers, work.params(2), work.loss, work.opt, co)
