@@ -167,6 +167,17 @@ int   seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta,
                           float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training);
 int   seera_batchnorm_bwd(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
                           float *dgamma, float *dbeta, int N, int C, int S);
+/* The same over the shards of ALL ranks of the data-parallel communicator (seera_dp_init; with one rank or none they are the
+ * calls above).  Forward: every rank's per-channel moments (count, mean, sum of squared differences) travel in one small sum over
+ * the ranks and are merged in rank order, so every rank normalises with the statistics of the joined batch and moves its running
+ * statistics by them.  Backward: the two sums of the dx formula and the element count are summed over the ranks first; dgamma /
+ * dbeta stay the rank's own sums, which the gradient exchange averages like every other parameter gradient.  A sharded step
+ * then equals the step on the joined batch.  The collectives run on the compute stream and can be recorded into a graph.
+ * No counterpart in the reference (it has neither a device BatchNorm nor a multi-GPU path). */
+int   seera_batchnorm_fwd_sync(const float *x, const float *gamma, const float *beta, float *running_mean, float *running_var, float *y,
+                               float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training);
+int   seera_batchnorm_bwd_sync(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
+                               float *dgamma, float *dbeta, int N, int C, int S);
 /* Concatenation of two tensors along axis 1 ([N, n1] and [N, n2] rows, n = C*H*W of each sample) and the backward
  * split of the joined gradient, one launch each.  Replaces the per-sample cudaMemcpy loops of cuten.concatenate2D /
  * concatenate1D and their backward forms (cuTen.py:688-796, used by Seera_init.py:764-779, Seera_Engine.py:418-429). */

@@ -118,23 +118,16 @@ __global__ void __launch_bounds__(256) bn_stats_rows_kernel(const float *__restr
     }
 }
 
-// What a reduction pass accumulates per channel (the backward uses mode 2; modes 0 and 1 are the two-pass statistics the forward
-// used before the one-pass form above and are not launched any more):
-//   0  sum x                                   -> out0
-//   1  sum (x - mean)^2, mean from `in0`       -> out0          (in0 = the [splits, C] sums of pass 0)
-//   2  sum dy and sum dy * x_hat               -> out0, out1    (x_hat = (x - mean[c]) * std_inv[c])
-template <int MODE>
+// ---- backward sums: per channel  sum dy -> out0  and  sum dy * x_hat -> out1,  x_hat = (x - mean[c]) * std_inv[c] ----------
 __global__ void __launch_bounds__(256) bn_reduce_planes_kernel(const float *__restrict__ x, const float *__restrict__ dy,
-                                                               const float *__restrict__ in0, const float *__restrict__ mean,
+                                                               const float *__restrict__ mean,
                                                                const float *__restrict__ std_inv, float *__restrict__ out0,
                                                                float *__restrict__ out1, int N, int C, int S, int splits) {
     __shared__ float sm[8];
     const int c = blockIdx.x, split = blockIdx.y;
-    float mu = 0.f, si = 0.f;
-    if (MODE == 1) mu = bn_sum_partials(in0, c, C, splits) / (float)((long long)N * S);
-    if (MODE == 2) { mu = mean[c]; si = std_inv[c]; }
+    const float mu = mean[c], si = std_inv[c];
     float a0 = 0.f, a1 = 0.f;
-    const bool vec = MODE == 2 && (S & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0;
+    const bool vec = (S & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0;
     for (int n = split; n < N; n += splits) {
         const long long base = ((long long)n * C + c) * S;
         if (vec) {
@@ -148,37 +141,32 @@ __global__ void __launch_bounds__(256) bn_reduce_planes_kernel(const float *__re
         }
         for (int s = threadIdx.x; s < S; s += 256) {
             const float v = __ldg(x + base + s);
-            if (MODE == 0) a0 += v;
-            if (MODE == 1) { const float d = v - mu; a0 += d * d; }
-            if (MODE == 2) { const float g = __ldg(dy + base + s); a0 += g; a1 += g * ((v - mu) * si); }
+            const float g = __ldg(dy + base + s);
+            a0 += g; a1 += g * ((v - mu) * si);
         }
     }
     a0 = bn_block_sum(a0, sm);
-    if (MODE == 2) a1 = bn_block_sum(a1, sm);
+    a1 = bn_block_sum(a1, sm);
     if (threadIdx.x == 0) {
         out0[(long long)split * C + c] = a0;
-        if (MODE == 2) out1[(long long)split * C + c] = a1;
+        out1[(long long)split * C + c] = a1;
     }
 }
-template <int MODE>
 __global__ void __launch_bounds__(256) bn_reduce_rows_kernel(const float *__restrict__ x, const float *__restrict__ dy,
-                                                             const float *__restrict__ in0, const float *__restrict__ mean,
+                                                             const float *__restrict__ mean,
                                                              const float *__restrict__ std_inv, float *__restrict__ out0,
                                                              float *__restrict__ out1, int N, int C, int splits) {
     __shared__ float s0[8][32], s1[8][32];
     const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
     const int c = blockIdx.x * 32 + cx, split = blockIdx.y;
     const bool live = c < C;
-    float mu = 0.f, si = 0.f;
-    if (MODE == 1 && live) mu = bn_sum_partials(in0, c, C, splits) / (float)N;
-    if (MODE == 2 && live) { mu = mean[c]; si = std_inv[c]; }
+    const float mu = live ? mean[c] : 0.f, si = live ? std_inv[c] : 0.f;
     float a0 = 0.f, a1 = 0.f;
     if (live) {
         for (int n = split * 8 + ry; n < N; n += splits * 8) {
             const float v = __ldg(x + (long long)n * C + c);
-            if (MODE == 0) a0 += v;
-            if (MODE == 1) { const float d = v - mu; a0 += d * d; }
-            if (MODE == 2) { const float g = __ldg(dy + (long long)n * C + c); a0 += g; a1 += g * ((v - mu) * si); }
+            const float g = __ldg(dy + (long long)n * C + c);
+            a0 += g; a1 += g * ((v - mu) * si);
         }
     }
     s0[ry][cx] = a0; s1[ry][cx] = a1;
@@ -188,7 +176,7 @@ __global__ void __launch_bounds__(256) bn_reduce_rows_kernel(const float *__rest
 #pragma unroll
         for (int r = 0; r < 8; r++) { t0 += s0[r][cx]; t1 += s1[r][cx]; }
         out0[(long long)split * C + c] = t0;
-        if (MODE == 2) out1[(long long)split * C + c] = t1;
+        out1[(long long)split * C + c] = t1;
     }
 }
 
@@ -206,7 +194,7 @@ __global__ void __launch_bounds__(256) bn_finalize_fwd_kernel(const float *__res
             const float *p = moments + ((long long)s * C + c) * 3;
             t = bn_merge(t, BnMoments{p[0], p[1], p[2]});
         }
-        const float mu = t.mean, var = t.m2 / M;
+        const float mu = t.mean, var = t.m2 / (M > 0.f ? M : t.n);        // M <= 0: the count comes with the moments (shards of several ranks)
         mean_out[c] = mu;
         std_inv_out[c] = 1.0f / sqrtf(var + eps);
         running_mean[c] = (1.0f - momentum) * running_mean[c] + momentum * mu;
@@ -215,6 +203,27 @@ __global__ void __launch_bounds__(256) bn_finalize_fwd_kernel(const float *__res
         mean_out[c] = running_mean[c];
         std_inv_out[c] = 1.0f / sqrtf(running_var[c] + eps);
     }
+}
+// Cross-rank statistics: this rank's moments (its split rows merged in split order) into its slot of a [world, C, 3] table whose
+// other slots are zero; the table is then summed over the ranks - adding zeros is exact, so every rank ends with every rank's
+// moments - and bn_finalize_fwd_kernel merges the `world` rows in rank order like split rows.
+__global__ void __launch_bounds__(256) bn_merge_local_kernel(const float *__restrict__ moments, float *__restrict__ slot, int C, int splits) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    BnMoments t{0.f, 0.f, 0.f};
+    for (int s = 0; s < splits; s++) {
+        const float *p = moments + ((long long)s * C + c) * 3;
+        t = bn_merge(t, BnMoments{p[0], p[1], p[2]});
+    }
+    slot[c * 3] = t.n; slot[c * 3 + 1] = t.mean; slot[c * 3 + 2] = t.m2;
+}
+// Backward across ranks: sums[0..C) = sum dy, sums[C..2C) = sum dy * x_hat of this rank, sums[2C] = its element count per channel;
+// summed over the ranks before bn_dx reads them.
+__global__ void __launch_bounds__(256) bn_pack_sums_kernel(const float *__restrict__ dbeta, const float *__restrict__ dgamma,
+                                                           float *__restrict__ sums, int C, float count) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < C) { sums[c] = dbeta[c]; sums[C + c] = dgamma[c]; }
+    if (c == 0) sums[2 * C] = count;
 }
 __global__ void __launch_bounds__(256) bn_finalize_bwd_kernel(const float *__restrict__ p0, const float *__restrict__ p1,
                                                               float *__restrict__ dbeta, float *__restrict__ dgamma, int C, int splits) {
@@ -246,8 +255,10 @@ __global__ void __launch_bounds__(256) bn_normalize_kernel(const float *__restri
 __global__ void __launch_bounds__(256) bn_dx_kernel(const float *__restrict__ dy, const float *__restrict__ x, const float *__restrict__ mean,
                                                     const float *__restrict__ std_inv, const float *__restrict__ gamma,
                                                     const float *__restrict__ dbeta, const float *__restrict__ dgamma,
-                                                    float *__restrict__ dx, long long total, int C, int S, float M) {
+                                                    float *__restrict__ dx, long long total, int C, int S, float M,
+                                                    const float *__restrict__ M_dev) {
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    if (M_dev) M = __ldg(M_dev);                    // the count over all ranks' shards
     const float inv_M = 1.0f / M;
     const bool small = total < (1LL << 31);
     for (long long e = tid; e < total; e += nthr) {
@@ -279,7 +290,9 @@ __global__ void __launch_bounds__(256) bn_normalize_planes_kernel(const float *_
 __global__ void __launch_bounds__(256) bn_dx_planes_kernel(const float *__restrict__ dy, const float *__restrict__ x, const float *__restrict__ mean,
                                                            const float *__restrict__ std_inv, const float *__restrict__ gamma,
                                                            const float *__restrict__ dbeta, const float *__restrict__ dgamma,
-                                                           float *__restrict__ dx, long long planes, int C, int S, float M) {
+                                                           float *__restrict__ dx, long long planes, int C, int S, float M,
+                                                           const float *__restrict__ M_dev) {
+    if (M_dev) M = __ldg(M_dev);
     const float inv_M = 1.0f / M;
     for (long long p = blockIdx.x; p < planes; p += gridDim.x) {
         const int c = (int)(p % C);
@@ -310,12 +323,11 @@ static int bn_splits(int N, int C, int S) {
     if (s > BN_MAX_SPLITS) s = BN_MAX_SPLITS;
     return s < 1 ? 1 : (int)s;
 }
-template <int MODE>
-static cudaError_t bn_reduce(const float *x, const float *dy, const float *in0, const float *mean, const float *std_inv, float *out0,
-                             float *out1, int N, int C, int S, int splits) {
+static cudaError_t bn_reduce(const float *x, const float *dy, const float *mean, const float *std_inv, float *out0, float *out1, int N, int C,
+                             int S, int splits) {
     cudaStream_t st = rt().stream;
-    if (S > 1) bn_reduce_planes_kernel<MODE><<<dim3(C, splits), 256, 0, st>>>(x, dy, in0, mean, std_inv, out0, out1, N, C, S, splits);
-    else bn_reduce_rows_kernel<MODE><<<dim3((C + 31) / 32, splits), 256, 0, st>>>(x, dy, in0, mean, std_inv, out0, out1, N, C, splits);
+    if (S > 1) bn_reduce_planes_kernel<<<dim3(C, splits), 256, 0, st>>>(x, dy, mean, std_inv, out0, out1, N, C, S, splits);
+    else bn_reduce_rows_kernel<<<dim3((C + 31) / 32, splits), 256, 0, st>>>(x, dy, mean, std_inv, out0, out1, N, C, splits);
     count_launch();
     return cudaGetLastError();
 }
@@ -326,16 +338,20 @@ using namespace seera;
 
 extern "C" {
 
-int seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta, float *running_mean, float *running_var, float *y,
-                        float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training) {
+// cross != 0 and a data-parallel communicator of more than one rank: statistics (forward) and the two sums of the dx formula
+// (backward) over the shards of all ranks; dgamma / dbeta stay this rank's own sums (the gradient exchange averages them like
+// every other parameter gradient).
+static int bn_fwd_impl(const float *x, const float *gamma, const float *beta, float *running_mean, float *running_var, float *y,
+                       float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training, int cross) {
     SEERA_ENSURE();
     if (N < 1 || C < 1 || S < 1 || C > 65535 || !x || !gamma || !beta || !running_mean || !running_var || !y || !mean_out || !std_inv_out)
         return fail(SEERA_E_ARG, "batchnorm_fwd: bad argument");
     const long long total = (long long)N * C * S;
+    const int world = cross ? seera_dp_world() : 1;
     cudaStream_t st = rt().stream;
     cudaError_t e = cudaSuccess;
-    float *sums = nullptr;                 // [splits, C, 3] moments of the split rows
-    int splits = 1;
+    float *sums = nullptr, *table = nullptr;      // [splits, C, 3] moments of the split rows; [world, C, 3] moments of the ranks
+    int splits = 1, status = SEERA_OK;
     if (training) {
         splits = bn_splits(N, C, S);
         sums = (float *)scratch_alloc((size_t)3 * splits * C * sizeof(float));
@@ -348,14 +364,28 @@ int seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta, f
         }
         count_launch();
         e = cudaGetLastError();
+        if (e == cudaSuccess && world > 1) {
+            const size_t tn = (size_t)world * C * 3;
+            table = (float *)scratch_alloc(tn * sizeof(float));
+            if (!table) { scratch_free(sums); return SEERA_E_OOM; }
+            e = cudaMemsetAsync(table, 0, tn * sizeof(float), st);
+            if (e == cudaSuccess) {
+                bn_merge_local_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, table + (size_t)seera_dp_rank() * C * 3, C, splits);
+                count_launch();
+                e = cudaGetLastError();
+            }
+            if (e == cudaSuccess) status = seera_dp_allreduce(table, (long long)tn, 0);
+        }
     }
-    if (e == cudaSuccess) {
-        bn_finalize_fwd_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, running_mean, running_var, mean_out, std_inv_out, C, splits,
-                                                                (float)((long long)N * S), momentum, eps, training);
+    if (e == cudaSuccess && status == SEERA_OK) {
+        if (table) bn_finalize_fwd_kernel<<<(C + 255) / 256, 256, 0, st>>>(table, running_mean, running_var, mean_out, std_inv_out, C, world,
+                                                                           0.f, momentum, eps, training);
+        else bn_finalize_fwd_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, running_mean, running_var, mean_out, std_inv_out, C, splits,
+                                                                     (float)((long long)N * S), momentum, eps, training);
         count_launch();
         e = cudaGetLastError();
     }
-    if (e == cudaSuccess) {
+    if (e == cudaSuccess && status == SEERA_OK) {
         if (bn_planes_ok(S, x, y, x)) {
             const long long planes = (long long)N * C;
             bn_normalize_planes_kernel<<<stride_grid(planes * 256), 256, 0, st>>>(x, mean_out, std_inv_out, gamma, beta, y, planes, C, S);
@@ -366,38 +396,72 @@ int seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta, f
         e = cudaGetLastError();
     }
     if (sums) scratch_free(sums);
+    if (table) scratch_free(table);
+    if (status != SEERA_OK) return status;
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, "batchnorm_fwd");
 }
 
-int seera_batchnorm_bwd(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
-                        float *dgamma, float *dbeta, int N, int C, int S) {
+static int bn_bwd_impl(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
+                       float *dgamma, float *dbeta, int N, int C, int S, int cross) {
     SEERA_ENSURE();
     if (N < 1 || C < 1 || S < 1 || C > 65535 || !dy || !x || !mean || !std_inv || !gamma || !dx || !dgamma || !dbeta)
         return fail(SEERA_E_ARG, "batchnorm_bwd: bad argument");
     const long long total = (long long)N * C * S;
+    const int world = cross ? seera_dp_world() : 1;
     const int splits = bn_splits(N, C, S);
     float *p0 = (float *)scratch_alloc((size_t)2 * splits * C * sizeof(float));
     if (!p0) return SEERA_E_OOM;
     float *p1 = p0 + (size_t)splits * C;
+    float *all = nullptr;                          // [2C + 1]: the two sums and the element count over every rank's shard
     cudaStream_t st = rt().stream;
-    cudaError_t e = bn_reduce<2>(x, dy, nullptr, mean, std_inv, p0, p1, N, C, S, splits);
+    int status = SEERA_OK;
+    cudaError_t e = bn_reduce(x, dy, mean, std_inv, p0, p1, N, C, S, splits);
     if (e == cudaSuccess) {
         bn_finalize_bwd_kernel<<<(C + 255) / 256, 256, 0, st>>>(p0, p1, dbeta, dgamma, C, splits);
         count_launch();
         e = cudaGetLastError();
     }
-    if (e == cudaSuccess) {
+    if (e == cudaSuccess && world > 1) {
+        all = (float *)scratch_alloc((size_t)(2 * C + 1) * sizeof(float));
+        if (!all) { scratch_free(p0); return SEERA_E_OOM; }
+        bn_pack_sums_kernel<<<(C + 255) / 256, 256, 0, st>>>(dbeta, dgamma, all, C, (float)((long long)N * S));
+        count_launch();
+        e = cudaGetLastError();
+        if (e == cudaSuccess) status = seera_dp_allreduce(all, 2 * C + 1, 0);
+    }
+    if (e == cudaSuccess && status == SEERA_OK) {
+        const float *sb = all ? all : dbeta, *sg = all ? all + C : dgamma, *md = all ? all + 2 * C : nullptr;
+        const float M = (float)((long long)N * S);
         if (bn_planes_ok(S, x, dy, dx)) {
             const long long planes = (long long)N * C;
-            bn_dx_planes_kernel<<<stride_grid(planes * 256), 256, 0, st>>>(dy, x, mean, std_inv, gamma, dbeta, dgamma, dx, planes, C, S, (float)((long long)N * S));
+            bn_dx_planes_kernel<<<stride_grid(planes * 256), 256, 0, st>>>(dy, x, mean, std_inv, gamma, sb, sg, dx, planes, C, S, M, md);
         } else {
-            bn_dx_kernel<<<stride_grid(total), 256, 0, st>>>(dy, x, mean, std_inv, gamma, dbeta, dgamma, dx, total, C, S, (float)((long long)N * S));
+            bn_dx_kernel<<<stride_grid(total), 256, 0, st>>>(dy, x, mean, std_inv, gamma, sb, sg, dx, total, C, S, M, md);
         }
         count_launch();
         e = cudaGetLastError();
     }
     scratch_free(p0);
+    if (all) scratch_free(all);
+    if (status != SEERA_OK) return status;
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, "batchnorm_bwd");
+}
+
+int seera_batchnorm_fwd(const float *x, const float *gamma, const float *beta, float *running_mean, float *running_var, float *y,
+                        float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training) {
+    return bn_fwd_impl(x, gamma, beta, running_mean, running_var, y, mean_out, std_inv_out, N, C, S, momentum, eps, training, 0);
+}
+int seera_batchnorm_bwd(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
+                        float *dgamma, float *dbeta, int N, int C, int S) {
+    return bn_bwd_impl(dy, x, mean, std_inv, gamma, dx, dgamma, dbeta, N, C, S, 0);
+}
+int seera_batchnorm_fwd_sync(const float *x, const float *gamma, const float *beta, float *running_mean, float *running_var, float *y,
+                             float *mean_out, float *std_inv_out, int N, int C, int S, float momentum, float eps, int training) {
+    return bn_fwd_impl(x, gamma, beta, running_mean, running_var, y, mean_out, std_inv_out, N, C, S, momentum, eps, training, 1);
+}
+int seera_batchnorm_bwd_sync(const float *dy, const float *x, const float *mean, const float *std_inv, const float *gamma, float *dx,
+                             float *dgamma, float *dbeta, int N, int C, int S) {
+    return bn_bwd_impl(dy, x, mean, std_inv, gamma, dx, dgamma, dbeta, N, C, S, 1);
 }
 
 }  // extern "C"

@@ -197,6 +197,13 @@ PYBIND11_MODULE(seera_cuda, m) {
     m.def("batchnorm_bwd", [](uptr dy, uptr x, uptr mean, uptr si, uptr g, uptr dx, uptr dg, uptr db, int N, int C, int S) {
         ck(seera_batchnorm_bwd(P<const F>(dy), P<const F>(x), P<const F>(mean), P<const F>(si), P<const F>(g), P<F>(dx), P<F>(dg),
                                P<F>(db), N, C, S)); });
+    m.def("batchnorm_fwd_sync", [](uptr x, uptr g, uptr b, uptr rm, uptr rv, uptr y, uptr mean, uptr si, int N, int C, int S, float momentum,
+                              float eps, bool training) {
+        ck(seera_batchnorm_fwd_sync(P<const F>(x), P<const F>(g), P<const F>(b), P<F>(rm), P<F>(rv), P<F>(y), P<F>(mean), P<F>(si), N, C, S,
+                               momentum, eps, training ? 1 : 0)); });
+    m.def("batchnorm_bwd_sync", [](uptr dy, uptr x, uptr mean, uptr si, uptr g, uptr dx, uptr dg, uptr db, int N, int C, int S) {
+        ck(seera_batchnorm_bwd_sync(P<const F>(dy), P<const F>(x), P<const F>(mean), P<const F>(si), P<const F>(g), P<F>(dx), P<F>(dg),
+                               P<F>(db), N, C, S)); });
     m.def("concat_fwd", [](uptr a, uptr b, uptr out, int N, int n1, int n2) { ck(seera_concat_fwd(P<const F>(a), P<const F>(b), P<F>(out), N, n1, n2)); });
     m.def("concat_bwd", [](uptr dout, uptr da, uptr db, int N, int n1, int n2) { ck(seera_concat_bwd(P<const F>(dout), P<F>(da), P<F>(db), N, n1, n2)); });
     m.def("onehot_f32", [](uptr labels, uptr out, int n, int classes) { ck(seera_onehot_f32(P<const int>(labels), P<F>(out), n, classes)); });

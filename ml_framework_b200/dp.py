@@ -192,12 +192,17 @@ def update_in_buckets(optimizer, complete=None):
     return after
 
 
-def attach_nccl(model, target_buckets=3, optimizer=None):
+def attach_nccl(model, target_buckets=3, optimizer=None, sync_batchnorm=False):
     """Moves the model's gradient arena into memory registered with the communicator and installs the bucket hooks over
     the engine's collectives.  With `optimizer`, each bucket is updated on the communication stream right behind its sum
-    (`update_in_buckets`).  Returns the bucket list."""
+    (`update_in_buckets`).  `sync_batchnorm`: the model's BatchNorm layers take their statistics over all ranks' shards
+    (seera_batchnorm_fwd_sync / _bwd_sync) instead of each rank's own.  Returns the bucket list."""
     from . import seera_cuda as sc
     world = sc.dp_world()
+    if sync_batchnorm:
+        for layer in model.model:
+            if hasattr(layer, "sync") and hasattr(layer, "_rm"):
+                layer.sync = True
     ptr = sc.dp_alloc(4 * max(model.n_arena, 1))
     model.rehome_grads(ptr)
     arena = model.grads.main_ptr

@@ -557,11 +557,13 @@ class _BatchNorm(_ParamLayer):
     """Batch normalisation on the device (the reference computes it on the host even in its GPU path: Seera.py:511-623,
     Seera_init.py:870-921, Seera_Engine.py:381-415).  gamma / beta are the layer's `weights` / `bais` (as in the reference)
     and live in the model's parameter arena; the running statistics are device buffers, readable as NumPy arrays through
-    `running_mean` / `running_var`.  In a data-parallel run each rank normalises with the statistics of its own shard."""
+    `running_mean` / `running_var`.  In a data-parallel run each rank normalises with the statistics of its own shard, unless
+    `sync` is set (also by `dp.attach_nccl(..., sync_batchnorm=True)`): then the statistics, and the sums of the backward
+    formula, are those of all ranks' shards together, so that a sharded step equals the step on the joined batch."""
 
-    def __init__(self, num, momentum=0.1, eps=1e-5):
+    def __init__(self, num, momentum=0.1, eps=1e-5, sync=False):
         super().__init__()
-        self.momentum, self.eps, self.training = momentum, eps, True
+        self.momentum, self.eps, self.training, self.sync = momentum, eps, True, bool(sync)
         self._w_init = np.ones((num,), np.float32)
         self._b_init = np.zeros((num,), np.float32)
         self.weights = Tensor(self._w_init, is_leaf=True)
@@ -602,7 +604,8 @@ class _BatchNorm(_ParamLayer):
             S *= d
         g, b = self.weights, self.bais
         y, mean, si = _new(xv.shape), _new((C,)), _new((C,))
-        sc.batchnorm_fwd(xv.main_ptr, g.value.main_ptr, b.value.main_ptr, self._rm.main_ptr, self._rv.main_ptr, y.main_ptr,
+        fwd, bwd = (sc.batchnorm_fwd_sync, sc.batchnorm_bwd_sync) if self.sync else (sc.batchnorm_fwd, sc.batchnorm_bwd)
+        fwd(xv.main_ptr, g.value.main_ptr, b.value.main_ptr, self._rm.main_ptr, self._rv.main_ptr, y.main_ptr,
                          mean.main_ptr, si.main_ptr, N, C, S, float(self.momentum), float(self.eps), bool(self.training))
         out = Tensor(y)
         out._parents = (x, g, b)
@@ -610,8 +613,7 @@ class _BatchNorm(_ParamLayer):
         def backward(dy, need_dx=not x.is_leaf):
             dg, db = g._grad_target(), b._grad_target()
             dx = _new(xv.shape)
-            sc.batchnorm_bwd(dy.main_ptr, xv.main_ptr, mean.main_ptr, si.main_ptr, g.value.main_ptr, dx.main_ptr, dg.main_ptr,
-                             db.main_ptr, N, C, S)
+            bwd(dy.main_ptr, xv.main_ptr, mean.main_ptr, si.main_ptr, g.value.main_ptr, dx.main_ptr, dg.main_ptr, db.main_ptr, N, C, S)
             g._accumulate(dg)
             b._accumulate(db)
             hook = getattr(getattr(self, "_model", None), "_on_grad_ready", None)
@@ -625,8 +627,8 @@ class _BatchNorm(_ParamLayer):
 
 
 class BatchNorm1d(_BatchNorm):
-    def __init__(self, num_features, momentum=0.1, eps=1e-5):
-        super().__init__(num_features, momentum, eps)
+    def __init__(self, num_features, momentum=0.1, eps=1e-5, sync=False):
+        super().__init__(num_features, momentum, eps, sync)
         self.num_features = num_features
 
     def _shape_ok(self, shape):
@@ -638,8 +640,8 @@ class BatchNorm1d(_BatchNorm):
 
 
 class BatchNorm2d(_BatchNorm):
-    def __init__(self, num_channels, momentum=0.1, eps=1e-5):
-        super().__init__(num_channels, momentum, eps)
+    def __init__(self, num_channels, momentum=0.1, eps=1e-5, sync=False):
+        super().__init__(num_channels, momentum, eps, sync)
         self.num_channels = num_channels
 
     def _shape_ok(self, shape):

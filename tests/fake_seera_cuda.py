@@ -384,6 +384,13 @@ def batchnorm_bwd(dy, x, mean, si, g, dx, dg, db, N, C, S):
     _view(db, C)[:] = c
 
 
+# one rank in this stand-in: the cross-rank forms are the local ones
+batchnorm_fwd_sync = batchnorm_fwd
+batchnorm_bwd_sync = batchnorm_bwd
+def dp_world(): return 1
+def dp_rank(): return 0
+
+
 def concat_fwd(a, b, out, N, n1, n2):
     _count("concat_fwd")
     F(out, (N, n1 + n2))[:] = np.concatenate([F(a, (N, n1)), F(b, (N, n2))], axis=1)
