@@ -192,9 +192,18 @@ __global__ void __launch_bounds__(256) shadow_weight_kernel(const float *__restr
                                                             __nv_bfloat16 *__restrict__ d1, __nv_bfloat16 *__restrict__ d2, Enc enc) {
     long long total = (long long)O * taps * Ip;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    const bool small = total < (1ll << 31);       // 32-bit index arithmetic then (a 64-bit division is ~10x the instructions)
     for (long long e = tid; e < total; e += nthr) {
-        int i = (int)(e % Ip); long long t2 = e / Ip;
-        int tap = (int)(t2 % taps); int o = (int)(t2 / taps);
+        int i, tap, o;
+        if (small) {
+            const unsigned t2 = (unsigned)e / (unsigned)Ip;
+            i = (int)((unsigned)e - t2 * (unsigned)Ip);
+            o = (int)(t2 / (unsigned)taps);
+            tap = (int)(t2 - (unsigned)o * (unsigned)taps);
+        } else {
+            i = (int)(e % Ip); long long t2 = e / Ip;
+            tap = (int)(t2 % taps); o = (int)(t2 / taps);
+        }
         float v = i < I ? __ldg(Wt + o * so + i * si + (flip ? taps - 1 - tap : tap)) : 0.f;
         store_split1(v, NS, enc, d0 + e, d1 + e, d2 + e);
     }

@@ -65,12 +65,13 @@ enum { CLS_ACT = 0, CLS_WEIGHT = 1, CLS_GRAD = 2 };
 template <int NS>
 __global__ void __launch_bounds__(256) shadow_rows_kernel(const float *__restrict__ src, long long src_ld, int rows, int cols,
                                                           __nv_bfloat16 *__restrict__ d0, __nv_bfloat16 *__restrict__ d1,
-                                                          __nv_bfloat16 *__restrict__ d2, int ld, Enc enc) {
+                                                          __nv_bfloat16 *__restrict__ d2, int ld, Enc enc, FastDiv by_groups) {
     // one thread per 8 consecutive elements of a row; ld is a multiple of 8 so the 16-byte stores are aligned
     long long groups_per_row = ld >> 3, total = (long long)rows * groups_per_row;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    const bool small = total < (1ll << 31);       // then the row index is one multiply and a shift instead of a 64-bit division
     for (long long g = tid; g < total; g += nthr) {
-        int r = (int)(g / groups_per_row), c0 = (int)(g - (long long)r * groups_per_row) * 8;
+        int r = small ? by_groups.div((int)g) : (int)(g / groups_per_row), c0 = (int)(g - (long long)r * groups_per_row) * 8;
         const float *s = src + (long long)r * src_ld + c0;
         float v[8];
         if (c0 + 8 <= cols && ((reinterpret_cast<uintptr_t>(s) & 15) == 0)) {
@@ -121,9 +122,9 @@ inline int make_shadow(const float *src, int rows, int cols, int ns, Shadow &s, 
     int grid = stride_grid(groups);
     cudaStream_t st = rt().stream;
     ProfBytes pb(4.0 * rows * cols + 2.0 * ns * rows * s.ld, "shadow_rows");
-    if (ns == 1) shadow_rows_kernel<1><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc);
-    else if (ns == 2) shadow_rows_kernel<2><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc);
-    else shadow_rows_kernel<3><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc);
+    if (ns == 1) shadow_rows_kernel<1><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc, fast_div(s.ld / 8));
+    else if (ns == 2) shadow_rows_kernel<2><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc, fast_div(s.ld / 8));
+    else shadow_rows_kernel<3><<<grid, 256, 0, st>>>(src, cols, rows, cols, s.p[0], s.p[1], s.p[2], s.ld, s.enc, fast_div(s.ld / 8));
     count_launch();
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SEERA_OK : check_cuda(e, "shadow_rows");
@@ -509,13 +510,16 @@ __global__ void __launch_bounds__(256) tma_splitk_reduce_kernel(const float *__r
     if (dinv) scale *= __ldg(dinv);
     long long total = (long long)M * N;
     long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    const bool small = total < (1ll << 31);       // 32-bit index arithmetic then: the 64-bit division costs more than the loads
     for (long long i = tid; i < total; i += nthr) {
         float s = 0.f;
-        for (int z = 0; z < splits; z++) s += partial[(long long)z * total + i];
+#pragma unroll 4
+        for (int z = 0; z < splits; z++) s += __ldg(partial + (long long)z * total + i);
         s *= scale;
-        const int n = (int)(i % N);
+        const int m = small ? (int)((unsigned)i / (unsigned)N) : (int)(i / N);
+        const int n = (int)(i - (long long)m * N);
         if (bias) s += __ldg(bias + n);
-        cs((int)(i / N), n, epilogue_act(s, act));
+        cs(m, n, epilogue_act(s, act));
     }
 }
 
