@@ -98,8 +98,9 @@ __global__ void __launch_bounds__(256) act_bias_bwd_nchw_kernel(const float *__r
     const int cnt = (outer - s + splits - 1) / splits;
     if (vec) {
         const int q = inner >> 2;
+        const bool small = (long long)cnt * q < (1ll << 31);       // 32-bit division then
         for (long long j = threadIdx.x; j < (long long)cnt * q; j += blockDim.x) {
-            int k = (int)(j / q), i = (int)(j - (long long)k * q);
+            int k = small ? (int)((unsigned)j / (unsigned)q) : (int)(j / q), i = (int)(j - (long long)k * q);
             long long base = ((long long)(s + k * splits) * channels + c) * inner;
             float4 d = reinterpret_cast<const float4 *>(dy + base)[i], yy = reinterpret_cast<const float4 *>(y + base)[i], r;
             r.x = d.x * act_grad_from_out(yy.x, act); r.y = d.y * act_grad_from_out(yy.y, act);
@@ -108,8 +109,9 @@ __global__ void __launch_bounds__(256) act_bias_bwd_nchw_kernel(const float *__r
             acc += (r.x + r.y) + (r.z + r.w);
         }
     } else {
+        const bool small = (long long)cnt * inner < (1ll << 31);
         for (long long j = threadIdx.x; j < (long long)cnt * inner; j += blockDim.x) {
-            int k = (int)(j / inner), i = (int)(j - (long long)k * inner);
+            int k = small ? (int)((unsigned)j / (unsigned)inner) : (int)(j / inner), i = (int)(j - (long long)k * inner);
             long long at = ((long long)(s + k * splits) * channels + c) * inner + i;
             float r = dy[at] * act_grad_from_out(y[at], act);
             dz[at] = r;
