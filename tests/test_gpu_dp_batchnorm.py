@@ -54,6 +54,30 @@ for sync in (True, False):
             rel(model.predict(S.Tensor(X, is_leaf=True)).to_numpy(), gold["pred_eval"]))
     assert dp.replicas_differ_by(model) == 0.0
     worst[sync] = w
+    if sync:
+        # the same sharded step as ONE recorded graph (the layer's small sums over the ranks ride on the compute stream inside it):
+        # replays keep the replicas identical and match the same number of eager steps on a second model
+        from ml_framework_b200 import train
+        Xd, Yd = S.Tensor(X[half], is_leaf=True), S.Tensor(Y[half], is_leaf=True)
+        def one_step():
+            yp = model.forward(Xd)
+            loss = lossf(yp, Yd)
+            model.zero_grad()
+            S.autograd4nn(loss)
+            opt.step()
+            return loss
+        before = model.params.to_host_f32()[:model.n_arena].copy()
+        sc.graph_begin()
+        loss_t = one_step()
+        g = sc.graph_end()
+        for _ in range(2):
+            opt.advance()
+            sc.graph_launch(g)
+        sc.dp_wait_host(20000)
+        after = model.params.to_host_f32()[:model.n_arena].copy()
+        assert np.all(np.isfinite(after)) and not np.array_equal(before, after)
+        assert dp.replicas_differ_by(model) == 0.0
+        sc.graph_destroy(g)
 print("RESULT rank %%d sync %%.3e local %%.3e" %% (rank, worst[True], worst[False]), flush=True)
 dp.finalize()                                   # before the checks: a rank that raised would leave its peer waiting here
 assert worst[True] < 2e-4, worst
