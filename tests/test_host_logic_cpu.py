@@ -213,6 +213,26 @@ def test_batchnorm_layers_against_reference_golden(host, golden_dir):
     _bn_model_against_golden(host.seera, golden_dir, 2e-5)
 
 
+def test_batchnorm_with_cross_rank_statistics_is_the_plain_layer_on_one_rank(host, golden_dir):
+    """`sync=True` routes the layer through the cross-rank entries; with a single rank they are the plain ones, so the model
+    still reproduces the reference's golden (the two-rank case runs on two GPUs: tests/test_gpu_dp_batchnorm.py)."""
+    S = host.seera
+    plain1d, plain2d = S.BatchNorm1d, S.BatchNorm2d
+
+    class Sync1d(plain1d):
+        def __init__(self, *a, **k):
+            super().__init__(*a, sync=True, **k)
+
+    class Sync2d(plain2d):
+        def __init__(self, *a, **k):
+            super().__init__(*a, sync=True, **k)
+    S.BatchNorm1d, S.BatchNorm2d = Sync1d, Sync2d
+    try:
+        _bn_model_against_golden(S, golden_dir, 2e-5)
+    finally:
+        S.BatchNorm1d, S.BatchNorm2d = plain1d, plain2d
+
+
 @pytest.mark.parametrize("kind", ["adam", "sgd"])
 def test_checkpoint_with_optimizer_state_resumes_exactly(host, tmp_path, kind):
     """Two steps, save with the optimizer, load, one more step == three steps straight (weights bit-equal); a non-zero
